@@ -1,0 +1,459 @@
+/*
+ * w4a8_oracle.c -- CPU restatement of the reference W4A8 quantized-linear path.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker that the parity tests,
+ * the smoke test and the benchmark's CPU-baseline leg compare the CUDA library
+ * against.  Nothing in the shipped library links, imports or calls it.
+ *
+ * Parity status: PINNED.  Every function below is checked (tests/test_oracle_*.py)
+ * against the known answers held by the reference's own tests and against the
+ * reference's own CPU stages compiled from its sources (oracle/ref_glue.cpp),
+ * on seeded inputs whose outputs are committed under tests/golden/.
+ *
+ * Each function cites the reference file:line it restates (paths are relative
+ * to the reference project root).
+ *
+ * Plain C11, optional OpenMP for the integer contraction (the only O(M*K*N) part).
+ */
+#include <float.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define ORC_OK 0
+#define ORC_ERR_PARAM (-3) /* same value as RK_NPU_ERR_PARAM, include/rk_npu_common.h:30 */
+
+/* ------------------------------------------------------------------ binary16
+ * src/rk_npu_half_bits.h:8-27  (half -> float, exact, subnormals normalised,
+ * NaN payload kept) and :28-53 (float -> half, round to nearest even, overflow
+ * to infinity, values below half the smallest subnormal flush to signed zero). */
+float orc_half_to_float(uint16_t h)
+{
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    const uint32_t e = (h >> 10) & 31u;
+    uint32_t m = h & 1023u, bits;
+    if (e == 0) {
+        if (m == 0) {
+            bits = sign;
+        } else {
+            int shift = 0;
+            while (!(m & 1024u)) { m <<= 1; ++shift; }
+            bits = sign | (uint32_t)(127 - 14 - shift) << 23 | (m & 1023u) << 13;
+        }
+    } else if (e == 31) {
+        bits = sign | 0x7f800000u | m << 13;
+    } else {
+        bits = sign | (e + 112u) << 23 | m << 13;
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+uint16_t orc_float_to_half(float f)
+{
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    const uint32_t sign = (x >> 16) & 0x8000u, biased = (x >> 23) & 255u;
+    uint32_t man = x & 0x7fffffu;
+    if (biased == 255u)
+        return (uint16_t)(sign | 0x7c00u | (man ? ((man >> 13) | 0x200u) : 0u));
+    const int e = (int)biased - 127 + 15;
+    if (e >= 31)
+        return (uint16_t)(sign | 0x7c00u);
+    if (e <= 0) {
+        if (e < -10)
+            return (uint16_t)sign;
+        man |= 0x800000u;
+        const int shift = 14 - e;
+        uint32_t hm = man >> shift;
+        const uint32_t half_bit = 1u << (shift - 1);
+        if ((man & half_bit) && ((man & (half_bit - 1)) || (hm & 1u)))
+            ++hm;
+        return (uint16_t)(sign | hm);
+    }
+    uint32_t h = sign | (uint32_t)e << 10 | man >> 13;
+    if ((man & 0x1000u) && ((man & 0xfffu) || (h & 1u)))
+        ++h; /* a carry out of the mantissa correctly bumps the exponent */
+    return (uint16_t)h;
+}
+
+void orc_half_to_float_n(const uint16_t *src, float *dst, int64_t n)
+{
+    for (int64_t i = 0; i < n; ++i) dst[i] = orc_half_to_float(src[i]);
+}
+void orc_float_to_half_n(const float *src, uint16_t *dst, int64_t n)
+{
+    for (int64_t i = 0; i < n; ++i) dst[i] = orc_float_to_half(src[i]);
+}
+
+static inline float load_act(const void *A, int half, int64_t i)
+{
+    return half ? orc_half_to_float(((const uint16_t *)A)[i]) : ((const float *)A)[i];
+}
+
+/* --------------------------------------------------------- per-token scales
+ * src/rk_npu_w4a8_quant.cpp:52-85 (scales_impl): full-row max|x|, any NaN/Inf
+ * makes the call fail, s = max(maxabs/127, FLT_MIN) (1 for an all-zero row),
+ * inverse = 1/s with an IEEE division. */
+int orc_scales(const void *A, int half, int M, int K, float *scales, float *inverse)
+{
+    if (!A || M < 1 || K < 1 || !scales || !inverse) return ORC_ERR_PARAM;
+    int bad = 0;
+    for (int m = 0; m < M; ++m) {
+        float maximum = 0.f;
+        for (int k = 0; k < K; ++k) {
+            const float x = load_act(A, half, (int64_t)m * K + k);
+            if (!isfinite(x)) bad = 1;
+            const float a = fabsf(x);
+            if (a > maximum) maximum = a;
+        }
+        float s = 1.0f;
+        if (maximum != 0.f) {
+            s = maximum / 127.0f;
+            if (s < FLT_MIN) s = FLT_MIN;
+        }
+        scales[m] = s;
+        inverse[m] = 1.0f / s;
+    }
+    return bad ? ORC_ERR_PARAM : ORC_OK;
+}
+
+/* src/rk_npu_w4a8_quant.cpp:119-121: q = clamp(round_half_away(x * inverse), -127, 127).
+ * The product is rounded to float before rounding to an integer (two steps). */
+static inline int quant_code(float x, float inv)
+{
+    float r = roundf(x * inv);
+    if (r > 127.f) r = 127.f;
+    if (r < -127.f) r = -127.f;
+    return (int)r;
+}
+
+void orc_quantize(const void *A, int half, int M, int K, const float *inverse, int8_t *q)
+{
+    for (int m = 0; m < M; ++m)
+        for (int k = 0; k < K; ++k)
+            q[(int64_t)m * K + k] = (int8_t)quant_code(load_act(A, half, (int64_t)m * K + k), inverse[m]);
+}
+
+/* src/rk_npu_w4a8_quant.cpp:122 : the reference splits each int8 code into two
+ * signed int4 digits, high = q >> 4 and low = ((q & 15) ^ 8) read as a 4-bit
+ * two's complement number, so that q = 16*high + low + 8.  Kept here only so
+ * that tests can rebuild codes from the reference's packed buffers. */
+void orc_msd_split(int8_t q, int *high, int *low)
+{
+    const uint8_t u = (uint8_t)q;
+    const int h = u >> 4, l = (u & 15) ^ 8;
+    *high = h >= 8 ? h - 16 : h;
+    *low = l >= 8 ? l - 16 : l;
+}
+
+/* ------------------------------------------------------- integer contraction
+ * tests/test_w4a8.cpp:31-37 : acc[m,n] = sum_k q[m,k] * B[k,n] in 64-bit, then
+ * narrowed to int32 (the library's accumulator type, src/rk_npu_w4a8_output.cpp:70).
+ * This equals correction + sum over waves of (16*hi + lo) whenever no INT16
+ * partial saturates (src/rk_npu_w4a8_output.cpp:38-44, src/rk_npu_w4a8.cpp:236-242). */
+void orc_gemm_i32(const int8_t *q, const int8_t *B, int M, int K, int N, int32_t *acc)
+{
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m) {
+        int64_t *row = (int64_t *)calloc((size_t)N, sizeof(int64_t));
+        for (int k = 0; k < K; ++k) {
+            const int64_t a = q[(int64_t)m * K + k];
+            if (!a) continue;
+            const int8_t *b = B + (int64_t)k * N;
+            for (int n = 0; n < N; ++n) row[n] += a * b[n];
+        }
+        for (int n = 0; n < N; ++n) acc[(int64_t)m * N + n] = (int32_t)row[n];
+        free(row);
+    }
+}
+
+/* Same contraction restricted to a list of columns (the reference's sampled
+ * check: 17 evenly spaced columns, src/rk_npu_w4a8_tune_data.cpp:30-33). */
+void orc_gemm_i32_columns(const int8_t *q, const int8_t *B, int M, int K, int N,
+                          const int *columns, int count, int32_t *acc)
+{
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+        for (int c = 0; c < count; ++c) {
+            const int n = columns[c];
+            int64_t sum = 0;
+            for (int k = 0; k < K; ++k)
+                sum += (int64_t)q[(int64_t)m * K + k] * B[(int64_t)k * N + n];
+            acc[(int64_t)m * count + c] = (int32_t)sum;
+        }
+}
+
+/* ------------------------------------------------------------------ dequant
+ * src/rk_npu_w4a8_output.cpp:226-262 (w4a8_dequant) and :70-76 (combine8):
+ * y = (float(acc) * a_scale[m]) * w_scale[n], two roundings in that order, then
+ * one round-to-nearest-even cast when the output is binary16. */
+void orc_dequant(int M, int N, const int32_t *acc, const float *a_scale, const float *w_scale,
+                 int half, void *out)
+{
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            const float t = (float)acc[(int64_t)m * N + n] * a_scale[m];
+            const float y = t * w_scale[n];
+            if (half) ((uint16_t *)out)[(int64_t)m * N + n] = orc_float_to_half(y);
+            else ((float *)out)[(int64_t)m * N + n] = y;
+        }
+}
+
+/* ------------------------------------------------------------------- SwiGLU
+ * Two activations exist in the reference:
+ *   mode 0: src/rk_npu_w4a8_swiglu.cpp:71  y = (g / (1 + expf(-g))) * u
+ *           (what the reference computes when built for a non-ARM host);
+ *   mode 1: src/rk_npu_swiglu_fp32_neon.h:13-51, the degree-7 polynomial the
+ *           reference uses on its production target: the argument -g is clamped
+ *           to [-80, 80], n = floor(x*log2(e) + 0.5) with one fused multiply-add,
+ *           two fused subtractions of n*ln2 (hi, lo), Horner with fused steps from
+ *           1/5040 down to 1, 2^n rebuilt from exponent bits, the denominator
+ *           1 + p*2^n as a separate multiply then add, an IEEE division, and
+ *           g < -80 mapped to -0.  Restated here with fmaf so every rounding is
+ *           the same as the vector code's. */
+float orc_silu_expf(float g) { return g / (1.f + expf(-g)); }
+
+float orc_silu_poly(float g)
+{
+    float x = -g;
+    if (x > 80.f) x = 80.f;
+    if (x < -80.f) x = -80.f;
+    const float n = floorf(fmaf(x, 1.4426950408889634f, 0.5f));
+    float r = fmaf(-n, 0.693145751953125f, x);
+    r = fmaf(-n, 1.428606765330187e-6f, r);
+    float p = 1.f / 5040.f;
+    p = fmaf(p, r, 1.f / 720.f);
+    p = fmaf(p, r, 1.f / 120.f);
+    p = fmaf(p, r, 1.f / 24.f);
+    p = fmaf(p, r, 1.f / 6.f);
+    p = fmaf(p, r, 0.5f);
+    p = fmaf(p, r, 1.f);
+    p = fmaf(p, r, 1.f);
+    const int32_t e = ((int32_t)n + 127) << 23;
+    float power;
+    memcpy(&power, &e, 4);
+    volatile float scaled = p * power; /* separate multiply: no contraction into the add */
+    const float d = 1.f + scaled;
+    return g < -80.f ? -0.f : g / d;
+}
+
+/* src/rk_npu_w4a8_swiglu.cpp:12-91 (finish_swiglu): the accumulator holds
+ * [gate(F), up(F)] columns; both are dequantised exactly as in orc_dequant, the
+ * activation is applied to gate, multiplied by up, stored as compact [M,F] fp32;
+ * row_max_bits[m] = max over the row of (bits(y) & 0x7fffffff) when requested. */
+void orc_swiglu(int M, int F, const int32_t *acc, const float *a_scale, const float *w_scale,
+                int mode, float *middle, uint32_t *row_max_bits)
+{
+    const int N = 2 * F;
+    for (int m = 0; m < M; ++m) {
+        uint32_t maximum = 0;
+        for (int f = 0; f < F; ++f) {
+            const float g = ((float)acc[(int64_t)m * N + f] * a_scale[m]) * w_scale[f];
+            const float u = ((float)acc[(int64_t)m * N + F + f] * a_scale[m]) * w_scale[F + f];
+            const float s = mode ? orc_silu_poly(g) : orc_silu_expf(g);
+            volatile float y = s * u;
+            middle[(int64_t)m * F + f] = y;
+            uint32_t bits;
+            float yy = y;
+            memcpy(&bits, &yy, 4);
+            bits &= 0x7fffffffu;
+            if (bits > maximum) maximum = bits;
+        }
+        if (row_max_bits) row_max_bits[m] = maximum;
+    }
+}
+
+/* src/rk_npu_w4a8_quant.cpp:145-161 (w4a8_finish_scales): turn the collected
+ * magnitude bit patterns into scales; any pattern >= +inf (0x7f800000) fails. */
+int orc_finish_scales(int M, const uint32_t *row_max_bits, float *scales, float *inverse)
+{
+    for (int m = 0; m < M; ++m) {
+        const uint32_t bits = row_max_bits[m];
+        if (bits >= 0x7f800000u) return ORC_ERR_PARAM;
+        float maximum;
+        memcpy(&maximum, &bits, 4);
+        float s = 1.f;
+        if (maximum != 0.f) {
+            s = maximum / 127.f;
+            if (s < FLT_MIN) s = FLT_MIN;
+        }
+        scales[m] = s;
+        inverse[m] = 1.f / s;
+    }
+    return ORC_OK;
+}
+
+/* ------------------------------------------------------------ complete calls
+ * src/rk_npu_w4a8.cpp:98-151 (run_locked) for one linear: scan, quantise, contract,
+ * dequantise.  acc_out (optional) receives the int32 accumulators. */
+int orc_linear(const void *A, int half, int M, int K, int N, const int8_t *B, const float *w_scale,
+               void *out, int32_t *acc_out, float *scales_out)
+{
+    float *s = (float *)malloc(sizeof(float) * (size_t)M * 2);
+    int8_t *q = (int8_t *)malloc((size_t)M * K);
+    int32_t *acc = acc_out ? acc_out : (int32_t *)malloc(sizeof(int32_t) * (size_t)M * N);
+    int rc = orc_scales(A, half, M, K, s, s + M);
+    if (!rc) {
+        orc_quantize(A, half, M, K, s + M, q);
+        orc_gemm_i32(q, B, M, K, N, acc);
+        orc_dequant(M, N, acc, s, w_scale, half, out);
+        if (scales_out) memcpy(scales_out, s, sizeof(float) * (size_t)M);
+    }
+    if (!acc_out) free(acc);
+    free(q);
+    free(s);
+    return rc;
+}
+
+/* src/rk_npu_w4a8.cpp:354-380 (rk_npu_w4a8_run_ffn_f32): gate/up projection with the
+ * fused SwiGLU epilogue collecting row maxima, scales finished from those maxima
+ * (no rescan), down projection quantising `middle` with the reused scales.
+ * Returns ORC_ERR_PARAM for non-finite input or non-finite middle (in which case
+ * the down projection is not evaluated). Optional outputs may be NULL. */
+int orc_ffn(const float *A, int M, int K, int F, int N, const int8_t *B_gate_up,
+            const float *scale_gate_up, const int8_t *B_down, const float *scale_down, int mode,
+            float *middle, float *C, int32_t *acc_gate_up, int32_t *acc_down, float *scales_down_in)
+{
+    const int N2 = 2 * F;
+    float *s = (float *)malloc(sizeof(float) * (size_t)M * 4);
+    uint32_t *maxima = (uint32_t *)malloc(sizeof(uint32_t) * (size_t)M);
+    int8_t *q = (int8_t *)malloc((size_t)M * (K > F ? K : F));
+    int32_t *acc1 = acc_gate_up ? acc_gate_up : (int32_t *)malloc(sizeof(int32_t) * (size_t)M * N2);
+    int32_t *acc2 = acc_down ? acc_down : (int32_t *)malloc(sizeof(int32_t) * (size_t)M * N);
+    int rc = orc_scales(A, 0, M, K, s, s + M);
+    if (!rc) {
+        orc_quantize(A, 0, M, K, s + M, q);
+        orc_gemm_i32(q, B_gate_up, M, K, N2, acc1);
+        orc_swiglu(M, F, acc1, s, scale_gate_up, mode, middle, maxima);
+        rc = orc_finish_scales(M, maxima, s + 2 * M, s + 3 * M);
+    }
+    if (!rc) {
+        orc_quantize(middle, 0, M, F, s + 3 * M, q);
+        orc_gemm_i32(q, B_down, M, F, N, acc2);
+        orc_dequant(M, N, acc2, s + 2 * M, scale_down, 0, C);
+        if (scales_down_in) memcpy(scales_down_in, s + 2 * M, sizeof(float) * (size_t)M);
+    }
+    if (!acc_down) free(acc2);
+    if (!acc_gate_up) free(acc1);
+    free(q);
+    free(maxima);
+    free(s);
+    return rc;
+}
+
+/* -------------------------------------------------------------- weight side
+ * src/rk_npu_w4a8.cpp:229-242: scales must be finite and > 0; codes must lie in
+ * [-8, 7]; correction[n] = 8 * sum_k B[k,n]. Returns ORC_ERR_PARAM otherwise. */
+int orc_weight_check(int K, int N, const int8_t *B, const float *w_scale, int32_t *correction)
+{
+    for (int n = 0; n < N; ++n) {
+        if (!isfinite(w_scale[n]) || !(w_scale[n] > 0)) return ORC_ERR_PARAM;
+        if (correction) correction[n] = 0;
+    }
+    for (int k = 0; k < K; ++k)
+        for (int n = 0; n < N; ++n) {
+            const int v = B[(int64_t)k * N + n];
+            if (v < -8 || v > 7) return ORC_ERR_PARAM;
+            if (correction) correction[n] += 8 * v;
+        }
+    return ORC_OK;
+}
+
+/* src/rk_npu_i4_bounds.cpp:9-69 (bound_i4_weights).  For a fixed partition of K
+ * into tiles of t*32 elements, a column is safe when, inside every tile,
+ *   P = sum(w >= 0 ? 7*w : -8*w) <= 32767  and  Q = sum(w >= 0 ? 8*w : -7*w) <= 32768,
+ * i.e. no int4 x int4 partial can leave INT16.  requested == 0 examines every
+ * t in 1..min(64, ceil(K/32)); a positive request examines that tile (and the
+ * optional smaller fallback) only.  Outputs: the largest safe tile, the maxima
+ * of P and Q seen for it, and a bit mask with bit (t-1) set for every safe t.
+ * Columns are walked in slabs of 128 and a tile stops being examined (and its
+ * maxima stop growing) at the first unsafe column, exactly as the reference. */
+int orc_bound_i4_weights(int K, int N, const int8_t *B, int requested, int fallback,
+                         int *k_tile, int64_t *positive, int64_t *negative, uint64_t *safe_tiles)
+{
+    if (!B || K < 1 || K > INT32_MAX / 64 || N < 1 || N > INT32_MAX - 63 || requested < 0 ||
+        requested > 2048 || requested % 32 || fallback < 0 || fallback % 32 ||
+        (fallback && fallback >= requested))
+        return ORC_ERR_PARAM;
+    const int blocks = (K + 31) / 32;
+    const int limit = requested ? requested / 32 : (blocks < 64 ? blocks : 64);
+    int safe[65] = {0};
+    int64_t max_pos[65] = {0}, max_neg[65] = {0};
+    for (int t = 1; t <= limit; ++t) safe[t] = !requested || t == limit || t * 32 == fallback;
+    const int slab = 128;
+    int64_t *pos = (int64_t *)malloc(sizeof(int64_t) * (size_t)(blocks + 1) * slab * 2);
+    int64_t *neg = pos + (size_t)(blocks + 1) * slab;
+    for (int n0 = 0; n0 < N; n0 += slab) {
+        const int width = N - n0 < slab ? N - n0 : slab;
+        memset(pos, 0, sizeof(int64_t) * (size_t)width);
+        memset(neg, 0, sizeof(int64_t) * (size_t)width);
+        for (int b = 0; b < blocks; ++b) {
+            int64_t *p = pos + (size_t)(b + 1) * width, *q = neg + (size_t)(b + 1) * width;
+            memcpy(p, p - width, sizeof(int64_t) * (size_t)width);
+            memcpy(q, q - width, sizeof(int64_t) * (size_t)width);
+            const int kend = (b + 1) * 32 < K ? (b + 1) * 32 : K;
+            for (int k = b * 32; k < kend; ++k) {
+                const int8_t *row = B + (int64_t)k * N + n0;
+                for (int n = 0; n < width; ++n) {
+                    const int w = row[n];
+                    if (w < -8 || w > 7) { free(pos); return ORC_ERR_PARAM; }
+                    p[n] += w >= 0 ? 7 * w : -8 * w;
+                    q[n] += w >= 0 ? 8 * w : -7 * w;
+                }
+            }
+        }
+        for (int t = 1; t <= limit; ++t) {
+            if (!safe[t]) continue;
+            for (int b = 0; b < blocks && safe[t]; b += t) {
+                const int e = b + t < blocks ? b + t : blocks;
+                for (int n = 0; n < width; ++n) {
+                    const int64_t hi = pos[(size_t)e * width + n] - pos[(size_t)b * width + n];
+                    const int64_t lo = neg[(size_t)e * width + n] - neg[(size_t)b * width + n];
+                    if (hi > max_pos[t]) max_pos[t] = hi;
+                    if (lo > max_neg[t]) max_neg[t] = lo;
+                    if (hi > 32767 || lo > 32768) { safe[t] = 0; break; }
+                }
+            }
+        }
+    }
+    free(pos);
+    uint64_t mask = 0;
+    for (int t = 1; t <= limit; ++t)
+        if (safe[t]) mask |= (uint64_t)1 << (t - 1);
+    for (int t = limit; t >= 1; --t)
+        if (safe[t]) {
+            *k_tile = t * 32;
+            *positive = max_pos[t];
+            *negative = max_neg[t];
+            *safe_tiles = mask;
+            return ORC_OK;
+        }
+    return ORC_ERR_PARAM;
+}
+
+/* src/rk_npu_autotune_common.cpp:83-89 (tune::Hash): 64-bit FNV-1a; integers are
+ * mixed as eight little-endian bytes.  src/rk_npu_w4a8.cpp:275-277: the weight
+ * fingerprint hashes K, N, the K*N code bytes and the N fp32 scales. */
+uint64_t orc_fnv_bytes(uint64_t h, const void *p, size_t n)
+{
+    const uint8_t *b = (const uint8_t *)p;
+    for (size_t i = 0; i < n; ++i) { h ^= b[i]; h *= 1099511628211ull; }
+    return h;
+}
+uint64_t orc_fnv_mix(uint64_t h, uint64_t v)
+{
+    for (int i = 0; i < 8; ++i) { const uint8_t b = (uint8_t)(v >> (8 * i)); h = orc_fnv_bytes(h, &b, 1); }
+    return h;
+}
+uint64_t orc_weight_fingerprint(int K, int N, const int8_t *B, const float *w_scale)
+{
+    uint64_t h = 1469598103934665603ull;
+    h = orc_fnv_mix(h, (uint64_t)(int64_t)K);
+    h = orc_fnv_mix(h, (uint64_t)(int64_t)N);
+    h = orc_fnv_bytes(h, B, (size_t)K * N);
+    h = orc_fnv_bytes(h, w_scale, (size_t)N * sizeof(float));
+    return h;
+}
