@@ -1,0 +1,73 @@
+/*
+ * rknpu_b200_ext.h -- entry points that exist only in the B200 library.
+ *
+ * The original project's W4A8 interface is blocking and takes host tensors.  A caller
+ * whose activations already live in GPU memory (an inference engine running a
+ * decoder layer on its own CUDA stream) needs neither the copies nor the host wait,
+ * so the same operators are also exposed in an enqueue form: device pointers in, work
+ * queued on the caller's stream, nothing allocated, nothing waited for.  None of
+ * these has a counterpart in the original project.
+ */
+#ifndef RKNPU_B200_EXT_H
+#define RKNPU_B200_EXT_H
+
+#include "rknpu_b200_w4a8.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* CUDA ordinal the context runs on; -1 for NULL or an offline context. */
+int rk_npu_b200_device(const rk_npu_ctx *ctx);
+
+/* A context with no GPU behind it, for tools that inspect or write tuning caches and
+ * query memory requirements on a machine without a device.  driver_version is the value
+ * the cache key should carry.  Only the tuning-cache, profile and *_query functions
+ * accept it; rk_npu_iommu_domain_create returns NULL for it.  Close with rk_npu_close. */
+rk_npu_ctx *rk_npu_b200_open_offline(uint32_t driver_version);
+
+/* Queue one W4A8 linear on `cuda_stream` (a cudaStream_t; NULL = the legacy default
+ * stream).  dA / dC are device pointers on the context's GPU with the shapes of the
+ * blocking calls.  Returns after queuing.  The workspace must not be used by another
+ * call until the queued work has finished.  Argument errors are reported as in the
+ * blocking calls; a non-finite activation is only known once the work has run: call
+ * rk_npu_b200_w4a8_finish after synchronising. */
+int rk_npu_b200_w4a8_enqueue_f32(rk_npu_w4a8_workspace *workspace, const rk_npu_w4a8_weights *weights,
+                                 const float *dA, float *dC, void *cuda_stream);
+int rk_npu_b200_w4a8_enqueue_f16(rk_npu_w4a8_workspace *workspace, const rk_npu_w4a8_weights *weights,
+                                 const uint16_t *dA, uint16_t *dC, void *cuda_stream);
+int rk_npu_b200_w4a8_enqueue_swiglu_f32(rk_npu_w4a8_workspace *workspace, const rk_npu_w4a8_weights *weights,
+                                        const float *dA, float *dMiddle, void *cuda_stream);
+/* gate/up -> SwiGLU -> down in one queue; a non-finite middle makes the down kernels
+ * return without writing and is reported by rk_npu_b200_w4a8_finish(down). */
+int rk_npu_b200_w4a8_enqueue_ffn_f32(rk_npu_w4a8_workspace *gate_up, const rk_npu_w4a8_weights *gate_up_weights,
+                                     rk_npu_w4a8_workspace *down, const rk_npu_w4a8_weights *down_weights,
+                                     const float *dA, float *dMiddle, float *dC, void *cuda_stream);
+
+/* After the caller has synchronised the stream: RK_NPU_OK, RK_NPU_ERR_PARAM (non-finite
+ * activation or middle in the last queued call) or RK_NPU_ERR_SUBMIT (a bounded device
+ * wait ran out).  Clears the recorded status. */
+int rk_npu_b200_w4a8_finish(rk_npu_w4a8_workspace *workspace);
+
+/* Diagnostic: the same linear as rk_npu_w4a8_run_f32 / _f16 (activation_is_f16 selects
+ * the input type) but the exact int32 sums sum_k q*B are returned in acc[M,N] instead of
+ * the dequantised output.  Blocking; host or device pointers. */
+int rk_npu_b200_w4a8_run_acc_i32(rk_npu_w4a8_workspace *workspace, const rk_npu_w4a8_weights *weights,
+                                 const void *A, int activation_is_f16, int32_t *acc);
+
+/* Diagnostic: the per-token scales and int8 codes [M,K] the last call on this workspace
+ * quantised its activations to (host pointers; either may be NULL). Blocking. */
+int rk_npu_b200_w4a8_last_quant(rk_npu_w4a8_workspace *workspace, float *scales, int8_t *codes);
+
+/* Scheduling override for experiments and tuning: variant 0 = automatic, 1 = the
+ * mma.sync kernel, 2 = the tcgen05 kernel; split_k 0 = automatic, else 1, 2, 4 or 8.
+ * Returns RK_NPU_ERR_PARAM when the workspace geometry cannot run the request. */
+int rk_npu_b200_w4a8_set_schedule(rk_npu_w4a8_workspace *workspace, int variant, int split_k);
+
+/* Kernels this workspace has launched since creation (for launch accounting). */
+uint64_t rk_npu_b200_w4a8_launch_count(const rk_npu_w4a8_workspace *workspace);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RKNPU_B200_EXT_H */

@@ -1,0 +1,181 @@
+"""ctypes declarations of the library's C ABI (include/rknpu_b200_w4a8.h, include/rknpu_b200_ext.h).
+
+The structures below have the field order and types of the C structs one for one, so
+Python code reads like a C caller of the original rk_npu_w4a8 interface.  Loading fails
+loudly when the shared library has not been built; there is no fallback implementation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "librk_npu_matmul_b200.so"
+
+RK_NPU_OK = 0
+RK_NPU_ERR_OPEN = -1
+RK_NPU_ERR_IOCTL = -2
+RK_NPU_ERR_PARAM = -3
+RK_NPU_ERR_NOMEM = -4
+RK_NPU_ERR_SUBMIT = -5
+RK_NPU_ERR_BUSY = -6
+RK_NPU_ERR_DOMAIN = -7
+RK_NPU_ERR_IO = -8
+RK_NPU_ERR_CACHE_MISS = -9
+
+RK_NPU_W4A8_SERIAL, RK_NPU_W4A8_PIPELINED, RK_NPU_W4A8_CHAIN = 0, 1, 2
+RK_NPU_W4A8_INPUT_NATIVE, RK_NPU_W4A8_INPUT_PANEL8 = 0, 1
+RK_NPU_W4A8_REDUCE_CPU, RK_NPU_W4A8_REDUCE_NPU = 0, 1
+RK_NPU_W4A8_F32, RK_NPU_W4A8_F16 = 0, 1
+
+
+class DomainMemoryStats(C.Structure):
+    _fields_ = [("live_bytes", C.c_uint64), ("peak_bytes", C.c_uint64), ("creates", C.c_uint64),
+                ("destroys", C.c_uint64)]
+
+
+class I4WeightConfig(C.Structure):
+    _fields_ = [("K", C.c_int), ("N", C.c_int), ("k_tile", C.c_int)]
+
+
+class I4MemoryInfo(C.Structure):
+    _fields_ = [("packed_weight_bytes", C.c_uint64), ("input_bytes", C.c_uint64), ("partial_bytes", C.c_uint64),
+                ("control_bytes", C.c_uint64), ("wave_count", C.c_uint32), ("tasks_per_wave", C.c_uint32)]
+
+
+class W4A8Config(C.Structure):
+    _fields_ = [("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("m_tile", C.c_int), ("k_tile", C.c_int),
+                ("n_tile", C.c_int), ("npu_core_mask", C.c_uint32), ("timeout_ms", C.c_uint32),
+                ("pipeline", C.c_int), ("cpu_threads", C.c_int)]
+
+
+class W4A8MemoryInfo(C.Structure):
+    _fields_ = [("backend", I4MemoryInfo), ("weight_metadata_bytes", C.c_uint64), ("cpu_scratch_bytes", C.c_uint64)]
+
+
+class W4A8Options(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("input_layout", C.c_int), ("reduce_backend", C.c_int)]
+
+
+class W4A8MemoryInfoEx(C.Structure):
+    _fields_ = [("base", W4A8MemoryInfo), ("reduction_output_bytes", C.c_uint64),
+                ("reduction_weight_bytes", C.c_uint64), ("reduction_control_bytes", C.c_uint64),
+                ("workspace_bytes", C.c_uint64), ("effective_reduce_backend", C.c_int)]
+
+
+class W4A8Timings(C.Structure):
+    _fields_ = [("activation_scan_us", C.c_double), ("quant_pack_us", C.c_double), ("sync_us", C.c_double),
+                ("submit_us", C.c_double), ("reduce_us", C.c_double), ("dequant_us", C.c_double),
+                ("total_us", C.c_double)]
+
+
+class W4A8FfnTimings(C.Structure):
+    _fields_ = [("gate_up", W4A8Timings), ("down", W4A8Timings), ("total_us", C.c_double)]
+
+
+class W4A8WeightInfo(C.Structure):
+    _fields_ = [("config", I4WeightConfig), ("safe_k_tile", C.c_int), ("multiplier", C.c_double),
+                ("bound_relaxed", C.c_int)]
+
+
+class W4A8AutotuneConfig(C.Structure):
+    _fields_ = [("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("activation_type", C.c_int),
+                ("allowed_npu_core_mask", C.c_uint32), ("allowed_cpu_core_mask", C.c_uint64), ("warmup", C.c_int),
+                ("loops", C.c_int), ("repeats", C.c_int), ("timeout_ms", C.c_uint32), ("verbose", C.c_int),
+                ("required_k_tile", C.c_int), ("k_tile_multiplier", C.c_double)]
+
+
+class W4A8Strategy(C.Structure):
+    _fields_ = [("config", W4A8Config), ("activation_type", C.c_int), ("cpu_core_mask", C.c_uint64),
+                ("weights", W4A8WeightInfo), ("weight_fingerprint", C.c_uint64), ("tuning_revision", C.c_uint32),
+                ("input_us", C.c_double), ("npu_us", C.c_double), ("sync_us", C.c_double), ("output_us", C.c_double),
+                ("total_us", C.c_double), ("jitter_pct", C.c_double), ("robust_us", C.c_double)]
+
+
+class W4A8StrategyEx(C.Structure):
+    _fields_ = [("base", W4A8Strategy), ("execution", W4A8Options)]
+
+
+_P = C.c_void_p
+_SIGNATURES = {
+    # context, domains
+    "rk_npu_open": (_P, [C.c_char_p]),
+    "rk_npu_close": (None, [_P]),
+    "rk_npu_iommu_domain_create": (_P, [_P, C.c_uint32]),
+    "rk_npu_iommu_domain_free": (None, [_P]),
+    "rk_npu_iommu_domain_id": (C.c_uint32, [_P]),
+    "rk_npu_iommu_domain_memory_stats": (C.c_int, [_P, C.POINTER(DomainMemoryStats)]),
+    "rk_npu_strerror": (C.c_char_p, [C.c_int]),
+    # accounting
+    "rk_npu_i4_weights_memory_query": (C.c_int, [C.POINTER(I4WeightConfig), C.POINTER(C.c_uint64)]),
+    "rk_npu_w4a8_config_init": (None, [C.POINTER(W4A8Config), C.c_int, C.c_int, C.c_int]),
+    "rk_npu_w4a8_options_init": (None, [C.POINTER(W4A8Options)]),
+    "rk_npu_w4a8_memory_query": (C.c_int, [C.POINTER(W4A8Config), C.POINTER(W4A8MemoryInfo)]),
+    "rk_npu_w4a8_memory_query_ex": (C.c_int, [C.POINTER(W4A8Config), C.POINTER(W4A8Options),
+                                              C.POINTER(W4A8MemoryInfoEx)]),
+    # weights, workspaces
+    "rk_npu_w4a8_weights_create": (_P, [_P, C.POINTER(I4WeightConfig), _P, _P]),
+    "rk_npu_w4a8_weights_free": (None, [_P]),
+    "rk_npu_w4a8_weights_query": (C.c_int, [_P, C.POINTER(W4A8WeightInfo)]),
+    "rk_npu_w4a8_workspace_create": (_P, [_P, C.POINTER(W4A8Config)]),
+    "rk_npu_w4a8_workspace_create_ex": (_P, [_P, C.POINTER(W4A8Config), C.POINTER(W4A8Options)]),
+    "rk_npu_w4a8_workspace_free": (None, [_P]),
+    # runs
+    "rk_npu_w4a8_run_f32": (C.c_int, [_P, _P, _P, _P, C.POINTER(W4A8Timings)]),
+    "rk_npu_w4a8_run_f16": (C.c_int, [_P, _P, _P, _P, C.POINTER(W4A8Timings)]),
+    "rk_npu_w4a8_run_swiglu_f32": (C.c_int, [_P, _P, _P, _P, C.POINTER(W4A8Timings)]),
+    "rk_npu_w4a8_run_ffn_f32": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(W4A8FfnTimings)]),
+    # tuning cache
+    "rk_npu_w4a8_tuning_profile_from_weights": (_P, [_P]),
+    "rk_npu_w4a8_tuning_profile_free": (None, [_P]),
+    "rk_npu_w4a8_tuning_profile_fingerprint": (C.c_uint64, [_P]),
+    "rk_npu_w4a8_autotune_config_init": (None, [C.POINTER(W4A8AutotuneConfig), C.c_int, C.c_int, C.c_int]),
+    "rk_npu_w4a8_autotune_cache_load_profile_ex": (C.c_int, [_P, C.POINTER(W4A8AutotuneConfig), _P, C.c_char_p,
+                                                             C.POINTER(W4A8StrategyEx), C.POINTER(W4A8StrategyEx)]),
+    "rk_npu_w4a8_autotune_cache_load": (C.c_int, [_P, C.POINTER(W4A8AutotuneConfig), _P, _P, C.c_char_p,
+                                                  C.POINTER(W4A8Strategy), C.POINTER(W4A8Strategy)]),
+    "rk_npu_w4a8_autotune_cache_save": (C.c_int, [_P, C.POINTER(W4A8AutotuneConfig), _P, _P, C.c_char_p,
+                                                  C.POINTER(W4A8Strategy), C.POINTER(W4A8Strategy)]),
+    "rk_npu_w4a8_autotune_cache_load_ex": (C.c_int, [_P, C.POINTER(W4A8AutotuneConfig), _P, _P, C.c_char_p,
+                                                     C.POINTER(W4A8StrategyEx), C.POINTER(W4A8StrategyEx)]),
+    "rk_npu_w4a8_autotune_cache_save_ex": (C.c_int, [_P, C.POINTER(W4A8AutotuneConfig), _P, _P, C.c_char_p,
+                                                     C.POINTER(W4A8StrategyEx), C.POINTER(W4A8StrategyEx)]),
+    "rk_npu_w4a8_weights_create_tuned": (_P, [_P, C.POINTER(W4A8Strategy), _P, _P]),
+    "rk_npu_w4a8_weights_create_tuned_ex": (_P, [_P, C.POINTER(W4A8StrategyEx), _P, _P]),
+    "rk_npu_w4a8_workspace_create_tuned_ex": (_P, [_P, C.POINTER(W4A8StrategyEx)]),
+    # B200 extensions
+    "rk_npu_b200_device": (C.c_int, [_P]),
+    "rk_npu_b200_open_offline": (_P, [C.c_uint32]),
+    "rk_npu_b200_w4a8_enqueue_f32": (C.c_int, [_P, _P, _P, _P, _P]),
+    "rk_npu_b200_w4a8_enqueue_f16": (C.c_int, [_P, _P, _P, _P, _P]),
+    "rk_npu_b200_w4a8_enqueue_swiglu_f32": (C.c_int, [_P, _P, _P, _P, _P]),
+    "rk_npu_b200_w4a8_enqueue_ffn_f32": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P]),
+    "rk_npu_b200_w4a8_finish": (C.c_int, [_P]),
+    "rk_npu_b200_w4a8_run_acc_i32": (C.c_int, [_P, _P, _P, C.c_int, _P]),
+    "rk_npu_b200_w4a8_last_quant": (C.c_int, [_P, _P, _P]),
+    "rk_npu_b200_w4a8_set_schedule": (C.c_int, [_P, C.c_int, C.c_int]),
+    "rk_npu_b200_w4a8_launch_count": (C.c_uint64, [_P]),
+}
+
+_lib = None
+
+
+def declared_symbols():
+    """Names of every entry point the headers declare."""
+    return sorted(_SIGNATURES)
+
+
+def load() -> C.CDLL:
+    """Load the built library and attach the prototypes. Raises if it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(f"{LIB_PATH} is not built: run `python -c 'import __graft_entry__ as g; g.build()'` "
+                           "(nvcc, sm_100a). There is no CPU fallback.")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib

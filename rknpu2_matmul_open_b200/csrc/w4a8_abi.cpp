@@ -1,0 +1,971 @@
+// w4a8_abi.cpp -- the C ABI of the W4A8 path: context and domains, geometry
+// validation and memory accounting, weight preparation, workspaces and the run entry
+// points.  Host C++ only; every tensor operation is a CUDA kernel (w4a8_kernels.cu,
+// w4a8_gemm_tc.cu).  There is no CPU compute path: without a GPU rk_npu_open fails.
+//
+// Behaviour mirrors the reference operator front-end src/rk_npu_w4a8.cpp (validation
+// order :83-94, BUSY guard :70-81, run :98-159, accounting :169-207, FFN :354-380) and
+// the backend geometry rules src/rk_npu_i4_plan.cpp:14-87.
+#include "w4a8_host.h"
+#include <algorithm>
+#include <cerrno>
+#include <chrono>
+#include <climits>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <memory>
+#include <new>
+#include <vector>
+
+using namespace rkb200;
+
+namespace {
+using Clock = std::chrono::steady_clock;
+double elapsed_us(Clock::time_point t) { return std::chrono::duration<double, std::micro>(Clock::now() - t).count(); }
+
+bool env_flag(const char* name, bool fallback)
+{
+    const char* v = std::getenv(name);
+    if (!v || !*v) return fallback;
+    return !(v[0] == '0' && v[1] == 0);
+}
+
+// ------------------------------------------------------------------ geometry rules
+constexpr int K_TILE_MAX = 2048;
+constexpr int N_TILE_MAX = 8128;
+constexpr int COMMAND_WORDS = 112;   // register words per task of the original device
+constexpr int TASK_BYTES = 40;
+constexpr int REDUCE_COMMAND_WORDS = 68;
+
+bool valid_shape(int K, int N) { return K > 0 && K <= INT32_MAX / 1024 && N > 0; }
+
+bool weight_key_valid(int K, int N, int k_tile)
+{
+    return K > 0 && K <= INT32_MAX / 64 && N > 0 && N <= INT_MAX - 63 && k_tile >= 32 && k_tile <= K_TILE_MAX &&
+           k_tile % 32 == 0;
+}
+
+struct Backend {   // the physical (two rows per token) problem the original device saw
+    int M, N, K, m_tile, k_tile, n_tile;
+    uint32_t mask, timeout_ms;
+    int pipeline, threads;
+};
+
+int panel_entries(int k)
+{
+    const int tail = k % 128;
+    return 8 * (k / 128) + (tail == 0 ? 0 : tail <= 32 ? 2 : tail <= 64 ? 4 : 8);
+}
+int panel_banks(int rows, int k) { return (rows / 8 * panel_entries(k) * 64 + 32767) / 32768; }
+int panel_rows(int remaining, int tile, bool panel8)
+{
+    const int rows = std::min(remaining, tile);
+    return panel8 && rows >= 8 ? rows / 8 * 8 : rows;
+}
+
+bool backend_valid(const Backend& c, bool panel8)
+{
+    if (!weight_key_valid(c.K, c.N, c.k_tile) || c.M < 1 || c.m_tile < 1) return false;
+    if (panel8 && (c.m_tile % 8 || c.m_tile > 512 || c.m_tile < 8 || c.M % 2 ||
+                   panel_banks(panel_rows(c.M, c.m_tile, true), align_up(std::min(c.K, c.k_tile), 32)) > 8))
+        return false;
+    const int cores = __builtin_popcount(c.mask);
+    return c.m_tile <= (panel8 ? 512 : 128) && c.n_tile >= 64 && c.n_tile <= N_TILE_MAX && c.n_tile % 64 == 0 &&
+           (c.mask == 1 || c.mask == 2 || c.mask == 4 || c.mask == 3 || c.mask == 7) && align_up(c.N, 64) / 64 >= cores &&
+           c.timeout_ms > 0 && (c.pipeline == 0 || c.pipeline == 1) && c.threads >= 1 && c.threads <= 4;
+}
+
+int weight_bytes_query(int K, int N, int k_tile, uint64_t& bytes)
+{
+    if (!weight_key_valid(K, N, k_tile)) return RK_NPU_ERR_PARAM;
+    bytes = uint64_t(align_up(K, 32)) * align_up(N, 64) / 2;
+    return bytes > UINT32_MAX ? RK_NPU_ERR_NOMEM : RK_NPU_OK;
+}
+
+struct Tile { int m0, m, n0, n, logical_n; };
+
+// Column partition over the selected cores, then N tiles, then M panels
+// (src/rk_npu_i4_plan.cpp:34-55).  Only used for accounting and validity.
+std::vector<Tile> plan_tiles(const Backend& c, bool panel8)
+{
+    std::vector<Tile> tiles;
+    const int cores = __builtin_popcount(c.mask), blocks = align_up(c.N, 64) / 64;
+    int n0 = 0;
+    for (int core = 0; core < cores; ++core) {
+        const int end = n0 + (blocks / cores + (core < blocks % cores)) * 64;
+        while (n0 < end) {
+            const int n = std::min(c.n_tile, end - n0);
+            for (int m0 = 0; m0 < c.M;) {
+                const int m = panel_rows(c.M - m0, c.m_tile, panel8);
+                tiles.push_back({m0, m, n0, n, std::max(0, std::min(n, c.N - n0))});
+                m0 += m;
+            }
+            n0 += n;
+        }
+    }
+    return tiles;
+}
+
+int backend_query(const Backend& c, bool panel8, rk_npu_i4_memory_info& out)
+{
+    if (!backend_valid(c, panel8)) return RK_NPU_ERR_PARAM;
+    out = {};
+    int rc = weight_bytes_query(c.K, c.N, c.k_tile, out.packed_weight_bytes);
+    if (rc) return rc;
+    out.wave_count = uint32_t((c.K + c.k_tile - 1) / c.k_tile);
+    const uint64_t slots = std::min(out.wave_count, 2u);
+    out.input_bytes = slots * uint64_t(c.M) * align_up(std::min(c.K, c.k_tile), 32) / 2;
+    out.partial_bytes = slots * uint64_t(c.M) * align_up(c.N, 64) * 2;
+    const int cores = __builtin_popcount(c.mask), blocks = align_up(c.N, 64) / 64;
+    uint64_t n_tiles = 0;
+    for (int i = 0; i < cores; ++i) {
+        const int cols = (blocks / cores + (i < blocks % cores)) * 64;
+        n_tiles += uint64_t((cols + c.n_tile - 1) / c.n_tile);
+    }
+    const uint64_t remainder = uint64_t(c.M % c.m_tile);
+    const uint64_t panels = !panel8 ? (uint64_t(c.M) + c.m_tile - 1) / c.m_tile
+                                    : uint64_t(c.M) / c.m_tile + (remainder >= 8) + (remainder % 8 != 0);
+    const uint64_t tasks = n_tiles * panels;
+    if (tasks > uint64_t(INT_MAX / COMMAND_WORDS) || out.input_bytes / slots > UINT32_MAX ||
+        out.partial_bytes / slots > UINT32_MAX)
+        return RK_NPU_ERR_NOMEM;
+    out.tasks_per_wave = uint32_t(tasks);
+    out.control_bytes = uint64_t(out.wave_count) * tasks * (COMMAND_WORDS * 8 + TASK_BYTES);
+    return RK_NPU_OK;
+}
+
+int chain_query(const Backend& c, bool panel8, rk_npu_i4_memory_info& info)   // src/rk_npu_w4a8_chain.cpp:49-58
+{
+    int rc = backend_query(c, panel8, info);
+    if (rc) return rc;
+    const uint64_t tasks = uint64_t(info.tasks_per_wave) * info.wave_count;
+    const uint64_t input = uint64_t(c.M) * align_up(c.K, 32) / 2;
+    const uint64_t stride = uint64_t(c.M) * align_up(c.N, 64) * 2;
+    if (tasks > uint64_t(INT_MAX / COMMAND_WORDS) || input > UINT32_MAX || stride > UINT32_MAX / info.wave_count)
+        return RK_NPU_ERR_NOMEM;
+    info.input_bytes = input;
+    info.partial_bytes = stride * info.wave_count;
+    return RK_NPU_OK;
+}
+
+int npu_reduce_query(const Backend& c, bool panel8, rk_npu_w4a8_memory_info_ex& info)   // src/rk_npu_w4a8_npu_reduce.cpp:90-137
+{
+    const int waves = (c.K + c.k_tile - 1) / c.k_tile;
+    if (waves > 31) return RK_NPU_ERR_PARAM;
+    if (uint64_t(c.M) * align_up(c.N, 64) * 2 * waves > UINT32_MAX) return RK_NPU_ERR_NOMEM;
+    int limit = 512;
+    while (limit * 64 * (waves + 1) > 11 * 32768) limit /= 2;
+    uint64_t bytes = 0, guard = 256 * 1024, parts = 0;
+    for (const auto& t : plan_tiles(c, panel8)) {
+        if (t.m % 2 || t.m0 % 2 || t.n % 64) return RK_NPU_ERR_PARAM;
+        const int storage = t.m * t.n / 16;
+        if (storage > 4096) return RK_NPU_ERR_PARAM;
+        guard = std::max(guard, uint64_t(t.m) * t.n * 2 * waves);
+        for (int r = 0; r < storage; r += limit) {
+            const int rows = std::min(limit, storage - r);
+            ++parts;
+            bytes += uint64_t(align_up(rows, 4)) * 64;
+        }
+    }
+    if (parts < uint64_t(__builtin_popcount(c.mask))) return RK_NPU_ERR_PARAM;
+    if (parts > uint64_t(INT_MAX / REDUCE_COMMAND_WORDS)) return RK_NPU_ERR_NOMEM;
+    info.base.backend.partial_bytes = uint64_t(c.M) * align_up(c.N, 64) * 2 * waves + guard;
+    info.reduction_output_bytes = bytes + 256 * 1024;
+    info.reduction_weight_bytes = uint64_t(waves) * 512;
+    info.reduction_control_bytes = parts * (REDUCE_COMMAND_WORDS * 8 + TASK_BYTES);
+    if (info.base.backend.partial_bytes > UINT32_MAX || info.reduction_output_bytes > UINT32_MAX ||
+        info.reduction_control_bytes > UINT32_MAX)
+        return RK_NPU_ERR_NOMEM;
+    return RK_NPU_OK;
+}
+
+int options_decode(const rk_npu_w4a8_options* opt, int M, bool& panel8, bool& npu)
+{
+    panel8 = false;
+    npu = false;
+    if (!opt) return RK_NPU_OK;
+    if (opt->struct_size != sizeof(*opt) ||
+        (opt->input_layout != RK_NPU_W4A8_INPUT_NATIVE && opt->input_layout != RK_NPU_W4A8_INPUT_PANEL8) ||
+        (opt->reduce_backend != RK_NPU_W4A8_REDUCE_CPU && opt->reduce_backend != RK_NPU_W4A8_REDUCE_NPU))
+        return RK_NPU_ERR_PARAM;
+    panel8 = opt->input_layout == RK_NPU_W4A8_INPUT_PANEL8;
+    npu = opt->reduce_backend == RK_NPU_W4A8_REDUCE_NPU && M > 16;
+    return RK_NPU_OK;
+}
+
+int backend_from(const rk_npu_w4a8_config& cfg, bool panel8, Backend& out)
+{
+    if (!valid_shape(cfg.K, cfg.N) || cfg.M < 1 || cfg.M > INT_MAX / 2 || cfg.m_tile < 1 ||
+        cfg.m_tile > (panel8 ? 256 : 64) || cfg.pipeline < RK_NPU_W4A8_SERIAL || cfg.pipeline > RK_NPU_W4A8_CHAIN)
+        return RK_NPU_ERR_PARAM;
+    out = {cfg.M * 2, cfg.N, cfg.K, cfg.m_tile * 2, cfg.k_tile, cfg.n_tile, cfg.npu_core_mask, cfg.timeout_ms,
+           cfg.pipeline == RK_NPU_W4A8_CHAIN ? 0 : cfg.pipeline, cfg.cpu_threads};
+    return RK_NPU_OK;
+}
+
+// ------------------------------------------------------------------ locking
+class WorkspaceLock {
+public:
+    explicit WorkspaceLock(rk_npu_w4a8_workspace& ws) : flag_(ws.busy), held_(!flag_.test_and_set(std::memory_order_acquire)) {}
+    ~WorkspaceLock() { if (held_) flag_.clear(std::memory_order_release); }
+    explicit operator bool() const { return held_; }
+    WorkspaceLock(const WorkspaceLock&) = delete;
+    WorkspaceLock& operator=(const WorkspaceLock&) = delete;
+private:
+    std::atomic_flag& flag_;
+    bool held_;
+};
+
+int validate(const rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const void* A, const void* C, bool swiglu)
+{
+    if (!ws || !w || !A || !C || A == C || (swiglu && (ws->npu_reduce || ws->config.N % 64))) return RK_NPU_ERR_PARAM;
+    if (w->ctx_id != ws->ctx_id || w->domain_id != ws->domain_id) return RK_NPU_ERR_DOMAIN;
+    const auto& wc = w->info.config;
+    if (wc.K != ws->config.K || wc.N != ws->config.N || wc.k_tile != ws->config.k_tile) return RK_NPU_ERR_PARAM;
+    return RK_NPU_OK;
+}
+
+bool on_device(const void* p)
+{
+    cudaPointerAttributes a{};
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+// ------------------------------------------------------------------ kernel sequencing
+int pick_split(const rk_npu_w4a8_workspace& ws, int tiles, int token_chunks)
+{
+    if (ws.split_override) return ws.split_override;
+    const int sms = ws.domain->ctx->sm_count;
+    int split = 1;
+    while (split < 8 && (long long)tiles * token_chunks * split * 2 <= (long long)(5 * sms) / 2 && ws.KB / (split * 2) >= 2)
+        split *= 2;
+    return split;
+}
+
+struct Call {
+    rk_npu_w4a8_workspace* ws;
+    const rk_npu_w4a8_weights* w;
+    const void* dA;        // device activations
+    void* dOut;            // device output
+    bool half;
+    int epi;
+    uint32_t* rowmax_out;  // SwiGLU row maxima to collect (device) or nullptr
+    const uint32_t* rowmax_in;  // scales come from these instead of a scan
+    cudaStream_t stream;
+    cudaEvent_t* events;   // nullptr or three events: start, after quantise, after GEMM
+};
+
+int enqueue(const Call& c)
+{
+    auto& ws = *c.ws;
+    const auto& cfg = ws.config;
+    const bool pdl = env_flag("RK_NPU_B200_PDL", true);
+    if (c.events) cudaEventRecord(c.events[0], c.stream);
+    QuantParams q{};
+    q.A = c.dA;
+    q.Xq = ws.codes;
+    q.scales = ws.scales;
+    q.inverse = ws.inverse;
+    q.rowmax_zero = c.rowmax_out;
+    q.rowmax = c.rowmax_in;
+    q.status = ws.status;
+    q.host_flag = nullptr;
+    q.M = cfg.M;
+    q.K = cfg.K;
+    q.Kp = ws.KB * KBLOCK;
+    q.T = ws.T;
+    q.half = c.half ? 1 : 0;
+    if (launch_quantize(q, c.stream, pdl) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    if (c.events) cudaEventRecord(c.events[1], c.stream);
+
+    GemmParams g{};
+    g.Wp = c.w->packed;
+    g.Xq = ws.codes;
+    g.sx = ws.scales;
+    g.sw = c.w->scales;
+    g.out = c.dOut;
+    g.rowmax = c.rowmax_out;
+    g.status = ws.status;
+    g.M = cfg.M;
+    g.N = cfg.N;
+    g.K = cfg.K;
+    g.KB = ws.KB;
+    g.NG = c.w->NG;
+    g.T = ws.T;
+    g.F = c.epi == EPI_SWIGLU ? cfg.N / 2 : 0;
+    g.epi = c.epi;
+    g.timeout_ns = (unsigned long long)cfg.timeout_ms * 1000000ull;
+    cudaError_t err;
+    if (ws.TC == 0) {
+        g.split = 1;
+        err = launch_gemm_tc(g, c.stream, pdl);
+    } else {
+        const int tiles = c.epi == EPI_SWIGLU ? (g.F + 63) / 64 : g.NG / 4;
+        g.split = pick_split(ws, tiles, (cfg.M + ws.TC - 1) / ws.TC);
+        err = launch_gemm_mma(g, ws.TC, c.stream, pdl);
+    }
+    if (err != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+    if (c.events) cudaEventRecord(c.events[2], c.stream);
+    ws.launches.fetch_add(2, std::memory_order_relaxed);
+    return RK_NPU_OK;
+}
+
+float event_us(cudaEvent_t a, cudaEvent_t b)
+{
+    float ms = 0;
+    if (cudaEventElapsedTime(&ms, a, b) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return ms * 1000.f;
+}
+
+int status_to_rc(rk_npu_w4a8_workspace& ws, cudaStream_t stream)
+{
+    const Status s = *ws.host_status;
+    if (s.device_error) {
+        cudaMemsetAsync(&ws.status->device_error, 0, sizeof(int), stream);
+        cudaStreamSynchronize(stream);
+        return RK_NPU_ERR_SUBMIT;
+    }
+    return s.bad_input ? RK_NPU_ERR_PARAM : RK_NPU_OK;
+}
+
+// One blocking projection; the caller holds the workspace.
+int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const void* A, void* C, bool half, int epi,
+               rk_npu_w4a8_timings* metrics)
+{
+    const auto start = Clock::now();
+    const auto& cfg = ws->config;
+    rk_npu_w4a8_timings t{};
+    if (cudaSetDevice(ws->domain->ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    const size_t in_bytes = size_t(cfg.M) * cfg.K * (half ? 2 : 4);
+    const int out_cols = epi == EPI_SWIGLU ? cfg.N / 2 : cfg.N;
+    const size_t out_bytes = size_t(cfg.M) * out_cols * (epi == EPI_F16 ? 2 : 4);
+    const bool a_dev = on_device(A), c_dev = on_device(C);
+    cudaStream_t s = ws->stream;
+    const void* dA = A;
+    void* dC = C;
+    auto copy_start = Clock::now();
+    if (!a_dev) {
+        if (cudaMemcpyAsync(ws->stage_in, A, in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+        dA = ws->stage_in;
+    }
+    if (!c_dev) dC = ws->stage_out;
+    t.sync_us += elapsed_us(copy_start);
+    Call call{ws, w, dA, dC, half, epi, nullptr, nullptr, s, metrics ? ws->events : nullptr};
+    int rc = enqueue(call);
+    if (rc) { cudaStreamSynchronize(s); return rc; }
+    copy_start = Clock::now();
+    if (!c_dev) cudaMemcpyAsync(C, dC, out_bytes, cudaMemcpyDeviceToHost, s);
+    cudaMemcpyAsync(ws->host_status, ws->status, sizeof(Status), cudaMemcpyDeviceToHost, s);
+    if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+    t.sync_us += elapsed_us(copy_start);
+    rc = status_to_rc(*ws, s);
+    if (metrics) {
+        t.activation_scan_us = event_us(ws->events[0], ws->events[1]);
+        t.submit_us = rc ? 0.0 : event_us(ws->events[1], ws->events[2]);
+        t.total_us = elapsed_us(start);
+        *metrics = t;
+    }
+    return rc;
+}
+
+int run(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const void* A, void* C, bool half, int epi,
+        rk_npu_w4a8_timings* metrics)
+{
+    const int rc = validate(ws, w, A, C, epi == EPI_SWIGLU);
+    if (rc) return rc;
+    WorkspaceLock lock(*ws);
+    if (!lock) return RK_NPU_ERR_BUSY;
+    try { return run_locked(ws, w, A, C, half, epi, metrics); } catch (...) { return RK_NPU_ERR_PARAM; }
+}
+
+void workspace_destroy(rk_npu_w4a8_workspace* ws)
+{
+    if (!ws) return;
+    auto* d = ws->domain;
+    if (d) cudaSetDevice(d->ctx->device);
+    if (ws->stream) cudaStreamSynchronize(ws->stream);
+    if (ws->codes) device_free(d, ws->codes, ws->codes_bytes);
+    if (ws->scales) device_free(d, ws->scales, sizeof(float) * 2 * ws->config.M);
+    if (ws->rowmax) device_free(d, ws->rowmax, sizeof(uint32_t) * ws->config.M);
+    if (ws->status) device_free(d, ws->status, sizeof(Status));
+    if (ws->stage_in) device_free(d, ws->stage_in, ws->stage_in_bytes);
+    if (ws->stage_out) device_free(d, ws->stage_out, ws->stage_out_bytes);
+    if (ws->host_status) cudaFreeHost(ws->host_status);
+    for (auto& e : ws->events) if (e) cudaEventDestroy(e);
+    if (ws->stream) cudaStreamDestroy(ws->stream);
+    if (d) domain_release(d);
+    delete ws;
+}
+} // namespace
+
+// ================================================================== domains, context
+namespace rkb200 {
+void domain_retain(rk_npu_iommu_domain* d) { if (d) d->refs.fetch_add(1, std::memory_order_relaxed); }
+void domain_release(rk_npu_iommu_domain* d)
+{
+    if (d && d->refs.fetch_sub(1, std::memory_order_acq_rel) == 1) delete d;
+}
+int device_alloc(rk_npu_iommu_domain* d, void** ptr, size_t bytes)
+{
+    *ptr = nullptr;
+    if (!bytes) bytes = 16;
+    if (cudaMalloc(ptr, bytes) != cudaSuccess) { cudaGetLastError(); *ptr = nullptr; return RK_NPU_ERR_NOMEM; }
+    std::lock_guard<std::mutex> g(d->lock);
+    d->stats.live_bytes += bytes;
+    d->stats.peak_bytes = std::max(d->stats.peak_bytes, d->stats.live_bytes);
+    ++d->stats.creates;
+    return RK_NPU_OK;
+}
+void device_free(rk_npu_iommu_domain* d, void* ptr, size_t bytes)
+{
+    if (!ptr) return;
+    if (!bytes) bytes = 16;
+    cudaFree(ptr);
+    std::lock_guard<std::mutex> g(d->lock);
+    d->stats.live_bytes -= std::min<uint64_t>(bytes, d->stats.live_bytes);
+    ++d->stats.destroys;
+}
+} // namespace rkb200
+
+extern "C" rk_npu_ctx* rk_npu_open(const char* dev)
+{
+    int device = -1;
+    const char* spec = (dev && *dev) ? dev : std::getenv("RK_NPU_CUDA_DEVICE");
+    if (spec && *spec) {
+        const char* digits = std::strncmp(spec, "cuda:", 5) == 0 ? spec + 5 : spec;
+        char* end = nullptr;
+        errno = 0;
+        const long v = std::strtol(digits, &end, 10);
+        if (errno || end == digits || *end || v < 0 || v > 1023) { errno = ENODEV; return nullptr; }
+        device = int(v);
+    }
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count < 1) { cudaGetLastError(); errno = ENODEV; return nullptr; }
+    if (device < 0 && cudaGetDevice(&device) != cudaSuccess) { cudaGetLastError(); errno = ENODEV; return nullptr; }
+    if (device >= count) { errno = ENODEV; return nullptr; }
+    cudaDeviceProp prop{};
+    if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+        cudaGetLastError();
+        errno = ENODEV;
+        return nullptr;
+    }
+    if (prop.major != 10) { errno = ENODEV; return nullptr; }   // kernels are built for sm_100a only
+    auto* ctx = new (std::nothrow) rk_npu_ctx;
+    if (!ctx) { errno = ENOMEM; return nullptr; }
+    ctx->device = device;
+    ctx->id = uint64_t(reinterpret_cast<uintptr_t>(ctx));
+    int driver = 0;
+    cudaDriverGetVersion(&driver);
+    ctx->driver_version = uint32_t(driver);
+    ctx->sm_count = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        cudaGetLastError();
+        delete ctx;
+        errno = ENODEV;
+        return nullptr;
+    }
+    return ctx;
+}
+
+extern "C" rk_npu_ctx* rk_npu_b200_open_offline(uint32_t driver_version)
+{
+    auto* ctx = new (std::nothrow) rk_npu_ctx;
+    if (!ctx) { errno = ENOMEM; return nullptr; }
+    ctx->device = -1;
+    ctx->id = uint64_t(reinterpret_cast<uintptr_t>(ctx));
+    ctx->driver_version = driver_version;
+    return ctx;
+}
+
+extern "C" void rk_npu_close(rk_npu_ctx* ctx)
+{
+    if (!ctx) return;
+    if (ctx->device < 0) { delete ctx; return; }
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) { cudaStreamSynchronize(ctx->stream); cudaStreamDestroy(ctx->stream); }
+    delete ctx;
+}
+
+extern "C" int rk_npu_b200_device(const rk_npu_ctx* ctx) { return ctx ? ctx->device : -1; }
+
+extern "C" rk_npu_iommu_domain* rk_npu_iommu_domain_create(rk_npu_ctx* ctx, uint32_t domain_id)
+{
+    if (!ctx || ctx->device < 0 || domain_id >= RK_NPU_IOMMU_DOMAIN_COUNT) { errno = EINVAL; return nullptr; }
+    auto* d = new (std::nothrow) rk_npu_iommu_domain;
+    if (!d) { errno = ENOMEM; return nullptr; }
+    d->ctx = ctx;
+    d->id = domain_id;
+    return d;
+}
+extern "C" void rk_npu_iommu_domain_free(rk_npu_iommu_domain* domain) { domain_release(domain); }
+extern "C" uint32_t rk_npu_iommu_domain_id(const rk_npu_iommu_domain* domain) { return domain ? domain->id : 0; }
+extern "C" int rk_npu_iommu_domain_memory_stats(const rk_npu_iommu_domain* domain, rk_npu_domain_memory_stats* stats)
+{
+    if (!domain || !stats) return RK_NPU_ERR_PARAM;
+    auto* d = const_cast<rk_npu_iommu_domain*>(domain);
+    std::lock_guard<std::mutex> g(d->lock);
+    *stats = d->stats;
+    return RK_NPU_OK;
+}
+
+extern "C" const char* rk_npu_strerror(int code)
+{
+    switch (code) {
+    case RK_NPU_OK: return "ok";
+    case RK_NPU_ERR_OPEN: return "could not open the device";
+    case RK_NPU_ERR_IOCTL: return "device runtime call failed";
+    case RK_NPU_ERR_PARAM: return "bad argument";
+    case RK_NPU_ERR_NOMEM: return "buffer too small or allocation failed";
+    case RK_NPU_ERR_SUBMIT: return "device job failed or timed out";
+    case RK_NPU_ERR_BUSY: return "workspace is already running";
+    case RK_NPU_ERR_DOMAIN: return "context or domain mismatch";
+    case RK_NPU_ERR_IO: return "file I/O failed";
+    case RK_NPU_ERR_CACHE_MISS: return "tuning cache miss";
+    default: return "unknown error";
+    }
+}
+
+// ================================================================== configuration and accounting
+extern "C" void rk_npu_w4a8_config_init(rk_npu_w4a8_config* cfg, int M, int N, int K)
+{
+    if (!cfg) return;
+    *cfg = {};
+    cfg->M = M; cfg->N = N; cfg->K = K;
+    cfg->m_tile = 64; cfg->k_tile = 480; cfg->n_tile = 1024;
+    cfg->npu_core_mask = 1; cfg->timeout_ms = 500;
+    cfg->pipeline = RK_NPU_W4A8_PIPELINED; cfg->cpu_threads = 1;
+}
+extern "C" void rk_npu_w4a8_options_init(rk_npu_w4a8_options* options)
+{
+    if (options) *options = {uint32_t(sizeof(*options)), RK_NPU_W4A8_INPUT_NATIVE, RK_NPU_W4A8_REDUCE_CPU};
+}
+extern "C" int rk_npu_i4_weights_memory_query(const rk_npu_i4_weight_config* cfg, uint64_t* bytes)
+{
+    if (!cfg || !bytes) return RK_NPU_ERR_PARAM;
+    return weight_bytes_query(cfg->K, cfg->N, cfg->k_tile, *bytes);
+}
+extern "C" int rk_npu_w4a8_memory_query_ex(const rk_npu_w4a8_config* cfg, const rk_npu_w4a8_options* options,
+                                           rk_npu_w4a8_memory_info_ex* out)
+{
+    if (!cfg || !out) return RK_NPU_ERR_PARAM;
+    bool panel8, npu;
+    int rc = options_decode(options, cfg->M, panel8, npu);
+    if (rc) return rc;
+    Backend inner{};
+    rc = backend_from(*cfg, panel8, inner);
+    if (rc) return rc;
+    rk_npu_w4a8_memory_info_ex info{};
+    info.effective_reduce_backend = npu ? RK_NPU_W4A8_REDUCE_NPU : RK_NPU_W4A8_REDUCE_CPU;
+    if (cfg->pipeline == RK_NPU_W4A8_CHAIN) {
+        if (npu) return RK_NPU_ERR_PARAM;
+        rc = chain_query(inner, panel8, info.base.backend);
+    } else {
+        rc = backend_query(inner, panel8, info.base.backend);
+    }
+    if (rc) return rc;
+    info.base.weight_metadata_bytes = uint64_t(cfg->N) * 8;
+    info.base.cpu_scratch_bytes = uint64_t(cfg->M) * 8;
+    if (npu) {
+        try { rc = npu_reduce_query(inner, panel8, info); } catch (...) { return RK_NPU_ERR_NOMEM; }
+        if (rc) return rc;
+    } else {
+        info.base.cpu_scratch_bytes += uint64_t(cfg->M) * uint64_t(align_up64(cfg->N, 64)) * 4;
+        if (cfg->N % 64 == 0) info.base.cpu_scratch_bytes += (uint64_t(cfg->M) + 16) * cfg->cpu_threads * 4;
+    }
+    info.workspace_bytes = info.base.backend.input_bytes + info.base.backend.partial_bytes +
+                           info.base.backend.control_bytes + info.base.cpu_scratch_bytes +
+                           info.reduction_output_bytes + info.reduction_weight_bytes + info.reduction_control_bytes;
+    *out = info;
+    return RK_NPU_OK;
+}
+extern "C" int rk_npu_w4a8_memory_query(const rk_npu_w4a8_config* cfg, rk_npu_w4a8_memory_info* out)
+{
+    if (!out) return RK_NPU_ERR_PARAM;
+    rk_npu_w4a8_memory_info_ex info{};
+    const int rc = rk_npu_w4a8_memory_query_ex(cfg, nullptr, &info);
+    if (!rc) *out = info.base;
+    return rc;
+}
+
+// ================================================================== weights
+rk_npu_w4a8_weights* rkb200::create_weights(rk_npu_iommu_domain* domain, const rk_npu_w4a8_weight_info& info,
+                                            const int8_t* B, const float* scales, const Profile* profile)
+{
+    const auto& key = info.config;
+    if (!domain || !domain->ctx || !B || !scales || !valid_shape(key.K, key.N)) return nullptr;
+    uint64_t reference_bytes = 0;
+    if (weight_bytes_query(key.K, key.N, key.k_tile, reference_bytes)) return nullptr;
+    std::unique_ptr<rk_npu_w4a8_weights> w(new (std::nothrow) rk_npu_w4a8_weights);
+    if (!w) return nullptr;
+    if (profile) {
+        w->profile = *profile;
+    } else {
+        // Explicit-k_tile factories still capture the full proof and the identity.
+        rk_npu_w4a8_autotune_config c;
+        rk_npu_w4a8_autotune_config_init(&c, 1, key.N, key.K);
+        c.required_k_tile = 0;
+        c.k_tile_multiplier = info.multiplier;
+        if (make_profile(c, B, scales, w->profile)) return nullptr;
+    }
+    for (int n = 0; n < key.N; ++n)
+        if (!std::isfinite(scales[n]) || !(scales[n] > 0)) return nullptr;
+    // An explicit tile above the universal 480 must be certified by the weights
+    // unless the caller's policy relaxed the bound (src/rk_npu_i4_plan.cpp:95-99).
+    if (key.k_tile > 480 && !info.bound_relaxed && !w->profile.certified(key.k_tile)) {
+        WeightBound b;
+        if (bound_weights(key.K, key.N, B, key.k_tile, b)) return nullptr;
+    }
+    auto* ctx = domain->ctx;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return nullptr;
+    w->info = info;
+    w->KB = (key.K + KBLOCK - 1) / KBLOCK;
+    w->NG = align_up((key.N + GROUP - 1) / GROUP, 4);
+    w->packed_bytes = size_t(w->NG) * (size_t(w->KB) * 4) * 512;
+    w->scale_bytes = size_t(w->NG) * GROUP * sizeof(float);
+    w->domain = domain;
+    w->ctx_id = ctx->id;
+    w->domain_id = domain->id;
+    domain_retain(domain);
+    auto fail = [&]() -> rk_npu_w4a8_weights* {
+        if (w->packed) device_free(domain, w->packed, w->packed_bytes);
+        if (w->scales) device_free(domain, w->scales, w->scale_bytes);
+        domain_release(domain);
+        return nullptr;
+    };
+    if (device_alloc(domain, reinterpret_cast<void**>(&w->packed), w->packed_bytes)) return fail();
+    if (device_alloc(domain, reinterpret_cast<void**>(&w->scales), w->scale_bytes)) return fail();
+    int8_t* codes = nullptr;
+    int* error = nullptr;
+    const size_t code_bytes = size_t(key.K) * key.N;
+    bool ok = cudaMalloc(reinterpret_cast<void**>(&codes), code_bytes) == cudaSuccess &&
+              cudaMalloc(reinterpret_cast<void**>(&error), sizeof(int)) == cudaSuccess;
+    if (ok) {
+        cudaStream_t s = ctx->stream;
+        ok = cudaMemcpyAsync(codes, B, code_bytes, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+             cudaMemsetAsync(error, 0, sizeof(int), s) == cudaSuccess &&
+             cudaMemsetAsync(w->scales, 0, w->scale_bytes, s) == cudaSuccess &&
+             cudaMemcpyAsync(w->scales, scales, sizeof(float) * key.N, cudaMemcpyHostToDevice, s) == cudaSuccess;
+        if (ok) {
+            PackParams p{codes, w->packed, error, key.K, key.N, w->KB * 4, w->NG};
+            ok = launch_pack_weights(p, s) == cudaSuccess;
+        }
+        int host_error = 1;
+        if (ok) ok = cudaMemcpyAsync(&host_error, error, sizeof(int), cudaMemcpyDeviceToHost, s) == cudaSuccess;
+        ok = cudaStreamSynchronize(s) == cudaSuccess && ok && host_error == 0;   // a code outside [-8,7] fails creation
+    }
+    if (codes) cudaFree(codes);
+    if (error) cudaFree(error);
+    if (!ok) { cudaGetLastError(); return fail(); }
+    return w.release();
+}
+
+const Profile& rkb200::weights_profile(const rk_npu_w4a8_weights* w) { return w->profile; }
+
+extern "C" rk_npu_w4a8_weights* rk_npu_w4a8_weights_create(rk_npu_iommu_domain* domain, const rk_npu_i4_weight_config* cfg,
+                                                           const int8_t* B, const float* scales)
+{
+    if (!domain || !cfg || !B || !scales || !valid_shape(cfg->K, cfg->N)) return nullptr;
+    try {
+        rk_npu_i4_weight_config actual = *cfg;
+        int safe = cfg->k_tile;
+        double factor = 1;
+        Profile profile;
+        if (cfg->k_tile == 0) {
+            WeightBound bound;
+            if (bound_weights(cfg->K, cfg->N, B, 0, bound)) return nullptr;
+            safe = bound.k_tile;
+            if (const char* text = std::getenv("RK_NPU_W4A8_K_TILE_MULTIPLIER")) {
+                errno = 0;
+                char* end = nullptr;
+                factor = std::strtod(text, &end);
+                if (errno || end == text || *end || !std::isfinite(factor) || factor < 1) return nullptr;
+            }
+            const int cap = std::min(K_TILE_MAX, align_up(cfg->K, 32));
+            actual.k_tile = int(std::min(double(cap), safe * factor) / 32) * 32;
+            profile.K = cfg->K;
+            profile.N = cfg->N;
+            profile.safe = safe;
+            profile.safe_tiles = bound.safe_tiles;
+            profile.multiplier = factor;
+            profile.limit = actual.k_tile;
+            profile.fingerprint = weight_fingerprint(cfg->K, cfg->N, B, scales);
+        }
+        const rk_npu_w4a8_weight_info info{actual, safe, factor, actual.k_tile > safe};
+        return create_weights(domain, info, B, scales, cfg->k_tile == 0 ? &profile : nullptr);
+    } catch (...) { return nullptr; }
+}
+
+extern "C" void rk_npu_w4a8_weights_free(rk_npu_w4a8_weights* w)
+{
+    if (!w) return;
+    cudaSetDevice(w->domain->ctx->device);
+    device_free(w->domain, w->packed, w->packed_bytes);
+    device_free(w->domain, w->scales, w->scale_bytes);
+    domain_release(w->domain);
+    delete w;
+}
+extern "C" int rk_npu_w4a8_weights_query(const rk_npu_w4a8_weights* w, rk_npu_w4a8_weight_info* out)
+{
+    if (!w || !out) return RK_NPU_ERR_PARAM;
+    *out = w->info;
+    return RK_NPU_OK;
+}
+
+// ================================================================== workspaces
+extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_domain* domain, const rk_npu_w4a8_config* cfg,
+                                                                  const rk_npu_w4a8_options* options)
+{
+    if (!domain || !domain->ctx || !cfg) return nullptr;
+    rk_npu_w4a8_memory_info_ex info{};
+    if (rk_npu_w4a8_memory_query_ex(cfg, options, &info)) return nullptr;
+    auto* ctx = domain->ctx;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return nullptr;
+    rk_npu_w4a8_workspace* ws = new (std::nothrow) rk_npu_w4a8_workspace;
+    if (!ws) return nullptr;
+    bool panel8 = false;
+    options_decode(options, cfg->M, panel8, ws->npu_reduce);
+    ws->input_layout = panel8;
+    ws->config = *cfg;
+    ws->domain = domain;
+    ws->ctx_id = ctx->id;
+    ws->domain_id = domain->id;
+    domain_retain(domain);
+    ws->KB = (cfg->K + KBLOCK - 1) / KBLOCK;
+    // Schedule: the mma.sync kernel serves up to 32 tokens per CTA pass; larger batches
+    // go to the tcgen05 kernel when it can run this geometry.
+    GemmParams probe{};
+    probe.M = cfg->M; probe.N = cfg->N; probe.K = cfg->K; probe.KB = ws->KB;
+    const int forced = std::getenv("RK_NPU_B200_VARIANT") ? std::atoi(std::getenv("RK_NPU_B200_VARIANT")) : 0;
+    const bool use_tc = forced == 2 ? gemm_tc_supported(probe) : forced == 1 ? false : (cfg->M > 32 && gemm_tc_supported(probe));
+    if (use_tc) {
+        ws->TC = 0;
+        ws->T = cfg->M >= 256 ? 256 : align_up(cfg->M, 16);
+        ws->variant = 2;
+    } else {
+        ws->TC = cfg->M <= 8 ? 8 : cfg->M <= 16 ? 16 : 32;
+        ws->T = ws->TC;
+        ws->variant = 1;
+    }
+    const size_t Mp = size_t(align_up(cfg->M, ws->T));
+    ws->codes_bytes = Mp * size_t(ws->KB) * KBLOCK;
+    const int out_cols = cfg->N;
+    ws->stage_in_bytes = size_t(cfg->M) * cfg->K * 4;
+    ws->stage_out_bytes = size_t(cfg->M) * out_cols * 4;
+    bool ok = !device_alloc(domain, reinterpret_cast<void**>(&ws->codes), ws->codes_bytes);
+    ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->scales), sizeof(float) * 2 * cfg->M);
+    ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->rowmax), sizeof(uint32_t) * cfg->M);
+    ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->status), sizeof(Status));
+    ok = ok && !device_alloc(domain, &ws->stage_in, ws->stage_in_bytes);
+    ok = ok && !device_alloc(domain, &ws->stage_out, ws->stage_out_bytes);
+    if (ok) {
+        ws->inverse = ws->scales + cfg->M;
+        ok = cudaHostAlloc(reinterpret_cast<void**>(&ws->host_status), sizeof(Status), cudaHostAllocDefault) == cudaSuccess &&
+             cudaStreamCreateWithFlags(&ws->stream, cudaStreamNonBlocking) == cudaSuccess;
+    }
+    for (auto& e : ws->events) ok = ok && cudaEventCreate(&e) == cudaSuccess;
+    if (ok) {
+        // Token and K padding of the code buffer stays zero for the life of the workspace.
+        ok = cudaMemsetAsync(ws->codes, 0, ws->codes_bytes, ws->stream) == cudaSuccess &&
+             cudaMemsetAsync(ws->status, 0, sizeof(Status), ws->stream) == cudaSuccess &&
+             cudaMemsetAsync(ws->rowmax, 0, sizeof(uint32_t) * cfg->M, ws->stream) == cudaSuccess &&
+             cudaStreamSynchronize(ws->stream) == cudaSuccess;
+        std::memset(ws->host_status, 0, sizeof(Status));
+    }
+    if (!ok) { cudaGetLastError(); workspace_destroy(ws); return nullptr; }
+    return ws;
+}
+extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create(rk_npu_iommu_domain* domain, const rk_npu_w4a8_config* cfg)
+{
+    return rk_npu_w4a8_workspace_create_ex(domain, cfg, nullptr);
+}
+extern "C" void rk_npu_w4a8_workspace_free(rk_npu_w4a8_workspace* ws) { workspace_destroy(ws); }
+
+// ================================================================== blocking runs
+extern "C" int rk_npu_w4a8_run_f32(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const float* A, float* C,
+                                   rk_npu_w4a8_timings* t)
+{
+    return run(ws, w, A, C, false, EPI_F32, t);
+}
+extern "C" int rk_npu_w4a8_run_f16(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const uint16_t* A,
+                                   uint16_t* C, rk_npu_w4a8_timings* t)
+{
+    return run(ws, w, A, C, true, EPI_F16, t);
+}
+extern "C" int rk_npu_w4a8_run_swiglu_f32(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const float* A,
+                                          float* middle, rk_npu_w4a8_timings* t)
+{
+    return run(ws, w, A, middle, false, EPI_SWIGLU, t);
+}
+extern "C" int rk_npu_b200_w4a8_run_acc_i32(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const void* A,
+                                            int activation_is_f16, int32_t* acc)
+{
+    return run(ws, w, A, acc, activation_is_f16 != 0, EPI_I32, nullptr);
+}
+
+extern "C" int rk_npu_w4a8_run_ffn_f32(rk_npu_w4a8_workspace* gate_up, const rk_npu_w4a8_weights* gate_up_weights,
+                                       rk_npu_w4a8_workspace* down, const rk_npu_w4a8_weights* down_weights,
+                                       const float* A, float* middle, float* C, rk_npu_w4a8_ffn_timings* metrics)
+{
+    if (metrics) *metrics = {};
+    if (gate_up == down || middle == C || A == C) return RK_NPU_ERR_PARAM;
+    int rc = validate(gate_up, gate_up_weights, A, middle, true);
+    if (rc) return rc;
+    rc = validate(down, down_weights, middle, C, false);
+    if (rc) return rc;
+    if (gate_up->config.M != down->config.M || gate_up->config.N / 2 != down->config.K) return RK_NPU_ERR_PARAM;
+    if (gate_up->ctx_id != down->ctx_id || gate_up->domain_id != down->domain_id) return RK_NPU_ERR_DOMAIN;
+    WorkspaceLock gate_lock(*gate_up);
+    if (!gate_lock) return RK_NPU_ERR_BUSY;
+    WorkspaceLock down_lock(*down);
+    if (!down_lock) return RK_NPU_ERR_BUSY;
+    try {
+        const auto begin = Clock::now();
+        rk_npu_w4a8_ffn_timings t{};
+        const int M = gate_up->config.M, K = gate_up->config.K, F = gate_up->config.N / 2, N = down->config.N;
+        if (cudaSetDevice(gate_up->domain->ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+        cudaStream_t s = gate_up->stream;
+        const bool a_dev = on_device(A), m_dev = on_device(middle), c_dev = on_device(C);
+        const void* dA = A;
+        float* dMiddle = m_dev ? middle : static_cast<float*>(gate_up->stage_out);
+        float* dC = c_dev ? C : static_cast<float*>(down->stage_out);
+        auto mark = Clock::now();
+        if (!a_dev) {
+            if (cudaMemcpyAsync(gate_up->stage_in, A, size_t(M) * K * 4, cudaMemcpyHostToDevice, s) != cudaSuccess)
+                return RK_NPU_ERR_SUBMIT;
+            dA = gate_up->stage_in;
+        }
+        t.gate_up.sync_us += elapsed_us(mark);
+        cudaEvent_t* ev = metrics ? gate_up->events : nullptr;
+        Call first{gate_up, gate_up_weights, dA, dMiddle, false, EPI_SWIGLU, gate_up->rowmax, nullptr, s, ev};
+        rc = enqueue(first);
+        if (!rc) {
+            // Down quantises `middle` with scales finished from the collected row maxima:
+            // no rescan (src/rk_npu_w4a8.cpp:112-121,376); a non-finite maximum makes the
+            // down kernels return without work.
+            Call second{down, down_weights, dMiddle, dC, false, EPI_F32, nullptr, gate_up->rowmax, s, metrics ? down->events : nullptr};
+            rc = enqueue(second);
+        }
+        if (rc) { cudaStreamSynchronize(s); return rc; }
+        mark = Clock::now();
+        if (!m_dev) cudaMemcpyAsync(middle, dMiddle, size_t(M) * F * 4, cudaMemcpyDeviceToHost, s);
+        if (!c_dev) cudaMemcpyAsync(C, dC, size_t(M) * N * 4, cudaMemcpyDeviceToHost, s);
+        cudaMemcpyAsync(gate_up->host_status, gate_up->status, sizeof(Status), cudaMemcpyDeviceToHost, s);
+        cudaMemcpyAsync(down->host_status, down->status, sizeof(Status), cudaMemcpyDeviceToHost, s);
+        if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+        t.down.sync_us += elapsed_us(mark);
+        rc = status_to_rc(*gate_up, s);
+        const int rc_down = status_to_rc(*down, s);
+        if (!rc) rc = rc_down;
+        if (metrics) {
+            t.gate_up.activation_scan_us = event_us(gate_up->events[0], gate_up->events[1]);
+            t.gate_up.submit_us = event_us(gate_up->events[1], gate_up->events[2]);
+            t.gate_up.total_us = event_us(gate_up->events[0], gate_up->events[2]);
+            t.down.quant_pack_us = event_us(down->events[0], down->events[1]);
+            t.down.submit_us = rc_down ? 0.0 : event_us(down->events[1], down->events[2]);
+            t.down.total_us = event_us(down->events[0], down->events[2]);
+            t.total_us = elapsed_us(begin);
+            *metrics = t;
+        }
+        return rc;
+    } catch (...) { return RK_NPU_ERR_PARAM; }
+}
+
+// ================================================================== enqueue forms
+namespace {
+int enqueue_public(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const void* dA, void* dC, bool half, int epi,
+                   void* stream)
+{
+    const int rc = validate(ws, w, dA, dC, epi == EPI_SWIGLU);
+    if (rc) return rc;
+    WorkspaceLock lock(*ws);
+    if (!lock) return RK_NPU_ERR_BUSY;
+    Call call{ws, w, dA, dC, half, epi, nullptr, nullptr, static_cast<cudaStream_t>(stream), nullptr};
+    return enqueue(call);
+}
+}
+extern "C" int rk_npu_b200_w4a8_enqueue_f32(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const float* dA,
+                                            float* dC, void* stream)
+{
+    return enqueue_public(ws, w, dA, dC, false, EPI_F32, stream);
+}
+extern "C" int rk_npu_b200_w4a8_enqueue_f16(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const uint16_t* dA,
+                                            uint16_t* dC, void* stream)
+{
+    return enqueue_public(ws, w, dA, dC, true, EPI_F16, stream);
+}
+extern "C" int rk_npu_b200_w4a8_enqueue_swiglu_f32(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w,
+                                                   const float* dA, float* dMiddle, void* stream)
+{
+    return enqueue_public(ws, w, dA, dMiddle, false, EPI_SWIGLU, stream);
+}
+extern "C" int rk_npu_b200_w4a8_enqueue_ffn_f32(rk_npu_w4a8_workspace* gate_up, const rk_npu_w4a8_weights* gate_up_weights,
+                                                rk_npu_w4a8_workspace* down, const rk_npu_w4a8_weights* down_weights,
+                                                const float* dA, float* dMiddle, float* dC, void* stream)
+{
+    if (gate_up == down || dMiddle == dC || dA == dC) return RK_NPU_ERR_PARAM;
+    int rc = validate(gate_up, gate_up_weights, dA, dMiddle, true);
+    if (rc) return rc;
+    rc = validate(down, down_weights, dMiddle, dC, false);
+    if (rc) return rc;
+    if (gate_up->config.M != down->config.M || gate_up->config.N / 2 != down->config.K) return RK_NPU_ERR_PARAM;
+    if (gate_up->ctx_id != down->ctx_id || gate_up->domain_id != down->domain_id) return RK_NPU_ERR_DOMAIN;
+    WorkspaceLock gate_lock(*gate_up);
+    if (!gate_lock) return RK_NPU_ERR_BUSY;
+    WorkspaceLock down_lock(*down);
+    if (!down_lock) return RK_NPU_ERR_BUSY;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    Call first{gate_up, gate_up_weights, dA, dMiddle, false, EPI_SWIGLU, gate_up->rowmax, nullptr, s, nullptr};
+    rc = enqueue(first);
+    if (rc) return rc;
+    Call second{down, down_weights, dMiddle, dC, false, EPI_F32, nullptr, gate_up->rowmax, s, nullptr};
+    return enqueue(second);
+}
+
+extern "C" int rk_npu_b200_w4a8_finish(rk_npu_w4a8_workspace* ws)
+{
+    if (!ws) return RK_NPU_ERR_PARAM;
+    WorkspaceLock lock(*ws);
+    if (!lock) return RK_NPU_ERR_BUSY;
+    if (cudaSetDevice(ws->domain->ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    if (cudaMemcpy(ws->host_status, ws->status, sizeof(Status), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return RK_NPU_ERR_SUBMIT;
+    }
+    return status_to_rc(*ws, ws->stream);
+}
+
+extern "C" int rk_npu_b200_w4a8_last_quant(rk_npu_w4a8_workspace* ws, float* scales, int8_t* codes)
+{
+    if (!ws) return RK_NPU_ERR_PARAM;
+    WorkspaceLock lock(*ws);
+    if (!lock) return RK_NPU_ERR_BUSY;
+    if (cudaSetDevice(ws->domain->ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    const int M = ws->config.M, K = ws->config.K, T = ws->T;
+    if (scales && cudaMemcpy(scales, ws->scales, sizeof(float) * M, cudaMemcpyDeviceToHost) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    if (codes) {
+        std::vector<uint8_t> raw(ws->codes_bytes);
+        if (cudaMemcpy(raw.data(), ws->codes, ws->codes_bytes, cudaMemcpyDeviceToHost) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+        const size_t chunks = size_t(ws->KB) * 8;
+        for (int m = 0; m < M; ++m)
+            for (int k = 0; k < K; ++k)
+                codes[size_t(m) * K + k] = int8_t(raw[((size_t(m / T) * chunks + k / 16) * T + m % T) * 16 + k % 16]);
+    }
+    return RK_NPU_OK;
+}
+
+extern "C" int rk_npu_b200_w4a8_set_schedule(rk_npu_w4a8_workspace* ws, int variant, int split_k)
+{
+    if (!ws || variant < 0 || variant > 2 || (split_k != 0 && split_k != 1 && split_k != 2 && split_k != 4 && split_k != 8))
+        return RK_NPU_ERR_PARAM;
+    if (variant != 0 && variant != ws->variant) return RK_NPU_ERR_PARAM;   // the code layout is fixed at creation
+    WorkspaceLock lock(*ws);
+    if (!lock) return RK_NPU_ERR_BUSY;
+    ws->split_override = split_k;
+    return RK_NPU_OK;
+}
+extern "C" uint64_t rk_npu_b200_w4a8_launch_count(const rk_npu_w4a8_workspace* ws)
+{
+    return ws ? ws->launches.load(std::memory_order_relaxed) : 0;
+}

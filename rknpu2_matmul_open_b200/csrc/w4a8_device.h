@@ -1,0 +1,91 @@
+// w4a8_device.h -- data layouts in HBM and the launch interface between the host
+// side of the library (w4a8_abi.cpp) and its CUDA kernels.
+//
+// Packed weights  Wp[g][c][r][16 B]
+//   g : group of 32 output channels, 0 .. NG-1 (NG = ceil(N/32) rounded up to 4)
+//   c : chunk of 32 reduction elements, 0 .. KC-1 (KC = Kp/32, Kp = K rounded up to 128)
+//   r : channel inside the group
+//   The 16 bytes are four 32-bit words j = 0..3; byte b of word j holds code(k = 32c+4j+b)
+//   in its LOW nibble and code(k = 32c+16+4j+b) in its HIGH nibble (two's complement int4).
+//   (w << 4) & 0xF0F0F0F0 and w & 0xF0F0F0F0 therefore give two words of four int8 values
+//   equal to 16 x code, already in the k order both tensor-core paths want.  Sums are
+//   16 x the true sum and are shifted right by four (exactly) before dequantisation.
+//   Padding (k >= K, n >= N) holds zero codes.  Replaces the reference's
+//   B[N/64, K/32, 64, 32] panel layout (src/rk_npu_i4_cpu.cpp:53-70).
+//
+// Activation codes  Xq[mt][kc][t][16 B]
+//   mt : token tile (T tokens per tile), kc : chunk of 16 reduction elements (Kp/16 of
+//   them), t : token inside the tile; the 16 bytes are the int8 codes k = 16kc .. 16kc+15.
+//   A k-block (128 k) of one token tile is contiguous, and a group of eight tokens x 16
+//   bytes is the 8x16-byte core matrix both mma.sync and tcgen05 (no-swizzle, K-major)
+//   consume.  Replaces the reference's MSD-split A[K/32, 2*rows, 32] int4 layout
+//   (src/rk_npu_w4a8_quant.cpp:87-135): int8 MMA is native here so no split is needed.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rkb200 {
+
+constexpr int KBLOCK = 128;        // reduction elements per pipeline stage
+constexpr int GROUP = 32;          // output channels per weight group
+constexpr int TILE_N = 128;        // output channels per CTA (4 groups)
+
+enum Epilogue : int { EPI_F32 = 0, EPI_F16 = 1, EPI_I32 = 2, EPI_SWIGLU = 3 };
+
+// Device-side status block of a workspace (all int32).
+struct Status {
+    int bad_input;      // set by the quantise kernel: 1 = NaN/Inf activation, 2 = non-finite middle
+    int bad_accum;      // scratch for the cross-CTA "any row bad" reduction
+    unsigned done;      // scratch counter (wraps to 0 by itself)
+    int device_error;   // 1 = a bounded wait inside a kernel ran out
+};
+
+struct QuantParams {
+    const void* A;          // [M,K] fp32 or binary16
+    uint8_t* Xq;            // activation codes, layout above
+    float* scales;          // [M]
+    float* inverse;         // [M]
+    uint32_t* rowmax_zero;  // [M] cleared for the following SwiGLU epilogue (nullable)
+    const uint32_t* rowmax; // [M] non-null: scales come from these magnitude bits, no scan
+    Status* status;
+    int* host_flag;         // mapped host word mirroring status->bad_input (nullable)
+    int M, K, Kp, T;
+    int half;
+};
+
+struct GemmParams {
+    const uint8_t* Wp;
+    const uint8_t* Xq;
+    const float* sx;        // per-token scales
+    const float* sw;        // per-channel scales (padded to 32*NG)
+    void* out;              // [M,N] fp32 / fp16 / int32, or middle [M,F] fp32
+    uint32_t* rowmax;       // SwiGLU: per-row max |middle| bit pattern (nullable)
+    Status* status;
+    int M, N, K;
+    int KB;                 // k-blocks (Kp / 128)
+    int NG;                 // weight groups (padded)
+    int T;                  // token tile of Xq
+    int F;                  // SwiGLU: N/2, else 0
+    int epi;
+    int split;              // split-K factor == cluster size along y (1, 2, 4, 8)
+    unsigned long long timeout_ns;
+};
+
+struct PackParams {
+    const int8_t* B;        // [K,N] codes on the device
+    uint8_t* Wp;
+    int* error;             // set to 1 when a code lies outside [-8,7]
+    int K, N, KC, NG;
+};
+
+// Launch wrappers (w4a8_kernels.cu / w4a8_gemm_tc.cu). All return the launch error.
+cudaError_t launch_pack_weights(const PackParams& p, cudaStream_t stream);
+cudaError_t launch_quantize(const QuantParams& p, cudaStream_t stream, bool pdl);
+// tokens_per_cta: 8, 16 or 32 (must divide p.T)
+cudaError_t launch_gemm_mma(const GemmParams& p, int tokens_per_cta, cudaStream_t stream, bool pdl);
+size_t gemm_mma_smem_bytes(int tokens_per_cta);
+// tcgen05 path: p.T is the token tile (multiple of 16, 32..256)
+cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl);
+bool gemm_tc_supported(const GemmParams& p);
+
+} // namespace rkb200

@@ -1,0 +1,101 @@
+// w4a8_host.h -- host-side objects behind the opaque handles of the C ABI.
+#pragma once
+#include "../../include/rknpu_b200_ext.h"
+#include "w4a8_device.h"
+#include <atomic>
+#include <cuda_runtime.h>
+#include <mutex>
+#include <string>
+
+struct rk_npu_ctx {
+    int device = 0;
+    uint64_t id = 0;              // cookie compared by the DOMAIN checks
+    uint32_t driver_version = 0;  // CUDA driver version; part of the tuning-cache key
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;  // weight uploads
+};
+
+struct rk_npu_iommu_domain {
+    rk_npu_ctx* ctx = nullptr;
+    uint32_t id = 0;
+    std::atomic<int> refs{1};
+    std::mutex lock;
+    rk_npu_domain_memory_stats stats{};
+};
+
+namespace rkb200 {
+
+// Weight identity and certified K tiles captured at creation
+// (the reference's w4_tune::Profile, src/rk_npu_w4a8_tune_internal.h:27-34).
+struct Profile {
+    int K = 0, N = 0, safe = 0, limit = 0;
+    double multiplier = 1;
+    uint64_t fingerprint = 0, safe_tiles = 0;
+    bool certified(int k) const { return k >= 32 && k <= 2048 && k % 32 == 0 && (safe_tiles & (uint64_t(1) << (k / 32 - 1))); }
+    bool permits(int k) const { return k >= 32 && k <= limit && k % 32 == 0 && (certified(k) || multiplier > 1); }
+    rk_npu_w4a8_weight_info info(int k) const { return {{K, N, k}, safe, multiplier, !certified(k)}; }
+};
+
+struct WeightBound {
+    int k_tile = 0;
+    int64_t positive = 0, negative_magnitude = 0;
+    uint64_t safe_tiles = 0;
+};
+int bound_weights(int K, int N, const int8_t* B, int requested, WeightBound& out, int fallback = 0);
+uint64_t weight_fingerprint(int K, int N, const int8_t* B, const float* scales);
+int make_profile(const rk_npu_w4a8_autotune_config& c, const int8_t* B, const float* scale, Profile& out);
+bool valid_autotune_config(const rk_npu_w4a8_autotune_config& c);
+rk_npu_w4a8_weights* create_weights(rk_npu_iommu_domain* domain, const rk_npu_w4a8_weight_info& info, const int8_t* B,
+                                    const float* scales, const Profile* profile);
+const Profile& weights_profile(const rk_npu_w4a8_weights* w);
+
+void domain_retain(rk_npu_iommu_domain* d);
+void domain_release(rk_npu_iommu_domain* d);
+// Device allocations are accounted to the owning domain.
+int device_alloc(rk_npu_iommu_domain* d, void** ptr, size_t bytes);
+void device_free(rk_npu_iommu_domain* d, void* ptr, size_t bytes);
+
+inline int align_up(int x, int a) { return (x + a - 1) / a * a; }
+inline int64_t align_up64(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+} // namespace rkb200
+
+struct rk_npu_w4a8_weights {
+    rk_npu_iommu_domain* domain = nullptr;
+    uint64_t ctx_id = 0;
+    uint32_t domain_id = 0;
+    rk_npu_w4a8_weight_info info{};
+    rkb200::Profile profile;
+    uint8_t* packed = nullptr;  // Wp
+    float* scales = nullptr;    // padded to 32*NG
+    size_t packed_bytes = 0, scale_bytes = 0;
+    int KB = 0, NG = 0;
+};
+
+struct rk_npu_w4a8_workspace {
+    rk_npu_w4a8_config config{};
+    rk_npu_iommu_domain* domain = nullptr;
+    uint64_t ctx_id = 0;
+    uint32_t domain_id = 0;
+    bool npu_reduce = false;
+    int input_layout = 0;
+    std::atomic_flag busy = ATOMIC_FLAG_INIT;
+    cudaStream_t stream = nullptr;
+    // geometry
+    int T = 0;        // token tile of the code layout
+    int TC = 0;       // tokens per CTA of the mma.sync kernel (0 when the tcgen05 kernel is used)
+    int KB = 0;       // k-blocks
+    int variant = 0, split_override = 0;
+    // device buffers
+    uint8_t* codes = nullptr;
+    float* scales = nullptr;
+    float* inverse = nullptr;
+    uint32_t* rowmax = nullptr;
+    rkb200::Status* status = nullptr;
+    void* stage_in = nullptr;   // device copy of host activations
+    void* stage_out = nullptr;  // device copy of host outputs
+    size_t codes_bytes = 0, stage_in_bytes = 0, stage_out_bytes = 0;
+    rkb200::Status* host_status = nullptr;  // pinned
+    cudaEvent_t events[8]{};
+    std::atomic<uint64_t> launches{0};
+};

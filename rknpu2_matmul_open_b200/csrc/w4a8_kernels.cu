@@ -1,0 +1,560 @@
+// w4a8_kernels.cu -- weight repacking, per-token activation quantisation and the
+// mma.sync W4A8 GEMM (decode / small-batch path and general fallback) for sm_100a.
+//
+// Reference behaviour reproduced (paths inside the reference project):
+//   quantise_kernel : src/rk_npu_w4a8_quant.cpp:52-85 (scales), :119-121 (codes),
+//                     :145-161 (scales from collected row maxima)
+//   gemm epilogues  : src/rk_npu_w4a8_output.cpp:70-76 (dequantise),
+//                     src/rk_npu_w4a8_swiglu.cpp:12-91 + src/rk_npu_swiglu_fp32_neon.h:13-51
+//   pack_weights    : src/rk_npu_w4a8.cpp:236-242 (code range check); layout is new.
+#include "w4a8_device.h"
+#include "w4a8_ptx.cuh"
+#include <cooperative_groups.h>
+#include <cuda_fp16.h>
+#include <float.h>
+
+namespace cg = cooperative_groups;
+
+namespace rkb200 {
+
+// =============================================================== weight repacking
+// One thread builds one 32-bit word of the packed layout: eight codes of one output
+// channel.  Consecutive threads take consecutive channels so the reads of B[k, :] are
+// coalesced; the 4-byte writes of a warp land 16 bytes apart and are merged in L2.
+__global__ void __launch_bounds__(256) pack_weights_kernel(const PackParams p)
+{
+    const long long total = (long long)p.NG * p.KC * 4 * GROUP;
+    long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int r = (int)(idx % GROUP);
+    long long rest = idx / GROUP;
+    const int j = (int)(rest % 4);
+    rest /= 4;
+    const int c = (int)(rest % p.KC);
+    const int g = (int)(rest / p.KC);
+    const int n = g * GROUP + r;
+    uint32_t word = 0;
+    int bad = 0;
+    if (n < p.N) {
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int k_lo = c * 32 + 4 * j + b, k_hi = k_lo + 16;
+            int lo = 0, hi = 0;
+            if (k_lo < p.K) lo = p.B[(size_t)k_lo * p.N + n];
+            if (k_hi < p.K) hi = p.B[(size_t)k_hi * p.N + n];
+            bad |= (lo < -8) | (lo > 7) | (hi < -8) | (hi > 7);
+            word |= (uint32_t)((lo & 15) | ((hi & 15) << 4)) << (8 * b);
+        }
+    }
+    if (bad) atomicOr(p.error, 1);
+    reinterpret_cast<uint32_t*>(p.Wp)[(((size_t)g * p.KC + c) * GROUP + r) * 4 + j] = word;
+}
+
+cudaError_t launch_pack_weights(const PackParams& p, cudaStream_t stream)
+{
+    const long long total = (long long)p.NG * p.KC * 4 * GROUP;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    pack_weights_kernel<<<blocks, 256, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+// =============================================================== activation quantisation
+// One CTA per token.  Pass 1: max |x| over the full row on the raw bit patterns (for
+// binary16 and fp32 alike the magnitude bits order like the magnitudes, and anything
+// at or above the infinity pattern is NaN/Inf).  Pass 2: q = clamp(round_half_away(
+// x * inverse), -127, 127), written as 16-byte units of the Xq layout.
+template <bool HALF> struct ActType;
+template <> struct ActType<true> { using type = uint16_t; };
+template <> struct ActType<false> { using type = float; };
+
+template <bool HALF>
+__device__ __forceinline__ void load16(const typename ActType<HALF>::type* row, int k0, int K, bool vec, float (&v)[16],
+                                       uint32_t& maxbits)
+{
+    if constexpr (HALF) {
+        uint16_t h[16];
+        if (vec && k0 + 16 <= K) {
+            const uint4 a = *reinterpret_cast<const uint4*>(row + k0);
+            const uint4 b = *reinterpret_cast<const uint4*>(row + k0 + 8);
+            const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { h[2 * i] = (uint16_t)(w[i] & 0xffffu); h[2 * i + 1] = (uint16_t)(w[i] >> 16); }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) h[i] = (k0 + i < K) ? row[k0 + i] : (uint16_t)0;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            maxbits = max(maxbits, (uint32_t)(h[i] & 0x7fffu));
+            v[i] = __half2float(__ushort_as_half(h[i]));
+        }
+    } else {
+        if (vec && k0 + 16 <= K) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 f = *reinterpret_cast<const float4*>(row + k0 + 4 * i);
+                v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = (k0 + i < K) ? row[k0 + i] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) maxbits = max(maxbits, __float_as_uint(v[i]) & 0x7fffffffu);
+    }
+}
+
+template <bool HALF>
+__global__ void __launch_bounds__(256) quantize_kernel(const QuantParams p)
+{
+    using T = typename ActType<HALF>::type;
+    pdl_launch_dependents();   // the GEMM behind this kernel may start prefetching weights
+    pdl_wait();                // A may be the output of the kernel in front of this one
+    const int m = blockIdx.x, tid = threadIdx.x;
+    const T* row = reinterpret_cast<const T*>(p.A) + (size_t)m * p.K;
+    const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
+    const int chunks = p.Kp / 16, live_chunks = (p.K + 15) / 16;
+    __shared__ uint32_t s_part[8];
+    __shared__ float s_inverse;
+    __shared__ int s_bad;
+
+    uint32_t maxbits = 0;
+    int bad = 0;
+    if (p.rowmax == nullptr) {
+        float v[16];
+        for (int kc = tid; kc < live_chunks; kc += 256) load16<HALF>(row, kc * 16, p.K, vec, v, maxbits);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) maxbits = max(maxbits, __shfl_xor_sync(0xffffffffu, maxbits, o));
+        if ((tid & 31) == 0) s_part[tid >> 5] = maxbits;
+        __syncthreads();
+        if (tid == 0) {
+            uint32_t mx = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mx = max(mx, s_part[i]);
+            float maximum;
+            if constexpr (HALF) {
+                bad = mx >= 0x7c00u ? 1 : 0;
+                maximum = __half2float(__ushort_as_half((uint16_t)mx));
+            } else {
+                bad = mx >= 0x7f800000u ? 1 : 0;
+                maximum = __uint_as_float(mx);
+            }
+            const float s = (maximum == 0.f || bad) ? 1.0f : fmaxf(__fdiv_rn(maximum, 127.0f), FLT_MIN);
+            const float inv = __fdiv_rn(1.0f, s);
+            p.scales[m] = s;
+            p.inverse[m] = inv;
+            s_inverse = inv;
+            s_bad = bad;
+        }
+    } else if (tid == 0) {
+        const uint32_t bits = p.rowmax[m];
+        bad = bits >= 0x7f800000u ? 2 : 0;
+        const float maximum = __uint_as_float(bits);
+        const float s = (maximum == 0.f || bad) ? 1.0f : fmaxf(__fdiv_rn(maximum, 127.0f), FLT_MIN);
+        const float inv = __fdiv_rn(1.0f, s);
+        p.scales[m] = s;
+        p.inverse[m] = inv;
+        s_inverse = inv;
+        s_bad = bad;
+    }
+    if (tid == 0) {
+        if (p.rowmax_zero) p.rowmax_zero[m] = 0u;
+        // "Any row bad" across CTAs without a reset pass: the last CTA to arrive
+        // publishes the accumulated flag and clears the scratch word; the counter
+        // wraps to zero by itself (atomicInc with limit M-1).
+        if (bad) atomicOr(&p.status->bad_accum, bad);
+        __threadfence();
+        const unsigned prev = atomicInc(&p.status->done, (unsigned)p.M - 1u);
+        if (prev == (unsigned)p.M - 1u) {
+            __threadfence();
+            const int any = atomicExch(&p.status->bad_accum, 0);
+            p.status->bad_input = any;
+            if (p.host_flag) *p.host_flag = any;
+        }
+    }
+    __syncthreads();
+    const float inv = s_inverse;
+    const int mt = m / p.T, t = m - mt * p.T;
+    uint4* dst = reinterpret_cast<uint4*>(p.Xq) + ((size_t)mt * chunks) * p.T + t;
+    for (int kc = tid; kc < chunks; kc += 256) {
+        uint32_t w[4] = {0u, 0u, 0u, 0u};
+        if (kc < live_chunks) {
+            float v[16];
+            uint32_t unused = 0;
+            load16<HALF>(row, kc * 16, p.K, vec, v, unused);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                float r = roundf(__fmul_rn(v[i], inv));
+                r = fminf(fmaxf(r, -127.f), 127.f);
+                const int q = (kc * 16 + i < p.K) ? (int)r : 0;
+                w[i >> 2] |= (uint32_t)(q & 0xff) << (8 * (i & 3));
+            }
+        }
+        dst[(size_t)kc * p.T] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+cudaError_t launch_quantize(const QuantParams& p, cudaStream_t stream, bool pdl)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)p.M);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return p.half ? cudaLaunchKernelEx(&cfg, quantize_kernel<true>, p) : cudaLaunchKernelEx(&cfg, quantize_kernel<false>, p);
+}
+
+// =============================================================== epilogue math (shared)
+// Degree-7 polynomial SiLU of the reference's production target, every rounding kept:
+// src/rk_npu_swiglu_fp32_neon.h:17-41.
+__device__ __forceinline__ float silu_poly(float g)
+{
+    float x = fminf(fmaxf(-g, -80.f), 80.f);
+    const float n = floorf(fmaf(x, 1.4426950408889634f, 0.5f));
+    float r = fmaf(-n, 0.693145751953125f, x);
+    r = fmaf(-n, 1.428606765330187e-6f, r);
+    float q = 1.f / 5040.f;
+    q = fmaf(q, r, 1.f / 720.f);
+    q = fmaf(q, r, 1.f / 120.f);
+    q = fmaf(q, r, 1.f / 24.f);
+    q = fmaf(q, r, 1.f / 6.f);
+    q = fmaf(q, r, 0.5f);
+    q = fmaf(q, r, 1.f);
+    q = fmaf(q, r, 1.f);
+    const float power = __int_as_float(((int)n + 127) << 23);
+    const float d = __fadd_rn(1.f, __fmul_rn(q, power));
+    return g < -80.f ? -0.f : __fdiv_rn(g, d);
+}
+__device__ __forceinline__ float dequant(int acc, float sx, float sw)
+{
+    return __fmul_rn(__fmul_rn(__int2float_rn(acc), sx), sw);
+}
+
+// =============================================================== mma.sync GEMM
+// Output-stationary, swap-AB: the 128 output channels of a CTA are the M side of
+// mma.m16n8k32 (weights = A fragments built from the packed nibbles with three ALU
+// instructions per eight codes), the tokens are the N side (8 per instruction).
+// One producer thread streams weight and activation k-blocks with bulk async copies
+// into a ring of stages; four consumer warps (one weight group each) do the math.
+// Split-K runs as a thread-block cluster along y: partial sums are exchanged through
+// distributed shared memory, each rank finishing a slice of the channels.
+constexpr int MMA_STAGES = 8;
+constexpr int RED_STRIDE = 132;   // int32 words per token row of the reduction buffer
+
+__host__ __device__ constexpr int mma_stage_bytes(int tc) { return 4 * 2048 + 128 * tc; }
+__host__ __device__ constexpr size_t mma_smem_bytes(int tc)
+{
+    return (size_t)MMA_STAGES * mma_stage_bytes(tc) + (size_t)tc * RED_STRIDE * 4 + 2 * MMA_STAGES * 8 + 16;
+}
+size_t gemm_mma_smem_bytes(int tokens_per_cta) { return mma_smem_bytes(tokens_per_cta); }
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT, bool BIGK>
+__global__ void __launch_bounds__(160, 1) gemm_mma_kernel(const GemmParams p)
+{
+    constexpr int TC = 8 * NT;
+    constexpr int XB = 128 * TC;
+    constexpr int STAGE = mma_stage_bytes(TC);
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* const stages = smem;
+    int32_t* const red = reinterpret_cast<int32_t*>(smem + MMA_STAGES * STAGE);
+    uint64_t* const full = reinterpret_cast<uint64_t*>(smem + MMA_STAGES * STAGE + TC * RED_STRIDE * 4);
+    uint64_t* const empty = full + MMA_STAGES;
+
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = blockIdx.x, rank = blockIdx.y, S = p.split;
+    const int tok0 = blockIdx.z * TC;
+    const bool swiglu = p.epi == EPI_SWIGLU;
+    const int KC = p.KB * 4;
+    const int kb0 = (int)(((long long)p.KB * rank) / S), kb1 = (int)(((long long)p.KB * (rank + 1)) / S);
+    const int nkb = kb1 - kb0;
+    const unsigned long long deadline = global_ns() + p.timeout_ns;
+
+    if (tid == 0) {
+        for (int s = 0; s < MMA_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 4); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    int acc[2][NT][4];
+    int hi[BIGK ? 2 : 1][BIGK ? NT : 1][4];
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[a][j][e] = 0;
+    if constexpr (BIGK) {
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) hi[a][j][e] = 0;
+    }
+
+    if (warp == 4) {
+        if (lane == 0) {
+            // ---------------- producer
+            int group[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+                group[w] = swiglu ? (w < 2 ? tile * 2 + w : p.F / GROUP + tile * 2 + (w - 2)) : tile * 4 + w;
+            const int mt = tok0 / p.T, r0 = tok0 - mt * p.T;
+            const size_t kc16_total = (size_t)p.KB * 8;
+            auto copy_w = [&](int it, int s) {
+#pragma unroll
+                for (int w = 0; w < 4; ++w)
+                    bulk_g2s(stages + (size_t)s * STAGE + w * 2048,
+                             p.Wp + ((size_t)group[w] * KC + (size_t)(kb0 + it) * 4) * 512, 2048, &full[s]);
+            };
+            auto copy_x = [&](int it, int s) {
+                uint8_t* dst = stages + (size_t)s * STAGE + 8192;
+                const size_t kc16 = (size_t)(kb0 + it) * 8;
+                if (p.T == TC) {
+                    bulk_g2s(dst, p.Xq + ((size_t)mt * kc16_total + kc16) * p.T * 16, XB, &full[s]);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        bulk_g2s(dst + c * TC * 16, p.Xq + (((size_t)mt * kc16_total + kc16 + c) * p.T + r0) * 16,
+                                 TC * 16, &full[s]);
+                }
+            };
+            const int pre = nkb < MMA_STAGES ? nkb : MMA_STAGES;
+            // Weights never change, so their first stages are requested before waiting
+            // for the kernel in front (which produces the activation codes).
+            for (int it = 0; it < pre; ++it) { mbar_expect_tx(&full[it], 8192); copy_w(it, it); }
+            pdl_wait();
+            const bool skip = *reinterpret_cast<volatile const int*>(&p.status->bad_input) != 0;
+            for (int it = 0; it < pre; ++it) {
+                if (skip) { mbar_arrive(&full[it]); }
+                else { mbar_arrive_expect_tx(&full[it], XB); copy_x(it, it); }
+            }
+            if (!skip) {
+                for (int it = pre; it < nkb; ++it) {
+                    const int s = it % MMA_STAGES;
+                    if (!mbar_wait(&empty[s], ((it / MMA_STAGES) - 1) & 1, deadline)) {
+                        atomicExch(&p.status->device_error, 1);
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&full[s], STAGE);
+                    copy_w(it, s);
+                    copy_x(it, s);
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- consumers: warp w owns weight group w (32 channels = two m16 tiles)
+        pdl_wait();
+        const bool skip = *reinterpret_cast<volatile const int*>(&p.status->bad_input) != 0;
+        const int iters = skip ? (nkb < MMA_STAGES ? nkb : MMA_STAGES) : nkb;
+        const int g8 = lane >> 2, t4 = lane & 3;
+        for (int it = 0; it < iters; ++it) {
+            const int s = it % MMA_STAGES;
+            if (!mbar_wait(&full[s], (it / MMA_STAGES) & 1, deadline)) {
+                if (lane == 0) atomicExch(&p.status->device_error, 1);
+                break;
+            }
+            if (!skip) {
+                const uint32_t wbase = smem_u32(stages + (size_t)s * STAGE + warp * 2048) + g8 * 16 + t4 * 4;
+                const uint32_t xbase = smem_u32(stages + (size_t)s * STAGE + 8192) + g8 * 16 + t4 * 4;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t a[2][4];
+#pragma unroll
+                    for (int mtile = 0; mtile < 2; ++mtile) {
+                        const uint32_t w0 = lds32(wbase + (c * 32 + mtile * 16) * 16);
+                        const uint32_t w1 = lds32(wbase + (c * 32 + mtile * 16 + 8) * 16);
+                        a[mtile][0] = (w0 << 4) & 0xF0F0F0F0u;
+                        a[mtile][1] = (w1 << 4) & 0xF0F0F0F0u;
+                        a[mtile][2] = w0 & 0xF0F0F0F0u;
+                        a[mtile][3] = w1 & 0xF0F0F0F0u;
+                    }
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        const uint32_t b0 = lds32(xbase + ((2 * c) * TC + 8 * j) * 16);
+                        const uint32_t b1 = lds32(xbase + ((2 * c + 1) * TC + 8 * j) * 16);
+                        mma_s8(acc[0][j], a[0][0], a[0][1], a[0][2], a[0][3], b0, b1);
+                        mma_s8(acc[1][j], a[1][0], a[1][1], a[1][2], a[1][3], b0, b1);
+                    }
+                }
+                if constexpr (BIGK) {
+                    // 16*|sum| stays below 2^31 for 512 k-blocks; fold the exact quotient away.
+                    if ((it & 511) == 511) {
+#pragma unroll
+                        for (int a = 0; a < 2; ++a)
+#pragma unroll
+                            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) { hi[a][j][e] += acc[a][j][e] >> 4; acc[a][j][e] = 0; }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+        // partial sums -> reduction buffer [token][channel]
+#pragma unroll
+        for (int mtile = 0; mtile < 2; ++mtile)
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    int v = acc[mtile][j][e] >> 4;
+                    if constexpr (BIGK) v += hi[mtile][j][e];
+                    const int ch = warp * 32 + mtile * 16 + g8 + (e >> 1) * 8;
+                    const int tok = 8 * j + 2 * t4 + (e & 1);
+                    red[tok * RED_STRIDE + ch] = v;
+                }
+    }
+    __syncthreads();
+    cg::cluster_group cluster = cg::this_cluster();
+    if (S > 1) cluster.sync();
+
+    const bool skip_out = *reinterpret_cast<volatile const int*>(&p.status->bad_input) != 0;
+    if (tid < 128 && !skip_out) {
+        const int CH = (swiglu ? 64 : 128) / S;       // channels (gate channels) this rank finishes
+        const int IPT = CH / 4;                       // 4-channel items per token
+        const int items = TC * IPT;
+        for (int base = 0; base < items; base += 128) {
+            const int i = base + tid;
+            const bool active = i < items;
+            const int tok = active ? i / IPT : 0, c4 = active ? i - tok * IPT : 0;
+            const int ch = rank * CH + c4 * 4;
+            const int m = tok0 + tok;
+            int4 v = make_int4(0, 0, 0, 0), u = make_int4(0, 0, 0, 0);
+            if (active) {
+                for (int q = 0; q < S; ++q) {
+                    const int32_t* src = S > 1 ? cluster.map_shared_rank(red, q) : red;
+                    const int4 a = *reinterpret_cast<const int4*>(src + tok * RED_STRIDE + ch);
+                    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                    if (swiglu) {
+                        const int4 b = *reinterpret_cast<const int4*>(src + tok * RED_STRIDE + 64 + ch);
+                        u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+                    }
+                }
+            }
+            const bool row_ok = active && m < p.M;
+            if (!swiglu) {
+                const int n = tile * TILE_N + ch;
+                if (row_ok && n < p.N) {
+                    const int va[4] = {v.x, v.y, v.z, v.w};
+                    if (p.epi == EPI_I32) {
+                        int* out = reinterpret_cast<int*>(p.out) + (size_t)m * p.N + n;
+                        if (n + 3 < p.N && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) *reinterpret_cast<int4*>(out) = v;
+                        else for (int e = 0; e < 4; ++e) if (n + e < p.N) out[e] = va[e];
+                    } else {
+                        const float sx = p.sx[m];
+                        float y[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) y[e] = dequant(va[e], sx, p.sw[n + e]);
+                        if (p.epi == EPI_F32) {
+                            float* out = reinterpret_cast<float*>(p.out) + (size_t)m * p.N + n;
+                            if (n + 3 < p.N && (reinterpret_cast<uintptr_t>(out) & 15u) == 0)
+                                *reinterpret_cast<float4*>(out) = make_float4(y[0], y[1], y[2], y[3]);
+                            else for (int e = 0; e < 4; ++e) if (n + e < p.N) out[e] = y[e];
+                        } else {
+                            __half* out = reinterpret_cast<__half*>(p.out) + (size_t)m * p.N + n;
+                            if (n + 3 < p.N && (reinterpret_cast<uintptr_t>(out) & 7u) == 0) {
+                                const __half2 h0 = __halves2half2(__float2half_rn(y[0]), __float2half_rn(y[1]));
+                                const __half2 h1 = __halves2half2(__float2half_rn(y[2]), __float2half_rn(y[3]));
+                                uint2 pk;
+                                pk.x = *reinterpret_cast<const uint32_t*>(&h0);
+                                pk.y = *reinterpret_cast<const uint32_t*>(&h1);
+                                *reinterpret_cast<uint2*>(out) = pk;
+                            } else for (int e = 0; e < 4; ++e) if (n + e < p.N) out[e] = __float2half_rn(y[e]);
+                        }
+                    }
+                }
+            } else {
+                const int f = tile * 64 + ch;
+                uint32_t mx = 0;
+                if (row_ok && f < p.F) {
+                    const float sx = p.sx[m];
+                    const int ga[4] = {v.x, v.y, v.z, v.w}, ua[4] = {u.x, u.y, u.z, u.w};
+                    float y[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float g = dequant(ga[e], sx, p.sw[f + e]);
+                        const float up = dequant(ua[e], sx, p.sw[p.F + f + e]);
+                        y[e] = __fmul_rn(silu_poly(g), up);
+                        mx = max(mx, __float_as_uint(y[e]) & 0x7fffffffu);
+                    }
+                    float* out = reinterpret_cast<float*>(p.out) + (size_t)m * p.F + f;
+                    if ((reinterpret_cast<uintptr_t>(out) & 15u) == 0) *reinterpret_cast<float4*>(out) = make_float4(y[0], y[1], y[2], y[3]);
+                    else for (int e = 0; e < 4; ++e) out[e] = y[e];
+                }
+                if (p.rowmax) {
+                    // lanes of an aligned group of IPT share the token: one atomic per group
+                    for (int o = 1; o < IPT && o < 32; o <<= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                    if (row_ok && (lane & (IPT - 1) & 31) == 0 && mx) atomicMax(&p.rowmax[m], mx);
+                }
+            }
+        }
+    }
+    if (S > 1) cluster.sync();   // nobody leaves while a peer may still read its partials
+}
+
+template <int NT, bool BIGK>
+static cudaError_t launch_mma_inst(const GemmParams& p, cudaStream_t stream, bool pdl)
+{
+    constexpr int TC = 8 * NT;
+    const size_t smem = mma_smem_bytes(TC);
+    static bool configured = false;
+    auto kernel = gemm_mma_kernel<NT, BIGK>;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const int tiles = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : p.NG / 4;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)tiles, (unsigned)p.split, (unsigned)((p.M + TC - 1) / TC));
+    cfg.blockDim = dim3(160);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = (unsigned)p.split;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+    if (pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
+cudaError_t launch_gemm_mma(const GemmParams& p, int tokens_per_cta, cudaStream_t stream, bool pdl)
+{
+    if (p.split != 1 && p.split != 2 && p.split != 4 && p.split != 8) return cudaErrorInvalidValue;
+    if (p.T % tokens_per_cta) return cudaErrorInvalidValue;
+    const bool big = (long long)p.KB * KBLOCK > 131072;
+    switch (tokens_per_cta) {
+    case 8: return big ? launch_mma_inst<1, true>(p, stream, pdl) : launch_mma_inst<1, false>(p, stream, pdl);
+    case 16: return big ? launch_mma_inst<2, true>(p, stream, pdl) : launch_mma_inst<2, false>(p, stream, pdl);
+    case 32: return big ? launch_mma_inst<4, true>(p, stream, pdl) : launch_mma_inst<4, false>(p, stream, pdl);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+} // namespace rkb200
