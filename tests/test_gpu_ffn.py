@@ -1,0 +1,160 @@
+"""Fused gate/up -> SwiGLU -> down through the C ABI.  Against the polynomial oracle the
+whole chain is bit-exact; against the reference build's expf variant the staged bars of
+the north star apply (middle <= 1e-6 relative, output <= 1e-3 relative)."""
+import numpy as np
+import pytest
+
+import rknpu2_matmul_open_b200 as rk
+from conftest import bits
+from oracle.harness import make_activations, make_weights
+from rknpu2_matmul_open_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+
+def build(dom, M, K, F, N, Bg, sg, Bd, sd, kt=480):
+    wg, wd = rk.Weights(dom, Bg, sg, k_tile=kt), rk.Weights(dom, Bd, sd, k_tile=kt)
+    g = rk.Workspace(dom, rk.default_config(M, 2 * F, K, k_tile=kt))
+    d = rk.Workspace(dom, rk.default_config(M, N, F, k_tile=kt))
+    return wg, wd, g, d
+
+
+def free(*objs):
+    for o in objs:
+        o.free()
+
+
+def test_reference_fixtures(gpu, oracle, golden_ffn):
+    _, dom, _ = gpu
+    g = golden_ffn
+    for i in range(int(g["count"])):
+        t = f"f{i}"
+        M, K, F, N = (int(x) for x in g[f"{t}_shape"])
+        wg, wd, gu, dn = build(dom, M, K, F, N, g[f"{t}_Bg"], g[f"{t}_sg"], g[f"{t}_Bd"], g[f"{t}_sd"])
+        middle, C = np.zeros((M, F), np.float32), np.zeros((M, N), np.float32)
+        assert rk.run_ffn_f32(gu, wg, dn, wd, g[f"{t}_A"], middle, C) == 0
+        ref_mid, ref_c = g[f"{t}_middle"], g[f"{t}_C"]
+        assert np.all(np.abs(middle - ref_mid) <= 1e-6 * np.abs(ref_mid) + 1e-30)
+        assert np.all(np.abs(C - ref_c) <= 1e-3 * np.abs(ref_c) + 1e-6)
+        poly = oracle.ffn(g[f"{t}_A"], g[f"{t}_Bg"], g[f"{t}_sg"], g[f"{t}_Bd"], g[f"{t}_sd"], mode=1)
+        assert np.array_equal(bits(middle), bits(poly["middle"])) and np.array_equal(bits(C), bits(poly["C"]))
+        free(gu, dn, wg, wd)
+
+
+# M x F x K grid of the reference's SwiGLU/FFN tests (F 96 and 992 are 32 mod 64)
+CASES = [(1, 479, 96, 192), (9, 959, 128, 192), (65, 1057, 992, 192), (2, 479, 128, 64), (4, 959, 128, 257),
+         (8, 1057, 9728, 128), (64, 479, 128, 65), (65, 959, 96, 193), (128, 1057, 128, 129), (33, 4096, 1024, 512)]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda s: "x".join(map(str, s)))
+def test_ffn_equals_staged_operators_bit_for_bit(gpu, oracle, case):
+    _, dom, _ = gpu
+    M, K, F, N = case
+    Bg, sg = make_weights(K, 2 * F, seed=F)
+    Bd, sd = make_weights(F, N, seed=N)
+    wg, wd, gu, dn = build(dom, M, K, F, N, Bg, sg, Bd, sd)
+    for pattern in range(3):
+        A = make_activations(M, K, seed=pattern, dtype="f32")
+        if pattern == 1:
+            A[:] = 0                                       # zero input: zero middle, scale 1, zero output
+        if pattern == 2:
+            A = -np.abs(A)
+        middle, C = np.zeros((M, F), np.float32), np.zeros((M, N), np.float32)
+        t = capi.W4A8FfnTimings()
+        assert rk.run_ffn_f32(gu, wg, dn, wd, A, middle, C, t) == 0
+        assert t.down.activation_scan_us == 0              # down never rescans: scales come from the epilogue
+        ref = oracle.ffn(A, Bg, sg, Bd, sd, mode=1)
+        assert np.array_equal(ref["acc_gate_up"], _acc(gu, wg, A))
+        assert np.array_equal(bits(middle), bits(ref["middle"]))
+        assert np.array_equal(bits(C), bits(ref["C"]))
+        # fused == separate SwiGLU call followed by an ordinary linear on middle
+        only = np.zeros((M, F), np.float32)
+        assert gu.run_swiglu_f32(wg, A, only) == 0 and np.array_equal(bits(only), bits(middle))
+        C2 = np.zeros((M, N), np.float32)
+        assert dn.run_f32(wd, middle, C2) == 0 and np.array_equal(bits(C2), bits(C))
+        rc, s, q = dn.last_quant()
+        assert np.array_equal(bits(s), bits(ref["scales_down_in"]))       # reused scale == rescanned scale
+        if pattern == 1:
+            assert not middle.any() and not C.any()
+    free(gu, dn, wg, wd)
+
+
+def _acc(ws, w, A):
+    acc = np.zeros((A.shape[0], ws.cfg.N), np.int32)
+    assert ws.run_acc_i32(w, A, acc) == 0
+    return acc
+
+
+def test_nonfinite_middle_is_rejected_before_down(gpu, oracle):
+    # w_scale = FLT_MAX drives middle to inf: PARAM after gate/up, down does no work
+    _, dom, _ = gpu
+    M, K, F, N = 3, 959, 128, 256
+    Bg = np.ones((K, 2 * F), np.int8)
+    sg = np.full(2 * F, np.finfo(np.float32).max, np.float32)
+    Bd, sd = make_weights(F, N, seed=1)
+    wg, wd, gu, dn = build(dom, M, K, F, N, Bg, sg, Bd, sd)
+    A = np.abs(make_activations(M, K, seed=1, dtype="f32")) + 1
+    middle, C = np.zeros((M, F), np.float32), np.full((M, N), 7.0, np.float32)
+    t = capi.W4A8FfnTimings()
+    assert rk.run_ffn_f32(gu, wg, dn, wd, A, middle, C, t) == capi.RK_NPU_ERR_PARAM
+    assert t.down.submit_us == 0
+    assert oracle.ffn(A, Bg, sg, Bd, sd, mode=1)["rc"] == -3
+    # NaN input is refused too, and both workspaces stay usable
+    A2 = make_activations(M, K, seed=2, dtype="f32")
+    A2[1, 1] = np.nan
+    assert rk.run_ffn_f32(gu, wg, dn, wd, A2, middle, C) == capi.RK_NPU_ERR_PARAM
+    free(gu, dn, wg, wd)
+    Bg, sg = make_weights(K, 2 * F, seed=3)
+    wg, wd, gu, dn = build(dom, M, K, F, N, Bg, sg, Bd, sd)
+    A3 = make_activations(M, K, seed=3, dtype="f32")
+    assert rk.run_ffn_f32(gu, wg, dn, wd, A3, middle, C) == 0
+    assert np.array_equal(bits(C), bits(oracle.ffn(A3, Bg, sg, Bd, sd, mode=1)["C"]))
+    free(gu, dn, wg, wd)
+
+
+def test_ffn_argument_errors(gpu):
+    ctx, dom, other = gpu
+    lib = capi.load()
+    M, K, F, N = 4, 256, 64, 96
+    Bg, sg = make_weights(K, 2 * F, seed=1)
+    Bd, sd = make_weights(F, N, seed=2)
+    wg, wd, gu, dn = build(dom, M, K, F, N, Bg, sg, Bd, sd)
+    A = make_activations(M, K, seed=1, dtype="f32")
+    middle, C = np.zeros((M, F), np.float32), np.zeros((M, N), np.float32)
+    t = capi.W4A8FfnTimings()
+    t.total_us = 5
+    assert lib.rk_npu_w4a8_run_ffn_f32(None, wg.handle, dn.handle, wd.handle, A.ctypes.data, middle.ctypes.data,
+                                       C.ctypes.data, t) == -3 and t.total_us == 0          # timings are zeroed
+    assert rk.run_ffn_f32(gu, wg, gu, wg, A, middle, C) == -3                                # same workspace twice
+    assert rk.run_ffn_f32(gu, wg, dn, wd, A, middle, middle) == -3                           # aliasing
+    wrong = rk.Workspace(dom, rk.default_config(M + 1, N, F))
+    assert rk.run_ffn_f32(gu, wg, wrong, wd, A, middle, C) == -3                             # M mismatch
+    wrong.free()
+    wrong = rk.Workspace(dom, rk.default_config(M, N, F + 32))
+    wd2 = rk.Weights(dom, *make_weights(F + 32, N, seed=3))
+    assert rk.run_ffn_f32(gu, wg, wrong, wd2, A, middle, C) == -3                            # F mismatch
+    free(wrong, wd2)
+    dn_other = rk.Workspace(other, rk.default_config(M, N, F))
+    wd_other = rk.Weights(other, Bd, sd)
+    assert rk.run_ffn_f32(gu, wg, dn_other, wd_other, A, middle, C) == capi.RK_NPU_ERR_DOMAIN
+    free(dn_other, wd_other)
+    # SwiGLU needs N % 64 == 0
+    odd = rk.Workspace(dom, rk.default_config(M, 96, K))
+    w_odd = rk.Weights(dom, *make_weights(K, 96, seed=4))
+    assert odd.run_swiglu_f32(w_odd, A, np.zeros((M, 48), np.float32)) == -3
+    free(odd, w_odd, gu, dn, wg, wd)
+
+
+def test_full_size_ffn_decode(gpu, oracle):
+    # BASELINE config 3 at M = 1: 4096 -> 2 x 14336 -> 4096, whole chain bit-exact vs the oracle
+    _, dom, _ = gpu
+    M, K, F, N = 1, 4096, 14336, 4096
+    Bg, sg = make_weights(K, 2 * F, seed=31)
+    Bd, sd = make_weights(F, N, seed=32)
+    wg, wd, gu, dn = build(dom, M, K, F, N, Bg, sg, Bd, sd)
+    A = make_activations(M, K, seed=31, dtype="f32")
+    middle, C = np.zeros((M, F), np.float32), np.zeros((M, N), np.float32)
+    assert rk.run_ffn_f32(gu, wg, dn, wd, A, middle, C) == 0
+    ref = oracle.ffn(A, Bg, sg, Bd, sd, mode=1)
+    assert np.array_equal(bits(middle), bits(ref["middle"])) and np.array_equal(bits(C), bits(ref["C"]))
+    free(gu, dn, wg, wd)

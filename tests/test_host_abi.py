@@ -1,0 +1,278 @@
+"""Host logic behind the C ABI that needs no GPU: the library loads and exports every
+declared entry point, the accounting and validation arithmetic equals the reference's,
+and tuning-cache files round-trip and interoperate with the reference's own build."""
+import ctypes as C
+import os
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from rknpu2_matmul_open_b200 import capi
+from rknpu2_matmul_open_b200.capi import (I4WeightConfig, W4A8AutotuneConfig, W4A8Config, W4A8MemoryInfo,
+                                          W4A8MemoryInfoEx, W4A8Options, W4A8Strategy, W4A8StrategyEx)
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def cfg_of(lib, m, n, k, **kw):
+    c = W4A8Config()
+    lib.rk_npu_w4a8_config_init(C.byref(c), m, n, k)
+    for k, v in kw.items():
+        setattr(c, k, v)
+    return c
+
+
+def test_library_exports_every_declared_symbol(lib):
+    declared = set()
+    for header in ("rknpu_b200_w4a8.h", "rknpu_b200_ext.h"):
+        text = (ROOT / "include" / header).read_text()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        declared |= set(re.findall(r"\b(rk_npu_\w+)\s*\(", text))
+    assert declared == set(capi.declared_symbols()), declared ^ set(capi.declared_symbols())
+    for name in declared:
+        assert hasattr(lib, name), name
+
+
+def test_no_gpu_means_open_fails_loudly(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    assert not lib.rk_npu_open(None)          # no CPU fallback: without a device there is no context
+    assert not lib.rk_npu_open(b"cuda:0")
+    assert not lib.rk_npu_open(b"renderD128")
+
+
+def test_defaults_and_strerror(lib):
+    c = cfg_of(lib, 7, 65, 513)
+    assert (c.M, c.N, c.K, c.m_tile, c.k_tile, c.n_tile, c.npu_core_mask, c.timeout_ms, c.pipeline, c.cpu_threads) == \
+        (7, 65, 513, 64, 480, 1024, 1, 500, 1, 1)
+    o = W4A8Options()
+    lib.rk_npu_w4a8_options_init(C.byref(o))
+    assert (o.struct_size, o.input_layout, o.reduce_backend) == (C.sizeof(W4A8Options), 0, 0)
+    a = W4A8AutotuneConfig()
+    lib.rk_npu_w4a8_autotune_config_init(C.byref(a), 1, 2, 3)
+    assert (a.M, a.N, a.K, a.activation_type, a.allowed_npu_core_mask, a.allowed_cpu_core_mask, a.warmup, a.loops,
+            a.repeats, a.timeout_ms, a.verbose, a.required_k_tile, a.k_tile_multiplier) == (1, 2, 3, 0, 7, 0, 2, 8, 3, 500, 0, 0, 0)
+    assert lib.rk_npu_strerror(0) == b"ok" and lib.rk_npu_strerror(-6) and lib.rk_npu_strerror(-99) == b"unknown error"
+
+
+def test_memory_query_known_answers(lib):
+    # tests/test_w4a8_cpu.cpp:143-152
+    info = W4A8MemoryInfo()
+    assert lib.rk_npu_w4a8_memory_query(C.byref(cfg_of(lib, 3, 65, 513)), C.byref(info)) == 0
+    assert info.weight_metadata_bytes == 520 and info.cpu_scratch_bytes == 3 * 128 * 4 + 3 * 8
+    assert lib.rk_npu_w4a8_memory_query(None, C.byref(info)) == -3
+    assert lib.rk_npu_w4a8_memory_query(C.byref(cfg_of(lib, 3, 65, 513)), None) == -3
+    # tests/test_w4a8_reduction.cpp:112-119
+    assert lib.rk_npu_w4a8_memory_query(C.byref(cfg_of(lib, 128, 4096, 11008)), C.byref(info)) == 0
+    assert info.backend.partial_bytes == 2 * 128 * 4096 * 4
+    # tests/test_w4a8_chain.cpp:46-50: all-K chain keeps every wave's partials
+    for M in (1, 2, 4, 8):
+        c = cfg_of(lib, M, 193, 1057, pipeline=capi.RK_NPU_W4A8_CHAIN)
+        assert lib.rk_npu_w4a8_memory_query(C.byref(c), C.byref(info)) == 0
+        assert info.backend.input_bytes == M * 1088 and info.backend.partial_bytes == 3 * 4 * M * 256
+    # weight bytes, tests/test_i4_cpu.cpp:43-47 (K513 N65 -> 544 x 128 / 2)
+    size = C.c_uint64()
+    assert lib.rk_npu_i4_weights_memory_query(C.byref(I4WeightConfig(513, 65, 480)), C.byref(size)) == 0
+    assert size.value == 34816
+    assert lib.rk_npu_i4_weights_memory_query(C.byref(I4WeightConfig(513, 65, 31)), C.byref(size)) == -3
+
+
+def test_memory_query_param_matrix(lib):
+    ok = cfg_of(lib, 5, 129, 1025)
+    ex = W4A8MemoryInfoEx()
+    assert lib.rk_npu_w4a8_memory_query_ex(C.byref(ok), None, C.byref(ex)) == 0
+    bad = dict(M=0, N=0, K=0, m_tile=0, k_tile=0, n_tile=32, npu_core_mask=5, timeout_ms=0, pipeline=3, cpu_threads=5)
+    for field, value in bad.items():
+        c = cfg_of(lib, 5, 129, 1025, **{field: value})
+        assert lib.rk_npu_w4a8_memory_query_ex(C.byref(c), None, C.byref(ex)) == -3, field
+    for field, value in dict(m_tile=65, k_tile=2080, n_tile=8192, K=(2 ** 31 - 1) // 1024 + 1).items():
+        c = cfg_of(lib, 5, 129, 1025, **{field: value})
+        assert lib.rk_npu_w4a8_memory_query_ex(C.byref(c), None, C.byref(ex)) == -3, field
+    assert lib.rk_npu_w4a8_memory_query_ex(C.byref(cfg_of(lib, 5, 64, 1025, npu_core_mask=7)), None, C.byref(ex)) == -3
+    o = W4A8Options()
+    lib.rk_npu_w4a8_options_init(C.byref(o))
+    o.struct_size = 4
+    assert lib.rk_npu_w4a8_memory_query_ex(C.byref(ok), C.byref(o), C.byref(ex)) == -3
+    lib.rk_npu_w4a8_options_init(C.byref(o))
+    o.reduce_backend = 1
+    assert lib.rk_npu_w4a8_memory_query_ex(C.byref(cfg_of(lib, 16, 129, 1025)), C.byref(o), C.byref(ex)) == 0
+    assert ex.effective_reduce_backend == 0       # M <= 16 falls back to the CPU-reduce policy
+    assert lib.rk_npu_w4a8_memory_query_ex(C.byref(cfg_of(lib, 33, 64, 480)), C.byref(o), C.byref(ex)) == 0
+    assert ex.effective_reduce_backend == 1 and ex.reduction_control_bytes == 584
+    c = cfg_of(lib, 33, 64, 480, pipeline=capi.RK_NPU_W4A8_CHAIN)
+    assert lib.rk_npu_w4a8_memory_query_ex(C.byref(c), C.byref(o), C.byref(ex)) == -3   # chain + NPU reduce
+
+
+def _fields(s):
+    out = []
+    for name, _ in s._fields_:
+        v = getattr(s, name)
+        out.extend(_fields(v) if isinstance(v, C.Structure) else [v])
+    return out
+
+
+def test_memory_query_equals_reference_build(lib, reference):
+    ref = reference.lib
+    rng = np.random.Generator(np.random.PCG64(7))
+    checked = accepted = 0
+    for _ in range(4000):
+        M = int(rng.choice([1, 2, 3, 8, 16, 17, 33, 64, 65, 128, 129, 257, 1024]))
+        N = int(rng.choice([1, 64, 65, 129, 193, 256, 1025, 4096, 11008]))
+        K = int(rng.choice([1, 33, 480, 513, 1025, 2049, 4096, 20003]))
+        c = cfg_of(lib, M, N, K, m_tile=int(rng.choice([1, 3, 4, 8, 16, 64, 65, 128, 256, 257])),
+                   k_tile=int(rng.choice([32, 256, 480, 992, 2048, 2080, 100])),
+                   n_tile=int(rng.choice([64, 128, 1024, 1408, 8128, 8192, 96])),
+                   npu_core_mask=int(rng.choice([1, 2, 3, 4, 7, 5])), pipeline=int(rng.integers(0, 4)),
+                   cpu_threads=int(rng.integers(0, 6)))
+        o = W4A8Options(C.sizeof(W4A8Options), int(rng.integers(0, 2)), int(rng.integers(0, 2)))
+        mine, theirs = W4A8MemoryInfoEx(), W4A8MemoryInfoEx()
+        rc_mine = lib.rk_npu_w4a8_memory_query_ex(C.byref(c), C.byref(o), C.byref(mine))
+        rc_ref = ref.rk_npu_w4a8_memory_query_ex(C.byref(c), C.byref(o), C.byref(theirs))
+        assert rc_mine == rc_ref, (_fields(c), _fields(o), rc_mine, rc_ref)
+        if rc_ref == 0:
+            assert _fields(mine) == _fields(theirs), (_fields(c), _fields(o))
+            accepted += 1
+        checked += 1
+    assert accepted > 200 and checked == 4000
+
+
+# ------------------------------------------------------------------ tuning cache
+def _affinity_first(n):
+    cpus = sorted(os.sched_getaffinity(0))
+    order = [c for c in range(4, 8) if c in cpus] + [c for c in cpus if c < 4 or c > 7]
+    return sum(1 << c for c in order[:n] if c < 64), min(n, len(order))
+
+
+def _strategy(lib, ctx, c, B, sw, k_tile, safe, fingerprint, m_tile=64, layout=0):
+    cpu_mask, threads = _affinity_first(4)
+    s = W4A8StrategyEx()
+    s.base.config = cfg_of(lib, c.M, c.N, c.K, m_tile=m_tile, k_tile=k_tile, n_tile=256, npu_core_mask=7,
+                           timeout_ms=c.timeout_ms, pipeline=1, cpu_threads=threads)
+    s.base.activation_type = c.activation_type
+    s.base.cpu_core_mask = cpu_mask
+    s.base.weights.config = I4WeightConfig(c.K, c.N, k_tile)
+    s.base.weights.safe_k_tile = safe
+    s.base.weights.multiplier = 1.0
+    s.base.weights.bound_relaxed = 0
+    s.base.weight_fingerprint = fingerprint
+    s.base.tuning_revision = 5
+    s.base.total_us, s.base.robust_us = 1.25, 1.5
+    s.execution = W4A8Options(C.sizeof(W4A8Options), layout, 0)
+    return s
+
+
+@pytest.fixture()
+def cache_case(lib, oracle, tmp_path, monkeypatch):
+    monkeypatch.delenv("RK_NPU_W4A8_CHAIN_MAX_M", raising=False)
+    monkeypatch.delenv("RK_NPU_W4A8_K_TILE_MULTIPLIER", raising=False)
+    ctx = lib.rk_npu_b200_open_offline(0x908)
+    assert ctx and lib.rk_npu_b200_device(ctx) == -1
+    assert not lib.rk_npu_iommu_domain_create(ctx, 0)     # an offline context can do no device work
+    c = W4A8AutotuneConfig()
+    lib.rk_npu_w4a8_autotune_config_init(C.byref(c), 128, 193, 2048)
+    c.k_tile_multiplier = 1.0
+    c.required_k_tile = 2048
+    B = np.ones((c.K, c.N), np.int8)
+    sw = np.full(c.N, .125, np.float32)
+    rc, safe, _, _, mask = oracle.bound(B)
+    assert rc == 0 and safe == 2048
+    s = _strategy(lib, ctx, c, B, sw, 2048, safe, oracle.fingerprint(B, sw), m_tile=128, layout=1)
+    yield lib, ctx, c, B, sw, s, str(tmp_path / "entry.tune")
+    lib.rk_npu_close(ctx)
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def test_cache_round_trip_and_invalidation(cache_case):
+    lib, ctx, c, B, sw, s, path = cache_case
+    p = path.encode()
+    f, st = W4A8StrategyEx(), W4A8StrategyEx()
+    assert lib.rk_npu_w4a8_autotune_cache_load_ex(ctx, C.byref(c), _p(B), _p(sw), p, C.byref(f), C.byref(st)) == -9   # absent
+    assert lib.rk_npu_w4a8_autotune_cache_save_ex(ctx, C.byref(c), _p(B), _p(sw), p, C.byref(s), C.byref(s)) == 0
+    assert lib.rk_npu_w4a8_autotune_cache_load_ex(ctx, C.byref(c), _p(B), _p(sw), p, C.byref(f), C.byref(st)) == 0
+    assert f.execution.input_layout == 1 and f.base.config.m_tile == 128 and f.base.total_us == 1.25
+    assert _fields(f) == _fields(s) and _fields(st) == _fields(s)
+    lines = Path(path).read_text().splitlines()
+    assert lines[0] == "rk_npu_w4a8_tuning_cache_v2" and lines[2].startswith("fastest ") and lines[3].startswith("stable ")
+    assert lines[1].split()[:7] == ["5", "3", str(0x908), "128", "193", "2048", "0"]
+    # the native-only (legacy) lookup uses another search-space id and must miss
+    lf, ls = W4A8Strategy(), W4A8Strategy()
+    assert lib.rk_npu_w4a8_autotune_cache_load(ctx, C.byref(c), _p(B), _p(sw), p, C.byref(lf), C.byref(ls)) == -9
+    # every key component invalidates: weights, scales, shape, measurement settings, dtype
+    B2 = B.copy(); B2[5, 5] = 2
+    assert lib.rk_npu_w4a8_autotune_cache_load_ex(ctx, C.byref(c), _p(B2), _p(sw), p, C.byref(f), C.byref(st)) == -9
+    sw2 = sw.copy(); sw2[0] = .25
+    assert lib.rk_npu_w4a8_autotune_cache_load_ex(ctx, C.byref(c), _p(B), _p(sw2), p, C.byref(f), C.byref(st)) == -9
+    for field, value in dict(loops=9, warmup=3, repeats=4, timeout_ms=400, activation_type=1).items():
+        c2 = W4A8AutotuneConfig.from_buffer_copy(c)
+        setattr(c2, field, value)
+        assert lib.rk_npu_w4a8_autotune_cache_load_ex(ctx, C.byref(c2), _p(B), _p(sw), p, C.byref(f), C.byref(st)) == -9, field
+    other = lib.rk_npu_b200_open_offline(0x909)      # another driver version
+    assert lib.rk_npu_w4a8_autotune_cache_load_ex(other, C.byref(c), _p(B), _p(sw), p, C.byref(f), C.byref(st)) == -9
+    lib.rk_npu_close(other)
+    # trailing bytes, an old magic line
+    text = Path(path).read_text()
+    Path(path).write_text(text + "junk\n")
+    assert lib.rk_npu_w4a8_autotune_cache_load_ex(ctx, C.byref(c), _p(B), _p(sw), p, C.byref(f), C.byref(st)) == -9
+    Path(path).write_text(text.replace("cache_v2", "cache_v1", 1))
+    assert lib.rk_npu_w4a8_autotune_cache_load_ex(ctx, C.byref(c), _p(B), _p(sw), p, C.byref(f), C.byref(st)) == -9
+    Path(path).write_text(text)
+    assert lib.rk_npu_w4a8_autotune_cache_load_ex(ctx, C.byref(c), _p(B), _p(sw), p, C.byref(f), C.byref(st)) == 0
+
+
+def test_cache_rejects_invalid_strategies(cache_case):
+    lib, ctx, c, B, sw, s, path = cache_case
+    p = path.encode()
+    for mutate in ("layout", "reduce", "size", "revision", "threads", "pipeline", "fingerprint", "ktile"):
+        bad = W4A8StrategyEx.from_buffer_copy(s)
+        if mutate == "layout": bad.execution.input_layout = 7
+        if mutate == "reduce": bad.execution.reduce_backend = 1
+        if mutate == "size": bad.execution.struct_size = 0
+        if mutate == "revision": bad.base.tuning_revision = 4
+        if mutate == "threads": bad.base.config.cpu_threads = 3 if s.base.config.cpu_threads != 3 else 2
+        if mutate == "pipeline": bad.base.config.pipeline = 3
+        if mutate == "fingerprint": bad.base.weight_fingerprint ^= 1
+        if mutate == "ktile": bad.base.config.k_tile = 480
+        assert lib.rk_npu_w4a8_autotune_cache_save_ex(ctx, C.byref(c), _p(B), _p(sw), p, C.byref(bad), C.byref(bad)) == -3, mutate
+    assert lib.rk_npu_w4a8_autotune_cache_save_ex(ctx, C.byref(c), _p(B), _p(sw), b"", C.byref(s), C.byref(s)) == -3
+    assert lib.rk_npu_w4a8_autotune_cache_save_ex(None, C.byref(c), _p(B), _p(sw), p, C.byref(s), C.byref(s)) == -3
+
+
+def test_cache_environment_is_part_of_the_key(cache_case, monkeypatch):
+    lib, ctx, c, B, sw, s, path = cache_case
+    p = path.encode()
+    f, st = W4A8StrategyEx(), W4A8StrategyEx()
+    assert lib.rk_npu_w4a8_autotune_cache_save_ex(ctx, C.byref(c), _p(B), _p(sw), p, C.byref(s), C.byref(s)) == 0
+    for value in ("0", "2", "16", "64"):
+        monkeypatch.setenv("RK_NPU_W4A8_CHAIN_MAX_M", value)
+        assert lib.rk_npu_w4a8_autotune_cache_load_ex(ctx, C.byref(c), _p(B), _p(sw), p, C.byref(f), C.byref(st)) == -9
+    for value in ("", "-1", "65", "eight", "99999999999999999"):
+        monkeypatch.setenv("RK_NPU_W4A8_CHAIN_MAX_M", value)
+        assert lib.rk_npu_w4a8_autotune_cache_load_ex(ctx, C.byref(c), _p(B), _p(sw), p, C.byref(f), C.byref(st)) == -3
+    monkeypatch.setenv("RK_NPU_W4A8_CHAIN_MAX_M", "8")
+    assert lib.rk_npu_w4a8_autotune_cache_load_ex(ctx, C.byref(c), _p(B), _p(sw), p, C.byref(f), C.byref(st)) == 0
+
+
+def test_cache_files_interoperate_with_reference_build(cache_case, reference, tmp_path):
+    """A file written by this library is a hit for the reference's loader and the reverse."""
+    lib, ctx, c, B, sw, s, path = cache_case
+    ref = reference.lib
+    # the reference's context object: fd at offset 0, driver version at offset 16
+    fake = (C.c_uint8 * 8192)()
+    C.cast(fake, C.POINTER(C.c_int))[0] = -1
+    C.cast(C.byref(fake, 16), C.POINTER(C.c_uint32))[0] = 0x908
+    f, st = W4A8StrategyEx(), W4A8StrategyEx()
+    assert lib.rk_npu_w4a8_autotune_cache_save_ex(ctx, C.byref(c), _p(B), _p(sw), path.encode(), C.byref(s), C.byref(s)) == 0
+    assert ref.rk_npu_w4a8_autotune_cache_load_ex(fake, C.byref(c), _p(B), _p(sw), path.encode(), C.byref(f), C.byref(st)) == 0
+    assert _fields(f) == _fields(s)
+    theirs = str(tmp_path / "theirs.tune").encode()
+    assert ref.rk_npu_w4a8_autotune_cache_save_ex(fake, C.byref(c), _p(B), _p(sw), theirs, C.byref(s), C.byref(s)) == 0
+    f2, st2 = W4A8StrategyEx(), W4A8StrategyEx()
+    assert lib.rk_npu_w4a8_autotune_cache_load_ex(ctx, C.byref(c), _p(B), _p(sw), theirs, C.byref(f2), C.byref(st2)) == 0
+    assert _fields(f2) == _fields(s)
+    assert Path(path).read_bytes() == Path(theirs.decode()).read_bytes()
