@@ -1,0 +1,445 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A8 hot path on B200 (one JSON line on stdout, rank 0).
+
+Workload (default, BASELINE config 1): Llama-7B decode linears, fp16 in/out, M tokens
+(default 8; 1 is reported beside it): per decoder layer four 4096->4096, two
+4096->11008 and one 11008->4096 projection.  A step is one pass over a ring of
+`--layers` distinct layers (>= 2x L2 of distinct weights, so nothing is re-read from
+cache); weights are prepared once outside the timed region, as the reference's own
+benchmark does.  `value` is algorithmic GB/s with activations resident in HBM (enqueue
+entry points, one CUDA graph per step when capture works); `e2e` is the same pass through
+the blocking reference ABI with pinned HOST activations and outputs, copies included.
+
+N > 1 (torchrun): every linear is column-sharded over the ranks in contiguous 64-column
+blocks (the reference's per-core split) and the shard outputs are reassembled by one
+NCCL all-gather per step; total work is fixed, so scaling is "strong".
+
+`--impl reference` times the reference's own CPU stages (oracle/_ref, or the C port when
+that was not built) on the host cores for the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LLAMA7B_LAYER = [(4096, 4096)] * 4 + [(4096, 11008)] * 2 + [(11008, 4096)]   # (K, N)
+
+
+def algorithmic_bytes(M, K, N, in_bytes=2, out_bytes=2):
+    """Packed int4 weights + fp32 channel scales + activations in + outputs out."""
+    return K * N // 2 + 4 * N + in_bytes * M * K + out_bytes * M * N
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(device)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        rows = [r.split(",") for r in Path(self.file.name).read_text().splitlines() if r.count(",") >= 8]
+        os.unlink(self.file.name)
+        clocks, reasons = [], set()
+        for r in rows:
+            try:
+                clocks.append(float(r[1]))
+                out["sm_max_mhz"] = float(r[2])
+            except ValueError:
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                if r[col].strip().lower() == "active":
+                    reasons.add(name)
+        if clocks:
+            busy = [c for c in clocks if c >= 0.5 * max(clocks)]
+            out["sm_mhz"] = statistics.median(busy)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def shard_columns(N: int, world: int, rank: int):
+    """Contiguous 64-column blocks, the first `blocks % world` ranks one block more
+    (the reference's split over NPU cores, src/rk_npu_i4_plan.cpp:37-43)."""
+    blocks = (N + 63) // 64
+    start = 0
+    for r in range(world):
+        count = blocks // world + (1 if r < blocks % world else 0)
+        if r == rank:
+            return min(N, start * 64), min(N, (start + count) * 64)
+        start += count
+    raise ValueError(rank)
+
+
+# ------------------------------------------------------------------ reference arm (CPU)
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    from oracle.harness import Oracle, Reference, make_activations, make_weights
+    M = args.tokens
+    use_ref = Reference.available()
+    ref = Reference() if use_ref else None
+    orc = Oracle()
+    shapes = [(4096, 4096), (4096, 11008), (11008, 4096)]
+    counts = [4, 2, 1]
+    layers = []
+    for i, (K, N) in enumerate(shapes):
+        B, sw = make_weights(K, N, seed=i)
+        A = make_activations(M, K, seed=i, dtype="f16")
+        handle = ref.layer(B, sw, 480) if use_ref else None
+        layers.append((K, N, B, sw, A, handle))
+    cores = ref.host_threads() if use_ref else int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+
+    def one_pass():
+        t0 = time.perf_counter()
+        for (K, N, B, sw, A, handle), count in zip(layers, counts):
+            for _ in range(count):
+                if use_ref:
+                    rc, _, _ = ref.layer_run(handle[0], handle[1], A, threads=4)
+                else:
+                    rc = orc.linear(A, B, sw)[0]
+                assert rc == 0
+        return time.perf_counter() - t0
+
+    for _ in range(args.warmup):
+        one_pass()
+    t = sum(one_pass() for _ in range(args.steps))
+    step_bytes = sum(algorithmic_bytes(M, K, N) * c for (K, N), c in zip(shapes, counts))
+    step_ops = sum(2 * M * K * N * c for (K, N), c in zip(shapes, counts))
+    gbs = step_bytes * args.steps / t / 1e9
+    sample = (f"one decoder layer (4x 4096->4096, 2x 4096->11008, 1x 11008->4096) at M={M} per step; "
+              + ("reference CPU stages (scan, MSD pack, INT16 reconstruct, dequant: 4 threads) around an "
+                 "all-core int4 stand-in for the NPU step" if use_ref else "C port of the reference path"))
+    line = {"impl": "reference", "metric": "w4a8_decode_weight_stream", "value": gbs, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": workload_config(args, world, layers=1),
+            "tops": step_ops * args.steps / t / 1e12,
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "reference" if use_ref else "port",
+                             "sample": sample},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(args, world, layers):
+    return {"workload": f"llama7b_decode_linears_M{args.tokens}", "shapes_KxN": "4x4096x4096+2x4096x11008+1x11008x4096",
+            "ring_layers": layers, "activation": "fp16 N(0,1), 0.5% channels x20", "weights": "int4 [-7,7] per-channel",
+            "cache": "ring of distinct weights larger than 2x L2, no flush needed", "parallelism": f"column-shard x{world}"}
+
+
+# ------------------------------------------------------------------ CUDA arm
+def run_cuda(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    import rknpu2_matmul_open_b200 as rk
+    from oracle.harness import Oracle, Reference, make_activations, make_weights, sample_columns
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = rk.Context(f"cuda:{local_rank}")
+    dom = ctx.domain(0)
+    M = args.tokens
+    hbm_peak, _, peak_kind = measured_peaks()
+
+    # ---- the ring: `layers` distinct decoder layers, each linear column-sharded over ranks
+    linears = []          # dicts: K, N(full), n0, n1, weights, workspace, dA, dC, hA, hC
+    act = {}
+    for K in (4096, 11008):
+        A = make_activations(M, K, seed=K, dtype="f16")
+        act[K] = (A, torch.from_numpy(A.view(np.int16)).to(dev))
+    check = None
+    generated = {}
+    for layer in range(args.layers):
+        for j, (K, N) in enumerate(LLAMA7B_LAYER):
+            seed = (layer * 16 + j) if args.distinct_values else j
+            if (K, N, seed) not in generated:
+                generated[(K, N, seed)] = make_weights(K, N, seed=seed)
+            B, sw = generated[(K, N, seed)]
+            n0, n1 = shard_columns(N, world, rank)
+            Bs, ss = np.ascontiguousarray(B[:, n0:n1]), np.ascontiguousarray(sw[n0:n1])
+            w = rk.Weights(dom, Bs, ss, k_tile=480)
+            ws = rk.Workspace(dom, rk.default_config(M, n1 - n0, K, k_tile=480))
+            dC = torch.zeros((M, n1 - n0), dtype=torch.int16, device=dev)
+            hA = torch.from_numpy(act[K][0].view(np.int16)).pin_memory()
+            hC = torch.zeros((M, n1 - n0), dtype=torch.int16).pin_memory()
+            linears.append(dict(K=K, N=N, n0=n0, n1=n1, w=w, ws=ws, dA=act[K][1], dC=dC, hA=hA, hC=hC))
+            if check is None:
+                check = (act[K][0], Bs, ss, len(linears) - 1)
+    step_bytes = sum(algorithmic_bytes(M, l["K"], l["N"]) for l in linears)          # whole job, all ranks
+    step_ops = sum(2 * M * l["K"] * l["N"] for l in linears)
+    out_cols = sum(l["n1"] - l["n0"] for l in linears)
+    gather_in = gather_out = None
+    if world > 1:
+        pad = max(int(x) for x in _all_gather_ints(dist, out_cols, world, dev))
+        gather_in = torch.zeros((M * pad,), dtype=torch.int16, device=dev)
+        gather_out = torch.zeros((world * M * pad,), dtype=torch.int16, device=dev)
+
+    stream = torch.cuda.Stream(device=dev)
+
+    def enqueue_step(s):
+        for l in linears:
+            rc = l["ws"].enqueue_f16(l["w"], l["dA"], l["dC"], s.cuda_stream)
+            if rc:
+                raise RuntimeError(f"enqueue failed: {rc}")
+        if world > 1:
+            offset = 0
+            for l in linears:     # pack the shard outputs, then reassemble them on every rank
+                n = M * (l["n1"] - l["n0"])
+                gather_in[offset:offset + n].copy_(l["dC"].reshape(-1), non_blocking=True)
+                offset += n
+            dist.all_gather_into_tensor(gather_out, gather_in)
+
+    # ---- correctness of what is timed: first linear of the ring against the oracle
+    oracle = Oracle()
+    with torch.cuda.stream(stream):
+        enqueue_step(stream)
+    stream.synchronize()
+    A0, B0, s0, idx = check
+    ref_out = oracle.linear(A0, B0, s0)[1]
+    got = linears[idx]["dC"].cpu().numpy().view(np.uint16)
+    if not np.array_equal(got, ref_out):
+        raise RuntimeError("CUDA output differs from the oracle; refusing to report a number")
+    for l in linears:
+        if l["ws"].finish() != 0:
+            raise RuntimeError("device status not clean after the check step")
+
+    # ---- device-resident timing (value)
+    graph = None
+    if not args.no_graph and world == 1:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                enqueue_step(stream)
+        except Exception as exc:   # capture is an optimisation; plain stream launches are the fallback
+            print(f"[bench] graph capture unavailable ({type(exc).__name__}: {exc}); using stream launches", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+
+    def do_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            enqueue_step(stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(3, args.warmup)):
+            do_step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(args.steps):
+            do_step()
+        e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_step = ms / args.steps
+
+    # ---- end to end through the blocking reference ABI, pinned host tensors
+    def e2e_step():
+        for l in linears:
+            rc = l["ws"].run_f16(l["w"], l["hA"], l["hC"])
+            if rc:
+                raise RuntimeError(f"run_f16 failed: {rc}")
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    e2e_steps = max(1, min(args.steps, 10))
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    clocks = sampler.stop() if sampler else None
+    h2d = sum(M * l["K"] * 2 for l in linears)
+    d2h = sum(M * (l["n1"] - l["n0"]) * 2 for l in linears)
+
+    # ---- M = 1 beside it (single GPU only, same ring)
+    also = {}
+    if world == 1 and args.tokens != 1 and not args.quick:
+        also["M1_GBps"] = _time_other_m(rk, dom, linears, 1, args, dev, stream)
+
+    # ---- CPU baseline on a bounded sample (rank 0, one GPU only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline(M, Reference if Reference.available() else None, oracle, make_weights, make_activations)
+
+    if rank == 0:
+        launches = 2 * len(linears) * args.steps
+        value = step_bytes / (ms_step * 1e-3) / 1e9
+        gemm_bytes_per_launch = step_bytes / len(linears)
+        line = {"metric": "w4a8_decode_weight_stream", "value": value, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+                "config": workload_config(args, world, args.layers),
+                "tops": step_ops / (ms_step * 1e-3) / 1e12,
+                "launch_mode": "cuda_graph" if graph is not None else "stream",
+                "clocks": clocks,
+                "e2e": {"value": step_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                        "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * e2e_s},
+                "gpu_launches": launches,
+                "roofline": {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
+                             "frac": value / world / hbm_peak, "traffic": None, "peak_kind": peak_kind,
+                             "kernel": "gemm_mma_kernel (+ quantize_kernel in the same interval)",
+                             "bytes_per_launch": gemm_bytes_per_launch,
+                             "us_per_launch": 1e3 * ms_step / len(linears)},
+                "cpu_baseline": cpu, "also": also}
+        print(json.dumps(line))
+    for l in linears:
+        l["ws"].free()
+        l["w"].free()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _all_gather_ints(dist, value, world, dev):
+    import torch
+    t = torch.tensor([value], device=dev, dtype=torch.int64)
+    out = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(out, t)
+    return [int(x.item()) for x in out]
+
+
+def _time_other_m(rk, dom, linears, M, args, dev, stream):
+    import torch
+    from oracle.harness import make_activations
+    extra = []
+    act = {K: torch.from_numpy(make_activations(M, K, seed=K, dtype="f16").view(np.int16)).to(dev) for K in (4096, 11008)}
+    for l in linears:
+        ws = rk.Workspace(dom, rk.default_config(M, l["n1"] - l["n0"], l["K"], k_tile=480))
+        extra.append((ws, l["w"], act[l["K"]], torch.zeros((M, l["n1"] - l["n0"]), dtype=torch.int16, device=dev), l))
+
+    def step():
+        for ws, w, dA, dC, _ in extra:
+            ws.enqueue_f16(w, dA, dC, stream.cuda_stream)
+
+    graph = None
+    if not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step()
+        except Exception:
+            graph = None
+            torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            graph.replay() if graph else step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay() if graph else step()
+        e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    total = sum(algorithmic_bytes(M, l["K"], l["N"]) for l in linears)
+    for ws, *_ in extra:
+        ws.free()
+    return total / (ms * 1e-3) / 1e9
+
+
+def cpu_baseline(M, Reference, oracle, make_weights, make_activations):
+    """One decoder layer's seven linears on the host, reference stages when built."""
+    shapes, counts = [(4096, 4096), (4096, 11008), (11008, 4096)], [4, 2, 1]
+    ref = Reference() if Reference else None
+    prepared = []
+    for i, (K, N) in enumerate(shapes):
+        B, sw = make_weights(K, N, seed=i)
+        A = make_activations(M, K, seed=i, dtype="f16")
+        prepared.append((K, N, B, sw, A, ref.layer(B, sw, 480) if ref else None))
+    best = None
+    for _ in range(3):
+        t0 = time.perf_counter()
+        for (K, N, B, sw, A, handle), count in zip(prepared, counts):
+            for _ in range(count):
+                if ref:
+                    ref.layer_run(handle[0], handle[1], A, threads=4)
+                else:
+                    oracle.linear(A, B, sw)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    total = sum(algorithmic_bytes(M, K, N) * c for (K, N), c in zip(shapes, counts))
+    cores = ref.host_threads() if ref else int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+    return {"value": total / best / 1e9, "unit": "GB/s", "cores": cores, "kind": "reference" if ref else "port",
+            "sample": f"one decoder layer (7 linears) at M={M}, best of 3 passes, {best * 1e3:.1f} ms per pass"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--tokens", type=int, default=8, help="decode batch M (BASELINE config 1 uses 1 and 8)")
+    ap.add_argument("--layers", type=int, default=4, help="distinct decoder layers in the ring (4 = 405 MB of int4)")
+    ap.add_argument("--distinct-values", action="store_true", help="different weight values per ring layer (slower setup)")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--quick", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    run_cuda(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -55,14 +55,26 @@ int rk_npu_b200_w4a8_finish(rk_npu_w4a8_workspace *workspace);
 int rk_npu_b200_w4a8_run_acc_i32(rk_npu_w4a8_workspace *workspace, const rk_npu_w4a8_weights *weights,
                                  const void *A, int activation_is_f16, int32_t *acc);
 
-/* Diagnostic: the per-token scales and int8 codes [M,K] the last call on this workspace
- * quantised its activations to (host pointers; either may be NULL). Blocking. */
+/* Diagnostic: the per-token scales of the last call on this workspace and the int8 codes
+ * [M,K] its activations were quantised to (host pointers; either may be NULL).  The codes
+ * are those of the last rk_npu_b200_w4a8_run_acc_i32 call when the workspace runs the
+ * single-kernel small-batch path, which otherwise keeps them in shared memory only. Blocking. */
 int rk_npu_b200_w4a8_last_quant(rk_npu_w4a8_workspace *workspace, float *scales, int8_t *codes);
 
-/* Scheduling override for experiments and tuning: variant 0 = automatic, 1 = the
- * mma.sync kernel, 2 = the tcgen05 kernel; split_k 0 = automatic, else 1, 2, 4 or 8.
+/* Scheduling override for experiments and tuning.  variant: 0 = keep, else it must equal
+ * the workspace's kernel family (1 quantise + mma.sync GEMM, 2 quantise + tcgen05 GEMM,
+ * 3 single-kernel small batch; chosen at creation, RK_NPU_B200_VARIANT overrides).
+ * split_k: 0 = automatic, else the split-K factor (1..8 for family 3; 1, 2, 4, 8 otherwise).
  * Returns RK_NPU_ERR_PARAM when the workspace geometry cannot run the request. */
 int rk_npu_b200_w4a8_set_schedule(rk_npu_w4a8_workspace *workspace, int variant, int split_k);
+
+/* Diagnostics: with tracing enabled the small-batch kernel records eight global-timer
+ * stamps (ns) per CTA -- start, weights requested, dependency met, scales known, slice
+ * quantised, contraction done, partials exchanged, outputs stored -- for the latest launch.
+ * trace_read copies stamps[ctas][8] to the host (CTA index = blockIdx.y * gridDim.x + blockIdx.x,
+ * at most 16384 CTAs).  The caller synchronises first. */
+int rk_npu_b200_w4a8_trace_enable(rk_npu_w4a8_workspace *workspace, int enable);
+int rk_npu_b200_w4a8_trace_read(rk_npu_w4a8_workspace *workspace, unsigned long long *stamps, int ctas);
 
 /* Kernels this workspace has launched since creation (for launch accounting). */
 uint64_t rk_npu_b200_w4a8_launch_count(const rk_npu_w4a8_workspace *workspace);

@@ -252,10 +252,30 @@ struct Call {
     bool half;
     int epi;
     uint32_t* rowmax_out;  // SwiGLU row maxima to collect (device) or nullptr
-    const uint32_t* rowmax_in;  // scales come from these instead of a scan
+    uint32_t* rowmax_in;   // scales come from these instead of a scan (cleared after use)
     cudaStream_t stream;
     cudaEvent_t* events;   // nullptr or three events: start, after quantise, after GEMM
+    bool keep_codes = false;   // fused kernel: also store the activation codes (diagnostic entry only)
 };
+
+// Split-K factor (= cluster size) of the single-kernel path: the largest split whose CTAs
+// are all resident at once (each holds its whole weight slice in shared memory).
+int fused_split(const rk_npu_w4a8_workspace& ws, int tiles)
+{
+    if (ws.split_override) return ws.split_override;
+    const int sms = ws.domain->ctx->sm_count;
+    const size_t smem_per_sm = 220 * 1024;
+    int best = 0;
+    for (int split = 1; split <= 8; ++split) {
+        const int stages = (ws.KB + split - 1) / split;
+        if (stages > FUSED_MAX_STAGES) continue;
+        if (!best) best = split;
+        const size_t bytes = gemm_fused_smem_bytes(ws.TC, stages) + 1024;
+        const long long slots = (long long)sms * std::min<long long>(8, (long long)(smem_per_sm / bytes));
+        if ((long long)tiles * split <= slots) best = split;
+    }
+    return best ? best : 8;
+}
 
 int enqueue(const Call& c)
 {
@@ -263,12 +283,40 @@ int enqueue(const Call& c)
     const auto& cfg = ws.config;
     const bool pdl = env_flag("RK_NPU_B200_PDL", true);
     if (c.events) cudaEventRecord(c.events[0], c.stream);
+    const int F = c.epi == EPI_SWIGLU ? cfg.N / 2 : 0;
+    const int tiles = c.epi == EPI_SWIGLU ? (F + 63) / 64 : c.w->NG / 4;
+    const unsigned long long timeout_ns = (unsigned long long)cfg.timeout_ms * 1000000ull;
+    if (ws.variant == 3) {
+        // One kernel: scan + quantise + GEMM + epilogue.
+        FusedParams f{};
+        f.Wp = c.w->packed;
+        f.A = c.dA;
+        f.sw = c.w->scales;
+        f.out = c.dOut;
+        f.rowmax_out = c.rowmax_out;
+        f.rowmax_in = c.rowmax_in;
+        f.scales_out = ws.scales;
+        f.codes_out = c.keep_codes ? ws.codes : nullptr;
+        f.status = ws.status;
+        f.M = cfg.M; f.N = cfg.N; f.K = cfg.K;
+        f.KB = ws.KB; f.NG = c.w->NG; f.F = F; f.epi = c.epi;
+        f.split = fused_split(ws, tiles);
+        f.stages = (ws.KB + f.split - 1) / f.split;
+        f.half = c.half ? 1 : 0;
+        f.timeout_ns = timeout_ns;
+        f.trace = ws.trace;
+        if (c.events) cudaEventRecord(c.events[1], c.stream);
+        if (launch_gemm_fused(f, ws.TC, c.stream, pdl) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+        if (c.events) cudaEventRecord(c.events[2], c.stream);
+        ws.launches.fetch_add(1, std::memory_order_relaxed);
+        return RK_NPU_OK;
+    }
     QuantParams q{};
     q.A = c.dA;
     q.Xq = ws.codes;
     q.scales = ws.scales;
     q.inverse = ws.inverse;
-    q.rowmax_zero = c.rowmax_out;
+    q.rowmax_zero = nullptr;
     q.rowmax = c.rowmax_in;
     q.status = ws.status;
     q.host_flag = nullptr;
@@ -277,7 +325,7 @@ int enqueue(const Call& c)
     q.Kp = ws.KB * KBLOCK;
     q.T = ws.T;
     q.half = c.half ? 1 : 0;
-    if (launch_quantize(q, c.stream, pdl) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    if (launch_quantize(q, c.stream, pdl) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
     if (c.events) cudaEventRecord(c.events[1], c.stream);
 
     GemmParams g{};
@@ -294,15 +342,14 @@ int enqueue(const Call& c)
     g.KB = ws.KB;
     g.NG = c.w->NG;
     g.T = ws.T;
-    g.F = c.epi == EPI_SWIGLU ? cfg.N / 2 : 0;
+    g.F = F;
     g.epi = c.epi;
-    g.timeout_ns = (unsigned long long)cfg.timeout_ms * 1000000ull;
+    g.timeout_ns = timeout_ns;
     cudaError_t err;
-    if (ws.TC == 0) {
+    if (ws.variant == 2) {
         g.split = 1;
         err = launch_gemm_tc(g, c.stream, pdl);
     } else {
-        const int tiles = c.epi == EPI_SWIGLU ? (g.F + 63) / 64 : g.NG / 4;
         g.split = pick_split(ws, tiles, (cfg.M + ws.TC - 1) / ws.TC);
         err = launch_gemm_mma(g, ws.TC, c.stream, pdl);
     }
@@ -352,7 +399,7 @@ int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const vo
     }
     if (!c_dev) dC = ws->stage_out;
     t.sync_us += elapsed_us(copy_start);
-    Call call{ws, w, dA, dC, half, epi, nullptr, nullptr, s, metrics ? ws->events : nullptr};
+    Call call{ws, w, dA, dC, half, epi, nullptr, nullptr, s, metrics ? ws->events : nullptr, epi == EPI_I32};
     int rc = enqueue(call);
     if (rc) { cudaStreamSynchronize(s); return rc; }
     copy_start = Clock::now();
@@ -363,7 +410,7 @@ int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const vo
     rc = status_to_rc(*ws, s);
     if (metrics) {
         t.activation_scan_us = event_us(ws->events[0], ws->events[1]);
-        t.submit_us = rc ? 0.0 : event_us(ws->events[1], ws->events[2]);
+        t.submit_us = rc ? 0.0 : event_us(ws->events[1], ws->events[2]);   // a rejected input did no GEMM work
         t.total_us = elapsed_us(start);
         *metrics = t;
     }
@@ -392,6 +439,7 @@ void workspace_destroy(rk_npu_w4a8_workspace* ws)
     if (ws->status) device_free(d, ws->status, sizeof(Status));
     if (ws->stage_in) device_free(d, ws->stage_in, ws->stage_in_bytes);
     if (ws->stage_out) device_free(d, ws->stage_out, ws->stage_out_bytes);
+    if (ws->trace) device_free(d, ws->trace, ws->trace_bytes);
     if (ws->host_status) cudaFreeHost(ws->host_status);
     for (auto& e : ws->events) if (e) cudaEventDestroy(e);
     if (ws->stream) cudaStreamDestroy(ws->stream);
@@ -738,15 +786,17 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
     GemmParams probe{};
     probe.M = cfg->M; probe.N = cfg->N; probe.K = cfg->K; probe.KB = ws->KB;
     const int forced = std::getenv("RK_NPU_B200_VARIANT") ? std::atoi(std::getenv("RK_NPU_B200_VARIANT")) : 0;
-    const bool use_tc = forced == 2 ? gemm_tc_supported(probe) : forced == 1 ? false : (cfg->M > 32 && gemm_tc_supported(probe));
-    if (use_tc) {
+    const bool tc_ok = gemm_tc_supported(probe);
+    const bool fused_ok = cfg->M <= 32 && ws->KB <= 8 * FUSED_MAX_STAGES;
+    int variant = fused_ok ? 3 : (cfg->M > 32 && tc_ok) ? 2 : 1;
+    if (forced == 1 || (forced == 2 && tc_ok) || (forced == 3 && fused_ok)) variant = forced;
+    ws->variant = variant;
+    if (variant == 2) {
         ws->TC = 0;
         ws->T = cfg->M >= 256 ? 256 : align_up(cfg->M, 16);
-        ws->variant = 2;
     } else {
         ws->TC = cfg->M <= 8 ? 8 : cfg->M <= 16 ? 16 : 32;
         ws->T = ws->TC;
-        ws->variant = 1;
     }
     const size_t Mp = size_t(align_up(cfg->M, ws->T));
     ws->codes_bytes = Mp * size_t(ws->KB) * KBLOCK;
@@ -957,9 +1007,10 @@ extern "C" int rk_npu_b200_w4a8_last_quant(rk_npu_w4a8_workspace* ws, float* sca
 
 extern "C" int rk_npu_b200_w4a8_set_schedule(rk_npu_w4a8_workspace* ws, int variant, int split_k)
 {
-    if (!ws || variant < 0 || variant > 2 || (split_k != 0 && split_k != 1 && split_k != 2 && split_k != 4 && split_k != 8))
-        return RK_NPU_ERR_PARAM;
+    if (!ws || variant < 0 || variant > 3 || split_k < 0 || split_k > 8) return RK_NPU_ERR_PARAM;
+    if (ws->variant != 3 && split_k != 0 && split_k != 1 && split_k != 2 && split_k != 4 && split_k != 8) return RK_NPU_ERR_PARAM;
     if (variant != 0 && variant != ws->variant) return RK_NPU_ERR_PARAM;   // the code layout is fixed at creation
+    if (ws->variant == 3 && split_k && (ws->KB + split_k - 1) / split_k > FUSED_MAX_STAGES) return RK_NPU_ERR_PARAM;
     WorkspaceLock lock(*ws);
     if (!lock) return RK_NPU_ERR_BUSY;
     ws->split_override = split_k;
@@ -968,4 +1019,29 @@ extern "C" int rk_npu_b200_w4a8_set_schedule(rk_npu_w4a8_workspace* ws, int vari
 extern "C" uint64_t rk_npu_b200_w4a8_launch_count(const rk_npu_w4a8_workspace* ws)
 {
     return ws ? ws->launches.load(std::memory_order_relaxed) : 0;
+}
+
+// ================================================================== phase stamps (diagnostics)
+extern "C" int rk_npu_b200_w4a8_trace_enable(rk_npu_w4a8_workspace* ws, int enable)
+{
+    if (!ws) return RK_NPU_ERR_PARAM;
+    WorkspaceLock lock(*ws);
+    if (!lock) return RK_NPU_ERR_BUSY;
+    if (cudaSetDevice(ws->domain->ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    if (enable && !ws->trace) {
+        ws->trace_bytes = size_t(1) << 20;
+        if (device_alloc(ws->domain, reinterpret_cast<void**>(&ws->trace), ws->trace_bytes)) return RK_NPU_ERR_NOMEM;
+        cudaMemset(ws->trace, 0, ws->trace_bytes);
+    } else if (!enable && ws->trace) {
+        cudaStreamSynchronize(ws->stream);
+        device_free(ws->domain, ws->trace, ws->trace_bytes);
+        ws->trace = nullptr;
+    }
+    return RK_NPU_OK;
+}
+extern "C" int rk_npu_b200_w4a8_trace_read(rk_npu_w4a8_workspace* ws, unsigned long long* stamps, int ctas)
+{
+    if (!ws || !stamps || ctas < 1 || !ws->trace || size_t(ctas) * 64 > ws->trace_bytes) return RK_NPU_ERR_PARAM;
+    if (cudaSetDevice(ws->domain->ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    return cudaMemcpy(stamps, ws->trace, size_t(ctas) * 64, cudaMemcpyDeviceToHost) == cudaSuccess ? RK_NPU_OK : RK_NPU_ERR_SUBMIT;
 }

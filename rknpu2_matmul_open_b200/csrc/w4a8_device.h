@@ -45,8 +45,8 @@ struct QuantParams {
     uint8_t* Xq;            // activation codes, layout above
     float* scales;          // [M]
     float* inverse;         // [M]
-    uint32_t* rowmax_zero;  // [M] cleared for the following SwiGLU epilogue (nullable)
-    const uint32_t* rowmax; // [M] non-null: scales come from these magnitude bits, no scan
+    uint32_t* rowmax_zero;  // [M] cleared before a SwiGLU epilogue maxes into it (nullable)
+    uint32_t* rowmax;       // [M] non-null: scales come from these magnitude bits (no scan); cleared after use
     Status* status;
     int* host_flag;         // mapped host word mirroring status->bad_input (nullable)
     int M, K, Kp, T;
@@ -71,6 +71,26 @@ struct GemmParams {
     unsigned long long timeout_ns;
 };
 
+// Single-kernel linear for small batches: quantisation fused in front of the GEMM.
+struct FusedParams {
+    const uint8_t* Wp;
+    const void* A;              // [M,K] fp32 or binary16 activations
+    const float* sw;
+    void* out;
+    uint32_t* rowmax_out;       // SwiGLU: per-row max |middle| bits, atomically maxed (nullable)
+    uint32_t* rowmax_in;        // non-null: row scales come from these bits (no scan); cleared after use
+    float* scales_out;          // [M] per-token scales, written by the first CTA
+    uint8_t* codes_out;         // activation codes in the Xq layout with T = tokens per CTA (nullable)
+    Status* status;
+    int M, N, K;
+    int KB, NG, F, epi;
+    int split;                  // cluster size along y == split-K factor
+    int stages;                 // k-blocks of smem per CTA (>= ceil(KB / split))
+    int half;                   // activations are binary16
+    unsigned long long timeout_ns;
+    unsigned long long* trace;  // optional [CTA][8] global-timer stamps of the kernel's phases (nullable)
+};
+
 struct PackParams {
     const int8_t* B;        // [K,N] codes on the device
     uint8_t* Wp;
@@ -84,6 +104,10 @@ cudaError_t launch_quantize(const QuantParams& p, cudaStream_t stream, bool pdl)
 // tokens_per_cta: 8, 16 or 32 (must divide p.T)
 cudaError_t launch_gemm_mma(const GemmParams& p, int tokens_per_cta, cudaStream_t stream, bool pdl);
 size_t gemm_mma_smem_bytes(int tokens_per_cta);
+// Fused small-batch kernel: tokens_per_cta 8, 16 or 32 (>= p.M); p.stages <= FUSED_MAX_STAGES.
+constexpr int FUSED_MAX_STAGES = 16;
+cudaError_t launch_gemm_fused(const FusedParams& p, int tokens_per_cta, cudaStream_t stream, bool pdl);
+size_t gemm_fused_smem_bytes(int tokens_per_cta, int stages);
 // tcgen05 path: p.T is the token tile (multiple of 16, 32..256)
 cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl);
 bool gemm_tc_supported(const GemmParams& p);

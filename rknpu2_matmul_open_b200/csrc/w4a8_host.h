@@ -85,7 +85,7 @@ struct rk_npu_w4a8_workspace {
     int T = 0;        // token tile of the code layout
     int TC = 0;       // tokens per CTA of the mma.sync kernel (0 when the tcgen05 kernel is used)
     int KB = 0;       // k-blocks
-    int variant = 0, split_override = 0;
+    int variant = 0, split_override = 0;   // variant: 1 quantise + mma.sync GEMM, 2 quantise + tcgen05 GEMM, 3 fused small batch
     // device buffers
     uint8_t* codes = nullptr;
     float* scales = nullptr;
@@ -98,4 +98,6 @@ struct rk_npu_w4a8_workspace {
     rkb200::Status* host_status = nullptr;  // pinned
     cudaEvent_t events[8]{};
     std::atomic<uint64_t> launches{0};
+    unsigned long long* trace = nullptr;   // device stamps, allocated by rk_npu_b200_w4a8_trace_enable
+    size_t trace_bytes = 0;
 };

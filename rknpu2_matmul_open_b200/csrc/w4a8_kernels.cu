@@ -9,6 +9,7 @@
 //   pack_weights    : src/rk_npu_w4a8.cpp:236-242 (code range check); layout is new.
 #include "w4a8_device.h"
 #include "w4a8_ptx.cuh"
+#include "w4a8_math.cuh"
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <float.h>
@@ -63,47 +64,6 @@ cudaError_t launch_pack_weights(const PackParams& p, cudaStream_t stream)
 // binary16 and fp32 alike the magnitude bits order like the magnitudes, and anything
 // at or above the infinity pattern is NaN/Inf).  Pass 2: q = clamp(round_half_away(
 // x * inverse), -127, 127), written as 16-byte units of the Xq layout.
-template <bool HALF> struct ActType;
-template <> struct ActType<true> { using type = uint16_t; };
-template <> struct ActType<false> { using type = float; };
-
-template <bool HALF>
-__device__ __forceinline__ void load16(const typename ActType<HALF>::type* row, int k0, int K, bool vec, float (&v)[16],
-                                       uint32_t& maxbits)
-{
-    if constexpr (HALF) {
-        uint16_t h[16];
-        if (vec && k0 + 16 <= K) {
-            const uint4 a = *reinterpret_cast<const uint4*>(row + k0);
-            const uint4 b = *reinterpret_cast<const uint4*>(row + k0 + 8);
-            const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { h[2 * i] = (uint16_t)(w[i] & 0xffffu); h[2 * i + 1] = (uint16_t)(w[i] >> 16); }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) h[i] = (k0 + i < K) ? row[k0 + i] : (uint16_t)0;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            maxbits = max(maxbits, (uint32_t)(h[i] & 0x7fffu));
-            v[i] = __half2float(__ushort_as_half(h[i]));
-        }
-    } else {
-        if (vec && k0 + 16 <= K) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float4 f = *reinterpret_cast<const float4*>(row + k0 + 4 * i);
-                v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = (k0 + i < K) ? row[k0 + i] : 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) maxbits = max(maxbits, __float_as_uint(v[i]) & 0x7fffffffu);
-    }
-}
-
 template <bool HALF>
 __global__ void __launch_bounds__(256) quantize_kernel(const QuantParams p)
 {
@@ -148,6 +108,7 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantParams p)
         }
     } else if (tid == 0) {
         const uint32_t bits = p.rowmax[m];
+        p.rowmax[m] = 0u;   // consumed: the next SwiGLU epilogue maxes into a clean word
         bad = bits >= 0x7f800000u ? 2 : 0;
         const float maximum = __uint_as_float(bits);
         const float s = (maximum == 0.f || bad) ? 1.0f : fmaxf(__fdiv_rn(maximum, 127.0f), FLT_MIN);
@@ -177,20 +138,14 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantParams p)
     const int mt = m / p.T, t = m - mt * p.T;
     uint4* dst = reinterpret_cast<uint4*>(p.Xq) + ((size_t)mt * chunks) * p.T + t;
     for (int kc = tid; kc < chunks; kc += 256) {
-        uint32_t w[4] = {0u, 0u, 0u, 0u};
+        uint4 q = make_uint4(0u, 0u, 0u, 0u);
         if (kc < live_chunks) {
             float v[16];
             uint32_t unused = 0;
             load16<HALF>(row, kc * 16, p.K, vec, v, unused);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                float r = roundf(__fmul_rn(v[i], inv));
-                r = fminf(fmaxf(r, -127.f), 127.f);
-                const int q = (kc * 16 + i < p.K) ? (int)r : 0;
-                w[i >> 2] |= (uint32_t)(q & 0xff) << (8 * (i & 3));
-            }
+            q = quantize16(v, inv, kc * 16, p.K);
         }
-        dst[(size_t)kc * p.T] = make_uint4(w[0], w[1], w[2], w[3]);
+        dst[(size_t)kc * p.T] = q;
     }
 }
 
@@ -207,32 +162,6 @@ cudaError_t launch_quantize(const QuantParams& p, cudaStream_t stream, bool pdl)
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     return p.half ? cudaLaunchKernelEx(&cfg, quantize_kernel<true>, p) : cudaLaunchKernelEx(&cfg, quantize_kernel<false>, p);
-}
-
-// =============================================================== epilogue math (shared)
-// Degree-7 polynomial SiLU of the reference's production target, every rounding kept:
-// src/rk_npu_swiglu_fp32_neon.h:17-41.
-__device__ __forceinline__ float silu_poly(float g)
-{
-    float x = fminf(fmaxf(-g, -80.f), 80.f);
-    const float n = floorf(fmaf(x, 1.4426950408889634f, 0.5f));
-    float r = fmaf(-n, 0.693145751953125f, x);
-    r = fmaf(-n, 1.428606765330187e-6f, r);
-    float q = 1.f / 5040.f;
-    q = fmaf(q, r, 1.f / 720.f);
-    q = fmaf(q, r, 1.f / 120.f);
-    q = fmaf(q, r, 1.f / 24.f);
-    q = fmaf(q, r, 1.f / 6.f);
-    q = fmaf(q, r, 0.5f);
-    q = fmaf(q, r, 1.f);
-    q = fmaf(q, r, 1.f);
-    const float power = __int_as_float(((int)n + 127) << 23);
-    const float d = __fadd_rn(1.f, __fmul_rn(q, power));
-    return g < -80.f ? -0.f : __fdiv_rn(g, d);
-}
-__device__ __forceinline__ float dequant(int acc, float sx, float sw)
-{
-    return __fmul_rn(__fmul_rn(__int2float_rn(acc), sx), sw);
 }
 
 // =============================================================== mma.sync GEMM
@@ -252,14 +181,6 @@ __host__ __device__ constexpr size_t mma_smem_bytes(int tc)
     return (size_t)MMA_STAGES * mma_stage_bytes(tc) + (size_t)tc * RED_STRIDE * 4 + 2 * MMA_STAGES * 8 + 16;
 }
 size_t gemm_mma_smem_bytes(int tokens_per_cta) { return mma_smem_bytes(tokens_per_cta); }
-
-__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                       uint32_t b1)
-{
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 
 template <int NT, bool BIGK>
 __global__ void __launch_bounds__(160, 1) gemm_mma_kernel(const GemmParams p)

@@ -1,0 +1,175 @@
+// w4a8_math.cuh -- device helpers shared by the kernels: activation loads, the exact
+// dequantise / SwiGLU epilogue arithmetic, the int8 mma.sync wrapper.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+namespace rkb200 {
+
+template <bool HALF> struct ActType;
+template <> struct ActType<true> { using type = uint16_t; };
+template <> struct ActType<false> { using type = float; };
+
+// 16 consecutive activations of one row as raw words (8 for binary16, 16 for fp32);
+// elements at or beyond K read as zero.  `vec` says the row allows 16-byte loads.
+template <bool HALF> struct Raw16 { uint32_t w[HALF ? 8 : 16]; };
+
+template <bool HALF>
+__device__ __forceinline__ void load_raw(const typename ActType<HALF>::type* row, int k0, int K, bool vec, Raw16<HALF>& r)
+{
+    if constexpr (HALF) {
+        if (vec && k0 + 16 <= K) {
+            const uint4 a = *reinterpret_cast<const uint4*>(row + k0);
+            const uint4 b = *reinterpret_cast<const uint4*>(row + k0 + 8);
+            r.w[0] = a.x; r.w[1] = a.y; r.w[2] = a.z; r.w[3] = a.w;
+            r.w[4] = b.x; r.w[5] = b.y; r.w[6] = b.z; r.w[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t lo = (k0 + 2 * i < K) ? row[k0 + 2 * i] : 0u;
+                const uint32_t hi = (k0 + 2 * i + 1 < K) ? row[k0 + 2 * i + 1] : 0u;
+                r.w[i] = lo | (hi << 16);
+            }
+        }
+    } else {
+        if (vec && k0 + 16 <= K) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 f = *reinterpret_cast<const uint4*>(row + k0 + 4 * i);
+                r.w[4 * i] = f.x; r.w[4 * i + 1] = f.y; r.w[4 * i + 2] = f.z; r.w[4 * i + 3] = f.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r.w[i] = (k0 + i < K) ? __float_as_uint(row[k0 + i]) : 0u;
+        }
+    }
+}
+// max over the 16 magnitudes, as bit patterns (binary16: 15 bits, fp32: 31 bits)
+template <bool HALF>
+__device__ __forceinline__ uint32_t raw_maxbits(const Raw16<HALF>& r)
+{
+    uint32_t m = 0;
+    if constexpr (HALF) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m = max(m, max(r.w[i] & 0x7fffu, (r.w[i] >> 16) & 0x7fffu));
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) m = max(m, r.w[i] & 0x7fffffffu);
+    }
+    return m;
+}
+template <bool HALF>
+__device__ __forceinline__ void raw_to_float(const Raw16<HALF>& r, float (&v)[16])
+{
+    if constexpr (HALF) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[2 * i] = __half2float(__ushort_as_half((uint16_t)(r.w[i] & 0xffffu)));
+            v[2 * i + 1] = __half2float(__ushort_as_half((uint16_t)(r.w[i] >> 16)));
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r.w[i]);
+    }
+}
+template <bool HALF>
+__device__ __forceinline__ void load16(const typename ActType<HALF>::type* row, int k0, int K, bool vec, float (&v)[16],
+                                       uint32_t& maxbits)
+{
+    Raw16<HALF> r;
+    load_raw<HALF>(row, k0, K, vec, r);
+    maxbits = max(maxbits, raw_maxbits<HALF>(r));
+    raw_to_float<HALF>(r, v);
+}
+
+// Degree-7 polynomial SiLU of the reference's production target, every rounding kept:
+// src/rk_npu_swiglu_fp32_neon.h:17-41.
+__device__ __forceinline__ float silu_poly(float g)
+{
+    float x = fminf(fmaxf(-g, -80.f), 80.f);
+    const float n = floorf(fmaf(x, 1.4426950408889634f, 0.5f));
+    float r = fmaf(-n, 0.693145751953125f, x);
+    r = fmaf(-n, 1.428606765330187e-6f, r);
+    float q = 1.f / 5040.f;
+    q = fmaf(q, r, 1.f / 720.f);
+    q = fmaf(q, r, 1.f / 120.f);
+    q = fmaf(q, r, 1.f / 24.f);
+    q = fmaf(q, r, 1.f / 6.f);
+    q = fmaf(q, r, 0.5f);
+    q = fmaf(q, r, 1.f);
+    q = fmaf(q, r, 1.f);
+    const float power = __int_as_float(((int)n + 127) << 23);
+    const float d = __fadd_rn(1.f, __fmul_rn(q, power));
+    return g < -80.f ? -0.f : __fdiv_rn(g, d);
+}
+__device__ __forceinline__ float dequant(int acc, float sx, float sw)
+{
+    return __fmul_rn(__fmul_rn(__int2float_rn(acc), sx), sw);
+}
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+
+// Four consecutive outputs of one token row: vector store when the address allows it.
+__device__ __forceinline__ void store4_f32(float* out, const float (&y)[4], int valid)
+{
+    if (valid == 4 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) *reinterpret_cast<float4*>(out) = make_float4(y[0], y[1], y[2], y[3]);
+    else for (int e = 0; e < valid; ++e) out[e] = y[e];
+}
+__device__ __forceinline__ void store4_f16(__half* out, const float (&y)[4], int valid)
+{
+    if (valid == 4 && (reinterpret_cast<uintptr_t>(out) & 7u) == 0) {
+        const __half2 h0 = __halves2half2(__float2half_rn(y[0]), __float2half_rn(y[1]));
+        const __half2 h1 = __halves2half2(__float2half_rn(y[2]), __float2half_rn(y[3]));
+        uint2 pk;
+        pk.x = *reinterpret_cast<const uint32_t*>(&h0);
+        pk.y = *reinterpret_cast<const uint32_t*>(&h1);
+        *reinterpret_cast<uint2*>(out) = pk;
+    } else for (int e = 0; e < valid; ++e) out[e] = __float2half_rn(y[e]);
+}
+__device__ __forceinline__ void store4_i32(int* out, const int (&v)[4], int valid)
+{
+    if (valid == 4 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) *reinterpret_cast<int4*>(out) = make_int4(v[0], v[1], v[2], v[3]);
+    else for (int e = 0; e < valid; ++e) out[e] = v[e];
+}
+// Per-token scale from the magnitude bits of the row maximum:
+// s = max(maximum / 127, FLT_MIN), 1 for a zero (or rejected) row; inverse = 1 / s.
+__device__ __forceinline__ void scale_from_max(float maximum, bool bad, float& s, float& inv)
+{
+    s = (maximum == 0.f || bad) ? 1.0f : fmaxf(__fdiv_rn(maximum, 127.0f), FLT_MIN);
+    inv = __fdiv_rn(1.0f, s);
+}
+// round half away from zero, then clamp to [-127, 127]; |x| < 2^22 (x is a value times
+// the inverse of its row scale, so |x| <= 127 up to rounding).  Adding 1.5 * 2^23 rounds
+// to an integer (ties to even) in the FP32 adder; x minus that integer is exact, so a tie
+// is recognised exactly and pushed away from zero.  No conversion instructions.
+__device__ __forceinline__ int round_clamp(float x)
+{
+    const float magic = 12582912.0f;
+    float r = __fadd_rn(__fadd_rn(x, magic), -magic);
+    const float d = __fadd_rn(x, -r);
+    if (d == copysignf(0.5f, x)) r = __fadd_rn(r, copysignf(1.0f, x));
+    r = fminf(fmaxf(r, -127.f), 127.f);
+    return __float_as_int(__fadd_rn(r, magic)) - 0x4B400000;
+}
+// 16 activations -> 16 int8 codes packed in four words (ties away from zero, clamp +-127).
+__device__ __forceinline__ uint4 quantize16(const float (&v)[16], float inv, int k0, int K)
+{
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int q = (k0 + i < K) ? round_clamp(__fmul_rn(v[i], inv)) : 0;
+        w[i >> 2] |= (uint32_t)(q & 0xff) << (8 * (i & 3));
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+} // namespace rkb200

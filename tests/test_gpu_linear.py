@@ -90,10 +90,13 @@ def test_extreme_codes_large_sums_and_fp16_overflow(gpu, oracle):
     assert np.abs(ref_acc).max() > 2 ** 24
 
 
-@pytest.mark.parametrize("split", [1, 2, 4, 8])
+@pytest.mark.parametrize("split", [1, 2, 3, 4, 5, 6, 7, 8])
 def test_split_k_clusters_are_exact(gpu, oracle, split):
     _, dom, _ = gpu
-    for (M, K, N) in [(8, 4096, 512), (16, 1153, 257), (32, 2048, 384), (40, 640, 130)]:
+    shapes = [(8, 2048, 512), (16, 1153, 257), (32, 2048, 384), (8, 2048 * split, 256)]
+    if split in (1, 2, 4, 8):
+        shapes.append((40, 640, 130))        # larger batch: quantise kernel + split-K GEMM kernel
+    for (M, K, N) in shapes:
         B, sw = make_weights(K, N, seed=split)
         A = make_activations(M, K, seed=split, dtype="f16")
         out, acc = run_case(dom, oracle, A, B, sw, split=split)
@@ -140,6 +143,7 @@ def test_quantized_codes_and_scales(gpu, oracle):
     for A in (a, oracle.float_to_half(a)):
         out = np.zeros((M, N), A.dtype)
         assert (ws.run_f16 if A.dtype == np.uint16 else ws.run_f32)(w, A, out) == 0
+        assert ws.run_acc_i32(w, A, np.zeros((M, N), np.int32)) == 0
         rc, s, q = ws.last_quant()
         _, so, inv = oracle.scales(A)
         assert rc == 0 and np.array_equal(bits(s), bits(so)) and np.array_equal(q, oracle.quantize(A, inv))
