@@ -10,13 +10,15 @@
 // tensor memory.  Per 128-element k-block:
 //   warp 0      one thread streams the packed int4 weights (4 x 2 KB) and the int8
 //               activation tile (T x 128 B) with bulk async copies into a ring of stages;
-//   warps 2-5   unpack the int4 weights (three ALU instructions per eight codes) and write
+//   warps 2-9   unpack the int4 weights (three ALU instructions per eight codes) and write
 //               them with tcgen05.st into a ring of TMEM buffers: the MMA's A operand comes
-//               from tensor memory, so unpacked weights never touch shared memory;
+//               from tensor memory, so unpacked weights never touch shared memory.  Two sets
+//               of four warps (one warp per TMEM lane quarter) take alternate k-blocks, and a
+//               warp overlaps the store of one k-block with the unpacking of its next;
 //   warp 1      one thread issues four tcgen05.mma (K = 32 each) with the activation tile as
 //               shared-memory B operand (K-major, no swizzle: the tile already is a sequence
 //               of 8 x 16-byte core matrices) and commits the stage / buffer back.
-// Warps 2-5 then read the accumulators with tcgen05.ld and run the epilogue.
+// Warps 2-9 then read the accumulators with tcgen05.ld and run the epilogue.
 // Every wait is bounded by the workspace's timeout; a wait that runs out sets the status
 // word, the kernel drains and frees its tensor memory and returns.
 #include "w4a8_device.h"
@@ -25,9 +27,10 @@
 
 namespace rkb200 {
 
-constexpr int TC_STAGES = 4;
-constexpr int TC_ABUF = 4;
-constexpr int TC_THREADS = 192;
+constexpr int TC_STAGES = 5;
+constexpr int TC_ABUF = 8;
+constexpr int TC_UNPACK_WARPS = 8;   // two sets of four (one warp per TMEM lane quarter), alternating k-blocks
+constexpr int TC_THREADS = 64 + 32 * TC_UNPACK_WARPS;
 constexpr int TC_A_COL0 = 256;      // A buffers live behind the accumulator columns
 constexpr int TC_TMEM_COLS = 512;
 
@@ -178,9 +181,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
         } else {
             // ---------------------------------------------------------------- weight unpack -> TMEM
             const int q = warp & 3;                       // TMEM lane quarter == weight group of the tile
+            const int set = (warp - 2) >> 2;              // this set takes k-blocks kb % 2 == set
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
             bool ok = true;
-            for (int kb = 0; kb < KB && ok; ++kb) {
+            int pending = -1;                             // buffer whose tensor-memory store is in flight
+            for (int kb = set; kb < KB && ok; kb += 2) {
                 const int s = kb % TC_STAGES, b = kb % TC_ABUF;
                 ok = mbar_wait(&full[s], (kb / TC_STAGES) & 1, deadline);
                 if (ok && kb >= TC_ABUF) ok = mbar_wait(&a_free[b], ((kb / TC_ABUF) - 1) & 1, deadline);
@@ -199,35 +204,46 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
                         r[c * 8 + 4 + j] = ww[j] & 0xF0F0F0F0u;          // k = 32c + 16 + 4j .. +3 (x16)
                     }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);    // the packed weights of this stage are in registers
+                if (pending >= 0) {                        // the previous store had the unpacking above to complete
+                    tc_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&a_ready[pending]);
+                }
                 tc_st32(lane_addr + TC_A_COL0 + b * 32, r);
+                pending = b;
+            }
+            if (pending >= 0) {
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) { mbar_arrive(&a_ready[b]); mbar_arrive(&empty[s]); }
+                if (lane == 0) mbar_arrive(&a_ready[pending]);
             }
         }
 
         // -------------------------------------------------------------------- epilogue
         if (warp >= 2) {
             const int q = warp & 3;
-            const int etid = q * 32 + lane;               // 0..127 in channel order
-            for (int i = etid; i < T; i += 128) {
+            const int set = (warp - 2) >> 2;              // the two sets take alternate 32-token chunks
+            for (int i = tid - 64; i < T; i += 32 * TC_UNPACK_WARPS) {
                 const int m = mt * T + i;
                 s_sx[i] = m < p.M ? p.sx[m] : 0.f;
             }
             if (!mbar_wait(acc_done, 0, deadline)) *s_error = 1;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             const bool done = *reinterpret_cast<volatile int*>(s_error) == 0;   // same answer in all 128 threads
             tc_fence_after();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-            float* const exch = reinterpret_cast<float*>(stages);   // all stages are drained by now
+            float* const exch = reinterpret_cast<float*>(stages) + set * 2048;   // all stages are drained by now
             const int ch = q * 32 + lane;
             int n;                                        // global output channel of this thread
             if (swiglu) n = ch < 64 ? tile * 64 + ch : p.F + tile * 64 + (ch - 64);
             else n = tile * TILE_N + ch;
             const bool n_ok = swiglu ? (tile * 64 + (ch & 63)) < p.F : n < p.N;
             const float sw = n_ok ? p.sw[n] : 0.f;
-            for (int t0 = 0; t0 < T && done; t0 += 32) {
+            for (int t0 = set * 32; t0 < T && done; t0 += 64) {
                 uint32_t r[32];
                 tc_ld32(lane_addr + t0, r);
                 tc_wait_ld();
@@ -253,7 +269,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
                         for (int i = 0; i < 32; ++i)
                             exch[i * 64 + (ch - 64)] = dequant((int)r[i] >> 4, t0 + i < T ? s_sx[t0 + i] : 0.f, sw);
                     }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    asm volatile("bar.sync %0, 128;" ::"r"(2 + set) : "memory");
                     if (ch < 64) {
                         const int f = tile * 64 + ch;
 #pragma unroll
@@ -269,7 +285,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
                             }
                         }
                     }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    asm volatile("bar.sync %0, 128;" ::"r"(2 + set) : "memory");
                 }
             }
         }
