@@ -284,7 +284,7 @@ int enqueue(const Call& c)
     const bool pdl = env_flag("RK_NPU_B200_PDL", true);
     if (c.events) cudaEventRecord(c.events[0], c.stream);
     const int F = c.epi == EPI_SWIGLU ? cfg.N / 2 : 0;
-    const int tiles = c.epi == EPI_SWIGLU ? (F + 63) / 64 : c.w->NG / 4;
+    const int tiles = c.epi == EPI_SWIGLU ? (F + 63) / 64 : (cfg.N + TILE_N - 1) / TILE_N;
     const unsigned long long timeout_ns = (unsigned long long)cfg.timeout_ms * 1000000ull;
     if (ws.variant == 3) {
         // One kernel: scan + quantise + GEMM + epilogue.
@@ -345,9 +345,11 @@ int enqueue(const Call& c)
     g.F = F;
     g.epi = c.epi;
     g.timeout_ns = timeout_ns;
+    g.trace = ws.trace;
     cudaError_t err;
     if (ws.variant == 2) {
         g.split = 1;
+        g.pair = ws.pair ? 1 : 0;
         err = launch_gemm_tc(g, c.stream, pdl);
     } else {
         g.split = pick_split(ws, tiles, (cfg.M + ws.TC - 1) / ws.TC);
@@ -669,7 +671,7 @@ rk_npu_w4a8_weights* rkb200::create_weights(rk_npu_iommu_domain* domain, const r
     if (cudaSetDevice(ctx->device) != cudaSuccess) return nullptr;
     w->info = info;
     w->KB = (key.K + KBLOCK - 1) / KBLOCK;
-    w->NG = align_up((key.N + GROUP - 1) / GROUP, 4);
+    w->NG = align_up((key.N + GROUP - 1) / GROUP, 8) + 8;   // zero groups: odd tile counts of CTA pairs, SwiGLU tails
     w->packed_bytes = size_t(w->NG) * (size_t(w->KB) * 4) * 512;
     w->scale_bytes = size_t(w->NG) * GROUP * sizeof(float);
     w->domain = domain;
@@ -792,13 +794,15 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
     if (forced == 1 || (forced == 2 && tc_ok) || (forced == 3 && fused_ok)) variant = forced;
     ws->variant = variant;
     if (variant == 2) {
+        // Batches above 128 tokens run two-CTA tiles: 128-token code tiles, two per MMA tile.
         ws->TC = 0;
-        ws->T = cfg->M >= 256 ? 256 : align_up(cfg->M, 16);
+        ws->pair = cfg->M > 128 && !env_flag("RK_NPU_B200_NO_PAIR", false);
+        ws->T = ws->pair ? 128 : (cfg->M >= 256 ? 256 : align_up(cfg->M, 16));
     } else {
         ws->TC = cfg->M <= 8 ? 8 : cfg->M <= 16 ? 16 : 32;
         ws->T = ws->TC;
     }
-    const size_t Mp = size_t(align_up(cfg->M, ws->T));
+    const size_t Mp = size_t(align_up(cfg->M, ws->pair ? 256 : ws->T));
     ws->codes_bytes = Mp * size_t(ws->KB) * KBLOCK;
     const int out_cols = cfg->N;
     ws->stage_in_bytes = size_t(cfg->M) * cfg->K * 4;

@@ -68,7 +68,9 @@ struct GemmParams {
     int F;                  // SwiGLU: N/2, else 0
     int epi;
     int split;              // split-K factor == cluster size along y (1, 2, 4, 8)
+    int pair;               // tcgen05 path: 1 = two-CTA tiles (cta_group::2), T must be 128
     unsigned long long timeout_ns;
+    unsigned long long* trace;  // optional cycle stamps of CTA (0,0): [role 0..2][k-block 0..63][2] (nullable)
 };
 
 // Single-kernel linear for small batches: quantisation fused in front of the GEMM.
@@ -108,7 +110,7 @@ size_t gemm_mma_smem_bytes(int tokens_per_cta);
 constexpr int FUSED_MAX_STAGES = 16;
 cudaError_t launch_gemm_fused(const FusedParams& p, int tokens_per_cta, cudaStream_t stream, bool pdl);
 size_t gemm_fused_smem_bytes(int tokens_per_cta, int stages);
-// tcgen05 path: p.T is the token tile (multiple of 16, 32..256)
+// tcgen05 path: p.T is the token tile of the code layout (multiple of 16, <= 256; 128 when p.pair)
 cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl);
 bool gemm_tc_supported(const GemmParams& p);
 

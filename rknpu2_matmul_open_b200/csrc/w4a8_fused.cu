@@ -334,7 +334,7 @@ static cudaError_t launch_fused_inst(const FusedParams& p, cudaStream_t stream, 
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const int tiles = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : p.NG / 4;
+    const int tiles = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : (p.N + TILE_N - 1) / TILE_N;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)tiles, (unsigned)p.split, 1);
     cfg.blockDim = dim3(FUSED_THREADS);

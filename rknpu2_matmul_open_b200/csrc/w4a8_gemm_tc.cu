@@ -19,6 +19,13 @@
 //               shared-memory B operand (K-major, no swizzle: the tile already is a sequence
 //               of 8 x 16-byte core matrices) and commits the stage / buffer back.
 // Warps 2-9 then read the accumulators with tcgen05.ld and run the epilogue.
+//
+// Two forms share the code.  PAIR = false: one CTA, token tile T <= 256 (batches of 33..128
+// tokens).  PAIR = true: two CTAs of a cluster form one 256-channel x 256-token tile with
+// tcgen05.mma.cta_group::2: each CTA unpacks its own 128 channels into its own tensor memory
+// and loads only its half (128 tokens) of the activation tile, which halves the activation
+// traffic per MMA; the leader CTA issues the MMAs for both and signals both with multicast
+// commits.  The activation loads stay plain (non-multicast) bulk copies.
 // Every wait is bounded by the workspace's timeout; a wait that runs out sets the status
 // word, the kernel drains and frees its tensor memory and returns.
 #include "w4a8_device.h"
@@ -27,17 +34,20 @@
 
 namespace rkb200 {
 
-constexpr int TC_STAGES = 5;
+// A stage holds TWO k-blocks, so five bulk copies feed two k-blocks of MMAs (the copy engine
+// sustains only a few requests in flight per SM; fewer, larger requests keep it ahead).
+constexpr int TC_STAGES = 2;          // single-CTA form: 2 x (8 KB weights + T x 128 B activations) per stage
+constexpr int TC_STAGES_PAIR = 4;     // paired form: 2 x (8 KB + 16 KB) per stage
 constexpr int TC_ABUF = 8;
 constexpr int TC_UNPACK_WARPS = 8;   // two sets of four (one warp per TMEM lane quarter), alternating k-blocks
 constexpr int TC_THREADS = 64 + 32 * TC_UNPACK_WARPS;
 constexpr int TC_A_COL0 = 256;      // A buffers live behind the accumulator columns
 constexpr int TC_TMEM_COLS = 512;
 
-__host__ __device__ constexpr size_t tc_stage_bytes(int T) { return 8192 + (size_t)T * 128; }
-__host__ __device__ constexpr size_t tc_smem_bytes(int T)
+__host__ __device__ constexpr size_t tc_stage_bytes(int T) { return 2 * (8192 + (size_t)T * 128); }
+__host__ __device__ constexpr size_t tc_smem_bytes(int T, int stages, int tokens)
 {
-    return TC_STAGES * tc_stage_bytes(T) + (size_t)T * 4 /* token scales */ + (2 * TC_STAGES + 2 * TC_ABUF + 1) * 8 + 32;
+    return stages * tc_stage_bytes(T) + (size_t)tokens * 4 /* token scales */ + (2 * stages + 2 * TC_ABUF + 1) * 8 + 32;
 }
 
 // ---- tcgen05 wrappers
@@ -56,6 +66,56 @@ __device__ __forceinline__ void tc_mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, u
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
+// paired forms: the MMA spans both CTAs of the cluster; the commit arrives on the barrier at
+// the same shared-memory offset in every CTA of the mask
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// arrive on the barrier at the same offset in CTA `rank` of the cluster
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank)
+{
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(smem_u32(bar)), "r"(rank)
+        : "memory");
+}
+// bounded wait with cluster-scope acquire (arrivals may come from the peer CTA or from a
+// multicast commit)
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, unsigned long long deadline_ns)
+{
+    for (;;) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)
+            : "memory");
+        if (ok) return true;
+        if (global_ns() > deadline_ns) return false;
+    }
+}
+__device__ __forceinline__ uint32_t cluster_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
 {
     asm volatile(
@@ -92,21 +152,24 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr, uint32_t lb
     return ((uint64_t)hi << 32) | lo;
 }
 // Instruction descriptor: int32 accumulators, signed 8-bit A and B, both K-major, M = 128.
-__device__ __forceinline__ uint32_t tc_idesc_s8(int n)
+__device__ __forceinline__ uint32_t tc_idesc_s8(int m, int n)
 {
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+template <bool PAIR>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
-    const int T = p.T;
+    constexpr int NSTAGE = PAIR ? TC_STAGES_PAIR : TC_STAGES;
+    const int T = p.T;                              // tokens of this CTA's activation tile (128 when paired)
+    const int TOK = PAIR ? 256 : T;                 // tokens (accumulator columns) of the MMA tile
     const size_t stage_bytes = tc_stage_bytes(T);
     uint8_t* const stages = smem;
-    float* const s_sx = reinterpret_cast<float*>(smem + TC_STAGES * stage_bytes);
-    uint64_t* const full = reinterpret_cast<uint64_t*>(s_sx + T);
-    uint64_t* const empty = full + TC_STAGES;
-    uint64_t* const a_ready = empty + TC_STAGES;
+    float* const s_sx = reinterpret_cast<float*>(smem + NSTAGE * stage_bytes);
+    uint64_t* const full = reinterpret_cast<uint64_t*>(s_sx + TOK);
+    uint64_t* const empty = full + NSTAGE;
+    uint64_t* const a_ready = empty + NSTAGE;
     uint64_t* const a_free = a_ready + TC_ABUF;
     uint64_t* const acc_done = a_free + TC_ABUF;
     uint32_t* const s_tmem = reinterpret_cast<uint32_t*>(acc_done + 1);
@@ -114,24 +177,37 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
 
     pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tile = blockIdx.x, mt = blockIdx.y;
+    const int tile = blockIdx.x;
+    const uint32_t rank = PAIR ? cluster_rank() : 0u;          // 0 = leader of the pair
+    const int mt = PAIR ? 2 * (int)blockIdx.y + (int)rank : (int)blockIdx.y;   // this CTA's activation tile
+    const int tok_base = (int)blockIdx.y * TOK;                 // first token of the MMA tile
     const bool swiglu = p.epi == EPI_SWIGLU;
     const int KB = p.KB, KC = KB * 4;
     const unsigned long long deadline = global_ns() + p.timeout_ns;
+    unsigned long long* const trace = (p.trace && blockIdx.x < 2 && blockIdx.y == 0) ? p.trace + blockIdx.x * 1024 : nullptr;
+    const long long c0 = clock64();
+    if (trace && threadIdx.x == 0) trace[770] = global_ns();
+#define TC_STAMP(role, kb, slot) do { if (trace && (kb) < 64) trace[((role) * 64 + (kb)) * 4 + (slot)] = (unsigned long long)(clock64() - c0); } while (0)
 
     if (tid == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 5); }
-        for (int b = 0; b < TC_ABUF; ++b) { mbar_init(&a_ready[b], 4); mbar_init(&a_free[b], 1); }
+        for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 9); }   // 2 x 4 unpack warps + 1 commit
+        for (int b = 0; b < TC_ABUF; ++b) { mbar_init(&a_ready[b], PAIR ? 8 : 4); mbar_init(&a_free[b], 1); }
         mbar_init(acc_done, 1);
         mbar_fence_init();
         *s_error = 0;
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(TC_TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(TC_TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(TC_TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) { cluster_arrive(); cluster_wait(); }   // the peer's barriers and tensor memory exist from here on
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
     pdl_wait();   // activation codes, scales and the status word come from the kernel in front
@@ -140,43 +216,59 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
     if (!skip) {
         if (warp == 0) {
             // ---------------------------------------------------------------- producer
-            if (lane == 0) {
-                int group[4];
-#pragma unroll
-                for (int w = 0; w < 4; ++w)
-                    group[w] = swiglu ? (w < 2 ? tile * 2 + w : p.F / GROUP + tile * 2 + (w - 2)) : tile * 4 + w;
-                const uint8_t* xtile = p.Xq + (size_t)mt * ((size_t)KB * 8) * T * 16;
-                for (int kb = 0; kb < KB; ++kb) {
-                    const int s = kb % TC_STAGES;
-                    if (kb >= TC_STAGES && !mbar_wait(&empty[s], ((kb / TC_STAGES) - 1) & 1, deadline)) { *s_error = 1; break; }
-                    uint8_t* dst = stages + (size_t)s * stage_bytes;
-                    mbar_arrive_expect_tx(&full[s], (uint32_t)stage_bytes);
-#pragma unroll
-                    for (int w = 0; w < 4; ++w)
-                        bulk_g2s(dst + w * 2048, p.Wp + ((size_t)group[w] * KC + (size_t)kb * 4) * 512, 2048, &full[s]);
-                    bulk_g2s(dst + 8192, xtile + (size_t)kb * 8 * T * 16, (uint32_t)T * 128u, &full[s]);
+            // Lane 0 waits for the stage and arms its barrier; lanes 0-3 then each request one
+            // weight group and lane 4 the activation tile, so the five requests issue in parallel.
+            const int w = lane & 3;
+            const int group = swiglu ? (w < 2 ? tile * 2 + w : p.F / GROUP + tile * 2 + (w - 2)) : tile * 4 + w;
+            const uint8_t* wsrc = p.Wp + (size_t)group * KC * 512;
+            const uint8_t* xtile = p.Xq + (size_t)mt * ((size_t)KB * 8) * T * 16;
+            bool ok = true;
+            const int nstage_iters = (KB + 1) / 2;
+            for (int it = 0; it < nstage_iters && ok; ++it) {
+                const int s = it % NSTAGE;
+                const int kbs = min(2, KB - 2 * it);              // k-blocks in this stage
+                if (lane == 0) {
+                    if (it >= NSTAGE) ok = mbar_wait_cluster(&empty[s], ((it / NSTAGE) - 1) & 1, deadline);
+                    if (ok) mbar_arrive_expect_tx(&full[s], (uint32_t)kbs * (8192u + (uint32_t)T * 128u));
+                    TC_STAMP(0, 2 * it, 0);
                 }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { *s_error = 1; break; }
+                uint8_t* dst = stages + (size_t)s * stage_bytes;
+                if (lane < 4) bulk_g2s(dst + w * 4096, wsrc + (size_t)it * 4096, (uint32_t)kbs * 2048u, &full[s]);
+                else if (lane == 4) bulk_g2s(dst + 16384, xtile + (size_t)it * 16 * T * 16, (uint32_t)kbs * (uint32_t)T * 128u, &full[s]);
             }
         } else if (warp == 1) {
             // ---------------------------------------------------------------- MMA issuer
-            if (lane == 0) {
-                const uint32_t idesc = tc_idesc_s8(T);
+            // (paired form: the leader issues for both CTAs; a_ready counts the unpack warps of
+            // both, each of which has seen its own stage complete, activation half included)
+            if (lane == 0 && rank == 0) {
+                const uint32_t idesc = tc_idesc_s8(PAIR ? 256 : 128, TOK);
                 bool ok = true;
                 for (int kb = 0; kb < KB && ok; ++kb) {
-                    const int s = kb % TC_STAGES, b = kb % TC_ABUF;
-                    ok = mbar_wait(&full[s], (kb / TC_STAGES) & 1, deadline) && mbar_wait(&a_ready[b], (kb / TC_ABUF) & 1, deadline);
+                    const int it = kb >> 1, s = it % NSTAGE, b = kb % TC_ABUF;
+                    TC_STAMP(1, kb, 2);
+                    if constexpr (PAIR) ok = mbar_wait_cluster(&a_ready[b], (kb / TC_ABUF) & 1, deadline);
+                    else ok = mbar_wait(&full[s], (it / NSTAGE) & 1, deadline) && mbar_wait(&a_ready[b], (kb / TC_ABUF) & 1, deadline);
                     if (!ok) { *s_error = 1; break; }
+                    TC_STAMP(1, kb, 0);
                     tc_fence_after();
-                    const uint32_t xaddr = smem_u32(stages + (size_t)s * stage_bytes + 8192);
+                    const uint32_t xaddr = smem_u32(stages + (size_t)s * stage_bytes + 16384 + (size_t)(kb & 1) * T * 128);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const uint64_t desc = tc_smem_desc(xaddr + (uint32_t)(2 * j) * T * 16, (uint32_t)T * 16u, 128u);
-                        tc_mma_i8_ts(tmem_base, tmem_base + TC_A_COL0 + b * 32 + j * 8, desc, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                        const uint32_t a_tmem = tmem_base + TC_A_COL0 + b * 32 + j * 8;
+                        if constexpr (PAIR) tc_mma_i8_ts_pair(tmem_base, a_tmem, desc, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                        else tc_mma_i8_ts(tmem_base, a_tmem, desc, idesc, (kb > 0 || j > 0) ? 1u : 0u);
                     }
-                    tc_commit(&empty[s]);    // activation stage may be refilled once these MMAs retire
-                    tc_commit(&a_free[b]);   // and the weight buffer in tensor memory rewritten
+                    // once these MMAs retire the activation stage may be refilled and the
+                    // weight buffer in tensor memory rewritten (in both CTAs when paired)
+                    const bool stage_done = (kb & 1) || kb == KB - 1;
+                    if constexpr (PAIR) { if (stage_done) tc_commit_pair(&empty[s]); tc_commit_pair(&a_free[b]); }
+                    else { if (stage_done) tc_commit(&empty[s]); tc_commit(&a_free[b]); }
+                    TC_STAMP(1, kb, 1);
                 }
-                tc_commit(acc_done);
+                if constexpr (PAIR) tc_commit_pair(acc_done); else tc_commit(acc_done);
             }
         } else {
             // ---------------------------------------------------------------- weight unpack -> TMEM
@@ -184,15 +276,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
             const int set = (warp - 2) >> 2;              // this set takes k-blocks kb % 2 == set
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
             bool ok = true;
-            int pending = -1;                             // buffer whose tensor-memory store is in flight
             for (int kb = set; kb < KB && ok; kb += 2) {
-                const int s = kb % TC_STAGES, b = kb % TC_ABUF;
-                ok = mbar_wait(&full[s], (kb / TC_STAGES) & 1, deadline);
-                if (ok && kb >= TC_ABUF) ok = mbar_wait(&a_free[b], ((kb / TC_ABUF) - 1) & 1, deadline);
+                const int it = kb >> 1, s = it % NSTAGE, b = kb % TC_ABUF;   // this set's half of the stage: kb & 1 == set
+                if (q == 2 && lane == 0) TC_STAMP(2, kb, 2);
+                ok = mbar_wait(&full[s], (it / NSTAGE) & 1, deadline);
+                if (q == 2 && lane == 0) TC_STAMP(2, kb, 3);
+                if (ok && kb >= TC_ABUF) ok = mbar_wait_cluster(&a_free[b], ((kb / TC_ABUF) - 1) & 1, deadline);
                 ok = __all_sync(0xffffffffu, ok);   // the tensor-memory store below needs the whole warp
                 if (!ok) { *s_error = 1; break; }
+                if (q == 2 && lane == 0) TC_STAMP(2, kb, 0);
                 tc_fence_after();
-                const uint4* src = reinterpret_cast<const uint4*>(stages + (size_t)s * stage_bytes + q * 2048) + lane;
+                const uint4* src = reinterpret_cast<const uint4*>(stages + (size_t)s * stage_bytes + q * 4096 + set * 2048) + lane;
                 uint32_t r[32];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -206,20 +300,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);    // the packed weights of this stage are in registers
-                if (pending >= 0) {                        // the previous store had the unpacking above to complete
-                    tc_wait_st();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&a_ready[pending]);
-                }
                 tc_st32(lane_addr + TC_A_COL0 + b * 32, r);
-                pending = b;
-            }
-            if (pending >= 0) {
+                if (q == 2 && lane == 0) TC_STAMP(2, kb, 1);
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&a_ready[pending]);
+                if (lane == 0) { if (PAIR && rank != 0) mbar_arrive_remote(&a_ready[b], 0); else mbar_arrive(&a_ready[b]); }
             }
         }
 
@@ -227,77 +313,121 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
         if (warp >= 2) {
             const int q = warp & 3;
             const int set = (warp - 2) >> 2;              // the two sets take alternate 32-token chunks
-            for (int i = tid - 64; i < T; i += 32 * TC_UNPACK_WARPS) {
-                const int m = mt * T + i;
+            for (int i = tid - 64; i < TOK; i += 32 * TC_UNPACK_WARPS) {
+                const int m = tok_base + i;
                 s_sx[i] = m < p.M ? p.sx[m] : 0.f;
             }
-            if (!mbar_wait(acc_done, 0, deadline)) *s_error = 1;
+            if (!mbar_wait_cluster(acc_done, 0, deadline)) *s_error = 1;
             asm volatile("bar.sync 1, 256;" ::: "memory");
             const bool done = *reinterpret_cast<volatile int*>(s_error) == 0;   // same answer in all 128 threads
+            if (trace && tid == 64) trace[768] = (unsigned long long)(clock64() - c0);
             tc_fence_after();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-            float* const exch = reinterpret_cast<float*>(stages) + set * 2048;   // all stages are drained by now
+            // All stages are drained by now: each set of four warps stages its 32-token chunks in
+            // 20 KB of the ring so that global stores are 16-byte pieces along the channel axis.
+            uint8_t* const stg = stages + (size_t)set * 20480;
             const int ch = q * 32 + lane;
+            const int sid = ch;                           // thread index inside the set (0..127)
             int n;                                        // global output channel of this thread
             if (swiglu) n = ch < 64 ? tile * 64 + ch : p.F + tile * 64 + (ch - 64);
             else n = tile * TILE_N + ch;
             const bool n_ok = swiglu ? (tile * 64 + (ch & 63)) < p.F : n < p.N;
             const float sw = n_ok ? p.sw[n] : 0.f;
-            for (int t0 = set * 32; t0 < T && done; t0 += 64) {
+            const int esize = p.epi == EPI_F16 ? 2 : 4;                       // bytes per output element
+            const int row_elems = swiglu ? 64 : 128;                           // outputs per token in this CTA
+            const int row_bytes = row_elems * esize + 16;                      // padded staging row
+            const int out_cols = swiglu ? p.F : p.N;
+            const int col0 = swiglu ? tile * 64 : tile * TILE_N;
+            // 16-byte stores need every row start and the tile's first column aligned
+            const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0) && ((size_t)out_cols * esize) % 16 == 0 &&
+                                ((size_t)col0 * esize) % 16 == 0;
+            for (int t0 = set * 32; t0 < TOK && done; t0 += 64) {
                 uint32_t r[32];
                 tc_ld32(lane_addr + t0, r);
                 tc_wait_ld();
                 if (!swiglu) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int m = mt * T + t0 + i;
-                        if (t0 + i < T && m < p.M && n_ok) {
-                            const int v = (int)r[i] >> 4;   // exact: sums are multiples of 16
-                            if (p.epi == EPI_I32) reinterpret_cast<int*>(p.out)[(size_t)m * p.N + n] = v;
-                            else {
-                                const float y = dequant(v, s_sx[t0 + i], sw);
-                                if (p.epi == EPI_F32) reinterpret_cast<float*>(p.out)[(size_t)m * p.N + n] = y;
-                                else reinterpret_cast<__half*>(p.out)[(size_t)m * p.N + n] = __float2half_rn(y);
-                            }
+                        const int v = (int)r[i] >> 4;   // exact: sums are multiples of 16
+                        uint8_t* cell = stg + (size_t)i * row_bytes + (size_t)ch * esize;
+                        if (p.epi == EPI_I32) *reinterpret_cast<int*>(cell) = v;
+                        else {
+                            const float y = dequant(v, s_sx[min(t0 + i, TOK - 1)], sw);
+                            if (p.epi == EPI_F32) *reinterpret_cast<float*>(cell) = y;
+                            else *reinterpret_cast<__half*>(cell) = __float2half_rn(y);
                         }
                     }
                 } else {
                     // lanes 64..127 of the accumulator hold the up projection of the same 64
                     // features: hand it to the gate threads through shared memory
+                    float* const exch = reinterpret_cast<float*>(stg + 10240);
                     if (ch >= 64) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            exch[i * 64 + (ch - 64)] = dequant((int)r[i] >> 4, t0 + i < T ? s_sx[t0 + i] : 0.f, sw);
+                            exch[i * 64 + (ch - 64)] = dequant((int)r[i] >> 4, s_sx[min(t0 + i, TOK - 1)], sw);
                     }
                     asm volatile("bar.sync %0, 128;" ::"r"(2 + set) : "memory");
                     if (ch < 64) {
-                        const int f = tile * 64 + ch;
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            const int m = mt * T + t0 + i;
-                            const float g = dequant((int)r[i] >> 4, t0 + i < T ? s_sx[t0 + i] : 0.f, sw);
+                            const int m = tok_base + t0 + i;
+                            const float g = dequant((int)r[i] >> 4, s_sx[min(t0 + i, TOK - 1)], sw);
                             const float y = __fmul_rn(silu_poly(g), exch[i * 64 + ch]);
-                            const bool ok = t0 + i < T && m < p.M && n_ok;
-                            if (ok) reinterpret_cast<float*>(p.out)[(size_t)m * p.F + f] = y;
+                            *reinterpret_cast<float*>(stg + (size_t)i * row_bytes + (size_t)ch * 4) = y;
                             if (p.rowmax) {
+                                const bool ok = t0 + i < TOK && m < p.M && n_ok;
                                 const uint32_t mx = __reduce_max_sync(0xffffffffu, ok ? (__float_as_uint(y) & 0x7fffffffu) : 0u);
                                 if (lane == 0 && mx) atomicMax(&p.rowmax[m], mx);
                             }
                         }
                     }
-                    asm volatile("bar.sync %0, 128;" ::"r"(2 + set) : "memory");
                 }
+                asm volatile("bar.sync %0, 128;" ::"r"(2 + set) : "memory");
+                // staged chunk -> global: 32 token rows of row_elems outputs
+                const int valid_cols = min(row_elems, out_cols - col0);        // > 0 for every launched tile
+                if (vec_ok) {
+                    const int pieces_per_row = row_elems * esize / 16;
+                    for (int pc = sid; pc < 32 * pieces_per_row; pc += 128) {
+                        const int i = pc / pieces_per_row, c16 = pc - i * pieces_per_row;
+                        const int m = tok_base + t0 + i;
+                        const int first = c16 * (16 / esize);
+                        if (t0 + i < TOK && m < p.M && first < valid_cols) {
+                            const uint4 val = *reinterpret_cast<const uint4*>(stg + (size_t)i * row_bytes + (size_t)c16 * 16);
+                            uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + ((size_t)m * out_cols + col0) * esize + (size_t)c16 * 16;
+                            if (first + 16 / esize <= valid_cols) *reinterpret_cast<uint4*>(dst) = val;
+                            else {
+                                const uint8_t* src = stg + (size_t)i * row_bytes + (size_t)c16 * 16;
+                                for (int e = 0; e < (valid_cols - first) * esize; ++e) dst[e] = src[e];
+                            }
+                        }
+                    }
+                } else {
+                    for (int el = sid; el < 32 * row_elems; el += 128) {
+                        const int i = el / row_elems, c = el - i * row_elems;
+                        const int m = tok_base + t0 + i;
+                        if (t0 + i < TOK && m < p.M && c < valid_cols) {
+                            const uint8_t* src = stg + (size_t)i * row_bytes + (size_t)c * esize;
+                            uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + ((size_t)m * out_cols + col0 + c) * esize;
+                            if (esize == 2) *reinterpret_cast<uint16_t*>(dst) = *reinterpret_cast<const uint16_t*>(src);
+                            else *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
+                        }
+                    }
+                }
+                asm volatile("bar.sync %0, 128;" ::"r"(2 + set) : "memory");
             }
         }
     }
 
     // ------------------------------------------------------------------------ teardown
+    if (trace && tid == 64) trace[769] = (unsigned long long)(clock64() - c0);
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) { cluster_arrive(); cluster_wait(); }   // neither CTA frees tensor memory or leaves while the other may still use it
     if (tid == 0 && *s_error) atomicExch(&p.status->device_error, 1);
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
+        if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
     }
 }
 
@@ -310,24 +440,45 @@ bool gemm_tc_supported(const GemmParams& p)
 cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl)
 {
     if (p.T < 16 || p.T > 256 || p.T % 16 || !gemm_tc_supported(p)) return cudaErrorInvalidValue;
+    const bool pair = p.pair != 0;
+    if (pair && p.T != 128) return cudaErrorInvalidValue;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(256));
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)tc_smem_bytes(256, TC_STAGES, 256));
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)tc_smem_bytes(128, TC_STAGES_PAIR, 256));
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const int tiles = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : p.NG / 4;
+    const int tiles = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : (p.N + TILE_N - 1) / TILE_N;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)tiles, (unsigned)((p.M + p.T - 1) / p.T), 1);
     cfg.blockDim = dim3(TC_THREADS);
-    cfg.dynamicSmemBytes = tc_smem_bytes(p.T);
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (pair) {
+        // CTA pairs along x: two neighbouring channel tiles share one 256-token tile
+        cfg.gridDim = dim3((unsigned)((tiles + 1) / 2 * 2), (unsigned)((p.M + 255) / 256), 1);
+        cfg.dynamicSmemBytes = tc_smem_bytes(128, TC_STAGES_PAIR, 256);
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 2;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    } else {
+        cfg.gridDim = dim3((unsigned)tiles, (unsigned)((p.M + p.T - 1) / p.T), 1);
+        cfg.dynamicSmemBytes = tc_smem_bytes(p.T, TC_STAGES, p.T);
+    }
+    if (pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel, p);
+    cfg.numAttrs = n;
+    return pair ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, p) : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false>, p);
 }
 
 } // namespace rkb200

@@ -82,6 +82,7 @@ struct rk_npu_w4a8_workspace {
     std::atomic_flag busy = ATOMIC_FLAG_INIT;
     cudaStream_t stream = nullptr;
     // geometry
+    bool pair = false; // tcgen05 path runs two-CTA tiles
     int T = 0;        // token tile of the code layout
     int TC = 0;       // tokens per CTA of the mma.sync kernel (0 when the tcgen05 kernel is used)
     int KB = 0;       // k-blocks

@@ -442,7 +442,7 @@ static cudaError_t launch_mma_inst(const GemmParams& p, cudaStream_t stream, boo
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const int tiles = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : p.NG / 4;
+    const int tiles = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : (p.N + TILE_N - 1) / TILE_N;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)tiles, (unsigned)p.split, (unsigned)((p.M + TC - 1) / TC));
     cfg.blockDim = dim3(160);

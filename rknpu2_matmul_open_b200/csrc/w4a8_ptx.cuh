@@ -33,14 +33,16 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
 }
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+// One suspended probe: the thread sleeps in hardware (no issue slots used) until the phase
+// with the given parity completes or about `hint_ns` passes.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
@@ -48,12 +50,9 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // (global timer).  Returns false when the wait ran out; the caller records the error
 // and leaves its loop, so a lost signal can never hang the GPU.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long deadline_ns) {
-    for (uint32_t spin = 0;; ++spin) {
-        if (mbar_test(bar, parity)) return true;
-        if ((spin & 255u) == 255u) {
-            if (global_ns() > deadline_ns) return false;
-            __nanosleep(64);
-        }
+    for (;;) {
+        if (mbar_try(bar, parity, 2000u)) return true;
+        if (global_ns() > deadline_ns) return false;
     }
 }
 
