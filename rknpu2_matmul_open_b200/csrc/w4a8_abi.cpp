@@ -350,7 +350,8 @@ int enqueue(const Call& c)
     if (ws.variant == 2) {
         g.split = 1;
         g.pair = ws.pair ? 1 : 0;
-        err = launch_gemm_tc(g, c.stream, pdl);
+        if (gemm_tc_persist_supported(g) && !env_flag("RK_NPU_B200_NO_PERSIST", false)) err = launch_gemm_tc_persist(g, c.stream, pdl);
+        else err = launch_gemm_tc(g, c.stream, pdl);
     } else {
         g.split = pick_split(ws, tiles, (cfg.M + ws.TC - 1) / ws.TC);
         err = launch_gemm_mma(g, ws.TC, c.stream, pdl);

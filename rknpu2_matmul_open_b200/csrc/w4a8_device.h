@@ -113,5 +113,8 @@ size_t gemm_fused_smem_bytes(int tokens_per_cta, int stages);
 // tcgen05 path: p.T is the token tile of the code layout (multiple of 16, <= 256; 128 when p.pair)
 cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl);
 bool gemm_tc_supported(const GemmParams& p);
+// persistent two-CTA form (binary16 output or fused SwiGLU); p.pair and p.T == 128 required
+cudaError_t launch_gemm_tc_persist(const GemmParams& p, cudaStream_t stream, bool pdl);
+bool gemm_tc_persist_supported(const GemmParams& p);
 
 } // namespace rkb200

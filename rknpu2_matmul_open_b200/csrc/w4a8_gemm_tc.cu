@@ -31,6 +31,7 @@
 #include "w4a8_device.h"
 #include "w4a8_math.cuh"
 #include "w4a8_ptx.cuh"
+#include "w4a8_tc.cuh"
 
 namespace rkb200 {
 
@@ -48,113 +49,6 @@ __host__ __device__ constexpr size_t tc_stage_bytes(int T) { return 2 * (8192 + 
 __host__ __device__ constexpr size_t tc_smem_bytes(int T, int stages, int tokens)
 {
     return stages * tc_stage_bytes(T) + (size_t)tokens * 4 /* token scales */ + (2 * stages + 2 * TC_ABUF + 1) * 8 + 32;
-}
-
-// ---- tcgen05 wrappers
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-// paired forms: the MMA spans both CTAs of the cluster; the commit arrives on the barrier at
-// the same shared-memory offset in every CTA of the mask
-__device__ __forceinline__ void tc_commit_pair(uint64_t* bar)
-{
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)), "h"((uint16_t)3)
-                 : "memory");
-}
-__device__ __forceinline__ void tc_mma_i8_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-// arrive on the barrier at the same offset in CTA `rank` of the cluster
-__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank)
-{
-    asm volatile(
-        "{\n\t.reg .b32 ra;\n\t"
-        "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
-        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
-        ::"r"(smem_u32(bar)), "r"(rank)
-        : "memory");
-}
-// bounded wait with cluster-scope acquire (arrivals may come from the peer CTA or from a
-// multicast commit)
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, unsigned long long deadline_ns)
-{
-    for (;;) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)
-            : "memory");
-        if (ok) return true;
-        if (global_ns() > deadline_ns) return false;
-    }
-}
-__device__ __forceinline__ uint32_t cluster_rank()
-{
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory operand descriptor: K-major, no swizzle.  A core matrix is eight rows of
-// 16 bytes, contiguous (128 B); `lbo` = bytes between core matrices adjacent in K, `sbo` =
-// bytes between core matrices adjacent in the row (token) direction.
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo)
-{
-    const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | ((lbo >> 4) << 16);
-    const uint32_t hi = (sbo >> 4) | (1u << 14);   // descriptor version 1 (sm_100); layout type 0 = no swizzle
-    return ((uint64_t)hi << 32) | lo;
-}
-// Instruction descriptor: int32 accumulators, signed 8-bit A and B, both K-major, M = 128.
-__device__ __forceinline__ uint32_t tc_idesc_s8(int m, int n)
-{
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 template <bool PAIR>
@@ -190,7 +84,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
 #define TC_STAMP(role, kb, slot) do { if (trace && (kb) < 64) trace[((role) * 64 + (kb)) * 4 + (slot)] = (unsigned long long)(clock64() - c0); } while (0)
 
     if (tid == 0) {
-        for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 9); }   // 2 x 4 unpack warps + 1 commit
+        for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 5); }   // 4 unpack warps + 1 commit
         for (int b = 0; b < TC_ABUF; ++b) { mbar_init(&a_ready[b], PAIR ? 8 : 4); mbar_init(&a_free[b], 1); }
         mbar_init(acc_done, 1);
         mbar_fence_init();
@@ -272,40 +166,58 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
             }
         } else {
             // ---------------------------------------------------------------- weight unpack -> TMEM
+            // A set takes every other STAGE and unpacks both of its k-blocks in one go: one
+            // round of barrier waits, eight shared-memory loads, two tensor-memory stores.
             const int q = warp & 3;                       // TMEM lane quarter == weight group of the tile
-            const int set = (warp - 2) >> 2;              // this set takes k-blocks kb % 2 == set
+            const int set = (warp - 2) >> 2;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
             bool ok = true;
-            for (int kb = set; kb < KB && ok; kb += 2) {
-                const int it = kb >> 1, s = it % NSTAGE, b = kb % TC_ABUF;   // this set's half of the stage: kb & 1 == set
+            const int nstage_iters = (KB + 1) / 2;
+            for (int it = set; it < nstage_iters && ok; it += 2) {
+                const int s = it % NSTAGE, kb = 2 * it;
+                const int kbs = min(2, KB - kb);
+                const int b0 = kb % TC_ABUF, b1 = (kb + 1) % TC_ABUF;
                 if (q == 2 && lane == 0) TC_STAMP(2, kb, 2);
                 ok = mbar_wait(&full[s], (it / NSTAGE) & 1, deadline);
                 if (q == 2 && lane == 0) TC_STAMP(2, kb, 3);
-                if (ok && kb >= TC_ABUF) ok = mbar_wait_cluster(&a_free[b], ((kb / TC_ABUF) - 1) & 1, deadline);
-                ok = __all_sync(0xffffffffu, ok);   // the tensor-memory store below needs the whole warp
+                if (ok && kb >= TC_ABUF) {
+                    ok = mbar_wait_cluster(&a_free[b0], ((kb / TC_ABUF) - 1) & 1, deadline);
+                    if (ok && kbs == 2) ok = mbar_wait_cluster(&a_free[b1], (((kb + 1) / TC_ABUF) - 1) & 1, deadline);
+                }
+                ok = __all_sync(0xffffffffu, ok);   // the tensor-memory stores below need the whole warp
                 if (!ok) { *s_error = 1; break; }
                 if (q == 2 && lane == 0) TC_STAMP(2, kb, 0);
                 tc_fence_after();
-                const uint4* src = reinterpret_cast<const uint4*>(stages + (size_t)s * stage_bytes + q * 4096 + set * 2048) + lane;
-                uint32_t r[32];
+                const uint4* src = reinterpret_cast<const uint4*>(stages + (size_t)s * stage_bytes + q * 4096) + lane;
+                uint4 w[8];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint4 w = src[c * 32];
-                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+                for (int c = 0; c < 8; ++c) w[c] = (c < 4 * kbs) ? src[c * 32] : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        r[c * 8 + j] = (ww[j] << 4) & 0xF0F0F0F0u;       // k = 32c + 4j .. +3      (x16)
-                        r[c * 8 + 4 + j] = ww[j] & 0xF0F0F0F0u;          // k = 32c + 16 + 4j .. +3 (x16)
+                for (int h = 0; h < 2; ++h) {
+                    if (h < kbs) {
+                        uint32_t r[32];
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const uint32_t ww[4] = {w[4 * h + c].x, w[4 * h + c].y, w[4 * h + c].z, w[4 * h + c].w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                r[c * 8 + j] = (ww[j] << 4) & 0xF0F0F0F0u;       // k = 32c + 4j .. +3      (x16)
+                                r[c * 8 + 4 + j] = ww[j] & 0xF0F0F0F0u;          // k = 32c + 16 + 4j .. +3 (x16)
+                            }
+                        }
+                        tc_st32(lane_addr + TC_A_COL0 + (h ? b1 : b0) * 32, r);
                     }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);    // the packed weights of this stage are in registers
-                tc_st32(lane_addr + TC_A_COL0 + b * 32, r);
                 if (q == 2 && lane == 0) TC_STAMP(2, kb, 1);
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) { if (PAIR && rank != 0) mbar_arrive_remote(&a_ready[b], 0); else mbar_arrive(&a_ready[b]); }
+                if (lane == 0) {
+                    if (PAIR && rank != 0) { mbar_arrive_remote(&a_ready[b0], 0); if (kbs == 2) mbar_arrive_remote(&a_ready[b1], 0); }
+                    else { mbar_arrive(&a_ready[b0]); if (kbs == 2) mbar_arrive(&a_ready[b1]); }
+                }
             }
         }
 

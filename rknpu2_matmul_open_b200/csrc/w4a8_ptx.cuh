@@ -49,7 +49,19 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity, uint32_
 // Wait for the phase with the given parity to complete, giving up at `deadline_ns`
 // (global timer).  Returns false when the wait ran out; the caller records the error
 // and leaves its loop, so a lost signal can never hang the GPU.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long deadline_ns) {
+    if (mbar_test(bar, parity)) return true;   // already complete: no suspend round trip
     for (;;) {
         if (mbar_try(bar, parity, 2000u)) return true;
         if (global_ns() > deadline_ns) return false;
