@@ -93,19 +93,6 @@ class ClockSampler:
         return out
 
 
-def shard_columns(N: int, world: int, rank: int):
-    """Contiguous 64-column blocks, the first `blocks % world` ranks one block more
-    (the reference's split over NPU cores, src/rk_npu_i4_plan.cpp:37-43)."""
-    blocks = (N + 63) // 64
-    start = 0
-    for r in range(world):
-        count = blocks // world + (1 if r < blocks % world else 0)
-        if r == rank:
-            return min(N, start * 64), min(N, (start + count) * 64)
-        start += count
-    raise ValueError(rank)
-
-
 # ------------------------------------------------------------------ reference arm (CPU)
 def run_reference(args, rank, world):
     if rank != 0:
@@ -169,6 +156,7 @@ def run_cuda(args, rank, world, local_rank):
 
     import rknpu2_matmul_open_b200 as rk
     from oracle.harness import Oracle, Reference, make_activations, make_weights, sample_columns
+    from rknpu2_matmul_open_b200.sharding import shard_columns
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -240,6 +228,11 @@ def run_cuda(args, rank, world, local_rank):
     for l in linears:
         if l["ws"].finish() != 0:
             raise RuntimeError("device status not clean after the check step")
+    count0 = sum(l["ws"].launch_count() for l in linears)
+    with torch.cuda.stream(stream):
+        enqueue_step(stream)
+    stream.synchronize()
+    launches_per_step = sum(l["ws"].launch_count() for l in linears) - count0   # this library's kernels per step
 
     # ---- device-resident timing (value)
     graph = None
@@ -312,13 +305,16 @@ def run_cuda(args, rank, world, local_rank):
     if world == 1 and args.tokens != 1 and not args.quick:
         also["M1_GBps"] = _time_other_m(rk, dom, linears, 1, args, dev, stream)
 
+    if world == 1 and not args.quick:
+        also.update(_prefill_and_ffn(rk, dom, dev, stream, oracle, make_weights, make_activations, sample_columns))
+
     # ---- CPU baseline on a bounded sample (rank 0, one GPU only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline(M, Reference if Reference.available() else None, oracle, make_weights, make_activations)
 
     if rank == 0:
-        launches = 2 * len(linears) * args.steps
+        launches = launches_per_step * args.steps
         value = step_bytes / (ms_step * 1e-3) / 1e9
         gemm_bytes_per_launch = step_bytes / len(linears)
         line = {"metric": "w4a8_decode_weight_stream", "value": value, "unit": "GB/s", "n_gpus": world,
@@ -333,7 +329,7 @@ def run_cuda(args, rank, world, local_rank):
                 "gpu_launches": launches,
                 "roofline": {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
                              "frac": value / world / hbm_peak, "traffic": None, "peak_kind": peak_kind,
-                             "kernel": "gemm_mma_kernel (+ quantize_kernel in the same interval)",
+                             "kernel": "gemm_fused_kernel (scan + quantise + GEMM + dequantise in one launch)",
                              "bytes_per_launch": gemm_bytes_per_launch,
                              "us_per_launch": 1e3 * ms_step / len(linears)},
                 "cpu_baseline": cpu, "also": also}
@@ -391,6 +387,72 @@ def _time_other_m(rk, dom, linears, M, args, dev, stream):
     for ws, *_ in extra:
         ws.free()
     return total / (ms * 1e-3) / 1e9
+
+
+INT8_PEAK_TOPS = 4550.0   # dense int8 tcgen05 peak measured on this pool's B200 with lib/int8_peak (burst, 1965 MHz)
+
+
+def _event_time(torch, stream, fn, reps):
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            fn()
+    stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+    stream.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def _prefill_and_ffn(rk, dom, dev, stream, oracle, make_weights, make_activations, sample_columns):
+    """BASELINE config 2 (prefill GEMM 2048 x 4096 x 14336, fp16) and config 3 (fused FFN 4096 -> 2 x 14336 -> 4096,
+    M = 1 and 1024), device-resident, each checked against the oracle on sampled columns / rows."""
+    import torch
+    out = {}
+    M, K, N = 2048, 4096, 14336
+    B, sw = make_weights(K, N, seed=21)
+    A = make_activations(M, K, seed=21, dtype="f16")
+    w = rk.Weights(dom, B, sw)
+    ws = rk.Workspace(dom, rk.default_config(M, N, K))
+    dA = torch.from_numpy(A.view(np.int16)).to(dev)
+    dC = torch.zeros((M, N), dtype=torch.int16, device=dev)
+    ms = _event_time(torch, stream, lambda: ws.enqueue_f16(w, dA, dC, stream.cuda_stream), 10)
+    cols = sample_columns(N)
+    _, s, inv = oracle.scales(A)
+    ref = oracle.dequant(oracle.gemm_i32_columns(oracle.quantize(A, inv), B, cols), s, sw[cols], True)
+    exact = bool(np.array_equal(dC.cpu().numpy().view(np.uint16)[:, cols], ref))
+    tops = 2.0 * M * K * N / (ms * 1e-3) / 1e12
+    out["prefill_M2048_K4096_N14336"] = {"us": ms * 1e3, "tops": tops, "frac_of_measured_int8_peak": tops / INT8_PEAK_TOPS,
+                                         "peak_tops": INT8_PEAK_TOPS, "sampled_exact": exact,
+                                         "includes": "quantise kernel + tcgen05 GEMM"}
+    ws.free()
+    w.free()
+    K, F, N = 4096, 14336, 4096
+    Bg, sg = make_weights(K, 2 * F, seed=31)
+    Bd, sd = make_weights(F, N, seed=32)
+    wg, wd = rk.Weights(dom, Bg, sg), rk.Weights(dom, Bd, sd)
+    for M in (1, 1024):
+        A = make_activations(M, K, seed=31, dtype="f32")
+        g = rk.Workspace(dom, rk.default_config(M, 2 * F, K))
+        d = rk.Workspace(dom, rk.default_config(M, N, F))
+        dA = torch.from_numpy(A).to(dev)
+        dM = torch.zeros((M, F), dtype=torch.float32, device=dev)
+        dC = torch.zeros((M, N), dtype=torch.float32, device=dev)
+        ms = _event_time(torch, stream, lambda: rk.enqueue_ffn_f32(g, wg, d, wd, dA, dM, dC, stream.cuda_stream), 10)
+        rows = min(M, 2)
+        ref = oracle.ffn(A[:rows], Bg, sg, Bd, sd, mode=1)
+        exact = bool(np.array_equal(dC.cpu().numpy()[:rows].view(np.uint32), ref["C"].view(np.uint32)))
+        weight_bytes = K * 2 * F // 2 + F * N // 2
+        out[f"ffn_M{M}"] = {"us": ms * 1e3, "weight_GBps": weight_bytes / (ms * 1e-3) / 1e9,
+                            "tops": 2.0 * M * (K * 2 * F + F * N) / (ms * 1e-3) / 1e12, "rows_checked_exact": exact}
+        g.free()
+        d.free()
+    wg.free()
+    wd.free()
+    return out
 
 
 def cpu_baseline(M, Reference, oracle, make_weights, make_activations):
