@@ -76,6 +76,27 @@ int rk_npu_b200_w4a8_set_schedule(rk_npu_w4a8_workspace *workspace, int variant,
 int rk_npu_b200_w4a8_trace_enable(rk_npu_w4a8_workspace *workspace, int enable);
 int rk_npu_b200_w4a8_trace_read(rk_npu_w4a8_workspace *workspace, unsigned long long *stamps, int ctas);
 
+/* One W4A8 linear (binary16 in and out) that allocates nothing.  It has no counterpart in the
+ * original project.  It is meant for callers that are not allowed to allocate when they need
+ * the result -- an engine that carved up its device memory once and forbids cudaMalloc from
+ * then on, a plugin inside a latency-critical loop -- and therefore cannot create a workspace.
+ * The scratch a workspace would own (activation codes, per-token scales, status) lives in a
+ * fixed 2 MiB + 4 KiB array inside the library image; every GPU that loads the library holds
+ * it until the process exits.
+ *   weights      an existing weight object (its creation did allocate; this call does not)
+ *   dA, dC       device pointers on the weights' GPU: [M,K] activations, [M,N] output
+ *   M            1..32 tokens, and 32 x K (K rounded up to 128; 8 or 16 x K for M <= 8 / 16)
+ *                must fit in 2 MiB, i.e. K <= 65536 for M > 16; larger sizes return
+ *                RK_NPU_ERR_NOMEM and do nothing
+ *   cuda_stream  a cudaStream_t; the work is queued, not waited for
+ * The first call on a device looks up the array's device address; make that first call before
+ * any stream capture starts.  All calls share the one array, which keeps the previous call's
+ * contents (the parts that must start at zero are cleared on the stream first): two calls
+ * whose GPU work overlaps -- different streams, no ordering between them -- race on it.
+ * A row of dA holding NaN or Inf leaves dC unwritten.  Returns RK_NPU_OK once queued. */
+int rk_npu_b200_w4a8_enqueue_f16_static(const rk_npu_w4a8_weights *weights, const uint16_t *dA, uint16_t *dC, int M,
+                                        void *cuda_stream);
+
 /* Kernels this workspace has launched since creation (for launch accounting). */
 uint64_t rk_npu_b200_w4a8_launch_count(const rk_npu_w4a8_workspace *workspace);
 

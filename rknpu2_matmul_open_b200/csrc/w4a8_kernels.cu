@@ -8,6 +8,7 @@
 //                     src/rk_npu_w4a8_swiglu.cpp:12-91 + src/rk_npu_swiglu_fp32_neon.h:13-51
 //   pack_weights    : src/rk_npu_w4a8.cpp:236-242 (code range check); layout is new.
 #include "w4a8_device.h"
+#include "w4a8_host.h"
 #include "w4a8_ptx.cuh"
 #include "w4a8_math.cuh"
 #include <cooperative_groups.h>
@@ -479,3 +480,97 @@ cudaError_t launch_gemm_mma(const GemmParams& p, int tokens_per_cta, cudaStream_
 }
 
 } // namespace rkb200
+
+// =============================================================== linear without any allocation
+// Some callers may not allocate at the moment they need a linear: an inference engine that
+// sized its one device pool at start-up and forbids cudaMalloc afterwards, a plugin running
+// inside somebody else's real-time loop, code on a path where an allocation (and the implicit
+// device synchronisation cudaMalloc and cudaFree bring) is not acceptable.  A workspace is
+// what normally owns the scratch of a call -- the quantised activation codes, the per-token
+// scales and the status word -- and creating one allocates.  The entry point below runs the
+// same two kernels as a small-batch workspace (quantise, then the mma.sync split-K GEMM) with
+// that scratch in a fixed array that is part of the library image, so the call itself
+// allocates nothing.  Every GPU that loads the library carries the array until exit.
+namespace {
+constexpr int STATIC_MAX_TOKENS = 32;
+constexpr size_t STATIC_CODE_BYTES = size_t(2) << 20;               // activation codes: tokens_per_cta x padded K bytes
+constexpr size_t STATIC_SCRATCH_BYTES = STATIC_CODE_BYTES + 4096;   // + scales, inverse scales, status block
+}
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_lock;
+unsigned char* g_static_ptr[64] = {};   // device address of the array, per CUDA ordinal
+
+// The array's name is only a host-side handle; kernels need its address on the current device.
+int static_scratch(int device, unsigned char** out)
+{
+    if (device < 0 || device >= 64) return RK_NPU_ERR_PARAM;
+    std::lock_guard<std::mutex> guard(g_static_lock);
+    if (!g_static_ptr[device]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) { cudaGetLastError(); return RK_NPU_ERR_IOCTL; }
+        g_static_ptr[device] = static_cast<unsigned char*>(ptr);
+    }
+    *out = g_static_ptr[device];
+    return RK_NPU_OK;
+}
+} // namespace
+
+extern "C" int rk_npu_b200_w4a8_enqueue_f16_static(const rk_npu_w4a8_weights* weights, const uint16_t* dA, uint16_t* dC,
+                                                   int M, void* cuda_stream)
+{
+    using namespace rkb200;
+    if (!weights || !dA || !dC || dA == dC || M < 1) return RK_NPU_ERR_PARAM;
+    const int K = weights->info.config.K, N = weights->info.config.N;
+    const int tokens = M <= 8 ? 8 : M <= 16 ? 16 : 32;
+    const size_t code_bytes = size_t(tokens) * weights->KB * KBLOCK;
+    // sizes beyond the fixed array are refused, never truncated
+    if (M > STATIC_MAX_TOKENS || code_bytes > STATIC_CODE_BYTES) return RK_NPU_ERR_NOMEM;
+    const rk_npu_ctx* ctx = weights->domain->ctx;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+    unsigned char* base = nullptr;
+    const int rc = static_scratch(ctx->device, &base);
+    if (rc) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    uint8_t* codes = base;
+    float* scales = reinterpret_cast<float*>(base + STATIC_CODE_BYTES);
+    Status* status = reinterpret_cast<Status*>(base + STATIC_CODE_BYTES + 1024);
+    // The array keeps whatever the previous call left: padding rows of the code tile and the
+    // status block must start at zero.
+    if (cudaMemsetAsync(codes, 0, code_bytes, stream) != cudaSuccess ||
+        cudaMemsetAsync(status, 0, sizeof(Status), stream) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+    QuantParams q{};
+    q.A = dA;
+    q.Xq = codes;
+    q.scales = scales;
+    q.inverse = scales + STATIC_MAX_TOKENS;
+    q.status = status;
+    q.M = M;
+    q.K = K;
+    q.Kp = weights->KB * KBLOCK;
+    q.T = tokens;
+    q.half = 1;
+    if (launch_quantize(q, stream, false) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+    GemmParams g{};
+    g.Wp = weights->packed;
+    g.Xq = codes;
+    g.sx = scales;
+    g.sw = weights->scales;
+    g.out = dC;
+    g.status = status;
+    g.M = M;
+    g.N = N;
+    g.K = K;
+    g.KB = weights->KB;
+    g.NG = weights->NG;
+    g.T = tokens;
+    g.epi = EPI_F16;
+    g.timeout_ns = 500ull * 1000000ull;
+    const int tiles = (N + TILE_N - 1) / TILE_N;
+    int split = 1;
+    while (split < 8 && (long long)tiles * split * 2 <= (long long)(5 * ctx->sm_count) / 2 && weights->KB / (split * 2) >= 2) split *= 2;
+    g.split = split;
+    if (launch_gemm_mma(g, tokens, stream, false) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+    return RK_NPU_OK;
+}
