@@ -47,6 +47,22 @@ __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank)
         ::"r"(smem_u32(bar)), "r"(rank)
         : "memory");
 }
+// Signal-only arrivals: nothing this thread wrote has to become visible with them (they
+// report that tensor-memory READS have completed, which tcgen05.wait::ld already ensured),
+// so they must not wait for the thread's outstanding global stores the way a release does.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote_relaxed(uint64_t* bar, uint32_t rank)
+{
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(smem_u32(bar)), "r"(rank)
+        : "memory");
+}
 // bounded wait with cluster-scope acquire (arrivals may come from the peer CTA or from a
 // multicast commit)
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, unsigned long long deadline_ns)
@@ -74,6 +90,43 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
         if (ok) return true;
         if (global_ns() > deadline_ns) return false;
     }
+}
+// Warp-wide bounded wait that keeps the issue slots free for the warps that have work: lane 0
+// alone polls (suspended try_wait, a short sleep between probes); once it has seen the phase
+// complete, every lane performs one successful test of its own, which gives each of them the
+// acquire it needs for data written by bulk copies or by the peer CTA.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, unsigned long long deadline_ns)
+{
+    uint32_t ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        while (!done) {
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(done) : "r"(smem_u32(bar)), "r"(parity), "r"(4000u) : "memory");
+            if (done) break;
+            if (global_ns() > deadline_ns) { ok = 0; break; }
+            __nanosleep(64);
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        (void)done;
+    }
+    return ok != 0;
 }
 __device__ __forceinline__ uint32_t cluster_rank()
 {
