@@ -276,7 +276,8 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
         const int col = swiglu ? (q >> 1) * 32 + (q & 1) * 16 + (lane & 15) : q * 32 + lane;
         const bool up_lane = swiglu && lane >= 16;
         const int odd = lane & 1;
-        const bool pair_ok = (out_cols % 2 == 0) && (reinterpret_cast<uintptr_t>(p.out) & 3u) == 0;
+        const bool quad_ok = (out_cols % 4 == 0) && (reinterpret_cast<uintptr_t>(p.out) & 7u) == 0;
+        const bool small_sums = (long long)KB * KBLOCK * 7 * 127 < (1ll << 22);
         bool ok = !skip;
         int j = 0;
         for (int t = cluster_id; t < total && ok; t += num_clusters, ++j) {
@@ -327,44 +328,68 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                         sxr[4 * v] = f.x; sxr[4 * v + 1] = f.y; sxr[4 * v + 2] = f.z; sxr[4 * v + 3] = f.w;
                     }
                 }
+                // int32 sum (a multiple of 16) -> float, rounded to nearest like the conversion instruction.
+                // The conversion unit is an eighth as wide as the FP32 pipe and would bound the whole
+                // drain, so when the bound K * 7 * 127 keeps every sum below 2^22 the exact
+                // magic-number form is used: bits(1.5 * 2^23) + v read as a float is 1.5 * 2^23 + v.
+                if (p.epi != EPI_I32) {
+                    if (small_sums) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__fsub_rn(__uint_as_float(0x4B400000u + (uint32_t)((int)r[i] >> 4)), 12582912.f));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__int2float_rn((int)r[i] >> 4));
+                    }
+                }
                 if (p.epi == EPI_F16) {
                     // a lane holds one channel of 32 tokens; neighbouring lanes swap halves so that
                     // every lane stores two neighbouring channels of one token as one 32-bit word
                     __half* const out = reinterpret_cast<__half*>(p.out);
-                    const int n2 = n - odd;
                     uint32_t word[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float y0 = dequant((int)r[2 * i] >> 4, sxr[2 * i], sw);
-                        const float y1 = dequant((int)r[2 * i + 1] >> 4, sxr[2 * i + 1], sw);
+                        const float y0 = __fmul_rn(__fmul_rn(__uint_as_float(r[2 * i]), sxr[2 * i]), sw);
+                        const float y1 = __fmul_rn(__fmul_rn(__uint_as_float(r[2 * i + 1]), sxr[2 * i + 1]), sw);
                         const __half2 h = __floats2half2_rn(y0, y1);
                         word[i] = *reinterpret_cast<const uint32_t*>(&h);
                     }
+                    // two exchange rounds turn (one channel, 32 tokens) per lane into (four neighbouring
+                    // channels, 8 tokens) per lane: lanes 4g..4g+3 end up with tokens 4i + (lane & 3)
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const uint32_t other = __shfl_xor_sync(0xffffffffu, word[i], 1);
                         word[i] = odd ? __byte_perm(other, word[i], 0x7632) : __byte_perm(word[i], other, 0x5410);
                     }
-                    __half* const row0 = out + (size_t)(m0 + odd) * out_cols + n2;
-                    if (pair_ok && n2 + 1 < out_cols) {
+                    const bool upper = (lane & 2) != 0;
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            if (m0 + 2 * i + odd < p.M) *reinterpret_cast<uint32_t*>(row0 + (size_t)(2 * i) * out_cols) = word[i];
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t recv = __shfl_xor_sync(0xffffffffu, upper ? word[2 * i] : word[2 * i + 1], 2);
+                        if (upper) word[2 * i] = recv; else word[2 * i + 1] = recv;
+                        // now (word[2i], word[2i+1]) = channels n4 .. n4+3 of token m0 + 4i + (lane & 3)
+                    }
+                    const int n4 = n - (lane & 3);
+                    const int mrow = m0 + 2 * (int)upper + odd;
+                    __half* const row0 = out + (size_t)mrow * out_cols + n4;
+                    if (quad_ok && n4 + 3 < out_cols) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            if (mrow + 4 * i < p.M) *reinterpret_cast<uint2*>(row0 + (size_t)(4 * i) * out_cols) = make_uint2(word[2 * i], word[2 * i + 1]);
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            if (m0 + 2 * i + odd < p.M) {
-                                __half* dst = row0 + (size_t)(2 * i) * out_cols;
-                                if (n2 < out_cols) dst[0] = __ushort_as_half((unsigned short)(word[i] & 0xffffu));
-                                if (n2 + 1 < out_cols) dst[1] = __ushort_as_half((unsigned short)(word[i] >> 16));
+                        for (int i = 0; i < 8; ++i)
+                            if (mrow + 4 * i < p.M) {
+                                __half* dst = row0 + (size_t)(4 * i) * out_cols;
+                                const uint32_t ww[2] = {word[2 * i], word[2 * i + 1]};
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    if (n4 + e < out_cols) dst[e] = __ushort_as_half((unsigned short)((ww[e >> 1] >> (16 * (e & 1))) & 0xffffu));
                             }
                     }
                 } else if (p.epi == EPI_F32 || p.epi == EPI_I32) {
                     const bool f32 = p.epi == EPI_F32;
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int v = (int)r[i] >> 4;
-                        r[i] = f32 ? __float_as_uint(dequant(v, sxr[i], sw)) : (uint32_t)v;
+                        r[i] = f32 ? __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r[i]), sxr[i]), sw)) : (uint32_t)((int)r[i] >> 4);
                     }
                     uint32_t* const row0 = reinterpret_cast<uint32_t*>(p.out) + (size_t)m0 * out_cols + n;
                     if (n_ok) {
@@ -376,7 +401,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                     uint32_t mx[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const float mine = dequant((int)r[i] >> 4, sxr[i], sw);           // gate lanes: g, up lanes: u
+                        const float mine = __fmul_rn(__fmul_rn(__uint_as_float(r[i]), sxr[i]), sw);   // gate lanes: g, up lanes: u
                         const float up = __shfl_xor_sync(0xffffffffu, mine, 16);
                         const float y = __fmul_rn(silu_poly(mine), up);                   // meaningful in gate lanes
                         const bool live = !up_lane && n_ok && m0 + i < p.M;

@@ -1,0 +1,91 @@
+"""Small fixed workloads for profilers: `python -m rknpu2_matmul_open_b200.profile_case <case>`.
+
+Each case runs a handful of launches of one hot-path configuration on seeded synthetic data
+and exits, so that a kernel profiler can capture one to three launches of the kernel of
+interest in a minute or two.  Cases:
+
+  decode   the seven Llama-7B decode linears (4 x 4096->4096, 2 x 4096->11008, 11008->4096)
+           at M = 8, binary16 in and out, one decoder layer, stream launches
+  prefill  one 2048 x 4096 x 14336 linear, binary16 in and out
+  ffn      gate/up 4096 -> 2 x 14336, SwiGLU, down 14336 -> 4096 at M = 1024, fp32
+
+Options: --repeat R (launch sets, default 4), --tokens M (override the batch).
+"""
+from __future__ import annotations
+
+import argparse
+
+import numpy as np
+
+
+def _weights(rng, K, N):
+    B = rng.integers(-7, 8, size=(K, N), dtype=np.int8)
+    scale = rng.uniform(0.001, 0.01, size=N).astype(np.float32)
+    return B, scale
+
+
+def _activations(rng, M, K, dtype):
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    x[:, rng.random(K) < 0.005] *= 20.0
+    return x.astype(dtype)
+
+
+def main() -> None:
+    import torch
+
+    import rknpu2_matmul_open_b200 as rk
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["decode", "prefill", "ffn"])
+    ap.add_argument("--repeat", type=int, default=4)
+    ap.add_argument("--tokens", type=int, default=0)
+    args = ap.parse_args()
+    rng = np.random.default_rng(0)
+    ctx = rk.Context()
+    dom = ctx.domain(0)
+    dev = torch.device("cuda", ctx.device)
+    stream = torch.cuda.Stream(device=dev)
+    calls = []
+    if args.case in ("decode", "prefill"):
+        M = args.tokens or (8 if args.case == "decode" else 2048)
+        shapes = [(4096, 4096)] * 4 + [(4096, 11008)] * 2 + [(11008, 4096)] if args.case == "decode" else [(4096, 14336)]
+        for K, N in shapes:
+            B, sw = _weights(rng, K, N)
+            w = rk.Weights(dom, B, sw)
+            ws = rk.Workspace(dom, rk.default_config(M, N, K))
+            dA = torch.from_numpy(_activations(rng, M, K, np.float16).view(np.int16)).to(dev)
+            dC = torch.zeros((M, N), dtype=torch.int16, device=dev)
+            calls.append((lambda ws=ws, w=w, dA=dA, dC=dC: ws.enqueue_f16(w, dA, dC, stream.cuda_stream), ws))
+    else:
+        M = args.tokens or 1024
+        K, F, N = 4096, 14336, 4096
+        Bg, sg = _weights(rng, K, 2 * F)
+        Bd, sd = _weights(rng, F, N)
+        wg, wd = rk.Weights(dom, Bg, sg), rk.Weights(dom, Bd, sd)
+        g = rk.Workspace(dom, rk.default_config(M, 2 * F, K))
+        d = rk.Workspace(dom, rk.default_config(M, N, F))
+        dA = torch.from_numpy(_activations(rng, M, K, np.float32)).to(dev)
+        dM = torch.zeros((M, F), dtype=torch.float32, device=dev)
+        dC = torch.zeros((M, N), dtype=torch.float32, device=dev)
+        calls.append((lambda: rk.enqueue_ffn_f32(g, wg, d, wd, dA, dM, dC, stream.cuda_stream), d))
+        calls.append((lambda: 0, g))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for rep in range(args.repeat):
+        with torch.cuda.stream(stream):
+            if rep == args.repeat - 1:
+                e0.record(stream)
+            for fn, _ in calls:
+                rc = fn()
+                if rc:
+                    raise RuntimeError(f"enqueue failed: {rc}")
+            if rep == args.repeat - 1:
+                e1.record(stream)
+        stream.synchronize()
+    for _, ws in calls:
+        if ws.finish() != 0:
+            raise RuntimeError("device status not clean")
+    print(f"{args.case}: M={M}, last set {e0.elapsed_time(e1) * 1e3:.1f} us for {len(calls)} call(s)")
+
+
+if __name__ == "__main__":
+    main()
