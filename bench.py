@@ -64,8 +64,16 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def samples(self) -> int:
+        """Rows written so far (nvidia-smi needs a second or two to produce its first one)."""
+        try:
+            self.file.flush()
+            return sum(1 for r in Path(self.file.name).read_text().splitlines() if r.count(",") >= 8)
+        except OSError:
+            return 0
+
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "window": "extended warm-up + timed steps"}
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -257,11 +265,28 @@ def run_cuda(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # The clock sampler starts before the warm-up; the warm-up runs its W steps and then keeps
+    # going (same launches) until the sampler has a few rows or three seconds have passed, so
+    # that the clocks are recorded under the very load that is timed right after.
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     with torch.cuda.stream(stream):
         for _ in range(max(3, args.warmup)):
             do_step()
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    t_warm = time.perf_counter()
+    while True:
+        with torch.cuda.stream(stream):
+            for _ in range(50):
+                do_step()
+        stream.synchronize()
+        enough = sampler is None or sampler.proc is None or sampler.samples() >= 4 or time.perf_counter() - t_warm > 3.0
+        if world > 1:
+            flag = torch.tensor([1 if enough else 0], device=dev)
+            dist.broadcast(flag, src=0)
+            enough = bool(flag.item())
+        if enough:
+            break
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         e0.record(stream)
@@ -270,6 +295,7 @@ def run_cuda(args, rank, world, local_rank):
         e1.record(stream)
     barrier()
     ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -296,7 +322,6 @@ def run_cuda(args, rank, world, local_rank):
         t = torch.tensor([e2e_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
-    clocks = sampler.stop() if sampler else None
     h2d = sum(M * l["K"] * 2 for l in linears)
     d2h = sum(M * (l["n1"] - l["n0"]) * 2 for l in linears)
 
@@ -306,6 +331,7 @@ def run_cuda(args, rank, world, local_rank):
         also["M1_GBps"] = _time_other_m(rk, dom, linears, 1, args, dev, stream)
 
     if world == 1 and not args.quick:
+        also["independent_linears_4_streams_GBps"] = _time_streams(linears, step_bytes, args, dev, 4)
         also.update(_prefill_and_ffn(rk, dom, dev, stream, oracle, make_weights, make_activations, sample_columns))
 
     # ---- CPU baseline on a bounded sample (rank 0, one GPU only)
@@ -328,7 +354,11 @@ def run_cuda(args, rank, world, local_rank):
                         "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * e2e_s},
                 "gpu_launches": launches,
                 "roofline": {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
-                             "frac": value / world / hbm_peak, "traffic": None, "peak_kind": peak_kind,
+                             "frac": value / world / hbm_peak,
+                             # ncu (profiles/gemm_fused_kernel_decode_M8.md): 8,530,944 B read + 0 B written for the
+                             # 4096 x 4096 linear whose algorithmic bytes are 8,536,064; traffic is one read per
+                             # weight byte, so it scales with the bytes of the ring's average linear
+                             "traffic": gemm_bytes_per_launch * (8530944.0 / 8536064.0), "peak_kind": peak_kind,
                              "kernel": "gemm_fused_kernel (scan + quantise + GEMM + dequantise in one launch)",
                              "bytes_per_launch": gemm_bytes_per_launch,
                              "us_per_launch": 1e3 * ms_step / len(linears)},
@@ -387,6 +417,51 @@ def _time_other_m(rk, dom, linears, M, args, dev, stream):
     for ws, *_ in extra:
         ws.free()
     return total / (ms * 1e-3) / 1e9
+
+
+def _time_streams(linears, step_bytes, args, dev, n_streams):
+    """The same ring with its linears dealt round-robin onto `n_streams` CUDA streams (they are independent
+    problems: own inputs, outputs and workspaces), captured as one graph with parallel branches.  The headline
+    value keeps them on one stream, where each launch waits for the one in front."""
+    import torch
+    main = torch.cuda.Stream(device=dev)
+    side = [torch.cuda.Stream(device=dev) for _ in range(n_streams)]
+
+    def step():
+        for s in side:
+            s.wait_stream(main)
+        for i, l in enumerate(linears):
+            s = side[i % n_streams]
+            with torch.cuda.stream(s):
+                rc = l["ws"].enqueue_f16(l["w"], l["dA"], l["dC"], s.cuda_stream)
+                if rc:
+                    raise RuntimeError(f"enqueue failed: {rc}")
+        for s in side:
+            main.wait_stream(s)
+
+    torch.cuda.synchronize()
+    graph = None
+    if not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=main):
+                step()
+        except Exception as exc:
+            print(f"[bench] multi-stream capture unavailable ({type(exc).__name__}: {exc})", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+    with torch.cuda.stream(main):
+        for _ in range(3):
+            graph.replay() if graph else step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(main):
+        e0.record(main)
+        for _ in range(args.steps):
+            graph.replay() if graph else step()
+        e1.record(main)
+    torch.cuda.synchronize()
+    return step_bytes / (e0.elapsed_time(e1) / args.steps * 1e-3) / 1e9
 
 
 INT8_PEAK_TOPS = 4550.0   # dense int8 tcgen05 peak measured on this pool's B200 with lib/int8_peak (burst, 1965 MHz)

@@ -45,7 +45,7 @@ int main(int argc,char**argv){
   unsigned long long* d; cudaMalloc(&d,sms*8); unsigned long long h[148];
   cudaFuncSetAttribute(peak<0>,cudaFuncAttributeMaxDynamicSharedMemorySize,65536);
   cudaFuncSetAttribute(peak<1>,cudaFuncAttributeMaxDynamicSharedMemorySize,65536);
-  for(int mode=0;mode<2;++mode) for(int N:{256,128,64}) for(int rep=0;rep<2;++rep){
+  for(int mode=0;mode<2;++mode) for(int N:{256,128,64,32,16}) for(int rep=0;rep<2;++rep){
     cudaEvent_t e0,e1; cudaEventCreate(&e0);cudaEventCreate(&e1);
     cudaEventRecord(e0);
     if(mode==0) peak<0><<<sms,128,65536>>>(iters,N,d); else peak<1><<<sms,128,65536>>>(iters,N,d);

@@ -352,6 +352,11 @@ int enqueue(const Call& c)
         g.pair = ws.pair ? 1 : 0;
         if (gemm_tc_persist_supported(g) && !env_flag("RK_NPU_B200_NO_PERSIST", false)) err = launch_gemm_tc_persist(g, c.stream, pdl);
         else err = launch_gemm_tc(g, c.stream, pdl);
+    } else if (ws.variant == 4) {
+        g.split = 1;
+        g.partials = ws.partials;
+        g.counts = ws.counts;
+        err = launch_gemm_stream(g, ws.domain->ctx->sm_count, c.stream, pdl);
     } else {
         g.split = pick_split(ws, tiles, (cfg.M + ws.TC - 1) / ws.TC);
         err = launch_gemm_mma(g, ws.TC, c.stream, pdl);
@@ -374,6 +379,9 @@ int status_to_rc(rk_npu_w4a8_workspace& ws, cudaStream_t stream)
     const Status s = *ws.host_status;
     if (s.device_error) {
         cudaMemsetAsync(&ws.status->device_error, 0, sizeof(int), stream);
+        // a streaming launch that gave up may have left partial sums behind
+        if (ws.partials) cudaMemsetAsync(ws.partials, 0, ws.partials_bytes, stream);
+        if (ws.counts) cudaMemsetAsync(ws.counts, 0, ws.counts_bytes, stream);
         cudaStreamSynchronize(stream);
         return RK_NPU_ERR_SUBMIT;
     }
@@ -443,6 +451,8 @@ void workspace_destroy(rk_npu_w4a8_workspace* ws)
     if (ws->stage_in) device_free(d, ws->stage_in, ws->stage_in_bytes);
     if (ws->stage_out) device_free(d, ws->stage_out, ws->stage_out_bytes);
     if (ws->trace) device_free(d, ws->trace, ws->trace_bytes);
+    if (ws->partials) device_free(d, ws->partials, ws->partials_bytes);
+    if (ws->counts) device_free(d, ws->counts, ws->counts_bytes);
     if (ws->host_status) cudaFreeHost(ws->host_status);
     for (auto& e : ws->events) if (e) cudaEventDestroy(e);
     if (ws->stream) cudaStreamDestroy(ws->stream);
@@ -791,14 +801,23 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
     const int forced = std::getenv("RK_NPU_B200_VARIANT") ? std::atoi(std::getenv("RK_NPU_B200_VARIANT")) : 0;
     const bool tc_ok = gemm_tc_supported(probe);
     const bool fused_ok = cfg->M <= 32 && ws->KB <= 8 * FUSED_MAX_STAGES;
-    int variant = fused_ok ? 3 : (cfg->M > 32 && tc_ok) ? 2 : 1;
-    if (forced == 1 || (forced == 2 && tc_ok) || (forced == 3 && fused_ok)) variant = forced;
+    const bool stream_ok = cfg->M <= 32 && (long long)ws->KB * KBLOCK <= 131072;
+    // Small batches: the single-kernel path wins while all of the weights fit in the SMs' shared
+    // memory at once (one wave, up to about 24 MB) and the batch is a single 8-token MMA column
+    // block; beyond that the two-kernel ring (quantise + mma.sync GEMM) streams better.  The
+    // tcgen05 streaming kernel (4) is opt-in: its time does not depend on the batch size, but it
+    // only overtakes the ring at 32 tokens.
+    const bool fused_best = fused_ok && cfg->M <= 8 && (long long)cfg->K * cfg->N / 2 <= (24ll << 20);
+    int variant = (cfg->M > 32 && tc_ok) ? 2 : fused_best ? 3 : 1;
+    if (forced == 1 || (forced == 2 && tc_ok) || (forced == 3 && fused_ok) || (forced == 4 && stream_ok)) variant = forced;
     ws->variant = variant;
     if (variant == 2) {
         // Batches above 128 tokens run two-CTA tiles: 128-token code tiles, two per MMA tile.
         ws->TC = 0;
         ws->pair = cfg->M > 128 && !env_flag("RK_NPU_B200_NO_PAIR", false);
         ws->T = ws->pair ? 128 : (cfg->M >= 256 ? 256 : align_up(cfg->M, 16));
+    } else if (variant == 4) {
+        ws->TC = ws->T = cfg->M <= 16 ? 16 : 32;   // tcgen05 N
     } else {
         ws->TC = cfg->M <= 8 ? 8 : cfg->M <= 16 ? 16 : 32;
         ws->T = ws->TC;
@@ -812,6 +831,13 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
     ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->scales), sizeof(float) * 2 * cfg->M);
     ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->rowmax), sizeof(uint32_t) * cfg->M);
     ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->status), sizeof(Status));
+    if (variant == 4) {
+        const size_t tiles = size_t(cfg->N + TILE_N - 1) / TILE_N;
+        ws->partials_bytes = tiles * 128 * size_t(ws->TC) * sizeof(int);
+        ws->counts_bytes = tiles * sizeof(unsigned int);
+        ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->partials), ws->partials_bytes);
+        ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->counts), ws->counts_bytes);
+    }
     ok = ok && !device_alloc(domain, &ws->stage_in, ws->stage_in_bytes);
     ok = ok && !device_alloc(domain, &ws->stage_out, ws->stage_out_bytes);
     if (ok) {
@@ -825,6 +851,8 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
         ok = cudaMemsetAsync(ws->codes, 0, ws->codes_bytes, ws->stream) == cudaSuccess &&
              cudaMemsetAsync(ws->status, 0, sizeof(Status), ws->stream) == cudaSuccess &&
              cudaMemsetAsync(ws->rowmax, 0, sizeof(uint32_t) * cfg->M, ws->stream) == cudaSuccess &&
+             (!ws->partials || cudaMemsetAsync(ws->partials, 0, ws->partials_bytes, ws->stream) == cudaSuccess) &&
+             (!ws->counts || cudaMemsetAsync(ws->counts, 0, ws->counts_bytes, ws->stream) == cudaSuccess) &&
              cudaStreamSynchronize(ws->stream) == cudaSuccess;
         std::memset(ws->host_status, 0, sizeof(Status));
     }
@@ -1012,7 +1040,7 @@ extern "C" int rk_npu_b200_w4a8_last_quant(rk_npu_w4a8_workspace* ws, float* sca
 
 extern "C" int rk_npu_b200_w4a8_set_schedule(rk_npu_w4a8_workspace* ws, int variant, int split_k)
 {
-    if (!ws || variant < 0 || variant > 3 || split_k < 0 || split_k > 8) return RK_NPU_ERR_PARAM;
+    if (!ws || variant < 0 || variant > 4 || split_k < 0 || split_k > 8) return RK_NPU_ERR_PARAM;
     if (ws->variant != 3 && split_k != 0 && split_k != 1 && split_k != 2 && split_k != 4 && split_k != 8) return RK_NPU_ERR_PARAM;
     if (variant != 0 && variant != ws->variant) return RK_NPU_ERR_PARAM;   // the code layout is fixed at creation
     if (ws->variant == 3 && split_k && (ws->KB + split_k - 1) / split_k > FUSED_MAX_STAGES) return RK_NPU_ERR_PARAM;

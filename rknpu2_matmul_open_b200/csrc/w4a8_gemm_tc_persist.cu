@@ -181,13 +181,15 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                     tc_fence_after();
                     const uint32_t xaddr = smem_u32(acts + (size_t)s * PS_XA_BYTES);
                     const uint32_t a_tmem = tmem_base + PS_A_COL0 + b * 64;
+                    // k-step q: k-block q / 4 of the stage, 32 k = two 16-byte chunks per token: the descriptor's
+                    // address field advances by 2 * PS_T (16-byte units) per step
+                    const uint64_t desc0 = tc_smem_desc(xaddr, PS_T * 16u, 128u);
+                    tc_mma_i8_ts_pair(tmem_base, a_tmem, desc0, idesc, it > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        if (q < 4 * kbs) {
-                            // k-step q: half q/4 of the stage, 32 k = two 16-byte chunks per token
-                            const uint64_t desc = tc_smem_desc(xaddr + (uint32_t)(q >> 2) * PS_T * 128 + (uint32_t)(2 * (q & 3)) * PS_T * 16, PS_T * 16u, 128u);
-                            tc_mma_i8_ts_pair(tmem_base, a_tmem + q * 8, desc, idesc, (it > 0 || q > 0) ? 1u : 0u);
-                        }
+                    for (int q = 1; q < 4; ++q) tc_mma_i8_ts_pair_acc(tmem_base, a_tmem + q * 8, desc0 + (uint64_t)(q * 2 * PS_T), idesc);
+                    if (kbs == 2) {
+#pragma unroll
+                        for (int q = 4; q < 8; ++q) tc_mma_i8_ts_pair_acc(tmem_base, a_tmem + q * 8, desc0 + (uint64_t)(q * 2 * PS_T), idesc);
                     }
                     tc_commit_pair(&xempty[s]);   // the activation stage may be refilled once these MMAs retire
                     tc_commit_pair(&a_free[b]);   // and the weight buffer rewritten, in both CTAs

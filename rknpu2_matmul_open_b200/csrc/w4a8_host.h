@@ -86,12 +86,16 @@ struct rk_npu_w4a8_workspace {
     int T = 0;        // token tile of the code layout
     int TC = 0;       // tokens per CTA of the mma.sync kernel (0 when the tcgen05 kernel is used)
     int KB = 0;       // k-blocks
-    int variant = 0, split_override = 0;   // variant: 1 quantise + mma.sync GEMM, 2 quantise + tcgen05 GEMM, 3 fused small batch
+    int variant = 0, split_override = 0;   // variant: 1 quantise + mma.sync GEMM, 2 quantise + tcgen05 GEMM, 3 fused small batch,
+                                           // 4 quantise + persistent streaming GEMM (small batch, large weights)
     // device buffers
     uint8_t* codes = nullptr;
     float* scales = nullptr;
     float* inverse = nullptr;
     uint32_t* rowmax = nullptr;
+    int* partials = nullptr;          // variant 4: per-tile partial sums and k-block counters
+    unsigned int* counts = nullptr;
+    size_t partials_bytes = 0, counts_bytes = 0;
     rkb200::Status* status = nullptr;
     void* stage_in = nullptr;   // device copy of host activations
     void* stage_out = nullptr;  // device copy of host outputs

@@ -67,6 +67,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
         if (global_ns() > deadline_ns) return false;
     }
 }
+// Warp-wide form: lane 0 polls, the others wait at the shuffle and then take one (successful)
+// probe of their own for the acquire.  Keeps 31 of 32 lanes off the barrier unit.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, unsigned long long deadline_ns) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, deadline_ns) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok) (void)mbar_test(bar, parity);
+    return ok != 0;
+}
 
 // ---- bulk async copy global -> shared, completion counted in bytes on an mbarrier.
 // Both addresses 16-byte aligned, size a multiple of 16.

@@ -21,6 +21,27 @@ __device__ __forceinline__ void tc_mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, u
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
+// Accumulating forms (D += A * B) without the predicate set-up.  The issuing thread is a single
+// thread: every instruction it spends between two MMAs costs its full latency, so the loops that
+// issue MMAs keep the per-instruction work to an add on the descriptor and one on the A address.
+__device__ __forceinline__ void tc_mma_i8_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%4, %4, %4, %4}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_ts_pair_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, {%4, %4, %4, %4, %4, %4, %4, %4}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(0u)
+        : "memory");
+}
 // paired forms: the MMA spans both CTAs of the cluster; the commit arrives on the barrier at
 // the same shared-memory offset in every CTA of the mask
 __device__ __forceinline__ void tc_commit_pair(uint64_t* bar)

@@ -158,3 +158,24 @@ def test_full_size_ffn_decode(gpu, oracle):
     ref = oracle.ffn(A, Bg, sg, Bd, sd, mode=1)
     assert np.array_equal(bits(middle), bits(ref["middle"])) and np.array_equal(bits(C), bits(ref["C"]))
     free(gu, dn, wg, wd)
+
+
+# the FFN through every small-batch schedule (SwiGLU epilogue + row-maximum reuse in each GEMM kernel)
+@pytest.mark.parametrize("variant", [1, 3, 4])
+@pytest.mark.parametrize("case", [(1, 1057, 992, 192), (8, 2304, 1600, 300), (20, 479, 96, 65), (32, 4096, 1024, 512)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_ffn_small_batch_schedules_agree(gpu, oracle, monkeypatch, variant, case):
+    _, dom, _ = gpu
+    monkeypatch.setenv("RK_NPU_B200_VARIANT", str(variant))
+    M, K, F, N = case
+    Bg, sg = make_weights(K, 2 * F, seed=F + 1)
+    Bd, sd = make_weights(F, N, seed=N + 1)
+    wg, wd, gu, dn = build(dom, M, K, F, N, Bg, sg, Bd, sd)
+    for rep in range(2):
+        A = make_activations(M, K, seed=rep, dtype="f32")
+        middle, C = np.zeros((M, F), np.float32), np.zeros((M, N), np.float32)
+        assert rk.run_ffn_f32(gu, wg, dn, wd, A, middle, C, None) == 0
+        ref = oracle.ffn(A, Bg, sg, Bd, sd, mode=1)
+        assert np.array_equal(bits(middle), bits(ref["middle"]))
+        assert np.array_equal(bits(C), bits(ref["C"]))
+    free(gu, dn, wg, wd)

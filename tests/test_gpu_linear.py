@@ -91,17 +91,29 @@ def test_extreme_codes_large_sums_and_fp16_overflow(gpu, oracle):
 
 
 @pytest.mark.parametrize("split", [1, 2, 3, 4, 5, 6, 7, 8])
-def test_split_k_clusters_are_exact(gpu, oracle, split):
+def test_split_k_clusters_are_exact(gpu, oracle, split, monkeypatch):
     _, dom, _ = gpu
     shapes = [(8, 2048, 512), (16, 1153, 257), (32, 2048, 384), (8, 2048 * split, 256)]
     if split in (1, 2, 4, 8):
         shapes.append((40, 640, 130))        # larger batch: quantise kernel + split-K GEMM kernel
+        shapes.append((16, 2048, 384))       # default schedule above 8 tokens: quantise kernel + cluster split-K ring
+    else:
+        monkeypatch.setenv("RK_NPU_B200_VARIANT", "3")   # odd cluster sizes exist only in the single-kernel path
     for (M, K, N) in shapes:
         B, sw = make_weights(K, N, seed=split)
         A = make_activations(M, K, seed=split, dtype="f16")
         out, acc = run_case(dom, oracle, A, B, sw, split=split)
         rc, ref, ref_acc, _ = oracle.linear(A, B, sw)
         assert np.array_equal(acc, ref_acc) and np.array_equal(bits(out), bits(ref))
+    if split in (1, 2, 4, 8):
+        # the same cluster sizes through the single-kernel path at 16 and 32 tokens
+        monkeypatch.setenv("RK_NPU_B200_VARIANT", "3")
+        for (M, K, N) in [(16, 1153, 257), (32, 2048, 384)]:
+            B, sw = make_weights(K, N, seed=split)
+            A = make_activations(M, K, seed=split, dtype="f16")
+            out, acc = run_case(dom, oracle, A, B, sw, split=split)
+            rc, ref, ref_acc, _ = oracle.linear(A, B, sw)
+            assert np.array_equal(acc, ref_acc) and np.array_equal(bits(out), bits(ref))
 
 
 def test_scheduling_hints_do_not_change_results(gpu, oracle):
@@ -342,3 +354,50 @@ def test_full_size_decode_sampled(gpu, oracle):
         assert np.array_equal(f2[finite], (f1 * 2)[finite])            # power-of-two scaling is exact
         for x in (ws, w, w2):
             x.free()
+
+
+# Every schedule the library can pick for a small batch (1: quantise + mma.sync ring, 3: single fused
+# kernel, 4: quantise + persistent tcgen05 streaming kernel with its cross-CTA integer fix-up) has to
+# give the same bits; the shapes make the streaming kernel split tiles between CTAs in the middle of K.
+@pytest.mark.parametrize("variant", [1, 3, 4])
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (8, 2304, 1000), (13, 1441, 385), (16, 5000, 300), (32, 1100, 2049),
+                                   (27, 8192, 512)], ids=lambda s: "x".join(map(str, s)))
+def test_small_batch_schedules_agree(gpu, oracle, monkeypatch, variant, shape):
+    _, dom, _ = gpu
+    M, K, N = shape
+    monkeypatch.setenv("RK_NPU_B200_VARIANT", str(variant))
+    B, sw = make_weights(K, N, seed=3 * K + N)
+    for dtype in ("f16", "f32"):
+        A = make_activations(M, K, seed=M + K, dtype=dtype)
+        out, acc = run_case(dom, oracle, A, B, sw)
+        out2, _ = run_case(dom, oracle, A, B, sw)            # the scratch buffers must come back clean
+        rc, ref, ref_acc, _ = oracle.linear(A, B, sw)
+        assert rc == 0
+        assert np.array_equal(acc, ref_acc)
+        assert np.array_equal(bits(out), bits(ref))
+        assert np.array_equal(bits(out2), bits(ref))
+
+
+def test_streaming_schedule_reuses_one_workspace(gpu, oracle, monkeypatch):
+    # many launches through ONE workspace of the streaming schedule: partial-sum slots and
+    # counters are handed back zeroed by the CTA that finishes each tile
+    _, dom, _ = gpu
+    monkeypatch.setenv("RK_NPU_B200_VARIANT", "4")
+    M, K, N = 5, 3000, 1500
+    B, sw = make_weights(K, N, seed=9)
+    w = rk.Weights(dom, B, sw)
+    ws = rk.Workspace(dom, rk.default_config(M, N, K))
+    for rep in range(6):
+        A = make_activations(M, K, seed=rep, dtype="f32")
+        out = np.zeros((M, N), np.float32)
+        assert ws.run_f32(w, A, out) == 0
+        rc, ref, _, _ = oracle.linear(A, B, sw)
+        assert rc == 0 and np.array_equal(bits(out), bits(ref)), rep
+    bad = make_activations(M, K, seed=1, dtype="f32")
+    bad[2, 17] = np.nan
+    assert ws.run_f32(w, bad, out) == capi.RK_NPU_ERR_PARAM   # rejected rows leave the scratch untouched
+    A = make_activations(M, K, seed=77, dtype="f32")
+    assert ws.run_f32(w, A, out) == 0
+    assert np.array_equal(bits(out), bits(oracle.linear(A, B, sw)[1]))
+    ws.free()
+    w.free()
