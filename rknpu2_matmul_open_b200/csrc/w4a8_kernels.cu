@@ -66,7 +66,7 @@ cudaError_t launch_pack_weights(const PackParams& p, cudaStream_t stream)
 // at or above the infinity pattern is NaN/Inf).  Pass 2: q = clamp(round_half_away(
 // x * inverse), -127, 127), written as 16-byte units of the Xq layout.
 template <bool HALF>
-__global__ void __launch_bounds__(256) quantize_kernel(const QuantParams p)
+__global__ void __launch_bounds__(256, 8) quantize_kernel(const QuantParams p)
 {
     using T = typename ActType<HALF>::type;
     pdl_launch_dependents();   // the GEMM behind this kernel may start prefetching weights
@@ -119,6 +119,22 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantParams p)
         s_inverse = inv;
         s_bad = bad;
     }
+    __syncthreads();
+    const float inv = s_inverse;
+    const int mt = m / p.T, t = m - mt * p.T;
+    uint4* dst = reinterpret_cast<uint4*>(p.Xq) + ((size_t)mt * chunks) * p.T + t;
+    for (int kc = tid; kc < chunks; kc += 256) {
+        uint4 q = make_uint4(0u, 0u, 0u, 0u);
+        if (kc < live_chunks) {
+            float v[16];
+            uint32_t unused = 0;
+            load16<HALF>(row, kc * 16, p.K, vec, v, unused);
+            q = quantize16(v, inv, kc * 16, p.K);
+        }
+        dst[(size_t)kc * p.T] = q;
+    }
+    // Cross-CTA bookkeeping last, so that the other 255 threads of the CTA never wait for its
+    // round trips to L2.
     if (tid == 0) {
         if (p.rowmax_zero) p.rowmax_zero[m] = 0u;
         // "Any row bad" across CTAs without a reset pass: the last CTA to arrive
@@ -133,20 +149,6 @@ __global__ void __launch_bounds__(256) quantize_kernel(const QuantParams p)
             p.status->bad_input = any;
             if (p.host_flag) *p.host_flag = any;
         }
-    }
-    __syncthreads();
-    const float inv = s_inverse;
-    const int mt = m / p.T, t = m - mt * p.T;
-    uint4* dst = reinterpret_cast<uint4*>(p.Xq) + ((size_t)mt * chunks) * p.T + t;
-    for (int kc = tid; kc < chunks; kc += 256) {
-        uint4 q = make_uint4(0u, 0u, 0u, 0u);
-        if (kc < live_chunks) {
-            float v[16];
-            uint32_t unused = 0;
-            load16<HALF>(row, kc * 16, p.K, vec, v, unused);
-            q = quantize16(v, inv, kc * 16, p.K);
-        }
-        dst[(size_t)kc * p.T] = q;
     }
 }
 
