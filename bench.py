@@ -105,6 +105,9 @@ class ClockSampler:
 def run_reference(args, rank, world):
     if rank != 0:
         return
+    if world > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
+        # torchrun pins every rank to one OpenMP thread; this arm is a single CPU process and may use the host
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     from oracle.harness import Oracle, Reference, make_activations, make_weights
     M = args.tokens
     use_ref = Reference.available()
@@ -169,6 +172,7 @@ def run_cuda(args, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     ctx = rk.Context(f"cuda:{local_rank}")
     dom = ctx.domain(0)
@@ -183,6 +187,12 @@ def run_cuda(args, rank, world, local_rank):
         act[K] = (A, torch.from_numpy(A.view(np.int16)).to(dev))
     check = None
     generated = {}
+    # every linear writes straight into one per-rank output buffer; with several ranks that buffer is
+    # what the all-gather sends, so no packing copies sit between the GEMMs and the collective
+    shard_cols = [shard_columns(N, world, rank) for _ in range(args.layers) for (_, N) in LLAMA7B_LAYER]
+    out_cols = sum(n1 - n0 for n0, n1 in shard_cols)
+    out_buf = torch.zeros((M * out_cols,), dtype=torch.float16, device=dev)   # binary16 bits (NCCL has no int16)
+    out_off = 0
     for layer in range(args.layers):
         for j, (K, N) in enumerate(LLAMA7B_LAYER):
             seed = (layer * 16 + j) if args.distinct_values else j
@@ -193,7 +203,8 @@ def run_cuda(args, rank, world, local_rank):
             Bs, ss = np.ascontiguousarray(B[:, n0:n1]), np.ascontiguousarray(sw[n0:n1])
             w = rk.Weights(dom, Bs, ss, k_tile=480)
             ws = rk.Workspace(dom, rk.default_config(M, n1 - n0, K, k_tile=480))
-            dC = torch.zeros((M, n1 - n0), dtype=torch.int16, device=dev)
+            dC = out_buf[out_off:out_off + M * (n1 - n0)].view(M, n1 - n0).view(torch.int16)
+            out_off += M * (n1 - n0)
             hA = torch.from_numpy(act[K][0].view(np.int16)).pin_memory()
             hC = torch.zeros((M, n1 - n0), dtype=torch.int16).pin_memory()
             linears.append(dict(K=K, N=N, n0=n0, n1=n1, w=w, ws=ws, dA=act[K][1], dC=dC, hA=hA, hC=hC))
@@ -201,12 +212,13 @@ def run_cuda(args, rank, world, local_rank):
                 check = (act[K][0], Bs, ss, len(linears) - 1)
     step_bytes = sum(algorithmic_bytes(M, l["K"], l["N"]) for l in linears)          # whole job, all ranks
     step_ops = sum(2 * M * l["K"] * l["N"] for l in linears)
-    out_cols = sum(l["n1"] - l["n0"] for l in linears)
-    gather_in = gather_out = None
+    gather_out = None
     if world > 1:
-        pad = max(int(x) for x in _all_gather_ints(dist, out_cols, world, dev))
-        gather_in = torch.zeros((M * pad,), dtype=torch.int16, device=dev)
-        gather_out = torch.zeros((world * M * pad,), dtype=torch.int16, device=dev)
+        sizes = [int(x) for x in _all_gather_ints(dist, M * out_cols, world, dev)]
+        if len(set(sizes)) == 1:
+            gather_out = torch.zeros((world * M * out_cols,), dtype=torch.float16, device=dev)
+        else:   # uneven shards: all_gather of a list of differently sized tensors
+            gather_out = [torch.zeros((n,), dtype=torch.float16, device=dev) for n in sizes]
 
     stream = torch.cuda.Stream(device=dev)
 
@@ -215,13 +227,12 @@ def run_cuda(args, rank, world, local_rank):
             rc = l["ws"].enqueue_f16(l["w"], l["dA"], l["dC"], s.cuda_stream)
             if rc:
                 raise RuntimeError(f"enqueue failed: {rc}")
-        if world > 1:
-            offset = 0
-            for l in linears:     # pack the shard outputs, then reassemble them on every rank
-                n = M * (l["n1"] - l["n0"])
-                gather_in[offset:offset + n].copy_(l["dC"].reshape(-1), non_blocking=True)
-                offset += n
-            dist.all_gather_into_tensor(gather_out, gather_in)
+        if world > 1:     # reassemble the column shards on every rank: the one exchange the path has
+            with torch.cuda.stream(s):
+                if isinstance(gather_out, list):
+                    dist.all_gather(gather_out, out_buf)
+                else:
+                    dist.all_gather_into_tensor(gather_out, out_buf)
 
     # ---- correctness of what is timed: first linear of the ring against the oracle
     oracle = Oracle()
@@ -244,7 +255,7 @@ def run_cuda(args, rank, world, local_rank):
 
     # ---- device-resident timing (value)
     graph = None
-    if not args.no_graph and world == 1:
+    if not args.no_graph:
         try:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
@@ -363,12 +374,19 @@ def run_cuda(args, rank, world, local_rank):
                              "bytes_per_launch": gemm_bytes_per_launch,
                              "us_per_launch": 1e3 * ms_step / len(linears)},
                 "cpu_baseline": cpu, "also": also}
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        # The captured graph holds NCCL kernels; tearing the communicator down under it has hung at
+        # exit.  Everything is finished: meet once more, then leave without running destructors.
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     for l in linears:
         l["ws"].free()
         l["w"].free()
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def _all_gather_ints(dist, value, world, dev):
