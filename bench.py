@@ -172,7 +172,10 @@ def run_cuda(args, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the one JSON line only
+        # stdout carries the one JSON line only: NCCL's version banner (NCCL_DEBUG=VERSION) would precede it
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     ctx = rk.Context(f"cuda:{local_rank}")
     dom = ctx.domain(0)
@@ -344,6 +347,12 @@ def run_cuda(args, rank, world, local_rank):
     if world == 1 and not args.quick:
         also["independent_linears_4_streams_GBps"] = _time_streams(linears, step_bytes, args, dev, 4)
         also.update(_prefill_and_ffn(rk, dom, dev, stream, oracle, make_weights, make_activations, sample_columns))
+
+    if world > 1 and not args.quick:
+        try:
+            also.update(_prefill_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_activations, shard_columns))
+        except Exception as exc:   # the extra figure must never cost the headline line
+            also["prefill_sharded_error"] = f"{type(exc).__name__}: {exc}"
 
     # ---- CPU baseline on a bounded sample (rank 0, one GPU only)
     cpu = None
@@ -546,6 +555,43 @@ def _prefill_and_ffn(rk, dom, dev, stream, oracle, make_weights, make_activation
     wg.free()
     wd.free()
     return out
+
+
+def _prefill_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_activations, shard_columns):
+    """BASELINE config 2 column-sharded over the ranks: every rank runs the 2048 x 4096 prefill GEMM on its run of
+    64-column blocks of N = 14336; figures are whole-job TOPS from the slowest rank's device time, without and
+    with the all-gather that reassembles the [M, N] output on every rank."""
+    import torch
+    M, K, N = 2048, 4096, 14336
+    B, sw = make_weights(K, N, seed=21)
+    A = make_activations(M, K, seed=21, dtype="f16")
+    n0, n1 = shard_columns(N, world, rank)
+    w = rk.Weights(dom, np.ascontiguousarray(B[:, n0:n1]), np.ascontiguousarray(sw[n0:n1]))
+    ws = rk.Workspace(dom, rk.default_config(M, n1 - n0, K))
+    dA = torch.from_numpy(A.view(np.int16)).to(dev)
+    dC = torch.zeros((M * (n1 - n0),), dtype=torch.float16, device=dev)
+    sizes = [int(x) for x in _all_gather_ints(dist, M * (n1 - n0), world, dev)]
+    parts = [torch.zeros((n,), dtype=torch.float16, device=dev) for n in sizes]
+
+    def compute():
+        rc = ws.enqueue_f16(w, dA, dC, stream.cuda_stream)
+        if rc:
+            raise RuntimeError(f"enqueue failed: {rc}")
+
+    def with_gather():
+        compute()
+        dist.all_gather(parts, dC)
+
+    out = {}
+    for name, fn in (("compute", compute), ("compute_plus_all_gather", with_gather)):
+        ms = _event_time(torch, stream, fn, 10)
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        out[name] = {"us": ms * 1e3, "tops": 2.0 * M * K * N / (ms * 1e-3) / 1e12}
+    ws.free()
+    w.free()
+    return {"prefill_M2048_K4096_N14336_sharded": out}
 
 
 def cpu_baseline(M, Reference, oracle, make_weights, make_activations):
