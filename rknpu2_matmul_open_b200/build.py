@@ -10,7 +10,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB_DIR = HERE / "lib"
 LIB = LIB_DIR / "librk_npu_matmul_b200.so"
-TOOLS = ["int8_peak.cu"]
+TOOLS = ["int8_peak.cu", "bulk_copy_bw.cu"]
 SOURCES = ["w4a8_kernels.cu", "w4a8_fused.cu", "w4a8_stream.cu", "w4a8_gemm_tc.cu", "w4a8_gemm_tc_persist.cu", "w4a8_abi.cpp", "w4a8_tune.cpp"]
 HEADERS = ["w4a8_device.h", "w4a8_host.h", "w4a8_ptx.cuh", "w4a8_math.cuh", "w4a8_tc.cuh", "../../include/rknpu_b200_w4a8.h", "../../include/rknpu_b200_ext.h"]
 NVCC_FLAGS = [
@@ -53,10 +53,11 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     out = subprocess.run(link, capture_output=True, text=True)
     if out.returncode:
         raise RuntimeError(f"link failed:\n{out.stdout}\n{out.stderr}")
-    peak = subprocess.run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-o", str(LIB_DIR / "int8_peak"),
-                           str(CSRC / "int8_peak.cu")], capture_output=True, text=True)
-    if peak.returncode:
-        raise RuntimeError(f"nvcc failed on int8_peak.cu:\n{peak.stderr}")
+    for tool in TOOLS:   # stand-alone measurement programs (roofline denominators)
+        out = subprocess.run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-o",
+                              str(LIB_DIR / tool.rsplit(".", 1)[0]), str(CSRC / tool)], capture_output=True, text=True)
+        if out.returncode:
+            raise RuntimeError(f"nvcc failed on {tool}:\n{out.stderr}")
     (LIB_DIR / "ptxas.log").write_text("\n".join(log))
     if verbose:
         print("\n".join(log))

@@ -9,7 +9,10 @@ interest in a minute or two.  Cases:
   prefill  one 2048 x 4096 x 14336 linear, binary16 in and out
   ffn      gate/up 4096 -> 2 x 14336, SwiGLU, down 14336 -> 4096 at M = 1024, fp32
 
-Options: --repeat R (launch sets, default 4), --tokens M (override the batch).
+Options: --repeat R (launch sets, default 4), --tokens M (override the batch), --stamps (after
+the launches, enable the kernels' phase stamps, run one more set and print them: per linear of
+the decode case the dependent phases of the fused kernel, for the prefill case the per-tile
+timeline of the persistent GEMM's MMA issuer and epilogue).
 """
 from __future__ import annotations
 
@@ -39,6 +42,7 @@ def main() -> None:
     ap.add_argument("case", choices=["decode", "prefill", "ffn"])
     ap.add_argument("--repeat", type=int, default=4)
     ap.add_argument("--tokens", type=int, default=0)
+    ap.add_argument("--stamps", action="store_true")
     args = ap.parse_args()
     rng = np.random.default_rng(0)
     ctx = rk.Context()
@@ -85,6 +89,58 @@ def main() -> None:
         if ws.finish() != 0:
             raise RuntimeError("device status not clean")
     print(f"{args.case}: M={M}, last set {e0.elapsed_time(e1) * 1e3:.1f} us for {len(calls)} call(s)")
+    if args.stamps:
+        _print_stamps(rk, args.case, calls, stream, torch)
+
+
+def _print_stamps(rk, case, calls, stream, torch):
+    lib = rk.capi.load()
+    for _, ws in calls:
+        lib.rk_npu_b200_w4a8_trace_enable(ws.handle, 1)
+    graph = None
+    if case == "decode":     # steady state of a dependent chain: replay the set as one CUDA graph
+        with torch.cuda.stream(stream):
+            for fn, _ in calls:
+                fn()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for fn, _ in calls:
+                fn()
+    for _ in range(3):
+        with torch.cuda.stream(stream):
+            if graph is not None:
+                graph.replay()
+            else:
+                for fn, _ in calls:
+                    fn()
+        stream.synchronize()
+    torch.cuda.synchronize()
+    if case == "decode":
+        prev_end = None
+        print("per linear, ns relative to the previous linear's last CTA end: first/last CTA start, first/last CTA end;"
+              " then median cycles since CTA start at: weights requested, dependency met, scales known, slice quantised,"
+              " contraction done, partials exchanged")
+        for i, (_, ws) in enumerate(calls):
+            buf = np.zeros((4096, 8), np.uint64)
+            lib.rk_npu_b200_w4a8_trace_read(ws.handle, buf.ctypes.data, 4096)
+            v = buf[buf[:, 0] > 0].astype(np.int64)
+            if not len(v):
+                continue
+            s0, s1, e0, e1 = v[:, 0].min(), v[:, 0].max(), v[:, 7].min(), v[:, 7].max()
+            ref = prev_end if prev_end is not None else s0
+            cyc = np.median(v[:, 1:7], axis=0).astype(int)
+            print(f"linear {i}: K={ws.cfg.K} N={ws.cfg.N} ctas={len(v)} start[{s0 - ref},{s1 - ref}] end[{e0 - ref},{e1 - ref}]"
+                  f" cycles {list(cyc)}")
+            prev_end = e1
+    elif case == "prefill":
+        raw = np.zeros(256, np.uint64)
+        lib.rk_npu_b200_w4a8_trace_read(calls[0][1].handle, raw.ctypes.data, 32)
+        print(f"clusters in the grid: {int(raw[200])}; per tile of cluster 0 (cycles since kernel start): MMA issuer begins,"
+              " first MMA issued, last commit, epilogue sees the accumulator, tensor memory handed back, tile stored,"
+              " cycles the issuer waited for operands | unpack warp: waited for weights, for a free buffer, for activations")
+        for j in range(7):
+            print(f"tile {j}: {[int(x) for x in raw[j * 8:j * 8 + 7]]} | {int(raw[128 + 2 * j])} {int(raw[129 + 2 * j])} {int(raw[160 + j])}")
 
 
 if __name__ == "__main__":
