@@ -32,7 +32,7 @@ __host__ __device__ constexpr size_t fused_smem_bytes(int tc, int stages)
            + (size_t)tc * 192 * 4           // inbox: partial sums for the channels this rank owns
            + (size_t)8 * tc * 4             // inbox: per-rank partial row maxima
            + (size_t)4 * tc * 4             // row max, scale, inverse, SwiGLU row max
-           + 128 * 4 + 8 + 16;              // channel scales, barrier, flags
+           + 128 * 4 + 24 + 16;             // channel scales, three barriers, flags
 }
 
 constexpr int FUSED_THREADS = 256;   // eight warps: (weight group, m16 tile) pairs in the contraction
@@ -53,8 +53,8 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
     float* const s_inv = s_scale + TC;
     uint32_t* const s_outmax = reinterpret_cast<uint32_t*>(s_inv + TC);
     float* const s_sw = reinterpret_cast<float*>(s_outmax + TC);   // 128 channel scales of this CTA
-    uint64_t* const full = reinterpret_cast<uint64_t*>(s_sw + 128);
-    int* const s_flags = reinterpret_cast<int*>(full + 1);   // [0] bad verdict, [1] wait ran out
+    uint64_t* const full = reinterpret_cast<uint64_t*>(s_sw + 128);   // [0] weights landed, [1] row maxima of all ranks, [2] partial sums
+    int* const s_flags = reinterpret_cast<int*>(full + 3);   // [0] bad verdict, [1] wait ran out
 
     pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -73,7 +73,10 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
     // copies on one barrier, requested before the dependency wait (weights never change).
     if (tid == 0) {
         mbar_init(&full[0], 1);
+        mbar_init(&full[1], 1);
+        mbar_init(&full[2], 1);
         mbar_fence_init();
+        if (S > 1 && p.rowmax_in == nullptr) mbar_arrive_expect_tx(&full[1], (uint32_t)(S * TC * 4));
         s_flags[0] = 0;
         s_flags[1] = 0;
         if (nkb > 0) mbar_arrive_expect_tx(&full[0], (uint32_t)nkb * 8192u);
@@ -104,6 +107,7 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
     constexpr int UMAX = HALF ? 2 : 1;
     Raw16<HALF> kept[UMAX];
     const int items = TC * units;
+    const bool warp_one_token = (units & 31) == 0;
 #pragma unroll
     for (int it = 0; it < UMAX; ++it) {
         const int idx = tid + FUSED_THREADS * it;
@@ -111,9 +115,18 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
         const int k0 = k_begin + u * 16;
 #pragma unroll
         for (int i = 0; i < (HALF ? 8 : 16); ++i) kept[it].w[i] = 0u;
+        uint32_t bits = 0;
         if (idx < items && tok < p.M && k0 < p.K) {
             load_raw<HALF>(A + (size_t)tok * p.K, k0, p.K, vec, kept[it]);
-            if (p.rowmax_in == nullptr) atomicMax(&s_max[tok], raw_maxbits<HALF>(kept[it]));
+            bits = raw_maxbits<HALF>(kept[it]);
+        }
+        if (p.rowmax_in == nullptr) {
+            // 256 threads hammering eight shared words serialise; when a warp's 32 items belong to one
+            // token (units a multiple of 32) the warp reduces first and issues one atomic
+            if (warp_one_token) {
+                bits = __reduce_max_sync(0xffffffffu, bits);
+                if (lane == 0 && bits) atomicMax(&s_max[min(tok, TC - 1)], bits);
+            } else if (bits) atomicMax(&s_max[tok], bits);
         }
     }
     if (p.rowmax_in == nullptr) {
@@ -128,12 +141,14 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
         }
         __syncthreads();
         if (S > 1) {
+            // every rank sends its slice maxima to every rank (itself included); a rank goes on as soon as
+            // the S * TC words it expects have landed -- no cluster-wide barrier on the critical path
             cluster_wait();
             for (int i = tid; i < S * TC; i += FUSED_THREADS) {
                 const int r = i / TC, t = i - r * TC;
-                cluster.map_shared_rank(inbox_max, r)[rank * TC + t] = s_max[t];
+                st_async_u32(map_to_cta(smem_u32(&inbox_max[rank * TC + t]), (uint32_t)r), s_max[t], map_to_cta(smem_u32(&full[1]), (uint32_t)r));
             }
-            cluster.sync();
+            if (!mbar_wait(&full[1], 0, deadline)) s_flags[1] = 1;
         }
     }
     if (tid < TC) {
@@ -160,6 +175,11 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
     __syncthreads();
     if (trace) trace[3] = (unsigned long long)(clock64() - c_start);
     const int verdict = s_flags[0];   // identical in every CTA: all of them saw the whole rows
+    // partial sums this rank will receive: its share of the channels, every token, from every rank
+    const int Qq = p.epi == EPI_SWIGLU ? 16 : 32;
+    const int my_quads = ((rank + 1) * Qq) / S - (rank * Qq) / S;
+    if (tid == 0 && S > 1 && !verdict)
+        mbar_arrive_expect_tx(&full[2], (uint32_t)(S * TC * my_quads * 4 * (p.epi == EPI_SWIGLU ? 2 : 1) * 4));
 
     // ---- 2. quantise the slice into shared memory: xs[unit][token][16 B]
     if (!verdict) {
@@ -239,11 +259,15 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
                 const int c = swiglu ? (ch & 63) : ch;
                 const int owner = (((c >> 2) + 1) * S + Q - 1) / Q - 1;
                 const int local = c - ((owner * Q) / S) * 4 + ((swiglu && ch >= 64) ? QW * 4 : 0);
-                int32_t* dst = S > 1 ? cluster.map_shared_rank(inbox_sum, owner) : inbox_sum;
-                dst[(rank * TC + tok) * W + local] = acc[j][e] >> 4;   // exact: sums are multiples of 16
+                const int word = (rank * TC + tok) * W + local;
+                const int value = acc[j][e] >> 4;                       // exact: sums are multiples of 16
+                if (S > 1) st_async_u32(map_to_cta(smem_u32(&inbox_sum[word]), (uint32_t)owner), (uint32_t)value, map_to_cta(smem_u32(&full[2]), (uint32_t)owner));
+                else inbox_sum[word] = value;
             }
     }
-    if (S > 1) cluster.sync(); else __syncthreads();
+    if (S > 1) {
+        if (!verdict && !mbar_wait(&full[2], 0, deadline)) s_flags[1] = 1;
+    } else __syncthreads();
     if (trace) trace[6] = (unsigned long long)(clock64() - c_start);
 
     // ---- 5. finish the channels this rank owns

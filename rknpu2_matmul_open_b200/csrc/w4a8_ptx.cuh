@@ -86,6 +86,20 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_global,
                  : "memory");
 }
 
+// ---- distributed shared memory: a 32-bit store into a peer CTA's shared memory that also counts
+// four bytes on a barrier in that CTA.  Data and signal travel together, so the receiver needs no
+// cluster-wide barrier: it waits on its own mbarrier for the bytes it expects.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta_rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+    return r;
+}
+__device__ __forceinline__ void st_async_u32(uint32_t remote_addr, uint32_t value, uint32_t remote_bar) {
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];" ::"r"(remote_addr), "r"(value),
+                 "r"(remote_bar)
+                 : "memory");
+}
+
 // ---- programmatic dependent launch
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
