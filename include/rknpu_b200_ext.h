@@ -63,16 +63,24 @@ int rk_npu_b200_w4a8_last_quant(rk_npu_w4a8_workspace *workspace, float *scales,
 
 /* Scheduling override for experiments and tuning.  variant: 0 = keep, else it must equal
  * the workspace's kernel family (1 quantise + mma.sync GEMM, 2 quantise + tcgen05 GEMM,
- * 3 single-kernel small batch; chosen at creation, RK_NPU_B200_VARIANT overrides).
- * split_k: 0 = automatic, else the split-K factor (1..8 for family 3; 1, 2, 4, 8 otherwise).
+ * 3 single-kernel small batch, 4 quantise + persistent tcgen05 streaming GEMM for up to 32
+ * tokens; chosen at creation, RK_NPU_B200_VARIANT overrides where the geometry allows).
+ * split_k: 0 = automatic, else the split-K factor (1..8 for family 3; 1, 2, 4, 8 for 1 and 2;
+ * ignored by family 4, which balances by itself).
  * Returns RK_NPU_ERR_PARAM when the workspace geometry cannot run the request. */
 int rk_npu_b200_w4a8_set_schedule(rk_npu_w4a8_workspace *workspace, int variant, int split_k);
 
-/* Diagnostics: with tracing enabled the small-batch kernel records eight global-timer
- * stamps (ns) per CTA -- start, weights requested, dependency met, scales known, slice
- * quantised, contraction done, partials exchanged, outputs stored -- for the latest launch.
- * trace_read copies stamps[ctas][8] to the host (CTA index = blockIdx.y * gridDim.x + blockIdx.x,
- * at most 16384 CTAs).  The caller synchronises first. */
+/* Diagnostics: with tracing enabled the kernels record device stamps of their latest launch.
+ * Single-kernel small-batch path: eight stamps per CTA -- start (global timer, ns), then cycles
+ * since the CTA's start at: weights requested, dependency met, scales known, slice quantised,
+ * contraction done, partials exchanged -- and the end (ns); trace_read copies stamps[ctas][8]
+ * (CTA index = blockIdx.y * gridDim.x + blockIdx.x, at most 16384 CTAs).
+ * Persistent large-batch GEMM: CTA pair 0 records per tile j < 16 at [8 j + 0..6] the cycles since
+ * kernel start at which the MMA issuer begins, issues its first MMA, commits the last, the epilogue
+ * sees the accumulator, hands tensor memory back, has stored the tile, and the cycles the issuer
+ * waited for operands; [128 + 2 j], [129 + 2 j], [160 + j] the cycles one unpack warp waited for
+ * weights, for a free tensor-memory buffer and for activations; [200] the CTA pairs in the grid.
+ * The caller synchronises first.  rknpu2_matmul_open_b200/profile_case.py --stamps prints both. */
 int rk_npu_b200_w4a8_trace_enable(rk_npu_w4a8_workspace *workspace, int enable);
 int rk_npu_b200_w4a8_trace_read(rk_npu_w4a8_workspace *workspace, unsigned long long *stamps, int ctas);
 
