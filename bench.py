@@ -353,6 +353,10 @@ def run_cuda(args, rank, world, local_rank):
             also.update(_prefill_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_activations, shard_columns))
         except Exception as exc:   # the extra figure must never cost the headline line
             also["prefill_sharded_error"] = f"{type(exc).__name__}: {exc}"
+        try:
+            also.update(_ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_activations))
+        except Exception as exc:
+            also["ffn_sharded_error"] = f"{type(exc).__name__}: {exc}"
 
     # ---- CPU baseline on a bounded sample (rank 0, one GPU only)
     cpu = None
@@ -592,6 +596,56 @@ def _prefill_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make
     ws.free()
     w.free()
     return {"prefill_M2048_K4096_N14336_sharded": out}
+
+
+def _ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_activations):
+    """BASELINE config 4: the 70B-shaped FFN (hidden 8192, intermediate 28672) column-sharded over the ranks.
+    Gate and up are sharded by the same feature slice so SwiGLU stays local; the middle slices are all-gathered
+    (the down projection contracts over all of F), the down projection is sharded by output columns and its
+    outputs are all-gathered.  The down projection rescans the row maxima of the gathered middle, which gives the
+    same scales as the single-GPU reuse of the SwiGLU maxima (a maximum is a maximum), so results stay bit-exact."""
+    import torch
+    from rknpu2_matmul_open_b200.sharding import gather_columns, shard_columns, shard_ffn_weights, shard_weights
+    K, F, N = 8192, 28672, 8192
+    # weights with BASELINE's distribution, generated once for a 2048-column block and repeated along N
+    # (generating 700 M codes from fp32 normals would take most of a minute per rank; only time is measured here)
+    blk_g, blk_sg = make_weights(K, 2048, seed=41)
+    blk_d, blk_sd = make_weights(F, 2048, seed=42)
+    Bg, sg = np.tile(blk_g, (1, 2 * F // 2048)), np.tile(blk_sg, 2 * F // 2048)
+    Bd, sd = np.tile(blk_d, (1, N // 2048)), np.tile(blk_sd, N // 2048)
+    Bg_s, sg_s, (f0, f1) = shard_ffn_weights(Bg, sg, world, rank)
+    Bd_s, sd_s, (n0, n1) = shard_weights(Bd, sd, world, rank)
+    del Bg, Bd
+    wg, wd = rk.Weights(dom, Bg_s, sg_s), rk.Weights(dom, Bd_s, sd_s)
+    out = {}
+    for M in (32, 1024):
+        A = make_activations(M, K, seed=41, dtype="f32")
+        gu = rk.Workspace(dom, rk.default_config(M, 2 * (f1 - f0), K))
+        dn = rk.Workspace(dom, rk.default_config(M, n1 - n0, F))
+        dA = torch.from_numpy(A).to(dev)
+        dMid = torch.zeros((M, f1 - f0), dtype=torch.float32, device=dev)
+        dC = torch.zeros((M, n1 - n0), dtype=torch.float32, device=dev)
+
+        def step():
+            rc = gu.enqueue_swiglu_f32(wg, dA, dMid, stream.cuda_stream)
+            middle = gather_columns(dMid, F)                       # [M, F] on every rank
+            rc = rc or dn.enqueue_f32(wd, middle, dC, stream.cuda_stream)
+            if rc:
+                raise RuntimeError(f"enqueue failed: {rc}")
+            return gather_columns(dC, N)
+
+        ms = _event_time(torch, stream, step, 5)
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        weight_bytes = K * 2 * F // 2 + F * N // 2
+        out[f"M{M}"] = {"us": ms * 1e3, "weight_GBps_whole_job": weight_bytes / (ms * 1e-3) / 1e9,
+                        "tops_whole_job": 2.0 * M * (K * 2 * F + F * N) / (ms * 1e-3) / 1e12}
+        gu.free()
+        dn.free()
+    wg.free()
+    wd.free()
+    return {"ffn_8192_28672_sharded": out}
 
 
 def cpu_baseline(M, Reference, oracle, make_weights, make_activations):

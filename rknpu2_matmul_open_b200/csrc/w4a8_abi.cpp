@@ -801,14 +801,18 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
     const int forced = std::getenv("RK_NPU_B200_VARIANT") ? std::atoi(std::getenv("RK_NPU_B200_VARIANT")) : 0;
     const bool tc_ok = gemm_tc_supported(probe);
     const bool fused_ok = cfg->M <= 32 && ws->KB <= 8 * FUSED_MAX_STAGES;
-    const bool stream_ok = cfg->M <= 32 && (long long)ws->KB * KBLOCK <= 131072;
+    const bool stream_ok = cfg->M <= 128 && (long long)ws->KB * KBLOCK <= 131072;
     // Small batches: the single-kernel path wins while all of the weights fit in the SMs' shared
     // memory at once (one wave, up to about 24 MB) and the batch is a single 8-token MMA column
-    // block; beyond that the two-kernel ring (quantise + mma.sync GEMM) streams better.  The
-    // tcgen05 streaming kernel (4) is opt-in: its time does not depend on the batch size, but it
-    // only overtakes the ring at 32 tokens.
+    // block; beyond that the two-kernel ring (quantise + mma.sync GEMM) streams better.  Up to 32
+    // tokens the tcgen05 streaming kernel (4) is opt-in: its time does not depend on the batch
+    // size, but it only overtakes the ring at 32 tokens.
     const bool fused_best = fused_ok && cfg->M <= 8 && (long long)cfg->K * cfg->N / 2 <= (24ll << 20);
-    int variant = (cfg->M > 32 && tc_ok) ? 2 : fused_best ? 3 : 1;
+    // 33..128 tokens: the per-tile tcgen05 kernel has one CTA per 128 output channels; when that is less than
+    // half the SMs and K is long, the streaming kernel (all SMs, K split between CTAs) is faster.
+    const bool stream_best = stream_ok && cfg->M > 32 && cfg->K >= 8192 &&
+                             (cfg->N + TILE_N - 1) / TILE_N * 2 <= ctx->sm_count;
+    int variant = (cfg->M > 32 && stream_best) ? 4 : (cfg->M > 32 && tc_ok) ? 2 : fused_best ? 3 : 1;
     if (forced == 1 || (forced == 2 && tc_ok) || (forced == 3 && fused_ok) || (forced == 4 && stream_ok)) variant = forced;
     ws->variant = variant;
     if (variant == 2) {
@@ -817,7 +821,7 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
         ws->pair = cfg->M > 128 && !env_flag("RK_NPU_B200_NO_PAIR", false);
         ws->T = ws->pair ? 128 : (cfg->M >= 256 ? 256 : align_up(cfg->M, 16));
     } else if (variant == 4) {
-        ws->TC = ws->T = cfg->M <= 16 ? 16 : 32;   // tcgen05 N
+        ws->TC = ws->T = cfg->M <= 16 ? 16 : cfg->M <= 32 ? 32 : cfg->M <= 64 ? 64 : 128;   // tcgen05 N
     } else {
         ws->TC = cfg->M <= 8 ? 8 : cfg->M <= 16 ? 16 : 32;
         ws->T = ws->TC;

@@ -37,7 +37,8 @@ namespace rkb200 {
 
 // A stage holds TWO k-blocks, so five bulk copies feed two k-blocks of MMAs (the copy engine
 // sustains only a few requests in flight per SM; fewer, larger requests keep it ahead).
-constexpr int TC_STAGES = 2;          // single-CTA form: 2 x (8 KB weights + T x 128 B activations) per stage
+constexpr int TC_STAGES = 2;          // single-CTA form, T > 128: 2 x (8 KB weights + T x 128 B activations) per stage
+constexpr int TC_STAGES_DEEP = 4;     // single-CTA form, T <= 128: the copies take several stage times to arrive
 constexpr int TC_STAGES_PAIR = 4;     // paired form: 2 x (8 KB + 16 KB) per stage
 constexpr int TC_ABUF = 8;
 constexpr int TC_UNPACK_WARPS = 8;   // two sets of four (one warp per TMEM lane quarter), alternating k-blocks
@@ -55,7 +56,7 @@ template <bool PAIR>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
-    constexpr int NSTAGE = PAIR ? TC_STAGES_PAIR : TC_STAGES;
+    const int NSTAGE = PAIR ? TC_STAGES_PAIR : (p.T <= 128 ? TC_STAGES_DEEP : TC_STAGES);
     const int T = p.T;                              // tokens of this CTA's activation tile (128 when paired)
     const int TOK = PAIR ? 256 : T;                 // tokens (accumulator columns) of the MMA tile
     const size_t stage_bytes = tc_stage_bytes(T);
@@ -357,7 +358,8 @@ cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl)
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)tc_smem_bytes(256, TC_STAGES, 256));
+                                             (int)(tc_smem_bytes(256, TC_STAGES, 256) > tc_smem_bytes(128, TC_STAGES_DEEP, 128)
+                                                       ? tc_smem_bytes(256, TC_STAGES, 256) : tc_smem_bytes(128, TC_STAGES_DEEP, 128)));
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)tc_smem_bytes(128, TC_STAGES_PAIR, 256));
@@ -381,7 +383,7 @@ cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl)
         ++n;
     } else {
         cfg.gridDim = dim3((unsigned)tiles, (unsigned)((p.M + p.T - 1) / p.T), 1);
-        cfg.dynamicSmemBytes = tc_smem_bytes(p.T, TC_STAGES, p.T);
+        cfg.dynamicSmemBytes = tc_smem_bytes(p.T, p.T <= 128 ? TC_STAGES_DEEP : TC_STAGES, p.T);
     }
     if (pdl) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;

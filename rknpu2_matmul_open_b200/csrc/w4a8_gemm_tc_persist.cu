@@ -400,30 +400,43 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                             if (m0 + i < p.M) row0[(size_t)i * out_cols] = r[i];
                     }
                 } else {
-                    uint32_t mx[32];
+                    // Lanes 0-15 hold the gate rows g, lanes 16-31 the matching up rows u of 16 features.  For
+                    // every token pair the halves swap what the other needs, so that the gate lanes finish the
+                    // even token and the up lanes the odd one: each lane evaluates 16 SiLUs instead of 32.
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float mine = __fmul_rn(__fmul_rn(__uint_as_float(r[i]), sxr[i]), sw);   // gate lanes: g, up lanes: u
-                        const float up = __shfl_xor_sync(0xffffffffu, mine, 16);
-                        const float y = __fmul_rn(silu_poly(mine), up);                   // meaningful in gate lanes
-                        const bool live = !up_lane && n_ok && m0 + i < p.M;
-                        r[i] = __float_as_uint(y);
-                        mx[i] = live ? (r[i] & 0x7fffffffu) : 0u;
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r[i]), sxr[i]), sw));
+                    float y[16];
+                    uint32_t mx[16];
+                    const int mine_row = m0 + (up_lane ? 1 : 0);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float a0 = __uint_as_float(r[2 * i]), a1 = __uint_as_float(r[2 * i + 1]);
+                        const float o0 = __shfl_xor_sync(0xffffffffu, a0, 16);   // gate lanes: u of token 2i; up lanes: g of token 2i
+                        const float o1 = __shfl_xor_sync(0xffffffffu, a1, 16);   // gate lanes: u of token 2i+1; up lanes: g of token 2i+1
+                        const float g = up_lane ? o1 : a0;
+                        const float u = up_lane ? a1 : o0;
+                        y[i] = __fmul_rn(silu_poly(g), u);
+                        const bool live = n_ok && mine_row + 2 * i < p.M;
+                        mx[i] = live ? (__float_as_uint(y[i]) & 0x7fffffffu) : 0u;
                     }
                     if (p.rowmax) {
+                        // maxima over the 16 lanes of each half (one token each)
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) mx[i] = __reduce_max_sync(0xffffffffu, mx[i]);
+                        for (int i = 0; i < 16; ++i) {
+#pragma unroll
+                            for (int o = 8; o > 0; o >>= 1) mx[i] = max(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], o));
+                        }
                     }
-                    uint32_t* const row0 = reinterpret_cast<uint32_t*>(p.out) + (size_t)m0 * out_cols + n;
-                    if (!up_lane && n_ok) {
+                    float* const row0 = reinterpret_cast<float*>(p.out) + (size_t)mine_row * out_cols + n;
+                    if (n_ok) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (m0 + i < p.M) row0[(size_t)i * out_cols] = r[i];
+                        for (int i = 0; i < 16; ++i)
+                            if (mine_row + 2 * i < p.M) row0[(size_t)(2 * i) * out_cols] = y[i];
                     }
-                    if (p.rowmax && lane == 0) {
+                    if (p.rowmax && (lane & 15) == 0) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (mx[i]) atomicMax(&p.rowmax[m0 + i], mx[i]);
+                        for (int i = 0; i < 16; ++i)
+                            if (mx[i]) atomicMax(&p.rowmax[mine_row + 2 * i], mx[i]);
                     }
                 }
             }

@@ -4,13 +4,14 @@
 // Why tcgen05 for 1..32 tokens: the legacy mma.sync int8 path of this GPU needs about as long
 // for the m16n8k32 instructions of one 8 KB weight block as HBM needs to deliver the block, so
 // a weight-streaming kernel built on it is compute-bound from 16 tokens on.  tcgen05.mma
-// kind::i8 (M = 128 channels, N = 16 or 32 tokens) costs a few cycles per block; the only
+// kind::i8 (M = 128 channels, N = 16 .. 128 tokens) costs a few cycles per block; the only
 // per-byte work left is unpacking int4 to int8 into tensor memory, which eight warps do at
 // several times the HBM rate.
 //
-// Schedule: the work is the flat list of (tile of 128 channels, stage of four k-blocks) items
-// -- 32 KB of packed weights each, requested as four 8 KB bulk copies: a thread gets a copy
-// request out only every few hundred cycles whatever its size, so requests have to be large -- and every CTA of a persistent grid (one per SM) takes one
+// Schedule: the work is the flat list of (tile of 128 channels, stage of four k-blocks -- two for
+// token tiles above 32, whose activation codes take the shared memory --) items, 32 or 16 KB of
+// packed weights each, requested as four bulk copies: a thread gets a copy request out only
+// every few hundred cycles whatever its size, so requests have to be large -- and every CTA of a persistent grid (one per SM) takes one
 // contiguous share of exactly total / CTAs items, so all SMs stream the same number of bytes
 // and finish together whatever N and K are.  A CTA's share is a run of segments (tile, stage
 // range).  Its copy ring never drains between segments, and the accumulator is double
@@ -34,20 +35,19 @@
 namespace rkb200 {
 
 constexpr int TS_STAGES = 4;
-constexpr int TS_KPS = 4;                    // k-blocks per stage
+constexpr int TS_KPS_MAX = 4;                // k-blocks per stage: 4 for token tiles up to 32, 2 above (shared memory)
 constexpr int TS_ABUF = 7;                   // weight buffers in tensor memory, one half stage (2 k-blocks, 64 columns) each:
                                              // the unpack -> MMA -> commit -> unpack loop is several half-stage times long
 constexpr int TS_UNPACK_WARP0 = 2, TS_UNPACK_WARPS = 8;
 constexpr int TS_EPI_WARP0 = TS_UNPACK_WARP0 + TS_UNPACK_WARPS, TS_EPI_WARPS = 4;
 constexpr int TS_THREADS = 32 * (TS_EPI_WARP0 + TS_EPI_WARPS);   // 448
-constexpr int TS_A_COL0 = 64;
-constexpr int TS_ACC_STRIDE = 32;            // columns between the two accumulator buffers (N <= 32)
-constexpr int TS_TMEM_COLS = 512;
+constexpr int TS_TMEM_COLS = 512;            // two accumulator buffers of max(T, 32) columns, then the weight buffers
 
-__host__ __device__ constexpr size_t ts_stage_bytes(int T) { return TS_KPS * (8192 + (size_t)T * 128); }
+__host__ __device__ constexpr int ts_kps(int T) { return T <= 32 ? 4 : 2; }
+__host__ __device__ constexpr size_t ts_stage_bytes(int T) { return ts_kps(T) * (8192 + (size_t)T * 128); }
 __host__ __device__ constexpr size_t ts_smem_bytes(int T)
 {
-    return TS_STAGES * ts_stage_bytes(T) + 32 * 4 + (2 * TS_STAGES + 2 * TS_ABUF + 4) * 8 + 32;
+    return TS_STAGES * ts_stage_bytes(T) + 128 * 4 + (2 * TS_STAGES + 2 * TS_ABUF + 4) * 8 + 32;
 }
 
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r)
@@ -63,11 +63,16 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r)
 __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const GemmParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
-    const int T = p.T;                                   // 16 or 32 tokens: MMA N, code tile
+    const int T = p.T;                                   // 16, 32, 64 or 128 tokens: MMA N, code tile
+    const int KPS = ts_kps(T);                           // k-blocks per stage
+    const int halves = KPS / 2;                          // a stage passes through tensor memory in pieces of two k-blocks
+    const int acc_stride = T < 32 ? 32 : T;              // tensor-memory columns per accumulator buffer
+    const int a_col0 = 2 * acc_stride;                   // weight buffers behind the accumulators
+    const int abuf = (TS_TMEM_COLS - a_col0) / 64 < TS_ABUF ? (TS_TMEM_COLS - a_col0) / 64 : TS_ABUF;
     const size_t stage_bytes = ts_stage_bytes(T);
     uint8_t* const stages = smem;
     float* const s_sx = reinterpret_cast<float*>(smem + TS_STAGES * stage_bytes);
-    uint64_t* const full = reinterpret_cast<uint64_t*>(s_sx + 32);
+    uint64_t* const full = reinterpret_cast<uint64_t*>(s_sx + 128);
     uint64_t* const empty = full + TS_STAGES;
     uint64_t* const a_ready = empty + TS_STAGES;
     uint64_t* const a_free = a_ready + TS_ABUF;
@@ -80,7 +85,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool swiglu = p.epi == EPI_SWIGLU;
     const int KB = p.KB, KC = KB * 4;
-    const int nst = (KB + TS_KPS - 1) / TS_KPS;          // stage iterations per tile
+    const int nst = (KB + KPS - 1) / KPS;                // stage iterations per tile
     const int tiles = swiglu ? (p.F + 63) / 64 : (p.N + TILE_N - 1) / TILE_N;
     const long long total = (long long)tiles * nst;
     const long long b0 = total * blockIdx.x / gridDim.x, b1 = total * (blockIdx.x + 1) / gridDim.x;
@@ -111,17 +116,17 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
     auto copy_weights = [&](int s, int tile, int it, int kbs) {
         if (lane < 4) {
             const int group = swiglu ? (lane < 2 ? tile * 2 + lane : p.F / GROUP + tile * 2 + (lane - 2)) : tile * 4 + lane;
-            bulk_g2s(stages + (size_t)s * stage_bytes + lane * (TS_KPS * 2048), p.Wp + (size_t)group * KC * 512 + (size_t)it * (TS_KPS * 2048), (uint32_t)kbs * 2048u, &full[s]);
+            bulk_g2s(stages + (size_t)s * stage_bytes + lane * (KPS * 2048), p.Wp + (size_t)group * KC * 512 + (size_t)it * (KPS * 2048), (uint32_t)kbs * 2048u, &full[s]);
         }
     };
     auto copy_codes = [&](int s, int it, int kbs) {
-        if (lane == 4) bulk_g2s(stages + (size_t)s * stage_bytes + TS_KPS * 8192, p.Xq + (size_t)it * T * (TS_KPS * 128), (uint32_t)kbs * T * 128u, &full[s]);
+        if (lane == 4) bulk_g2s(stages + (size_t)s * stage_bytes + KPS * 8192, p.Xq + (size_t)it * T * (KPS * 128), (uint32_t)kbs * T * 128u, &full[s]);
     };
     const int pre = n_items < TS_STAGES ? n_items : TS_STAGES;
     if (warp == 0) {
         // Weights never change: the first ring-full is requested before waiting for the kernel in front.
         for (; pr_gi < pre; ++pr_gi) {
-            const int kbs = min(TS_KPS, KB - TS_KPS * pr_it);
+            const int kbs = min(KPS, KB - KPS * pr_it);
             if (lane == 0) mbar_expect_tx(&full[pr_gi], (uint32_t)kbs * 8192u);
             __syncwarp();
             copy_weights(pr_gi, pr_tile, pr_it, kbs);
@@ -136,7 +141,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
         {
             int it = it0;
             for (int gi = 0; gi < pre; ++gi) {
-                const int kbs = min(TS_KPS, KB - TS_KPS * it);
+                const int kbs = min(KPS, KB - KPS * it);
                 if (lane == 0) { if (skip) mbar_arrive(&full[gi]); else mbar_arrive_expect_tx(&full[gi], (uint32_t)kbs * T * 128u); }
                 __syncwarp();
                 if (!skip) copy_codes(gi, it, kbs);
@@ -151,7 +156,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
         } else {
             for (; pr_gi < n_items; ++pr_gi) {
                 const int s = pr_gi % TS_STAGES;
-                const int kbs = min(TS_KPS, KB - TS_KPS * pr_it);
+                const int kbs = min(KPS, KB - KPS * pr_it);
                 int ok = 1;
                 if (lane == 0) {
                     ok = mbar_wait(&empty[s], ((pr_gi / TS_STAGES) - 1) & 1, deadline) ? 1 : 0;
@@ -178,18 +183,18 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
                     if (!ok) { s_flag[1] = 1; break; }
                     tc_fence_after();
                 }
-                const uint32_t d_tmem = tmem_base + buf * TS_ACC_STRIDE;
+                const uint32_t d_tmem = tmem_base + buf * acc_stride;
                 for (int i = 0; i < nseg && ok; ++i) {
                     const int g = gi + i, s = g % TS_STAGES;
-                    const int kbs = min(TS_KPS, KB - TS_KPS * (it + i));
-                    const uint32_t xaddr = smem_u32(stages + (size_t)s * stage_bytes + TS_KPS * 8192);
-                    for (int half = 0; half < 2 && ok; ++half) {
-                        const int h = 2 * g + half, b = h % TS_ABUF;
+                    const int kbs = min(KPS, KB - KPS * (it + i));
+                    const uint32_t xaddr = smem_u32(stages + (size_t)s * stage_bytes + KPS * 8192);
+                    for (int half = 0; half < halves && ok; ++half) {
+                        const int h = halves * g + half, b = h % abuf;
                         const int kh = min(2, kbs - 2 * half);           // k-blocks in this half (<= 0: none, bookkeeping only)
-                        ok = mbar_wait(&a_ready[b], (h / TS_ABUF) & 1, deadline);
+                        ok = mbar_wait(&a_ready[b], (h / abuf) & 1, deadline);
                         if (!ok) { s_flag[1] = 1; break; }
                         tc_fence_after();
-                        const uint32_t a_tmem = tmem_base + TS_A_COL0 + b * 64;
+                        const uint32_t a_tmem = tmem_base + a_col0 + b * 64;
                         // k-step q of the half: k-block q / 4, 32 k = two 16-byte chunks per token, i.e. the
                         // descriptor's address field advances by 2 * T (16-byte units) per step
                         const uint64_t desc0 = tc_smem_desc(xaddr + (uint32_t)(2 * half) * T * 128, (uint32_t)T * 16u, 128u);
@@ -228,25 +233,25 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
         bool ok = !skip;
         int it = it0;
         for (int g = 0; g < n_items && ok; ++g) {
-            const int kbs = min(TS_KPS, KB - TS_KPS * it);
+            const int kbs = min(KPS, KB - KPS * it);
             if (++it == nst) it = 0;
             if ((g & 1) != set) continue;                      // the two sets take alternate stages
             const int s = g % TS_STAGES;
             ok = mbar_wait(&full[s], (g / TS_STAGES) & 1, deadline);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { s_flag[1] = 1; break; }
-            for (int half = 0; half < 2 && ok; ++half) {
-                const int h = 2 * g + half, b = h % TS_ABUF;
+            for (int half = 0; half < halves && ok; ++half) {
+                const int h = halves * g + half, b = h % abuf;
                 const int kh = min(2, kbs - 2 * half);           // k-blocks in this half (<= 0: none, bookkeeping only)
-                if (h >= TS_ABUF) ok = mbar_wait(&a_free[b], ((h / TS_ABUF) - 1) & 1, deadline);
+                if (h >= abuf) ok = mbar_wait(&a_free[b], ((h / abuf) - 1) & 1, deadline);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) { s_flag[1] = 1; break; }
                 tc_fence_after();
-                const uint4* src = reinterpret_cast<const uint4*>(stages + (size_t)s * stage_bytes + src_group * (TS_KPS * 2048) + half * 4096) + src_row;
+                const uint4* src = reinterpret_cast<const uint4*>(stages + (size_t)s * stage_bytes + src_group * (KPS * 2048) + half * 4096) + src_row;
                 uint4 w[8];
 #pragma unroll
                 for (int c = 0; c < 8; ++c) w[c] = (c < 4 * kh) ? src[c * 32] : make_uint4(0u, 0u, 0u, 0u);
-                if (half == 1) {
+                if (half == halves - 1) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&empty[s]);   // the packed copy is in registers; the codes stay until the commit
                 }
@@ -263,7 +268,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
                                 r[c * 8 + 4 + jj] = ww[jj] & 0xF0F0F0F0u;
                             }
                         }
-                        tc_st32(lane_addr + TS_A_COL0 + b * 64 + hh * 32, r);
+                        tc_st32(lane_addr + a_col0 + b * 64 + hh * 32, r);
                     }
                 }
                 tc_wait_st();
@@ -283,7 +288,64 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
         const bool up_lane = swiglu && lane >= 16;
         bool ok = !skip;
         int gi = 0, seg = 0, tile = tile0, it = it0;
-        if (et < 32) s_sx[et] = et < p.M ? p.sx[et] : 0.f;   // visible to all four warps after the first barrier below
+        s_sx[et] = et < p.M ? p.sx[et] : 0.f;   // visible to all four warps after the first barrier below
+        const int nchunk = (T + 31) / 32;        // the accumulator is read in pieces of up to 32 token columns
+        // finish 32 tokens of one output channel: dequantise (+ SwiGLU), store
+        auto finish_chunk = [&](const int (&v)[32], int tile, int c) {
+            const int n = (swiglu ? tile * 64 : tile * TILE_N) + col;
+            const bool n_ok = n < out_cols;
+            const float sw = n_ok ? p.sw[(up_lane ? p.F : 0) + n] : 0.f;
+            const int m0 = 32 * c;
+            float y[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) y[i] = dequant(v[i], s_sx[m0 + i], sw);
+            if (p.epi == EPI_F16) {
+                __half* const out = reinterpret_cast<__half*>(p.out) + (size_t)m0 * out_cols + n;
+                if (n_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (m0 + i < p.M) out[(size_t)i * out_cols] = __float2half_rn(y[i]);
+                }
+            } else if (p.epi == EPI_F32) {
+                float* const out = reinterpret_cast<float*>(p.out) + (size_t)m0 * out_cols + n;
+                if (n_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (m0 + i < p.M) out[(size_t)i * out_cols] = y[i];
+                }
+            } else if (p.epi == EPI_I32) {
+                int* const out = reinterpret_cast<int*>(p.out) + (size_t)m0 * out_cols + n;
+                if (n_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (m0 + i < p.M) out[(size_t)i * out_cols] = v[i];
+                }
+            } else {
+                uint32_t mx[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float up = __shfl_xor_sync(0xffffffffu, y[i], 16);       // gate lanes receive u
+                    y[i] = __fmul_rn(silu_poly(y[i]), up);                          // meaningful in gate lanes
+                    const bool live = !up_lane && n_ok && m0 + i < p.M;
+                    mx[i] = live ? (__float_as_uint(y[i]) & 0x7fffffffu) : 0u;
+                }
+                if (p.rowmax) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx[i] = __reduce_max_sync(0xffffffffu, mx[i]);
+                }
+                float* const out = reinterpret_cast<float*>(p.out) + (size_t)m0 * out_cols + n;
+                if (!up_lane && n_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (m0 + i < p.M) out[(size_t)i * out_cols] = y[i];
+                }
+                if (p.rowmax && lane == 0) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (m0 + i < p.M && mx[i]) atomicMax(&p.rowmax[m0 + i], mx[i]);
+                }
+            }
+        };
         while (gi < n_items && ok) {
             const int nseg = min(nst - it, n_items - gi);
             const int buf = seg & 1;
@@ -294,28 +356,36 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
             asm volatile("bar.sync 2, 128;" ::: "memory");
             if (*reinterpret_cast<volatile int*>(&s_flag[1])) break;
             tc_fence_after();
-            uint32_t r[32];
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * TS_ACC_STRIDE;
-            tc_ld16(taddr, r);
-            if (T > 16) tc_ld16(taddr + 16, r + 16);
-            else {
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
+            const bool whole = nseg == nst;          // this segment covers its tile's whole K
+            int* const slot = p.partials + (size_t)tile * 128 * T;
+            for (int c = 0; c < nchunk; ++c) {
+                uint32_t r[32];
+                tc_ld16(taddr + 32 * c, r);
+                if (T > 16) tc_ld16(taddr + 32 * c + 16, r + 16);
+                else {
 #pragma unroll
-                for (int i = 16; i < 32; ++i) r[i] = 0u;
+                    for (int i = 16; i < 32; ++i) r[i] = 0u;
+                }
+                tc_wait_ld();
+                if (c == nchunk - 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_relaxed(&acc_empty[buf]);   // the MMAs of segment seg + 2 may overwrite it
+                }
+                int v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = (int)r[i] >> 4;     // exact: sums are multiples of 16
+                if (whole) finish_chunk(v, tile, c);
+                else {
+                    // ---- part of a tile: add to the tile's slot [token][row]
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (32 * c + i < T && v[i]) atomicAdd(slot + (32 * c + i) * 128 + row, v[i]);
+                }
             }
-            tc_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_relaxed(&acc_empty[buf]);   // the MMAs of segment seg + 2 may overwrite it
-            int v[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = (int)r[i] >> 4;     // exact: sums are multiples of 16
-            bool finish = true;
-            if (nseg != nst) {
-                // ---- part of a tile: add to the tile's slot [token][row], advance its stage counter
-                int* const slot = p.partials + (size_t)tile * 128 * T;
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (i < T && v[i]) atomicAdd(slot + i * 128 + row, v[i]);
+            if (!whole) {
+                // ---- advance the tile's stage counter; whoever completes it finishes the tile
                 __threadfence();
                 asm volatile("bar.sync 2, 128;" ::: "memory");
                 if (et == 0) {
@@ -323,70 +393,22 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
                     s_flag[0] = (before + (unsigned)nseg == (unsigned)nst) ? 1 : 0;
                 }
                 asm volatile("bar.sync 2, 128;" ::: "memory");
-                finish = *reinterpret_cast<volatile int*>(&s_flag[0]) != 0;
+                const bool finish = *reinterpret_cast<volatile int*>(&s_flag[0]) != 0;
                 if (finish) {
                     // last contributor: fetch the complete sums, leave slot and counter clean
                     __threadfence();
+                    for (int c = 0; c < nchunk; ++c) {
+                        int v[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (i < T) { v[i] = __ldcg(slot + i * 128 + row); slot[i * 128 + row] = 0; }
+                        for (int i = 0; i < 32; ++i) {
+                            v[i] = 0;
+                            if (32 * c + i < T) { v[i] = __ldcg(slot + (32 * c + i) * 128 + row); slot[(32 * c + i) * 128 + row] = 0; }
+                        }
+                        finish_chunk(v, tile, c);
+                    }
                     if (et == 0) p.counts[tile] = 0u;
                 }
                 asm volatile("bar.sync 2, 128;" ::: "memory");   // s_flag[0] may be rewritten by the next segment
-            }
-            if (finish) {
-                const int n = (swiglu ? tile * 64 : tile * TILE_N) + col;
-                const bool n_ok = n < out_cols;
-                const float sw = n_ok ? p.sw[(up_lane ? p.F : 0) + n] : 0.f;
-                float y[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) y[i] = dequant(v[i], s_sx[i], sw);
-                if (p.epi == EPI_F16) {
-                    __half* const out = reinterpret_cast<__half*>(p.out) + n;
-                    if (n_ok) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (i < p.M) out[(size_t)i * out_cols] = __float2half_rn(y[i]);
-                    }
-                } else if (p.epi == EPI_F32) {
-                    float* const out = reinterpret_cast<float*>(p.out) + n;
-                    if (n_ok) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (i < p.M) out[(size_t)i * out_cols] = y[i];
-                    }
-                } else if (p.epi == EPI_I32) {
-                    int* const out = reinterpret_cast<int*>(p.out) + n;
-                    if (n_ok) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (i < p.M) out[(size_t)i * out_cols] = v[i];
-                    }
-                } else {
-                    uint32_t mx[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float up = __shfl_xor_sync(0xffffffffu, y[i], 16);       // gate lanes receive u
-                        y[i] = __fmul_rn(silu_poly(y[i]), up);                          // meaningful in gate lanes
-                        const bool live = !up_lane && n_ok && i < p.M;
-                        mx[i] = live ? (__float_as_uint(y[i]) & 0x7fffffffu) : 0u;
-                    }
-                    if (p.rowmax) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) mx[i] = __reduce_max_sync(0xffffffffu, mx[i]);
-                    }
-                    float* const out = reinterpret_cast<float*>(p.out) + n;
-                    if (!up_lane && n_ok) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (i < p.M) out[(size_t)i * out_cols] = y[i];
-                    }
-                    if (p.rowmax && lane == 0) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (i < p.M && mx[i]) atomicMax(&p.rowmax[i], mx[i]);
-                    }
-                }
             }
             gi += nseg;
             it += nseg;
@@ -407,16 +429,16 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
 
 cudaError_t launch_gemm_stream(const GemmParams& p, int sm_count, cudaStream_t stream, bool pdl)
 {
-    if ((p.T != 16 && p.T != 32) || p.M > p.T || (long long)p.KB * KBLOCK > 131072 || !p.partials || !p.counts)
+    if ((p.T != 16 && p.T != 32 && p.T != 64 && p.T != 128) || p.M > p.T || (long long)p.KB * KBLOCK > 131072 || !p.partials || !p.counts)
         return cudaErrorInvalidValue;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ts_smem_bytes(32));
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ts_smem_bytes(128) > ts_smem_bytes(32) ? ts_smem_bytes(128) : ts_smem_bytes(32)));
         if (e != cudaSuccess) return e;
         configured = true;
     }
     const int tiles = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : (p.N + TILE_N - 1) / TILE_N;
-    const long long total = (long long)tiles * ((p.KB + TS_KPS - 1) / TS_KPS);
+    const long long total = (long long)tiles * ((p.KB + ts_kps(p.T) - 1) / ts_kps(p.T));
     long long ctas = sm_count;
     if (ctas > total / 2) ctas = total / 2 > 0 ? total / 2 : 1;   // at least two stages per CTA
     cudaLaunchConfig_t cfg = {};

@@ -162,7 +162,8 @@ def test_full_size_ffn_decode(gpu, oracle):
 
 # the FFN through every small-batch schedule (SwiGLU epilogue + row-maximum reuse in each GEMM kernel)
 @pytest.mark.parametrize("variant", [1, 3, 4])
-@pytest.mark.parametrize("case", [(1, 1057, 992, 192), (8, 2304, 1600, 300), (20, 479, 96, 65), (32, 4096, 1024, 512)],
+@pytest.mark.parametrize("case", [(1, 1057, 992, 192), (8, 2304, 1600, 300), (20, 479, 96, 65), (32, 4096, 1024, 512),
+                                  (70, 1057, 992, 192), (128, 4096, 1024, 512)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_ffn_small_batch_schedules_agree(gpu, oracle, monkeypatch, variant, case):
     _, dom, _ = gpu

@@ -401,3 +401,24 @@ def test_streaming_schedule_reuses_one_workspace(gpu, oracle, monkeypatch):
     assert np.array_equal(bits(out), bits(oracle.linear(A, B, sw)[1]))
     ws.free()
     w.free()
+
+
+# 33..128 tokens: the per-tile tcgen05 kernel (2) and the persistent streaming kernel (4, token tiles of
+# 64 and 128, partial tiles combined across CTAs) against the oracle, plain and ragged shapes
+@pytest.mark.parametrize("variant", [2, 4])
+@pytest.mark.parametrize("shape", [(33, 1057, 257), (64, 4096, 1024), (100, 2304, 385), (128, 11008, 512), (65, 8192, 130)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_mid_batch_schedules_agree(gpu, oracle, monkeypatch, variant, shape):
+    _, dom, _ = gpu
+    M, K, N = shape
+    monkeypatch.setenv("RK_NPU_B200_VARIANT", str(variant))
+    B, sw = make_weights(K, N, seed=K + 7 * N)
+    for dtype in ("f16", "f32"):
+        A = make_activations(M, K, seed=M + K, dtype=dtype)
+        out, acc = run_case(dom, oracle, A, B, sw)
+        out2, _ = run_case(dom, oracle, A, B, sw)
+        rc, ref, ref_acc, _ = oracle.linear(A, B, sw)
+        assert rc == 0
+        assert np.array_equal(acc, ref_acc)
+        assert np.array_equal(bits(out), bits(ref))
+        assert np.array_equal(bits(out2), bits(ref))
