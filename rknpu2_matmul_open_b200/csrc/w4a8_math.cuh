@@ -147,27 +147,29 @@ __device__ __forceinline__ void scale_from_max(float maximum, bool bad, float& s
     s = (maximum == 0.f || bad) ? 1.0f : fmaxf(__fdiv_rn(maximum, 127.0f), FLT_MIN);
     inv = __fdiv_rn(1.0f, s);
 }
-// round half away from zero, then clamp to [-127, 127]; |x| < 2^22 (x is a value times
-// the inverse of its row scale, so |x| <= 127 up to rounding).  Adding 1.5 * 2^23 rounds
-// to an integer (ties to even) in the FP32 adder; x minus that integer is exact, so a tie
-// is recognised exactly and pushed away from zero.  No conversion instructions.
+// round half away from zero, then clamp to [-127, 127], without conversion instructions.
+// |x| + 0.5 added with rounding TOWARD ZERO never reaches an integer the exact sum does not reach,
+// so its floor is round-half-away of |x| (a round-to-nearest add would turn 0.49999997 + 0.5 into 1).
+// A second toward-zero add of 1.5 * 2^23 leaves that floor in the low mantissa bits; the sign goes
+// back on with two integer operations.
 __device__ __forceinline__ int round_clamp(float x)
 {
-    const float magic = 12582912.0f;
-    float r = __fadd_rn(__fadd_rn(x, magic), -magic);
-    const float d = __fadd_rn(x, -r);
-    if (d == copysignf(0.5f, x)) r = __fadd_rn(r, copysignf(1.0f, x));
-    r = fminf(fmaxf(r, -127.f), 127.f);
-    return __float_as_int(__fadd_rn(r, magic)) - 0x4B400000;
+    const float s = fminf(__fadd_rz(fabsf(x), 0.5f), 127.0f);
+    const int n = __float_as_int(__fadd_rz(s, 12582912.0f)) - 0x4B400000;   // floor(s): 0..127
+    const int m = __float_as_int(x) >> 31;                                    // 0 or -1
+    return (n ^ m) - m;
 }
 // 16 activations -> 16 int8 codes packed in four words (ties away from zero, clamp +-127).
 __device__ __forceinline__ uint4 quantize16(const float (&v)[16], float inv, int k0, int K)
 {
-    uint32_t w[4] = {0u, 0u, 0u, 0u};
+    uint32_t w[4];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const int q = (k0 + i < K) ? round_clamp(__fmul_rn(v[i], inv)) : 0;
-        w[i >> 2] |= (uint32_t)(q & 0xff) << (8 * (i & 3));
+    for (int j = 0; j < 4; ++j) {
+        int q[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) q[i] = (k0 + 4 * j + i < K) ? round_clamp(__fmul_rn(v[4 * j + i], inv)) : 0;
+        // low bytes of four ints -> one word: three byte permutes
+        w[j] = __byte_perm(__byte_perm((uint32_t)q[0], (uint32_t)q[1], 0x0040), __byte_perm((uint32_t)q[2], (uint32_t)q[3], 0x0040), 0x5410);
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
