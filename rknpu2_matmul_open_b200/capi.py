@@ -1,4 +1,4 @@
-"""ctypes declarations of the library's C ABI (include/rknpu_b200_w4a8.h, include/rknpu_b200_ext.h).
+"""ctypes declarations of the library's C ABI (include/rknpu_b200_w4a8.h, rknpu_b200_quant.h, rknpu_b200_ext.h).
 
 The structures below have the field order and types of the C structs one for one, so
 Python code reads like a C caller of the original rk_npu_w4a8 interface.  Loading fails
@@ -91,6 +91,40 @@ class W4A8Strategy(C.Structure):
                 ("total_us", C.c_double), ("jitter_pct", C.c_double), ("robust_us", C.c_double)]
 
 
+class MatmulAutotuneConfig(C.Structure):
+    """rk_npu_matmul_autotune_config (include/rknpu_b200_quant.h): request key of the W8 tuning cache."""
+    _fields_ = [("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("allowed_npu_core_mask", C.c_uint32),
+                ("allowed_cpu_core_mask", C.c_uint64), ("warmup", C.c_int), ("loops", C.c_int), ("repeats", C.c_int),
+                ("timeout_ms", C.c_uint32), ("verbose", C.c_int), ("required_k_tile", C.c_int)]
+
+
+class MatmulFamilyAutotuneConfig(C.Structure):
+    _fields_ = [("K", C.c_int), ("N", C.c_int), ("m_count", C.c_int), ("m_values", C.POINTER(C.c_int)),
+                ("frequencies", C.POINTER(C.c_double)), ("allowed_npu_core_mask", C.c_uint32),
+                ("allowed_cpu_core_mask", C.c_uint64), ("warmup", C.c_int), ("loops", C.c_int), ("repeats", C.c_int),
+                ("timeout_ms", C.c_uint32), ("verbose", C.c_int)]
+
+
+class MatmulStrategy(C.Structure):
+    """rk_npu_matmul_strategy: one record of the W8 tuning cache."""
+    _fields_ = [("op_kind", C.c_int), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("k_tile", C.c_int),
+                ("n_tile", C.c_int), ("a_layout", C.c_int), ("wave_count", C.c_int), ("n_groups", C.c_int),
+                ("npu_core_mask", C.c_uint32), ("cpu_core_mask", C.c_uint64), ("cpu_threads", C.c_int),
+                ("input_us", C.c_double), ("npu_us", C.c_double), ("sync_us", C.c_double), ("output_us", C.c_double),
+                ("total_us", C.c_double), ("jitter_pct", C.c_double), ("robust_us", C.c_double), ("c_layout", C.c_int)]
+
+
+class I4Config(C.Structure):
+    _fields_ = [("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("m_tile", C.c_int), ("k_tile", C.c_int),
+                ("n_tile", C.c_int), ("npu_core_mask", C.c_uint32), ("timeout_ms", C.c_uint32), ("pipeline", C.c_int),
+                ("cpu_threads", C.c_int)]
+
+
+class W4A8FamilyConfig(C.Structure):
+    _fields_ = [("base", W4A8AutotuneConfig), ("m_count", C.c_int), ("m_values", C.POINTER(C.c_int)),
+                ("frequencies", C.POINTER(C.c_double))]
+
+
 class W4A8StrategyEx(C.Structure):
     _fields_ = [("base", W4A8Strategy), ("execution", W4A8Options)]
 
@@ -142,6 +176,14 @@ _SIGNATURES = {
     "rk_npu_w4a8_weights_create_tuned": (_P, [_P, C.POINTER(W4A8Strategy), _P, _P]),
     "rk_npu_w4a8_weights_create_tuned_ex": (_P, [_P, C.POINTER(W4A8StrategyEx), _P, _P]),
     "rk_npu_w4a8_workspace_create_tuned_ex": (_P, [_P, C.POINTER(W4A8StrategyEx)]),
+    # second header: W8 load-only cache and configuration initialisers (include/rknpu_b200_quant.h)
+    "rk_npu_matmul_autotune_config_init": (None, [C.POINTER(MatmulAutotuneConfig), C.c_int, C.c_int, C.c_int]),
+    "rk_npu_matmul_family_autotune_config_init": (None, [C.POINTER(MatmulFamilyAutotuneConfig), C.c_int, C.c_int, C.c_int,
+                                                         C.POINTER(C.c_int)]),
+    "rk_npu_matmul_autotune_cache_load": (C.c_int, [_P, C.c_char_p, C.c_int, C.POINTER(MatmulAutotuneConfig),
+                                                    C.POINTER(MatmulStrategy), C.POINTER(MatmulStrategy)]),
+    "rk_npu_i4_config_init": (None, [C.POINTER(I4Config), C.c_int, C.c_int, C.c_int]),
+    "rk_npu_w4a8_family_config_init": (None, [C.POINTER(W4A8FamilyConfig), C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int)]),
     # B200 extensions
     "rk_npu_b200_device": (C.c_int, [_P]),
     "rk_npu_b200_open_offline": (_P, [C.c_uint32]),

@@ -11,6 +11,7 @@
 // The cache files are interchangeable with the reference's: same magic line, same key
 // line (the driver-version field holds the CUDA driver version here), same records.
 #include "w4a8_host.h"
+#include "../../include/rknpu_b200_quant.h"
 #include <algorithm>
 #include <atomic>
 #include <cerrno>
@@ -593,4 +594,164 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_tuned_ex(rk_npu_i
         s->base.config.k_tile != s->base.weights.config.k_tile)
         return nullptr;
     return rk_npu_w4a8_workspace_create_ex(domain, &s->base.config, &s->execution);
+}
+
+// ================================================================== W8 load-only tuning cache
+// The second public header's cache reader, restated from src/rk_npu_quant_matmul.cpp:183-349
+// (key fields, record fields, validity rules) and :1522-1563 (defaults, entry point).  The
+// records describe executions of the original device; this library only has to answer the
+// question "is there a valid, current record for this request" the way the original does.
+namespace rkb200 {
+namespace {
+constexpr const char* W8_CACHE_MAGIC = "rk_npu_matmul_tuning_cache_v2";
+constexpr uint32_t W8_CACHE_FORMAT = 2, W8_TUNING_REVISION = 6;
+constexpr int W8_N_TILE_MAX = 3072, W8_CHANNEL_TILE = 32;
+
+struct W8Key {
+    uint32_t format = W8_CACHE_FORMAT, revision = W8_TUNING_REVISION, driver = 0;
+    int op = 0, M = 0, N = 0, K = 0;
+    uint32_t npu = 0;
+    uint64_t cpu = 0;
+    int warmup = 0, loops = 0, repeats = 0;
+    uint32_t timeout_ms = 0;
+    int required_k_tile = 0;
+    bool operator==(const W8Key& o) const
+    {
+        return format == o.format && revision == o.revision && driver == o.driver && op == o.op && M == o.M && N == o.N &&
+               K == o.K && npu == o.npu && cpu == o.cpu && warmup == o.warmup && loops == o.loops && repeats == o.repeats &&
+               timeout_ms == o.timeout_ms && required_k_tile == o.required_k_tile;
+    }
+};
+bool w8_kind_ok(int kind) { return kind >= RK_NPU_MATMUL_I8I8I32 && kind <= RK_NPU_MATMUL_F32I8F32_STATIC; }
+// bit 0: reduction on the device, bit 1: dequantisation on the device; both chosen by the
+// original's environment switches and part of a record's identity
+uint32_t w8_execution_mode(int kind)
+{
+    auto on = [](const char* name) { const char* v = std::getenv(name); return v && std::strcmp(v, "1") == 0; };
+    const bool dequant = kind != RK_NPU_MATMUL_I8I8I32 && on("RK_NPU_W8A8_NPU_DEQUANT");
+    return ((on("RK_NPU_I8_NPU_REDUCE") || dequant) ? 1u : 0u) | (dequant ? 2u : 0u);
+}
+bool w8_config_ok(const rk_npu_matmul_autotune_config* c)
+{
+    return c && c->M > 0 && c->N > 0 && c->K > 0 && (c->allowed_npu_core_mask & ~7u) == 0 && c->warmup >= 0 && c->loops > 0 &&
+           c->repeats > 0 && c->timeout_ms > 0 && c->required_k_tile >= 0 && c->required_k_tile <= c->K;
+}
+bool w8_make_key(const rk_npu_ctx* ctx, const rk_npu_matmul_autotune_config* c, int kind, W8Key& key)
+{
+    if (!ctx || !w8_config_ok(c) || !w8_kind_ok(kind)) return false;
+    const uint64_t affinity = process_cpu_mask();
+    key.driver = ctx->driver_version;
+    key.revision |= w8_execution_mode(kind) << 16;
+    key.op = kind;
+    key.M = c->M; key.N = c->N; key.K = c->K;
+    key.npu = c->allowed_npu_core_mask ? c->allowed_npu_core_mask : 7u;
+    key.cpu = (c->allowed_cpu_core_mask ? c->allowed_cpu_core_mask : affinity) & affinity;
+    key.warmup = c->warmup; key.loops = c->loops; key.repeats = c->repeats;
+    key.timeout_ms = c->timeout_ms;
+    key.required_k_tile = c->required_k_tile;
+    return key.cpu != 0 && key.npu != 0;
+}
+bool w8_read_record(std::istream& in, const char* label, rk_npu_matmul_strategy& s)
+{
+    std::string word;
+    int op = 0, a = 0, c = 0;
+    uint64_t t[7] = {};
+    if (!(in >> word >> op >> s.M >> s.N >> s.K >> s.k_tile >> s.n_tile >> a >> c >> s.wave_count >> s.n_groups >>
+          s.npu_core_mask >> s.cpu_core_mask >> s.cpu_threads >> t[0] >> t[1] >> t[2] >> t[3] >> t[4] >> t[5] >> t[6]) ||
+        word != label)
+        return false;
+    s.op_kind = static_cast<rk_npu_matmul_op_kind>(op);
+    s.a_layout = static_cast<rk_npu_matmul_a_layout>(a);
+    s.c_layout = static_cast<rk_npu_matmul_c_layout>(c);
+    s.input_us = bits_double(t[0]); s.npu_us = bits_double(t[1]); s.sync_us = bits_double(t[2]);
+    s.output_us = bits_double(t[3]); s.total_us = bits_double(t[4]); s.jitter_pct = bits_double(t[5]);
+    s.robust_us = bits_double(t[6]);
+    return true;
+}
+bool w8_record_ok(const rk_npu_matmul_strategy& s, const W8Key& key)
+{
+    const uint32_t m = s.npu_core_mask;
+    if (int(s.op_kind) != key.op || s.M <= 0 || s.N <= 0 || s.K <= 0 || s.k_tile <= 0 || s.k_tile > s.K || s.n_tile <= 0 ||
+        s.n_tile > W8_N_TILE_MAX || s.a_layout < RK_NPU_MATMUL_A_LAYOUT_NORMAL || s.a_layout > RK_NPU_MATMUL_A_LAYOUT_PANEL16 ||
+        s.c_layout < RK_NPU_MATMUL_C_LAYOUT_NATIVE || s.c_layout > RK_NPU_MATMUL_C_LAYOUT_PANEL16 ||
+        !(m == 1u || m == 2u || m == 4u || m == 3u || m == 7u) || s.cpu_core_mask == 0 || s.cpu_threads <= 0 ||
+        s.cpu_threads != __builtin_popcountll(s.cpu_core_mask) || (s.cpu_core_mask & ~process_cpu_mask()))
+        return false;
+    // Panel recipes are checked by the original against its device plan; they have no meaning
+    // here and their rules are not restated: such a record is treated as not usable.
+    if (s.a_layout >= RK_NPU_MATMUL_A_LAYOUT_PANEL8 || s.c_layout != RK_NPU_MATMUL_C_LAYOUT_NATIVE) return false;
+    const int align_n = std::max(W8_CHANNEL_TILE, rkb200::align_up(s.N, W8_CHANNEL_TILE));
+    const int nt = std::min(align_n, rkb200::align_up(s.n_tile, W8_CHANNEL_TILE));
+    if ((align_n + nt - 1) / nt < __builtin_popcount(m)) return false;
+    if (s.M != key.M || s.N != key.N || s.K != key.K || (m & ~key.npu) || (s.cpu_core_mask & ~key.cpu) ||
+        s.n_tile != rkb200::align_up(s.n_tile, W8_CHANNEL_TILE) || (key.required_k_tile > 0 && s.k_tile != key.required_k_tile) ||
+        s.wave_count != (s.K + s.k_tile - 1) / s.k_tile || s.n_groups != (align_n + s.n_tile - 1) / s.n_tile)
+        return false;
+    for (double v : {s.input_us, s.npu_us, s.sync_us, s.output_us, s.total_us, s.jitter_pct, s.robust_us})
+        if (!std::isfinite(v) || v < 0) return false;
+    return true;
+}
+} // namespace
+} // namespace rkb200
+
+extern "C" void rk_npu_matmul_autotune_config_init(rk_npu_matmul_autotune_config* c, int M, int N, int K)
+{
+    if (!c) return;
+    *c = {};
+    c->M = M; c->N = N; c->K = K;
+    c->allowed_npu_core_mask = 7;
+    c->warmup = 2; c->loops = 8; c->repeats = 3;
+    c->timeout_ms = 500;
+}
+extern "C" void rk_npu_matmul_family_autotune_config_init(rk_npu_matmul_family_autotune_config* c, int N, int K, int m_count,
+                                                          const int* m_values)
+{
+    if (!c) return;
+    *c = {};
+    c->K = K; c->N = N;
+    c->m_count = m_count;
+    c->m_values = m_values;
+    c->allowed_npu_core_mask = 7;
+    c->warmup = 2; c->loops = 8; c->repeats = 3;
+    c->timeout_ms = 500;
+}
+extern "C" int rk_npu_matmul_autotune_cache_load(rk_npu_ctx* ctx, const char* path, rk_npu_matmul_op_kind kind,
+                                                 const rk_npu_matmul_autotune_config* cfg, rk_npu_matmul_strategy* fastest,
+                                                 rk_npu_matmul_strategy* stable)
+{
+    using namespace rkb200;
+    try {
+        if (!path || !*path || !fastest || !stable) return RK_NPU_ERR_PARAM;
+        W8Key expected;
+        if (!w8_make_key(ctx, cfg, int(kind), expected)) return RK_NPU_ERR_PARAM;
+        std::ifstream in(path, std::ios::binary);
+        if (!in) return RK_NPU_ERR_CACHE_MISS;
+        in.imbue(std::locale::classic());
+        std::string magic, label;
+        W8Key stored;
+        rk_npu_matmul_strategy f{}, s{};
+        if (!(in >> magic >> label >> stored.format >> stored.revision >> stored.driver >> stored.op >> stored.M >> stored.N >>
+              stored.K >> stored.npu >> stored.cpu >> stored.warmup >> stored.loops >> stored.repeats >> stored.timeout_ms >>
+              stored.required_k_tile) ||
+            magic != W8_CACHE_MAGIC || label != "key" || !(stored == expected) || !w8_read_record(in, "fastest", f) ||
+            !w8_read_record(in, "stable", s) || !w8_record_ok(f, expected) || !w8_record_ok(s, expected))
+            return RK_NPU_ERR_CACHE_MISS;
+        in >> std::ws;
+        if (!in.eof()) return RK_NPU_ERR_CACHE_MISS;
+        *fastest = f;
+        *stable = s;
+        return RK_NPU_OK;
+    } catch (...) { return RK_NPU_ERR_PARAM; }
+}
+extern "C" void rk_npu_i4_config_init(rk_npu_i4_config* c, int M, int N, int K)
+{
+    if (c) *c = {M, N, K, 128, 480, 1024, 1, 500, 1, 1};
+}
+extern "C" void rk_npu_w4a8_family_config_init(rk_npu_w4a8_family_config* c, int N, int K, int m_count, const int* m_values)
+{
+    if (!c) return;
+    *c = {};
+    rk_npu_w4a8_autotune_config_init(&c->base, 1, N, K);
+    c->m_count = m_count;
+    c->m_values = m_values;
 }

@@ -26,7 +26,7 @@ def cfg_of(lib, m, n, k, **kw):
 
 def test_library_exports_every_declared_symbol(lib):
     declared = set()
-    for header in ("rknpu_b200_w4a8.h", "rknpu_b200_ext.h"):
+    for header in ("rknpu_b200_w4a8.h", "rknpu_b200_quant.h", "rknpu_b200_ext.h"):
         text = (ROOT / "include" / header).read_text()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
         declared |= set(re.findall(r"\b(rk_npu_\w+)\s*\(", text))
@@ -276,3 +276,118 @@ def test_cache_files_interoperate_with_reference_build(cache_case, reference, tm
     assert lib.rk_npu_w4a8_autotune_cache_load_ex(ctx, C.byref(c), _p(B), _p(sw), theirs, C.byref(f2), C.byref(st2)) == 0
     assert _fields(f2) == _fields(s)
     assert Path(path).read_bytes() == Path(theirs.decode()).read_bytes()
+
+
+# ---------------------------------------------------------------- the rest of the original headers
+def test_every_entry_point_of_the_original_headers_links(lib):
+    # tests/golden/reference_header_symbols.txt: every function the five public headers of the path declare
+    # (rk_npu_common.h, rk_npu_matmul_i4.h, rk_npu_w4a8.h, rk_npu_w4a8_tune.h, rk_npu_quant_matmul.h)
+    names = (ROOT / "tests" / "golden" / "reference_header_symbols.txt").read_text().split()
+    assert len(names) > 90
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+    # operators that are not built decline instead of pretending
+    for name in ("rk_npu_i8i8i32_run", "rk_npu_f16i8f16_run_dynamic", "rk_npu_w4a8_autotune", "rk_npu_i4i4i32_run",
+                 "rk_npu_matmul_autotune_cache_save", "rk_npu_mem_alloc"):
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = C.c_int, []
+        assert fn() == capi.RK_NPU_ERR_PARAM, name
+    for name in ("rk_npu_i8i8i32_weights_create", "rk_npu_matmul_workspace_create", "rk_npu_i4_workspace_create"):
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = C.c_void_p, []
+        assert fn() is None, name
+
+
+def test_second_header_defaults(lib):
+    c = capi.MatmulAutotuneConfig()
+    lib.rk_npu_matmul_autotune_config_init(C.byref(c), 5, 6, 7)
+    assert (c.M, c.N, c.K, c.allowed_npu_core_mask, c.allowed_cpu_core_mask, c.warmup, c.loops, c.repeats, c.timeout_ms,
+            c.verbose, c.required_k_tile) == (5, 6, 7, 7, 0, 2, 8, 3, 500, 0, 0)
+    ms = (C.c_int * 3)(1, 8, 32)
+    f = capi.MatmulFamilyAutotuneConfig()
+    lib.rk_npu_matmul_family_autotune_config_init(C.byref(f), 64, 96, 3, ms)
+    assert (f.K, f.N, f.m_count, f.allowed_npu_core_mask, f.warmup, f.loops, f.repeats, f.timeout_ms) == (96, 64, 3, 7, 2, 8, 3, 500)
+    i4 = capi.I4Config()
+    lib.rk_npu_i4_config_init(C.byref(i4), 3, 4, 5)
+    assert (i4.M, i4.N, i4.K, i4.m_tile, i4.k_tile, i4.n_tile, i4.npu_core_mask, i4.timeout_ms, i4.pipeline,
+            i4.cpu_threads) == (3, 4, 5, 128, 480, 1024, 1, 500, 1, 1)
+    fam = capi.W4A8FamilyConfig()
+    lib.rk_npu_w4a8_family_config_init(C.byref(fam), 64, 96, 3, ms)
+    assert (fam.base.M, fam.base.N, fam.base.K, fam.m_count, fam.base.loops) == (1, 64, 96, 3, 8)
+
+
+def _w8_file(path, key, fastest, stable, magic="rk_npu_matmul_tuning_cache_v2"):
+    # text layout of src/rk_npu_quant_matmul.cpp:252-262,336-347: doubles travel as their 64-bit patterns
+    def bits(x):
+        return str(np.float64(x).view(np.uint64))
+
+    def record(label, s):
+        return " ".join([label] + [str(v) for v in s[:13]] + [bits(v) for v in s[13:]])
+
+    Path(path).write_text(magic + "\n" + "key " + " ".join(str(v) for v in key) + "\n" + record("fastest", fastest) + "\n"
+                          + record("stable", stable) + "\n")
+
+
+def test_w8_load_only_cache(lib, tmp_path, monkeypatch):
+    import os
+    monkeypatch.delenv("RK_NPU_I8_NPU_REDUCE", raising=False)
+    monkeypatch.delenv("RK_NPU_W8A8_NPU_DEQUANT", raising=False)
+    ctx = lib.rk_npu_b200_open_offline(0x908)
+    c = capi.MatmulAutotuneConfig()
+    lib.rk_npu_matmul_autotune_config_init(C.byref(c), 128, 4096, 11008)
+    affinity = 0
+    for cpu in os.sched_getaffinity(0):
+        if cpu < 64:
+            affinity |= 1 << cpu
+    cpu_mask = affinity & -affinity                      # one permitted CPU
+    kind = 1                                             # RK_NPU_MATMUL_F16I8F16_DYNAMIC
+    key = [2, 6, 0x908, kind, 128, 4096, 11008, 7, affinity, 2, 8, 3, 500, 0]
+    #        op    M    N     K      kt    nt  a  c  waves        groups  npu cpu       thr  seven timings
+    rec = [kind, 128, 4096, 11008, 1376, 1408, 1, 0, 8, -(-4096 // 1408), 7, cpu_mask, 1, 10.5, 200.25, 3.0, 40.0, 250.75, 1.5, 260.0]
+    path = str(tmp_path / "w8.tune")
+    f, s = capi.MatmulStrategy(), capi.MatmulStrategy()
+
+    def load(cfg=c, k=kind, context=ctx):
+        return lib.rk_npu_matmul_autotune_cache_load(context, path.encode(), k, C.byref(cfg), C.byref(f), C.byref(s))
+
+    assert load() == capi.RK_NPU_ERR_CACHE_MISS          # absent
+    _w8_file(path, key, rec, rec)
+    assert load() == 0
+    assert (f.op_kind, f.M, f.N, f.K, f.k_tile, f.n_tile, f.a_layout, f.c_layout, f.wave_count, f.n_groups, f.npu_core_mask,
+            f.cpu_core_mask, f.cpu_threads) == tuple(rec[:6] + [1, 0] + rec[8:13])
+    assert (f.input_us, f.npu_us, f.sync_us, f.output_us, f.total_us, f.jitter_pct, f.robust_us) == tuple(rec[13:])
+    assert s.total_us == 250.75
+    # arguments
+    assert lib.rk_npu_matmul_autotune_cache_load(ctx, b"", kind, C.byref(c), C.byref(f), C.byref(s)) == capi.RK_NPU_ERR_PARAM
+    assert lib.rk_npu_matmul_autotune_cache_load(ctx, path.encode(), 9, C.byref(c), C.byref(f), C.byref(s)) == capi.RK_NPU_ERR_PARAM
+    bad = capi.MatmulAutotuneConfig.from_buffer_copy(c); bad.loops = 0
+    assert load(bad) == capi.RK_NPU_ERR_PARAM
+    # every key component invalidates
+    for field, value in dict(M=64, loops=9, warmup=3, repeats=4, timeout_ms=400, required_k_tile=32, allowed_npu_core_mask=3).items():
+        c2 = capi.MatmulAutotuneConfig.from_buffer_copy(c)
+        setattr(c2, field, value)
+        assert load(c2) == capi.RK_NPU_ERR_CACHE_MISS, field
+    assert load(k=2) == capi.RK_NPU_ERR_CACHE_MISS       # another operator
+    other = lib.rk_npu_b200_open_offline(0x909)
+    assert load(context=other) == capi.RK_NPU_ERR_CACHE_MISS
+    lib.rk_npu_close(other)
+    monkeypatch.setenv("RK_NPU_I8_NPU_REDUCE", "1")      # the execution mode is part of the stored revision
+    assert load() == capi.RK_NPU_ERR_CACHE_MISS
+    monkeypatch.delenv("RK_NPU_I8_NPU_REDUCE")
+    assert load() == 0
+    # stale files and invalid records
+    for k2 in ([2, 5] + key[2:], [1] + key[1:]):
+        _w8_file(path, k2, rec, rec)
+        assert load() == capi.RK_NPU_ERR_CACHE_MISS
+    _w8_file(path, key, rec, rec, magic="rk_npu_matmul_tuning_cache_v1")
+    assert load() == capi.RK_NPU_ERR_CACHE_MISS
+    for index, value in ((4, 20000), (5, 1400), (5, 3104), (8, 7), (9, 2), (10, 5), (12, 2), (6, 2), (7, 1), (17, -1.0),
+                         (15, float("nan"))):
+        r2 = list(rec)
+        r2[index] = value
+        _w8_file(path, key, rec, r2)
+        assert load() == capi.RK_NPU_ERR_CACHE_MISS, (index, value)
+    _w8_file(path, key, rec, rec)
+    Path(path).write_text(Path(path).read_text() + "junk\n")
+    assert load() == capi.RK_NPU_ERR_CACHE_MISS          # trailing bytes
+    lib.rk_npu_close(ctx)
