@@ -391,3 +391,18 @@ def test_w8_load_only_cache(lib, tmp_path, monkeypatch):
     Path(path).write_text(Path(path).read_text() + "junk\n")
     assert load() == capi.RK_NPU_ERR_CACHE_MISS          # trailing bytes
     lib.rk_npu_close(ctx)
+
+
+def test_public_headers_are_valid_c(tmp_path):
+    # the original checks its headers with a C translation unit (tests/test_w4a8_header.c, tests/test_quant_header.c)
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if not gcc:
+        pytest.skip("no C compiler")
+    src = tmp_path / "headers.c"
+    src.write_text('#include "rknpu_b200_w4a8.h"\n#include "rknpu_b200_quant.h"\n#include "rknpu_b200_ext.h"\n'
+                   "int main(void) { rk_npu_w4a8_config c; rk_npu_matmul_strategy s; (void)c; (void)s; return 0; }\n")
+    out = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", f"-I{ROOT / 'include'}",
+                          str(src)], capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
