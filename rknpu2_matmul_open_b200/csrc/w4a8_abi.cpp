@@ -238,9 +238,10 @@ int pick_split(const rk_npu_w4a8_workspace& ws, int tiles, int token_chunks)
 {
     if (ws.split_override) return ws.split_override;
     const int sms = ws.domain->ctx->sm_count;
+    // The smallest split that gives every SM a CTA: more only adds reduction traffic and shortens
+    // each CTA's stream (measured on 4096x11008: split 2 -> 13 us, split 4 -> 17 us).
     int split = 1;
-    while (split < 8 && (long long)tiles * token_chunks * split * 2 <= (long long)(5 * sms) / 2 && ws.KB / (split * 2) >= 2)
-        split *= 2;
+    while (split < 8 && (long long)tiles * token_chunks * split < sms && ws.KB / (split * 2) >= 2) split *= 2;
     return split;
 }
 
