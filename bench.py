@@ -108,7 +108,8 @@ def run_reference(args, rank, world):
     if world > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
         # torchrun pins every rank to one OpenMP thread; this arm is a single CPU process and may use the host
         os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
-    from oracle.harness import Oracle, Reference, make_activations, make_weights
+    from oracle.harness import Oracle, Reference            # this arm IS the CPU checker being timed
+    from rknpu2_matmul_open_b200.synthetic import make_activations, make_weights
     M = args.tokens
     use_ref = Reference.available()
     ref = Reference() if use_ref else None
@@ -166,7 +167,8 @@ def run_cuda(args, rank, world, local_rank):
     import torch.distributed as dist
 
     import rknpu2_matmul_open_b200 as rk
-    from oracle.harness import Oracle, Reference, make_activations, make_weights, sample_columns
+    from oracle.harness import Oracle, Reference            # checker of what is timed, and the cpu_baseline leg
+    from rknpu2_matmul_open_b200.synthetic import make_activations, make_weights, sample_columns
     from rknpu2_matmul_open_b200.sharding import shard_columns
 
     torch.cuda.set_device(local_rank)
@@ -412,7 +414,7 @@ def _all_gather_ints(dist, value, world, dev):
 
 def _time_other_m(rk, dom, linears, M, args, dev, stream):
     import torch
-    from oracle.harness import make_activations
+    from rknpu2_matmul_open_b200.synthetic import make_activations
     extra = []
     act = {K: torch.from_numpy(make_activations(M, K, seed=K, dtype="f16").view(np.int16)).to(dev) for K in (4096, 11008)}
     for l in linears:
