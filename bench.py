@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the W4A8 hot path on B200 (one JSON line on stdout, rank 0).
 
-Workload (default, BASELINE config 1): Llama-7B decode linears, fp16 in/out, M tokens
+Workload (default, benchmark configuration 1): Llama-7B decode linears, fp16 in/out, M tokens
 (default 8; 1 is reported beside it): per decoder layer four 4096->4096, two
 4096->11008 and one 11008->4096 projection.  A step is one pass over a ring of
 `--layers` distinct layers (>= 2x L2 of distinct weights, so nothing is re-read from
@@ -516,7 +516,7 @@ def _event_time(torch, stream, fn, reps):
 
 
 def _prefill_and_ffn(rk, dom, dev, stream, oracle, make_weights, make_activations, sample_columns):
-    """BASELINE config 2 (prefill GEMM 2048 x 4096 x 14336, fp16) and config 3 (fused FFN 4096 -> 2 x 14336 -> 4096,
+    """Benchmark configuration 2 (prefill GEMM 2048 x 4096 x 14336, fp16) and config 3 (fused FFN 4096 -> 2 x 14336 -> 4096,
     M = 1 and 1024), device-resident, each checked against the oracle on sampled columns / rows."""
     import torch
     out = {}
@@ -564,7 +564,7 @@ def _prefill_and_ffn(rk, dom, dev, stream, oracle, make_weights, make_activation
 
 
 def _prefill_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_activations, shard_columns):
-    """BASELINE config 2 column-sharded over the ranks: every rank runs the 2048 x 4096 prefill GEMM on its run of
+    """Benchmark configuration 2 column-sharded over the ranks: every rank runs the 2048 x 4096 prefill GEMM on its run of
     64-column blocks of N = 14336; figures are whole-job TOPS from the slowest rank's device time, without and
     with the all-gather that reassembles the [M, N] output on every rank."""
     import torch
@@ -601,7 +601,7 @@ def _prefill_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make
 
 
 def _ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_activations):
-    """BASELINE config 4: the 70B-shaped FFN (hidden 8192, intermediate 28672) column-sharded over the ranks.
+    """Benchmark configuration 4: the 70B-shaped FFN (hidden 8192, intermediate 28672) column-sharded over the ranks.
     Gate and up are sharded by the same feature slice so SwiGLU stays local; the middle slices are all-gathered
     (the down projection contracts over all of F), the down projection is sharded by output columns and its
     outputs are all-gathered.  The down projection rescans the row maxima of the gathered middle, which gives the
@@ -609,7 +609,7 @@ def _ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_act
     import torch
     from rknpu2_matmul_open_b200.sharding import gather_columns, shard_columns, shard_ffn_weights, shard_weights
     K, F, N = 8192, 28672, 8192
-    # weights with BASELINE's distribution, generated once for a 2048-column block and repeated along N
+    # weights with the benchmark's value distribution, generated once for a 2048-column block and repeated along N
     # (generating 700 M codes from fp32 normals would take most of a minute per rank; only time is measured here)
     blk_g, blk_sg = make_weights(K, 2048, seed=41)
     blk_d, blk_sd = make_weights(F, 2048, seed=42)
@@ -698,7 +698,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
-    ap.add_argument("--tokens", type=int, default=8, help="decode batch M (BASELINE config 1 uses 1 and 8)")
+    ap.add_argument("--tokens", type=int, default=8, help="decode batch M (benchmark configuration 1 uses 1 and 8)")
     ap.add_argument("--layers", type=int, default=4, help="distinct decoder layers in the ring (4 = 405 MB of int4)")
     ap.add_argument("--distinct-values", action="store_true", help="different weight values per ring layer (slower setup)")
     ap.add_argument("--no-graph", action="store_true")

@@ -333,6 +333,6 @@ class Reference:
 
 
 # --------------------------------------------------------------------- inputs
-# The seeded synthetic tensors (BASELINE distributions) live in the package, where bench.py and the
+# The seeded synthetic tensors (the benchmark configurations' value distributions) live in the package, where bench.py and the
 # profiler workloads use them too; they are re-exported here for the tests.
 from rknpu2_matmul_open_b200.synthetic import make_activations, make_weights, sample_columns  # noqa: E402,F401

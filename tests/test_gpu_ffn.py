@@ -1,6 +1,6 @@
 """Fused gate/up -> SwiGLU -> down through the C ABI.  Against the polynomial oracle the
 whole chain is bit-exact; against the reference build's expf variant the staged bars of
-the north star apply (middle <= 1e-6 relative, output <= 1e-3 relative)."""
+the stated parity bars apply (middle <= 1e-6 relative, output <= 1e-3 relative)."""
 import numpy as np
 import pytest
 
@@ -146,7 +146,7 @@ def test_ffn_argument_errors(gpu):
 
 
 def test_full_size_ffn_decode(gpu, oracle):
-    # BASELINE config 3 at M = 1: 4096 -> 2 x 14336 -> 4096, whole chain bit-exact vs the oracle
+    # benchmark configuration 3 at M = 1: 4096 -> 2 x 14336 -> 4096, whole chain bit-exact vs the oracle
     _, dom, _ = gpu
     M, K, F, N = 1, 4096, 14336, 4096
     Bg, sg = make_weights(K, 2 * F, seed=31)

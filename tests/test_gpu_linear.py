@@ -1,5 +1,5 @@
 """CUDA W4A8 linear through the C ABI against the oracle and the reference fixtures.
-Integer accumulators and outputs are compared bit for bit (north-star bar: int32 exact,
+Integer accumulators and outputs are compared bit for bit (the bar: int32 exact,
 fp16 within 1 ulp -- the observed difference is 0 ulp, so equality is asserted)."""
 import ctypes as C
 import threading
@@ -329,7 +329,7 @@ def test_device_pointers_and_enqueue(gpu, oracle):
 
 
 def test_full_size_decode_sampled(gpu, oracle):
-    # BASELINE decode shapes at full size: 17 sampled columns x all rows (the reference's
+    # the benchmark's decode shapes at full size: 17 sampled columns x all rows (the reference's
     # own sampling for large shapes) plus linearity in the weights scale as a whole-output property
     ctx, dom, _ = gpu
     for (M, K, N) in [(1, 4096, 4096), (8, 4096, 11008), (8, 11008, 4096)]:
