@@ -538,11 +538,29 @@ def _prefill_and_ffn(rk, dom, dev, stream, oracle, make_weights, make_activation
                                          "includes": "quantise kernel + tcgen05 GEMM"}
     ws.free()
     w.free()
+    # the one complete-call figure the original project publishes: binary16, M = 128, K = 11008, N = 4096
+    # (about 4.0 ms on its RK3588 target)
+    M, K, N = 128, 11008, 4096
+    B, sw = make_weights(K, N, seed=22)
+    A = make_activations(M, K, seed=22, dtype="f16")
+    w = rk.Weights(dom, B, sw)
+    ws = rk.Workspace(dom, rk.default_config(M, N, K))
+    dA = torch.from_numpy(A.view(np.int16)).to(dev)
+    dC = torch.zeros((M, N), dtype=torch.int16, device=dev)
+    ms = _event_time(torch, stream, lambda: ws.enqueue_f16(w, dA, dC, stream.cuda_stream), 10)
+    cols = sample_columns(N)
+    _, s, inv = oracle.scales(A)
+    ref = oracle.dequant(oracle.gemm_i32_columns(oracle.quantize(A, inv), B, cols), s, sw[cols], True)
+    out["published_shape_M128_K11008_N4096"] = {
+        "us": ms * 1e3, "tops": 2.0 * M * K * N / (ms * 1e-3) / 1e12, "published_ms_on_rk3588": 4.0,
+        "sampled_exact": bool(np.array_equal(dC.cpu().numpy().view(np.uint16)[:, cols], ref))}
+    ws.free()
+    w.free()
     K, F, N = 4096, 14336, 4096
     Bg, sg = make_weights(K, 2 * F, seed=31)
     Bd, sd = make_weights(F, N, seed=32)
     wg, wd = rk.Weights(dom, Bg, sg), rk.Weights(dom, Bd, sd)
-    for M in (1, 1024):
+    for M in (1, 128, 1024):
         A = make_activations(M, K, seed=31, dtype="f32")
         g = rk.Workspace(dom, rk.default_config(M, 2 * F, K))
         d = rk.Workspace(dom, rk.default_config(M, N, F))

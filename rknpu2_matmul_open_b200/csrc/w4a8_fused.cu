@@ -213,11 +213,11 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
 
     if (trace) trace[4] = (unsigned long long)(clock64() - c_start);
     // ---- 3. contraction: warp w owns the m16 tile (w & 1) of weight group (w >> 1)
-    int acc[NT][4];
+    int acc[NT][4], acc2[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[j][e] = 0;
+        for (int e = 0; e < 4; ++e) { acc[j][e] = 0; acc2[j][e] = 0; }
     const int g8 = lane >> 2, t4 = lane & 3;
     const int wgroup = warp >> 1, mtile = warp & 1;
     // The copies have to land before this CTA may leave, whatever the verdict.
@@ -235,10 +235,16 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
             for (int j = 0; j < NT; ++j) {
                 const uint32_t b0 = lds32(xbase + ((2 * c) * TC + 8 * j) * 16);
                 const uint32_t b1 = lds32(xbase + ((2 * c + 1) * TC + 8 * j) * 16);
-                mma_s8(acc[j], a0, a1, a2, a3, b0, b1);
+                // two accumulator sets halve the chain of dependent MMAs (integer sums: any order is exact)
+                if (c & 1) mma_s8(acc2[j], a0, a1, a2, a3, b0, b1);
+                else mma_s8(acc[j], a0, a1, a2, a3, b0, b1);
             }
         }
     }
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[j][e] += acc2[j][e];
 
     if (trace) trace[5] = (unsigned long long)(clock64() - c_start);
     // ---- 4. partial sums to the rank that owns the channel: inbox_sum[source][token][W]

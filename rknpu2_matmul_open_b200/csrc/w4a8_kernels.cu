@@ -65,8 +65,8 @@ cudaError_t launch_pack_weights(const PackParams& p, cudaStream_t stream)
 // binary16 and fp32 alike the magnitude bits order like the magnitudes, and anything
 // at or above the infinity pattern is NaN/Inf).  Pass 2: q = clamp(round_half_away(
 // x * inverse), -127, 127), written as 16-byte units of the Xq layout.
-template <bool HALF>
-__global__ void __launch_bounds__(256, 8) quantize_kernel(const QuantParams p)
+template <bool HALF, int BS>
+__global__ void __launch_bounds__(BS, 2048 / BS) quantize_kernel(const QuantParams p)
 {
     using T = typename ActType<HALF>::type;
     pdl_launch_dependents();   // the GEMM behind this kernel may start prefetching weights
@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(256, 8) quantize_kernel(const QuantParams p)
     const T* row = reinterpret_cast<const T*>(p.A) + (size_t)m * p.K;
     const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
     const int chunks = p.Kp / 16, live_chunks = (p.K + 15) / 16;
-    __shared__ uint32_t s_part[8];
+    __shared__ uint32_t s_part[BS / 32];
     __shared__ float s_inverse;
     __shared__ int s_bad;
 
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(256, 8) quantize_kernel(const QuantParams p)
     int bad = 0;
     if (p.rowmax == nullptr) {
         float v[16];
-        for (int kc = tid; kc < live_chunks; kc += 256) load16<HALF>(row, kc * 16, p.K, vec, v, maxbits);
+        for (int kc = tid; kc < live_chunks; kc += BS) load16<HALF>(row, kc * 16, p.K, vec, v, maxbits);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) maxbits = max(maxbits, __shfl_xor_sync(0xffffffffu, maxbits, o));
         if ((tid & 31) == 0) s_part[tid >> 5] = maxbits;
@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(256, 8) quantize_kernel(const QuantParams p)
         if (tid == 0) {
             uint32_t mx = 0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) mx = max(mx, s_part[i]);
+            for (int i = 0; i < BS / 32; ++i) mx = max(mx, s_part[i]);
             float maximum;
             if constexpr (HALF) {
                 bad = mx >= 0x7c00u ? 1 : 0;
@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(256, 8) quantize_kernel(const QuantParams p)
     const float inv = s_inverse;
     const int mt = m / p.T, t = m - mt * p.T;
     uint4* dst = reinterpret_cast<uint4*>(p.Xq) + ((size_t)mt * chunks) * p.T + t;
-    for (int kc = tid; kc < chunks; kc += 256) {
+    for (int kc = tid; kc < chunks; kc += BS) {
         uint4 q = make_uint4(0u, 0u, 0u, 0u);
         if (kc < live_chunks) {
             float v[16];
@@ -154,9 +154,12 @@ __global__ void __launch_bounds__(256, 8) quantize_kernel(const QuantParams p)
 
 cudaError_t launch_quantize(const QuantParams& p, cudaStream_t stream, bool pdl)
 {
+    // One CTA per token.  With many tokens the kernel is bound by how many rows are in flight, so
+    // rows of up to 4096 elements get 128-thread CTAs (16 resident per SM instead of 8).
+    const bool narrow = p.M >= 512 && p.K <= 4096;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p.M);
-    cfg.blockDim = dim3(256);
+    cfg.blockDim = dim3(narrow ? 128 : 256);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -164,7 +167,8 @@ cudaError_t launch_quantize(const QuantParams& p, cudaStream_t stream, bool pdl)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return p.half ? cudaLaunchKernelEx(&cfg, quantize_kernel<true>, p) : cudaLaunchKernelEx(&cfg, quantize_kernel<false>, p);
+    if (narrow) return p.half ? cudaLaunchKernelEx(&cfg, quantize_kernel<true, 128>, p) : cudaLaunchKernelEx(&cfg, quantize_kernel<false, 128>, p);
+    return p.half ? cudaLaunchKernelEx(&cfg, quantize_kernel<true, 256>, p) : cudaLaunchKernelEx(&cfg, quantize_kernel<false, 256>, p);
 }
 
 // =============================================================== mma.sync GEMM
