@@ -381,10 +381,10 @@ def run_cuda(args, rank, world, local_rank):
                 "gpu_launches": launches,
                 "roofline": {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
                              "frac": value / world / hbm_peak,
-                             # ncu (profiles/gemm_fused_kernel_decode_M8.md): 8,530,944 B read + 0 B written for the
+                             # ncu (profiles/gemm_fused_kernel_decode_M8.md): 8,525,824 B read + 0 B written for the
                              # 4096 x 4096 linear whose algorithmic bytes are 8,536,064; traffic is one read per
                              # weight byte, so it scales with the bytes of the ring's average linear
-                             "traffic": gemm_bytes_per_launch * (8530944.0 / 8536064.0), "peak_kind": peak_kind,
+                             "traffic": gemm_bytes_per_launch * (8525824.0 / 8536064.0), "peak_kind": peak_kind,
                              "kernel": "gemm_fused_kernel (scan + quantise + GEMM + dequantise in one launch)",
                              "bytes_per_launch": gemm_bytes_per_launch,
                              "us_per_launch": 1e3 * ms_step / len(linears)},

@@ -140,14 +140,20 @@ __global__ void __launch_bounds__(BS, 2048 / BS) quantize_kernel(const QuantPara
         // "Any row bad" across CTAs without a reset pass: the last CTA to arrive
         // publishes the accumulated flag and clears the scratch word; the counter
         // wraps to zero by itself (atomicInc with limit M-1).
-        if (bad) atomicOr(&p.status->bad_accum, bad);
-        __threadfence();
-        const unsigned prev = atomicInc(&p.status->done, (unsigned)p.M - 1u);
-        if (prev == (unsigned)p.M - 1u) {
+        if (gridDim.x == 1) {
+            // a single row: its verdict is the verdict, no round trips through L2 before the kernel can end
+            p.status->bad_input = bad;
+            if (p.host_flag) *p.host_flag = bad;
+        } else {
+            if (bad) atomicOr(&p.status->bad_accum, bad);
             __threadfence();
-            const int any = atomicExch(&p.status->bad_accum, 0);
-            p.status->bad_input = any;
-            if (p.host_flag) *p.host_flag = any;
+            const unsigned prev = atomicInc(&p.status->done, (unsigned)p.M - 1u);
+            if (prev == (unsigned)p.M - 1u) {
+                __threadfence();
+                const int any = atomicExch(&p.status->bad_accum, 0);
+                p.status->bad_input = any;
+                if (p.host_flag) *p.host_flag = any;
+            }
         }
     }
 }
