@@ -196,7 +196,11 @@ def run_cuda(args, rank, world, local_rank):
     # what the all-gather sends, so no packing copies sit between the GEMMs and the collective
     shard_cols = [shard_columns(N, world, rank) for _ in range(args.layers) for (_, N) in LLAMA7B_LAYER]
     out_cols = sum(n1 - n0 for n0, n1 in shard_cols)
-    out_buf = torch.zeros((M * out_cols,), dtype=torch.float16, device=dev)   # binary16 bits (NCCL has no int16)
+    # Shards may differ by one 64-column block between ranks; NCCL's all-gather wants equal pieces, so every
+    # rank's buffer has the size of the widest shard set (the tail of a narrower one stays zero).
+    pad_cols = max(sum(b - a for a, b in (shard_columns(N, world, r) for _ in range(args.layers) for (_, N) in LLAMA7B_LAYER))
+                   for r in range(world))
+    out_buf = torch.zeros((M * pad_cols,), dtype=torch.float16, device=dev)   # binary16 bits (NCCL has no int16)
     out_off = 0
     for layer in range(args.layers):
         for j, (K, N) in enumerate(LLAMA7B_LAYER):
@@ -219,11 +223,7 @@ def run_cuda(args, rank, world, local_rank):
     step_ops = sum(2 * M * l["K"] * l["N"] for l in linears)
     gather_out = None
     if world > 1:
-        sizes = [int(x) for x in _all_gather_ints(dist, M * out_cols, world, dev)]
-        if len(set(sizes)) == 1:
-            gather_out = torch.zeros((world * M * out_cols,), dtype=torch.float16, device=dev)
-        else:   # uneven shards: all_gather of a list of differently sized tensors
-            gather_out = [torch.zeros((n,), dtype=torch.float16, device=dev) for n in sizes]
+        gather_out = torch.zeros((world * M * pad_cols,), dtype=torch.float16, device=dev)
 
     stream = torch.cuda.Stream(device=dev)
 
@@ -234,10 +234,7 @@ def run_cuda(args, rank, world, local_rank):
                 raise RuntimeError(f"enqueue failed: {rc}")
         if world > 1:     # reassemble the column shards on every rank: the one exchange the path has
             with torch.cuda.stream(s):
-                if isinstance(gather_out, list):
-                    dist.all_gather(gather_out, out_buf)
-                else:
-                    dist.all_gather_into_tensor(gather_out, out_buf)
+                dist.all_gather_into_tensor(gather_out, out_buf)
 
     # ---- correctness of what is timed: first linear of the ring against the oracle
     oracle = Oracle()
@@ -402,14 +399,6 @@ def run_cuda(args, rank, world, local_rank):
     for l in linears:
         l["ws"].free()
         l["w"].free()
-
-
-def _all_gather_ints(dist, value, world, dev):
-    import torch
-    t = torch.tensor([value], device=dev, dtype=torch.int64)
-    out = [torch.zeros_like(t) for _ in range(world)]
-    dist.all_gather(out, t)
-    return [int(x.item()) for x in out]
 
 
 def _time_other_m(rk, dom, linears, M, args, dev, stream):
@@ -593,9 +582,9 @@ def _prefill_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make
     w = rk.Weights(dom, np.ascontiguousarray(B[:, n0:n1]), np.ascontiguousarray(sw[n0:n1]))
     ws = rk.Workspace(dom, rk.default_config(M, n1 - n0, K))
     dA = torch.from_numpy(A.view(np.int16)).to(dev)
-    dC = torch.zeros((M * (n1 - n0),), dtype=torch.float16, device=dev)
-    sizes = [int(x) for x in _all_gather_ints(dist, M * (n1 - n0), world, dev)]
-    parts = [torch.zeros((n,), dtype=torch.float16, device=dev) for n in sizes]
+    widest = max(b - a for a, b in (shard_columns(N, world, r) for r in range(world)))
+    dC = torch.zeros((M * widest,), dtype=torch.float16, device=dev)          # equal pieces for the collective
+    parts = torch.zeros((world * M * widest,), dtype=torch.float16, device=dev)
 
     def compute():
         rc = ws.enqueue_f16(w, dA, dC, stream.cuda_stream)
@@ -604,7 +593,7 @@ def _prefill_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make
 
     def with_gather():
         compute()
-        dist.all_gather(parts, dC)
+        dist.all_gather_into_tensor(parts, dC)
 
     out = {}
     for name, fn in (("compute", compute), ("compute_plus_all_gather", with_gather)):
