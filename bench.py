@@ -365,7 +365,7 @@ def run_cuda(args, rank, world, local_rank):
     if rank == 0:
         launches = launches_per_step * args.steps
         value = step_bytes / (ms_step * 1e-3) / 1e9
-        gemm_bytes_per_launch = step_bytes / len(linears)
+        gemm_bytes_per_launch = step_bytes / len(linears) / world   # what one rank's launch reads
         line = {"metric": "w4a8_decode_weight_stream", "value": value, "unit": "GB/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
