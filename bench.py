@@ -609,10 +609,10 @@ def _prefill_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make
 
 def _ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_activations):
     """Benchmark configuration 4: the 70B-shaped FFN (hidden 8192, intermediate 28672) column-sharded over the ranks.
-    Gate and up are sharded by the same feature slice so SwiGLU stays local; the middle slices are all-gathered
-    (the down projection contracts over all of F), the down projection is sharded by output columns and its
-    outputs are all-gathered.  The down projection rescans the row maxima of the gathered middle, which gives the
-    same scales as the single-GPU reuse of the SwiGLU maxima (a maximum is a maximum), so results stay bit-exact."""
+    Gate and up are sharded by the same feature slice so SwiGLU stays local.  The down projection contracts over
+    all of F with the scale of the whole row: the ranks all-reduce (max) their slice maxima, quantise their slice
+    with the combined scale and all-gather the int8 codes; the down projection is sharded by output columns and
+    its outputs are all-gathered.  A maximum is a maximum however it is grouped, so results stay bit-exact."""
     import torch
     from rknpu2_matmul_open_b200.sharding import gather_columns, shard_columns, shard_ffn_weights, shard_weights
     K, F, N = 8192, 28672, 8192
@@ -627,7 +627,7 @@ def _ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_act
     del Bg, Bd
     wg, wd = rk.Weights(dom, Bg_s, sg_s), rk.Weights(dom, Bd_s, sd_s)
     out = {}
-    for M in (32, 1024):
+    for M in (32, 1024, 4096):
         A = make_activations(M, K, seed=41, dtype="f32")
         gu = rk.Workspace(dom, rk.default_config(M, 2 * (f1 - f0), K))
         dn = rk.Workspace(dom, rk.default_config(M, n1 - n0, F))
@@ -635,28 +635,33 @@ def _ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_act
         dMid = torch.zeros((M, f1 - f0), dtype=torch.float32, device=dev)
         dC = torch.zeros((M, n1 - n0), dtype=torch.float32, device=dev)
 
+        # Equal feature slices that are multiples of 16: the ranks exchange int8 codes (a quarter of the fp32
+        # middle's bytes) after agreeing on the row maxima; otherwise the fp32 middle is gathered.
         even = (F // 64) % world == 0 and (N // 64) % world == 0
-        if even:   # equal shards: one collective into [world, M, cols] and one strided copy into [M, world * cols]
-            mid_parts = torch.empty((world, M, f1 - f0), dtype=torch.float32, device=dev)
-            mid_full = torch.empty((M, F), dtype=torch.float32, device=dev)
+        if even:
+            maxima = torch.zeros(M, dtype=torch.int32, device=dev)
+            codes = torch.empty((M, f1 - f0), dtype=torch.int8, device=dev)
+            code_parts = torch.empty((world, M, f1 - f0), dtype=torch.int8, device=dev)
             out_parts = torch.empty((world, M, n1 - n0), dtype=torch.float32, device=dev)
             out_full = torch.empty((M, N), dtype=torch.float32, device=dev)
 
         def step():
-            rc = gu.enqueue_swiglu_f32(wg, dA, dMid, stream.cuda_stream)
             if even:
-                dist.all_gather_into_tensor(mid_parts, dMid)
-                mid_full.view(M, world, f1 - f0).copy_(mid_parts.permute(1, 0, 2))
-                middle = mid_full
-            else:
-                middle = gather_columns(dMid, F)                   # [M, F] on every rank
-            rc = rc or dn.enqueue_f32(wd, middle, dC, stream.cuda_stream)
-            if rc:
-                raise RuntimeError(f"enqueue failed: {rc}")
-            if even:
+                rc = gu.enqueue_swiglu_collect_f32(wg, dA, dMid, maxima, stream.cuda_stream)
+                dist.all_reduce(maxima, op=dist.ReduceOp.MAX)        # bit patterns of non-negative floats order like ints
+                rc = rc or gu.enqueue_quantize_slice(dMid, maxima, codes, stream.cuda_stream)
+                dist.all_gather_into_tensor(code_parts, codes)
+                rc = rc or dn.enqueue_codes_f32(wd, code_parts, world, maxima, dC, stream.cuda_stream)
+                if rc:
+                    raise RuntimeError(f"enqueue failed: {rc}")
                 dist.all_gather_into_tensor(out_parts, dC)
                 out_full.view(M, world, n1 - n0).copy_(out_parts.permute(1, 0, 2))
                 return out_full
+            rc = gu.enqueue_swiglu_f32(wg, dA, dMid, stream.cuda_stream)
+            middle = gather_columns(dMid, F)                       # [M, F] on every rank
+            rc = rc or dn.enqueue_f32(wd, middle, dC, stream.cuda_stream)
+            if rc:
+                raise RuntimeError(f"enqueue failed: {rc}")
             return gather_columns(dC, N)
 
         ms = _event_time(torch, stream, step, 5)
@@ -666,6 +671,7 @@ def _ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_act
         weight_bytes = K * 2 * F // 2 + F * N // 2
         out[f"M{M}"] = {"us": ms * 1e3, "weight_GBps_whole_job": weight_bytes / (ms * 1e-3) / 1e9,
                         "tops_whole_job": 2.0 * M * (K * 2 * F + F * N) / (ms * 1e-3) / 1e12}
+        out[f"M{M}"]["exchange"] = "allreduce(max) of row maxima + all-gather of int8 codes" if even else "all-gather of the fp32 middle"
         gu.free()
         dn.free()
     wg.free()

@@ -44,6 +44,33 @@ int rk_npu_b200_w4a8_enqueue_ffn_f32(rk_npu_w4a8_workspace *gate_up, const rk_np
                                      rk_npu_w4a8_workspace *down, const rk_npu_w4a8_weights *down_weights,
                                      const float *dA, float *dMiddle, float *dC, void *cuda_stream);
 
+/* ---- Column-sharded FFN: the pieces around the exchange between GPUs ----------------------
+ * When gate/up and down are sharded by output columns over g GPUs (each GPU holds the gate and
+ * up columns of one feature slice f0..f1 and a column slice of down), a GPU produces
+ * middle[:, f0:f1] but the down projection needs the whole row, quantised with the scale of the
+ * whole row.  The three calls below let the caller exchange int8 codes instead of the fp32
+ * middle (a quarter of the bytes) and still obtain bit-identical results:
+ *   1. rk_npu_b200_w4a8_enqueue_swiglu_collect_f32: the SwiGLU projection of this GPU's slice;
+ *      additionally maxes the bit patterns of max|middle[m, f0:f1]| into dRowMaxima[M]
+ *      (caller-owned device words that must be zero before the call).
+ *   2. the caller combines dRowMaxima across GPUs with an integer maximum (e.g. ncclAllReduce,
+ *      ncclMax on 32-bit integers: the patterns are non-negative) on the same stream;
+ *   3. rk_npu_b200_w4a8_enqueue_quantize_slice: dMiddle[M, f1-f0] -> dCodes[M, f1-f0] int8 with the
+ *      combined maxima (the rule of the down projection's own quantiser); dRowMaxima is only read;
+ *   4. the caller all-gathers the code slices: [g][M][F/g] on every GPU;
+ *   5. rk_npu_b200_w4a8_enqueue_codes_f32 on the down workspace: dCodes is [parts][M][K/parts]
+ *      (parts = g; K/parts a multiple of 16; parts = 1 accepts a plain [M,K] matrix), scales come
+ *      from dRowMaxima, which is cleared for the next step.  A non-finite middle shows as a
+ *      non-finite maximum: the GEMM returns without writing and rk_npu_b200_w4a8_finish(down)
+ *      reports RK_NPU_ERR_PARAM, as in the single-GPU FFN.
+ * None of these has a counterpart in the original project, whose FFN runs on one device. */
+int rk_npu_b200_w4a8_enqueue_swiglu_collect_f32(rk_npu_w4a8_workspace *gate_up, const rk_npu_w4a8_weights *gate_up_weights,
+                                                const float *dA, float *dMiddle, uint32_t *dRowMaxima, void *cuda_stream);
+int rk_npu_b200_w4a8_enqueue_quantize_slice(rk_npu_w4a8_workspace *gate_up, const float *dMiddle,
+                                            const uint32_t *dRowMaxima, int8_t *dCodes, void *cuda_stream);
+int rk_npu_b200_w4a8_enqueue_codes_f32(rk_npu_w4a8_workspace *down, const rk_npu_w4a8_weights *down_weights,
+                                       const int8_t *dCodes, int parts, uint32_t *dRowMaxima, float *dC, void *cuda_stream);
+
 /* After the caller has synchronised the stream: RK_NPU_OK, RK_NPU_ERR_PARAM (non-finite
  * activation or middle in the last queued call) or RK_NPU_ERR_SUBMIT (a bounded device
  * wait ran out).  Clears the recorded status. */

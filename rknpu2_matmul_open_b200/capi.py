@@ -191,6 +191,9 @@ _SIGNATURES = {
     "rk_npu_b200_w4a8_enqueue_f16": (C.c_int, [_P, _P, _P, _P, _P]),
     "rk_npu_b200_w4a8_enqueue_swiglu_f32": (C.c_int, [_P, _P, _P, _P, _P]),
     "rk_npu_b200_w4a8_enqueue_ffn_f32": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P]),
+    "rk_npu_b200_w4a8_enqueue_swiglu_collect_f32": (C.c_int, [_P, _P, _P, _P, _P, _P]),
+    "rk_npu_b200_w4a8_enqueue_quantize_slice": (C.c_int, [_P, _P, _P, _P, _P]),
+    "rk_npu_b200_w4a8_enqueue_codes_f32": (C.c_int, [_P, _P, _P, C.c_int, _P, _P, _P]),
     "rk_npu_b200_w4a8_finish": (C.c_int, [_P]),
     "rk_npu_b200_w4a8_run_acc_i32": (C.c_int, [_P, _P, _P, C.c_int, _P]),
     "rk_npu_b200_w4a8_last_quant": (C.c_int, [_P, _P, _P]),

@@ -234,15 +234,19 @@ bool on_device(const void* p)
 }
 
 // ------------------------------------------------------------------ kernel sequencing
-int pick_split(const rk_npu_w4a8_workspace& ws, int tiles, int token_chunks)
+constexpr size_t PIN_LIMIT = 512 * 1024;   // host tensors up to this size go through the workspace's pinned buffers
+int pick_split_auto(const rk_npu_w4a8_workspace& ws, int tiles, int token_chunks)
 {
-    if (ws.split_override) return ws.split_override;
     const int sms = ws.domain->ctx->sm_count;
     // The smallest split that gives every SM a CTA: more only adds reduction traffic and shortens
     // each CTA's stream (measured on 4096x11008: split 2 -> 13 us, split 4 -> 17 us).
     int split = 1;
     while (split < 8 && (long long)tiles * token_chunks * split < sms && ws.KB / (split * 2) >= 2) split *= 2;
     return split;
+}
+int pick_split(const rk_npu_w4a8_workspace& ws, int tiles, int token_chunks)
+{
+    return ws.split_override ? ws.split_override : pick_split_auto(ws, tiles, token_chunks);
 }
 
 struct Call {
@@ -257,6 +261,8 @@ struct Call {
     cudaStream_t stream;
     cudaEvent_t* events;   // nullptr or three events: start, after quantise, after GEMM
     bool keep_codes = false;   // fused kernel: also store the activation codes (diagnostic entry only)
+    const int8_t* codes_in = nullptr;   // activations arrive as int8 codes [parts][M][K/parts]; scales from rowmax_in
+    int parts = 1;
 };
 
 // Split-K factor (= cluster size) of the single-kernel path: the largest split whose CTAs
@@ -287,7 +293,7 @@ int enqueue(const Call& c)
     const int F = c.epi == EPI_SWIGLU ? cfg.N / 2 : 0;
     const int tiles = c.epi == EPI_SWIGLU ? (F + 63) / 64 : (cfg.N + TILE_N - 1) / TILE_N;
     const unsigned long long timeout_ns = (unsigned long long)cfg.timeout_ms * 1000000ull;
-    if (ws.variant == 3) {
+    if (ws.variant == 3 && !c.codes_in) {
         // One kernel: scan + quantise + GEMM + epilogue.
         FusedParams f{};
         f.Wp = c.w->packed;
@@ -312,6 +318,18 @@ int enqueue(const Call& c)
         ws.launches.fetch_add(1, std::memory_order_relaxed);
         return RK_NPU_OK;
     }
+    if (c.codes_in) {
+        CodesInParams ci{};
+        ci.codes = c.codes_in;
+        ci.Xq = ws.codes;
+        ci.scales = ws.scales;
+        ci.inverse = ws.inverse;
+        ci.rowmax = c.rowmax_in;
+        ci.status = ws.status;
+        ci.M = cfg.M; ci.K = cfg.K; ci.Kp = ws.KB * KBLOCK; ci.T = ws.T;
+        ci.parts = c.parts;
+        if (launch_codes_in(ci, c.stream) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+    } else {
     QuantParams q{};
     q.A = c.dA;
     q.Xq = ws.codes;
@@ -327,6 +345,7 @@ int enqueue(const Call& c)
     q.T = ws.T;
     q.half = c.half ? 1 : 0;
     if (launch_quantize(q, c.stream, pdl) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+    }
     if (c.events) cudaEventRecord(c.events[1], c.stream);
 
     GemmParams g{};
@@ -359,7 +378,9 @@ int enqueue(const Call& c)
         g.counts = ws.counts;
         err = launch_gemm_stream(g, ws.domain->ctx->sm_count, c.stream, pdl);
     } else {
-        g.split = pick_split(ws, tiles, (cfg.M + ws.TC - 1) / ws.TC);
+        // (a single-kernel workspace given codes runs the ring GEMM; its split override may be odd, so it is not used here)
+        g.split = ws.variant == 3 ? pick_split_auto(ws, tiles, (cfg.M + ws.TC - 1) / ws.TC)
+                                  : pick_split(ws, tiles, (cfg.M + ws.TC - 1) / ws.TC);
         err = launch_gemm_mma(g, ws.TC, c.stream, pdl);
     }
     if (err != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
@@ -405,8 +426,14 @@ int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const vo
     const void* dA = A;
     void* dC = C;
     auto copy_start = Clock::now();
+    // Small host tensors (a decode step's activations and outputs) bounce through pinned memory: a copy
+    // from or to pageable memory makes the driver stage it and wait, which costs more than the kernel.
+    const bool pin_a = !a_dev && ws->pin_in && in_bytes <= PIN_LIMIT;
+    const bool pin_c = !c_dev && ws->pin_out && out_bytes <= PIN_LIMIT;
     if (!a_dev) {
-        if (cudaMemcpyAsync(ws->stage_in, A, in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+        const void* src = A;
+        if (pin_a) { std::memcpy(ws->pin_in, A, in_bytes); src = ws->pin_in; }
+        if (cudaMemcpyAsync(ws->stage_in, src, in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
         dA = ws->stage_in;
     }
     if (!c_dev) dC = ws->stage_out;
@@ -415,11 +442,12 @@ int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const vo
     int rc = enqueue(call);
     if (rc) { cudaStreamSynchronize(s); return rc; }
     copy_start = Clock::now();
-    if (!c_dev) cudaMemcpyAsync(C, dC, out_bytes, cudaMemcpyDeviceToHost, s);
+    if (!c_dev) cudaMemcpyAsync(pin_c ? ws->pin_out : C, dC, out_bytes, cudaMemcpyDeviceToHost, s);
     cudaMemcpyAsync(ws->host_status, ws->status, sizeof(Status), cudaMemcpyDeviceToHost, s);
     if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
-    t.sync_us += elapsed_us(copy_start);
     rc = status_to_rc(*ws, s);
+    if (pin_c && rc == RK_NPU_OK) std::memcpy(C, ws->pin_out, out_bytes);
+    t.sync_us += elapsed_us(copy_start);
     if (metrics) {
         t.activation_scan_us = event_us(ws->events[0], ws->events[1]);
         t.submit_us = rc ? 0.0 : event_us(ws->events[1], ws->events[2]);   // a rejected input did no GEMM work
@@ -455,6 +483,8 @@ void workspace_destroy(rk_npu_w4a8_workspace* ws)
     if (ws->partials) device_free(d, ws->partials, ws->partials_bytes);
     if (ws->counts) device_free(d, ws->counts, ws->counts_bytes);
     if (ws->host_status) cudaFreeHost(ws->host_status);
+    if (ws->pin_in) cudaFreeHost(ws->pin_in);
+    if (ws->pin_out) cudaFreeHost(ws->pin_out);
     for (auto& e : ws->events) if (e) cudaEventDestroy(e);
     if (ws->stream) cudaStreamDestroy(ws->stream);
     if (d) domain_release(d);
@@ -850,6 +880,8 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
         ok = cudaHostAlloc(reinterpret_cast<void**>(&ws->host_status), sizeof(Status), cudaHostAllocDefault) == cudaSuccess &&
              cudaStreamCreateWithFlags(&ws->stream, cudaStreamNonBlocking) == cudaSuccess;
     }
+    if (ok && ws->stage_in_bytes <= PIN_LIMIT) ok = cudaHostAlloc(&ws->pin_in, ws->stage_in_bytes, cudaHostAllocDefault) == cudaSuccess;
+    if (ok && ws->stage_out_bytes <= PIN_LIMIT) ok = cudaHostAlloc(&ws->pin_out, ws->stage_out_bytes, cudaHostAllocDefault) == cudaSuccess;
     for (auto& e : ws->events) ok = ok && cudaEventCreate(&e) == cudaSuccess;
     if (ok) {
         // Token and K padding of the code buffer stays zero for the life of the workspace.
@@ -1009,6 +1041,46 @@ extern "C" int rk_npu_b200_w4a8_enqueue_ffn_f32(rk_npu_w4a8_workspace* gate_up, 
     if (rc) return rc;
     Call second{down, down_weights, dMiddle, dC, false, EPI_F32, nullptr, gate_up->rowmax, s, nullptr};
     return enqueue(second);
+}
+
+// ---- column-sharded FFN: the pieces around the exchange between GPUs
+extern "C" int rk_npu_b200_w4a8_enqueue_swiglu_collect_f32(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w,
+                                                           const float* dA, float* dMiddle, uint32_t* dRowMaxima, void* stream)
+{
+    if (!dRowMaxima) return RK_NPU_ERR_PARAM;
+    const int rc = validate(ws, w, dA, dMiddle, true);
+    if (rc) return rc;
+    WorkspaceLock lock(*ws);
+    if (!lock) return RK_NPU_ERR_BUSY;
+    Call call{ws, w, dA, dMiddle, false, EPI_SWIGLU, dRowMaxima, nullptr, static_cast<cudaStream_t>(stream), nullptr};
+    return enqueue(call);
+}
+extern "C" int rk_npu_b200_w4a8_enqueue_quantize_slice(rk_npu_w4a8_workspace* gate_up, const float* dMiddle,
+                                                       const uint32_t* dRowMaxima, int8_t* dCodes, void* stream)
+{
+    if (!gate_up || !dMiddle || !dRowMaxima || !dCodes || gate_up->config.N % 2) return RK_NPU_ERR_PARAM;
+    WorkspaceLock lock(*gate_up);
+    if (!lock) return RK_NPU_ERR_BUSY;
+    if (cudaSetDevice(gate_up->domain->ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    SliceQuantParams q{dMiddle, dCodes, dRowMaxima, gate_up->config.M, gate_up->config.N / 2};
+    if (launch_quantize_slice(q, static_cast<cudaStream_t>(stream)) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+    gate_up->launches.fetch_add(1, std::memory_order_relaxed);
+    return RK_NPU_OK;
+}
+extern "C" int rk_npu_b200_w4a8_enqueue_codes_f32(rk_npu_w4a8_workspace* down, const rk_npu_w4a8_weights* w,
+                                                  const int8_t* dCodes, int parts, uint32_t* dRowMaxima, float* dC, void* stream)
+{
+    if (!dRowMaxima) return RK_NPU_ERR_PARAM;
+    const int rc = validate(down, w, dCodes, dC, false);
+    if (rc) return rc;
+    const int K = down->config.K;
+    if (parts < 1 || K % parts || (parts > 1 && (K / parts) % 16)) return RK_NPU_ERR_PARAM;
+    WorkspaceLock lock(*down);
+    if (!lock) return RK_NPU_ERR_BUSY;
+    Call call{down, w, nullptr, dC, false, EPI_F32, nullptr, dRowMaxima, static_cast<cudaStream_t>(stream), nullptr};
+    call.codes_in = dCodes;
+    call.parts = parts;
+    return enqueue(call);
 }
 
 extern "C" int rk_npu_b200_w4a8_finish(rk_npu_w4a8_workspace* ws)

@@ -53,6 +53,26 @@ struct QuantParams {
     int half;
 };
 
+// Column-sharded FFN (w4a8_shard.cu): this GPU's slice of the SwiGLU output to int8 codes with the
+// scale of the whole row.
+struct SliceQuantParams {
+    const float* X;         // [M, cols] fp32, compact
+    int8_t* codes;          // [M, cols] int8, compact
+    const uint32_t* rowmax; // [M] magnitude bits of max |middle[m, :]| over the whole row (read only)
+    int M, cols;
+};
+// Column-sharded FFN: already quantised activations into the Xq layout.
+struct CodesInParams {
+    const int8_t* codes;    // [parts][M][K / parts] int8 (parts = 1: plain [M, K])
+    uint8_t* Xq;
+    float* scales;          // [M]
+    float* inverse;         // [M]
+    uint32_t* rowmax;       // [M] magnitude bits the scales come from; cleared after use
+    Status* status;
+    int M, K, Kp, T;
+    int parts;
+};
+
 struct GemmParams {
     const uint8_t* Wp;
     const uint8_t* Xq;
@@ -105,6 +125,8 @@ struct PackParams {
 // Launch wrappers (w4a8_kernels.cu / w4a8_gemm_tc.cu). All return the launch error.
 cudaError_t launch_pack_weights(const PackParams& p, cudaStream_t stream);
 cudaError_t launch_quantize(const QuantParams& p, cudaStream_t stream, bool pdl);
+cudaError_t launch_quantize_slice(const SliceQuantParams& p, cudaStream_t stream);
+cudaError_t launch_codes_in(const CodesInParams& p, cudaStream_t stream);
 // tokens_per_cta: 8, 16 or 32 (must divide p.T)
 cudaError_t launch_gemm_mma(const GemmParams& p, int tokens_per_cta, cudaStream_t stream, bool pdl);
 size_t gemm_mma_smem_bytes(int tokens_per_cta);

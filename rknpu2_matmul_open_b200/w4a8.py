@@ -172,6 +172,19 @@ class Workspace:
         return self.lib.rk_npu_b200_w4a8_enqueue_swiglu_f32(self.handle, weights.handle, _ptr(dA), _ptr(dMiddle),
                                                             C.c_void_p(stream))
 
+    # ---- column-sharded FFN: the pieces around the exchange between GPUs (rknpu_b200_ext.h)
+    def enqueue_swiglu_collect_f32(self, weights: Weights, dA, dMiddle, dRowMaxima, stream: int = 0) -> int:
+        return self.lib.rk_npu_b200_w4a8_enqueue_swiglu_collect_f32(self.handle, weights.handle, _ptr(dA), _ptr(dMiddle),
+                                                                    _ptr(dRowMaxima), C.c_void_p(stream))
+
+    def enqueue_quantize_slice(self, dMiddle, dRowMaxima, dCodes, stream: int = 0) -> int:
+        return self.lib.rk_npu_b200_w4a8_enqueue_quantize_slice(self.handle, _ptr(dMiddle), _ptr(dRowMaxima), _ptr(dCodes),
+                                                                C.c_void_p(stream))
+
+    def enqueue_codes_f32(self, weights: Weights, dCodes, parts: int, dRowMaxima, dC, stream: int = 0) -> int:
+        return self.lib.rk_npu_b200_w4a8_enqueue_codes_f32(self.handle, weights.handle, _ptr(dCodes), int(parts),
+                                                           _ptr(dRowMaxima), _ptr(dC), C.c_void_p(stream))
+
     def finish(self) -> int:
         return self.lib.rk_npu_b200_w4a8_finish(self.handle)
 

@@ -180,3 +180,105 @@ def test_ffn_small_batch_schedules_agree(gpu, oracle, monkeypatch, variant, case
         assert np.array_equal(bits(middle), bits(ref["middle"]))
         assert np.array_equal(bits(C), bits(ref["C"]))
     free(gu, dn, wg, wd)
+
+
+# The column-sharded FFN's code exchange, with the "ranks" run one after another on this GPU: per-slice SwiGLU with
+# collected row maxima, maxima combined, slices quantised with the combined scale, codes stacked as an all-gather
+# would leave them, down projection per column shard on the stacked codes.  Must equal the unsharded chain.
+@pytest.mark.parametrize("case", [(1, 479, 128, 192, 2), (8, 1057, 1024, 256, 4), (33, 959, 512, 320, 2),
+                                  (160, 1057, 2048, 512, 4), (5, 4096, 4096, 4096, 8)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_sharded_ffn_code_exchange_is_bit_exact(gpu, oracle, case):
+    import torch
+    from rknpu2_matmul_open_b200.sharding import shard_ffn_weights, shard_weights
+    _, dom, _ = gpu
+    M, K, F, N, g = case
+    Bg, sg = make_weights(K, 2 * F, seed=F + 2)
+    Bd, sd = make_weights(F, N, seed=N + 2)
+    A = make_activations(M, K, seed=g, dtype="f32")
+    ref = oracle.ffn(A, Bg, sg, Bd, sd, mode=1)
+    dev = torch.device("cuda:0")
+    dA = torch.from_numpy(A).to(dev)
+    pc = F // g
+    maxima = [torch.zeros(M, dtype=torch.int32, device=dev) for _ in range(g)]
+    middles, handles = [], []
+    for r in range(g):
+        Bs, ss, (f0, f1) = shard_ffn_weights(Bg, sg, g, r)
+        assert f1 - f0 == pc
+        w = rk.Weights(dom, Bs, ss)
+        ws = rk.Workspace(dom, rk.default_config(M, 2 * pc, K))
+        mid = torch.zeros((M, pc), dtype=torch.float32, device=dev)
+        assert ws.enqueue_swiglu_collect_f32(w, dA, mid, maxima[r]) == 0
+        middles.append(mid)
+        handles.append((w, ws))
+    torch.cuda.synchronize()
+    middle = torch.cat(middles, dim=1).cpu().numpy()
+    assert np.array_equal(bits(middle), bits(ref["middle"]))
+    combined = torch.stack(maxima).max(dim=0).values.contiguous()          # what the integer all-reduce(max) gives
+    assert np.array_equal(combined.cpu().numpy().view(np.uint32), np.abs(ref["middle"]).max(axis=1).view(np.uint32))
+    codes = torch.zeros((g, M, pc), dtype=torch.int8, device=dev)
+    for r, (w, ws) in enumerate(handles):
+        assert ws.enqueue_quantize_slice(middles[r], combined, codes[r]) == 0
+    torch.cuda.synchronize()
+    out = np.zeros((M, N), np.float32)
+    for r in range(g):
+        Bs, ss, (n0, n1) = shard_weights(Bd, sd, g, r)
+        if n1 == n0:
+            continue
+        w = rk.Weights(dom, Bs, ss)
+        ws = rk.Workspace(dom, rk.default_config(M, n1 - n0, F))
+        dC = torch.zeros((M, n1 - n0), dtype=torch.float32, device=dev)
+        mx = combined.clone()
+        assert ws.enqueue_codes_f32(w, codes, g, mx, dC) == 0
+        torch.cuda.synchronize()
+        assert ws.finish() == 0
+        assert int(mx.abs().sum()) == 0                                      # consumed and cleared
+        out[:, n0:n1] = dC.cpu().numpy()
+        free(ws, w)
+    assert np.array_equal(bits(out), bits(ref["C"]))
+    for w, ws in handles:
+        free(ws, w)
+
+
+def test_codes_entry_plain_matrix_and_errors(gpu, oracle):
+    """parts = 1 takes a plain [M, K] code matrix (any K); a non-finite maximum is reported after the run."""
+    import torch
+    _, dom, _ = gpu
+    M, K, N = 7, 1001, 130
+    B, sw = make_weights(K, N, seed=9)
+    X = make_activations(M, K, seed=9, dtype="f32")
+    ref_rc, ref, _, _ = oracle.linear(X, B, sw)
+    assert ref_rc == 0
+    dev = torch.device("cuda:0")
+    w = rk.Weights(dom, B, sw)
+    ws = rk.Workspace(dom, rk.default_config(M, N, K))
+    # the same linear through the ordinary entry gives the codes and the reference output
+    dC0 = torch.zeros((M, N), dtype=torch.float32, device=dev)
+    assert ws.enqueue_f32(w, torch.from_numpy(X).to(dev), dC0) == 0
+    torch.cuda.synchronize()
+    acc = np.zeros((M, N), np.int32)
+    assert ws.run_acc_i32(w, X, acc) == 0
+    rc, scales, q = ws.last_quant()
+    assert rc == 0
+    maxima = torch.from_numpy(np.abs(X).max(axis=1).view(np.int32).copy()).to(dev)
+    dC = torch.zeros((M, N), dtype=torch.float32, device=dev)
+    assert ws.enqueue_codes_f32(w, torch.from_numpy(q).to(dev), 1, maxima, dC) == 0
+    torch.cuda.synchronize()
+    assert ws.finish() == 0
+    assert np.array_equal(bits(dC.cpu().numpy()), bits(dC0.cpu().numpy()))
+    assert np.array_equal(bits(dC.cpu().numpy()), bits(ref))
+    # argument errors: parts must divide K into multiples of 16
+    assert ws.enqueue_codes_f32(w, torch.from_numpy(q).to(dev), 7, maxima, dC) == capi.RK_NPU_ERR_PARAM
+    assert ws.enqueue_codes_f32(w, torch.from_numpy(q).to(dev), 0, maxima, dC) == capi.RK_NPU_ERR_PARAM
+    # an infinite row maximum: the GEMM does not write, finish reports PARAM, the workspace stays usable
+    bad = torch.from_numpy(np.full(M, 0x7f800000, np.int32)).to(dev)
+    dC.fill_(7.0)
+    assert ws.enqueue_codes_f32(w, torch.from_numpy(q).to(dev), 1, bad, dC) == 0
+    torch.cuda.synchronize()
+    assert ws.finish() == capi.RK_NPU_ERR_PARAM
+    assert float(dC.min()) == 7.0
+    assert ws.enqueue_f32(w, torch.from_numpy(X).to(dev), dC) == 0
+    torch.cuda.synchronize()
+    assert ws.finish() == 0
+    assert np.array_equal(bits(dC.cpu().numpy()), bits(dC0.cpu().numpy()))
+    free(ws, w)

@@ -42,7 +42,7 @@ def _rank_main(rank: int, world: int, port: int, shape, out_queue):
     dC = torch.zeros((M, n1 - n0), dtype=torch.float16, device=dev)
     assert ws.enqueue_f16(w, dA, dC, stream.cuda_stream) == 0
     full = gather_columns(dC, N)
-    # FFN: gate/up sharded by feature slice, middle gathered, down sharded by output columns
+    # FFN: gate/up sharded by feature slice, fp32 middle gathered, down sharded by output columns
     Bg, sg = make_weights(K, 2 * F, seed=6)
     Bd, sd = make_weights(F, N, seed=7)
     A32 = make_activations(M, K, seed=6, dtype="f32")
@@ -60,13 +60,30 @@ def _rank_main(rank: int, world: int, port: int, shape, out_queue):
     ffn = gather_columns(dOut, N)
     torch.cuda.synchronize()
     assert ws.finish() == 0 and gu.finish() == 0 and dn.finish() == 0
+    # the same FFN exchanging int8 codes instead of the fp32 middle (equal feature slices only)
+    ffn_codes = None
+    if (F // 64) % world == 0 and F % 64 == 0:
+        pc = f1 - f0
+        maxima = torch.zeros(M, dtype=torch.int32, device=dev)
+        codes = torch.empty((M, pc), dtype=torch.int8, device=dev)
+        parts = torch.empty((world, M, pc), dtype=torch.int8, device=dev)
+        dOut.zero_()
+        assert gu.enqueue_swiglu_collect_f32(wg, dA32, dMid, maxima, stream.cuda_stream) == 0
+        dist.all_reduce(maxima, op=dist.ReduceOp.MAX)
+        assert gu.enqueue_quantize_slice(dMid, maxima, codes, stream.cuda_stream) == 0
+        dist.all_gather_into_tensor(parts, codes)
+        assert dn.enqueue_codes_f32(wd, parts, world, maxima, dOut, stream.cuda_stream) == 0
+        ffn_codes = gather_columns(dOut, N)
+        torch.cuda.synchronize()
+        assert gu.finish() == 0 and dn.finish() == 0
+        ffn_codes = ffn_codes.cpu().numpy()
     if rank == 0:
-        out_queue.put((full.cpu().numpy().view(np.uint16), middle.cpu().numpy(), ffn.cpu().numpy()))
+        out_queue.put((full.cpu().numpy().view(np.uint16), middle.cpu().numpy(), ffn.cpu().numpy(), ffn_codes))
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("shape", [(8, 1057, 992, 1000), (40, 2304, 1600, 385)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("shape", [(8, 1057, 992, 1000), (40, 2304, 1600, 385), (33, 1057, 1024, 512)], ids=lambda s: "x".join(map(str, s)))
 def test_sharded_linear_and_ffn_are_bit_exact(oracle, shape):
     import torch
     import torch.multiprocessing as mp
@@ -97,3 +114,5 @@ def test_sharded_linear_and_ffn_are_bit_exact(oracle, shape):
     ref_ffn = oracle.ffn(A32, Bg, sg, Bd, sd, mode=1)
     assert np.array_equal(got[1].view(np.uint32), ref_ffn["middle"].view(np.uint32))
     assert np.array_equal(got[2].view(np.uint32), ref_ffn["C"].view(np.uint32))
+    if (F // 64) % world == 0 and F % 64 == 0:
+        assert got[3] is not None and np.array_equal(got[3].view(np.uint32), ref_ffn["C"].view(np.uint32))

@@ -49,6 +49,31 @@ def _worker(rank, world, port, tmp):
     ref_mid, ref_max = oracle.swiglu(acc_full, s, sg, mode=1)
     ok &= bool(np.array_equal(middle.view(np.uint32), ref_mid.view(np.uint32)))
     ok &= bool(np.array_equal(t.numpy().astype(np.uint32), ref_max))
+    # FFN with equal feature slices: the ranks agree on the row maxima (integer max of the bit patterns), quantise
+    # their own slice with the combined scale, all-gather int8 codes as [ranks][M][F/ranks], and run the
+    # column-sharded down projection on them -- the protocol of the GPU path, arithmetic by the oracle.
+    M, K, F, N = 5, 160, 384, 192
+    Bg, sg = make_weights(K, 2 * F, seed=2)
+    Bd, sd = make_weights(F, N, seed=3)
+    A = make_activations(M, K, seed=2, dtype="f32")
+    Bl, sl, (f0, f1) = shard_ffn_weights(Bg, sg, world, rank)
+    _, s, inv = oracle.scales(A)
+    middle_local, maxima = oracle.swiglu(oracle.gemm_i32(oracle.quantize(A, inv), Bl), s, sl, mode=1)
+    t = torch.from_numpy(maxima.view(np.int32).copy())
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    rc, s_mid, inv_mid = oracle.finish_scales(t.numpy().view(np.uint32))
+    codes = torch.from_numpy(oracle.quantize(middle_local, inv_mid))
+    parts = [torch.empty_like(codes) for _ in range(world)]
+    dist.all_gather(parts, codes)
+    gathered = torch.stack(parts).numpy()                                   # [ranks][M][F/ranks]
+    codes_full = np.ascontiguousarray(gathered.transpose(1, 0, 2).reshape(M, F))
+    Bd_l, sd_l, (n0, n1) = shard_weights(Bd, sd, world, rank)
+    out_local = oracle.dequant(oracle.gemm_i32(codes_full, Bd_l), s_mid, sd_l, half=False)
+    out = gather_columns(torch.from_numpy(out_local), N).numpy()
+    ref = oracle.ffn(A, Bg, sg, Bd, sd, mode=1)
+    ok &= rc == 0 and ref["rc"] == 0
+    ok &= bool(np.array_equal(s_mid.view(np.uint32), ref["scales_down_in"].view(np.uint32)))
+    ok &= bool(np.array_equal(out.view(np.uint32), ref["C"].view(np.uint32)))
     Path(tmp, f"rank{rank}.ok").write_text("1" if ok else "0")
     dist.destroy_process_group()
 
