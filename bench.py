@@ -645,8 +645,8 @@ def _ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_act
             out_parts = torch.empty((world, M, n1 - n0), dtype=torch.float32, device=dev)
             out_full = torch.empty((M, N), dtype=torch.float32, device=dev)
 
-        def step():
-            if even:
+        def step(codes_exchange=even):
+            if codes_exchange:
                 rc = gu.enqueue_swiglu_collect_f32(wg, dA, dMid, maxima, stream.cuda_stream)
                 dist.all_reduce(maxima, op=dist.ReduceOp.MAX)        # bit patterns of non-negative floats order like ints
                 rc = rc or gu.enqueue_quantize_slice(dMid, maxima, codes, stream.cuda_stream)
@@ -664,14 +664,19 @@ def _ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_act
                 raise RuntimeError(f"enqueue failed: {rc}")
             return gather_columns(dC, N)
 
-        ms = _event_time(torch, stream, step, 5)
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        # Both exchanges are timed where both apply: with few tokens the extra all-reduce of the code exchange
+        # costs more than the bytes it saves; every rank takes the same (max-reduced) decision.
+        timed = {}
+        for name, flag in ([("int8 codes", True)] if even else []) + [("fp32 middle", False)]:
+            t = torch.tensor([_event_time(torch, stream, lambda: step(flag), 5)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            timed[name] = float(t.item())
+        best = min(timed, key=timed.get)
+        ms = timed[best]
         weight_bytes = K * 2 * F // 2 + F * N // 2
         out[f"M{M}"] = {"us": ms * 1e3, "weight_GBps_whole_job": weight_bytes / (ms * 1e-3) / 1e9,
-                        "tops_whole_job": 2.0 * M * (K * 2 * F + F * N) / (ms * 1e-3) / 1e12}
-        out[f"M{M}"]["exchange"] = "allreduce(max) of row maxima + all-gather of int8 codes" if even else "all-gather of the fp32 middle"
+                        "tops_whole_job": 2.0 * M * (K * 2 * F + F * N) / (ms * 1e-3) / 1e12,
+                        "exchange": best, "us_by_exchange": {k: v * 1e3 for k, v in timed.items()}}
         gu.free()
         dn.free()
     wg.free()

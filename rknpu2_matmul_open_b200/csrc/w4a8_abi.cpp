@@ -868,7 +868,7 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
     ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->status), sizeof(Status));
     if (variant == 4) {
         const size_t tiles = size_t(cfg->N + TILE_N - 1) / TILE_N;
-        ws->partials_bytes = tiles * 128 * size_t(ws->TC) * sizeof(int);
+        ws->partials_bytes = 2 * size_t(ctx->sm_count) * 128 * size_t(ws->TC) * sizeof(int);   // two slots per CTA
         ws->counts_bytes = tiles * sizeof(unsigned int);
         ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->partials), ws->partials_bytes);
         ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->counts), ws->counts_bytes);

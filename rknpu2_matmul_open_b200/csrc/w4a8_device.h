@@ -91,7 +91,7 @@ struct GemmParams {
     int pair;               // tcgen05 path: 1 = two-CTA tiles (cta_group::2), T must be 128
     unsigned long long timeout_ns;
     unsigned long long* trace;  // optional cycle stamps of CTA (0,0): [role 0..2][k-block 0..63][2] (nullable)
-    int* partials;              // streaming kernel: [tiles][T][128] int32 partial sums, zero between launches
+    int* partials;              // streaming kernel: [2 x CTAs][T / 4][128][4] int32 partial sums (two slots per CTA, never cleared)
     unsigned int* counts;       // streaming kernel: [tiles] stages accumulated so far, zero between launches
 };
 
@@ -131,7 +131,7 @@ cudaError_t launch_codes_in(const CodesInParams& p, cudaStream_t stream);
 cudaError_t launch_gemm_mma(const GemmParams& p, int tokens_per_cta, cudaStream_t stream, bool pdl);
 size_t gemm_mma_smem_bytes(int tokens_per_cta);
 // Persistent, evenly balanced small-batch tcgen05 GEMM (w4a8_stream.cu): p.T in {16, 32} >= p.M, K <= 131072,
-// p.partials ([tiles][p.T][128] int32) and p.counts ([tiles]) zeroed once at allocation.
+// p.partials (2 x sm_count slots of p.T x 128 int32) and p.counts ([tiles], zeroed once at allocation).
 cudaError_t launch_gemm_stream(const GemmParams& p, int sm_count, cudaStream_t stream, bool pdl);
 // Fused small-batch kernel: tokens_per_cta 8, 16 or 32 (>= p.M); p.stages <= FUSED_MAX_STAGES.
 constexpr int FUSED_MAX_STAGES = 16;

@@ -17,10 +17,12 @@
 // range).  Its copy ring never drains between segments, and the accumulator is double
 // buffered in tensor memory, so the epilogue of one segment overlaps the MMAs of the next.
 // A segment that covers its tile's whole K is dequantised and stored directly.  Otherwise the
-// int32 partial sums are added to the tile's slot in a global scratch buffer (integer
-// addition: exact in any order) and the tile's stage counter is advanced; whoever brings the
-// counter to the tile's stage count reads the slot back, finishes the tile and leaves slot and
-// counter zero for the next launch.  Nobody waits for anybody.
+// int32 partial sums are written to a scratch slot of this CTA (a CTA's run begins and ends
+// with at most one partial segment each, so it owns two slots) with plain 16-byte stores and
+// the tile's stage counter is advanced; whoever brings the counter to the tile's stage count
+// works out from the schedule which CTAs contributed, adds their slots (integer addition:
+// exact in any order), finishes the tile and leaves the counter zero for the next launch.
+// Nobody waits for anybody, and no slot needs clearing.
 //
 // Roles: warp 0 producer (bulk copies: weights 4 x 8 KB + codes T x 512 B per stage; the first
 // ring-full of weights is requested before the programmatic dependency wait), warp 1 MMA
@@ -358,7 +360,9 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
             const bool whole = nseg == nst;          // this segment covers its tile's whole K
-            int* const slot = p.partials + (size_t)tile * 128 * T;
+            // slot layout [token / 4][row][4 tokens]: a warp's 16-byte accesses are contiguous
+            int4* const scratch = reinterpret_cast<int4*>(p.partials);
+            int4* const my_slot = scratch + (size_t)(2 * blockIdx.x + (gi == 0 ? 0 : 1)) * 32 * T;
             for (int c = 0; c < nchunk; ++c) {
                 uint32_t r[32];
                 tc_ld16(taddr + 32 * c, r);
@@ -378,10 +382,11 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
                 for (int i = 0; i < 32; ++i) v[i] = (int)r[i] >> 4;     // exact: sums are multiples of 16
                 if (whole) finish_chunk(v, tile, c);
                 else {
-                    // ---- part of a tile: add to the tile's slot [token][row]
+                    // ---- part of a tile: into this CTA's slot
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (32 * c + i < T && v[i]) atomicAdd(slot + (32 * c + i) * 128 + row, v[i]);
+                    for (int j = 0; j < 8; ++j)
+                        if (32 * c + 4 * j < T)
+                            my_slot[(size_t)(8 * c + j) * 128 + row] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 }
             }
             if (!whole) {
@@ -395,14 +400,28 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_tc_stream_kernel(const Gem
                 asm volatile("bar.sync 2, 128;" ::: "memory");
                 const bool finish = *reinterpret_cast<volatile int*>(&s_flag[0]) != 0;
                 if (finish) {
-                    // last contributor: fetch the complete sums, leave slot and counter clean
+                    // last contributor: every CTA whose share of the flat list overlaps this tile's stages wrote a
+                    // slot -- its first one if its run starts in this tile, else its second
                     __threadfence();
+                    const long long s0 = (long long)tile * nst, s1 = s0 + nst, grid = gridDim.x;
+                    int c_lo = (int)(s0 * grid / total);
+                    while (total * (c_lo + 1) / grid <= s0) ++c_lo;
+                    while (total * c_lo / grid > s0) --c_lo;
                     for (int c = 0; c < nchunk; ++c) {
                         int v[32];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            v[i] = 0;
-                            if (32 * c + i < T) { v[i] = __ldcg(slot + (32 * c + i) * 128 + row); slot[(32 * c + i) * 128 + row] = 0; }
+                        for (int i = 0; i < 32; ++i) v[i] = 0;
+                        for (int cc = c_lo; cc < (int)grid && total * cc / grid < s1; ++cc) {
+                            const int first_tile = (int)((total * cc / grid) / nst);
+                            const int4* const src = scratch + (size_t)(2 * cc + (first_tile == tile ? 0 : 1)) * 32 * T;
+                            int4 part[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                part[j] = (32 * c + 4 * j < T) ? __ldcg(src + (size_t)(8 * c + j) * 128 + row) : make_int4(0, 0, 0, 0);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                v[4 * j] += part[j].x; v[4 * j + 1] += part[j].y; v[4 * j + 2] += part[j].z; v[4 * j + 3] += part[j].w;
+                            }
                         }
                         finish_chunk(v, tile, c);
                     }
