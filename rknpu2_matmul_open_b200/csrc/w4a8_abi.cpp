@@ -234,7 +234,6 @@ bool on_device(const void* p)
 }
 
 // ------------------------------------------------------------------ kernel sequencing
-constexpr size_t PIN_LIMIT = 512 * 1024;   // host tensors up to this size go through the workspace's pinned buffers
 int pick_split_auto(const rk_npu_w4a8_workspace& ws, int tiles, int token_chunks)
 {
     const int sms = ws.domain->ctx->sm_count;
@@ -426,14 +425,8 @@ int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const vo
     const void* dA = A;
     void* dC = C;
     auto copy_start = Clock::now();
-    // Small host tensors (a decode step's activations and outputs) bounce through pinned memory: a copy
-    // from or to pageable memory makes the driver stage it and wait, which costs more than the kernel.
-    const bool pin_a = !a_dev && ws->pin_in && in_bytes <= PIN_LIMIT;
-    const bool pin_c = !c_dev && ws->pin_out && out_bytes <= PIN_LIMIT;
     if (!a_dev) {
-        const void* src = A;
-        if (pin_a) { std::memcpy(ws->pin_in, A, in_bytes); src = ws->pin_in; }
-        if (cudaMemcpyAsync(ws->stage_in, src, in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+        if (cudaMemcpyAsync(ws->stage_in, A, in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
         dA = ws->stage_in;
     }
     if (!c_dev) dC = ws->stage_out;
@@ -442,12 +435,13 @@ int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const vo
     int rc = enqueue(call);
     if (rc) { cudaStreamSynchronize(s); return rc; }
     copy_start = Clock::now();
-    if (!c_dev) cudaMemcpyAsync(pin_c ? ws->pin_out : C, dC, out_bytes, cudaMemcpyDeviceToHost, s);
+    // Host tensors are copied straight from and to the caller's (pageable) memory: bouncing small ones through
+    // pinned buffers was measured slower (the extra host memcpy costs more than the driver's own staging).
+    if (!c_dev) cudaMemcpyAsync(C, dC, out_bytes, cudaMemcpyDeviceToHost, s);
     cudaMemcpyAsync(ws->host_status, ws->status, sizeof(Status), cudaMemcpyDeviceToHost, s);
     if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
-    rc = status_to_rc(*ws, s);
-    if (pin_c && rc == RK_NPU_OK) std::memcpy(C, ws->pin_out, out_bytes);
     t.sync_us += elapsed_us(copy_start);
+    rc = status_to_rc(*ws, s);
     if (metrics) {
         t.activation_scan_us = event_us(ws->events[0], ws->events[1]);
         t.submit_us = rc ? 0.0 : event_us(ws->events[1], ws->events[2]);   // a rejected input did no GEMM work
@@ -483,8 +477,6 @@ void workspace_destroy(rk_npu_w4a8_workspace* ws)
     if (ws->partials) device_free(d, ws->partials, ws->partials_bytes);
     if (ws->counts) device_free(d, ws->counts, ws->counts_bytes);
     if (ws->host_status) cudaFreeHost(ws->host_status);
-    if (ws->pin_in) cudaFreeHost(ws->pin_in);
-    if (ws->pin_out) cudaFreeHost(ws->pin_out);
     for (auto& e : ws->events) if (e) cudaEventDestroy(e);
     if (ws->stream) cudaStreamDestroy(ws->stream);
     if (d) domain_release(d);
@@ -843,7 +835,12 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
     // half the SMs and K is long, the streaming kernel (all SMs, K split between CTAs) is faster.
     const bool stream_best = stream_ok && cfg->M > 32 && cfg->K >= 8192 &&
                              (cfg->N + TILE_N - 1) / TILE_N * 2 <= ctx->sm_count;
-    int variant = (cfg->M > 32 && stream_best) ? 4 : (cfg->M > 32 && tc_ok) ? 2 : fused_best ? 3 : 1;
+    // 33..128 tokens with so few tiles that tiles x 32-token chunks fit the SMs in one wave (N = 4096: 32 x 4): the
+    // mma.sync ring, one CTA per (tile, chunk, K split), fills the GPU where the tcgen05 kernels leave SMs idle or
+    // pay for combining partial tiles (11008 -> 4096 at 128 tokens: 33 us against 44 and 47 us).
+    const bool ring_best = cfg->M > 32 && cfg->M <= 128 &&
+                           (long long)((cfg->N + TILE_N - 1) / TILE_N) * ((cfg->M + 31) / 32) <= ctx->sm_count;
+    int variant = ring_best ? 1 : (cfg->M > 32 && stream_best) ? 4 : (cfg->M > 32 && tc_ok) ? 2 : fused_best ? 3 : 1;
     if (forced == 1 || (forced == 2 && tc_ok) || (forced == 3 && fused_ok) || (forced == 4 && stream_ok)) variant = forced;
     ws->variant = variant;
     if (variant == 2) {
@@ -880,8 +877,6 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
         ok = cudaHostAlloc(reinterpret_cast<void**>(&ws->host_status), sizeof(Status), cudaHostAllocDefault) == cudaSuccess &&
              cudaStreamCreateWithFlags(&ws->stream, cudaStreamNonBlocking) == cudaSuccess;
     }
-    if (ok && ws->stage_in_bytes <= PIN_LIMIT) ok = cudaHostAlloc(&ws->pin_in, ws->stage_in_bytes, cudaHostAllocDefault) == cudaSuccess;
-    if (ok && ws->stage_out_bytes <= PIN_LIMIT) ok = cudaHostAlloc(&ws->pin_out, ws->stage_out_bytes, cudaHostAllocDefault) == cudaSuccess;
     for (auto& e : ws->events) ok = ok && cudaEventCreate(&e) == cudaSuccess;
     if (ok) {
         // Token and K padding of the code buffer stays zero for the life of the workspace.

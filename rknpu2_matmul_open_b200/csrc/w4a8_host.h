@@ -101,8 +101,6 @@ struct rk_npu_w4a8_workspace {
     void* stage_out = nullptr;  // device copy of host outputs
     size_t codes_bytes = 0, stage_in_bytes = 0, stage_out_bytes = 0;
     rkb200::Status* host_status = nullptr;  // pinned
-    void* pin_in = nullptr;     // pinned bounce buffers for small host tensors (nullptr above PIN_LIMIT bytes)
-    void* pin_out = nullptr;
     cudaEvent_t events[8]{};
     std::atomic<uint64_t> launches{0};
     unsigned long long* trace = nullptr;   // device stamps, allocated by rk_npu_b200_w4a8_trace_enable

@@ -403,9 +403,10 @@ def test_streaming_schedule_reuses_one_workspace(gpu, oracle, monkeypatch):
     w.free()
 
 
-# 33..128 tokens: the per-tile tcgen05 kernel (2) and the persistent streaming kernel (4, token tiles of
-# 64 and 128, partial tiles combined across CTAs) against the oracle, plain and ragged shapes
-@pytest.mark.parametrize("variant", [2, 4])
+# 33..128 tokens: the mma.sync ring in 32-token chunks (1), the per-tile tcgen05 kernel (2) and the persistent
+# streaming kernel (4, token tiles of 64 and 128, partial tiles combined across CTAs) against the oracle,
+# plain and ragged shapes
+@pytest.mark.parametrize("variant", [1, 2, 4])
 @pytest.mark.parametrize("shape", [(33, 1057, 257), (64, 4096, 1024), (100, 2304, 385), (128, 11008, 512), (65, 8192, 130)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_mid_batch_schedules_agree(gpu, oracle, monkeypatch, variant, shape):
