@@ -383,6 +383,7 @@ def run_cuda(args, rank, world, local_rank):
                              # weight byte, so it scales with the bytes of the ring's average linear
                              "traffic": gemm_bytes_per_launch * (8525824.0 / 8536064.0), "peak_kind": peak_kind,
                              "kernel": "gemm_fused_kernel (scan + quantise + GEMM + dequantise in one launch)",
+                             "frac_of_nominal": value / world / 8000.0, "nominal_peak": 8000.0,   # 8 TB/s data-sheet HBM3e
                              "bytes_per_launch": gemm_bytes_per_launch,
                              "us_per_launch": 1e3 * ms_step / len(linears)},
                 "cpu_baseline": cpu, "also": also}
@@ -523,7 +524,7 @@ def _prefill_and_ffn(rk, dom, dev, stream, oracle, make_weights, make_activation
     exact = bool(np.array_equal(dC.cpu().numpy().view(np.uint16)[:, cols], ref))
     tops = 2.0 * M * K * N / (ms * 1e-3) / 1e12
     out["prefill_M2048_K4096_N14336"] = {"us": ms * 1e3, "tops": tops, "frac_of_measured_int8_peak": tops / INT8_PEAK_TOPS,
-                                         "peak_tops": INT8_PEAK_TOPS, "sampled_exact": exact,
+                                         "peak_tops": INT8_PEAK_TOPS, "frac_of_nominal_4500": tops / 4500.0, "sampled_exact": exact,
                                          "includes": "quantise kernel + tcgen05 GEMM"}
     ws.free()
     w.free()

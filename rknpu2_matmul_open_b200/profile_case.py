@@ -7,7 +7,7 @@ interest in a minute or two.  Cases:
   decode   the seven Llama-7B decode linears (4 x 4096->4096, 2 x 4096->11008, 11008->4096)
            at M = 8, binary16 in and out, one decoder layer, stream launches
   prefill  one 2048 x 4096 x 14336 linear, binary16 in and out
-  mid      one 64 x 11008 x 4096 linear, binary16 (few tiles, long K: the streaming tcgen05 kernel)
+  mid      one 128 x 11008 x 8192 linear, binary16 (64 tiles, long K: the streaming tcgen05 kernel)
   ffn      gate/up 4096 -> 2 x 14336, SwiGLU, down 14336 -> 4096 at M = 1024, fp32
 
 Options: --repeat R (launch sets, default 4), --tokens M (override the batch), --stamps (after
@@ -52,9 +52,9 @@ def main() -> None:
     stream = torch.cuda.Stream(device=dev)
     calls = []
     if args.case in ("decode", "prefill", "mid"):
-        M = args.tokens or {"decode": 8, "prefill": 2048, "mid": 64}[args.case]
+        M = args.tokens or {"decode": 8, "prefill": 2048, "mid": 128}[args.case]
         shapes = {"decode": [(4096, 4096)] * 4 + [(4096, 11008)] * 2 + [(11008, 4096)], "prefill": [(4096, 14336)],
-                  "mid": [(11008, 4096)]}[args.case]
+                  "mid": [(11008, 8192)]}[args.case]
         for K, N in shapes:
             B, sw = _weights(rng, K, N)
             w = rk.Weights(dom, B, sw)
