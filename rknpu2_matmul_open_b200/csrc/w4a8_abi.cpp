@@ -276,11 +276,24 @@ int fused_split(const rk_npu_w4a8_workspace& ws, int tiles)
         const int stages = (ws.KB + split - 1) / split;
         if (stages > FUSED_MAX_STAGES) continue;
         if (!best) best = split;
-        const size_t bytes = gemm_fused_smem_bytes(ws.TC, stages) + 1024;
+        const size_t bytes = gemm_fused_smem_bytes(ws.TC, stages, 1) + 1024;
         const long long slots = (long long)sms * std::min<long long>(8, (long long)(smem_per_sm / bytes));
         if ((long long)tiles * split <= slots) best = split;
     }
     return best ? best : 8;
+}
+
+// Column tiles per CTA of the single-kernel path.  Its CTAs hold their whole weight slice in shared memory
+// from launch to exit, and a launch starts while the one in front still runs: when one launch alone would
+// take more than half of the GPU's shared memory, part of its CTAs could only start once earlier CTAs leave,
+// and they would then run the whole dependent chain a second time.  Such launches run two tiles per CTA.
+int fused_tiles_per_cta(const rk_npu_w4a8_workspace& ws, int tiles, int split, int stages)
+{
+    if (tiles < 2 || gemm_fused_smem_bytes(ws.TC, stages, 2) > 227 * 1024) return 1;
+    if (ws.tiles_per_cta_override) return ws.tiles_per_cta_override;
+    const size_t all = size_t(tiles) * split * (gemm_fused_smem_bytes(ws.TC, stages, 1) + 1024);
+    const size_t half_gpu = size_t(ws.domain->ctx->sm_count) * (220 * 1024) / 2;
+    return all > half_gpu ? 2 : 1;
 }
 
 int enqueue(const Call& c)
@@ -308,6 +321,7 @@ int enqueue(const Call& c)
         f.KB = ws.KB; f.NG = c.w->NG; f.F = F; f.epi = c.epi;
         f.split = fused_split(ws, tiles);
         f.stages = (ws.KB + f.split - 1) / f.split;
+        f.tiles_per_cta = fused_tiles_per_cta(ws, tiles, f.split, f.stages);
         f.half = c.half ? 1 : 0;
         f.timeout_ns = timeout_ns;
         f.trace = ws.trace;
@@ -843,6 +857,10 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
     int variant = ring_best ? 1 : (cfg->M > 32 && stream_best) ? 4 : (cfg->M > 32 && tc_ok) ? 2 : fused_best ? 3 : 1;
     if (forced == 1 || (forced == 2 && tc_ok) || (forced == 3 && fused_ok) || (forced == 4 && stream_ok)) variant = forced;
     ws->variant = variant;
+    if (const char* e = std::getenv("RK_NPU_B200_TILES_PER_CTA")) {   // experiments and tests: 1 or 2, else automatic
+        const int v = std::atoi(e);
+        ws->tiles_per_cta_override = (v == 1 || v == 2) ? v : 0;
+    }
     if (variant == 2) {
         // Batches above 128 tokens run two-CTA tiles: 128-token code tiles, two per MMA tile.
         ws->TC = 0;

@@ -110,6 +110,7 @@ struct FusedParams {
     int KB, NG, F, epi;
     int split;                  // cluster size along y == split-K factor
     int stages;                 // k-blocks of smem per CTA (>= ceil(KB / split))
+    int tiles_per_cta;          // 1, or 2: a CTA runs two adjacent column tiles one after the other
     int half;                   // activations are binary16
     unsigned long long timeout_ns;
     unsigned long long* trace;  // optional [CTA][8] global-timer stamps of the kernel's phases (nullable)
@@ -136,7 +137,7 @@ cudaError_t launch_gemm_stream(const GemmParams& p, int sm_count, cudaStream_t s
 // Fused small-batch kernel: tokens_per_cta 8, 16 or 32 (>= p.M); p.stages <= FUSED_MAX_STAGES.
 constexpr int FUSED_MAX_STAGES = 16;
 cudaError_t launch_gemm_fused(const FusedParams& p, int tokens_per_cta, cudaStream_t stream, bool pdl);
-size_t gemm_fused_smem_bytes(int tokens_per_cta, int stages);
+size_t gemm_fused_smem_bytes(int tokens_per_cta, int stages, int tiles_per_cta);
 // tcgen05 path: p.T is the token tile of the code layout (multiple of 16, <= 256; 128 when p.pair)
 cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl);
 bool gemm_tc_supported(const GemmParams& p);

@@ -16,6 +16,10 @@
 //   3. the slice of A is quantised into shared memory in the layout the mma.sync B fragments
 //      read; 4. int8 mma.sync over the slice; 5. partial sums are pushed to the cluster rank
 //      that owns each channel, one more cluster barrier, local sum, dequantise / SwiGLU, store.
+// A launch whose CTAs would fill more shared memory than the launches around it leave free runs
+// two column tiles per CTA (tiles_per_cta = 2): half the CTAs, all resident at once beside their
+// neighbours; steps 1-3 are shared, the second tile's weights are requested into the first tile's
+// place once its contraction has read them, and steps 4-5 of the first tile hide their arrival.
 #include "w4a8_device.h"
 #include "w4a8_math.cuh"
 #include "w4a8_ptx.cuh"
@@ -25,16 +29,17 @@ namespace cg = cooperative_groups;
 
 namespace rkb200 {
 
-__host__ __device__ constexpr size_t fused_smem_bytes(int tc, int stages)
+__host__ __device__ constexpr size_t fused_smem_bytes(int tc, int stages, int tiles_per_cta)
 {
-    return (size_t)stages * 8192            // weight k-blocks
-           + (size_t)stages * tc * 128      // activation codes of the slice
-           + (size_t)tc * 192 * 4           // inbox: partial sums for the channels this rank owns
-           + (size_t)8 * tc * 4             // inbox: per-rank partial row maxima
-           + (size_t)4 * tc * 4             // row max, scale, inverse, SwiGLU row max
-           + 128 * 4 + 24 + 16;             // channel scales, three barriers, flags
+    return (size_t)stages * 8192                       // weight k-blocks
+           + (size_t)stages * tc * 128                 // activation codes of the slice
+           + (size_t)tiles_per_cta * tc * 192 * 4      // inbox per tile: partial sums for the channels this rank owns
+           + (size_t)8 * tc * 4                        // inbox: per-rank partial row maxima
+           + (size_t)4 * tc * 4                        // row max, scale, inverse, SwiGLU row max
+           + 128 * 4 + 40 + 16;                        // channel scales, five barriers, flags
 }
 
+constexpr size_t FUSED_SMEM_LIMIT = 227 * 1024;   // dynamic shared memory one CTA may ask for
 constexpr int FUSED_THREADS = 256;   // eight warps: (weight group, m16 tile) pairs in the contraction
 
 template <int NT, bool HALF>
@@ -46,19 +51,25 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
     const int nst = p.stages;
     uint8_t* const wst = smem;
     uint8_t* const xs = wst + (size_t)nst * 8192;
-    int32_t* const inbox_sum = reinterpret_cast<int32_t*>(xs + (size_t)nst * TC * 128);
-    uint32_t* const inbox_max = reinterpret_cast<uint32_t*>(inbox_sum + TC * 192);
+    const int TPC = p.tiles_per_cta;                   // 1 or 2 column tiles per CTA, one after the other
+    int32_t* const inbox_all = reinterpret_cast<int32_t*>(xs + (size_t)nst * TC * 128);
+    uint32_t* const inbox_max = reinterpret_cast<uint32_t*>(inbox_all + TPC * TC * 192);
     uint32_t* const s_max = inbox_max + 8 * TC;
     float* const s_scale = reinterpret_cast<float*>(s_max + TC);
     float* const s_inv = s_scale + TC;
     uint32_t* const s_outmax = reinterpret_cast<uint32_t*>(s_inv + TC);
     float* const s_sw = reinterpret_cast<float*>(s_outmax + TC);   // 128 channel scales of this CTA
-    uint64_t* const full = reinterpret_cast<uint64_t*>(s_sw + 128);   // [0] weights landed, [1] row maxima of all ranks, [2] partial sums
-    int* const s_flags = reinterpret_cast<int*>(full + 3);   // [0] bad verdict, [1] wait ran out
+    // barriers, each used for one phase only: [0] row maxima of all ranks, [1 + i] weights of tile i landed,
+    // [3 + i] partial sums of tile i
+    uint64_t* const full = reinterpret_cast<uint64_t*>(s_sw + 128);
+    int* const s_flags = reinterpret_cast<int*>(full + 5);   // [0] bad verdict, [1] wait ran out
 
     pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tile = blockIdx.x, rank = blockIdx.y, S = p.split;
+    const int rank = blockIdx.y, S = p.split;
+    const int tiles_total = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : (p.N + TILE_N - 1) / TILE_N;
+    const int tile_first = blockIdx.x * TPC;
+    const int ntile = min(TPC, tiles_total - tile_first);   // the last CTA of an odd count has one tile
     unsigned long long* const trace = (p.trace && tid == 0) ? p.trace + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
     const long long c_start = clock64();
     if (trace) trace[0] = global_ns();
@@ -72,28 +83,38 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
     // Weights of the slice: per group one contiguous run of nkb k-blocks -> four bulk
     // copies on one barrier, requested before the dependency wait (weights never change).
     if (tid == 0) {
-        mbar_init(&full[0], 1);
-        mbar_init(&full[1], 1);
-        mbar_init(&full[2], 1);
+        for (int b = 0; b < 5; ++b) mbar_init(&full[b], 1);
         mbar_fence_init();
-        if (S > 1 && p.rowmax_in == nullptr) mbar_arrive_expect_tx(&full[1], (uint32_t)(S * TC * 4));
+        if (S > 1 && p.rowmax_in == nullptr) mbar_arrive_expect_tx(&full[0], (uint32_t)(S * TC * 4));
         s_flags[0] = 0;
         s_flags[1] = 0;
-        if (nkb > 0) mbar_arrive_expect_tx(&full[0], (uint32_t)nkb * 8192u);
+        if (nkb > 0) mbar_arrive_expect_tx(&full[1], (uint32_t)nkb * 8192u);
     }
     if (tid < TC) { s_max[tid] = 0u; s_outmax[tid] = 0u; }
     if (S > 1) cluster_arrive();   // matched by the wait in front of the first remote store
     __syncthreads();
-    if (tid < 4 && nkb > 0) {
+    // four bulk copies bring one tile's weight slice (per group one contiguous run of nkb k-blocks)
+    auto request_weights = [&](int tile, uint64_t* bar) {
         const int w = tid;
         const int group = swiglu ? (w < 2 ? tile * 2 + w : p.F / GROUP + tile * 2 + (w - 2)) : tile * 4 + w;
-        bulk_g2s(wst + (size_t)w * nkb * 2048, p.Wp + ((size_t)group * KC + (size_t)kb0 * 4) * 512, (uint32_t)nkb * 2048u, &full[0]);
+        bulk_g2s(wst + (size_t)w * nkb * 2048, p.Wp + ((size_t)group * KC + (size_t)kb0 * 4) * 512, (uint32_t)nkb * 2048u, bar);
+    };
+    // channel scales of a tile's outputs (constants)
+    auto stage_channel_scales = [&](int tile) {
+        if (tid < 128) {
+            const int n0 = swiglu ? (tid < 64 ? tile * 64 + tid : p.F + tile * 64 + (tid - 64)) : tile * TILE_N + tid;
+            s_sw[tid] = n0 < p.NG * GROUP ? p.sw[n0] : 0.f;
+        }
+    };
+    if (tid < 4 && nkb > 0) request_weights(tile_first, &full[1]);
+    if (ntile == 2 && tid >= 32 && tid < 36 && nkb > 0) {
+        // the second tile's weights cannot be held yet: bring them as far as L2 so that their copy, requested
+        // after the first tile's contraction, does not wait for DRAM
+        const int w = tid - 32, tile = tile_first + 1;
+        const int group = swiglu ? (w < 2 ? tile * 2 + w : p.F / GROUP + tile * 2 + (w - 2)) : tile * 4 + w;
+        bulk_prefetch_l2(p.Wp + ((size_t)group * KC + (size_t)kb0 * 4) * 512, (uint32_t)nkb * 2048u);
     }
-    // Channel scales of this CTA's outputs are constants too: stage them now.
-    if (tid < 128) {
-        const int n0 = swiglu ? (tid < 64 ? tile * 64 + tid : p.F + tile * 64 + (tid - 64)) : tile * TILE_N + tid;
-        s_sw[tid] = n0 < p.NG * GROUP ? p.sw[n0] : 0.f;
-    }
+    stage_channel_scales(tile_first);
     if (trace) trace[1] = (unsigned long long)(clock64() - c_start);
     pdl_wait();   // the producer of A (and of the row maxima) has finished
     if (trace) trace[2] = (unsigned long long)(clock64() - c_start);
@@ -146,9 +167,9 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
             cluster_wait();
             for (int i = tid; i < S * TC; i += FUSED_THREADS) {
                 const int r = i / TC, t = i - r * TC;
-                st_async_u32(map_to_cta(smem_u32(&inbox_max[rank * TC + t]), (uint32_t)r), s_max[t], map_to_cta(smem_u32(&full[1]), (uint32_t)r));
+                st_async_u32(map_to_cta(smem_u32(&inbox_max[rank * TC + t]), (uint32_t)r), s_max[t], map_to_cta(smem_u32(&full[0]), (uint32_t)r));
             }
-            if (!mbar_wait(&full[1], 0, deadline)) s_flags[1] = 1;
+            if (!mbar_wait(&full[0], 0, deadline)) s_flags[1] = 1;
         }
     }
     if (tid < TC) {
@@ -170,7 +191,7 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
         s_scale[tid] = s;
         s_inv[tid] = inv;
         if (bad) atomicOr(&s_flags[0], bad);
-        if (tile == 0 && rank == 0 && tid < p.M && p.scales_out) p.scales_out[tid] = s;
+        if (blockIdx.x == 0 && rank == 0 && tid < p.M && p.scales_out) p.scales_out[tid] = s;
     }
     __syncthreads();
     if (trace) trace[3] = (unsigned long long)(clock64() - c_start);
@@ -179,7 +200,8 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
     const int Qq = p.epi == EPI_SWIGLU ? 16 : 32;
     const int my_quads = ((rank + 1) * Qq) / S - (rank * Qq) / S;
     if (tid == 0 && S > 1 && !verdict)
-        mbar_arrive_expect_tx(&full[2], (uint32_t)(S * TC * my_quads * 4 * (p.epi == EPI_SWIGLU ? 2 : 1) * 4));
+        for (int i = 0; i < ntile; ++i)
+            mbar_arrive_expect_tx(&full[3 + i], (uint32_t)(S * TC * my_quads * 4 * (p.epi == EPI_SWIGLU ? 2 : 1) * 4));
 
     // ---- 2. quantise the slice into shared memory: xs[unit][token][16 B]
     if (!verdict) {
@@ -192,7 +214,7 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
                 raw_to_float<HALF>(kept[it], v);
                 const uint4 q = quantize16(v, s_inv[tok], k_begin + u * 16, p.K);   // padding rows hold zeros
                 reinterpret_cast<uint4*>(xs)[(size_t)u * TC + tok] = q;
-                if (p.codes_out && tile == 0) reinterpret_cast<uint4*>(p.codes_out)[((size_t)kb0 * 8 + u) * TC + tok] = q;
+                if (p.codes_out && blockIdx.x == 0) reinterpret_cast<uint4*>(p.codes_out)[((size_t)kb0 * 8 + u) * TC + tok] = q;
             }
         }
         for (int idx = tid + FUSED_THREADS * UMAX; idx < items; idx += FUSED_THREADS) {
@@ -206,22 +228,37 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
                 q = quantize16(v, s_inv[tok], k0, p.K);
             }
             reinterpret_cast<uint4*>(xs)[(size_t)u * TC + tok] = q;
-            if (p.codes_out && tile == 0) reinterpret_cast<uint4*>(p.codes_out)[((size_t)kb0 * 8 + u) * TC + tok] = q;
+            if (p.codes_out && blockIdx.x == 0) reinterpret_cast<uint4*>(p.codes_out)[((size_t)kb0 * 8 + u) * TC + tok] = q;
         }
     }
     __syncthreads();
 
     if (trace) trace[4] = (unsigned long long)(clock64() - c_start);
+    const int g8 = lane >> 2, t4 = lane & 3;
+    const int wgroup = warp >> 1, mtile = warp & 1;
+    // Channel ownership in quads of four: rank r finishes quads [r*Q/S, (r+1)*Q/S) of the CTA's
+    // Q quads (gate quads for SwiGLU, whose up partner travels with it); W = widest share.
+    const int Q = swiglu ? 16 : 32;
+    const int q_first = (rank * Q) / S, q_count = ((rank + 1) * Q) / S - q_first;
+    const int QW = (Q + S - 1) / S;                // quads per inbox row half
+    const int W = (swiglu ? 2 : 1) * QW * 4;       // words per token per source rank
+    if (S > 1 && p.rowmax_in != nullptr) cluster_wait();
+
+    // The CTA's column tiles one after the other: the quantised slice is shared, the second tile's weights
+    // are requested into the same shared memory as soon as the first tile's contraction has read them, and
+    // arrive while the first tile's partial sums are exchanged and finished.
+    for (int ti = 0; ti < ntile; ++ti) {
+    if (verdict && ti > 0) break;            // rejected input: nothing was requested for the second tile
+    const int tile = tile_first + ti;
+    int32_t* const inbox_sum = inbox_all + (size_t)ti * TC * 192;
     // ---- 3. contraction: warp w owns the m16 tile (w & 1) of weight group (w >> 1)
     int acc[NT][4], acc2[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) { acc[j][e] = 0; acc2[j][e] = 0; }
-    const int g8 = lane >> 2, t4 = lane & 3;
-    const int wgroup = warp >> 1, mtile = warp & 1;
     // The copies have to land before this CTA may leave, whatever the verdict.
-    if (nkb > 0 && !mbar_wait(&full[0], 0, deadline)) s_flags[1] = 1;
+    if (nkb > 0 && !mbar_wait(&full[1 + ti], 0, deadline)) s_flags[1] = 1;
     for (int s = 0; s < (verdict ? 0 : nkb); ++s) {
         const uint32_t wbase = smem_u32(wst + ((size_t)wgroup * nkb + s) * 2048) + (mtile * 16 + g8) * 16 + t4 * 4;
         const uint32_t xbase = smem_u32(xs + (size_t)s * TC * 128) + g8 * 16 + t4 * 4;
@@ -246,15 +283,14 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[j][e] += acc2[j][e];
 
+    if (ti + 1 < ntile && !verdict) {
+        // every warp has read this tile's weights: fetch the next tile's into the same place
+        __syncthreads();
+        if (tid == 0 && nkb > 0) mbar_arrive_expect_tx(&full[2 + ti], (uint32_t)nkb * 8192u);
+        if (tid < 4 && nkb > 0) request_weights(tile + 1, &full[2 + ti]);
+    }
     if (trace) trace[5] = (unsigned long long)(clock64() - c_start);
     // ---- 4. partial sums to the rank that owns the channel: inbox_sum[source][token][W]
-    // Channel ownership in quads of four: rank r finishes quads [r*Q/S, (r+1)*Q/S) of the CTA's
-    // Q quads (gate quads for SwiGLU, whose up partner travels with it); W = widest share.
-    const int Q = swiglu ? 16 : 32;
-    const int q_first = (rank * Q) / S, q_count = ((rank + 1) * Q) / S - q_first;
-    const int QW = (Q + S - 1) / S;                // quads per inbox row half
-    const int W = (swiglu ? 2 : 1) * QW * 4;       // words per token per source rank
-    if (S > 1 && p.rowmax_in != nullptr) cluster_wait();
     if (!verdict) {
 #pragma unroll
         for (int j = 0; j < NT; ++j)
@@ -267,12 +303,12 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
                 const int local = c - ((owner * Q) / S) * 4 + ((swiglu && ch >= 64) ? QW * 4 : 0);
                 const int word = (rank * TC + tok) * W + local;
                 const int value = acc[j][e] >> 4;                       // exact: sums are multiples of 16
-                if (S > 1) st_async_u32(map_to_cta(smem_u32(&inbox_sum[word]), (uint32_t)owner), (uint32_t)value, map_to_cta(smem_u32(&full[2]), (uint32_t)owner));
+                if (S > 1) st_async_u32(map_to_cta(smem_u32(&inbox_sum[word]), (uint32_t)owner), (uint32_t)value, map_to_cta(smem_u32(&full[3 + ti]), (uint32_t)owner));
                 else inbox_sum[word] = value;
             }
     }
     if (S > 1) {
-        if (!verdict && !mbar_wait(&full[2], 0, deadline)) s_flags[1] = 1;
+        if (!verdict && !mbar_wait(&full[3 + ti], 0, deadline)) s_flags[1] = 1;
     } else __syncthreads();
     if (trace) trace[6] = (unsigned long long)(clock64() - c_start);
 
@@ -328,17 +364,23 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
                 }
             }
         }
-        if (swiglu && p.rowmax_out) {
-            __syncthreads();
-            if (tid < p.M && s_outmax[tid]) atomicMax(&p.rowmax_out[tid], s_outmax[tid]);
-        }
+    }
+    if (ti + 1 < ntile) {
+        __syncthreads();                      // the channel scales of this tile have been used by everybody
+        stage_channel_scales(tile + 1);
+        __syncthreads();
+    }
+    }   // tiles of this CTA
+    if (!verdict && swiglu && p.rowmax_out) {
+        __syncthreads();
+        if (tid < p.M && s_outmax[tid]) atomicMax(&p.rowmax_out[tid], s_outmax[tid]);
     }
 
     // ---- bookkeeping by one thread per CTA
     if (trace) trace[7] = global_ns();
     if (tid == 0) {
         if (s_flags[1]) atomicExch(&p.status->device_error, 1);
-        if (tile == 0 && rank == 0) p.status->bad_input = verdict;
+        if (blockIdx.x == 0 && rank == 0) p.status->bad_input = verdict;
         if (p.rowmax_in != nullptr) {
             // Every CTA has read the row maxima by now; the last one to get here clears
             // them for the next SwiGLU epilogue.  The ticket counter wraps by itself.
@@ -350,7 +392,7 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
     }
 }
 
-size_t gemm_fused_smem_bytes(int tokens_per_cta, int stages) { return fused_smem_bytes(tokens_per_cta, stages); }
+size_t gemm_fused_smem_bytes(int tokens_per_cta, int stages, int tiles_per_cta) { return fused_smem_bytes(tokens_per_cta, stages, tiles_per_cta); }
 
 template <int NT, bool HALF>
 static cudaError_t launch_fused_inst(const FusedParams& p, cudaStream_t stream, bool pdl)
@@ -359,16 +401,16 @@ static cudaError_t launch_fused_inst(const FusedParams& p, cudaStream_t stream, 
     auto kernel = gemm_fused_kernel<NT, HALF>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)fused_smem_bytes(TC, FUSED_MAX_STAGES));
+        const size_t most = fused_smem_bytes(TC, FUSED_MAX_STAGES, 2) < FUSED_SMEM_LIMIT ? fused_smem_bytes(TC, FUSED_MAX_STAGES, 2) : FUSED_SMEM_LIMIT;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
         if (e != cudaSuccess) return e;
         configured = true;
     }
     const int tiles = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : (p.N + TILE_N - 1) / TILE_N;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)tiles, (unsigned)p.split, 1);
+    cfg.gridDim = dim3((unsigned)((tiles + p.tiles_per_cta - 1) / p.tiles_per_cta), (unsigned)p.split, 1);
     cfg.blockDim = dim3(FUSED_THREADS);
-    cfg.dynamicSmemBytes = fused_smem_bytes(TC, p.stages);
+    cfg.dynamicSmemBytes = fused_smem_bytes(TC, p.stages, p.tiles_per_cta);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int n = 0;
@@ -389,7 +431,8 @@ static cudaError_t launch_fused_inst(const FusedParams& p, cudaStream_t stream, 
 
 cudaError_t launch_gemm_fused(const FusedParams& p, int tokens_per_cta, cudaStream_t stream, bool pdl)
 {
-    if (p.split < 1 || p.split > 8 || p.M > tokens_per_cta ||
+    if (p.split < 1 || p.split > 8 || p.M > tokens_per_cta || p.tiles_per_cta < 1 || p.tiles_per_cta > 2 ||
+        fused_smem_bytes(tokens_per_cta, p.stages, p.tiles_per_cta) > FUSED_SMEM_LIMIT ||
         p.stages > FUSED_MAX_STAGES || p.stages * p.split < p.KB || (long long)p.KB * KBLOCK > 131072)
         return cudaErrorInvalidValue;
     switch (tokens_per_cta) {

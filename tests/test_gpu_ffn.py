@@ -282,3 +282,24 @@ def test_codes_entry_plain_matrix_and_errors(gpu, oracle):
     assert ws.finish() == 0
     assert np.array_equal(bits(dC.cpu().numpy()), bits(dC0.cpu().numpy()))
     free(ws, w)
+
+
+@pytest.mark.parametrize("case", [(1, 1057, 992, 192), (8, 2304, 1600, 300), (20, 479, 192, 257)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_ffn_single_kernel_two_tiles_per_cta(gpu, oracle, monkeypatch, case):
+    """SwiGLU epilogue, collected row maxima and their reuse with two column tiles per CTA."""
+    _, dom, _ = gpu
+    monkeypatch.setenv("RK_NPU_B200_VARIANT", "3")
+    monkeypatch.setenv("RK_NPU_B200_TILES_PER_CTA", "2")
+    M, K, F, N = case
+    Bg, sg = make_weights(K, 2 * F, seed=F + 3)
+    Bd, sd = make_weights(F, N, seed=N + 3)
+    wg, wd, gu, dn = build(dom, M, K, F, N, Bg, sg, Bd, sd)
+    for rep in range(2):
+        A = make_activations(M, K, seed=rep, dtype="f32")
+        middle, C = np.zeros((M, F), np.float32), np.zeros((M, N), np.float32)
+        assert rk.run_ffn_f32(gu, wg, dn, wd, A, middle, C, None) == 0
+        ref = oracle.ffn(A, Bg, sg, Bd, sd, mode=1)
+        assert np.array_equal(bits(middle), bits(ref["middle"]))
+        assert np.array_equal(bits(C), bits(ref["C"]))
+    free(gu, dn, wg, wd)

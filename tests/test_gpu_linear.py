@@ -423,3 +423,41 @@ def test_mid_batch_schedules_agree(gpu, oracle, monkeypatch, variant, shape):
         assert np.array_equal(acc, ref_acc)
         assert np.array_equal(bits(out), bits(ref))
         assert np.array_equal(bits(out2), bits(ref))
+
+
+# The single-kernel path with two column tiles per CTA (chosen by itself for launches that would fill more than
+# half of the GPU's shared memory; forced here on small shapes): even, odd and single tile counts, every
+# cluster size, both input types, a rejected input (nothing may be left waiting for the second tile).
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (8, 2304, 1000), (13, 1441, 385), (8, 1057, 257), (16, 640, 129),
+                                   (32, 1100, 2049), (5, 513, 64)], ids=lambda s: "x".join(map(str, s)))
+def test_single_kernel_two_tiles_per_cta(gpu, oracle, monkeypatch, shape):
+    _, dom, _ = gpu
+    M, K, N = shape
+    monkeypatch.setenv("RK_NPU_B200_VARIANT", "3")
+    monkeypatch.setenv("RK_NPU_B200_TILES_PER_CTA", "2")
+    B, sw = make_weights(K, N, seed=5 * K + N)
+    for dtype in ("f16", "f32"):
+        A = make_activations(M, K, seed=M + K, dtype=dtype)
+        rc, ref, ref_acc, _ = oracle.linear(A, B, sw)
+        assert rc == 0
+        for split in (0, 1, 2, 3, 8):
+            kb = (K + 127) // 128
+            if split and (kb < split or (kb + split - 1) // split > 16):     # at most 16 k-blocks per CTA
+                continue
+            out, acc = run_case(dom, oracle, A, B, sw, split=split)
+            assert np.array_equal(acc, ref_acc)
+            assert np.array_equal(bits(out), bits(ref))
+    # NaN input: PARAM without a timeout, then the same workspace computes again
+    w = rk.Weights(dom, B, sw)
+    ws = rk.Workspace(dom, rk.default_config(M, N, K))
+    A = make_activations(M, K, seed=1, dtype="f32")
+    bad = A.copy()
+    bad[M - 1, K // 2] = np.nan
+    out = np.zeros((M, N), np.float32)
+    t = capi.W4A8Timings()
+    assert ws.run_f32(w, bad, out, t) == capi.RK_NPU_ERR_PARAM
+    assert t.total_us < 100e3          # far below the 500 ms a bounded wait would take to give up
+    assert ws.run_f32(w, A, out) == 0
+    assert np.array_equal(bits(out), bits(oracle.linear(A, B, sw)[1]))
+    ws.free()
+    w.free()
