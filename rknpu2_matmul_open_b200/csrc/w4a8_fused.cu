@@ -107,13 +107,6 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
         }
     };
     if (tid < 4 && nkb > 0) request_weights(tile_first, &full[1]);
-    if (ntile == 2 && tid >= 32 && tid < 36 && nkb > 0) {
-        // the second tile's weights cannot be held yet: bring them as far as L2 so that their copy, requested
-        // after the first tile's contraction, does not wait for DRAM
-        const int w = tid - 32, tile = tile_first + 1;
-        const int group = swiglu ? (w < 2 ? tile * 2 + w : p.F / GROUP + tile * 2 + (w - 2)) : tile * 4 + w;
-        bulk_prefetch_l2(p.Wp + ((size_t)group * KC + (size_t)kb0 * 4) * 512, (uint32_t)nkb * 2048u);
-    }
     stage_channel_scales(tile_first);
     if (trace) trace[1] = (unsigned long long)(clock64() - c_start);
     pdl_wait();   // the producer of A (and of the row maxima) has finished

@@ -86,12 +86,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_global,
                  : "memory");
 }
 
-// Ask for a run of global memory to be brought into L2 (no destination, nothing to wait for).
-// Address 16-byte aligned, size a multiple of 16.
-__device__ __forceinline__ void bulk_prefetch_l2(const void* src_global, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_global), "r"(bytes) : "memory");
-}
-
 // ---- distributed shared memory: a 32-bit store into a peer CTA's shared memory that also counts
 // four bytes on a barrier in that CTA.  Data and signal travel together, so the receiver needs no
 // cluster-wide barrier: it waits on its own mbarrier for the bytes it expects.
