@@ -645,6 +645,8 @@ def _ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_act
             code_parts = torch.empty((world, M, f1 - f0), dtype=torch.int8, device=dev)
             out_parts = torch.empty((world, M, n1 - n0), dtype=torch.float32, device=dev)
             out_full = torch.empty((M, N), dtype=torch.float32, device=dev)
+            mid_parts = torch.empty((world, M, f1 - f0), dtype=torch.float32, device=dev)
+            mid_full = torch.empty((M, F), dtype=torch.float32, device=dev)
 
         def step(codes_exchange=even):
             if codes_exchange:
@@ -659,10 +661,19 @@ def _ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_act
                 out_full.view(M, world, n1 - n0).copy_(out_parts.permute(1, 0, 2))
                 return out_full
             rc = gu.enqueue_swiglu_f32(wg, dA, dMid, stream.cuda_stream)
-            middle = gather_columns(dMid, F)                       # [M, F] on every rank
-            rc = rc or dn.enqueue_f32(wd, middle, dC, stream.cuda_stream)
+            if even:   # equal shards: one collective into [world, M, cols] and one strided copy into [M, world * cols]
+                dist.all_gather_into_tensor(mid_parts, dMid)
+                mid_full.view(M, world, f1 - f0).copy_(mid_parts.permute(1, 0, 2))
+                middle = mid_full
+            else:
+                middle = gather_columns(dMid, F)                   # [M, F] on every rank, shards padded to the widest
+            rc = rc or dn.enqueue_f32(wd, middle, dC, stream.cuda_stream)   # rescans the gathered rows: same maxima
             if rc:
                 raise RuntimeError(f"enqueue failed: {rc}")
+            if even:
+                dist.all_gather_into_tensor(out_parts, dC)
+                out_full.view(M, world, n1 - n0).copy_(out_parts.permute(1, 0, 2))
+                return out_full
             return gather_columns(dC, N)
 
         # Both exchanges are timed where both apply: with few tokens the extra all-reduce of the code exchange
