@@ -128,9 +128,19 @@ int rk_npu_b200_w4a8_trace_read(rk_npu_w4a8_workspace *workspace, unsigned long 
  * any stream capture starts.  All calls share the one array, which keeps the previous call's
  * contents (the parts that must start at zero are cleared on the stream first): two calls
  * whose GPU work overlaps -- different streams, no ordering between them -- race on it.
- * A row of dA holding NaN or Inf leaves dC unwritten.  Returns RK_NPU_OK once queued. */
+ * A row of dA holding NaN or Inf leaves dC unwritten, and a bounded wait inside the kernels that
+ * ran out leaves dC undefined; neither is known when the call returns (RK_NPU_OK once queued):
+ * ask rk_npu_b200_w4a8_static_status after synchronising.  The caller's current CUDA device is
+ * the same after the call as before it. */
 int rk_npu_b200_w4a8_enqueue_f16_static(const rk_npu_w4a8_weights *weights, const uint16_t *dA, uint16_t *dC, int M,
                                         void *cuda_stream);
+/* Verdict of the last rk_npu_b200_w4a8_enqueue_f16_static call on the weights' GPU, read from the
+ * same fixed array (no allocation; a 16-byte blocking copy).  Call it after synchronising the stream
+ * the linear was queued on.  *bad_input: 1 when a row of dA held NaN or Inf (dC was not written);
+ * *device_error: 1 when a bounded wait ran out (dC undefined).  Returns RK_NPU_OK, RK_NPU_ERR_PARAM
+ * (bad input) or RK_NPU_ERR_SUBMIT (device error or the copy failed).  No counterpart in the
+ * original project. */
+int rk_npu_b200_w4a8_static_status(const rk_npu_w4a8_weights *weights, int *bad_input, int *device_error);
 
 /* Kernels this workspace has launched since creation (for launch accounting). */
 uint64_t rk_npu_b200_w4a8_launch_count(const rk_npu_w4a8_workspace *workspace);

@@ -199,6 +199,7 @@ _SIGNATURES = {
     "rk_npu_b200_w4a8_last_quant": (C.c_int, [_P, _P, _P]),
     "rk_npu_b200_w4a8_set_schedule": (C.c_int, [_P, C.c_int, C.c_int]),
     "rk_npu_b200_w4a8_enqueue_f16_static": (C.c_int, [_P, _P, _P, C.c_int, _P]),
+    "rk_npu_b200_w4a8_static_status": (C.c_int, [_P, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "rk_npu_b200_w4a8_launch_count": (C.c_uint64, [_P]),
     "rk_npu_b200_w4a8_trace_enable": (C.c_int, [_P, C.c_int]),
     "rk_npu_b200_w4a8_trace_read": (C.c_int, [_P, _P, C.c_int]),

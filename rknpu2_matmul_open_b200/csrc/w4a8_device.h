@@ -21,10 +21,27 @@
 //   consume.  Replaces the reference's MSD-split A[K/32, 2*rows, 32] int4 layout
 //   (src/rk_npu_w4a8_quant.cpp:87-135): int8 MMA is native here so no split is needed.
 #pragma once
+#include <atomic>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace rkb200 {
+
+// A function attribute such as the dynamic shared-memory opt-in belongs to one device.  A process may
+// open contexts on several GPUs, so "already set" is remembered per CUDA ordinal (one bit each; ordinals
+// beyond 63 simply set the attribute on every launch).
+struct PerDeviceOnce {
+    std::atomic<unsigned long long> done{0};
+    bool needed(int& device) const
+    {
+        if (cudaGetDevice(&device) != cudaSuccess) { device = -1; return true; }
+        return device < 0 || device >= 64 || !(done.load(std::memory_order_acquire) & (1ull << device));
+    }
+    void mark(int device)
+    {
+        if (device >= 0 && device < 64) done.fetch_or(1ull << device, std::memory_order_release);
+    }
+};
 
 constexpr int KBLOCK = 128;        // reduction elements per pipeline stage
 constexpr int GROUP = 32;          // output channels per weight group

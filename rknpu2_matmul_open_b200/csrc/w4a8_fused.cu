@@ -392,12 +392,13 @@ static cudaError_t launch_fused_inst(const FusedParams& p, cudaStream_t stream, 
 {
     constexpr int TC = 8 * NT;
     auto kernel = gemm_fused_kernel<NT, HALF>;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;
+    int configured_device = -1;
+    if (configured.needed(configured_device)) {
         const size_t most = fused_smem_bytes(TC, FUSED_MAX_STAGES, 2) < FUSED_SMEM_LIMIT ? fused_smem_bytes(TC, FUSED_MAX_STAGES, 2) : FUSED_SMEM_LIMIT;
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured.mark(configured_device);
     }
     const int tiles = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : (p.N + TILE_N - 1) / TILE_N;
     cudaLaunchConfig_t cfg = {};

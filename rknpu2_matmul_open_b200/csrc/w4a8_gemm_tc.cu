@@ -355,8 +355,9 @@ cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl)
     if (p.T < 16 || p.T > 256 || p.T % 16 || !gemm_tc_supported(p)) return cudaErrorInvalidValue;
     const bool pair = p.pair != 0;
     if (pair && p.T != 128) return cudaErrorInvalidValue;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;
+    int configured_device = -1;
+    if (configured.needed(configured_device)) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)(tc_smem_bytes(256, TC_STAGES, 256) > tc_smem_bytes(128, TC_STAGES_DEEP, 128)
                                                        ? tc_smem_bytes(256, TC_STAGES, 256) : tc_smem_bytes(128, TC_STAGES_DEEP, 128)));
@@ -364,7 +365,7 @@ cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl)
             e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)tc_smem_bytes(128, TC_STAGES_PAIR, 256));
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured.mark(configured_device);
     }
     const int tiles = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : (p.N + TILE_N - 1) / TILE_N;
     cudaLaunchConfig_t cfg = {};

@@ -464,7 +464,12 @@ bool gemm_tc_persist_supported(const GemmParams& p)
 cudaError_t launch_gemm_tc_persist(const GemmParams& p, cudaStream_t stream, bool pdl)
 {
     if (!gemm_tc_persist_supported(p)) return cudaErrorInvalidValue;
-    static int max_clusters = 0;
+    static PerDeviceOnce configured;
+    static int clusters_of_device[64] = {};   // resident CTA pairs, per CUDA ordinal
+    int device = -1;
+    int max_clusters = 0;
+    const bool setup = configured.needed(device);
+    if (!setup) max_clusters = clusters_of_device[device];
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(PS_THREADS);
     cfg.dynamicSmemBytes = PS_SMEM_BYTES;
@@ -474,7 +479,7 @@ cudaError_t launch_gemm_tc_persist(const GemmParams& p, cudaStream_t stream, boo
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    if (!max_clusters) {
+    if (setup || !max_clusters) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PS_SMEM_BYTES);
         if (e != cudaSuccess) return e;
         // how many CTA pairs can be resident at once: the grid is exactly that many
@@ -485,6 +490,7 @@ cudaError_t launch_gemm_tc_persist(const GemmParams& p, cudaStream_t stream, boo
         e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_persist_kernel, &cfg);
         if (e != cudaSuccess || n < 1) { cudaGetLastError(); int dev = 0, sms = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); n = sms / 2; }
         max_clusters = n;
+        if (device >= 0 && device < 64) { clusters_of_device[device] = n; configured.mark(device); }
     }
     const int tiles_n = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : (p.N + TILE_N - 1) / TILE_N;
     const int total = ((tiles_n + 1) / 2) * ((p.M + PS_TOK - 1) / PS_TOK);

@@ -448,12 +448,13 @@ static cudaError_t launch_mma_inst(const GemmParams& p, cudaStream_t stream, boo
 {
     constexpr int TC = 8 * NT;
     const size_t smem = mma_smem_bytes(TC);
-    static bool configured = false;
+    static PerDeviceOnce configured;
+    int configured_device = -1;
     auto kernel = gemm_mma_kernel<NT, BIGK>;
-    if (!configured) {
+    if (configured.needed(configured_device)) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured.mark(configured_device);
     }
     const int tiles = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : (p.N + TILE_N - 1) / TILE_N;
     cudaLaunchConfig_t cfg = {};
@@ -529,6 +530,44 @@ int static_scratch(int device, unsigned char** out)
 }
 } // namespace
 
+namespace {
+// Makes `device` current for the duration of a call and restores what the caller had.
+struct DeviceScope {
+    int previous = -1;
+    bool ok = false;
+    explicit DeviceScope(int device)
+    {
+        if (cudaGetDevice(&previous) != cudaSuccess) { cudaGetLastError(); previous = -1; }
+        ok = previous == device || cudaSetDevice(device) == cudaSuccess;
+        if (!ok) cudaGetLastError();
+        if (previous == device) previous = -1;
+    }
+    ~DeviceScope() { if (previous >= 0) cudaSetDevice(previous); }
+};
+} // namespace
+
+// What the last allocation-free linear on `weights`' GPU left in the array's status block.  Copies 16 bytes
+// into the caller's variables; allocates nothing.  The caller has synchronised the stream of that call.
+extern "C" int rk_npu_b200_w4a8_static_status(const rk_npu_w4a8_weights* weights, int* bad_input, int* device_error)
+{
+    using namespace rkb200;
+    if (!weights || !bad_input || !device_error) return RK_NPU_ERR_PARAM;
+    const rk_npu_ctx* ctx = weights->domain->ctx;
+    DeviceScope scope(ctx->device);
+    if (!scope.ok) return RK_NPU_ERR_SUBMIT;
+    unsigned char* base = nullptr;
+    const int rc = static_scratch(ctx->device, &base);
+    if (rc) return rc;
+    Status host{};
+    if (cudaMemcpy(&host, base + STATIC_CODE_BYTES + 1024, sizeof(Status), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return RK_NPU_ERR_SUBMIT;
+    }
+    *bad_input = host.bad_input;
+    *device_error = host.device_error;
+    return host.device_error ? RK_NPU_ERR_SUBMIT : host.bad_input ? RK_NPU_ERR_PARAM : RK_NPU_OK;
+}
+
 extern "C" int rk_npu_b200_w4a8_enqueue_f16_static(const rk_npu_w4a8_weights* weights, const uint16_t* dA, uint16_t* dC,
                                                    int M, void* cuda_stream)
 {
@@ -540,7 +579,8 @@ extern "C" int rk_npu_b200_w4a8_enqueue_f16_static(const rk_npu_w4a8_weights* we
     // sizes beyond the fixed array are refused, never truncated
     if (M > STATIC_MAX_TOKENS || code_bytes > STATIC_CODE_BYTES) return RK_NPU_ERR_NOMEM;
     const rk_npu_ctx* ctx = weights->domain->ctx;
-    if (cudaSetDevice(ctx->device) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+    DeviceScope scope(ctx->device);   // the caller's current device is put back on return
+    if (!scope.ok) return RK_NPU_ERR_SUBMIT;
     unsigned char* base = nullptr;
     const int rc = static_scratch(ctx->device, &base);
     if (rc) return rc;

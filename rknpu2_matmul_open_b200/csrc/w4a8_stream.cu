@@ -450,11 +450,12 @@ cudaError_t launch_gemm_stream(const GemmParams& p, int sm_count, cudaStream_t s
 {
     if ((p.T != 16 && p.T != 32 && p.T != 64 && p.T != 128) || p.M > p.T || (long long)p.KB * KBLOCK > 131072 || !p.partials || !p.counts)
         return cudaErrorInvalidValue;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;
+    int configured_device = -1;
+    if (configured.needed(configured_device)) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ts_smem_bytes(128) > ts_smem_bytes(32) ? ts_smem_bytes(128) : ts_smem_bytes(32)));
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured.mark(configured_device);
     }
     const int tiles = p.epi == EPI_SWIGLU ? (p.F + 63) / 64 : (p.N + TILE_N - 1) / TILE_N;
     const long long total = (long long)tiles * ((p.KB + ts_kps(p.T) - 1) / ts_kps(p.T));

@@ -17,6 +17,18 @@ def _free_port() -> int:
 
 
 def _rank_main(rank: int, world: int, port: int, shape, out_queue):
+    """Child process body: any exception goes to the parent through the queue so it fails fast."""
+    try:
+        _rank_body(rank, world, port, shape, out_queue)
+    except BaseException as exc:   # noqa: BLE001 -- reported, then the process ends
+        import traceback
+        out_queue.put(("error", rank, f"{type(exc).__name__}: {exc}\n{traceback.format_exc()}"))
+        raise
+
+
+def _rank_body(rank: int, world: int, port: int, shape, out_queue):
+    import datetime
+
     import torch
     import torch.distributed as dist
 
@@ -27,7 +39,8 @@ def _rank_main(rank: int, world: int, port: int, shape, out_queue):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    # a short collective timeout: a rank that died makes the others' next collective fail instead of waiting
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=120))
     M, K, F, N = shape
     ctx = rk.Context(f"cuda:{rank}")
     dom = ctx.domain(0)
@@ -78,7 +91,7 @@ def _rank_main(rank: int, world: int, port: int, shape, out_queue):
         assert gu.finish() == 0 and dn.finish() == 0
         ffn_codes = ffn_codes.cpu().numpy()
     if rank == 0:
-        out_queue.put((full.cpu().numpy().view(np.uint16), middle.cpu().numpy(), ffn.cpu().numpy(), ffn_codes))
+        out_queue.put(("ok", full.cpu().numpy().view(np.uint16), middle.cpu().numpy(), ffn.cpu().numpy(), ffn_codes))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -96,13 +109,26 @@ def test_sharded_linear_and_ffn_are_bit_exact(oracle, shape):
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, shape, queue)) for r in range(world)]
-    for p in procs:
-        p.start()
-    got = queue.get(timeout=300)
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, shape, queue), daemon=True) for r in range(world)]
+    try:
+        for p in procs:
+            p.start()
+        got = queue.get(timeout=300)
+        assert got[0] == "ok", f"rank {got[1]} failed: {got[2]}"
+        got = got[1:]
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    finally:
+        # whatever happened, no child stays behind on a GPU
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        for p in procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=10)
     M, K, F, N = shape
     B, sw = make_weights(K, N, seed=5)
     A = make_activations(M, K, seed=5, dtype="f16")

@@ -1,14 +1,15 @@
-"""The allocation-free linear (rk_npu_b200_w4a8_enqueue_f16_static) against the ordinary
-workspace entry point.
+"""The allocation-free linear (rk_npu_b200_w4a8_enqueue_f16_static) against the oracle and the
+ordinary workspace entry point.
 
 The entry point serves callers that must not allocate while they run -- an engine that fixed
 its device memory budget at start-up, a plugin inside a latency-critical loop -- so it keeps
 its scratch (activation codes, token scales, status) in an array inside the library image
 instead of a workspace.  The array is shared by all calls and keeps old contents, so the
 test calls it twice in a row, with different batch sizes and inputs, and expects each result
-to equal (bit for bit, the tolerance of the other GPU tests) what rk_npu_w4a8_run_f16
-produces.  It also checks that sizes beyond the array are refused and that nothing was
-allocated through the domain.  The file sorts last so that a stop-at-first-failure run has
+to equal (bit for bit, the tolerance of the other GPU tests) both the CPU oracle's linear and
+what rk_npu_w4a8_run_f16 produces.  It also checks that sizes beyond the array are refused, that
+nothing was allocated through the domain, and that the verdict of a call (a NaN row leaves the
+output unwritten) can be read back without allocating.  The file sorts last so that a stop-at-first-failure run has
 already executed every other test.
 """
 import ctypes as C
@@ -23,9 +24,10 @@ from rknpu2_matmul_open_b200 import capi
 pytestmark = pytest.mark.gpu
 
 
-def test_static_scratch_linear_matches_workspace_linear_twice():
+def test_static_scratch_linear_matches_workspace_linear_twice(oracle):
     import torch
     lib = capi.load()
+    bad, err = C.c_int(-1), C.c_int(-1)
     ctx = rk.Context("cuda:0")
     dom = ctx.domain(3)
     K, N = 1057, 385
@@ -42,6 +44,7 @@ def test_static_scratch_linear_matches_workspace_linear_twice():
         rc = lib.rk_npu_b200_w4a8_enqueue_f16_static(w.handle, dA.data_ptr(), dC.data_ptr(), M, stream.cuda_stream)
         assert rc == 0
         stream.synchronize()
+        assert lib.rk_npu_b200_w4a8_static_status(w.handle, C.byref(bad), C.byref(err)) == 0 and (bad.value, err.value) == (0, 0)
         results.append((A, dC.cpu().numpy().view(np.uint16)))
     after = dom.memory_stats()
     assert (after.creates, after.live_bytes) == (before.creates, before.live_bytes)   # nothing allocated on the way
@@ -51,7 +54,21 @@ def test_static_scratch_linear_matches_workspace_linear_twice():
         ref = np.zeros((M, N), np.uint16)
         assert ws.run_f16(w, A, ref) == 0
         ws.free()
-        assert np.array_equal(got, ref)
+        rc, want, _, _ = oracle.linear(A, B, sw)
+        assert rc == 0 and np.array_equal(got, want)        # the CPU oracle
+        assert np.array_equal(got, ref)                     # and the workspace entry point
+    # a NaN row: output untouched, and the verdict can be read back (still without allocating)
+    A = make_activations(4, K, seed=9, dtype="f16")
+    A[2, 5] = 0x7E00
+    dA = torch.from_numpy(A.view(np.int16)).cuda()
+    dC = torch.full((4, N), 0x5555, dtype=torch.int16, device="cuda")
+    torch.cuda.synchronize()
+    assert lib.rk_npu_b200_w4a8_enqueue_f16_static(w.handle, dA.data_ptr(), dC.data_ptr(), 4, stream.cuda_stream) == 0
+    stream.synchronize()
+    assert lib.rk_npu_b200_w4a8_static_status(w.handle, C.byref(bad), C.byref(err)) == capi.RK_NPU_ERR_PARAM
+    assert (bad.value, err.value) == (1, 0) and int(dC.min()) == 0x5555 and int(dC.max()) == 0x5555
+    after = dom.memory_stats()
+    assert (after.creates, after.live_bytes) == (before.creates, before.live_bytes)
     # beyond the fixed array: refused with a clear code, output untouched
     dA = torch.zeros((33, K), dtype=torch.int16, device="cuda")
     dC = torch.full((33, N), 7, dtype=torch.int16, device="cuda")
