@@ -305,6 +305,34 @@ int enqueue(const Call& c)
     const int F = c.epi == EPI_SWIGLU ? cfg.N / 2 : 0;
     const int tiles = c.epi == EPI_SWIGLU ? (F + 63) / 64 : (cfg.N + TILE_N - 1) / TILE_N;
     const unsigned long long timeout_ns = (unsigned long long)cfg.timeout_ms * 1000000ull;
+    if (ws.variant == 5 && !c.codes_in) {
+        // One kernel, whole-K CTAs: scan + quantise (shared by a cluster) + GEMM + epilogue.
+        DecodeParams d{};
+        d.Wp = c.w->packed;
+        d.A = c.dA;
+        d.sw = c.w->scales;
+        d.out = c.dOut;
+        d.rowmax_out = c.rowmax_out;
+        d.rowmax_in = c.rowmax_in;
+        d.scales_out = ws.scales;
+        d.codes_out = c.keep_codes ? ws.codes : nullptr;
+        d.status = ws.status;
+        d.M = cfg.M; d.N = cfg.N; d.K = cfg.K;
+        d.KB = ws.KB; d.NG = c.w->NG; d.F = F; d.epi = c.epi;
+        d.half = c.half ? 1 : 0;
+        const bool swiglu = c.epi == EPI_SWIGLU;
+        d.cluster = ws.split_override ? ws.split_override : gemm_decode_cluster(cfg.M, ws.KB);
+        d.ring = gemm_decode_ring(cfg.M, ws.KB, swiglu);
+        const int slot = d.cluster == 1 ? 0 : d.cluster == 2 ? 1 : d.cluster == 4 ? 2 : 3;
+        d.ctas = gemm_decode_ctas(swiglu ? F / GROUP : (cfg.N + GROUP - 1) / GROUP, d.cluster, ws.decode_cap[slot]);
+        d.timeout_ns = timeout_ns;
+        d.trace = ws.trace;
+        if (c.events) cudaEventRecord(c.events[1], c.stream);
+        if (launch_gemm_decode(d, c.stream, pdl) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+        if (c.events) cudaEventRecord(c.events[2], c.stream);
+        ws.launches.fetch_add(1, std::memory_order_relaxed);
+        return RK_NPU_OK;
+    }
     if (ws.variant == 3 && !c.codes_in) {
         // One kernel: scan + quantise + GEMM + epilogue.
         FusedParams f{};
@@ -392,7 +420,7 @@ int enqueue(const Call& c)
         err = launch_gemm_stream(g, ws.domain->ctx->sm_count, c.stream, pdl);
     } else {
         // (a single-kernel workspace given codes runs the ring GEMM; its split override may be odd, so it is not used here)
-        g.split = ws.variant == 3 ? pick_split_auto(ws, tiles, (cfg.M + ws.TC - 1) / ws.TC)
+        g.split = (ws.variant == 3 || ws.variant == 5) ? pick_split_auto(ws, tiles, (cfg.M + ws.TC - 1) / ws.TC)
                                   : pick_split(ws, tiles, (cfg.M + ws.TC - 1) / ws.TC);
         err = launch_gemm_mma(g, ws.TC, c.stream, pdl);
     }
@@ -845,6 +873,9 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
     // tokens the tcgen05 streaming kernel (4) is opt-in: its time does not depend on the batch
     // size, but it only overtakes the ring at 32 tokens.
     const bool fused_best = fused_ok && cfg->M <= 8 && (long long)cfg->K * cfg->N / 2 <= (24ll << 20);
+    // Up to eight tokens: the decode kernel (5), whose CTAs own whole output channels over all of K, so a
+    // launch has a single exchange (the int8 codes inside a cluster) instead of the two of the split-K kernel (3).
+    const bool decode_ok = gemm_decode_supported(cfg->M, cfg->K);
     // 33..128 tokens: the per-tile tcgen05 kernel has one CTA per 128 output channels; when that is less than
     // half the SMs and K is long, the streaming kernel (all SMs, K split between CTAs) is faster.
     const bool stream_best = stream_ok && cfg->M > 32 && cfg->K >= 8192 &&
@@ -854,8 +885,9 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
     // pay for combining partial tiles (11008 -> 4096 at 128 tokens: 33 us against 44 and 47 us).
     const bool ring_best = cfg->M > 32 && cfg->M <= 128 &&
                            (long long)((cfg->N + TILE_N - 1) / TILE_N) * ((cfg->M + 31) / 32) <= ctx->sm_count;
-    int variant = ring_best ? 1 : (cfg->M > 32 && stream_best) ? 4 : (cfg->M > 32 && tc_ok) ? 2 : fused_best ? 3 : 1;
-    if (forced == 1 || (forced == 2 && tc_ok) || (forced == 3 && fused_ok) || (forced == 4 && stream_ok)) variant = forced;
+    int variant = decode_ok ? 5 : ring_best ? 1 : (cfg->M > 32 && stream_best) ? 4 : (cfg->M > 32 && tc_ok) ? 2 : fused_best ? 3 : 1;
+    if (forced == 1 || (forced == 2 && tc_ok) || (forced == 3 && fused_ok) || (forced == 4 && stream_ok) || (forced == 5 && decode_ok))
+        variant = forced;
     ws->variant = variant;
     if (const char* e = std::getenv("RK_NPU_B200_TILES_PER_CTA")) {   // experiments and tests: 1 or 2, else automatic
         const int v = std::atoi(e);
@@ -872,6 +904,8 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
         ws->TC = cfg->M <= 8 ? 8 : cfg->M <= 16 ? 16 : 32;
         ws->T = ws->TC;
     }
+    if (variant == 5)
+        for (int i = 0; i < 4; ++i) ws->decode_cap[i] = gemm_decode_resident_ctas(1 << i, 227 * 1024, ctx->sm_count);
     const size_t Mp = size_t(align_up(cfg->M, ws->pair ? 256 : ws->T));
     ws->codes_bytes = Mp * size_t(ws->KB) * KBLOCK;
     const int out_cols = cfg->N;
@@ -1130,7 +1164,7 @@ extern "C" int rk_npu_b200_w4a8_last_quant(rk_npu_w4a8_workspace* ws, float* sca
 
 extern "C" int rk_npu_b200_w4a8_set_schedule(rk_npu_w4a8_workspace* ws, int variant, int split_k)
 {
-    if (!ws || variant < 0 || variant > 4 || split_k < 0 || split_k > 8) return RK_NPU_ERR_PARAM;
+    if (!ws || variant < 0 || variant > 5 || split_k < 0 || split_k > 8) return RK_NPU_ERR_PARAM;
     if (ws->variant != 3 && split_k != 0 && split_k != 1 && split_k != 2 && split_k != 4 && split_k != 8) return RK_NPU_ERR_PARAM;
     if (variant != 0 && variant != ws->variant) return RK_NPU_ERR_PARAM;   // the code layout is fixed at creation
     if (ws->variant == 3 && split_k && (ws->KB + split_k - 1) / split_k > FUSED_MAX_STAGES) return RK_NPU_ERR_PARAM;

@@ -1,0 +1,513 @@
+// w4a8_decode.cu -- single-kernel W4A8 linear for up to eight tokens (decode) on sm_100a.
+//
+// One launch does what the reference does in three stages (scan + quantise, src/
+// rk_npu_w4a8_quant.cpp:52-135; contraction; reconstruct + dequantise / SwiGLU, src/
+// rk_npu_w4a8_output.cpp:35-161, src/rk_npu_w4a8_swiglu.cpp:12-91).  The launch is HBM-bound on its
+// weight stream, and in a chain of dependent linears what is not hidden behind that stream is the
+// latency between "the activations exist" and "the outputs are stored".  The kernel is built to keep
+// that chain short:
+//
+//   * A CTA owns whole output channels: 32-channel weight groups (a gate group and its up partner for
+//     SwiGLU) over ALL of K, dealt round-robin to the CTAs.  Nothing is summed across CTAs; the K range
+//     is split over the CTA's own eight contraction warps and summed through its shared memory.
+//   * A ninth warp streams the CTA's weights through a ring of 16 KB stages with bulk async copies.
+//     Weights never change, so everything the ring holds is requested BEFORE the programmatic
+//     dependency wait and arrives while the launch in front is still running.
+//   * Quantising M x K activations in every CTA would cost more than the whole contraction, so the
+//     CTAs of a cluster share it: each scans the full rows of its tokens for the maximum (or its
+//     tokens' scale comes from collected row maxima), quantises its share and pushes the int8 codes
+//     into every cluster member's shared memory with st.async, which counts the bytes on the
+//     receiver's mbarrier.  That is the only exchange of the launch; small problems run without a
+//     cluster and quantise locally.
+//
+// Integer sums are exact in any order, so the warp split and the two accumulator sets per warp do not
+// change results.
+#include "w4a8_device.h"
+#include "w4a8_math.cuh"
+#include "w4a8_ptx.cuh"
+
+namespace rkb200 {
+
+constexpr int DEC_WARPS = 8;                        // contraction warps
+constexpr int DEC_THREADS = (DEC_WARPS + 1) * 32;   // + the copy warp
+constexpr int DEC_STAGE_CHUNKS = 32;                // 32-element chunks of one weight group per stage
+constexpr int DEC_STAGE_BYTES = DEC_STAGE_CHUNKS * 512;
+constexpr size_t DEC_SMEM_LIMIT = 227 * 1024;
+
+__host__ __device__ constexpr int dec_token_slots(int M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8; }
+__host__ __device__ constexpr size_t dec_fixed_bytes(int M, int KB, bool swiglu)
+{
+    return (size_t)dec_token_slots(M) * KB * KBLOCK          // activation codes of all of K
+           + (size_t)DEC_WARPS * (swiglu ? 64 : 32) * 8 * 4  // per-warp partial sums
+           + 64 + 8;                                         // row maxima, scale words; + barriers below
+}
+__host__ __device__ constexpr size_t dec_smem_bytes(int M, int KB, bool swiglu, int ring)
+{
+    return dec_fixed_bytes(M, KB, swiglu) + (size_t)ring * DEC_STAGE_BYTES + (size_t)(2 * ring + 1) * 8;
+}
+
+// 16-byte store into a cluster member's shared memory that counts its bytes on a barrier there.
+__device__ __forceinline__ void st_async_v4(uint32_t remote_addr, const uint4& v, uint32_t remote_bar)
+{
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(remote_addr),
+                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(remote_bar)
+                 : "memory");
+}
+__device__ __forceinline__ void bar_sync_contraction() { asm volatile("bar.sync 1, %0;" ::"n"(DEC_WARPS * 32) : "memory"); }
+
+// Partial-sum scratch index: [warp][row][token], the token position XOR-ed with row bits so that both the
+// fragment-shaped writes and the (token, row)-shaped reads are free of bank conflicts.
+__device__ __forceinline__ int red_index(int warp, int rows, int row, int tok)
+{
+    return (warp * rows + row) * 8 + (tok ^ ((row >> 2) & 7));
+}
+
+template <bool HALF, bool TRACE>
+__global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const DecodeParams p)
+{
+    using AT = typename ActType<HALF>::type;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int R = p.ring;
+    const int M = p.M;
+    const int Mc = dec_token_slots(M);
+    const int Kp = p.KB * KBLOCK, U = Kp / 16, KC = p.KB * 4;
+    const bool swiglu = p.epi == EPI_SWIGLU;
+    const int rows = swiglu ? 64 : 32;
+    uint8_t* const ring = smem;
+    uint8_t* const xs = ring + (size_t)R * DEC_STAGE_BYTES;                     // codes: [unit][Mc][16 B]
+    int* const red = reinterpret_cast<int*>(xs + (size_t)Mc * Kp);
+    uint32_t* const s_max = reinterpret_cast<uint32_t*>(red + DEC_WARPS * rows * 8);   // [8] row maxima of this CTA's tokens
+    uint32_t* const s_scale = s_max + 8;                                         // [8] scale bits per token (or 0xFFFFFFF0 | verdict)
+    uint64_t* const full = reinterpret_cast<uint64_t*>(s_scale + 8 + 2);
+    uint64_t* const empty = full + R;
+    uint64_t* const code_bar = empty + R;
+
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int S = p.cluster, rank = S > 1 ? (int)(blockIdx.x % (unsigned)S) : 0;
+    const int ncta = (int)gridDim.x;
+    const int items = swiglu ? p.F / GROUP : (p.N + GROUP - 1) / GROUP;
+    const int spg = (KC + DEC_STAGE_CHUNKS - 1) / DEC_STAGE_CHUNKS;             // stages per weight group
+    const int gpi = swiglu ? 2 : 1;                                              // weight groups per item
+    const int my_items = (int)blockIdx.x < items ? (items - 1 - (int)blockIdx.x) / ncta + 1 : 0;
+    const int my_stages = my_items * gpi * spg;
+    unsigned long long* const trace = (TRACE && p.trace && tid == 0) ? p.trace + (size_t)blockIdx.x * 8 : nullptr;
+    long long c_start = 0;
+    if (TRACE) { c_start = clock64(); if (trace) trace[0] = global_ns(); }
+
+    if (tid == 0) {
+        for (int i = 0; i < R; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], DEC_WARPS); }
+        mbar_init(code_bar, 1);
+        mbar_fence_init();
+        if (S > 1) mbar_arrive_expect_tx(code_bar, (uint32_t)(M * U * 16 + M * 4));
+    }
+    if (tid < 8) s_max[tid] = 0u;
+    __syncthreads();
+    if (S > 1) cluster_arrive();   // every member's barriers exist once the matching wait returns
+
+    // ------------------------------------------------------------------ copy warp
+    if (warp == DEC_WARPS) {
+        if (S > 1) cluster_wait();
+        if (lane == 0) {
+            unsigned long long deadline = ~0ull;
+            const int per_item = gpi * spg;
+            for (int i = 0; i < my_stages; ++i) {
+                const int slot = i % R;
+                if (i >= R) {
+                    if (i == R) {   // from here on a slot must be handed back first, which cannot happen before the dependency
+                        pdl_wait();
+                        deadline = global_ns() + p.timeout_ns;
+                    }
+                    if (!mbar_wait(&empty[slot], (uint32_t)((i / R - 1) & 1), deadline)) {
+                        atomicExch(&p.status->device_error, 1);
+                        break;
+                    }
+                }
+                const int j = i / per_item, rem = i - j * per_item;
+                const int g = rem / spg, s = rem - g * spg;
+                const int item = (int)blockIdx.x + j * ncta;
+                const int group = g == 0 ? item : p.F / GROUP + item;
+                const int c0 = s * DEC_STAGE_CHUNKS;
+                const uint32_t bytes = (uint32_t)min(DEC_STAGE_CHUNKS, KC - c0) * 512u;
+                mbar_arrive_expect_tx(&full[slot], bytes);
+                bulk_g2s(ring + (size_t)slot * DEC_STAGE_BYTES, p.Wp + ((size_t)group * KC + c0) * 512, bytes, &full[slot]);
+            }
+        }
+        return;
+    }
+
+    // ------------------------------------------------------------------ contraction warps
+    // channel scales of an item's outputs (constants: the first item's are read before the dependency)
+    float sw_a = 0.f, sw_b = 0.f;
+    auto load_channel_scales = [&](int item) {
+        const int n = item * GROUP + lane;
+        sw_a = n < p.NG * GROUP ? p.sw[n] : 0.f;
+        if (swiglu) sw_b = p.sw[p.F + n];
+    };
+    if (my_items > 0) load_channel_scales((int)blockIdx.x);
+    if (TRACE && trace) trace[1] = (unsigned long long)(clock64() - c_start);
+    pdl_wait();   // the producer of A (and of the collected row maxima) has finished
+    const unsigned long long deadline = global_ns() + p.timeout_ns;
+    if (TRACE && trace) trace[2] = (unsigned long long)(clock64() - c_start);
+
+    // ---- 1. this CTA's share of the quantisation.  Mc >= S: whole rows of TQ tokens; else one token's
+    // K range is split over P CTAs, each of which still scans the whole row for the maximum.
+    int TQ, P, t0, part;
+    if (Mc >= S) { TQ = Mc / S; P = 1; t0 = rank * TQ; part = 0; }
+    else { TQ = 1; P = S / Mc; t0 = rank / P; part = rank - t0 * P; }
+    const int pu0 = (int)((long long)U * part / P), pu1 = (int)((long long)U * (part + 1) / P);
+    const bool no_scan = p.rowmax_in != nullptr;
+    const int su0 = no_scan ? pu0 : 0, sn = (no_scan ? pu1 : U) - su0;
+    const int scan_items = TQ * sn;
+    const AT* A = reinterpret_cast<const AT*>(p.A);
+    const bool vec = (reinterpret_cast<uintptr_t>(A) & 15u) == 0 && (p.K % (HALF ? 8 : 4)) == 0;
+    constexpr int UMAX = HALF ? 3 : 2;     // units a thread keeps in registers between the scan and the quantisation
+    constexpr int CT = DEC_WARPS * 32;
+    Raw16<HALF> kept[UMAX];
+    uint32_t kept_bits[UMAX];              // no_scan: the row's collected maximum
+#pragma unroll
+    for (int it = 0; it < UMAX; ++it) {
+        const int idx = tid + CT * it;
+#pragma unroll
+        for (int i = 0; i < (HALF ? 8 : 16); ++i) kept[it].w[i] = 0u;
+        kept_bits[it] = 0u;
+        uint32_t bits = 0;
+        int tl = 0;
+        if (idx < scan_items) {
+            tl = idx / sn;
+            const int u = su0 + idx - tl * sn, tok = t0 + tl;
+            if (tok < M) {
+                if (no_scan) kept_bits[it] = p.rowmax_in[tok];
+                if (u * 16 < p.K) {
+                    load_raw<HALF>(A + (size_t)tok * p.K, u * 16, p.K, vec, kept[it]);
+                    bits = raw_maxbits<HALF>(kept[it]);
+                }
+            }
+        }
+        if (!no_scan) {
+            // a warp whose 32 units belong to one token reduces first and issues a single shared atomic
+            const int tl0 = __shfl_sync(0xffffffffu, tl, 0);
+            if (__all_sync(0xffffffffu, tl == tl0)) {
+                bits = __reduce_max_sync(0xffffffffu, bits);
+                if (lane == 0 && bits) atomicMax(&s_max[tl0], bits);
+            } else if (bits) atomicMax(&s_max[tl], bits);
+        }
+    }
+    if (!no_scan) {
+        for (int idx = tid + CT * UMAX; idx < scan_items; idx += CT) {
+            const int tl = idx / sn, u = su0 + idx - tl * sn, tok = t0 + tl;
+            if (tok < M && u * 16 < p.K) {
+                Raw16<HALF> r;
+                load_raw<HALF>(A + (size_t)tok * p.K, u * 16, p.K, vec, r);
+                atomicMax(&s_max[tl], raw_maxbits<HALF>(r));
+            }
+        }
+        bar_sync_contraction();
+    }
+    // scale of one of this CTA's tokens; every CTA that shares a token derives the same values
+    auto token_scale = [&](int tl, uint32_t collected, float& s, float& inv) -> int {
+        int bad;
+        float maximum;
+        if (no_scan) {
+            bad = collected >= 0x7f800000u ? 2 : 0;
+            maximum = __uint_as_float(collected);
+        } else {
+            const uint32_t bits = s_max[tl];
+            if constexpr (HALF) { bad = bits >= 0x7c00u ? 1 : 0; maximum = __half2float(__ushort_as_half((uint16_t)bits)); }
+            else { bad = bits >= 0x7f800000u ? 1 : 0; maximum = __uint_as_float(bits); }
+        }
+        scale_from_max(maximum, bad != 0, s, inv);
+        return bad;
+    };
+    const bool first_cluster = (int)blockIdx.x < S;
+    const uint32_t xs_base = smem_u32(xs), bar_base = smem_u32(code_bar);
+    if (S > 1) cluster_wait();
+    auto publish = [&](int tok, int u, const uint4& q) {
+        const uint32_t off = (uint32_t)(u * Mc + tok) * 16u;
+        if (S > 1) {
+            for (int d = 0; d < S; ++d) st_async_v4(map_to_cta(xs_base + off, (uint32_t)d), q, map_to_cta(bar_base, (uint32_t)d));
+        } else {
+            *reinterpret_cast<uint4*>(xs + off) = q;
+        }
+        if (p.codes_out && first_cluster) reinterpret_cast<uint4*>(p.codes_out)[(size_t)u * 8 + tok] = q;
+    };
+    // ---- 2. quantise this CTA's share and hand the codes to every member of the cluster
+#pragma unroll
+    for (int it = 0; it < UMAX; ++it) {
+        const int idx = tid + CT * it;
+        if (idx < scan_items) {
+            const int tl = idx / sn, u = su0 + idx - tl * sn, tok = t0 + tl;
+            if (tok < M && u >= pu0 && u < pu1) {
+                float s, inv, v[16];
+                token_scale(tl, kept_bits[it], s, inv);
+                raw_to_float<HALF>(kept[it], v);
+                publish(tok, u, quantize16(v, inv, u * 16, p.K));
+            }
+        }
+    }
+    for (int idx = tid + CT * UMAX; idx < scan_items; idx += CT) {
+        const int tl = idx / sn, u = su0 + idx - tl * sn, tok = t0 + tl;
+        if (tok < M && u >= pu0 && u < pu1) {
+            float s, inv, v[16];
+            uint32_t unused = 0;
+            token_scale(tl, no_scan ? p.rowmax_in[tok] : 0u, s, inv);
+            load16<HALF>(A + (size_t)tok * p.K, u * 16, p.K, vec, v, unused);
+            publish(tok, u, quantize16(v, inv, u * 16, p.K));
+        }
+    }
+    if (part == 0 && tid < TQ && t0 + tid < M) {
+        // the token's scale (or the reason it has none) travels with the codes
+        const int tok = t0 + tid;
+        float s, inv;
+        const int bad = token_scale(tid, no_scan ? p.rowmax_in[tok] : 0u, s, inv);
+        const uint32_t word = bad ? (0xFFFFFFF0u | (uint32_t)bad) : __float_as_uint(s);
+        if (S > 1) {
+            for (int d = 0; d < S; ++d)
+                st_async_u32(map_to_cta(smem_u32(&s_scale[tok]), (uint32_t)d), word, map_to_cta(bar_base, (uint32_t)d));
+        } else s_scale[tok] = word;
+        if (first_cluster && p.scales_out) p.scales_out[tok] = s;
+    }
+    if (TRACE && trace) trace[3] = (unsigned long long)(clock64() - c_start);
+    bool failed = false;
+    if (S > 1) {
+        if (!mbar_wait_warp(code_bar, 0, deadline)) failed = true;
+    } else bar_sync_contraction();
+    if (TRACE && trace) trace[4] = (unsigned long long)(clock64() - c_start);
+    int verdict = 0;
+    for (int t = 0; t < M; ++t) {
+        const uint32_t w = s_scale[t];
+        if (w >= 0xFFFFFFF0u) verdict |= (int)(w & 0xFu);
+    }
+
+    // ---- 3. contraction: warp w takes the chunks w, w + 8, ... of every stage, all 32 (64) channels
+    const int g8 = lane >> 2, t4 = lane & 3;
+    const bool col_live = g8 < M;
+    const uint32_t xs_lane = xs_base + (uint32_t)(g8 * 16 + t4 * 4);
+    const uint32_t ring_lane = smem_u32(ring) + (uint32_t)(g8 * 16 + t4 * 4);
+    const int tok_out = tid >> 5;                         // epilogue: this thread's token; its channel is `lane`
+    const float sx = (tok_out < M && !verdict) ? __uint_as_float(s_scale[tok_out]) : 0.f;
+    uint32_t run_max = 0;
+    int stage_i = 0;
+    for (int j = 0; j < my_items; ++j) {
+        const int item = (int)blockIdx.x + j * ncta;
+        int acc[2][2][4];                                 // [gate | up][m16 tile][fragment]
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+            if (g >= gpi) break;
+            int a0[2][4], a1[2][4];
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { a0[m][e] = 0; a1[m][e] = 0; }
+            for (int s = 0; s < spg; ++s, ++stage_i) {
+                const int slot = stage_i % R;
+                if (!mbar_wait_warp(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
+                if (!verdict && !failed) {
+                    const int c0 = s * DEC_STAGE_CHUNKS, nch = min(DEC_STAGE_CHUNKS, KC - c0);
+                    const uint32_t wslot = ring_lane + (uint32_t)slot * DEC_STAGE_BYTES;
+                    auto chunk = [&](int cc, int (&a)[2][4]) {
+                        const uint32_t wb = wslot + (uint32_t)cc * 512u;
+                        const uint32_t w00 = lds32(wb), w01 = lds32(wb + 128), w10 = lds32(wb + 256), w11 = lds32(wb + 384);
+                        const uint32_t xb = xs_lane + (uint32_t)((c0 + cc) * 2 * Mc) * 16u;
+                        uint32_t b0 = 0, b1 = 0;
+                        if (col_live) { b0 = lds32(xb); b1 = lds32(xb + (uint32_t)Mc * 16u); }
+                        mma_s8(a[0], (w00 << 4) & 0xF0F0F0F0u, (w01 << 4) & 0xF0F0F0F0u, w00 & 0xF0F0F0F0u, w01 & 0xF0F0F0F0u, b0, b1);
+                        mma_s8(a[1], (w10 << 4) & 0xF0F0F0F0u, (w11 << 4) & 0xF0F0F0F0u, w10 & 0xF0F0F0F0u, w11 & 0xF0F0F0F0u, b0, b1);
+                    };
+                    // two accumulator sets halve the chains of dependent MMAs
+                    for (int cc = warp; cc < nch; cc += 2 * DEC_WARPS) {
+                        chunk(cc, a0);
+                        if (cc + DEC_WARPS < nch) chunk(cc + DEC_WARPS, a1);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[slot]);
+            }
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[g][m][e] = a0[m][e] + a1[m][e];
+        }
+        if (TRACE && trace && j == my_items - 1) trace[5] = (unsigned long long)(clock64() - c_start);
+        // ---- 4. sum the warps' partial sums, dequantise, store
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+            if (g >= gpi) break;
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    red[red_index(warp, rows, g * 32 + m * 16 + g8 + (e >> 1) * 8, 2 * t4 + (e & 1))] = acc[g][m][e];
+        }
+        bar_sync_contraction();
+        const float ca = sw_a, cb = sw_b;
+        if (j + 1 < my_items) load_channel_scales(item + ncta);
+        if (!verdict && !failed && tok_out < M) {
+            int v = 0, u = 0;
+#pragma unroll
+            for (int w = 0; w < DEC_WARPS; ++w) {
+                v += red[red_index(w, rows, lane, tok_out)];
+                if (swiglu) u += red[red_index(w, rows, 32 + lane, tok_out)];
+            }
+            v >>= 4;   // exact: the unpacked weights are 16 x code
+            u >>= 4;
+            const int n = item * GROUP + lane;
+            if (swiglu) {
+                const float y = __fmul_rn(silu_poly(dequant(v, sx, ca)), dequant(u, sx, cb));
+                reinterpret_cast<float*>(p.out)[(size_t)tok_out * p.F + n] = y;
+                run_max = max(run_max, __float_as_uint(y) & 0x7fffffffu);
+            } else if (n < p.N) {
+                if (p.epi == EPI_I32) reinterpret_cast<int*>(p.out)[(size_t)tok_out * p.N + n] = v;
+                else if (p.epi == EPI_F32) reinterpret_cast<float*>(p.out)[(size_t)tok_out * p.N + n] = dequant(v, sx, ca);
+                else reinterpret_cast<__half*>(p.out)[(size_t)tok_out * p.N + n] = __float2half_rn(dequant(v, sx, ca));
+            }
+        }
+        if (j + 1 < my_items) bar_sync_contraction();   // the scratch is written again by the next item
+    }
+    if (TRACE && trace) trace[6] = (unsigned long long)(clock64() - c_start);
+    if (swiglu && p.rowmax_out && !verdict) {
+        const uint32_t m = __reduce_max_sync(0xffffffffu, run_max);   // a warp's 32 threads share one token
+        if (lane == 0 && m && tok_out < M) atomicMax(&p.rowmax_out[tok_out], m);
+    }
+
+    // ---- bookkeeping
+    if (failed && lane == 0) atomicExch(&p.status->device_error, 1);
+    if (TRACE && trace) trace[7] = global_ns();
+    if (tid == 0) {
+        if (blockIdx.x == 0) p.status->bad_input = verdict;
+        if (no_scan) {
+            // Every CTA has read the collected maxima by now; the last one to get here clears them
+            // for the next SwiGLU epilogue.  The ticket counter wraps by itself.
+            __threadfence();
+            if (atomicInc(&p.status->done, gridDim.x - 1u) == gridDim.x - 1u)
+                for (int t = 0; t < M; ++t) p.rowmax_in[t] = 0u;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------- host side
+size_t gemm_decode_smem_bytes(int M, int KB, bool swiglu, int ring) { return dec_smem_bytes(M, KB, swiglu, ring); }
+
+bool gemm_decode_supported(int M, int K)
+{
+    const int KB = (K + KBLOCK - 1) / KBLOCK;
+    return M >= 1 && M <= 8 && (long long)KB * KBLOCK <= 131072 && dec_smem_bytes(M, KB, true, 2) <= DEC_SMEM_LIMIT;
+}
+
+// Ring depth: as deep as fits beside a second launch on the same SM (so that the next launch's CTAs, which
+// request their weights before their dependency wait, are resident while this one runs); problems whose
+// activation codes alone take most of that share get what one CTA per SM allows.
+int gemm_decode_ring(int M, int KB, bool swiglu)
+{
+    const size_t fixed = dec_fixed_bytes(M, KB, swiglu) + 256;
+    const size_t shared_budget = 112 * 1024;
+    int ring = fixed < shared_budget ? (int)((shared_budget - fixed) / (DEC_STAGE_BYTES + 16)) : 0;
+    if (ring < 4) ring = (int)((DEC_SMEM_LIMIT - fixed) / (DEC_STAGE_BYTES + 16));
+    if (ring > 8 && fixed >= shared_budget) ring = 8;
+    return ring < DEC_MAX_RING ? ring : DEC_MAX_RING;
+}
+
+// Cluster size (= how many CTAs share the quantisation): about two 16-element units per thread.
+int gemm_decode_cluster(int M, int KB)
+{
+    const long long units = (long long)dec_token_slots(M) * KB * 8;
+    int s = 1;
+    while (s < 8 && units > 512ll * s) s *= 2;
+    return s;
+}
+
+// CTAs: at most `cap` (a multiple of the cluster size), and among the counts down to half of that the one
+// that deals the items most evenly (every CTA streams the same number of weight groups).
+int gemm_decode_ctas(int items, int cluster, int cap)
+{
+    cap = cap / cluster * cluster;
+    if (cap < cluster) cap = cluster;
+    const int need = (items + cluster - 1) / cluster * cluster;
+    if (need <= cap) return need;
+    int best = cap;
+    double best_eff = 0;
+    for (int n = cap; n >= cap / 2 && n >= cluster; n -= cluster) {
+        const int per = (items + n - 1) / n;
+        const double eff = (double)items / ((double)per * n);
+        if (eff > best_eff + 1e-9) { best_eff = eff; best = n; }
+    }
+    return best;
+}
+
+template <bool HALF, bool TRACE>
+static cudaError_t launch_decode_inst(const DecodeParams& p, cudaStream_t stream, bool pdl)
+{
+    auto kernel = gemm_decode_kernel<HALF, TRACE>;
+    static PerDeviceOnce configured;
+    int device = -1;
+    if (configured.needed(device)) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_LIMIT);
+        if (e != cudaSuccess) return e;
+        configured.mark(device);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)p.ctas, 1, 1);
+    cfg.blockDim = dim3(DEC_THREADS);
+    cfg.dynamicSmemBytes = dec_smem_bytes(p.M, p.KB, p.epi == EPI_SWIGLU, p.ring);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (p.cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)p.cluster;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
+cudaError_t launch_gemm_decode(const DecodeParams& p, cudaStream_t stream, bool pdl)
+{
+    const bool swiglu = p.epi == EPI_SWIGLU;
+    if (p.M < 1 || p.M > 8 || (p.cluster != 1 && p.cluster != 2 && p.cluster != 4 && p.cluster != 8) || p.ring < 2 ||
+        p.ring > DEC_MAX_RING || p.ctas < p.cluster || p.ctas % p.cluster || (swiglu && p.F % GROUP) ||
+        dec_smem_bytes(p.M, p.KB, swiglu, p.ring) > DEC_SMEM_LIMIT || (long long)p.KB * KBLOCK > 131072)
+        return cudaErrorInvalidValue;
+    if (p.trace) return p.half ? launch_decode_inst<true, true>(p, stream, pdl) : launch_decode_inst<false, true>(p, stream, pdl);
+    return p.half ? launch_decode_inst<true, false>(p, stream, pdl) : launch_decode_inst<false, false>(p, stream, pdl);
+}
+
+// Resident clusters of this kernel with `smem` bytes of dynamic shared memory, times the cluster size:
+// the most CTAs a launch may have if all of them are to run at once.
+int gemm_decode_resident_ctas(int cluster, size_t smem, int sm_count)
+{
+    auto kernel = gemm_decode_kernel<true, false>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_LIMIT) != cudaSuccess) {
+        cudaGetLastError();
+        return sm_count / cluster * cluster;
+    }
+    if (cluster == 1) return sm_count;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)cluster, 1, 1);
+    cfg.blockDim = dim3(DEC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters < 1) {
+        cudaGetLastError();
+        return sm_count / cluster * cluster;
+    }
+    const int ctas = clusters * cluster;
+    return ctas < sm_count ? ctas : sm_count / cluster * cluster;   // never more than one CTA per SM
+}
+
+} // namespace rkb200

@@ -133,6 +133,28 @@ struct FusedParams {
     unsigned long long* trace;  // optional [CTA][8] global-timer stamps of the kernel's phases (nullable)
 };
 
+// Single-kernel linear for up to eight tokens (w4a8_decode.cu): every CTA owns whole output channels over
+// all of K; the CTAs of a cluster share the quantisation and exchange int8 codes.
+struct DecodeParams {
+    const uint8_t* Wp;
+    const void* A;              // [M,K] fp32 or binary16 activations
+    const float* sw;
+    void* out;
+    uint32_t* rowmax_out;       // SwiGLU: per-row max |middle| bits, atomically maxed (nullable)
+    uint32_t* rowmax_in;        // non-null: row scales come from these bits (no scan); cleared after use
+    float* scales_out;          // [M] per-token scales, written by the first cluster
+    uint8_t* codes_out;         // activation codes in the Xq layout with T = 8 (nullable)
+    Status* status;
+    int M, N, K;
+    int KB, NG, F, epi;
+    int half;                   // activations are binary16
+    int cluster;                // CTAs that share the quantisation: 1, 2, 4 or 8
+    int ring;                   // 16 KB weight stages per CTA
+    int ctas;                   // grid size, a multiple of `cluster`
+    unsigned long long timeout_ns;
+    unsigned long long* trace;  // optional [CTA][8] stamps of the kernel's phases (nullable)
+};
+
 struct PackParams {
     const int8_t* B;        // [K,N] codes on the device
     uint8_t* Wp;
@@ -155,6 +177,15 @@ cudaError_t launch_gemm_stream(const GemmParams& p, int sm_count, cudaStream_t s
 constexpr int FUSED_MAX_STAGES = 16;
 cudaError_t launch_gemm_fused(const FusedParams& p, int tokens_per_cta, cudaStream_t stream, bool pdl);
 size_t gemm_fused_smem_bytes(int tokens_per_cta, int stages, int tiles_per_cta);
+// Decode kernel (up to eight tokens).  The plan helpers pick the cluster size, the ring depth and the grid.
+constexpr int DEC_MAX_RING = 12;
+bool gemm_decode_supported(int M, int K);
+size_t gemm_decode_smem_bytes(int M, int KB, bool swiglu, int ring);
+int gemm_decode_ring(int M, int KB, bool swiglu);
+int gemm_decode_cluster(int M, int KB);
+int gemm_decode_ctas(int items, int cluster, int cap);
+int gemm_decode_resident_ctas(int cluster, size_t smem, int sm_count);
+cudaError_t launch_gemm_decode(const DecodeParams& p, cudaStream_t stream, bool pdl);
 // tcgen05 path: p.T is the token tile of the code layout (multiple of 16, <= 256; 128 when p.pair)
 cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl);
 bool gemm_tc_supported(const GemmParams& p);

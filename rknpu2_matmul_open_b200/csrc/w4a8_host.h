@@ -87,8 +87,10 @@ struct rk_npu_w4a8_workspace {
     int TC = 0;       // tokens per CTA of the mma.sync kernel (0 when the tcgen05 kernel is used)
     int KB = 0;       // k-blocks
     int tiles_per_cta_override = 0;        // single-kernel path: 0 = automatic, 1 or 2 (RK_NPU_B200_TILES_PER_CTA)
-    int variant = 0, split_override = 0;   // variant: 1 quantise + mma.sync GEMM, 2 quantise + tcgen05 GEMM, 3 fused small batch,
-                                           // 4 quantise + persistent streaming GEMM (small batch, large weights)
+    int variant = 0, split_override = 0;   // variant: 1 quantise + mma.sync GEMM, 2 quantise + tcgen05 GEMM, 3 fused small batch
+                                           // (split-K clusters), 4 quantise + persistent streaming GEMM (small batch, large
+                                           // weights), 5 single-kernel decode (whole-K CTAs, up to eight tokens)
+    int decode_cap[4] = {0, 0, 0, 0};      // variant 5: CTAs resident at once for cluster sizes 1, 2, 4, 8
     // device buffers
     uint8_t* codes = nullptr;
     float* scales = nullptr;

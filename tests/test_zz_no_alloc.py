@@ -58,6 +58,7 @@ def test_static_scratch_linear_matches_workspace_linear_twice(oracle):
         assert rc == 0 and np.array_equal(got, want)        # the CPU oracle
         assert np.array_equal(got, ref)                     # and the workspace entry point
     # a NaN row: output untouched, and the verdict can be read back (still without allocating)
+    before = dom.memory_stats()                             # (the comparison above created and freed workspaces)
     A = make_activations(4, K, seed=9, dtype="f16")
     A[2, 5] = 0x7E00
     dA = torch.from_numpy(A.view(np.int16)).cuda()
