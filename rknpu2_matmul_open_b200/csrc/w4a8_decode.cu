@@ -400,10 +400,12 @@ bool gemm_decode_supported(int M, int K)
 int gemm_decode_ring(int M, int KB, bool swiglu)
 {
     const size_t fixed = dec_fixed_bytes(M, KB, swiglu) + 256;
-    const size_t shared_budget = 112 * 1024;
-    int ring = fixed < shared_budget ? (int)((shared_budget - fixed) / (DEC_STAGE_BYTES + 16)) : 0;
-    if (ring < 4) ring = (int)((DEC_SMEM_LIMIT - fixed) / (DEC_STAGE_BYTES + 16));
-    if (ring > 8 && fixed >= shared_budget) ring = 8;
+    const size_t stage = DEC_STAGE_BYTES + 16, shared_budget = 112 * 1024;
+    int ring = fixed < shared_budget ? (int)((shared_budget - fixed) / stage) : 0;
+    if (ring < 3) {
+        ring = fixed < DEC_SMEM_LIMIT ? (int)((DEC_SMEM_LIMIT - fixed) / stage) : 0;
+        if (ring > 8) ring = 8;
+    }
     return ring < DEC_MAX_RING ? ring : DEC_MAX_RING;
 }
 
