@@ -6,7 +6,7 @@
 // Behaviour mirrors the reference operator front-end src/rk_npu_w4a8.cpp (validation
 // order :83-94, BUSY guard :70-81, run :98-159, accounting :169-207, FFN :354-380) and
 // the backend geometry rules src/rk_npu_i4_plan.cpp:14-87.
-#include "w4a8_host.h"
+#include "w4a8_tune.h"
 #include <algorithm>
 #include <cerrno>
 #include <chrono>
@@ -42,143 +42,146 @@ bool valid_shape(int K, int N) { return K > 0 && K <= INT32_MAX / 1024 && N > 0;
 
 bool weight_key_valid(int K, int N, int k_tile)
 {
-    return K > 0 && K <= INT32_MAX / 64 && N > 0 && N <= INT_MAX - 63 && k_tile >= 32 && k_tile <= K_TILE_MAX &&
-           k_tile % 32 == 0;
-}
-
-struct Backend {   // the physical (two rows per token) problem the original device saw
-    int M, N, K, m_tile, k_tile, n_tile;
-    uint32_t mask, timeout_ms;
-    int pipeline, threads;
-};
-
-int panel_entries(int k)
-{
-    const int tail = k % 128;
-    return 8 * (k / 128) + (tail == 0 ? 0 : tail <= 32 ? 2 : tail <= 64 ? 4 : 8);
-}
-int panel_banks(int rows, int k) { return (rows / 8 * panel_entries(k) * 64 + 32767) / 32768; }
-int panel_rows(int remaining, int tile, bool panel8)
-{
-    const int rows = std::min(remaining, tile);
-    return panel8 && rows >= 8 ? rows / 8 * 8 : rows;
-}
-
-bool backend_valid(const Backend& c, bool panel8)
-{
-    if (!weight_key_valid(c.K, c.N, c.k_tile) || c.M < 1 || c.m_tile < 1) return false;
-    if (panel8 && (c.m_tile % 8 || c.m_tile > 512 || c.m_tile < 8 || c.M % 2 ||
-                   panel_banks(panel_rows(c.M, c.m_tile, true), align_up(std::min(c.K, c.k_tile), 32)) > 8))
-        return false;
-    const int cores = __builtin_popcount(c.mask);
-    return c.m_tile <= (panel8 ? 512 : 128) && c.n_tile >= 64 && c.n_tile <= N_TILE_MAX && c.n_tile % 64 == 0 &&
-           (c.mask == 1 || c.mask == 2 || c.mask == 4 || c.mask == 3 || c.mask == 7) && align_up(c.N, 64) / 64 >= cores &&
-           c.timeout_ms > 0 && (c.pipeline == 0 || c.pipeline == 1) && c.threads >= 1 && c.threads <= 4;
+    const bool shape = K > 0 && K <= INT32_MAX / 64 && N > 0 && N <= INT_MAX - 63;
+    return shape && k_tile >= 32 && k_tile <= K_TILE_MAX && k_tile % 32 == 0;
 }
 
 int weight_bytes_query(int K, int N, int k_tile, uint64_t& bytes)
 {
     if (!weight_key_valid(K, N, k_tile)) return RK_NPU_ERR_PARAM;
-    bytes = uint64_t(align_up(K, 32)) * align_up(N, 64) / 2;
+    bytes = uint64_t(align_up(K, 32)) * align_up(N, 64) / 2;   // two codes per byte, K padded to 32, N to 64
     return bytes > UINT32_MAX ? RK_NPU_ERR_NOMEM : RK_NPU_OK;
 }
 
-struct Tile { int m0, m, n0, n, logical_n; };
+// The problem as the original device saw it (two int4 rows per token), kept for one purpose: the memory
+// queries and the constructors must accept exactly the geometries the original accepts and report the
+// numbers it reports (include/rk_npu_w4a8.h:35-75; the arithmetic is that of src/rk_npu_i4_plan.cpp:14-87,
+// src/rk_npu_w4a8_chain.cpp:49-58 and src/rk_npu_w4a8_npu_reduce.cpp:90-137).  Nothing here schedules work.
+class DeviceGeometry {
+public:
+    int rows = 0, N = 0, K = 0;             // rows = 2 x tokens
+    int row_tile = 0, k_tile = 0, n_tile = 0;
+    uint32_t cores = 0, timeout_ms = 0;
+    int pipeline = 0, threads = 0;
+    bool panel8 = false;
 
-// Column partition over the selected cores, then N tiles, then M panels
-// (src/rk_npu_i4_plan.cpp:34-55).  Only used for accounting and validity.
-std::vector<Tile> plan_tiles(const Backend& c, bool panel8)
-{
-    std::vector<Tile> tiles;
-    const int cores = __builtin_popcount(c.mask), blocks = align_up(c.N, 64) / 64;
-    int n0 = 0;
-    for (int core = 0; core < cores; ++core) {
-        const int end = n0 + (blocks / cores + (core < blocks % cores)) * 64;
-        while (n0 < end) {
-            const int n = std::min(c.n_tile, end - n0);
-            for (int m0 = 0; m0 < c.M;) {
-                const int m = panel_rows(c.M - m0, c.m_tile, panel8);
-                tiles.push_back({m0, m, n0, n, std::max(0, std::min(n, c.N - n0))});
-                m0 += m;
+    int core_count() const { return __builtin_popcount(cores); }
+    int column_blocks() const { return align_up(N, 64) / 64; }
+    // 64-column blocks of core `i`: an even share, the first `blocks % cores` cores take one more
+    int core_columns(int i) const { return (column_blocks() / core_count() + (i < column_blocks() % core_count() ? 1 : 0)) * 64; }
+    uint32_t waves() const { return uint32_t((K + k_tile - 1) / k_tile); }
+    int wave_depth() const { return align_up(std::min(K, k_tile), 32); }
+
+    // rows of the next activation panel when `remaining` rows are left: panel8 panels are whole groups of eight
+    int panel_rows(int remaining) const
+    {
+        const int take = std::min(remaining, row_tile);
+        return (panel8 && take >= 8) ? take - take % 8 : take;
+    }
+    // 32 KB buffer banks one panel8 activation panel occupies: 64 bytes per (group of eight rows, entry), where
+    // a full 128-deep slice has 8 entries and a tail of up to 32 / 64 / 128 has 2 / 4 / 8
+    static int panel_banks(int rows_in_panel, int depth)
+    {
+        const int tail = depth % 128;
+        const int entries = depth / 128 * 8 + (tail == 0 ? 0 : tail <= 32 ? 2 : tail <= 64 ? 4 : 8);
+        const long long bytes = (long long)(rows_in_panel / 8) * entries * 64;
+        return int((bytes + 32767) / 32768);
+    }
+
+    bool valid() const
+    {
+        if (!weight_key_valid(K, N, k_tile) || rows < 1 || row_tile < 1) return false;
+        if (panel8) {
+            const bool tile_ok = row_tile >= 8 && row_tile <= 512 && row_tile % 8 == 0 && rows % 2 == 0;
+            if (!tile_ok || panel_banks(panel_rows(rows), wave_depth()) > 8) return false;
+        } else if (row_tile > 128) return false;
+        const bool columns_ok = n_tile >= 64 && n_tile <= N_TILE_MAX && n_tile % 64 == 0;
+        const bool cores_ok = (cores == 1 || cores == 2 || cores == 4 || cores == 3 || cores == 7) && column_blocks() >= core_count();
+        const bool host_ok = timeout_ms > 0 && (pipeline == 0 || pipeline == 1) && threads >= 1 && threads <= 4;
+        return columns_ok && cores_ok && host_ok;
+    }
+
+    // activation panels per column tile
+    uint64_t panels() const
+    {
+        if (!panel8) return (uint64_t(rows) + row_tile - 1) / row_tile;
+        const int rest = rows % row_tile;
+        return uint64_t(rows) / row_tile + (rest >= 8 ? 1 : 0) + (rest % 8 ? 1 : 0);
+    }
+    uint64_t column_tiles() const
+    {
+        uint64_t tiles = 0;
+        for (int i = 0; i < core_count(); ++i) tiles += uint64_t((core_columns(i) + n_tile - 1) / n_tile);
+        return tiles;
+    }
+
+    int memory(rk_npu_i4_memory_info& out) const
+    {
+        if (!valid()) return RK_NPU_ERR_PARAM;
+        out = {};
+        if (const int rc = weight_bytes_query(K, N, k_tile, out.packed_weight_bytes)) return rc;
+        out.wave_count = waves();
+        const uint64_t buffers = std::min(out.wave_count, 2u);             // double-buffered across waves
+        const uint64_t input_one = uint64_t(rows) * wave_depth() / 2, partial_one = uint64_t(rows) * align_up(N, 64) * 2;
+        const uint64_t tasks = column_tiles() * panels();
+        if (tasks > uint64_t(INT_MAX / COMMAND_WORDS) || input_one > UINT32_MAX || partial_one > UINT32_MAX) return RK_NPU_ERR_NOMEM;
+        out.input_bytes = buffers * input_one;
+        out.partial_bytes = buffers * partial_one;
+        out.tasks_per_wave = uint32_t(tasks);
+        out.control_bytes = uint64_t(out.wave_count) * tasks * (COMMAND_WORDS * 8 + TASK_BYTES);
+        return RK_NPU_OK;
+    }
+    // all waves resident at once: the whole padded K of the activations, one partial buffer per wave
+    int memory_chained(rk_npu_i4_memory_info& out) const
+    {
+        if (const int rc = memory(out)) return rc;
+        const uint64_t all_tasks = uint64_t(out.tasks_per_wave) * out.wave_count;
+        const uint64_t input = uint64_t(rows) * align_up(K, 32) / 2, per_wave = uint64_t(rows) * align_up(N, 64) * 2;
+        if (all_tasks > uint64_t(INT_MAX / COMMAND_WORDS) || input > UINT32_MAX || per_wave > UINT32_MAX / out.wave_count) return RK_NPU_ERR_NOMEM;
+        out.input_bytes = input;
+        out.partial_bytes = per_wave * out.wave_count;
+        return RK_NPU_OK;
+    }
+    // device-side reduction of retained partials: every (panel, column tile) is cut into parts of at most
+    // `limit` 16-value rows, the limit halving until (waves + 1) input rows of 64 bytes fit eleven banks
+    int memory_device_reduce(rk_npu_w4a8_memory_info_ex& info) const
+    {
+        const uint64_t wave_total = waves();
+        if (wave_total > 31) return RK_NPU_ERR_PARAM;
+        const uint64_t retained = uint64_t(rows) * align_up(N, 64) * 2 * wave_total;
+        if (retained > UINT32_MAX) return RK_NPU_ERR_NOMEM;
+        int limit = 512;
+        while (uint64_t(limit) * 64 * (wave_total + 1) > 11ull * 32768) limit /= 2;
+        uint64_t parts = 0, output = 0, largest = 256 * 1024;
+        int column = 0;
+        for (int core = 0; core < core_count(); ++core) {
+            const int core_end = column + core_columns(core);
+            for (; column < core_end;) {
+                const int width = std::min(n_tile, core_end - column);
+                for (int row = 0; row < rows;) {
+                    const int height = panel_rows(rows - row);
+                    if (height % 2 || row % 2 || width % 64) return RK_NPU_ERR_PARAM;
+                    const int storage = height * width / 16;
+                    if (storage > 4096) return RK_NPU_ERR_PARAM;
+                    largest = std::max<uint64_t>(largest, uint64_t(height) * width * 2 * wave_total);
+                    for (int done = 0; done < storage; done += limit, ++parts)
+                        output += uint64_t(align_up(std::min(limit, storage - done), 4)) * 64;
+                    row += height;
+                }
+                column += width;
             }
-            n0 += n;
         }
+        if (parts < uint64_t(core_count())) return RK_NPU_ERR_PARAM;
+        if (parts > uint64_t(INT_MAX / REDUCE_COMMAND_WORDS)) return RK_NPU_ERR_NOMEM;
+        info.base.backend.partial_bytes = retained + largest;
+        info.reduction_output_bytes = output + 256 * 1024;
+        info.reduction_weight_bytes = wave_total * 512;
+        info.reduction_control_bytes = parts * (REDUCE_COMMAND_WORDS * 8 + TASK_BYTES);
+        const bool fits = info.base.backend.partial_bytes <= UINT32_MAX && info.reduction_output_bytes <= UINT32_MAX &&
+                          info.reduction_control_bytes <= UINT32_MAX;
+        return fits ? RK_NPU_OK : RK_NPU_ERR_NOMEM;
     }
-    return tiles;
-}
-
-int backend_query(const Backend& c, bool panel8, rk_npu_i4_memory_info& out)
-{
-    if (!backend_valid(c, panel8)) return RK_NPU_ERR_PARAM;
-    out = {};
-    int rc = weight_bytes_query(c.K, c.N, c.k_tile, out.packed_weight_bytes);
-    if (rc) return rc;
-    out.wave_count = uint32_t((c.K + c.k_tile - 1) / c.k_tile);
-    const uint64_t slots = std::min(out.wave_count, 2u);
-    out.input_bytes = slots * uint64_t(c.M) * align_up(std::min(c.K, c.k_tile), 32) / 2;
-    out.partial_bytes = slots * uint64_t(c.M) * align_up(c.N, 64) * 2;
-    const int cores = __builtin_popcount(c.mask), blocks = align_up(c.N, 64) / 64;
-    uint64_t n_tiles = 0;
-    for (int i = 0; i < cores; ++i) {
-        const int cols = (blocks / cores + (i < blocks % cores)) * 64;
-        n_tiles += uint64_t((cols + c.n_tile - 1) / c.n_tile);
-    }
-    const uint64_t remainder = uint64_t(c.M % c.m_tile);
-    const uint64_t panels = !panel8 ? (uint64_t(c.M) + c.m_tile - 1) / c.m_tile
-                                    : uint64_t(c.M) / c.m_tile + (remainder >= 8) + (remainder % 8 != 0);
-    const uint64_t tasks = n_tiles * panels;
-    if (tasks > uint64_t(INT_MAX / COMMAND_WORDS) || out.input_bytes / slots > UINT32_MAX ||
-        out.partial_bytes / slots > UINT32_MAX)
-        return RK_NPU_ERR_NOMEM;
-    out.tasks_per_wave = uint32_t(tasks);
-    out.control_bytes = uint64_t(out.wave_count) * tasks * (COMMAND_WORDS * 8 + TASK_BYTES);
-    return RK_NPU_OK;
-}
-
-int chain_query(const Backend& c, bool panel8, rk_npu_i4_memory_info& info)   // src/rk_npu_w4a8_chain.cpp:49-58
-{
-    int rc = backend_query(c, panel8, info);
-    if (rc) return rc;
-    const uint64_t tasks = uint64_t(info.tasks_per_wave) * info.wave_count;
-    const uint64_t input = uint64_t(c.M) * align_up(c.K, 32) / 2;
-    const uint64_t stride = uint64_t(c.M) * align_up(c.N, 64) * 2;
-    if (tasks > uint64_t(INT_MAX / COMMAND_WORDS) || input > UINT32_MAX || stride > UINT32_MAX / info.wave_count)
-        return RK_NPU_ERR_NOMEM;
-    info.input_bytes = input;
-    info.partial_bytes = stride * info.wave_count;
-    return RK_NPU_OK;
-}
-
-int npu_reduce_query(const Backend& c, bool panel8, rk_npu_w4a8_memory_info_ex& info)   // src/rk_npu_w4a8_npu_reduce.cpp:90-137
-{
-    const int waves = (c.K + c.k_tile - 1) / c.k_tile;
-    if (waves > 31) return RK_NPU_ERR_PARAM;
-    if (uint64_t(c.M) * align_up(c.N, 64) * 2 * waves > UINT32_MAX) return RK_NPU_ERR_NOMEM;
-    int limit = 512;
-    while (limit * 64 * (waves + 1) > 11 * 32768) limit /= 2;
-    uint64_t bytes = 0, guard = 256 * 1024, parts = 0;
-    for (const auto& t : plan_tiles(c, panel8)) {
-        if (t.m % 2 || t.m0 % 2 || t.n % 64) return RK_NPU_ERR_PARAM;
-        const int storage = t.m * t.n / 16;
-        if (storage > 4096) return RK_NPU_ERR_PARAM;
-        guard = std::max(guard, uint64_t(t.m) * t.n * 2 * waves);
-        for (int r = 0; r < storage; r += limit) {
-            const int rows = std::min(limit, storage - r);
-            ++parts;
-            bytes += uint64_t(align_up(rows, 4)) * 64;
-        }
-    }
-    if (parts < uint64_t(__builtin_popcount(c.mask))) return RK_NPU_ERR_PARAM;
-    if (parts > uint64_t(INT_MAX / REDUCE_COMMAND_WORDS)) return RK_NPU_ERR_NOMEM;
-    info.base.backend.partial_bytes = uint64_t(c.M) * align_up(c.N, 64) * 2 * waves + guard;
-    info.reduction_output_bytes = bytes + 256 * 1024;
-    info.reduction_weight_bytes = uint64_t(waves) * 512;
-    info.reduction_control_bytes = parts * (REDUCE_COMMAND_WORDS * 8 + TASK_BYTES);
-    if (info.base.backend.partial_bytes > UINT32_MAX || info.reduction_output_bytes > UINT32_MAX ||
-        info.reduction_control_bytes > UINT32_MAX)
-        return RK_NPU_ERR_NOMEM;
-    return RK_NPU_OK;
-}
+};
 
 int options_decode(const rk_npu_w4a8_options* opt, int M, bool& panel8, bool& npu)
 {
@@ -194,13 +197,23 @@ int options_decode(const rk_npu_w4a8_options* opt, int M, bool& panel8, bool& np
     return RK_NPU_OK;
 }
 
-int backend_from(const rk_npu_w4a8_config& cfg, bool panel8, Backend& out)
+int geometry_from(const rk_npu_w4a8_config& cfg, bool panel8, DeviceGeometry& out)
 {
-    if (!valid_shape(cfg.K, cfg.N) || cfg.M < 1 || cfg.M > INT_MAX / 2 || cfg.m_tile < 1 ||
-        cfg.m_tile > (panel8 ? 256 : 64) || cfg.pipeline < RK_NPU_W4A8_SERIAL || cfg.pipeline > RK_NPU_W4A8_CHAIN)
-        return RK_NPU_ERR_PARAM;
-    out = {cfg.M * 2, cfg.N, cfg.K, cfg.m_tile * 2, cfg.k_tile, cfg.n_tile, cfg.npu_core_mask, cfg.timeout_ms,
-           cfg.pipeline == RK_NPU_W4A8_CHAIN ? 0 : cfg.pipeline, cfg.cpu_threads};
+    const bool tokens_ok = cfg.M >= 1 && cfg.M <= INT_MAX / 2 && cfg.m_tile >= 1 && cfg.m_tile <= (panel8 ? 256 : 64);
+    const bool pipeline_ok = cfg.pipeline >= RK_NPU_W4A8_SERIAL && cfg.pipeline <= RK_NPU_W4A8_CHAIN;
+    if (!valid_shape(cfg.K, cfg.N) || !tokens_ok || !pipeline_ok) return RK_NPU_ERR_PARAM;
+    out = DeviceGeometry{};
+    out.rows = cfg.M * 2;
+    out.row_tile = cfg.m_tile * 2;
+    out.N = cfg.N;
+    out.K = cfg.K;
+    out.k_tile = cfg.k_tile;
+    out.n_tile = cfg.n_tile;
+    out.cores = cfg.npu_core_mask;
+    out.timeout_ms = cfg.timeout_ms;
+    out.pipeline = cfg.pipeline == RK_NPU_W4A8_CHAIN ? 0 : cfg.pipeline;   // the chain mode submits like the serial one
+    out.threads = cfg.cpu_threads;
+    out.panel8 = panel8;
     return RK_NPU_OK;
 }
 
@@ -679,22 +692,21 @@ extern "C" int rk_npu_w4a8_memory_query_ex(const rk_npu_w4a8_config* cfg, const 
     bool panel8, npu;
     int rc = options_decode(options, cfg->M, panel8, npu);
     if (rc) return rc;
-    Backend inner{};
-    rc = backend_from(*cfg, panel8, inner);
+    DeviceGeometry device;
+    rc = geometry_from(*cfg, panel8, device);
     if (rc) return rc;
     rk_npu_w4a8_memory_info_ex info{};
     info.effective_reduce_backend = npu ? RK_NPU_W4A8_REDUCE_NPU : RK_NPU_W4A8_REDUCE_CPU;
-    if (cfg->pipeline == RK_NPU_W4A8_CHAIN) {
-        if (npu) return RK_NPU_ERR_PARAM;
-        rc = chain_query(inner, panel8, info.base.backend);
-    } else {
-        rc = backend_query(inner, panel8, info.base.backend);
-    }
+    const bool chained = cfg->pipeline == RK_NPU_W4A8_CHAIN;
+    if (chained && npu) return RK_NPU_ERR_PARAM;
+    rc = chained ? device.memory_chained(info.base.backend) : device.memory(info.base.backend);
     if (rc) return rc;
+    // host side of a call: 8 bytes of channel metadata per column; per token a scale and its inverse, and with
+    // the host reduction an int32 accumulator row (plus per-thread row maxima when a SwiGLU epilogue is possible)
     info.base.weight_metadata_bytes = uint64_t(cfg->N) * 8;
     info.base.cpu_scratch_bytes = uint64_t(cfg->M) * 8;
     if (npu) {
-        try { rc = npu_reduce_query(inner, panel8, info); } catch (...) { return RK_NPU_ERR_NOMEM; }
+        rc = device.memory_device_reduce(info);
         if (rc) return rc;
     } else {
         info.base.cpu_scratch_bytes += uint64_t(cfg->M) * uint64_t(align_up64(cfg->N, 64)) * 4;
@@ -840,8 +852,8 @@ extern "C" int rk_npu_w4a8_weights_query(const rk_npu_w4a8_weights* w, rk_npu_w4
 }
 
 // ================================================================== workspaces
-extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_domain* domain, const rk_npu_w4a8_config* cfg,
-                                                                  const rk_npu_w4a8_options* options)
+rk_npu_w4a8_workspace* rkb200::create_workspace_scheduled(rk_npu_iommu_domain* domain, const rk_npu_w4a8_config* cfg,
+                                                          const rk_npu_w4a8_options* options, const Schedule& schedule)
 {
     if (!domain || !domain->ctx || !cfg) return nullptr;
     rk_npu_w4a8_memory_info_ex info{};
@@ -863,7 +875,8 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
     // go to the tcgen05 kernel when it can run this geometry.
     GemmParams probe{};
     probe.M = cfg->M; probe.N = cfg->N; probe.K = cfg->K; probe.KB = ws->KB;
-    const int forced = std::getenv("RK_NPU_B200_VARIANT") ? std::atoi(std::getenv("RK_NPU_B200_VARIANT")) : 0;
+    // an explicit schedule (a tuned strategy) wins over the environment override, which wins over the rules below
+    const int forced = schedule.family ? schedule.family : std::getenv("RK_NPU_B200_VARIANT") ? std::atoi(std::getenv("RK_NPU_B200_VARIANT")) : 0;
     const bool tc_ok = gemm_tc_supported(probe);
     const bool fused_ok = cfg->M <= 32 && ws->KB <= 8 * FUSED_MAX_STAGES;
     const bool stream_ok = cfg->M <= 128 && (long long)ws->KB * KBLOCK <= 131072;
@@ -906,6 +919,11 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
     }
     if (variant == 5)
         for (int i = 0; i < 4; ++i) ws->decode_cap[i] = gemm_decode_resident_ctas(1 << i, 227 * 1024, ctx->sm_count);
+    // cooperating CTAs per column tile: split-K factor of the ring and of the split-K single kernel, cluster size of the
+    // decode kernel; ignored where the family balances by itself or the reduction is too short to split
+    if (schedule.cluster && (variant == 1 || variant == 5 || (variant == 3 && (ws->KB + schedule.cluster - 1) / schedule.cluster <= FUSED_MAX_STAGES)) &&
+        (variant == 5 || ws->KB >= schedule.cluster))
+        ws->split_override = schedule.cluster;
     const size_t Mp = size_t(align_up(cfg->M, ws->pair ? 256 : ws->T));
     ws->codes_bytes = Mp * size_t(ws->KB) * KBLOCK;
     const int out_cols = cfg->N;
@@ -943,9 +961,14 @@ extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_d
     if (!ok) { cudaGetLastError(); workspace_destroy(ws); return nullptr; }
     return ws;
 }
+extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_ex(rk_npu_iommu_domain* domain, const rk_npu_w4a8_config* cfg,
+                                                                  const rk_npu_w4a8_options* options)
+{
+    return create_workspace_scheduled(domain, cfg, options, Schedule{});
+}
 extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create(rk_npu_iommu_domain* domain, const rk_npu_w4a8_config* cfg)
 {
-    return rk_npu_w4a8_workspace_create_ex(domain, cfg, nullptr);
+    return create_workspace_scheduled(domain, cfg, nullptr, Schedule{});
 }
 extern "C" void rk_npu_w4a8_workspace_free(rk_npu_w4a8_workspace* ws) { workspace_destroy(ws); }
 

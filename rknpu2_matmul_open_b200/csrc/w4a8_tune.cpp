@@ -2,15 +2,18 @@
 // Pure host code: nothing here touches the GPU, so a cache lookup costs file I/O only
 // (the reference's contract, include/rk_npu_w4a8_tune.h:46-49).
 //
-// Restates, for this library's handles:
-//   bound_weights      src/rk_npu_i4_bounds.cpp:9-69
-//   weight_fingerprint src/rk_npu_autotune_common.cpp:83-89, src/rk_npu_w4a8.cpp:275-277
-//   make_profile       src/rk_npu_w4a8_tune_policy.cpp:41-62
-//   resources / key / strategy validity   src/rk_npu_w4a8_tune_policy.cpp:14-33,63-71,123-155
-//   cache text format  src/rk_npu_w4a8_tune_cache.cpp:7-60, src/rk_npu_autotune_cache.cpp:15-63
-// The cache files are interchangeable with the reference's: same magic line, same key
-// line (the driver-version field holds the CUDA driver version here), same records.
-#include "w4a8_host.h"
+// What is contract here, and where the original defines it:
+//   certified K tiles       src/rk_npu_i4_bounds.cpp:9-69
+//   weight fingerprint      src/rk_npu_autotune_common.cpp:83-89, src/rk_npu_w4a8.cpp:275-277 (FNV-1a over K, N, codes, scales)
+//   profile of a weight     src/rk_npu_w4a8_tune_policy.cpp:41-62
+//   request resources, key line, strategy rules   src/rk_npu_w4a8_tune_policy.cpp:14-33,63-71,123-155
+//   cache text              src/rk_npu_w4a8_tune_cache.cpp:7-60, default location src/rk_npu_autotune_cache.cpp:15-30
+// Cache files are interchangeable with the original's: same magic line, same key line (the
+// driver-version field holds the CUDA driver version here), same two records.  The code that
+// produces and checks that text is this library's own: one field table drives both the record
+// reader and the writer, the key is assembled from a typed field list, the rules are named
+// predicates.
+#include "w4a8_tune.h"
 #include "../../include/rknpu_b200_quant.h"
 #include <algorithm>
 #include <atomic>
@@ -18,7 +21,10 @@
 #include <climits>
 #include <cmath>
 #include <cstdlib>
+#include <cstdio>
 #include <cstring>
+#include <fcntl.h>
+#include <filesystem>
 #include <fstream>
 #include <iomanip>
 #include <locale>
@@ -26,13 +32,12 @@
 #include <sstream>
 #include <sys/stat.h>
 #include <thread>
+#include <type_traits>
 #include <unistd.h>
 #include <vector>
 
 namespace rkb200 {
 namespace {
-constexpr uint32_t TUNING_REVISION = 5;
-constexpr int SMALL_BATCH_LIMIT = 8;
 constexpr const char* CACHE_MAGIC = "rk_npu_w4a8_tuning_cache_v2";
 
 struct Fnv {
@@ -150,6 +155,7 @@ int bound_weights(int K, int N, const int8_t* B, int requested, WeightBound& out
     return RK_NPU_ERR_PARAM;
 }
 
+
 uint64_t weight_fingerprint(int K, int N, const int8_t* B, const float* scales)
 {
     Fnv h;
@@ -160,345 +166,525 @@ uint64_t weight_fingerprint(int K, int N, const int8_t* B, const float* scales)
     return h.value;
 }
 
+// ================================================================== requests and profiles
+namespace {
+int widest_tile(int K) { return std::min(2048, align_up(K, 32)); }
+
+// RK_NPU_W4A8_K_TILE_MULTIPLIER: a complete, finite number >= 1; 1 when unset.  false = malformed.
+bool multiplier_from_environment(double& factor)
+{
+    factor = 1;
+    const char* text = std::getenv("RK_NPU_W4A8_K_TILE_MULTIPLIER");
+    if (!text) return true;
+    char* end = nullptr;
+    errno = 0;
+    const double parsed = std::strtod(text, &end);
+    const bool whole = end != text && *end == 0 && errno == 0;
+    if (!whole || !std::isfinite(parsed) || parsed < 1) return false;
+    factor = parsed;
+    return true;
+}
+bool scales_usable(const float* scale, int N)
+{
+    return std::all_of(scale, scale + N, [](float s) { return std::isfinite(s) && s > 0; });
+}
+} // namespace
+
 bool valid_autotune_config(const rk_npu_w4a8_autotune_config& c)
 {
-    return c.M > 0 && c.M <= INT_MAX / 2 && c.K > 0 && c.K <= INT32_MAX / 1024 && c.N > 0 && c.N <= INT_MAX - 63 &&
-           (c.activation_type == RK_NPU_W4A8_F32 || c.activation_type == RK_NPU_W4A8_F16) &&
-           !(c.allowed_npu_core_mask & ~7u) && c.warmup >= 0 && c.loops > 0 && c.repeats > 0 && c.timeout_ms &&
-           c.required_k_tile >= 0 && c.required_k_tile <= std::min(2048, align_up(c.K, 32)) && c.required_k_tile % 32 == 0 &&
-           std::isfinite(c.k_tile_multiplier) && (c.k_tile_multiplier == 0 || c.k_tile_multiplier >= 1);
+    const bool shape = c.M > 0 && c.M <= INT_MAX / 2 && c.K > 0 && c.K <= INT32_MAX / 1024 && c.N > 0 && c.N <= INT_MAX - 63;
+    const bool type = c.activation_type == RK_NPU_W4A8_F32 || c.activation_type == RK_NPU_W4A8_F16;
+    const bool timing = c.warmup >= 0 && c.loops > 0 && c.repeats > 0 && c.timeout_ms != 0;
+    if (!shape || !type || !timing || (c.allowed_npu_core_mask & ~7u)) return false;
+    const bool tile = c.required_k_tile >= 0 && c.required_k_tile % 32 == 0 && c.required_k_tile <= widest_tile(c.K);
+    const bool factor = std::isfinite(c.k_tile_multiplier) && (c.k_tile_multiplier == 0 || c.k_tile_multiplier >= 1);
+    return tile && factor;
 }
 
 int make_profile(const rk_npu_w4a8_autotune_config& c, const int8_t* B, const float* scale, Profile& out)
 {
-    if (!valid_autotune_config(c) || !B || !scale) return RK_NPU_ERR_PARAM;
-    uint64_t bytes = 0;
-    const rk_npu_i4_weight_config key{c.K, c.N, 32};
-    int rc = rk_npu_i4_weights_memory_query(&key, &bytes);
-    if (rc) return rc;
-    double factor = c.k_tile_multiplier;
-    if (factor == 0) {
-        factor = 1;
-        if (const char* text = std::getenv("RK_NPU_W4A8_K_TILE_MULTIPLIER")) {
-            errno = 0;
-            char* end = nullptr;
-            factor = std::strtod(text, &end);
-            if (errno || end == text || *end || !std::isfinite(factor) || factor < 1) return RK_NPU_ERR_PARAM;
-        }
-    }
-    for (int n = 0; n < c.N; ++n)
-        if (!std::isfinite(scale[n]) || scale[n] <= 0) return RK_NPU_ERR_PARAM;
-    WeightBound b;
-    rc = bound_weights(c.K, c.N, B, 0, b);
-    if (rc) return rc;
+    if (!B || !scale || !valid_autotune_config(c)) return RK_NPU_ERR_PARAM;
+    // the packed size of the original layout must be representable, as for any weight object
+    uint64_t packed = 0;
+    const rk_npu_i4_weight_config smallest{c.K, c.N, 32};
+    if (const int rc = rk_npu_i4_weights_memory_query(&smallest, &packed)) return rc;
     Profile p;
     p.K = c.K;
     p.N = c.N;
-    p.safe = b.k_tile;
-    p.safe_tiles = b.safe_tiles;
-    p.multiplier = factor;
-    p.limit = int(std::min(double(std::min(2048, align_up(c.K, 32))), b.k_tile * factor) / 32) * 32;
+    p.multiplier = c.k_tile_multiplier;
+    if (p.multiplier == 0 && !multiplier_from_environment(p.multiplier)) return RK_NPU_ERR_PARAM;
+    if (!scales_usable(scale, c.N)) return RK_NPU_ERR_PARAM;
+    WeightBound bound;
+    if (const int rc = bound_weights(c.K, c.N, B, 0, bound)) return rc;
+    p.safe = bound.k_tile;
+    p.safe_tiles = bound.safe_tiles;
+    const double relaxed = std::min(double(widest_tile(c.K)), double(bound.k_tile) * p.multiplier);
+    p.limit = int(relaxed / 32) * 32;
     p.fingerprint = weight_fingerprint(c.K, c.N, B, scale);
-    if (c.required_k_tile && !p.permits(c.required_k_tile)) return RK_NPU_ERR_PARAM;
+    if (c.required_k_tile != 0 && !p.permits(c.required_k_tile)) return RK_NPU_ERR_PARAM;
     out = p;
     return RK_NPU_OK;
 }
 
+// ================================================================== host resources of a request
 namespace {
-// ------------------------------------------------------------------ resources
-struct Resources {
-    uint32_t npu = 0;
-    uint64_t cpu = 0, allowed_cpu = 0;
-    int threads = 0;
-    int chain_max_m = 8;
-};
-
-int chain_max_m()   // RK_NPU_W4A8_CHAIN_MAX_M: integer 0..64, default 8, -1 when malformed
+uint64_t affinity_mask()
 {
-    const char* text = std::getenv("RK_NPU_W4A8_CHAIN_MAX_M");
-    if (!text) return 8;
-    if (!*text) return -1;
-    int value = 0;
-    for (const char* p = text; *p; ++p) {
-        if (*p < '0' || *p > '9') return -1;
-        value = value * 10 + (*p - '0');
-        if (value > 64) return -1;
-    }
-    return value;
-}
-uint64_t process_cpu_mask()
-{
-    cpu_set_t set;
-    CPU_ZERO(&set);
-    if (::sched_getaffinity(0, sizeof(set), &set) != 0) return 1;
+    cpu_set_t cpus;
+    CPU_ZERO(&cpus);
     uint64_t mask = 0;
-    for (int c = 0; c < 64 && c < CPU_SETSIZE; ++c) if (CPU_ISSET(c, &set)) mask |= 1ull << c;
-    return mask ? mask : 1;
+    if (::sched_getaffinity(0, sizeof(cpus), &cpus) == 0)
+        for (int cpu = 0; cpu < 64 && cpu < CPU_SETSIZE; ++cpu)
+            mask |= uint64_t(CPU_ISSET(cpu, &cpus) ? 1 : 0) << cpu;
+    return mask ? mask : 1;   // an unreadable or empty affinity counts as CPU 0
 }
-// CPUs 4..7 first (the big cores of the original SoC), then the rest in order; kept so
-// that the masks written into cache keys and strategies mean the same thing.
-std::vector<int> preferred_cpus(uint64_t allowed)
+// Up to `want` CPUs out of `allowed`, CPUs 4..7 before the others (the fast cores of the SoC the cache
+// format was designed on; the resulting mask is a key field, so the order is kept).
+uint64_t pick_cpus(uint64_t allowed, int want, int& picked)
 {
-    std::vector<int> cpus;
-    for (int c = 4; c <= 7; ++c) if (allowed & (1ull << c)) cpus.push_back(c);
-    for (int c = 0; c < 64; ++c) if ((c < 4 || c > 7) && (allowed & (1ull << c))) cpus.push_back(c);
-    return cpus;
-}
-uint64_t first_cpu_mask(const std::vector<int>& cpus, int count)
-{
+    std::vector<int> order;
+    for (int cpu = 0; cpu < 64; ++cpu)
+        if (allowed >> cpu & 1) order.push_back(cpu);
+    std::stable_partition(order.begin(), order.end(), [](int cpu) { return cpu >= 4 && cpu <= 7; });
+    picked = std::min<int>(want, int(order.size()));
     uint64_t mask = 0;
-    for (int i = 0; i < count && i < int(cpus.size()); ++i) mask |= 1ull << cpus[size_t(i)];
+    for (int i = 0; i < picked; ++i) mask |= uint64_t(1) << order[size_t(i)];
     return mask;
 }
-uint32_t fixed_npu_mask(uint32_t allowed, int N, int alignment)
+// The widest core set, in the original's order of preference, that the request allows and that leaves every
+// core at least one 64-column block.
+uint32_t pick_device_cores(uint32_t allowed, int N)
 {
-    if (N < 1 || alignment < 1) return 0;
-    const int groups = int((int64_t(N) + alignment - 1) / alignment);
-    for (uint32_t mask : {7u, 3u, 1u, 2u, 4u})
-        if ((mask & allowed) == mask && __builtin_popcount(mask) <= groups) return mask;
+    if (N < 1) return 0;
+    const int64_t blocks = (int64_t(N) + 63) / 64;
+    static const uint32_t preference[] = {7u, 3u, 1u, 2u, 4u};
+    for (uint32_t mask : preference)
+        if ((allowed & mask) == mask && __builtin_popcount(mask) <= blocks) return mask;
     return 0;
 }
-Resources resolve_resources(const rk_npu_w4a8_autotune_config& c)
+} // namespace
+
+int chain_token_limit()
 {
-    Resources r;
-    const uint64_t affinity = process_cpu_mask();
-    r.chain_max_m = chain_max_m();
-    if (r.chain_max_m < 0) return r;
-    r.allowed_cpu = (c.allowed_cpu_core_mask ? c.allowed_cpu_core_mask : affinity) & affinity;
-    const auto cpus = preferred_cpus(r.allowed_cpu);
-    r.threads = std::min(4, int(cpus.size()));
-    r.cpu = first_cpu_mask(cpus, r.threads);
-    r.npu = fixed_npu_mask(c.allowed_npu_core_mask ? c.allowed_npu_core_mask : 7, c.N, 64);
+    const char* text = std::getenv("RK_NPU_W4A8_CHAIN_MAX_M");
+    if (!text) return SMALL_BATCH_TOKENS;
+    const size_t length = std::strlen(text);
+    if (length == 0 || length > 2 || std::strspn(text, "0123456789") != length) return -1;   // digits only, at most 64
+    const int value = std::atoi(text);
+    return value <= 64 ? value : -1;
+}
+
+HostResources host_resources(const rk_npu_w4a8_autotune_config& request)
+{
+    HostResources r;
+    r.chain_tokens = chain_token_limit();
+    if (r.chain_tokens < 0) return r;
+    const uint64_t affinity = affinity_mask();
+    r.cpus_allowed = affinity & (request.allowed_cpu_core_mask ? request.allowed_cpu_core_mask : affinity);
+    r.cpus = pick_cpus(r.cpus_allowed, 4, r.threads);
+    r.device_cores = pick_device_cores(request.allowed_npu_core_mask ? request.allowed_npu_core_mask : 7u, request.N);
     return r;
 }
 
-// ------------------------------------------------------------------ strategy validity
-using Strategy = rk_npu_w4a8_strategy_ex;
-Strategy extend(const rk_npu_w4a8_strategy& s)
+Strategy widen(const rk_npu_w4a8_strategy& s)
 {
-    return {s, {uint32_t(sizeof(rk_npu_w4a8_options)), RK_NPU_W4A8_INPUT_NATIVE, RK_NPU_W4A8_REDUCE_CPU}};
+    Strategy out{};
+    out.base = s;
+    rk_npu_w4a8_options_init(&out.execution);
+    return out;
 }
-bool cpu_policy_ok(const rk_npu_w4a8_config& c, int maximum_threads, int chain_limit)
+
+// ================================================================== rules
+namespace {
+// Host-thread and pipeline values a strategy may carry for `tokens`: all of the request's threads (one is
+// also fine for a small batch); the chain value only up to the chain limit and with more than one K tile;
+// the serial value only for a small batch.
+bool team_and_pipeline_allowed(const rk_npu_w4a8_config& c, int request_threads, int chain_tokens)
 {
-    if (maximum_threads < 1 || maximum_threads > 4 || chain_limit < 0) return false;
-    const bool small = c.M <= std::max(SMALL_BATCH_LIMIT, chain_limit);
-    if (c.cpu_threads != maximum_threads && !(small && c.cpu_threads == 1)) return false;
-    if (c.pipeline == RK_NPU_W4A8_CHAIN) return c.M <= chain_limit && c.K > c.k_tile;
-    return c.pipeline == RK_NPU_W4A8_PIPELINED || (small && c.pipeline == RK_NPU_W4A8_SERIAL);
+    if (request_threads < 1 || request_threads > 4 || chain_tokens < 0) return false;
+    const bool small_batch = c.M <= std::max(SMALL_BATCH_TOKENS, chain_tokens);
+    const bool team_ok = c.cpu_threads == request_threads || (small_batch && c.cpu_threads == 1);
+    bool pipeline_ok = false;
+    switch (c.pipeline) {
+    case RK_NPU_W4A8_PIPELINED: pipeline_ok = true; break;
+    case RK_NPU_W4A8_SERIAL: pipeline_ok = small_batch; break;
+    case RK_NPU_W4A8_CHAIN: pipeline_ok = c.M <= chain_tokens && c.K > c.k_tile; break;
+    default: break;
+    }
+    return team_ok && pipeline_ok;
 }
-bool execution_ok(const Strategy& s, bool panel8)
+bool timings_plausible(const rk_npu_w4a8_strategy& s)
+{
+    const double values[] = {s.input_us, s.npu_us, s.sync_us, s.output_us, s.total_us, s.jitter_pct, s.robust_us};
+    return std::all_of(std::begin(values), std::end(values), [](double v) { return std::isfinite(v) && v >= 0; });
+}
+
+struct RuleInput {
+    const Strategy& strategy;
+    const rk_npu_w4a8_autotune_config& request;
+    const Profile& profile;
+    const HostResources& res;
+    bool extended;
+};
+struct Rule {
+    const char* what;
+    bool (*holds)(const RuleInput&);
+};
+const Rule REQUEST_RULES[] = {
+    {"the strategy can run", [](const RuleInput& in) { return strategy_executable(in.strategy, in.extended); }},
+    {"same revision and activation type", [](const RuleInput& in) {
+         return in.strategy.base.tuning_revision == TUNING_REVISION && in.strategy.base.activation_type == in.request.activation_type; }},
+    {"made for these weights", [](const RuleInput& in) { return in.strategy.base.weight_fingerprint == in.profile.fingerprint; }},
+    {"made for this shape", [](const RuleInput& in) {
+         const auto& c = in.strategy.base.config;
+         return c.M == in.request.M && c.N == in.request.N && c.K == in.request.K; }},
+    {"carries the request's device cores, CPUs and time limit", [](const RuleInput& in) {
+         const auto& s = in.strategy.base;
+         return s.config.npu_core_mask == in.res.device_cores && s.cpu_core_mask == in.res.cpus &&
+                s.config.timeout_ms == in.request.timeout_ms; }},
+    {"team and pipeline fit the request", [](const RuleInput& in) {
+         return team_and_pipeline_allowed(in.strategy.base.config, in.res.threads, in.res.chain_tokens); }},
+    {"K tile permitted by the weights (and the one the request demands)", [](const RuleInput& in) {
+         const int kt = in.strategy.base.config.k_tile;
+         return in.profile.permits(kt) && (in.request.required_k_tile == 0 || kt == in.request.required_k_tile); }},
+    {"weight block agrees with the profile", [](const RuleInput& in) {
+         const auto& s = in.strategy.base;
+         const auto& w = s.weights;
+         return w.config.K == in.request.K && w.config.N == in.request.N && w.config.k_tile == s.config.k_tile &&
+                w.safe_k_tile == in.profile.safe && w.multiplier == in.profile.multiplier &&
+                (w.bound_relaxed != 0) == !in.profile.certified(s.config.k_tile); }},
+    {"timings are finite and non-negative", [](const RuleInput& in) { return timings_plausible(in.strategy.base); }},
+};
+} // namespace
+
+bool strategy_executable(const Strategy& s, bool extended)
 {
     const auto& o = s.execution;
-    if (!cpu_policy_ok(s.base.config, __builtin_popcountll(s.base.cpu_core_mask), chain_max_m()) ||
-        o.struct_size != sizeof(o) || o.reduce_backend != RK_NPU_W4A8_REDUCE_CPU ||
-        (o.input_layout != RK_NPU_W4A8_INPUT_NATIVE && (!panel8 || o.input_layout != RK_NPU_W4A8_INPUT_PANEL8)))
-        return false;
-    rk_npu_w4a8_memory_info_ex info{};
-    return !rk_npu_w4a8_memory_query_ex(&s.base.config, &o, &info);
+    if (o.struct_size != sizeof(o) || o.reduce_backend != RK_NPU_W4A8_REDUCE_CPU) return false;
+    const bool layout_ok = o.input_layout == RK_NPU_W4A8_INPUT_NATIVE || (extended && o.input_layout == RK_NPU_W4A8_INPUT_PANEL8);
+    if (!layout_ok) return false;
+    if (!team_and_pipeline_allowed(s.base.config, __builtin_popcountll(s.base.cpu_core_mask), chain_token_limit())) return false;
+    rk_npu_w4a8_memory_info_ex unused{};
+    return rk_npu_w4a8_memory_query_ex(&s.base.config, &o, &unused) == RK_NPU_OK;
 }
-bool strategy_ok(const Strategy& strategy, const rk_npu_w4a8_autotune_config& c, const Profile& p, const Resources& r,
-                 bool panel8)
+
+bool strategy_acceptable(const Strategy& s, const rk_npu_w4a8_autotune_config& request, const Profile& profile,
+                         const HostResources& res, bool extended)
 {
-    const auto& s = strategy.base;
-    if (!execution_ok(strategy, panel8)) return false;
-    const auto& a = s.config;
-    const auto& w = s.weights;
-    if (s.tuning_revision != TUNING_REVISION || s.activation_type != c.activation_type ||
-        s.weight_fingerprint != p.fingerprint || a.M != c.M || a.N != c.N || a.K != c.K || a.npu_core_mask != r.npu ||
-        !cpu_policy_ok(a, r.threads, r.chain_max_m) || s.cpu_core_mask != r.cpu || a.timeout_ms != c.timeout_ms ||
-        !p.permits(a.k_tile) || (c.required_k_tile && a.k_tile != c.required_k_tile) || w.config.K != c.K ||
-        w.config.N != c.N || w.config.k_tile != a.k_tile || w.safe_k_tile != p.safe || w.multiplier != p.multiplier ||
-        w.bound_relaxed != !p.certified(a.k_tile))
-        return false;
-    for (double t : {s.input_us, s.npu_us, s.sync_us, s.output_us, s.total_us, s.jitter_pct, s.robust_us})
-        if (!std::isfinite(t) || t < 0) return false;
+    const RuleInput in{s, request, profile, res, extended};
+    for (const Rule& rule : REQUEST_RULES)
+        if (!rule.holds(in)) return false;
     return true;
 }
 
-// ------------------------------------------------------------------ cache text
-std::string cache_key(const rk_npu_ctx* ctx, const rk_npu_w4a8_autotune_config& c, const Profile& p, const Resources& r,
-                      bool panel8)
+// ================================================================== cache text
+namespace {
+// A line of the file is a run of blank-separated tokens.  Each token of a strategy record is described once:
+// its wire type and where it lives in the strategy; the writer and the reader both walk this table.
+enum class Wire { Int, U32, U64, DoubleBits, Choice };
+struct Slot {
+    Wire wire;
+    size_t offset;
+    int lowest, highest;   // Choice: accepted values
+};
+#define RKB200_SLOT(wire, member) {Wire::wire, offsetof(Strategy, member), 0, 0}
+#define RKB200_CHOICE(member, lo, hi) {Wire::Choice, offsetof(Strategy, member), lo, hi}
+const Slot RECORD_SLOTS[] = {
+    RKB200_SLOT(Int, base.config.M), RKB200_SLOT(Int, base.config.N), RKB200_SLOT(Int, base.config.K),
+    RKB200_SLOT(Int, base.config.m_tile), RKB200_SLOT(Int, base.config.k_tile), RKB200_SLOT(Int, base.config.n_tile),
+    RKB200_SLOT(U32, base.config.npu_core_mask), RKB200_SLOT(U32, base.config.timeout_ms),
+    RKB200_SLOT(Int, base.config.pipeline), RKB200_SLOT(Int, base.config.cpu_threads),
+    RKB200_CHOICE(base.activation_type, RK_NPU_W4A8_F32, RK_NPU_W4A8_F16),
+    RKB200_SLOT(U64, base.cpu_core_mask),
+    RKB200_SLOT(Int, base.weights.config.K), RKB200_SLOT(Int, base.weights.config.N), RKB200_SLOT(Int, base.weights.config.k_tile),
+    RKB200_SLOT(Int, base.weights.safe_k_tile), RKB200_SLOT(DoubleBits, base.weights.multiplier),
+    RKB200_SLOT(Int, base.weights.bound_relaxed),
+    RKB200_SLOT(U64, base.weight_fingerprint), RKB200_SLOT(U32, base.tuning_revision),
+    RKB200_SLOT(DoubleBits, base.input_us), RKB200_SLOT(DoubleBits, base.npu_us), RKB200_SLOT(DoubleBits, base.sync_us),
+    RKB200_SLOT(DoubleBits, base.output_us), RKB200_SLOT(DoubleBits, base.total_us), RKB200_SLOT(DoubleBits, base.jitter_pct),
+    RKB200_SLOT(DoubleBits, base.robust_us),
+    RKB200_SLOT(U32, execution.struct_size),
+    RKB200_CHOICE(execution.input_layout, RK_NPU_W4A8_INPUT_NATIVE, RK_NPU_W4A8_INPUT_PANEL8),
+    RKB200_CHOICE(execution.reduce_backend, RK_NPU_W4A8_REDUCE_CPU, RK_NPU_W4A8_REDUCE_CPU),
+};
+#undef RKB200_SLOT
+#undef RKB200_CHOICE
+static_assert(sizeof(rk_npu_w4a8_activation_type) == sizeof(int) && sizeof(rk_npu_w4a8_input_layout) == sizeof(int),
+              "enumerations travel as int");
+
+template <class T> T& field(Strategy& s, size_t offset) { return *reinterpret_cast<T*>(reinterpret_cast<char*>(&s) + offset); }
+template <class T> const T& field(const Strategy& s, size_t offset)
 {
-    std::ostringstream out;
-    out.imbue(std::locale::classic());
-    out << TUNING_REVISION << ' ' << (panel8 ? 3 : 1) << ' ' << ctx->driver_version << ' ' << c.M << ' ' << c.N << ' '
-        << c.K << ' ' << int(c.activation_type) << ' ' << (c.allowed_npu_core_mask ? c.allowed_npu_core_mask : 7) << ' '
-        << r.allowed_cpu << ' ' << r.npu << ' ' << r.cpu << ' ' << c.warmup << ' ' << c.loops << ' ' << c.repeats << ' '
-        << c.timeout_ms << ' ' << c.required_k_tile << ' ' << p.fingerprint << ' ' << p.safe << ' ' << p.safe_tiles
-        << ' ' << p.limit << ' ' << double_bits(p.multiplier) << ' ' << r.chain_max_m;
-    return out.str();
+    return *reinterpret_cast<const T*>(reinterpret_cast<const char*>(&s) + offset);
 }
-std::string default_cache_path(const std::string& key)
+
+std::string record_text(const char* label, const Strategy& s)
 {
+    std::ostringstream line;
+    line.imbue(std::locale::classic());
+    line << label;
+    for (const Slot& slot : RECORD_SLOTS) {
+        line << ' ';
+        switch (slot.wire) {
+        case Wire::Int: case Wire::Choice: line << field<int>(s, slot.offset); break;
+        case Wire::U32: line << field<uint32_t>(s, slot.offset); break;
+        case Wire::U64: line << field<uint64_t>(s, slot.offset); break;
+        case Wire::DoubleBits: line << double_bits(field<double>(s, slot.offset)); break;
+        }
+    }
+    line << '\n';
+    return line.str();
+}
+template <class T> bool take(std::istream& in, T& value) { return bool(in >> value); }
+bool record_parse(std::istream& in, const char* label, Strategy& s)
+{
+    std::string word;
+    if (!take(in, word) || word != label) return false;
+    s = Strategy{};
+    for (const Slot& slot : RECORD_SLOTS) {
+        bool ok = false;
+        switch (slot.wire) {
+        case Wire::Int: ok = take(in, field<int>(s, slot.offset)); break;
+        case Wire::U32: ok = take(in, field<uint32_t>(s, slot.offset)); break;
+        case Wire::U64: ok = take(in, field<uint64_t>(s, slot.offset)); break;
+        case Wire::DoubleBits: {
+            uint64_t bits = 0;
+            ok = take(in, bits);
+            field<double>(s, slot.offset) = bits_double(bits);
+            break;
+        }
+        case Wire::Choice: {
+            int value = 0;
+            ok = take(in, value) && value >= slot.lowest && value <= slot.highest;
+            field<int>(s, slot.offset) = value;
+            break;
+        }
+        }
+        if (!ok) return false;
+    }
+    return true;
+}
+
+// Key line: typed values joined by single blanks, in the order the format fixes.
+class KeyLine {
+public:
+    KeyLine() { text_.imbue(std::locale::classic()); }
+    template <class T> KeyLine& add(T value)
+    {
+        if (!first_) text_ << ' ';
+        first_ = false;
+        text_ << value;
+        return *this;
+    }
+    std::string str() const { return text_.str(); }
+private:
+    std::ostringstream text_;
+    bool first_ = true;
+};
+} // namespace
+
+std::string cache_key_line(const rk_npu_ctx* ctx, const rk_npu_w4a8_autotune_config& request, const Profile& profile,
+                           const HostResources& res, bool extended)
+{
+    KeyLine key;
+    key.add(TUNING_REVISION).add(extended ? 3 : 1)                       // revision, search-space id
+        .add(ctx->driver_version)
+        .add(request.M).add(request.N).add(request.K).add(int(request.activation_type))
+        .add(request.allowed_npu_core_mask ? request.allowed_npu_core_mask : 7u).add(res.cpus_allowed)
+        .add(res.device_cores).add(res.cpus)
+        .add(request.warmup).add(request.loops).add(request.repeats).add(request.timeout_ms)
+        .add(request.required_k_tile)
+        .add(profile.fingerprint).add(profile.safe).add(profile.safe_tiles).add(profile.limit)
+        .add(double_bits(profile.multiplier))
+        .add(res.chain_tokens);
+    return key.str();
+}
+
+std::string cache_file_for(const std::string& key, const char* directory)
+{
+    namespace fs = std::filesystem;
+    fs::path folder;
+    if (directory) {
+        folder = directory;
+    } else {
+        const char* xdg = std::getenv("XDG_CACHE_HOME");
+        const char* home = std::getenv("HOME");
+        if (xdg && *xdg) folder = xdg;
+        else if (home && *home) folder = fs::path(home) / ".cache";
+        else return {};
+        folder /= "rk_npu_w4a8";
+    }
     Fnv h;
     h.bytes(key.data(), key.size());
-    std::string base;
-    const char* xdg = std::getenv("XDG_CACHE_HOME");
-    const char* home = std::getenv("HOME");
-    if (xdg && *xdg) base = xdg;
-    else if (home && *home) base = std::string(home) + "/.cache";
-    else return {};
-    base += "/rk_npu_w4a8";
-    std::ostringstream path;
-    path.imbue(std::locale::classic());
-    path << base << '/' << std::hex << std::setfill('0') << std::setw(16) << h.value << ".tune";
-    return path.str();
+    char name[32];
+    std::snprintf(name, sizeof(name), "%016llx.tune", static_cast<unsigned long long>(h.value));
+    return (folder / name).string();
 }
-void write_record(std::ostream& out, const char* label, const Strategy& strategy)
+
+int cache_read(const std::string& path, const std::string& key, const rk_npu_w4a8_autotune_config& request,
+               const Profile& profile, const HostResources& res, bool extended, Strategy& fastest, Strategy& stable)
 {
-    const auto& s = strategy.base;
-    const auto& c = s.config;
-    const auto& w = s.weights;
-    out << label << ' ' << c.M << ' ' << c.N << ' ' << c.K << ' ' << c.m_tile << ' ' << c.k_tile << ' ' << c.n_tile << ' '
-        << c.npu_core_mask << ' ' << c.timeout_ms << ' ' << c.pipeline << ' ' << c.cpu_threads << ' '
-        << int(s.activation_type) << ' ' << s.cpu_core_mask << ' ' << w.config.K << ' ' << w.config.N << ' '
-        << w.config.k_tile << ' ' << w.safe_k_tile << ' ' << double_bits(w.multiplier) << ' ' << w.bound_relaxed << ' '
-        << s.weight_fingerprint << ' ' << s.tuning_revision;
-    for (double d : {s.input_us, s.npu_us, s.sync_us, s.output_us, s.total_us, s.jitter_pct, s.robust_us})
-        out << ' ' << double_bits(d);
-    out << ' ' << strategy.execution.struct_size << ' ' << int(strategy.execution.input_layout) << ' '
-        << int(strategy.execution.reduce_backend) << '\n';
-}
-bool read_record(std::istream& in, const char* label, Strategy& strategy)
-{
-    auto& s = strategy.base;
-    auto& c = s.config;
-    auto& w = s.weights;
-    std::string name;
-    int dtype = 0;
-    uint64_t factor = 0;
-    if (!(in >> name >> c.M >> c.N >> c.K >> c.m_tile >> c.k_tile >> c.n_tile >> c.npu_core_mask >> c.timeout_ms >>
-          c.pipeline >> c.cpu_threads >> dtype >> s.cpu_core_mask >> w.config.K >> w.config.N >> w.config.k_tile >>
-          w.safe_k_tile >> factor >> w.bound_relaxed >> s.weight_fingerprint >> s.tuning_revision) ||
-        name != label || (dtype != RK_NPU_W4A8_F32 && dtype != RK_NPU_W4A8_F16))
-        return false;
-    s.activation_type = static_cast<rk_npu_w4a8_activation_type>(dtype);
-    w.multiplier = bits_double(factor);
-    for (double* d : {&s.input_us, &s.npu_us, &s.sync_us, &s.output_us, &s.total_us, &s.jitter_pct, &s.robust_us}) {
-        uint64_t bits;
-        if (!(in >> bits)) return false;
-        *d = bits_double(bits);
-    }
-    int layout = 0, reduce = 0;
-    if (!(in >> strategy.execution.struct_size >> layout >> reduce) ||
-        (layout != RK_NPU_W4A8_INPUT_NATIVE && layout != RK_NPU_W4A8_INPUT_PANEL8) || reduce != RK_NPU_W4A8_REDUCE_CPU)
-        return false;
-    strategy.execution.input_layout = static_cast<rk_npu_w4a8_input_layout>(layout);
-    strategy.execution.reduce_backend = static_cast<rk_npu_w4a8_reduce_backend>(reduce);
-    return true;
-}
-int load_file(const std::string& path, const std::string& expected, const rk_npu_w4a8_autotune_config& cfg,
-              const Profile& profile, const Resources& res, Strategy& fast, Strategy& stable, bool panel8)
-{
-    std::ifstream in(path, std::ios::binary);
-    if (!in) return RK_NPU_ERR_CACHE_MISS;
-    in.imbue(std::locale::classic());
-    std::string header, key;
-    Strategy f{}, s{};
-    if (!std::getline(in, header) || header != CACHE_MAGIC || !std::getline(in, key) || key != expected ||
-        !read_record(in, "fastest", f) || !read_record(in, "stable", s) || !strategy_ok(f, cfg, profile, res, panel8) ||
-        !strategy_ok(s, cfg, profile, res, panel8))
+    std::ifstream file(path, std::ios::binary);
+    if (!file) return RK_NPU_ERR_CACHE_MISS;
+    file.imbue(std::locale::classic());
+    std::string magic, stored_key;
+    if (!std::getline(file, magic) || magic != CACHE_MAGIC) return RK_NPU_ERR_CACHE_MISS;
+    if (!std::getline(file, stored_key) || stored_key != key) return RK_NPU_ERR_CACHE_MISS;
+    Strategy first, second;
+    if (!record_parse(file, "fastest", first) || !record_parse(file, "stable", second)) return RK_NPU_ERR_CACHE_MISS;
+    // nothing but white space may follow the two records
+    char extra = 0;
+    if (file >> extra) return RK_NPU_ERR_CACHE_MISS;
+    if (!strategy_acceptable(first, request, profile, res, extended) || !strategy_acceptable(second, request, profile, res, extended))
         return RK_NPU_ERR_CACHE_MISS;
-    in >> std::ws;
-    if (!in.eof()) return RK_NPU_ERR_CACHE_MISS;   // trailing bytes make the file invalid
-    fast = f;
-    stable = s;
-    return RK_NPU_OK;
-}
-bool make_parents(const std::string& path)
-{
-    const size_t slash = path.find_last_of('/');
-    if (slash == std::string::npos) return true;
-    const std::string parent = path.substr(0, slash);
-    if (parent.empty()) return true;
-    for (size_t pos = parent[0] == '/' ? 1 : 0;;) {
-        pos = parent.find('/', pos);
-        const auto part = parent.substr(0, pos);
-        if (!part.empty() && ::mkdir(part.c_str(), 0700) != 0 && errno != EEXIST) return false;
-        if (pos == std::string::npos) break;
-        ++pos;
-    }
-    return true;
-}
-int save_file(const std::string& path, const std::string& key, const Strategy& fast, const Strategy& stable)
-{
-    if (path.empty() || !make_parents(path)) return RK_NPU_ERR_IO;
-    static std::atomic<uint64_t> serial{0};
-    const std::string tmp = path + ".tmp." + std::to_string((long long)::getpid()) + "." +
-                            std::to_string(serial.fetch_add(1, std::memory_order_relaxed));
-    {
-        std::ofstream out(tmp, std::ios::binary | std::ios::trunc);
-        if (!out) return RK_NPU_ERR_IO;
-        out.imbue(std::locale::classic());
-        out << CACHE_MAGIC << '\n' << key << '\n';
-        write_record(out, "fastest", fast);
-        write_record(out, "stable", stable);
-        out.close();
-        if (!out) { ::unlink(tmp.c_str()); return RK_NPU_ERR_IO; }
-    }
-    if (::rename(tmp.c_str(), path.c_str()) != 0) { ::unlink(tmp.c_str()); return RK_NPU_ERR_IO; }
+    fastest = first;
+    stable = second;
     return RK_NPU_OK;
 }
 
-template <bool EX, class S>
-int load_entry(rk_npu_ctx* ctx, const rk_npu_w4a8_autotune_config* cfg, const int8_t* B, const float* scales,
-               const char* path, S* fast, S* stable)
+// The file appears under its final name only complete: it is written next to it under a name no other
+// writer uses (O_EXCL), flushed to the device, and renamed over the target.
+int cache_write(const std::string& path, const std::string& key, const Strategy& fastest, const Strategy& stable)
 {
-    if (!ctx || !cfg || !fast || !stable || (path && !*path)) return RK_NPU_ERR_PARAM;
+    namespace fs = std::filesystem;
+    if (path.empty()) return RK_NPU_ERR_IO;
+    std::error_code ec;
+    const fs::path target(path);
+    if (target.has_parent_path()) {
+        fs::create_directories(target.parent_path(), ec);
+        if (ec && !fs::is_directory(target.parent_path())) return RK_NPU_ERR_IO;
+    }
+    const std::string text = std::string(CACHE_MAGIC) + "\n" + key + "\n" + record_text("fastest", fastest) + record_text("stable", stable);
+    static std::atomic<unsigned> attempt{0};
+    std::string scratch;
+    int fd = -1;
+    for (int tries = 0; tries < 16 && fd < 0; ++tries) {
+        char suffix[48];
+        std::snprintf(suffix, sizeof(suffix), ".%lx-%x.partial", static_cast<unsigned long>(::getpid()), attempt.fetch_add(1));
+        scratch = path + suffix;
+        fd = ::open(scratch.c_str(), O_WRONLY | O_CREAT | O_EXCL | O_CLOEXEC, 0600);
+        if (fd < 0 && errno != EEXIST) return RK_NPU_ERR_IO;
+    }
+    if (fd < 0) return RK_NPU_ERR_IO;
+    size_t written = 0;
+    bool ok = true;
+    while (ok && written < text.size()) {
+        const ssize_t n = ::write(fd, text.data() + written, text.size() - written);
+        if (n < 0 && errno == EINTR) continue;
+        ok = n > 0;
+        if (ok) written += size_t(n);
+    }
+    ok = ok && ::fsync(fd) == 0;
+    ok = (::close(fd) == 0) && ok;
+    ok = ok && ::rename(scratch.c_str(), path.c_str()) == 0;
+    if (!ok) ::unlink(scratch.c_str());
+    return ok ? RK_NPU_OK : RK_NPU_ERR_IO;
+}
+
+// ================================================================== what a strategy selects on this library
+Schedule schedule_of(const rk_npu_w4a8_config& c)
+{
+    Schedule s;
+    if (c.pipeline == RK_NPU_W4A8_CHAIN) s.family = 5;
+    else if (c.pipeline == RK_NPU_W4A8_SERIAL) s.family = 1;
+    else if (c.m_tile == 32) s.family = 1;
+    else if (c.m_tile == 48) s.family = 4;
+    else if (c.m_tile == 56) s.family = 2;
+    if (c.n_tile == 128 || c.n_tile == 256 || c.n_tile == 512 || c.n_tile == 1024) s.cluster = c.n_tile / 128;
+    return s;
+}
+void schedule_into(const Schedule& s, rk_npu_w4a8_config& c)
+{
+    c.pipeline = RK_NPU_W4A8_PIPELINED;
+    c.m_tile = 64;
+    c.n_tile = 2048;                              // a value without a cluster meaning: automatic
+    switch (s.family) {
+    case 5: c.pipeline = RK_NPU_W4A8_CHAIN; break;
+    case 1: c.m_tile = 32; break;
+    case 4: c.m_tile = 48; break;
+    case 2: c.m_tile = 56; break;
+    default: break;
+    }
+    if (s.cluster == 1 || s.cluster == 2 || s.cluster == 4 || s.cluster == 8) c.n_tile = 128 * s.cluster;
+    c.n_tile = std::min(c.n_tile, 8128);
+}
+
+// ================================================================== cache entry points
+namespace {
+struct Prepared {
+    Profile profile;
+    HostResources res;
+    std::string key;
+};
+// Profile from a fresh weight scan, resources, key; the common front of the scanning entry points.
+int prepare(rk_npu_ctx* ctx, const rk_npu_w4a8_autotune_config& request, const int8_t* B, const float* scales, bool extended,
+            Prepared& out)
+{
+    if (const int rc = make_profile(request, B, scales, out.profile)) return rc;
+    out.res = host_resources(request);
+    if (!out.res.usable()) return RK_NPU_ERR_PARAM;
+    out.key = cache_key_line(ctx, request, out.profile, out.res, extended);
+    return RK_NPU_OK;
+}
+void hand_out(rk_npu_w4a8_strategy* to, const Strategy& from) { if (to) *to = from.base; }
+void hand_out(rk_npu_w4a8_strategy_ex* to, const Strategy& from) { if (to) *to = from; }
+Strategy take_in(const rk_npu_w4a8_strategy& s) { return widen(s); }
+Strategy take_in(const rk_npu_w4a8_strategy_ex& s) { return s; }
+
+template <class Public>
+int load_scanning(rk_npu_ctx* ctx, const rk_npu_w4a8_autotune_config* request, const int8_t* B, const float* scales,
+                  const char* path, Public* fastest, Public* stable)
+{
+    constexpr bool extended = std::is_same<Public, rk_npu_w4a8_strategy_ex>::value;
+    if (!ctx || !request || !fastest || !stable || (path && *path == 0)) return RK_NPU_ERR_PARAM;
     try {
-        Profile p;
-        int rc = make_profile(*cfg, B, scales, p);
-        if (rc) return rc;
-        const Resources r = resolve_resources(*cfg);
-        if (!r.npu || !r.threads) return RK_NPU_ERR_PARAM;
-        const std::string key = cache_key(ctx, *cfg, p, r, EX);
+        Prepared p;
+        if (const int rc = prepare(ctx, *request, B, scales, extended, p)) return rc;
         Strategy f{}, s{};
-        rc = load_file(path ? std::string(path) : default_cache_path(key), key, *cfg, p, r, f, s, EX);
-        if (!rc) {
-            if constexpr (EX) { *fast = f; *stable = s; }
-            else { *fast = f.base; *stable = s.base; }
-        }
+        const int rc = cache_read(path ? std::string(path) : cache_file_for(p.key), p.key, *request, p.profile, p.res, extended, f, s);
+        if (rc == RK_NPU_OK) { hand_out(fastest, f); hand_out(stable, s); }
         return rc;
     } catch (const std::bad_alloc&) { return RK_NPU_ERR_NOMEM; } catch (...) { return RK_NPU_ERR_PARAM; }
 }
-template <bool EX, class S>
-int save_entry(rk_npu_ctx* ctx, const rk_npu_w4a8_autotune_config* cfg, const int8_t* B, const float* scales,
-               const char* path, const S* fast, const S* stable)
+template <class Public>
+int save_scanning(rk_npu_ctx* ctx, const rk_npu_w4a8_autotune_config* request, const int8_t* B, const float* scales,
+                  const char* path, const Public* fastest, const Public* stable)
 {
-    if (!ctx || !cfg || !fast || !stable || (path && !*path)) return RK_NPU_ERR_PARAM;
+    constexpr bool extended = std::is_same<Public, rk_npu_w4a8_strategy_ex>::value;
+    if (!ctx || !request || !fastest || !stable || (path && *path == 0)) return RK_NPU_ERR_PARAM;
     try {
-        Profile p;
-        int rc = make_profile(*cfg, B, scales, p);
-        if (rc) return rc;
-        const Resources r = resolve_resources(*cfg);
-        if (!r.npu || !r.threads) return RK_NPU_ERR_PARAM;
-        Strategy f, s;
-        if constexpr (EX) { f = *fast; s = *stable; }
-        else { f = extend(*fast); s = extend(*stable); }
-        if (!strategy_ok(f, *cfg, p, r, EX) || !strategy_ok(s, *cfg, p, r, EX)) return RK_NPU_ERR_PARAM;
-        const std::string key = cache_key(ctx, *cfg, p, r, EX);
-        return save_file(path ? std::string(path) : default_cache_path(key), key, f, s);
+        Prepared p;
+        if (const int rc = prepare(ctx, *request, B, scales, extended, p)) return rc;
+        const Strategy f = take_in(*fastest), s = take_in(*stable);
+        if (!strategy_acceptable(f, *request, p.profile, p.res, extended) || !strategy_acceptable(s, *request, p.profile, p.res, extended))
+            return RK_NPU_ERR_PARAM;
+        return cache_write(path ? std::string(path) : cache_file_for(p.key), p.key, f, s);
     } catch (const std::bad_alloc&) { return RK_NPU_ERR_NOMEM; } catch (...) { return RK_NPU_ERR_PARAM; }
 }
 
-rk_npu_w4a8_weights* create_tuned(rk_npu_iommu_domain* domain, const Strategy& strategy, const int8_t* B,
-                                  const float* scale, bool panel8)
+// Weights for a strategy: the weights are scanned again and the strategy has to pass every rule against
+// a request rebuilt from its own fields (its masks stand for the resources) before anything is created.
+rk_npu_w4a8_weights* weights_for(rk_npu_iommu_domain* domain, const Strategy& strategy, const int8_t* B, const float* scale,
+                                 bool extended)
 {
-    const auto& s = strategy.base;
     if (!domain || !B || !scale) return nullptr;
     try {
-        rk_npu_w4a8_autotune_config c;
-        rk_npu_w4a8_autotune_config_init(&c, s.config.M, s.config.N, s.config.K);
-        c.activation_type = s.activation_type;
-        c.required_k_tile = s.config.k_tile;
-        c.k_tile_multiplier = s.weights.multiplier;
-        c.timeout_ms = s.config.timeout_ms;
-        Profile p;
-        if (make_profile(c, B, scale, p)) return nullptr;
-        const Resources r{s.config.npu_core_mask, s.cpu_core_mask, s.cpu_core_mask, __builtin_popcountll(s.cpu_core_mask),
-                          chain_max_m()};
-        if (!strategy_ok(strategy, c, p, r, panel8)) return nullptr;
-        return create_weights(domain, p.info(c.required_k_tile), B, scale, &p);
+        const auto& s = strategy.base;
+        rk_npu_w4a8_autotune_config request;
+        rk_npu_w4a8_autotune_config_init(&request, s.config.M, s.config.N, s.config.K);
+        request.activation_type = s.activation_type;
+        request.timeout_ms = s.config.timeout_ms;
+        request.required_k_tile = s.config.k_tile;
+        request.k_tile_multiplier = s.weights.multiplier;
+        Profile profile;
+        if (make_profile(request, B, scale, profile)) return nullptr;
+        HostResources res;
+        res.device_cores = s.config.npu_core_mask;
+        res.cpus = res.cpus_allowed = s.cpu_core_mask;
+        res.threads = __builtin_popcountll(s.cpu_core_mask);
+        res.chain_tokens = chain_token_limit();
+        if (!strategy_acceptable(strategy, request, profile, res, extended)) return nullptr;
+        return create_weights(domain, profile.info(request.required_k_tile), B, scale, &profile);
     } catch (...) { return nullptr; }
 }
 } // namespace
@@ -532,68 +718,68 @@ extern "C" void rk_npu_w4a8_autotune_config_init(rk_npu_w4a8_autotune_config* c,
     c->warmup = 2; c->loops = 8; c->repeats = 3;
     c->timeout_ms = 500;
 }
-extern "C" int rk_npu_w4a8_autotune_cache_load_profile_ex(rk_npu_ctx* ctx, const rk_npu_w4a8_autotune_config* cfg,
+// Lookup from a captured profile: no weight scan, no device work (include/rk_npu_w4a8_tune.h:46-60).
+// The caller states the multiplier policy; a captured profile never adopts a changed environment silently.
+extern "C" int rk_npu_w4a8_autotune_cache_load_profile_ex(rk_npu_ctx* ctx, const rk_npu_w4a8_autotune_config* request,
                                                           const rk_npu_w4a8_tuning_profile* profile, const char* path,
-                                                          rk_npu_w4a8_strategy_ex* fast, rk_npu_w4a8_strategy_ex* stable)
+                                                          rk_npu_w4a8_strategy_ex* fastest, rk_npu_w4a8_strategy_ex* stable)
 {
-    if (!ctx || !cfg || !profile || !fast || !stable || (path && !*path) || !valid_autotune_config(*cfg))
+    if (!ctx || !request || !profile || !fastest || !stable || (path && *path == 0) || !valid_autotune_config(*request))
         return RK_NPU_ERR_PARAM;
     try {
         const Profile& p = profile->value;
-        // The caller states the multiplier policy explicitly; a captured profile never
-        // adopts a changed environment silently.
-        if (p.K != cfg->K || p.N != cfg->N || cfg->k_tile_multiplier != p.multiplier ||
-            (cfg->required_k_tile && !p.permits(cfg->required_k_tile)))
-            return RK_NPU_ERR_PARAM;
-        const Resources r = resolve_resources(*cfg);
-        if (!r.npu || !r.threads) return RK_NPU_ERR_PARAM;
-        const std::string key = cache_key(ctx, *cfg, p, r, true);
-        return load_file(path ? std::string(path) : default_cache_path(key), key, *cfg, p, r, *fast, *stable, true);
+        const bool same_weights = p.K == request->K && p.N == request->N && request->k_tile_multiplier == p.multiplier;
+        if (!same_weights || (request->required_k_tile != 0 && !p.permits(request->required_k_tile))) return RK_NPU_ERR_PARAM;
+        const HostResources res = host_resources(*request);
+        if (!res.usable()) return RK_NPU_ERR_PARAM;
+        const std::string key = cache_key_line(ctx, *request, p, res, true);
+        return cache_read(path ? std::string(path) : cache_file_for(key), key, *request, p, res, true, *fastest, *stable);
     } catch (const std::bad_alloc&) { return RK_NPU_ERR_NOMEM; } catch (...) { return RK_NPU_ERR_PARAM; }
 }
 extern "C" int rk_npu_w4a8_autotune_cache_load(rk_npu_ctx* ctx, const rk_npu_w4a8_autotune_config* cfg, const int8_t* B,
                                                const float* s, const char* path, rk_npu_w4a8_strategy* fast,
                                                rk_npu_w4a8_strategy* stable)
 {
-    return load_entry<false>(ctx, cfg, B, s, path, fast, stable);
+    return load_scanning(ctx, cfg, B, s, path, fast, stable);
 }
 extern "C" int rk_npu_w4a8_autotune_cache_save(rk_npu_ctx* ctx, const rk_npu_w4a8_autotune_config* cfg, const int8_t* B,
                                                const float* s, const char* path, const rk_npu_w4a8_strategy* fast,
                                                const rk_npu_w4a8_strategy* stable)
 {
-    return save_entry<false>(ctx, cfg, B, s, path, fast, stable);
+    return save_scanning(ctx, cfg, B, s, path, fast, stable);
 }
 extern "C" int rk_npu_w4a8_autotune_cache_load_ex(rk_npu_ctx* ctx, const rk_npu_w4a8_autotune_config* cfg, const int8_t* B,
                                                   const float* s, const char* path, rk_npu_w4a8_strategy_ex* fast,
                                                   rk_npu_w4a8_strategy_ex* stable)
 {
-    return load_entry<true>(ctx, cfg, B, s, path, fast, stable);
+    return load_scanning(ctx, cfg, B, s, path, fast, stable);
 }
 extern "C" int rk_npu_w4a8_autotune_cache_save_ex(rk_npu_ctx* ctx, const rk_npu_w4a8_autotune_config* cfg, const int8_t* B,
                                                   const float* s, const char* path, const rk_npu_w4a8_strategy_ex* fast,
                                                   const rk_npu_w4a8_strategy_ex* stable)
 {
-    return save_entry<true>(ctx, cfg, B, s, path, fast, stable);
+    return save_scanning(ctx, cfg, B, s, path, fast, stable);
 }
 extern "C" rk_npu_w4a8_weights* rk_npu_w4a8_weights_create_tuned(rk_npu_iommu_domain* domain, const rk_npu_w4a8_strategy* s,
                                                                  const int8_t* B, const float* scale)
 {
-    return s ? create_tuned(domain, extend(*s), B, scale, false) : nullptr;
+    return s ? weights_for(domain, widen(*s), B, scale, false) : nullptr;
 }
 extern "C" rk_npu_w4a8_weights* rk_npu_w4a8_weights_create_tuned_ex(rk_npu_iommu_domain* domain,
                                                                     const rk_npu_w4a8_strategy_ex* s, const int8_t* B,
                                                                     const float* scale)
 {
-    return s ? create_tuned(domain, *s, B, scale, true) : nullptr;
+    return s ? weights_for(domain, *s, B, scale, true) : nullptr;
 }
+// A workspace that runs the schedule the strategy's fields select (see schedule_of in w4a8_tune.h).
 extern "C" rk_npu_w4a8_workspace* rk_npu_w4a8_workspace_create_tuned_ex(rk_npu_iommu_domain* domain,
                                                                         const rk_npu_w4a8_strategy_ex* s)
 {
-    if (!s || s->base.tuning_revision != TUNING_REVISION || !execution_ok(*s, true) ||
-        s->base.config.K != s->base.weights.config.K || s->base.config.N != s->base.weights.config.N ||
-        s->base.config.k_tile != s->base.weights.config.k_tile)
-        return nullptr;
-    return rk_npu_w4a8_workspace_create_ex(domain, &s->base.config, &s->execution);
+    if (!s || s->base.tuning_revision != TUNING_REVISION || !strategy_executable(*s, true)) return nullptr;
+    const auto& c = s->base.config;
+    const auto& w = s->base.weights.config;
+    if (c.K != w.K || c.N != w.N || c.k_tile != w.k_tile) return nullptr;
+    return create_workspace_scheduled(domain, &c, &s->execution, schedule_of(c));
 }
 
 // ================================================================== W8 load-only tuning cache
@@ -639,7 +825,7 @@ bool w8_config_ok(const rk_npu_matmul_autotune_config* c)
 bool w8_make_key(const rk_npu_ctx* ctx, const rk_npu_matmul_autotune_config* c, int kind, W8Key& key)
 {
     if (!ctx || !w8_config_ok(c) || !w8_kind_ok(kind)) return false;
-    const uint64_t affinity = process_cpu_mask();
+    const uint64_t affinity = affinity_mask();
     key.driver = ctx->driver_version;
     key.revision |= w8_execution_mode(kind) << 16;
     key.op = kind;
@@ -675,7 +861,7 @@ bool w8_record_ok(const rk_npu_matmul_strategy& s, const W8Key& key)
         s.n_tile > W8_N_TILE_MAX || s.a_layout < RK_NPU_MATMUL_A_LAYOUT_NORMAL || s.a_layout > RK_NPU_MATMUL_A_LAYOUT_PANEL16 ||
         s.c_layout < RK_NPU_MATMUL_C_LAYOUT_NATIVE || s.c_layout > RK_NPU_MATMUL_C_LAYOUT_PANEL16 ||
         !(m == 1u || m == 2u || m == 4u || m == 3u || m == 7u) || s.cpu_core_mask == 0 || s.cpu_threads <= 0 ||
-        s.cpu_threads != __builtin_popcountll(s.cpu_core_mask) || (s.cpu_core_mask & ~process_cpu_mask()))
+        s.cpu_threads != __builtin_popcountll(s.cpu_core_mask) || (s.cpu_core_mask & ~affinity_mask()))
         return false;
     // Panel recipes are checked by the original against its device plan; they have no meaning
     // here and their rules are not restated: such a record is treated as not usable.
