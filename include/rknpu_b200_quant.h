@@ -3,7 +3,7 @@
  * callers touch: the load-only W8 tuning cache and the configuration initialisers.
  *
  * Every other entry point of those two headers (W8A8 weights / workspaces / runs, the exact
- * int4 x int4 -> int32 API, the search-based tuners and their family forms, cache saving of
+ * int4 x int4 -> int32 API, the W8 search tuners and their family forms, cache saving of
  * the W8 tuner, the DMA-buffer helpers of rk_npu_common.h) is exported by the library so that
  * existing programs link, and answers RK_NPU_ERR_PARAM, NULL or 0: those operators are not
  * built here.  Programs may include the original headers instead of this one; the layouts
@@ -101,15 +101,6 @@ typedef struct rk_npu_i4_config {
     int cpu_threads;
 } rk_npu_i4_config;
 void rk_npu_i4_config_init(rk_npu_i4_config *cfg, int M, int N, int K);
-
-/* include/rk_npu_w4a8_tune.h:62-67, src/rk_npu_w4a8_tune_policy.cpp:161-164 */
-typedef struct rk_npu_w4a8_family_config {
-    rk_npu_w4a8_autotune_config base;
-    int m_count;
-    const int *m_values;
-    const double *frequencies;
-} rk_npu_w4a8_family_config;
-void rk_npu_w4a8_family_config_init(rk_npu_w4a8_family_config *cfg, int N, int K, int m_count, const int *m_values);
 
 #ifdef __cplusplus
 }

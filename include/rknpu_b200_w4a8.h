@@ -280,6 +280,69 @@ rk_npu_w4a8_weights *rk_npu_w4a8_weights_create_tuned_ex(rk_npu_iommu_domain *do
 rk_npu_w4a8_workspace *rk_npu_w4a8_workspace_create_tuned_ex(rk_npu_iommu_domain *domain,
                                                              const rk_npu_w4a8_strategy_ex *strategy);
 
+/* ------------------------------------------------------------------ search tuner
+ * include/rk_npu_w4a8_tune.h:62-167.  The original searches tiles, host teams and pipeline modes of
+ * its three-core device.  On this library the search space is: which kernel family runs the shape
+ * (single-launch decode kernel, mma.sync split-K ring, tcgen05 per-tile / persistent / streaming
+ * kernels) and how many CTAs cooperate on a column tile (split-K factor / cluster size).  The
+ * protocol is the original's: complete blocking calls on a deterministic calibration tensor, the
+ * first result checked against the int64 formula, every later output compared with it, warm-up,
+ * loops x repeats, median, jitter and robust figures.  Candidates are ranked by the device part of
+ * the call (host copies are the same for all of them); total_us / robust_us record the whole call.
+ * The winner is written into the strategy's existing fields -- pipeline, m_tile, n_tile keep their
+ * names, ranges and validity rules and select the schedule (rk_npu_w4a8_workspace_create_tuned_ex
+ * honours them; rk_npu_w4a8_workspace_create[_ex] keeps choosing by itself):
+ *   pipeline  CHAIN: single-launch decode kernel; SERIAL: quantise + mma.sync ring; PIPELINED: see m_tile
+ *   m_tile    64 automatic; 32 mma.sync ring; 48 tcgen05 streaming kernel; 56 tcgen05 tile kernel
+ *   n_tile    128 / 256 / 512 / 1024: 1 / 2 / 4 / 8 cooperating CTAs; anything else automatic
+ * Either output may be NULL, not both.  Needs a context opened on a GPU. */
+int rk_npu_w4a8_autotune(rk_npu_ctx *ctx, const rk_npu_w4a8_autotune_config *cfg, const int8_t *B, const float *w_scale,
+                         rk_npu_w4a8_strategy *fastest, rk_npu_w4a8_strategy *stable);
+int rk_npu_w4a8_autotune_ex(rk_npu_ctx *ctx, const rk_npu_w4a8_autotune_config *cfg, const int8_t *B,
+                            const float *w_scale, rk_npu_w4a8_strategy_ex *fastest, rk_npu_w4a8_strategy_ex *stable);
+/* A valid cache file answers without device work (cache_hit = 1) unless refresh; otherwise search and save
+ * (a failed save leaves the strategies valid).  NULL cache_path: the default location. */
+int rk_npu_w4a8_autotune_cached(rk_npu_ctx *ctx, const rk_npu_w4a8_autotune_config *cfg, const int8_t *B,
+                                const float *w_scale, const char *cache_path, int refresh, rk_npu_w4a8_strategy *fastest,
+                                rk_npu_w4a8_strategy *stable, int *cache_hit);
+int rk_npu_w4a8_autotune_cached_ex(rk_npu_ctx *ctx, const rk_npu_w4a8_autotune_config *cfg, const int8_t *B,
+                                   const float *w_scale, const char *cache_path, int refresh,
+                                   rk_npu_w4a8_strategy_ex *fastest, rk_npu_w4a8_strategy_ex *stable, int *cache_hit);
+
+/* include/rk_npu_w4a8_tune.h:62-73: several batch sizes of one weight, sharing one K partition. */
+typedef struct rk_npu_w4a8_family_config {
+    rk_npu_w4a8_autotune_config base; /* M ignored */
+    int m_count;
+    const int *m_values;
+    const double *frequencies;        /* relative call counts; NULL = equal */
+} rk_npu_w4a8_family_config;
+typedef struct rk_npu_w4a8_family_summary {
+    rk_npu_w4a8_weight_info weights;
+    uint64_t weight_fingerprint;
+    double weighted_total_us, weighted_robust_us;
+} rk_npu_w4a8_family_summary;
+void rk_npu_w4a8_family_config_init(rk_npu_w4a8_family_config *cfg, int N, int K, int m_count, const int *m_values);
+/* Each requested summary needs a strategy array of m_count elements; cached forms keep one file per batch
+ * size under cache_directory (NULL: the default location). */
+int rk_npu_w4a8_autotune_family(rk_npu_ctx *ctx, const rk_npu_w4a8_family_config *cfg, const int8_t *B,
+                                const float *w_scale, rk_npu_w4a8_family_summary *fastest,
+                                rk_npu_w4a8_strategy *fastest_strategies, rk_npu_w4a8_family_summary *stable,
+                                rk_npu_w4a8_strategy *stable_strategies);
+int rk_npu_w4a8_autotune_family_cached(rk_npu_ctx *ctx, const rk_npu_w4a8_family_config *cfg, const int8_t *B,
+                                       const float *w_scale, const char *cache_directory, int refresh,
+                                       rk_npu_w4a8_family_summary *fastest, rk_npu_w4a8_strategy *fastest_strategies,
+                                       rk_npu_w4a8_family_summary *stable, rk_npu_w4a8_strategy *stable_strategies,
+                                       int *cache_hits, int *cache_misses);
+int rk_npu_w4a8_autotune_family_ex(rk_npu_ctx *ctx, const rk_npu_w4a8_family_config *cfg, const int8_t *B,
+                                   const float *w_scale, rk_npu_w4a8_family_summary *fastest,
+                                   rk_npu_w4a8_strategy_ex *fastest_strategies, rk_npu_w4a8_family_summary *stable,
+                                   rk_npu_w4a8_strategy_ex *stable_strategies);
+int rk_npu_w4a8_autotune_family_cached_ex(rk_npu_ctx *ctx, const rk_npu_w4a8_family_config *cfg, const int8_t *B,
+                                          const float *w_scale, const char *cache_directory, int refresh,
+                                          rk_npu_w4a8_family_summary *fastest, rk_npu_w4a8_strategy_ex *fastest_strategies,
+                                          rk_npu_w4a8_family_summary *stable, rk_npu_w4a8_strategy_ex *stable_strategies,
+                                          int *cache_hits, int *cache_misses);
+
 #ifdef __cplusplus
 }
 #endif

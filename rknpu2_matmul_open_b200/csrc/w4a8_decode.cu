@@ -62,7 +62,9 @@ __device__ __forceinline__ int red_index(int warp, int rows, int row, int tok)
     return (warp * rows + row) * 8 + (tok ^ ((row >> 2) & 7));
 }
 
-template <bool HALF, bool TRACE>
+// DOT: up to four tokens, contraction on the integer dot-product units (eight-column tensor-core tiles would be
+// at most half empty, and this GPU's legacy mma.sync int8 path issues one tile per ~11 cycles per SM).
+template <bool HALF, bool DOT, bool TRACE>
 __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const DecodeParams p)
 {
     using AT = typename ActType<HALF>::type;
@@ -145,10 +147,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
         if (swiglu) sw_b = p.sw[p.F + n];
     };
     if (my_items > 0) load_channel_scales((int)blockIdx.x);
-    if (TRACE && trace) trace[1] = (unsigned long long)(clock64() - c_start);
-    pdl_wait();   // the producer of A (and of the collected row maxima) has finished
-    const unsigned long long deadline = global_ns() + p.timeout_ns;
-    if (TRACE && trace) trace[2] = (unsigned long long)(clock64() - c_start);
 
     // ---- 1. this CTA's share of the quantisation.  Mc >= S: whole rows of TQ tokens; else one token's
     // K range is split over P CTAs, each of which still scans the whole row for the maximum.
@@ -163,28 +161,44 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
     const bool vec = (reinterpret_cast<uintptr_t>(A) & 15u) == 0 && (p.K % (HALF ? 8 : 4)) == 0;
     constexpr int UMAX = HALF ? 3 : 2;     // units a thread keeps in registers between the scan and the quantisation
     constexpr int CT = DEC_WARPS * 32;
+    // The rows this CTA will read, pulled towards L2 while the launch in front still runs.  A prefetch is only a
+    // hint: the L2 is the point of coherence, so whatever the producer still writes is what the loads below see.
+    {
+        const int unit_bytes = HALF ? 32 : 64;
+        for (int idx = tid * (128 / unit_bytes); idx < scan_items; idx += CT * (128 / unit_bytes)) {
+            const int tl = idx / sn, u = su0 + idx - tl * sn, tok = t0 + tl;
+            if (tok < M && u * 16 < p.K)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(A) + ((size_t)tok * p.K + (size_t)u * 16) * sizeof(AT)));
+        }
+    }
+    if (TRACE && trace) trace[1] = (unsigned long long)(clock64() - c_start);
+    pdl_wait();   // the producer of A (and of the collected row maxima) has finished
+    const unsigned long long deadline = global_ns() + p.timeout_ns;
+    if (TRACE && trace) trace[2] = (unsigned long long)(clock64() - c_start);
+
     Raw16<HALF> kept[UMAX];
     uint32_t kept_bits[UMAX];              // no_scan: the row's collected maximum
+    // every load is issued before anything waits for one: a round trip to L2 costs more than the rest of the scan
 #pragma unroll
     for (int it = 0; it < UMAX; ++it) {
         const int idx = tid + CT * it;
 #pragma unroll
         for (int i = 0; i < (HALF ? 8 : 16); ++i) kept[it].w[i] = 0u;
         kept_bits[it] = 0u;
-        uint32_t bits = 0;
-        int tl = 0;
         if (idx < scan_items) {
-            tl = idx / sn;
-            const int u = su0 + idx - tl * sn, tok = t0 + tl;
+            const int tl = idx / sn, u = su0 + idx - tl * sn, tok = t0 + tl;
             if (tok < M) {
                 if (no_scan) kept_bits[it] = p.rowmax_in[tok];
-                if (u * 16 < p.K) {
-                    load_raw<HALF>(A + (size_t)tok * p.K, u * 16, p.K, vec, kept[it]);
-                    bits = raw_maxbits<HALF>(kept[it]);
-                }
+                if (u * 16 < p.K) load_raw<HALF>(A + (size_t)tok * p.K, u * 16, p.K, vec, kept[it]);
             }
         }
-        if (!no_scan) {
+    }
+    if (!no_scan) {
+#pragma unroll
+        for (int it = 0; it < UMAX; ++it) {
+            const int idx = tid + CT * it;
+            const int tl = idx < scan_items ? idx / sn : 0;
+            uint32_t bits = raw_maxbits<HALF>(kept[it]);    // units never loaded hold zeros
             // a warp whose 32 units belong to one token reduces first and issues a single shared atomic
             const int tl0 = __shfl_sync(0xffffffffu, tl, 0);
             if (__all_sync(0xffffffffu, tl == tl0)) {
@@ -192,8 +206,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
                 if (lane == 0 && bits) atomicMax(&s_max[tl0], bits);
             } else if (bits) atomicMax(&s_max[tl], bits);
         }
-    }
-    if (!no_scan) {
         for (int idx = tid + CT * UMAX; idx < scan_items; idx += CT) {
             const int tl = idx / sn, u = su0 + idx - tl * sn, tok = t0 + tl;
             if (tok < M && u * 16 < p.K) {
@@ -283,62 +295,125 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
     const int g8 = lane >> 2, t4 = lane & 3;
     const bool col_live = g8 < M;
     const uint32_t xs_lane = xs_base + (uint32_t)(g8 * 16 + t4 * 4);
-    const uint32_t ring_lane = smem_u32(ring) + (uint32_t)(g8 * 16 + t4 * 4);
+    const uint32_t ring_lane = smem_u32(ring) + (uint32_t)(DOT ? lane * 16 : g8 * 16 + t4 * 4);
     const int tok_out = tid >> 5;                         // epilogue: this thread's token; its channel is `lane`
     const float sx = (tok_out < M && !verdict) ? __uint_as_float(s_scale[tok_out]) : 0.f;
     uint32_t run_max = 0;
     int stage_i = 0;
     for (int j = 0; j < my_items; ++j) {
         const int item = (int)blockIdx.x + j * ncta;
-        int acc[2][2][4];                                 // [gate | up][m16 tile][fragment]
+        if constexpr (DOT) {
+            // Integer dot products: lane = channel of the group, every lane the same 32 activations of a chunk
+            // (broadcast reads).  One weight word holds eight codes; (w << 4) & mask and w & mask are the two
+            // int8 x 16 words that pair with the chunk's first and second sixteen activations.
+            int dacc[2][4];
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
-            if (g >= gpi) break;
-            int a0[2][4], a1[2][4];
+            for (int g = 0; g < 2; ++g)
 #pragma unroll
-            for (int m = 0; m < 2; ++m)
+                for (int t = 0; t < 4; ++t) dacc[g][t] = 0;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) { a0[m][e] = 0; a1[m][e] = 0; }
-            for (int s = 0; s < spg; ++s, ++stage_i) {
-                const int slot = stage_i % R;
-                if (!mbar_wait_warp(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
-                if (!verdict && !failed) {
-                    const int c0 = s * DEC_STAGE_CHUNKS, nch = min(DEC_STAGE_CHUNKS, KC - c0);
-                    const uint32_t wslot = ring_lane + (uint32_t)slot * DEC_STAGE_BYTES;
-                    auto chunk = [&](int cc, int (&a)[2][4]) {
-                        const uint32_t wb = wslot + (uint32_t)cc * 512u;
-                        const uint32_t w00 = lds32(wb), w01 = lds32(wb + 128), w10 = lds32(wb + 256), w11 = lds32(wb + 384);
-                        const uint32_t xb = xs_lane + (uint32_t)((c0 + cc) * 2 * Mc) * 16u;
-                        uint32_t b0 = 0, b1 = 0;
-                        if (col_live) { b0 = lds32(xb); b1 = lds32(xb + (uint32_t)Mc * 16u); }
-                        mma_s8(a[0], (w00 << 4) & 0xF0F0F0F0u, (w01 << 4) & 0xF0F0F0F0u, w00 & 0xF0F0F0F0u, w01 & 0xF0F0F0F0u, b0, b1);
-                        mma_s8(a[1], (w10 << 4) & 0xF0F0F0F0u, (w11 << 4) & 0xF0F0F0F0u, w10 & 0xF0F0F0F0u, w11 & 0xF0F0F0F0u, b0, b1);
-                    };
-                    // two accumulator sets halve the chains of dependent MMAs
-                    for (int cc = warp; cc < nch; cc += 2 * DEC_WARPS) {
-                        chunk(cc, a0);
-                        if (cc + DEC_WARPS < nch) chunk(cc + DEC_WARPS, a1);
+            for (int g = 0; g < 2; ++g) {
+                if (g >= gpi) break;
+                for (int s = 0; s < spg; ++s, ++stage_i) {
+                    const int slot = stage_i % R;
+                    if (!mbar_wait_warp(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
+                    if (!verdict && !failed) {
+                        const int c0 = s * DEC_STAGE_CHUNKS, nch = min(DEC_STAGE_CHUNKS, KC - c0);
+                        const uint32_t wslot = ring_lane + (uint32_t)slot * DEC_STAGE_BYTES;
+#pragma unroll 4
+                        for (int cc = warp; cc < nch; cc += DEC_WARPS) {
+                            uint32_t w[4];
+                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(wslot + (uint32_t)cc * 512u));
+                            const uint32_t xb = xs_base + (uint32_t)((c0 + cc) * 2 * Mc) * 16u;
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                if (t >= Mc) break;
+                                uint32_t x0[4], x1[4];
+                                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(x0[0]), "=r"(x0[1]), "=r"(x0[2]), "=r"(x0[3]) : "r"(xb + (uint32_t)t * 16u));
+                                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(x1[0]), "=r"(x1[1]), "=r"(x1[2]), "=r"(x1[3]) : "r"(xb + (uint32_t)(Mc + t) * 16u));
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    dacc[g][t] = __dp4a((int)((w[q] << 4) & 0xF0F0F0F0u), (int)x0[q], dacc[g][t]);
+                                    dacc[g][t] = __dp4a((int)(w[q] & 0xF0F0F0F0u), (int)x1[q], dacc[g][t]);
+                                }
+                            }
+                        }
                     }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[slot]);
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[slot]);
             }
+            if (TRACE && trace && j == my_items - 1) trace[5] = (unsigned long long)(clock64() - c_start);
+            // partial sums: [warp][token][row], row = lane (+ 32 for the up group)
 #pragma unroll
-            for (int m = 0; m < 2; ++m)
+            for (int g = 0; g < 2; ++g) {
+                if (g >= gpi) break;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) acc[g][m][e] = a0[m][e] + a1[m][e];
+                for (int t = 0; t < 4; ++t)
+                    if (t < Mc) red[(warp * 4 + t) * rows + g * 32 + lane] = dacc[g][t];
+            }
+        } else {
+            int acc[2][2][4];                                 // [gate | up][m16 tile][fragment]
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+                if (g >= gpi) break;
+                // four accumulator sets: a warp's four chunks of a stage are independent MMAs, so their loads and the
+                // long latency of the legacy int8 MMA overlap
+                int a[4][2][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int m = 0; m < 2; ++m)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) a[i][m][e] = 0;
+                for (int s = 0; s < spg; ++s, ++stage_i) {
+                    const int slot = stage_i % R;
+                    if (!mbar_wait_warp(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
+                    if (!verdict && !failed) {
+                        const int c0 = s * DEC_STAGE_CHUNKS, nch = min(DEC_STAGE_CHUNKS, KC - c0);
+                        const uint32_t wslot = ring_lane + (uint32_t)slot * DEC_STAGE_BYTES;
+                        uint32_t w[4][4], b[4][2];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int cc = warp + DEC_WARPS * i;
+                            const bool live = cc < nch;
+                            const uint32_t wb = wslot + (uint32_t)cc * 512u;
+                            const uint32_t xb = xs_lane + (uint32_t)((c0 + cc) * 2 * Mc) * 16u;
+#pragma unroll
+                            for (int r = 0; r < 4; ++r) w[i][r] = live ? lds32(wb + r * 128) : 0u;
+                            b[i][0] = (live && col_live) ? lds32(xb) : 0u;
+                            b[i][1] = (live && col_live) ? lds32(xb + (uint32_t)Mc * 16u) : 0u;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            if (warp + DEC_WARPS * i < nch) {
+                                mma_s8(a[i][0], (w[i][0] << 4) & 0xF0F0F0F0u, (w[i][1] << 4) & 0xF0F0F0F0u, w[i][0] & 0xF0F0F0F0u,
+                                       w[i][1] & 0xF0F0F0F0u, b[i][0], b[i][1]);
+                                mma_s8(a[i][1], (w[i][2] << 4) & 0xF0F0F0F0u, (w[i][3] << 4) & 0xF0F0F0F0u, w[i][2] & 0xF0F0F0F0u,
+                                       w[i][3] & 0xF0F0F0F0u, b[i][0], b[i][1]);
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[slot]);
+                }
+#pragma unroll
+                for (int m = 0; m < 2; ++m)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[g][m][e] = (a[0][m][e] + a[1][m][e]) + (a[2][m][e] + a[3][m][e]);
+            }
+            if (TRACE && trace && j == my_items - 1) trace[5] = (unsigned long long)(clock64() - c_start);
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+                if (g >= gpi) break;
+#pragma unroll
+                for (int m = 0; m < 2; ++m)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        red[red_index(warp, rows, g * 32 + m * 16 + g8 + (e >> 1) * 8, 2 * t4 + (e & 1))] = acc[g][m][e];
+            }
         }
-        if (TRACE && trace && j == my_items - 1) trace[5] = (unsigned long long)(clock64() - c_start);
         // ---- 4. sum the warps' partial sums, dequantise, store
-#pragma unroll
-        for (int g = 0; g < 2; ++g) {
-            if (g >= gpi) break;
-#pragma unroll
-            for (int m = 0; m < 2; ++m)
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    red[red_index(warp, rows, g * 32 + m * 16 + g8 + (e >> 1) * 8, 2 * t4 + (e & 1))] = acc[g][m][e];
-        }
         bar_sync_contraction();
         const float ca = sw_a, cb = sw_b;
         if (j + 1 < my_items) load_channel_scales(item + ncta);
@@ -346,8 +421,13 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
             int v = 0, u = 0;
 #pragma unroll
             for (int w = 0; w < DEC_WARPS; ++w) {
-                v += red[red_index(w, rows, lane, tok_out)];
-                if (swiglu) u += red[red_index(w, rows, 32 + lane, tok_out)];
+                if constexpr (DOT) {
+                    v += red[(w * 4 + tok_out) * rows + lane];
+                    if (swiglu) u += red[(w * 4 + tok_out) * rows + 32 + lane];
+                } else {
+                    v += red[red_index(w, rows, lane, tok_out)];
+                    if (swiglu) u += red[red_index(w, rows, 32 + lane, tok_out)];
+                }
             }
             v >>= 4;   // exact: the unpacked weights are 16 x code
             u >>= 4;
@@ -436,10 +516,10 @@ int gemm_decode_ctas(int items, int cluster, int cap)
     return best;
 }
 
-template <bool HALF, bool TRACE>
+template <bool HALF, bool DOT, bool TRACE>
 static cudaError_t launch_decode_inst(const DecodeParams& p, cudaStream_t stream, bool pdl)
 {
-    auto kernel = gemm_decode_kernel<HALF, TRACE>;
+    auto kernel = gemm_decode_kernel<HALF, DOT, TRACE>;
     static PerDeviceOnce configured;
     int device = -1;
     if (configured.needed(device)) {
@@ -478,15 +558,20 @@ cudaError_t launch_gemm_decode(const DecodeParams& p, cudaStream_t stream, bool 
         p.ring > DEC_MAX_RING || p.ctas < p.cluster || p.ctas % p.cluster || (swiglu && p.F % GROUP) ||
         dec_smem_bytes(p.M, p.KB, swiglu, p.ring) > DEC_SMEM_LIMIT || (long long)p.KB * KBLOCK > 131072)
         return cudaErrorInvalidValue;
-    if (p.trace) return p.half ? launch_decode_inst<true, true>(p, stream, pdl) : launch_decode_inst<false, true>(p, stream, pdl);
-    return p.half ? launch_decode_inst<true, false>(p, stream, pdl) : launch_decode_inst<false, false>(p, stream, pdl);
+    const bool dot = p.M <= 4;
+    if (p.trace) {
+        if (dot) return p.half ? launch_decode_inst<true, true, true>(p, stream, pdl) : launch_decode_inst<false, true, true>(p, stream, pdl);
+        return p.half ? launch_decode_inst<true, false, true>(p, stream, pdl) : launch_decode_inst<false, false, true>(p, stream, pdl);
+    }
+    if (dot) return p.half ? launch_decode_inst<true, true, false>(p, stream, pdl) : launch_decode_inst<false, true, false>(p, stream, pdl);
+    return p.half ? launch_decode_inst<true, false, false>(p, stream, pdl) : launch_decode_inst<false, false, false>(p, stream, pdl);
 }
 
 // Resident clusters of this kernel with `smem` bytes of dynamic shared memory, times the cluster size:
 // the most CTAs a launch may have if all of them are to run at once.
 int gemm_decode_resident_ctas(int cluster, size_t smem, int sm_count)
 {
-    auto kernel = gemm_decode_kernel<true, false>;
+    auto kernel = gemm_decode_kernel<true, false, false>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_LIMIT) != cudaSuccess) {
         cudaGetLastError();
         return sm_count / cluster * cluster;

@@ -1,7 +1,6 @@
 // w4a8_unbuilt.cpp -- entry points of the original project's public headers that this library
 // does not implement: the W8A8 operators and their tuners (include/rk_npu_quant_matmul.h), the
-// exact int4 x int4 -> int32 API (include/rk_npu_matmul_i4.h), the search-based W4A8 tuners and
-// their family forms (include/rk_npu_w4a8_tune.h) and the DMA-buffer helpers of
+// exact int4 x int4 -> int32 API (include/rk_npu_matmul_i4.h), and the DMA-buffer helpers of
 // include/rk_npu_common.h.  They are exported so that programs written against those headers
 // link and start; each one declines: RK_NPU_ERR_PARAM, NULL, or 0, and does nothing else.
 // C linkage carries no parameter types, so the definitions take none; the callers' arguments
@@ -47,14 +46,6 @@ RKB200_DECLINE_INT(rk_npu_mem_free)
 RKB200_DECLINE_INT(rk_npu_mem_import_dmabuf)
 RKB200_DECLINE_INT(rk_npu_mem_sync)
 RKB200_DECLINE_INT(rk_npu_mem_view)
-RKB200_DECLINE_INT(rk_npu_w4a8_autotune)
-RKB200_DECLINE_INT(rk_npu_w4a8_autotune_cached)
-RKB200_DECLINE_INT(rk_npu_w4a8_autotune_cached_ex)
-RKB200_DECLINE_INT(rk_npu_w4a8_autotune_ex)
-RKB200_DECLINE_INT(rk_npu_w4a8_autotune_family)
-RKB200_DECLINE_INT(rk_npu_w4a8_autotune_family_cached)
-RKB200_DECLINE_INT(rk_npu_w4a8_autotune_family_cached_ex)
-RKB200_DECLINE_INT(rk_npu_w4a8_autotune_family_ex)
 
 // constructors: no object
 RKB200_DECLINE_PTR(rk_npu_f16i8f16_weights_create)

@@ -118,11 +118,20 @@ def _print_stamps(rk, case, calls, stream, torch):
                     fn()
         stream.synchronize()
     torch.cuda.synchronize()
+    if graph is not None:
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            t0.record(stream)
+            for _ in range(20):
+                graph.replay()
+            t1.record(stream)
+        stream.synchronize()
+        print(f"graph replay: {t0.elapsed_time(t1) * 1e3 / 20:.1f} us per set of {len(calls)} linears")
     if case == "decode":
         prev_end = None
         print("per linear, ns relative to the previous linear's last CTA end: first/last CTA start, first/last CTA end;"
-              " then median cycles since CTA start at: weights requested, dependency met, scales known, slice quantised,"
-              " contraction done, partials exchanged")
+              " then median cycles since CTA start at (decode kernel): before the dependency wait, dependency met, share"
+              " quantised and sent, all codes landed, last contraction done, last output stored")
         for i, (_, ws) in enumerate(calls):
             buf = np.zeros((4096, 8), np.uint64)
             lib.rk_npu_b200_w4a8_trace_read(ws.handle, buf.ctypes.data, 4096)
