@@ -19,12 +19,41 @@ extern "C" {
 
 /* CUDA ordinal the context runs on; -1 for NULL or an offline context. */
 int rk_npu_b200_device(const rk_npu_ctx *ctx);
+/* The driver version the context writes into tuning-cache keys (the CUDA driver version of an online
+ * context; what rk_npu_b200_open_offline was given for an offline one); 0 for NULL. */
+uint32_t rk_npu_b200_driver_version(const rk_npu_ctx *ctx);
 
 /* A context with no GPU behind it, for tools that inspect or write tuning caches and
  * query memory requirements on a machine without a device.  driver_version is the value
  * the cache key should carry.  Only the tuning-cache, profile and *_query functions
  * accept it; rk_npu_iommu_domain_create returns NULL for it.  Close with rk_npu_close. */
 rk_npu_ctx *rk_npu_b200_open_offline(uint32_t driver_version);
+
+/* ---- A group of GPUs: column sharding inside the library ------------------------------------------
+ * The original splits a GEMM's output columns over its NPU cores in contiguous runs of 64-column blocks
+ * (src/rk_npu_i4_plan.cpp:37-43).  A group context does the same over the GPUs of a box, one process per
+ * GPU: rank 0 calls rk_npu_b200_group_id, hands the 128 bytes to the other ranks by whatever means the
+ * application has (MPI, a file, torch.distributed ...), and every rank opens its context with
+ * rk_npu_b200_open_group(dev, rank, world, id).  From then on the ordinary interface applies unchanged:
+ *   - rk_npu_w4a8_weights_create[_tuned] takes the FULL B[K,N] and w_scale[N] on every rank and keeps this
+ *     rank's columns (N % 128 == 0: the same slice of both halves of N, so a [gate | up] packing keeps its
+ *     SwiGLU pairs on one GPU; otherwise one contiguous run);
+ *   - workspaces are created with the full (M, N, K);
+ *   - rk_npu_w4a8_run_f32 / _f16 and their enqueue forms take the full A on every rank (activations are
+ *     replicated), compute this rank's columns, all-gather them over NVLink (NCCL, C API, loaded on first
+ *     use) and leave the full C on every rank;
+ *   - rk_npu_w4a8_run_swiglu_f32 / _ffn_f32 (N % 128 == 0 for the gate/up weights) do the same for the
+ *     middle tensor; the down projection's row scales are the all-reduced (integer maximum) row maxima.
+ * Results are bit-identical to a single GPU's for any group size.  Every rank must make the same calls in
+ * the same order (they contain collectives).  A rank whose communicator cannot be created gets NULL from
+ * rk_npu_b200_open_group before any GPU work.  None of this has a counterpart in the original project. */
+#define RK_NPU_B200_GROUP_ID_BYTES 128
+int rk_npu_b200_group_id(unsigned char *id);
+rk_npu_ctx *rk_npu_b200_open_group(const char *dev, int rank, int world, const unsigned char *id);
+int rk_npu_b200_group_rank(const rk_npu_ctx *ctx);   /* 0 outside a group; -1 for NULL */
+int rk_npu_b200_group_size(const rk_npu_ctx *ctx);   /* 1 outside a group; 0 for NULL */
+/* The partition rule itself: [*n0, *n1) of `rank` among `world` for N columns. */
+int rk_npu_b200_shard_columns(int N, int world, int rank, int *n0, int *n1);
 
 /* Queue one W4A8 linear on `cuda_stream` (a cudaStream_t; NULL = the legacy default
  * stream).  dA / dC are device pointers on the context's GPU with the shapes of the

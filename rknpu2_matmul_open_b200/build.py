@@ -11,7 +11,7 @@ CSRC = HERE / "csrc"
 LIB_DIR = HERE / "lib"
 LIB = LIB_DIR / "librk_npu_matmul_b200.so"
 TOOLS = ["int8_peak.cu", "bulk_copy_bw.cu"]
-SOURCES = ["w4a8_kernels.cu", "w4a8_fused.cu", "w4a8_decode.cu", "w4a8_stream.cu", "w4a8_shard.cu", "w4a8_gemm_tc.cu", "w4a8_gemm_tc_persist.cu", "w4a8_abi.cpp", "w4a8_tune.cpp", "w4a8_autotune.cpp", "w4a8_unbuilt.cpp"]
+SOURCES = ["w4a8_kernels.cu", "w4a8_fused.cu", "w4a8_decode.cu", "w4a8_stream.cu", "w4a8_shard.cu", "w4a8_gemm_tc.cu", "w4a8_gemm_tc_persist.cu", "w4a8_abi.cpp", "w4a8_group.cpp", "w4a8_tune.cpp", "w4a8_autotune.cpp", "w4a8_unbuilt.cpp"]
 HEADERS = ["w4a8_device.h", "w4a8_host.h", "w4a8_tune.h", "w4a8_ptx.cuh", "w4a8_math.cuh", "w4a8_tc.cuh", "../../include/rknpu_b200_w4a8.h", "../../include/rknpu_b200_ext.h"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -48,7 +48,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         if out.returncode:
             raise RuntimeError(f"nvcc failed on {src}:\n{out.stdout}\n{out.stderr}")
         objects.append(str(obj))
-    link = [_nvcc(), "-shared", "-o", str(LIB), *objects, "-cudart", "static", "-Xlinker", "-Bsymbolic",
+    link = [_nvcc(), "-shared", "-o", str(LIB), *objects, "-cudart", "static", "-ldl", "-Xlinker", "-Bsymbolic",
             "-Xlinker", f"--version-script={CSRC / 'exports.map'}", "-lpthread"]
     out = subprocess.run(link, capture_output=True, text=True)
     if out.returncode:

@@ -129,6 +129,11 @@ class W4A8StrategyEx(C.Structure):
     _fields_ = [("base", W4A8Strategy), ("execution", W4A8Options)]
 
 
+class W4A8FamilySummary(C.Structure):
+    _fields_ = [("weights", W4A8WeightInfo), ("weight_fingerprint", C.c_uint64), ("weighted_total_us", C.c_double),
+                ("weighted_robust_us", C.c_double)]
+
+
 _P = C.c_void_p
 _SIGNATURES = {
     # context, domains
@@ -184,8 +189,35 @@ _SIGNATURES = {
                                                     C.POINTER(MatmulStrategy), C.POINTER(MatmulStrategy)]),
     "rk_npu_i4_config_init": (None, [C.POINTER(I4Config), C.c_int, C.c_int, C.c_int]),
     "rk_npu_w4a8_family_config_init": (None, [C.POINTER(W4A8FamilyConfig), C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int)]),
+    # search tuner
+    "rk_npu_w4a8_autotune": (C.c_int, [_P, C.POINTER(W4A8AutotuneConfig), _P, _P, C.POINTER(W4A8Strategy), C.POINTER(W4A8Strategy)]),
+    "rk_npu_w4a8_autotune_ex": (C.c_int, [_P, C.POINTER(W4A8AutotuneConfig), _P, _P, C.POINTER(W4A8StrategyEx),
+                                          C.POINTER(W4A8StrategyEx)]),
+    "rk_npu_w4a8_autotune_cached": (C.c_int, [_P, C.POINTER(W4A8AutotuneConfig), _P, _P, C.c_char_p, C.c_int,
+                                              C.POINTER(W4A8Strategy), C.POINTER(W4A8Strategy), C.POINTER(C.c_int)]),
+    "rk_npu_w4a8_autotune_cached_ex": (C.c_int, [_P, C.POINTER(W4A8AutotuneConfig), _P, _P, C.c_char_p, C.c_int,
+                                                 C.POINTER(W4A8StrategyEx), C.POINTER(W4A8StrategyEx), C.POINTER(C.c_int)]),
+    "rk_npu_w4a8_autotune_family": (C.c_int, [_P, C.POINTER(W4A8FamilyConfig), _P, _P, C.POINTER(W4A8FamilySummary),
+                                              C.POINTER(W4A8Strategy), C.POINTER(W4A8FamilySummary), C.POINTER(W4A8Strategy)]),
+    "rk_npu_w4a8_autotune_family_ex": (C.c_int, [_P, C.POINTER(W4A8FamilyConfig), _P, _P, C.POINTER(W4A8FamilySummary),
+                                                 C.POINTER(W4A8StrategyEx), C.POINTER(W4A8FamilySummary),
+                                                 C.POINTER(W4A8StrategyEx)]),
+    "rk_npu_w4a8_autotune_family_cached": (C.c_int, [_P, C.POINTER(W4A8FamilyConfig), _P, _P, C.c_char_p, C.c_int,
+                                                     C.POINTER(W4A8FamilySummary), C.POINTER(W4A8Strategy),
+                                                     C.POINTER(W4A8FamilySummary), C.POINTER(W4A8Strategy),
+                                                     C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "rk_npu_w4a8_autotune_family_cached_ex": (C.c_int, [_P, C.POINTER(W4A8FamilyConfig), _P, _P, C.c_char_p, C.c_int,
+                                                        C.POINTER(W4A8FamilySummary), C.POINTER(W4A8StrategyEx),
+                                                        C.POINTER(W4A8FamilySummary), C.POINTER(W4A8StrategyEx),
+                                                        C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     # B200 extensions
     "rk_npu_b200_device": (C.c_int, [_P]),
+    "rk_npu_b200_driver_version": (C.c_uint32, [_P]),
+    "rk_npu_b200_group_id": (C.c_int, [_P]),
+    "rk_npu_b200_open_group": (_P, [C.c_char_p, C.c_int, C.c_int, _P]),
+    "rk_npu_b200_group_rank": (C.c_int, [_P]),
+    "rk_npu_b200_group_size": (C.c_int, [_P]),
+    "rk_npu_b200_shard_columns": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "rk_npu_b200_open_offline": (_P, [C.c_uint32]),
     "rk_npu_b200_w4a8_enqueue_f32": (C.c_int, [_P, _P, _P, _P, _P]),
     "rk_npu_b200_w4a8_enqueue_f16": (C.c_int, [_P, _P, _P, _P, _P]),

@@ -233,6 +233,7 @@ private:
 int validate(const rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const void* A, const void* C, bool swiglu)
 {
     if (!ws || !w || !A || !C || A == C || (swiglu && (ws->npu_reduce || ws->config.N % 64))) return RK_NPU_ERR_PARAM;
+    if (swiglu && ws->domain->ctx->world > 1 && !ws->shard.two_range) return RK_NPU_ERR_PARAM;   // gate/up pairs must share a GPU
     if (w->ctx_id != ws->ctx_id || w->domain_id != ws->domain_id) return RK_NPU_ERR_DOMAIN;
     const auto& wc = w->info.config;
     if (wc.K != ws->config.K || wc.N != ws->config.N || wc.k_tile != ws->config.k_tile) return RK_NPU_ERR_PARAM;
@@ -315,8 +316,9 @@ int enqueue(const Call& c)
     const auto& cfg = ws.config;
     const bool pdl = env_flag("RK_NPU_B200_PDL", true);
     if (c.events) cudaEventRecord(c.events[0], c.stream);
-    const int F = c.epi == EPI_SWIGLU ? cfg.N / 2 : 0;
-    const int tiles = c.epi == EPI_SWIGLU ? (F + 63) / 64 : (cfg.N + TILE_N - 1) / TILE_N;
+    const int N = ws.shard_N;                       // the columns this GPU computes (all of them outside a group)
+    const int F = c.epi == EPI_SWIGLU ? N / 2 : 0;
+    const int tiles = c.epi == EPI_SWIGLU ? (F + 63) / 64 : (N + TILE_N - 1) / TILE_N;
     const unsigned long long timeout_ns = (unsigned long long)cfg.timeout_ms * 1000000ull;
     if (ws.variant == 5 && !c.codes_in) {
         // One kernel, whole-K CTAs: scan + quantise (shared by a cluster) + GEMM + epilogue.
@@ -330,14 +332,14 @@ int enqueue(const Call& c)
         d.scales_out = ws.scales;
         d.codes_out = c.keep_codes ? ws.codes : nullptr;
         d.status = ws.status;
-        d.M = cfg.M; d.N = cfg.N; d.K = cfg.K;
+        d.M = cfg.M; d.N = N; d.K = cfg.K;
         d.KB = ws.KB; d.NG = c.w->NG; d.F = F; d.epi = c.epi;
         d.half = c.half ? 1 : 0;
         const bool swiglu = c.epi == EPI_SWIGLU;
         d.cluster = ws.split_override ? ws.split_override : gemm_decode_cluster(cfg.M, ws.KB);
         d.ring = gemm_decode_ring(cfg.M, ws.KB, swiglu);
         const int slot = d.cluster == 1 ? 0 : d.cluster == 2 ? 1 : d.cluster == 4 ? 2 : 3;
-        d.ctas = gemm_decode_ctas(swiglu ? F / GROUP : (cfg.N + GROUP - 1) / GROUP, d.cluster, ws.decode_cap[slot]);
+        d.ctas = gemm_decode_ctas(swiglu ? F / GROUP : (N + GROUP - 1) / GROUP, d.cluster, ws.decode_cap[slot]);
         d.timeout_ns = timeout_ns;
         d.trace = ws.trace;
         if (c.events) cudaEventRecord(c.events[1], c.stream);
@@ -358,7 +360,7 @@ int enqueue(const Call& c)
         f.scales_out = ws.scales;
         f.codes_out = c.keep_codes ? ws.codes : nullptr;
         f.status = ws.status;
-        f.M = cfg.M; f.N = cfg.N; f.K = cfg.K;
+        f.M = cfg.M; f.N = N; f.K = cfg.K;
         f.KB = ws.KB; f.NG = c.w->NG; f.F = F; f.epi = c.epi;
         f.split = fused_split(ws, tiles);
         f.stages = (ws.KB + f.split - 1) / f.split;
@@ -411,7 +413,7 @@ int enqueue(const Call& c)
     g.rowmax = c.rowmax_out;
     g.status = ws.status;
     g.M = cfg.M;
-    g.N = cfg.N;
+    g.N = N;
     g.K = cfg.K;
     g.KB = ws.KB;
     g.NG = c.w->NG;
@@ -464,6 +466,42 @@ int status_to_rc(rk_npu_w4a8_workspace& ws, cudaStream_t stream)
     return s.bad_input ? RK_NPU_ERR_PARAM : RK_NPU_OK;
 }
 
+// Group of GPUs: the kernels have written this rank's compact [M][its columns] block into its slot of the
+// workspace's gather buffer; one all-gather brings the other ranks' blocks and a copy kernel puts every row piece
+// at its place in `dst` [M][cols] (elements of `elem` bytes).
+int gather_output(rk_npu_w4a8_workspace& ws, void* dst, int cols, int elem, bool two_range, cudaStream_t stream)
+{
+    rk_npu_ctx* ctx = ws.domain->ctx;
+    if (const int rc = group_all_gather(ctx, ws.gather, ws.gather_slot, stream)) return rc;
+    AssembleParams a{};
+    a.gathered = ws.gather;
+    a.out = static_cast<uint8_t*>(dst);
+    a.slot_bytes = ws.gather_slot;
+    a.M = ws.config.M;
+    a.N = cols;
+    a.world = ctx->world;
+    a.elem = elem;
+    a.two_range = two_range ? 1 : 0;
+    if (launch_assemble_columns(a, stream) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+    ws.launches.fetch_add(1, std::memory_order_relaxed);
+    return RK_NPU_OK;
+}
+bool grouped(const rk_npu_w4a8_workspace& ws) { return ws.domain->ctx->world > 1; }
+void* own_slot(const rk_npu_w4a8_workspace& ws) { return ws.gather + size_t(ws.domain->ctx->rank) * ws.gather_slot; }
+int element_bytes(int epi) { return epi == EPI_F16 ? 2 : 4; }
+
+// One linear queued on `stream`: outside a group straight into dOut; in a group into this rank's slot, then the
+// exchange that leaves the whole [M][columns] tensor in dOut on every rank.
+int enqueue_linear(Call call, void* dOut)
+{
+    auto& ws = *call.ws;
+    call.dOut = grouped(ws) ? own_slot(ws) : dOut;
+    if (const int rc = enqueue(call)) return rc;
+    if (!grouped(ws)) return RK_NPU_OK;
+    const bool swiglu = call.epi == EPI_SWIGLU;
+    return gather_output(ws, dOut, swiglu ? ws.config.N / 2 : ws.config.N, element_bytes(call.epi), !swiglu && ws.shard.two_range, call.stream);
+}
+
 // One blocking projection; the caller holds the workspace.
 int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const void* A, void* C, bool half, int epi,
                rk_npu_w4a8_timings* metrics)
@@ -487,7 +525,7 @@ int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const vo
     if (!c_dev) dC = ws->stage_out;
     t.sync_us += elapsed_us(copy_start);
     Call call{ws, w, dA, dC, half, epi, nullptr, nullptr, s, metrics ? ws->events : nullptr, epi == EPI_I32};
-    int rc = enqueue(call);
+    int rc = enqueue_linear(call, dC);
     if (rc) { cudaStreamSynchronize(s); return rc; }
     copy_start = Clock::now();
     // Host tensors are copied straight from and to the caller's (pageable) memory: bouncing small ones through
@@ -531,6 +569,7 @@ void workspace_destroy(rk_npu_w4a8_workspace* ws)
     if (ws->trace) device_free(d, ws->trace, ws->trace_bytes);
     if (ws->partials) device_free(d, ws->partials, ws->partials_bytes);
     if (ws->counts) device_free(d, ws->counts, ws->counts_bytes);
+    if (ws->gather) device_free(d, ws->gather, ws->gather_bytes);
     if (ws->host_status) cudaFreeHost(ws->host_status);
     for (auto& e : ws->events) if (e) cudaEventDestroy(e);
     if (ws->stream) cudaStreamDestroy(ws->stream);
@@ -624,10 +663,12 @@ extern "C" void rk_npu_close(rk_npu_ctx* ctx)
     if (ctx->device < 0) { delete ctx; return; }
     cudaSetDevice(ctx->device);
     if (ctx->stream) { cudaStreamSynchronize(ctx->stream); cudaStreamDestroy(ctx->stream); }
+    group_close(ctx);
     delete ctx;
 }
 
 extern "C" int rk_npu_b200_device(const rk_npu_ctx* ctx) { return ctx ? ctx->device : -1; }
+extern "C" uint32_t rk_npu_b200_driver_version(const rk_npu_ctx* ctx) { return ctx ? ctx->driver_version : 0; }
 
 extern "C" rk_npu_iommu_domain* rk_npu_iommu_domain_create(rk_npu_ctx* ctx, uint32_t domain_id)
 {
@@ -758,8 +799,28 @@ rk_npu_w4a8_weights* rkb200::create_weights(rk_npu_iommu_domain* domain, const r
     auto* ctx = domain->ctx;
     if (cudaSetDevice(ctx->device) != cudaSuccess) return nullptr;
     w->info = info;
+    // In a group of GPUs this object holds its rank's columns only; identity (profile, fingerprint, the checks
+    // above) is that of the whole matrix, so every rank agrees on it.
+    w->shard = shard_plan(key.N, ctx->world, ctx->rank);
+    w->shard_N = w->shard.columns();
+    const int local_N = std::max(w->shard_N, 1);            // a rank beyond the last block still builds valid (empty) tensors
+    std::vector<int8_t> local_B;
+    std::vector<float> local_scales;
+    if (ctx->world > 1) {
+        local_B.assign(size_t(key.K) * local_N, 0);
+        local_scales.assign(size_t(local_N), 1.0f);
+        const int width = w->shard.n1 - w->shard.n0, pieces = w->shard.two_range ? 2 : 1;
+        for (int piece = 0; piece < pieces; ++piece) {
+            const int from = piece * (key.N / 2) + w->shard.n0, to = piece * width;
+            for (int k = 0; k < key.K; ++k)
+                std::memcpy(local_B.data() + size_t(k) * local_N + to, B + size_t(k) * key.N + from, size_t(width));
+            std::memcpy(local_scales.data() + to, scales + from, sizeof(float) * size_t(width));
+        }
+        B = local_B.data();
+        scales = local_scales.data();
+    }
     w->KB = (key.K + KBLOCK - 1) / KBLOCK;
-    w->NG = align_up((key.N + GROUP - 1) / GROUP, 8) + 8;   // zero groups: odd tile counts of CTA pairs, SwiGLU tails
+    w->NG = align_up((local_N + GROUP - 1) / GROUP, 8) + 8;   // zero groups: odd tile counts of CTA pairs, SwiGLU tails
     w->packed_bytes = size_t(w->NG) * (size_t(w->KB) * 4) * 512;
     w->scale_bytes = size_t(w->NG) * GROUP * sizeof(float);
     w->domain = domain;
@@ -776,7 +837,7 @@ rk_npu_w4a8_weights* rkb200::create_weights(rk_npu_iommu_domain* domain, const r
     if (device_alloc(domain, reinterpret_cast<void**>(&w->scales), w->scale_bytes)) return fail();
     int8_t* codes = nullptr;
     int* error = nullptr;
-    const size_t code_bytes = size_t(key.K) * key.N;
+    const size_t code_bytes = size_t(key.K) * local_N;
     bool ok = cudaMalloc(reinterpret_cast<void**>(&codes), code_bytes) == cudaSuccess &&
               cudaMalloc(reinterpret_cast<void**>(&error), sizeof(int)) == cudaSuccess;
     if (ok) {
@@ -784,9 +845,9 @@ rk_npu_w4a8_weights* rkb200::create_weights(rk_npu_iommu_domain* domain, const r
         ok = cudaMemcpyAsync(codes, B, code_bytes, cudaMemcpyHostToDevice, s) == cudaSuccess &&
              cudaMemsetAsync(error, 0, sizeof(int), s) == cudaSuccess &&
              cudaMemsetAsync(w->scales, 0, w->scale_bytes, s) == cudaSuccess &&
-             cudaMemcpyAsync(w->scales, scales, sizeof(float) * key.N, cudaMemcpyHostToDevice, s) == cudaSuccess;
+             cudaMemcpyAsync(w->scales, scales, sizeof(float) * local_N, cudaMemcpyHostToDevice, s) == cudaSuccess;
         if (ok) {
-            PackParams p{codes, w->packed, error, key.K, key.N, w->KB * 4, w->NG};
+            PackParams p{codes, w->packed, error, key.K, local_N, w->KB * 4, w->NG};
             ok = launch_pack_weights(p, s) == cudaSuccess;
         }
         int host_error = 1;
@@ -871,10 +932,14 @@ rk_npu_w4a8_workspace* rkb200::create_workspace_scheduled(rk_npu_iommu_domain* d
     ws->domain_id = domain->id;
     domain_retain(domain);
     ws->KB = (cfg->K + KBLOCK - 1) / KBLOCK;
+    ws->shard = shard_plan(cfg->N, ctx->world, ctx->rank);
+    ws->shard_N = ws->shard.columns();
+    if (ws->shard_N < 1) { workspace_destroy(ws); return nullptr; }   // fewer 64-column blocks than GPUs in the group
+    const int local_N = ws->shard_N;      // what this GPU's kernels compute; schedules are chosen for it
     // Schedule: the mma.sync kernel serves up to 32 tokens per CTA pass; larger batches
     // go to the tcgen05 kernel when it can run this geometry.
     GemmParams probe{};
-    probe.M = cfg->M; probe.N = cfg->N; probe.K = cfg->K; probe.KB = ws->KB;
+    probe.M = cfg->M; probe.N = local_N; probe.K = cfg->K; probe.KB = ws->KB;
     // an explicit schedule (a tuned strategy) wins over the environment override, which wins over the rules below
     const int forced = schedule.family ? schedule.family : std::getenv("RK_NPU_B200_VARIANT") ? std::atoi(std::getenv("RK_NPU_B200_VARIANT")) : 0;
     const bool tc_ok = gemm_tc_supported(probe);
@@ -885,19 +950,19 @@ rk_npu_w4a8_workspace* rkb200::create_workspace_scheduled(rk_npu_iommu_domain* d
     // block; beyond that the two-kernel ring (quantise + mma.sync GEMM) streams better.  Up to 32
     // tokens the tcgen05 streaming kernel (4) is opt-in: its time does not depend on the batch
     // size, but it only overtakes the ring at 32 tokens.
-    const bool fused_best = fused_ok && cfg->M <= 8 && (long long)cfg->K * cfg->N / 2 <= (24ll << 20);
+    const bool fused_best = fused_ok && cfg->M <= 8 && (long long)cfg->K * local_N / 2 <= (24ll << 20);
     // Up to eight tokens: the decode kernel (5), whose CTAs own whole output channels over all of K, so a
     // launch has a single exchange (the int8 codes inside a cluster) instead of the two of the split-K kernel (3).
     const bool decode_ok = gemm_decode_supported(cfg->M, cfg->K);
     // 33..128 tokens: the per-tile tcgen05 kernel has one CTA per 128 output channels; when that is less than
     // half the SMs and K is long, the streaming kernel (all SMs, K split between CTAs) is faster.
     const bool stream_best = stream_ok && cfg->M > 32 && cfg->K >= 8192 &&
-                             (cfg->N + TILE_N - 1) / TILE_N * 2 <= ctx->sm_count;
+                             (local_N + TILE_N - 1) / TILE_N * 2 <= ctx->sm_count;
     // 33..128 tokens with so few tiles that tiles x 32-token chunks fit the SMs in one wave (N = 4096: 32 x 4): the
     // mma.sync ring, one CTA per (tile, chunk, K split), fills the GPU where the tcgen05 kernels leave SMs idle or
     // pay for combining partial tiles (11008 -> 4096 at 128 tokens: 33 us against 44 and 47 us).
     const bool ring_best = cfg->M > 32 && cfg->M <= 128 &&
-                           (long long)((cfg->N + TILE_N - 1) / TILE_N) * ((cfg->M + 31) / 32) <= ctx->sm_count;
+                           (long long)((local_N + TILE_N - 1) / TILE_N) * ((cfg->M + 31) / 32) <= ctx->sm_count;
     int variant = decode_ok ? 5 : ring_best ? 1 : (cfg->M > 32 && stream_best) ? 4 : (cfg->M > 32 && tc_ok) ? 2 : fused_best ? 3 : 1;
     if (forced == 1 || (forced == 2 && tc_ok) || (forced == 3 && fused_ok) || (forced == 4 && stream_ok) || (forced == 5 && decode_ok))
         variant = forced;
@@ -934,11 +999,16 @@ rk_npu_w4a8_workspace* rkb200::create_workspace_scheduled(rk_npu_iommu_domain* d
     ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->rowmax), sizeof(uint32_t) * cfg->M);
     ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->status), sizeof(Status));
     if (variant == 4) {
-        const size_t tiles = size_t(cfg->N + TILE_N - 1) / TILE_N;
+        const size_t tiles = size_t(local_N + TILE_N - 1) / TILE_N;
         ws->partials_bytes = 2 * size_t(ctx->sm_count) * 128 * size_t(ws->TC) * sizeof(int);   // two slots per CTA
         ws->counts_bytes = tiles * sizeof(unsigned int);
         ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->partials), ws->partials_bytes);
         ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->counts), ws->counts_bytes);
+    }
+    if (ctx->world > 1) {
+        ws->gather_slot = size_t(cfg->M) * size_t(shard_plan(cfg->N, ctx->world, 0).columns()) * 4;   // rank 0's share is the widest
+        ws->gather_bytes = ws->gather_slot * size_t(ctx->world);
+        ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->gather), ws->gather_bytes);
     }
     ok = ok && !device_alloc(domain, &ws->stage_in, ws->stage_in_bytes);
     ok = ok && !device_alloc(domain, &ws->stage_out, ws->stage_out_bytes);
@@ -1029,13 +1099,15 @@ extern "C" int rk_npu_w4a8_run_ffn_f32(rk_npu_w4a8_workspace* gate_up, const rk_
         t.gate_up.sync_us += elapsed_us(mark);
         cudaEvent_t* ev = metrics ? gate_up->events : nullptr;
         Call first{gate_up, gate_up_weights, dA, dMiddle, false, EPI_SWIGLU, gate_up->rowmax, nullptr, s, ev};
-        rc = enqueue(first);
+        rc = enqueue_linear(first, dMiddle);
+        // in a group every GPU has collected the maxima of its feature slice: the row maximum is their maximum
+        if (!rc && grouped(*gate_up)) rc = group_all_reduce_max_u32(gate_up->domain->ctx, gate_up->rowmax, size_t(M), s);
         if (!rc) {
             // Down quantises `middle` with scales finished from the collected row maxima:
             // no rescan (src/rk_npu_w4a8.cpp:112-121,376); a non-finite maximum makes the
             // down kernels return without work.
             Call second{down, down_weights, dMiddle, dC, false, EPI_F32, nullptr, gate_up->rowmax, s, metrics ? down->events : nullptr};
-            rc = enqueue(second);
+            rc = enqueue_linear(second, dC);
         }
         if (rc) { cudaStreamSynchronize(s); return rc; }
         mark = Clock::now();
@@ -1072,7 +1144,7 @@ int enqueue_public(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, cons
     WorkspaceLock lock(*ws);
     if (!lock) return RK_NPU_ERR_BUSY;
     Call call{ws, w, dA, dC, half, epi, nullptr, nullptr, static_cast<cudaStream_t>(stream), nullptr};
-    return enqueue(call);
+    return enqueue_linear(call, dC);
 }
 }
 extern "C" int rk_npu_b200_w4a8_enqueue_f32(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const float* dA,
@@ -1107,10 +1179,11 @@ extern "C" int rk_npu_b200_w4a8_enqueue_ffn_f32(rk_npu_w4a8_workspace* gate_up, 
     if (!down_lock) return RK_NPU_ERR_BUSY;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     Call first{gate_up, gate_up_weights, dA, dMiddle, false, EPI_SWIGLU, gate_up->rowmax, nullptr, s, nullptr};
-    rc = enqueue(first);
+    rc = enqueue_linear(first, dMiddle);
+    if (!rc && grouped(*gate_up)) rc = group_all_reduce_max_u32(gate_up->domain->ctx, gate_up->rowmax, size_t(gate_up->config.M), s);
     if (rc) return rc;
     Call second{down, down_weights, dMiddle, dC, false, EPI_F32, nullptr, gate_up->rowmax, s, nullptr};
-    return enqueue(second);
+    return enqueue_linear(second, dC);
 }
 
 // ---- column-sharded FFN: the pieces around the exchange between GPUs
@@ -1120,6 +1193,7 @@ extern "C" int rk_npu_b200_w4a8_enqueue_swiglu_collect_f32(rk_npu_w4a8_workspace
     if (!dRowMaxima) return RK_NPU_ERR_PARAM;
     const int rc = validate(ws, w, dA, dMiddle, true);
     if (rc) return rc;
+    if (grouped(*ws)) return RK_NPU_ERR_PARAM;   // a group context shards by itself; these pieces are for callers that shard by hand
     WorkspaceLock lock(*ws);
     if (!lock) return RK_NPU_ERR_BUSY;
     Call call{ws, w, dA, dMiddle, false, EPI_SWIGLU, dRowMaxima, nullptr, static_cast<cudaStream_t>(stream), nullptr};
@@ -1128,7 +1202,7 @@ extern "C" int rk_npu_b200_w4a8_enqueue_swiglu_collect_f32(rk_npu_w4a8_workspace
 extern "C" int rk_npu_b200_w4a8_enqueue_quantize_slice(rk_npu_w4a8_workspace* gate_up, const float* dMiddle,
                                                        const uint32_t* dRowMaxima, int8_t* dCodes, void* stream)
 {
-    if (!gate_up || !dMiddle || !dRowMaxima || !dCodes || gate_up->config.N % 2) return RK_NPU_ERR_PARAM;
+    if (!gate_up || !dMiddle || !dRowMaxima || !dCodes || gate_up->config.N % 2 || grouped(*gate_up)) return RK_NPU_ERR_PARAM;
     WorkspaceLock lock(*gate_up);
     if (!lock) return RK_NPU_ERR_BUSY;
     if (cudaSetDevice(gate_up->domain->ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
@@ -1144,7 +1218,7 @@ extern "C" int rk_npu_b200_w4a8_enqueue_codes_f32(rk_npu_w4a8_workspace* down, c
     const int rc = validate(down, w, dCodes, dC, false);
     if (rc) return rc;
     const int K = down->config.K;
-    if (parts < 1 || K % parts || (parts > 1 && (K / parts) % 16)) return RK_NPU_ERR_PARAM;
+    if (parts < 1 || K % parts || (parts > 1 && (K / parts) % 16) || grouped(*down)) return RK_NPU_ERR_PARAM;
     WorkspaceLock lock(*down);
     if (!lock) return RK_NPU_ERR_BUSY;
     Call call{down, w, nullptr, dC, false, EPI_F32, nullptr, dRowMaxima, static_cast<cudaStream_t>(stream), nullptr};

@@ -316,7 +316,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
                 if (g >= gpi) break;
                 for (int s = 0; s < spg; ++s, ++stage_i) {
                     const int slot = stage_i % R;
+                    if (TRACE && trace && blockIdx.x == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i] = (unsigned long long)(clock64() - c_start);
                     if (!mbar_wait_warp(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
+                    if (TRACE && trace && blockIdx.x == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i + 1] = (unsigned long long)(clock64() - c_start);
                     if (!verdict && !failed) {
                         const int c0 = s * DEC_STAGE_CHUNKS, nch = min(DEC_STAGE_CHUNKS, KC - c0);
                         const uint32_t wslot = ring_lane + (uint32_t)slot * DEC_STAGE_BYTES;
@@ -368,7 +370,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
                         for (int e = 0; e < 4; ++e) a[i][m][e] = 0;
                 for (int s = 0; s < spg; ++s, ++stage_i) {
                     const int slot = stage_i % R;
+                    if (TRACE && trace && blockIdx.x == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i] = (unsigned long long)(clock64() - c_start);
                     if (!mbar_wait_warp(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
+                    if (TRACE && trace && blockIdx.x == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i + 1] = (unsigned long long)(clock64() - c_start);
                     if (!verdict && !failed) {
                         const int c0 = s * DEC_STAGE_CHUNKS, nch = min(DEC_STAGE_CHUNKS, KC - c0);
                         const uint32_t wslot = ring_lane + (uint32_t)slot * DEC_STAGE_BYTES;

@@ -155,6 +155,28 @@ struct DecodeParams {
     unsigned long long* trace;  // optional [CTA][8] stamps of the kernel's phases (nullable)
 };
 
+// Column partition of a group of GPUs: contiguous runs of 64-column blocks, the first `blocks % world` ranks
+// one block more (the reference's split over its cores, src/rk_npu_i4_plan.cpp:37-43).
+__host__ __device__ inline void shard_range(int N, int world, int rank, int& n0, int& n1)
+{
+    const int blocks = (N + 63) / 64;
+    const int even = blocks / world, extra = blocks % world;
+    const int first = rank * even + (rank < extra ? rank : extra);
+    const int count = even + (rank < extra ? 1 : 0);
+    n0 = first * 64 < N ? first * 64 : N;
+    n1 = (first + count) * 64 < N ? (first + count) * 64 : N;
+}
+// Reassembly of all-gathered column shards: slot r of `gathered` holds rank r's compact [M][its columns] block.
+struct AssembleParams {
+    const uint8_t* gathered;
+    uint8_t* out;           // [M][N] row-major
+    size_t slot_bytes;      // distance between two ranks' blocks
+    int M, N, world;
+    int elem;               // bytes per element (1, 2 or 4)
+    int two_range;          // 1: a rank holds the same slice of both halves of N (gate | up packing)
+};
+cudaError_t launch_assemble_columns(const AssembleParams& p, cudaStream_t stream);
+
 struct PackParams {
     const int8_t* B;        // [K,N] codes on the device
     uint8_t* Wp;

@@ -13,6 +13,9 @@ struct rk_npu_ctx {
     uint32_t driver_version = 0;  // CUDA driver version; part of the tuning-cache key
     int sm_count = 0;
     cudaStream_t stream = nullptr;  // weight uploads
+    // group of GPUs (rk_npu_b200_open_group): this context is `rank` of `world`; comm is the NCCL communicator
+    int rank = 0, world = 1;
+    void* comm = nullptr;
 };
 
 struct rk_npu_iommu_domain {
@@ -55,6 +58,25 @@ void domain_release(rk_npu_iommu_domain* d);
 int device_alloc(rk_npu_iommu_domain* d, void** ptr, size_t bytes);
 void device_free(rk_npu_iommu_domain* d, void* ptr, size_t bytes);
 
+// ---- group of GPUs (w4a8_group.cpp)
+void group_close(rk_npu_ctx* ctx);
+int group_all_gather(rk_npu_ctx* ctx, void* buffer, size_t bytes_per_rank, cudaStream_t stream);
+int group_all_reduce_max_u32(rk_npu_ctx* ctx, uint32_t* values, size_t count, cudaStream_t stream);
+// Columns of a weight [K, N] this rank holds: N % 128 == 0 -> the same slice [f0, f1) of both halves of N
+// (so that a [gate | up] packing keeps its SwiGLU pairs on one GPU; `two_range`), else one contiguous run.
+struct ShardPlan {
+    bool two_range = false;
+    int n0 = 0, n1 = 0;          // slice of N (contiguous) or of N / 2 (two_range)
+    int columns() const { return (two_range ? 2 : 1) * (n1 - n0); }
+};
+inline ShardPlan shard_plan(int N, int world, int rank)
+{
+    ShardPlan p;
+    p.two_range = world > 1 && N % 128 == 0;
+    shard_range(p.two_range ? N / 2 : N, world, rank, p.n0, p.n1);
+    return p;
+}
+
 inline int align_up(int x, int a) { return (x + a - 1) / a * a; }
 inline int64_t align_up64(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
 
@@ -70,6 +92,8 @@ struct rk_npu_w4a8_weights {
     float* scales = nullptr;    // padded to 32*NG
     size_t packed_bytes = 0, scale_bytes = 0;
     int KB = 0, NG = 0;
+    rkb200::ShardPlan shard;    // the columns this object holds (all of them outside a group)
+    int shard_N = 0;            // == shard.columns()
 };
 
 struct rk_npu_w4a8_workspace {
@@ -108,4 +132,11 @@ struct rk_npu_w4a8_workspace {
     std::atomic<uint64_t> launches{0};
     unsigned long long* trace = nullptr;   // device stamps, allocated by rk_npu_b200_w4a8_trace_enable
     size_t trace_bytes = 0;
+    // group of GPUs: the kernels compute `shard_N` columns into this rank's slot of `gather` (world slots of
+    // gather_slot bytes: a compact [M][widest shard] block of 4-byte elements), an all-gather fills the others
+    // and the rows are reassembled into the caller's tensor (or `stage_out` for a host caller)
+    rkb200::ShardPlan shard;
+    int shard_N = 0;
+    uint8_t* gather = nullptr;
+    size_t gather_slot = 0, gather_bytes = 0;
 };

@@ -107,4 +107,33 @@ cudaError_t launch_codes_in(const CodesInParams& p, cudaStream_t stream)
     return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------ reassembly after the all-gather
+// One CTA per (row, source rank): the rank's compact row piece goes to its place in the row-major result.
+__global__ void __launch_bounds__(128) assemble_columns_kernel(const AssembleParams p)
+{
+    const int m = blockIdx.x, r = blockIdx.y;
+    const int span = p.two_range ? p.N / 2 : p.N;
+    int n0, n1;
+    shard_range(span, p.world, r, n0, n1);
+    const int width = n1 - n0, pieces = p.two_range ? 2 : 1;
+    if (width <= 0) return;
+    const uint8_t* src_row = p.gathered + (size_t)r * p.slot_bytes + (size_t)m * pieces * width * p.elem;
+    for (int piece = 0; piece < pieces; ++piece) {
+        const uint8_t* src = src_row + (size_t)piece * width * p.elem;
+        uint8_t* dst = p.out + ((size_t)m * p.N + (size_t)piece * span + n0) * p.elem;
+        const size_t bytes = (size_t)width * p.elem;
+        if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) | bytes) & 15u) == 0) {
+            for (size_t i = threadIdx.x; i < bytes / 16; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+        } else {
+            for (size_t i = threadIdx.x; i < bytes; i += blockDim.x) dst[i] = src[i];
+        }
+    }
+}
+cudaError_t launch_assemble_columns(const AssembleParams& p, cudaStream_t stream)
+{
+    if (p.M < 1 || p.world < 1 || p.elem < 1) return cudaErrorInvalidValue;
+    assemble_columns_kernel<<<dim3((unsigned)p.M, (unsigned)p.world), 128, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
 } // namespace rkb200

@@ -50,6 +50,18 @@ class Context:
         if not self.handle:
             raise W4A8Error(capi.RK_NPU_ERR_OPEN, f"rk_npu_open({dev!r})")
 
+    @classmethod
+    def open_group(cls, dev: str, rank: int, world: int, group_id: bytes) -> "Context":
+        """rk_npu_b200_open_group: this process is `rank` of `world` GPUs sharing the 128-byte id rank 0 obtained from
+        rk_npu_b200_group_id; weights are column-sharded and results all-gathered inside the library."""
+        self = cls.__new__(cls)
+        self.lib = capi.load()
+        ident = (C.c_ubyte * 128).from_buffer_copy(bytes(group_id))
+        self.handle = self.lib.rk_npu_b200_open_group(dev.encode(), rank, world, ident)
+        if not self.handle:
+            raise W4A8Error(capi.RK_NPU_ERR_OPEN, f"rk_npu_b200_open_group({dev!r}, {rank}, {world})")
+        return self
+
     @property
     def device(self) -> int:
         return self.lib.rk_npu_b200_device(self.handle)

@@ -287,7 +287,7 @@ def test_every_entry_point_of_the_original_headers_links(lib):
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, missing
     # operators that are not built decline instead of pretending
-    for name in ("rk_npu_i8i8i32_run", "rk_npu_f16i8f16_run_dynamic", "rk_npu_w4a8_autotune", "rk_npu_i4i4i32_run",
+    for name in ("rk_npu_i8i8i32_run", "rk_npu_f16i8f16_run_dynamic", "rk_npu_i4i4i32_run",
                  "rk_npu_matmul_autotune_cache_save", "rk_npu_mem_alloc"):
         fn = getattr(lib, name)
         fn.restype, fn.argtypes = C.c_int, []
@@ -296,6 +296,10 @@ def test_every_entry_point_of_the_original_headers_links(lib):
         fn = getattr(lib, name)
         fn.restype, fn.argtypes = C.c_void_p, []
         assert fn() is None, name
+    # the search tuners are built: argument errors are answered as such, without a device
+    fast = capi.W4A8Strategy()
+    assert lib.rk_npu_w4a8_autotune(None, None, None, None, C.byref(fast), None) == capi.RK_NPU_ERR_PARAM
+    assert lib.rk_npu_w4a8_autotune_cached(None, None, None, None, None, 0, C.byref(fast), None, None) == capi.RK_NPU_ERR_PARAM
 
 
 def test_second_header_defaults(lib):
