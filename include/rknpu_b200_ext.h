@@ -54,6 +54,19 @@ int rk_npu_b200_group_rank(const rk_npu_ctx *ctx);   /* 0 outside a group; -1 fo
 int rk_npu_b200_group_size(const rk_npu_ctx *ctx);   /* 1 outside a group; 0 for NULL */
 /* The partition rule itself: [*n0, *n1) of `rank` among `world` for N columns. */
 int rk_npu_b200_shard_columns(int N, int world, int rank, int *n0, int *n1);
+/* A caller that keeps column-parallel outputs sharded (tensor-parallel attention heads, a row-parallel layer
+ * behind) needs no exchange per linear.  rk_npu_b200_w4a8_workspace_shard tells which columns this rank
+ * computes: [*n0, *n1) of N, or with *two_range the same [*n0, *n1) of both halves of N; *columns in all.
+ * rk_npu_b200_w4a8_enqueue_local_f16 / _f32 queue the linear and write only those columns, compact
+ * [M][*columns], to dLocal -- no collective.  rk_npu_b200_group_all_gather is the group's all-gather for
+ * whatever the caller batches up: every rank's piece of bytes_per_rank bytes already lies at
+ * dBuffer + rank * bytes_per_rank (in place), afterwards every rank holds all pieces. */
+int rk_npu_b200_w4a8_workspace_shard(const rk_npu_w4a8_workspace *workspace, int *two_range, int *n0, int *n1, int *columns);
+int rk_npu_b200_w4a8_enqueue_local_f16(rk_npu_w4a8_workspace *workspace, const rk_npu_w4a8_weights *weights,
+                                       const uint16_t *dA, uint16_t *dLocal, void *cuda_stream);
+int rk_npu_b200_w4a8_enqueue_local_f32(rk_npu_w4a8_workspace *workspace, const rk_npu_w4a8_weights *weights,
+                                       const float *dA, float *dLocal, void *cuda_stream);
+int rk_npu_b200_group_all_gather(rk_npu_ctx *ctx, void *dBuffer, size_t bytes_per_rank, void *cuda_stream);
 
 /* Queue one W4A8 linear on `cuda_stream` (a cudaStream_t; NULL = the legacy default
  * stream).  dA / dC are device pointers on the context's GPU with the shapes of the
@@ -68,7 +81,10 @@ int rk_npu_b200_w4a8_enqueue_f16(rk_npu_w4a8_workspace *workspace, const rk_npu_
 int rk_npu_b200_w4a8_enqueue_swiglu_f32(rk_npu_w4a8_workspace *workspace, const rk_npu_w4a8_weights *weights,
                                         const float *dA, float *dMiddle, void *cuda_stream);
 /* gate/up -> SwiGLU -> down in one queue; a non-finite middle makes the down kernels
- * return without writing and is reported by rk_npu_b200_w4a8_finish(down). */
+ * return without writing and is reported by rk_npu_b200_w4a8_finish(down).
+ * On a group context dMiddle may be NULL when the caller does not need the middle tensor (feature count a
+ * multiple of 64 x group size): the GPUs then agree on the row maxima, quantise their own feature slice and
+ * all-gather int8 codes -- a quarter of the bytes of the fp32 middle -- with bit-identical results. */
 int rk_npu_b200_w4a8_enqueue_ffn_f32(rk_npu_w4a8_workspace *gate_up, const rk_npu_w4a8_weights *gate_up_weights,
                                      rk_npu_w4a8_workspace *down, const rk_npu_w4a8_weights *down_weights,
                                      const float *dA, float *dMiddle, float *dC, void *cuda_stream);

@@ -570,6 +570,7 @@ void workspace_destroy(rk_npu_w4a8_workspace* ws)
     if (ws->partials) device_free(d, ws->partials, ws->partials_bytes);
     if (ws->counts) device_free(d, ws->counts, ws->counts_bytes);
     if (ws->gather) device_free(d, ws->gather, ws->gather_bytes);
+    if (ws->code_gather) device_free(d, ws->code_gather, ws->code_gather_bytes);
     if (ws->host_status) cudaFreeHost(ws->host_status);
     for (auto& e : ws->events) if (e) cudaEventDestroy(e);
     if (ws->stream) cudaStreamDestroy(ws->stream);
@@ -1009,6 +1010,9 @@ rk_npu_w4a8_workspace* rkb200::create_workspace_scheduled(rk_npu_iommu_domain* d
         ws->gather_slot = size_t(cfg->M) * size_t(shard_plan(cfg->N, ctx->world, 0).columns()) * 4;   // rank 0's share is the widest
         ws->gather_bytes = ws->gather_slot * size_t(ctx->world);
         ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->gather), ws->gather_bytes);
+        // a down projection of a group FFN may receive its activations as all-gathered int8 codes [world][M][K / world]
+        ws->code_gather_bytes = size_t(cfg->M) * size_t(align_up(cfg->K, 64));
+        ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->code_gather), ws->code_gather_bytes);
     }
     ok = ok && !device_alloc(domain, &ws->stage_in, ws->stage_in_bytes);
     ok = ok && !device_alloc(domain, &ws->stage_out, ws->stage_out_bytes);
@@ -1157,6 +1161,44 @@ extern "C" int rk_npu_b200_w4a8_enqueue_f16(rk_npu_w4a8_workspace* ws, const rk_
 {
     return enqueue_public(ws, w, dA, dC, true, EPI_F16, stream);
 }
+// ---- group of GPUs without the exchange: this rank's columns only, compact [M][columns]
+extern "C" int rk_npu_b200_w4a8_workspace_shard(const rk_npu_w4a8_workspace* ws, int* two_range, int* n0, int* n1, int* columns)
+{
+    if (!ws) return RK_NPU_ERR_PARAM;
+    if (two_range) *two_range = ws->shard.two_range ? 1 : 0;
+    if (n0) *n0 = ws->shard.n0;
+    if (n1) *n1 = ws->shard.n1;
+    if (columns) *columns = ws->shard_N;
+    return RK_NPU_OK;
+}
+namespace {
+int enqueue_local(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const void* dA, void* dLocal, bool half, int epi, void* stream)
+{
+    const int rc = validate(ws, w, dA, dLocal, false);
+    if (rc) return rc;
+    WorkspaceLock lock(*ws);
+    if (!lock) return RK_NPU_ERR_BUSY;
+    Call call{ws, w, dA, dLocal, half, epi, nullptr, nullptr, static_cast<cudaStream_t>(stream), nullptr};
+    return enqueue(call);
+}
+}
+extern "C" int rk_npu_b200_w4a8_enqueue_local_f16(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const uint16_t* dA,
+                                                  uint16_t* dLocal, void* stream)
+{
+    return enqueue_local(ws, w, dA, dLocal, true, EPI_F16, stream);
+}
+extern "C" int rk_npu_b200_w4a8_enqueue_local_f32(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const float* dA,
+                                                  float* dLocal, void* stream)
+{
+    return enqueue_local(ws, w, dA, dLocal, false, EPI_F32, stream);
+}
+extern "C" int rk_npu_b200_group_all_gather(rk_npu_ctx* ctx, void* dBuffer, size_t bytes_per_rank, void* stream)
+{
+    if (!ctx || !dBuffer || !bytes_per_rank || ctx->world < 2) return RK_NPU_ERR_PARAM;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    return group_all_gather(ctx, dBuffer, bytes_per_rank, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int rk_npu_b200_w4a8_enqueue_swiglu_f32(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w,
                                                    const float* dA, float* dMiddle, void* stream)
 {
@@ -1166,10 +1208,17 @@ extern "C" int rk_npu_b200_w4a8_enqueue_ffn_f32(rk_npu_w4a8_workspace* gate_up, 
                                                 rk_npu_w4a8_workspace* down, const rk_npu_w4a8_weights* down_weights,
                                                 const float* dA, float* dMiddle, float* dC, void* stream)
 {
-    if (gate_up == down || dMiddle == dC || dA == dC) return RK_NPU_ERR_PARAM;
-    int rc = validate(gate_up, gate_up_weights, dA, dMiddle, true);
+    if (!gate_up || !down || gate_up == down || !dC || (dMiddle && dMiddle == dC) || dA == dC) return RK_NPU_ERR_PARAM;
+    // In a group a NULL dMiddle says the caller does not need the middle tensor: the GPUs then exchange int8 codes
+    // (a quarter of the fp32 middle's bytes) instead of gathering it.
+    const bool codes_only = dMiddle == nullptr;
+    if (codes_only && !(grouped(*gate_up) && down->code_gather && gate_up->config.N / 2 == down->config.K &&
+                        (down->config.K / 64) % gate_up->domain->ctx->world == 0 && down->config.K % 64 == 0))
+        return RK_NPU_ERR_PARAM;
+    float* local_middle = codes_only ? static_cast<float*>(own_slot(*gate_up)) : dMiddle;
+    int rc = validate(gate_up, gate_up_weights, dA, local_middle, true);
     if (rc) return rc;
-    rc = validate(down, down_weights, dMiddle, dC, false);
+    rc = validate(down, down_weights, local_middle, dC, false);
     if (rc) return rc;
     if (gate_up->config.M != down->config.M || gate_up->config.N / 2 != down->config.K) return RK_NPU_ERR_PARAM;
     if (gate_up->ctx_id != down->ctx_id || gate_up->domain_id != down->domain_id) return RK_NPU_ERR_DOMAIN;
@@ -1178,9 +1227,28 @@ extern "C" int rk_npu_b200_w4a8_enqueue_ffn_f32(rk_npu_w4a8_workspace* gate_up, 
     WorkspaceLock down_lock(*down);
     if (!down_lock) return RK_NPU_ERR_BUSY;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int M = gate_up->config.M;
+    if (codes_only) {
+        rk_npu_ctx* ctx = gate_up->domain->ctx;
+        const int slice = gate_up->shard.n1 - gate_up->shard.n0;          // features of this GPU
+        Call first{gate_up, gate_up_weights, dA, local_middle, false, EPI_SWIGLU, gate_up->rowmax, nullptr, s, nullptr};
+        rc = enqueue(first);                                              // middle slice stays local
+        if (!rc) rc = group_all_reduce_max_u32(ctx, gate_up->rowmax, size_t(M), s);
+        if (rc) return rc;
+        const size_t piece = size_t(M) * slice;                            // int8 codes of one GPU's slice
+        SliceQuantParams q{local_middle, reinterpret_cast<int8_t*>(down->code_gather) + size_t(ctx->rank) * piece, gate_up->rowmax, M, slice};
+        if (launch_quantize_slice(q, s) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+        gate_up->launches.fetch_add(1, std::memory_order_relaxed);
+        rc = group_all_gather(ctx, down->code_gather, piece, s);
+        if (rc) return rc;
+        Call second{down, down_weights, nullptr, dC, false, EPI_F32, nullptr, gate_up->rowmax, s, nullptr};
+        second.codes_in = reinterpret_cast<const int8_t*>(down->code_gather);
+        second.parts = ctx->world;
+        return enqueue_linear(second, dC);
+    }
     Call first{gate_up, gate_up_weights, dA, dMiddle, false, EPI_SWIGLU, gate_up->rowmax, nullptr, s, nullptr};
     rc = enqueue_linear(first, dMiddle);
-    if (!rc && grouped(*gate_up)) rc = group_all_reduce_max_u32(gate_up->domain->ctx, gate_up->rowmax, size_t(gate_up->config.M), s);
+    if (!rc && grouped(*gate_up)) rc = group_all_reduce_max_u32(gate_up->domain->ctx, gate_up->rowmax, size_t(M), s);
     if (rc) return rc;
     Call second{down, down_weights, dMiddle, dC, false, EPI_F32, nullptr, gate_up->rowmax, s, nullptr};
     return enqueue_linear(second, dC);

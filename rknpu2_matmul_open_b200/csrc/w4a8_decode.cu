@@ -53,6 +53,14 @@ __device__ __forceinline__ void st_async_v4(uint32_t remote_addr, const uint4& v
                  "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(remote_bar)
                  : "memory");
 }
+// Wait of a whole warp on an mbarrier phase.  Fast path: the phase is already complete (weights are normally
+// requested long before they are needed) and one test by every lane both sees that and gives each lane its
+// acquire; otherwise one lane polls with the bounded wait and the others follow it.
+__device__ __forceinline__ bool mbar_wait_all_lanes(uint64_t* bar, uint32_t parity, unsigned long long deadline_ns)
+{
+    if (__all_sync(0xffffffffu, mbar_test(bar, parity))) return true;
+    return mbar_wait_warp(bar, parity, deadline_ns);
+}
 __device__ __forceinline__ void bar_sync_contraction() { asm volatile("bar.sync 1, %0;" ::"n"(DEC_WARPS * 32) : "memory"); }
 
 // Partial-sum scratch index: [warp][row][token], the token position XOR-ed with row bits so that both the
@@ -172,7 +180,11 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
         }
     }
     if (TRACE && trace) trace[1] = (unsigned long long)(clock64() - c_start);
-    pdl_wait();   // the producer of A (and of the collected row maxima) has finished
+    // The producer of A (and of the collected row maxima) has finished once the dependency wait returns.  One warp
+    // executes it; the others block at the hardware barrier behind it, where they take no issue slots from the
+    // launch in front, whose CTAs share this SM while it finishes.
+    if (warp == 0) pdl_wait();
+    bar_sync_contraction();
     const unsigned long long deadline = global_ns() + p.timeout_ns;
     if (TRACE && trace) trace[2] = (unsigned long long)(clock64() - c_start);
 
@@ -193,6 +205,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
             }
         }
     }
+    if (TRACE && trace && blockIdx.x == 0) p.trace[8 * 4096 + 64] = (unsigned long long)(clock64() - c_start);   // loads issued
     if (!no_scan) {
 #pragma unroll
         for (int it = 0; it < UMAX; ++it) {
@@ -214,8 +227,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
                 atomicMax(&s_max[tl], raw_maxbits<HALF>(r));
             }
         }
+        if (TRACE && trace && blockIdx.x == 0) p.trace[8 * 4096 + 65] = (unsigned long long)(clock64() - c_start);   // own maxima in
         bar_sync_contraction();
     }
+    if (TRACE && trace && blockIdx.x == 0) p.trace[8 * 4096 + 66] = (unsigned long long)(clock64() - c_start);       // row maxima known
     // scale of one of this CTA's tokens; every CTA that shares a token derives the same values
     auto token_scale = [&](int tl, uint32_t collected, float& s, float& inv) -> int {
         int bad;
@@ -267,6 +282,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
             publish(tok, u, quantize16(v, inv, u * 16, p.K));
         }
     }
+    if (TRACE && trace && blockIdx.x == 0) p.trace[8 * 4096 + 67] = (unsigned long long)(clock64() - c_start);       // share quantised
     if (part == 0 && tid < TQ && t0 + tid < M) {
         // the token's scale (or the reason it has none) travels with the codes
         const int tok = t0 + tid;
@@ -282,7 +298,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
     if (TRACE && trace) trace[3] = (unsigned long long)(clock64() - c_start);
     bool failed = false;
     if (S > 1) {
-        if (!mbar_wait_warp(code_bar, 0, deadline)) failed = true;
+        if (!mbar_wait_all_lanes(code_bar, 0, deadline)) failed = true;
     } else bar_sync_contraction();
     if (TRACE && trace) trace[4] = (unsigned long long)(clock64() - c_start);
     int verdict = 0;
@@ -294,8 +310,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
     // ---- 3. contraction: warp w takes the chunks w, w + 8, ... of every stage, all 32 (64) channels
     const int g8 = lane >> 2, t4 = lane & 3;
     const bool col_live = g8 < M;
-    const uint32_t xs_lane = xs_base + (uint32_t)(g8 * 16 + t4 * 4);
-    const uint32_t ring_lane = smem_u32(ring) + (uint32_t)(DOT ? lane * 16 : g8 * 16 + t4 * 4);
     const int tok_out = tid >> 5;                         // epilogue: this thread's token; its channel is `lane`
     const float sx = (tok_out < M && !verdict) ? __uint_as_float(s_scale[tok_out]) : 0.f;
     uint32_t run_max = 0;
@@ -312,31 +326,46 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
 #pragma unroll
                 for (int t = 0; t < 4; ++t) dacc[g][t] = 0;
 #pragma unroll
+            const uint8_t* const wring = ring + lane * 16;
             for (int g = 0; g < 2; ++g) {
                 if (g >= gpi) break;
+                int dacc4[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) dacc4[i][t] = 0;
                 for (int s = 0; s < spg; ++s, ++stage_i) {
                     const int slot = stage_i % R;
                     if (TRACE && trace && blockIdx.x == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i] = (unsigned long long)(clock64() - c_start);
-                    if (!mbar_wait_warp(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
+                    if (!mbar_wait_all_lanes(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
                     if (TRACE && trace && blockIdx.x == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i + 1] = (unsigned long long)(clock64() - c_start);
                     if (!verdict && !failed) {
                         const int c0 = s * DEC_STAGE_CHUNKS, nch = min(DEC_STAGE_CHUNKS, KC - c0);
-                        const uint32_t wslot = ring_lane + (uint32_t)slot * DEC_STAGE_BYTES;
-#pragma unroll 4
-                        for (int cc = warp; cc < nch; cc += DEC_WARPS) {
-                            uint32_t w[4];
-                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(wslot + (uint32_t)cc * 512u));
-                            const uint32_t xb = xs_base + (uint32_t)((c0 + cc) * 2 * Mc) * 16u;
+                        // a warp's four chunks of the stage: every load first, then four independent dot-product chains per token
+                        uint4 w[4];
 #pragma unroll
-                            for (int t = 0; t < 4; ++t) {
-                                if (t >= Mc) break;
-                                uint32_t x0[4], x1[4];
-                                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(x0[0]), "=r"(x0[1]), "=r"(x0[2]), "=r"(x0[3]) : "r"(xb + (uint32_t)t * 16u));
-                                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(x1[0]), "=r"(x1[1]), "=r"(x1[2]), "=r"(x1[3]) : "r"(xb + (uint32_t)(Mc + t) * 16u));
+                        for (int i = 0; i < 4; ++i) {
+                            const int cc = warp + DEC_WARPS * i;
+                            w[i] = cc < nch ? *reinterpret_cast<const uint4*>(wring + (size_t)slot * DEC_STAGE_BYTES + (size_t)cc * 512) : make_uint4(0u, 0u, 0u, 0u);
+                        }
 #pragma unroll
-                                for (int q = 0; q < 4; ++q) {
-                                    dacc[g][t] = __dp4a((int)((w[q] << 4) & 0xF0F0F0F0u), (int)x0[q], dacc[g][t]);
-                                    dacc[g][t] = __dp4a((int)(w[q] & 0xF0F0F0F0u), (int)x1[q], dacc[g][t]);
+                        for (int i = 0; i < 4; ++i) {
+                            const int cc = warp + DEC_WARPS * i;
+                            if (cc < nch) {
+                                const uint4* xp = reinterpret_cast<const uint4*>(xs) + (size_t)(c0 + cc) * 2 * Mc;
+                                const uint32_t wl[4] = {(w[i].x << 4) & 0xF0F0F0F0u, (w[i].y << 4) & 0xF0F0F0F0u, (w[i].z << 4) & 0xF0F0F0F0u, (w[i].w << 4) & 0xF0F0F0F0u};
+                                const uint32_t wh[4] = {w[i].x & 0xF0F0F0F0u, w[i].y & 0xF0F0F0F0u, w[i].z & 0xF0F0F0F0u, w[i].w & 0xF0F0F0F0u};
+#pragma unroll
+                                for (int t = 0; t < 4; ++t) {
+                                    if (t < Mc) {
+                                        const uint4 x0 = xp[t], x1 = xp[Mc + t];
+                                        int a = dacc4[i][t];
+                                        a = __dp4a((int)wl[0], (int)x0.x, a); a = __dp4a((int)wh[0], (int)x1.x, a);
+                                        a = __dp4a((int)wl[1], (int)x0.y, a); a = __dp4a((int)wh[1], (int)x1.y, a);
+                                        a = __dp4a((int)wl[2], (int)x0.z, a); a = __dp4a((int)wh[2], (int)x1.z, a);
+                                        a = __dp4a((int)wl[3], (int)x0.w, a); a = __dp4a((int)wh[3], (int)x1.w, a);
+                                        dacc4[i][t] = a;
+                                    }
                                 }
                             }
                         }
@@ -344,6 +373,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&empty[slot]);
                 }
+#pragma unroll
+                for (int t = 0; t < 4; ++t) dacc[g][t] = (dacc4[0][t] + dacc4[1][t]) + (dacc4[2][t] + dacc4[3][t]);
             }
             if (TRACE && trace && j == my_items - 1) trace[5] = (unsigned long long)(clock64() - c_start);
             // partial sums: [warp][token][row], row = lane (+ 32 for the up group)
@@ -371,22 +402,21 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
                 for (int s = 0; s < spg; ++s, ++stage_i) {
                     const int slot = stage_i % R;
                     if (TRACE && trace && blockIdx.x == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i] = (unsigned long long)(clock64() - c_start);
-                    if (!mbar_wait_warp(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
+                    if (!mbar_wait_all_lanes(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
                     if (TRACE && trace && blockIdx.x == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i + 1] = (unsigned long long)(clock64() - c_start);
                     if (!verdict && !failed) {
                         const int c0 = s * DEC_STAGE_CHUNKS, nch = min(DEC_STAGE_CHUNKS, KC - c0);
-                        const uint32_t wslot = ring_lane + (uint32_t)slot * DEC_STAGE_BYTES;
+                        const uint32_t* const wslot = reinterpret_cast<const uint32_t*>(ring + (size_t)slot * DEC_STAGE_BYTES) + g8 * 4 + t4;
+                        const uint32_t* const xlane = reinterpret_cast<const uint32_t*>(xs) + g8 * 4 + t4;
                         uint32_t w[4][4], b[4][2];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const int cc = warp + DEC_WARPS * i;
                             const bool live = cc < nch;
-                            const uint32_t wb = wslot + (uint32_t)cc * 512u;
-                            const uint32_t xb = xs_lane + (uint32_t)((c0 + cc) * 2 * Mc) * 16u;
 #pragma unroll
-                            for (int r = 0; r < 4; ++r) w[i][r] = live ? lds32(wb + r * 128) : 0u;
-                            b[i][0] = (live && col_live) ? lds32(xb) : 0u;
-                            b[i][1] = (live && col_live) ? lds32(xb + (uint32_t)Mc * 16u) : 0u;
+                            for (int r = 0; r < 4; ++r) w[i][r] = live ? wslot[cc * 128 + r * 32] : 0u;
+                            b[i][0] = (live && col_live) ? xlane[(c0 + cc) * 2 * Mc * 4] : 0u;
+                            b[i][1] = (live && col_live) ? xlane[((c0 + cc) * 2 + 1) * Mc * 4] : 0u;
                         }
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {

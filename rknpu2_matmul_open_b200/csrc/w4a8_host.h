@@ -139,4 +139,6 @@ struct rk_npu_w4a8_workspace {
     int shard_N = 0;
     uint8_t* gather = nullptr;
     size_t gather_slot = 0, gather_bytes = 0;
+    uint8_t* code_gather = nullptr;     // all-gathered int8 activation codes of a group FFN's down projection
+    size_t code_gather_bytes = 0;
 };

@@ -164,15 +164,15 @@ __global__ void __launch_bounds__(BS, 2048 / BS) quantize_kernel(const QuantPara
 // row), and the codes leave through a shared-memory stage so that each 128-byte line of the Xq layout -- the
 // same unit of eight consecutive tokens -- is written by eight adjacent threads instead of as eight scattered
 // 16-byte pieces from eight CTAs.
-constexpr int Q8_SEGMENT = 256;   // units staged per pass: 256 x 8 tokens x 16 B = 32 KB
+constexpr int Q8_SEGMENT = 256;   // units staged per pass: (256 + 1) x 8 tokens x 16 B = 32.1 KB
 
 template <bool HALF>
-__global__ void __launch_bounds__(256) quantize_rows8_kernel(const QuantParams p)
+__global__ void __launch_bounds__(256, 2) quantize_rows8_kernel(const QuantParams p)
 {
     using T = typename ActType<HALF>::type;
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ __align__(16) uint4 q8_stage[];   // [unit in segment][8 tokens]
+    extern __shared__ __align__(16) uint4 q8_stage[];   // [token][unit in segment], rows one unit apart in the banks
     __shared__ int s_bad;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m0 = blockIdx.x * 8, m = m0 + warp;
@@ -237,11 +237,11 @@ __global__ void __launch_bounds__(256) quantize_rows8_kernel(const QuantParams p
                     else { uint32_t unused = 0; load16<HALF>(row, kc * 16, p.K, vec, v, unused); }
                     q = quantize16(v, inv, kc * 16, p.K);
                 }
-                q8_stage[(kc - seg0) * 8 + warp] = q;
+                q8_stage[warp * (Q8_SEGMENT + 1) + (kc - seg0)] = q;
             }
         }
         __syncthreads();
-        for (int idx = tid; idx < n * 8; idx += 256) dst[(size_t)(seg0 + (idx >> 3)) * p.T + (idx & 7)] = q8_stage[idx];
+        for (int idx = tid; idx < n * 8; idx += 256) dst[(size_t)(seg0 + (idx >> 3)) * p.T + (idx & 7)] = q8_stage[(idx & 7) * (Q8_SEGMENT + 1) + (idx >> 3)];
         __syncthreads();
     }
     if (tid == 0) {
@@ -276,7 +276,7 @@ cudaError_t launch_quantize(const QuantParams& p, cudaStream_t stream, bool pdl)
         // eight tokens per CTA: rows read once, whole 128-byte lines written
         cfg.gridDim = dim3((unsigned)((p.M + 7) / 8));
         cfg.blockDim = dim3(256);
-        cfg.dynamicSmemBytes = (size_t)Q8_SEGMENT * 8 * sizeof(uint4);
+        cfg.dynamicSmemBytes = (size_t)(Q8_SEGMENT + 1) * 8 * sizeof(uint4);
         return p.half ? cudaLaunchKernelEx(&cfg, quantize_rows8_kernel<true>, p) : cudaLaunchKernelEx(&cfg, quantize_rows8_kernel<false>, p);
     }
     // One CTA per token.  With many tokens the kernel is bound by how many rows are in flight, so

@@ -133,9 +133,10 @@ def _print_stamps(rk, case, calls, stream, torch):
               " then median cycles since CTA start at (decode kernel): before the dependency wait, dependency met, share"
               " quantised and sent, all codes landed, last contraction done, last output stored")
         for i, (_, ws) in enumerate(calls):
-            buf = np.zeros((4104, 8), np.uint64)
-            lib.rk_npu_b200_w4a8_trace_read(ws.handle, buf.ctypes.data, 4104)
+            buf = np.zeros((4112, 8), np.uint64)
+            lib.rk_npu_b200_w4a8_trace_read(ws.handle, buf.ctypes.data, 4112)
             extra = buf[4096:4098].reshape(-1).astype(np.int64)
+            fine = buf[4104].astype(np.int64)[:4]
             buf = buf[:4096]
             v = buf[buf[:, 0] > 0].astype(np.int64)
             if not len(v):
@@ -147,6 +148,7 @@ def _print_stamps(rk, case, calls, stream, torch):
                   f" cycles {list(cyc)}")
             prev_end = e1
             print(f"   CTA 0, first stages (cycles since its start: wait begins, wait ends): {[int(x) for x in extra]}")
+            print(f"   CTA 0, scan (cycles since its start): loads issued, own maxima in, row maxima known, share quantised: {[int(x) for x in fine]}")
     elif case == "prefill":
         raw = np.zeros(256, np.uint64)
         lib.rk_npu_b200_w4a8_trace_read(calls[0][1].handle, raw.ctypes.data, 32)

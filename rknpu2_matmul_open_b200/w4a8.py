@@ -66,6 +66,10 @@ class Context:
     def device(self) -> int:
         return self.lib.rk_npu_b200_device(self.handle)
 
+    def all_gather(self, dBuffer, bytes_per_rank: int, stream: int = 0) -> int:
+        """rk_npu_b200_group_all_gather: in-place all-gather of the group (every rank's piece at its slot)."""
+        return self.lib.rk_npu_b200_group_all_gather(self.handle, _ptr(dBuffer), bytes_per_rank, C.c_void_p(stream))
+
     def domain(self, domain_id: int = 0) -> "Domain":
         return Domain(self, domain_id)
 
@@ -196,6 +200,19 @@ class Workspace:
     def enqueue_codes_f32(self, weights: Weights, dCodes, parts: int, dRowMaxima, dC, stream: int = 0) -> int:
         return self.lib.rk_npu_b200_w4a8_enqueue_codes_f32(self.handle, weights.handle, _ptr(dCodes), int(parts),
                                                            _ptr(dRowMaxima), _ptr(dC), C.c_void_p(stream))
+
+    # ---- group of GPUs: this rank's columns only, no exchange
+    def shard(self):
+        """(two_range, n0, n1, columns) of the columns this rank computes."""
+        v = [C.c_int() for _ in range(4)]
+        self.lib.rk_npu_b200_w4a8_workspace_shard(self.handle, *[C.byref(x) for x in v])
+        return bool(v[0].value), v[1].value, v[2].value, v[3].value
+
+    def enqueue_local_f16(self, weights: Weights, dA, dLocal, stream: int = 0) -> int:
+        return self.lib.rk_npu_b200_w4a8_enqueue_local_f16(self.handle, weights.handle, _ptr(dA), _ptr(dLocal), C.c_void_p(stream))
+
+    def enqueue_local_f32(self, weights: Weights, dA, dLocal, stream: int = 0) -> int:
+        return self.lib.rk_npu_b200_w4a8_enqueue_local_f32(self.handle, weights.handle, _ptr(dA), _ptr(dLocal), C.c_void_p(stream))
 
     def finish(self) -> int:
         return self.lib.rk_npu_b200_w4a8_finish(self.handle)
