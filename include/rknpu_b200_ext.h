@@ -187,6 +187,20 @@ int rk_npu_b200_w4a8_enqueue_f16_static(const rk_npu_w4a8_weights *weights, cons
  * original project. */
 int rk_npu_b200_w4a8_static_status(const rk_npu_w4a8_weights *weights, int *bad_input, int *device_error);
 
+/* ---- Test hooks: failures produced on the host, or by a wait that is allowed to run out ---------------
+ * None of these faults, traps or hangs a GPU.
+ * rk_npu_b200_test_fail_allocation(n): the (n+1)-th device allocation from now on fails as if memory were
+ *   exhausted (constructors return NULL and release what they had); n < 0 switches the hook off.  Process-wide.
+ * rk_npu_b200_w4a8_test_starve(ws, 1): launches of a decode-kernel workspace make the first weight barrier of
+ *   every CTA expect 16 bytes that no copy brings, so the bounded wait on it runs out after the workspace's
+ *   timeout_ms, the kernel records the error and returns (all real copies have landed), and the call reports
+ *   RK_NPU_ERR_SUBMIT; (ws, 0) restores normal launches.  RK_NPU_ERR_PARAM for other kernel families.
+ * rk_npu_b200_w4a8_test_device_error(ws): sets the workspace's device-side error word from the host, as a kernel
+ *   whose wait ran out would; the next status read reports RK_NPU_ERR_SUBMIT and clears it. */
+void rk_npu_b200_test_fail_allocation(long long after);
+int rk_npu_b200_w4a8_test_starve(rk_npu_w4a8_workspace *workspace, int on);
+int rk_npu_b200_w4a8_test_device_error(rk_npu_w4a8_workspace *workspace);
+
 /* Kernels this workspace has launched since creation (for launch accounting). */
 uint64_t rk_npu_b200_w4a8_launch_count(const rk_npu_w4a8_workspace *workspace);
 

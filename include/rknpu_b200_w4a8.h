@@ -137,11 +137,14 @@ typedef struct rk_npu_w4a8_memory_info_ex {
     rk_npu_w4a8_reduce_backend effective_reduce_backend;
 } rk_npu_w4a8_memory_info_ex;
 
-/* include/rk_npu_w4a8.h:76-83.  On this library: activation_scan_us is the absmax +
- * quantise kernel, quant_pack_us the re-quantise kernel of an FFN's down projection,
- * sync_us host<->device copies plus the final stream wait, submit_us the GEMM kernel
- * (split-K reduction and dequantisation are fused into it, so reduce_us and
- * dequant_us are 0), total_us the wall time of the blocking call. */
+/* include/rk_npu_w4a8.h:76-83.  On this library (device times from CUDA events, host times from the wall clock):
+ *   activation_scan_us  the absmax + quantise kernel in front of a two-kernel GEMM (0 for the single-launch decode
+ *                       kernel, which scans inside the GEMM launch, and for an FFN's down projection, which never scans)
+ *   quant_pack_us       the re-quantise kernel of an FFN's down projection (scales from the collected row maxima)
+ *   submit_us           the GEMM kernel(s); split-K reduction and dequantisation are fused into it, so dequant_us is 0
+ *   reduce_us           in a group of GPUs: the all-gather and reassembly of the column shards; 0 on one GPU
+ *   sync_us             host<->device copies plus the final stream wait
+ *   total_us            the wall time of the blocking call */
 typedef struct rk_npu_w4a8_timings {
     double activation_scan_us;
     double quant_pack_us, sync_us, submit_us, reduce_us;

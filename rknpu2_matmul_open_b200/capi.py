@@ -236,6 +236,9 @@ _SIGNATURES = {
     "rk_npu_b200_w4a8_set_schedule": (C.c_int, [_P, C.c_int, C.c_int]),
     "rk_npu_b200_w4a8_enqueue_f16_static": (C.c_int, [_P, _P, _P, C.c_int, _P]),
     "rk_npu_b200_w4a8_static_status": (C.c_int, [_P, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "rk_npu_b200_test_fail_allocation": (None, [C.c_longlong]),
+    "rk_npu_b200_w4a8_test_starve": (C.c_int, [_P, C.c_int]),
+    "rk_npu_b200_w4a8_test_device_error": (C.c_int, [_P]),
     "rk_npu_b200_w4a8_launch_count": (C.c_uint64, [_P]),
     "rk_npu_b200_w4a8_trace_enable": (C.c_int, [_P, C.c_int]),
     "rk_npu_b200_w4a8_trace_read": (C.c_int, [_P, _P, C.c_int]),

@@ -342,6 +342,7 @@ int enqueue(const Call& c)
         d.ctas = gemm_decode_ctas(swiglu ? F / GROUP : (N + GROUP - 1) / GROUP, d.cluster, ws.decode_cap[slot]);
         d.timeout_ns = timeout_ns;
         d.trace = ws.trace;
+        d.starve = ws.starve ? 1 : 0;
         if (c.events) cudaEventRecord(c.events[1], c.stream);
         if (launch_gemm_decode(d, c.stream, pdl) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
         if (c.events) cudaEventRecord(c.events[2], c.stream);
@@ -499,7 +500,9 @@ int enqueue_linear(Call call, void* dOut)
     if (const int rc = enqueue(call)) return rc;
     if (!grouped(ws)) return RK_NPU_OK;
     const bool swiglu = call.epi == EPI_SWIGLU;
-    return gather_output(ws, dOut, swiglu ? ws.config.N / 2 : ws.config.N, element_bytes(call.epi), !swiglu && ws.shard.two_range, call.stream);
+    const int rc = gather_output(ws, dOut, swiglu ? ws.config.N / 2 : ws.config.N, element_bytes(call.epi), !swiglu && ws.shard.two_range, call.stream);
+    if (call.events) cudaEventRecord(call.events[3], call.stream);   // the exchange between GPUs ends here
+    return rc;
 }
 
 // One blocking projection; the caller holds the workspace.
@@ -538,6 +541,7 @@ int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const vo
     if (metrics) {
         t.activation_scan_us = event_us(ws->events[0], ws->events[1]);
         t.submit_us = rc ? 0.0 : event_us(ws->events[1], ws->events[2]);   // a rejected input did no GEMM work
+        if (grouped(*ws)) t.reduce_us = event_us(ws->events[2], ws->events[3]);   // all-gather + reassembly of the column shards
         t.total_us = elapsed_us(start);
         *metrics = t;
     }
@@ -586,10 +590,15 @@ void domain_release(rk_npu_iommu_domain* d)
 {
     if (d && d->refs.fetch_sub(1, std::memory_order_acq_rel) == 1) delete d;
 }
+// Test hook: the allocation that brings this counter to zero fails as if the device were out of memory.
+static std::atomic<long long> g_allocations_until_failure{-1};
 int device_alloc(rk_npu_iommu_domain* d, void** ptr, size_t bytes)
 {
     *ptr = nullptr;
     if (!bytes) bytes = 16;
+    if (g_allocations_until_failure.load(std::memory_order_relaxed) >= 0 &&
+        g_allocations_until_failure.fetch_sub(1, std::memory_order_relaxed) == 0)
+        return RK_NPU_ERR_NOMEM;
     if (cudaMalloc(ptr, bytes) != cudaSuccess) { cudaGetLastError(); *ptr = nullptr; return RK_NPU_ERR_NOMEM; }
     std::lock_guard<std::mutex> g(d->lock);
     d->stats.live_bytes += bytes;
@@ -607,6 +616,11 @@ void device_free(rk_npu_iommu_domain* d, void* ptr, size_t bytes)
     ++d->stats.destroys;
 }
 } // namespace rkb200
+
+extern "C" void rk_npu_b200_test_fail_allocation(long long after)
+{
+    rkb200::g_allocations_until_failure.store(after, std::memory_order_relaxed);
+}
 
 extern "C" rk_npu_ctx* rk_npu_open(const char* dev)
 {
@@ -1337,6 +1351,23 @@ extern "C" int rk_npu_b200_w4a8_set_schedule(rk_npu_w4a8_workspace* ws, int vari
     if (!lock) return RK_NPU_ERR_BUSY;
     ws->split_override = split_k;
     return RK_NPU_OK;
+}
+extern "C" int rk_npu_b200_w4a8_test_starve(rk_npu_w4a8_workspace* ws, int on)
+{
+    if (!ws || ws->variant != 5) return RK_NPU_ERR_PARAM;
+    WorkspaceLock lock(*ws);
+    if (!lock) return RK_NPU_ERR_BUSY;
+    ws->starve = on != 0;
+    return RK_NPU_OK;
+}
+extern "C" int rk_npu_b200_w4a8_test_device_error(rk_npu_w4a8_workspace* ws)
+{
+    if (!ws) return RK_NPU_ERR_PARAM;
+    WorkspaceLock lock(*ws);
+    if (!lock) return RK_NPU_ERR_BUSY;
+    if (cudaSetDevice(ws->domain->ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    const int one = 1;
+    return cudaMemcpy(&ws->status->device_error, &one, sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess ? RK_NPU_OK : RK_NPU_ERR_SUBMIT;
 }
 extern "C" uint64_t rk_npu_b200_w4a8_launch_count(const rk_npu_w4a8_workspace* ws)
 {

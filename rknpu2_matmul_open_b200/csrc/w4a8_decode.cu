@@ -139,7 +139,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
                 const int group = g == 0 ? item : p.F / GROUP + item;
                 const int c0 = s * DEC_STAGE_CHUNKS;
                 const uint32_t bytes = (uint32_t)min(DEC_STAGE_CHUNKS, KC - c0) * 512u;
-                mbar_arrive_expect_tx(&full[slot], bytes);
+                // (test hook: 16 bytes that no copy brings keep the first barrier open until the wait gives up;
+                // every real copy still lands)
+                mbar_arrive_expect_tx(&full[slot], bytes + ((p.starve && i == 0) ? 16u : 0u));
                 bulk_g2s(ring + (size_t)slot * DEC_STAGE_BYTES, p.Wp + ((size_t)group * KC + c0) * 512, bytes, &full[slot]);
             }
         }

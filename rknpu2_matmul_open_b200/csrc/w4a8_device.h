@@ -151,6 +151,7 @@ struct DecodeParams {
     int cluster;                // CTAs that share the quantisation: 1, 2, 4 or 8
     int ring;                   // 16 KB weight stages per CTA
     int ctas;                   // grid size, a multiple of `cluster`
+    int starve;                 // test hook: the first weight barrier of every CTA expects 16 bytes that never arrive
     unsigned long long timeout_ns;
     unsigned long long* trace;  // optional [CTA][8] stamps of the kernel's phases (nullable)
 };

@@ -115,6 +115,7 @@ struct rk_npu_w4a8_workspace {
                                            // (split-K clusters), 4 quantise + persistent streaming GEMM (small batch, large
                                            // weights), 5 single-kernel decode (whole-K CTAs, up to eight tokens)
     int decode_cap[4] = {0, 0, 0, 0};      // variant 5: CTAs resident at once for cluster sizes 1, 2, 4, 8
+    bool starve = false;                   // test hook (rk_npu_b200_w4a8_test_starve): first weight barrier never completes
     // device buffers
     uint8_t* codes = nullptr;
     float* scales = nullptr;
