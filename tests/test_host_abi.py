@@ -397,6 +397,47 @@ def test_w8_load_only_cache(lib, tmp_path, monkeypatch):
     lib.rk_npu_close(ctx)
 
 
+def test_w8_cache_files_written_by_the_reference_load_here(lib, reference, tmp_path, monkeypatch):
+    """Files written by the reference's own W8 cache writer (src/rk_npu_quant_matmul.cpp:337-349, compiled into the
+    reference checker) are hits for this library's loader with identical records, and misses for every other key.
+    Records that name a panel layout are accepted by the reference after a check against its device plan; here they
+    are a documented miss."""
+    import os
+    ref = reference.lib
+    if not hasattr(ref, "rk_npu_matmul_autotune_cache_save"):
+        pytest.skip("reference checker built without its W8 sources")
+    monkeypatch.delenv("RK_NPU_I8_NPU_REDUCE", raising=False)
+    monkeypatch.delenv("RK_NPU_W8A8_NPU_DEQUANT", raising=False)
+    fake = (C.c_uint8 * 8192)()                                     # the reference's context: fd at 0, driver version at 16
+    C.cast(fake, C.POINTER(C.c_int))[0] = -1
+    C.cast(C.byref(fake, 16), C.POINTER(C.c_uint32))[0] = 0x908
+    ctx = lib.rk_npu_b200_open_offline(0x908)
+    affinity = sum(1 << cpu for cpu in os.sched_getaffinity(0) if cpu < 64)
+    one_cpu = affinity & -affinity
+    for kind, (M, N, K), kt, nt in ((1, (128, 4096, 11008), 1376, 1408), (0, (8, 1000, 513), 513, 512), (3, (33, 4096, 4096), 2048, 2048)):
+        c = capi.MatmulAutotuneConfig()
+        lib.rk_npu_matmul_autotune_config_init(C.byref(c), M, N, K)
+        s = capi.MatmulStrategy()
+        s.op_kind, s.M, s.N, s.K, s.k_tile, s.n_tile = kind, M, N, K, kt, nt
+        s.a_layout, s.c_layout = 1, 0
+        s.wave_count = -(-K // kt)
+        s.n_groups = -(-max(32, -(-N // 32) * 32) // nt)
+        s.npu_core_mask, s.cpu_core_mask, s.cpu_threads = 7 if s.n_groups >= 3 else 1, one_cpu, 1
+        s.input_us, s.npu_us, s.sync_us, s.output_us, s.total_us, s.jitter_pct, s.robust_us = 1.5, 20.25, 3.0, 4.0, 30.0, 2.0, 31.0
+        path = str(tmp_path / f"ref_w8_{kind}.tune").encode()
+        assert ref.rk_npu_matmul_autotune_cache_save(fake, path, kind, C.byref(c), C.byref(s), C.byref(s)) == 0
+        f, st = capi.MatmulStrategy(), capi.MatmulStrategy()
+        assert lib.rk_npu_matmul_autotune_cache_load(ctx, path, kind, C.byref(c), C.byref(f), C.byref(st)) == 0
+        assert _fields(f) == _fields(s) and _fields(st) == _fields(s)
+        f2, st2 = capi.MatmulStrategy(), capi.MatmulStrategy()
+        assert ref.rk_npu_matmul_autotune_cache_load(fake, path, kind, C.byref(c), C.byref(f2), C.byref(st2)) == 0
+        c2 = capi.MatmulAutotuneConfig.from_buffer_copy(c)
+        c2.loops += 1
+        assert lib.rk_npu_matmul_autotune_cache_load(ctx, path, kind, C.byref(c2), C.byref(f), C.byref(st)) == capi.RK_NPU_ERR_CACHE_MISS
+        assert ref.rk_npu_matmul_autotune_cache_load(fake, path, kind, C.byref(c2), C.byref(f2), C.byref(st2)) == capi.RK_NPU_ERR_CACHE_MISS
+    lib.rk_npu_close(ctx)
+
+
 def test_public_headers_are_valid_c(tmp_path):
     # the original checks its headers with a C translation unit (tests/test_w4a8_header.c, tests/test_quant_header.c)
     import shutil
