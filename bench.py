@@ -10,9 +10,15 @@ benchmark does.  `value` is algorithmic GB/s with activations resident in HBM (e
 entry points, one CUDA graph per step when capture works); `e2e` is the same pass through
 the blocking reference ABI with pinned HOST activations and outputs, copies included.
 
-N > 1 (torchrun): every linear is column-sharded over the ranks in contiguous 64-column
-blocks (the reference's per-core split) and the shard outputs are reassembled by one
-NCCL all-gather per step; total work is fixed, so scaling is "strong".
+N > 1 (torchrun, one rank per GPU): every rank opens a GROUP context; the library itself
+shards each weight by output columns (contiguous 64-column blocks, the reference's
+per-core split), runs this rank's columns and reassembles outputs with its own NCCL
+communicator -- torch.distributed only carries the group id and the timing reductions.
+The device-resident figure keeps column-parallel outputs sharded and gathers them once per
+step; the end-to-end figure uses the blocking call, which gathers inside every call.
+Total work is fixed, so scaling is "strong".
+
+`--case decode|prefill|mid|ffn` runs a small fixed workload for a kernel profiler instead.
 
 `--impl reference` times the reference's own CPU stages (oracle/_ref, or the C port when
 that was not built) on the host cores for the same workload.
@@ -141,13 +147,13 @@ def run_reference(args, rank, world):
     step_bytes = sum(algorithmic_bytes(M, K, N) * c for (K, N), c in zip(shapes, counts))
     step_ops = sum(2 * M * K * N * c for (K, N), c in zip(shapes, counts))
     gbs = step_bytes * args.steps / t / 1e9
-    sample = (f"one decoder layer (4x 4096->4096, 2x 4096->11008, 1x 11008->4096) at M={M} per step; "
+    sample = (f"a step of this arm is ONE decoder layer of the ring (4x 4096->4096, 2x 4096->11008, 1x 11008->4096) at M={M}; "
               + ("reference CPU stages (scan, MSD pack, INT16 reconstruct, dequant: 4 threads) around an "
                  "all-core int4 stand-in for the NPU step" if use_ref else "C port of the reference path"))
     line = {"impl": "reference", "metric": "w4a8_decode_weight_stream", "value": gbs, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": workload_config(args, world, layers=1),
+            "config": workload_config(args, world, args.layers),
             "tops": step_ops * args.steps / t / 1e12,
             "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "reference" if use_ref else "port",
                              "sample": sample},
@@ -162,6 +168,100 @@ def workload_config(args, world, layers):
 
 
 # ------------------------------------------------------------------ CUDA arm
+def _event_time(torch, stream, fn, reps):
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            fn()
+    stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+    stream.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def _max_over_ranks(torch, dist, dev, world, value):
+    if world == 1:
+        return value
+    t = torch.tensor([value], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _all_ranks_agree(torch, dist, dev, world, ok):
+    if world == 1:
+        return bool(ok)
+    t = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(t.item())
+
+
+def _graph_of(torch, stream, fn, enabled=True):
+    if not enabled:
+        return None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            fn()
+        return graph
+    except Exception as exc:   # capture is an optimisation; plain stream launches are the fallback
+        print(f"[bench] graph capture unavailable ({type(exc).__name__}: {exc}); using stream launches", file=sys.stderr)
+        torch.cuda.synchronize()
+        return None
+
+
+def open_context(rk, torch, dist, rank, world, local_rank, dev):
+    """One GPU: an ordinary context.  Several: every rank opens a group context -- the library shards the
+    weights, runs this rank's columns and all-gathers over NVLink with its own NCCL communicator;
+    torch.distributed only carries the 128-byte group id and the timing reductions."""
+    if world == 1:
+        return rk.Context(f"cuda:{local_rank}")
+    ident = torch.zeros(128, dtype=torch.uint8, device=dev)
+    if rank == 0:
+        raw = (__import__("ctypes").c_ubyte * 128)()
+        if rk.capi.load().rk_npu_b200_group_id(raw):
+            raise RuntimeError("rk_npu_b200_group_id failed (NCCL not loadable)")
+        ident.copy_(torch.tensor(list(raw), dtype=torch.uint8))
+    dist.broadcast(ident, src=0)
+    return rk.Context.open_group(f"cuda:{local_rank}", rank, world, bytes(ident.cpu().numpy().tobytes()))
+
+
+def shard_of(N, world, rank):
+    """Columns a rank holds (the library's rule): N % 128 == 0 -> the same slice of both halves of N, else one run."""
+    from rknpu2_matmul_open_b200.sharding import shard_columns
+    if world > 1 and N % 128 == 0:
+        f0, f1 = shard_columns(N // 2, world, rank)
+        return np.r_[f0:f1, N // 2 + f0:N // 2 + f1]
+    n0, n1 = shard_columns(N, world, rank)
+    return np.arange(n0, n1)
+
+
+def measure_int8_peak():
+    """Dense int8 tensor peak of this GPU, measured now: the issue loop of csrc/int8_peak.cu (bare tcgen05.mma
+    kind::i8 on resident operands, every SM) run for a fraction of a second, with the SM clock sampled meanwhile."""
+    exe = ROOT / "rknpu2_matmul_open_b200" / "lib" / "int8_peak"
+    if not exe.exists():
+        return None
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    try:
+        out = subprocess.run([str(exe), "60000"], capture_output=True, text=True, timeout=120).stdout
+    except (OSError, subprocess.TimeoutExpired):
+        out = ""
+    clocks = sampler.stop()
+    best = 0.0
+    for line in out.splitlines():
+        if "N=256" in line and "TOPS (event)" in line:
+            try:
+                best = max(best, float(line.split("->")[1].split("TOPS")[0]))
+            except (IndexError, ValueError):
+                pass
+    return {"tops": best, "sm_mhz": clocks["sm_mhz"], "reasons": clocks["reasons"],
+            "how": "lib/int8_peak 60000: 128x256x32 kind::i8 MMAs back to back on every SM, best of the runs"} if best else None
+
+
 def run_cuda(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -169,7 +269,6 @@ def run_cuda(args, rank, world, local_rank):
     import rknpu2_matmul_open_b200 as rk
     from oracle.harness import Oracle, Reference            # checker of what is timed, and the cpu_baseline leg
     from rknpu2_matmul_open_b200.synthetic import make_activations, make_weights, sample_columns
-    from rknpu2_matmul_open_b200.sharding import shard_columns
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -179,73 +278,67 @@ def run_cuda(args, rank, world, local_rank):
             os.environ["NCCL_DEBUG"] = "WARN"
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
-    ctx = rk.Context(f"cuda:{local_rank}")
+    ctx = open_context(rk, torch, dist, rank, world, local_rank, dev)
     dom = ctx.domain(0)
     M = args.tokens
     hbm_peak, _, peak_kind = measured_peaks()
+    oracle = Oracle()
+    stream = torch.cuda.Stream(device=dev)
 
-    # ---- the ring: `layers` distinct decoder layers, each linear column-sharded over ranks
-    linears = []          # dicts: K, N(full), n0, n1, weights, workspace, dA, dC, hA, hC
-    act = {}
-    for K in (4096, 11008):
-        A = make_activations(M, K, seed=K, dtype="f16")
-        act[K] = (A, torch.from_numpy(A.view(np.int16)).to(dev))
-    check = None
-    generated = {}
-    # every linear writes straight into one per-rank output buffer; with several ranks that buffer is
-    # what the all-gather sends, so no packing copies sit between the GEMMs and the collective
-    shard_cols = [shard_columns(N, world, rank) for _ in range(args.layers) for (_, N) in LLAMA7B_LAYER]
-    out_cols = sum(n1 - n0 for n0, n1 in shard_cols)
-    # Shards may differ by one 64-column block between ranks; NCCL's all-gather wants equal pieces, so every
-    # rank's buffer has the size of the widest shard set (the tail of a narrower one stays zero).
-    pad_cols = max(sum(b - a for a, b in (shard_columns(N, world, r) for _ in range(args.layers) for (_, N) in LLAMA7B_LAYER))
-                   for r in range(world))
-    out_buf = torch.zeros((M * pad_cols,), dtype=torch.float16, device=dev)   # binary16 bits (NCCL has no int16)
-    out_off = 0
+    # ---- the ring: `layers` distinct decoder layers.  Every rank passes the FULL weights; a group context keeps
+    # its columns.  The device-resident figure computes this rank's columns of all linears into one buffer and
+    # reassembles them with ONE all-gather per step (column-parallel outputs stay sharded until somebody needs
+    # all of them); the end-to-end figure goes through the blocking reference call, which gathers per linear.
+    act = {K: make_activations(M, K, seed=K, dtype="f16") for K in (4096, 11008)}
+    dact = {K: torch.from_numpy(a.view(np.int16)).to(dev) for K, a in act.items()}
+    generated, linears = {}, []
     for layer in range(args.layers):
         for j, (K, N) in enumerate(LLAMA7B_LAYER):
             seed = (layer * 16 + j) if args.distinct_values else j
             if (K, N, seed) not in generated:
                 generated[(K, N, seed)] = make_weights(K, N, seed=seed)
             B, sw = generated[(K, N, seed)]
-            n0, n1 = shard_columns(N, world, rank)
-            Bs, ss = np.ascontiguousarray(B[:, n0:n1]), np.ascontiguousarray(sw[n0:n1])
-            w = rk.Weights(dom, Bs, ss, k_tile=480)
-            ws = rk.Workspace(dom, rk.default_config(M, n1 - n0, K, k_tile=480))
-            dC = out_buf[out_off:out_off + M * (n1 - n0)].view(M, n1 - n0).view(torch.int16)
-            out_off += M * (n1 - n0)
-            hA = torch.from_numpy(act[K][0].view(np.int16)).pin_memory()
-            hC = torch.zeros((M, n1 - n0), dtype=torch.int16).pin_memory()
-            linears.append(dict(K=K, N=N, n0=n0, n1=n1, w=w, ws=ws, dA=act[K][1], dC=dC, hA=hA, hC=hC))
-            if check is None:
-                check = (act[K][0], Bs, ss, len(linears) - 1)
+            w = rk.Weights(dom, B, sw, k_tile=480)
+            ws = rk.Workspace(dom, rk.default_config(M, N, K, k_tile=480))
+            cols = ws.shard()[3]
+            linears.append(dict(K=K, N=N, seed=seed, w=w, ws=ws, cols=cols, dA=dact[K],
+                                hA=torch.from_numpy(act[K].view(np.int16)).pin_memory(),
+                                hC=torch.zeros((M, N), dtype=torch.int16).pin_memory()))
+    # slot of a rank in the step's output buffer: its linears' compact [M][columns] blocks one after the other,
+    # padded to the widest rank so that every piece of the all-gather has one size
+    def slot_elems(r):
+        return sum(M * len(shard_of(l["N"], world, r)) for l in linears)
+    slot = max(slot_elems(r) for r in range(world))
+    out_buf = torch.zeros((world * slot,), dtype=torch.int16, device=dev)
+    offset = rank * slot
+    for l in linears:
+        l["dC"] = out_buf[offset:offset + M * l["cols"]].view(M, l["cols"])
+        offset += M * l["cols"]
     step_bytes = sum(algorithmic_bytes(M, l["K"], l["N"]) for l in linears)          # whole job, all ranks
     step_ops = sum(2 * M * l["K"] * l["N"] for l in linears)
-    gather_out = None
-    if world > 1:
-        gather_out = torch.zeros((world * M * pad_cols,), dtype=torch.float16, device=dev)
-
-    stream = torch.cuda.Stream(device=dev)
 
     def enqueue_step(s):
         for l in linears:
-            rc = l["ws"].enqueue_f16(l["w"], l["dA"], l["dC"], s.cuda_stream)
+            rc = l["ws"].enqueue_local_f16(l["w"], l["dA"], l["dC"], s.cuda_stream)
             if rc:
                 raise RuntimeError(f"enqueue failed: {rc}")
         if world > 1:     # reassemble the column shards on every rank: the one exchange the path has
-            with torch.cuda.stream(s):
-                dist.all_gather_into_tensor(gather_out, out_buf)
+            rc = ctx.all_gather(out_buf, slot * 2, s.cuda_stream)
+            if rc:
+                raise RuntimeError(f"all-gather failed: {rc}")
 
-    # ---- correctness of what is timed: first linear of the ring against the oracle
-    oracle = Oracle()
+    # ---- correctness of what is timed: the first linear, reassembled from ALL ranks' pieces, against the oracle
     with torch.cuda.stream(stream):
         enqueue_step(stream)
     stream.synchronize()
-    A0, B0, s0, idx = check
-    ref_out = oracle.linear(A0, B0, s0)[1]
-    got = linears[idx]["dC"].cpu().numpy().view(np.uint16)
-    if not np.array_equal(got, ref_out):
-        raise RuntimeError("CUDA output differs from the oracle; refusing to report a number")
+    first = linears[0]
+    ref_out = oracle.linear(act[first["K"]], *generated[(first["K"], first["N"], first["seed"])])[1]
+    gathered = out_buf.cpu().numpy().view(np.uint16)
+    for r in range(world):
+        cols = shard_of(first["N"], world, r)
+        piece = gathered[r * slot:r * slot + M * len(cols)].reshape(M, len(cols))
+        if not np.array_equal(piece, ref_out[:, cols]):
+            raise RuntimeError(f"rank {rank}: the output gathered from rank {r} differs from the oracle; refusing to report a number")
     for l in linears:
         if l["ws"].finish() != 0:
             raise RuntimeError("device status not clean after the check step")
@@ -256,16 +349,7 @@ def run_cuda(args, rank, world, local_rank):
     launches_per_step = sum(l["ws"].launch_count() for l in linears) - count0   # this library's kernels per step
 
     # ---- device-resident timing (value)
-    graph = None
-    if not args.no_graph:
-        try:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                enqueue_step(stream)
-        except Exception as exc:   # capture is an optimisation; plain stream launches are the fallback
-            print(f"[bench] graph capture unavailable ({type(exc).__name__}: {exc}); using stream launches", file=sys.stderr)
-            graph = None
-            torch.cuda.synchronize()
+    graph = _graph_of(torch, stream, lambda: enqueue_step(stream), not args.no_graph)
 
     def do_step():
         if graph is not None:
@@ -307,15 +391,11 @@ def run_cuda(args, rank, world, local_rank):
             do_step()
         e1.record(stream)
     barrier()
-    ms = e0.elapsed_time(e1)
+    ms = _max_over_ranks(torch, dist, dev, world, e0.elapsed_time(e1))
     clocks = sampler.stop() if sampler else None
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
     ms_step = ms / args.steps
 
-    # ---- end to end through the blocking reference ABI, pinned host tensors
+    # ---- end to end through the blocking reference ABI, pinned host tensors (a group gathers inside every call)
     def e2e_step():
         for l in linears:
             rc = l["ws"].run_f16(l["w"], l["hA"], l["hC"])
@@ -324,38 +404,33 @@ def run_cuda(args, rank, world, local_rank):
 
     for _ in range(2):
         e2e_step()
+    if not np.array_equal(first["hC"].numpy().view(np.uint16), ref_out):
+        raise RuntimeError("blocking call: output differs from the oracle")
     barrier()
     t0 = time.perf_counter()
     e2e_steps = max(1, min(args.steps, 10))
     for _ in range(e2e_steps):
         e2e_step()
     barrier()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_s], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    e2e_s = _max_over_ranks(torch, dist, dev, world, (time.perf_counter() - t0) / e2e_steps)
     h2d = sum(M * l["K"] * 2 for l in linears)
-    d2h = sum(M * (l["n1"] - l["n0"]) * 2 for l in linears)
+    d2h = sum(M * l["N"] * 2 for l in linears)
 
-    # ---- M = 1 beside it (single GPU only, same ring)
     also = {}
-    if world == 1 and args.tokens != 1 and not args.quick:
-        also["M1_GBps"] = _time_other_m(rk, dom, linears, 1, args, dev, stream)
-
     if world == 1 and not args.quick:
+        if args.tokens != 1:
+            also["M1_GBps"] = _time_other_m(rk, dom, linears, 1, args, dev, stream)
         also["independent_linears_4_streams_GBps"] = _time_streams(linears, step_bytes, args, dev, 4)
-        also.update(_prefill_and_ffn(rk, dom, dev, stream, oracle, make_weights, make_activations, sample_columns))
-
-    if world > 1 and not args.quick:
-        try:
-            also.update(_prefill_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_activations, shard_columns))
-        except Exception as exc:   # the extra figure must never cost the headline line
-            also["prefill_sharded_error"] = f"{type(exc).__name__}: {exc}"
-        try:
-            also.update(_ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_activations))
-        except Exception as exc:
-            also["ffn_sharded_error"] = f"{type(exc).__name__}: {exc}"
+        also["layer_dependencies_only_GBps"] = _time_batched(rk, linears, step_bytes, args, stream)
+    if not args.quick:
+        peak = measure_int8_peak() if rank == 0 else None
+        for name, fn in (("prefill", _prefill), ("ffn_4096_14336", _ffn_llama8b), ("ffn_8192_28672", _ffn_70b)):
+            try:
+                also.update(fn(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak))
+            except Exception as exc:   # an extra figure must never cost the headline line
+                also[f"{name}_error"] = f"{type(exc).__name__}: {exc}"
+        if peak:
+            also["int8_peak_measured_now"] = peak
 
     # ---- CPU baseline on a bounded sample (rank 0, one GPU only)
     cpu = None
@@ -363,9 +438,8 @@ def run_cuda(args, rank, world, local_rank):
         cpu = cpu_baseline(M, Reference if Reference.available() else None, oracle, make_weights, make_activations)
 
     if rank == 0:
-        launches = launches_per_step * args.steps
         value = step_bytes / (ms_step * 1e-3) / 1e9
-        gemm_bytes_per_launch = step_bytes / len(linears) / world   # what one rank's launch reads
+        bytes_per_launch = step_bytes / len(linears) / world   # what one rank's launch reads
         line = {"metric": "w4a8_decode_weight_stream", "value": value, "unit": "GB/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
@@ -375,31 +449,31 @@ def run_cuda(args, rank, world, local_rank):
                 "clocks": clocks,
                 "e2e": {"value": step_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                         "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * e2e_s},
-                "gpu_launches": launches,
+                "gpu_launches": launches_per_step * args.steps,
                 "roofline": {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
                              "frac": value / world / hbm_peak,
-                             # ncu (profiles/gemm_fused_kernel_decode_M8.md): 8,525,824 B read + 0 B written for the
-                             # 4096 x 4096 linear whose algorithmic bytes are 8,536,064; traffic is one read per
-                             # weight byte, so it scales with the bytes of the ring's average linear
-                             "traffic": gemm_bytes_per_launch * (8525824.0 / 8536064.0), "peak_kind": peak_kind,
-                             "kernel": "gemm_fused_kernel (scan + quantise + GEMM + dequantise in one launch)",
+                             # one read per weight byte (ncu: DRAM bytes read equal the algorithmic bytes to 0.1 %), so the
+                             # traffic of a launch is its algorithmic bytes
+                             "traffic": bytes_per_launch, "peak_kind": peak_kind,
+                             "kernel": "gemm_decode_kernel (scan + quantise + GEMM + dequantise in one launch)",
                              "frac_of_nominal": value / world / 8000.0, "nominal_peak": 8000.0,   # 8 TB/s data-sheet HBM3e
-                             "bytes_per_launch": gemm_bytes_per_launch,
+                             "bytes_per_launch": bytes_per_launch,
                              "us_per_launch": 1e3 * ms_step / len(linears)},
                 "cpu_baseline": cpu, "also": also}
         print(json.dumps(line), flush=True)
+    torch.cuda.synchronize()
     if world > 1:
-        # The captured graph holds NCCL kernels; tearing the communicator down under it has hung at
-        # exit.  Everything is finished: meet once more, then leave without running destructors.
-        torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(0)
     for l in linears:
         l["ws"].free()
         l["w"].free()
+    dom.free()
+    ctx.close()
+    if world > 1:
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)     # the process group's teardown under captured graphs has hung at exit; everything is finished
 
 
 def _time_other_m(rk, dom, linears, M, args, dev, stream):
@@ -408,34 +482,18 @@ def _time_other_m(rk, dom, linears, M, args, dev, stream):
     extra = []
     act = {K: torch.from_numpy(make_activations(M, K, seed=K, dtype="f16").view(np.int16)).to(dev) for K in (4096, 11008)}
     for l in linears:
-        ws = rk.Workspace(dom, rk.default_config(M, l["n1"] - l["n0"], l["K"], k_tile=480))
-        extra.append((ws, l["w"], act[l["K"]], torch.zeros((M, l["n1"] - l["n0"]), dtype=torch.int16, device=dev), l))
+        ws = rk.Workspace(dom, rk.default_config(M, l["N"], l["K"], k_tile=480))
+        extra.append((ws, l["w"], act[l["K"]], torch.zeros((M, l["N"]), dtype=torch.int16, device=dev)))
 
     def step():
-        for ws, w, dA, dC, _ in extra:
+        for ws, w, dA, dC in extra:
             ws.enqueue_f16(w, dA, dC, stream.cuda_stream)
 
-    graph = None
-    if not args.no_graph:
-        try:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                step()
-        except Exception:
-            graph = None
-            torch.cuda.synchronize()
     with torch.cuda.stream(stream):
-        for _ in range(3):
-            graph.replay() if graph else step()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        e0.record(stream)
-        for _ in range(args.steps):
-            graph.replay() if graph else step()
-        e1.record(stream)
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
+        step()
+    stream.synchronize()
+    graph = _graph_of(torch, stream, step, not args.no_graph)
+    ms = _event_time(torch, stream, (graph.replay if graph else step), args.steps)
     total = sum(algorithmic_bytes(M, l["K"], l["N"]) for l in linears)
     for ws, *_ in extra:
         ws.free()
@@ -456,60 +514,60 @@ def _time_streams(linears, step_bytes, args, dev, n_streams):
         for i, l in enumerate(linears):
             s = side[i % n_streams]
             with torch.cuda.stream(s):
-                rc = l["ws"].enqueue_f16(l["w"], l["dA"], l["dC"], s.cuda_stream)
+                rc = l["ws"].enqueue_local_f16(l["w"], l["dA"], l["dC"], s.cuda_stream)
                 if rc:
                     raise RuntimeError(f"enqueue failed: {rc}")
         for s in side:
             main.wait_stream(s)
 
     torch.cuda.synchronize()
-    graph = None
-    if not args.no_graph:
-        try:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=main):
-                step()
-        except Exception as exc:
-            print(f"[bench] multi-stream capture unavailable ({type(exc).__name__}: {exc})", file=sys.stderr)
-            graph = None
-            torch.cuda.synchronize()
     with torch.cuda.stream(main):
-        for _ in range(3):
-            graph.replay() if graph else step()
+        step()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(main):
-        e0.record(main)
-        for _ in range(args.steps):
-            graph.replay() if graph else step()
-        e1.record(main)
-    torch.cuda.synchronize()
-    return step_bytes / (e0.elapsed_time(e1) / args.steps * 1e-3) / 1e9
+    graph = _graph_of(torch, main, step, not args.no_graph)
+    ms = _event_time(torch, main, (graph.replay if graph else step), args.steps)
+    return step_bytes / (ms * 1e-3) / 1e9
 
 
-INT8_PEAK_TOPS = 4550.0   # dense int8 tcgen05 peak measured on this pool's B200 with lib/int8_peak (burst, 1965 MHz)
-
-
-def _event_time(torch, stream, fn, reps):
-    with torch.cuda.stream(stream):
-        for _ in range(3):
-            fn()
-    stream.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        e0.record(stream)
-        for _ in range(reps):
-            fn()
-        e1.record(stream)
-    stream.synchronize()
-    return e0.elapsed_time(e1) / reps
-
-
-def _prefill_and_ffn(rk, dom, dev, stream, oracle, make_weights, make_activations, sample_columns):
-    """Benchmark configuration 2 (prefill GEMM 2048 x 4096 x 14336, fp16) and config 3 (fused FFN 4096 -> 2 x 14336 -> 4096,
-    M = 1 and 1024), device-resident, each checked against the oracle on sampled columns / rows."""
+def _time_batched(rk, linears, step_bytes, args, stream):
+    """The same ring with only the dependencies a decoder layer really has: q, k and v read the same activations and
+    are independent of each other, so are gate and up.  Each such set goes out as ONE launch
+    (rk_npu_b200_w4a8_enqueue_batch_f16); o and down stay launches of their own.  Four launches per layer instead of
+    seven, each still waiting for the one in front."""
     import torch
-    out = {}
+    layers = [linears[i:i + len(LLAMA7B_LAYER)] for i in range(0, len(linears), len(LLAMA7B_LAYER))]
+
+    def step():
+        for layer in layers:
+            for group in (layer[0:3], layer[3:4], layer[4:6], layer[6:7]):    # q|k|v, o, gate|up, down
+                rc = rk.enqueue_batch_f16([l["ws"] for l in group], [l["w"] for l in group], [l["dA"] for l in group],
+                                          [l["dC"] for l in group], stream.cuda_stream)
+                if rc:
+                    raise RuntimeError(f"batched enqueue failed: {rc}")
+
+    with torch.cuda.stream(stream):
+        step()
+    stream.synchronize()
+    graph = _graph_of(torch, stream, step, not args.no_graph)
+    ms = _event_time(torch, stream, (graph.replay if graph else step), args.steps)
+    return step_bytes / (ms * 1e-3) / 1e9
+
+
+def _tiled_weights(make_weights, K, N, seed, block=2048):
+    """Weights with the benchmark's value distribution, generated for a 2048-column block and repeated along N
+    (drawing hundreds of millions of fp32 normals would take most of a minute; only time and parity are measured)."""
+    if N <= 2 * block or N % block:
+        return make_weights(K, N, seed=seed)
+    B, s = make_weights(K, block, seed=seed)
+    return np.tile(B, (1, N // block)), np.tile(s, N // block)
+
+
+def _prefill(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak):
+    """Benchmark configuration 2: prefill GEMM 2048 x 4096 x 14336, fp16 in and out.  One GPU: quantise + GEMM.  A
+    group: every rank's columns (compute) and the same with the all-gather and reassembly that leave the whole
+    [M, N] tensor on every rank; the gathered tensor is compared with the oracle on sampled columns, all rows."""
+    import torch
+    from rknpu2_matmul_open_b200.synthetic import make_activations, make_weights, sample_columns
     M, K, N = 2048, 4096, 14336
     B, sw = make_weights(K, N, seed=21)
     A = make_activations(M, K, seed=21, dtype="f16")
@@ -517,183 +575,122 @@ def _prefill_and_ffn(rk, dom, dev, stream, oracle, make_weights, make_activation
     ws = rk.Workspace(dom, rk.default_config(M, N, K))
     dA = torch.from_numpy(A.view(np.int16)).to(dev)
     dC = torch.zeros((M, N), dtype=torch.int16, device=dev)
-    ms = _event_time(torch, stream, lambda: ws.enqueue_f16(w, dA, dC, stream.cuda_stream), 10)
+    local = torch.zeros((M, ws.shard()[3]), dtype=torch.int16, device=dev)
     cols = sample_columns(N)
     _, s, inv = oracle.scales(A)
     ref = oracle.dequant(oracle.gemm_i32_columns(oracle.quantize(A, inv), B, cols), s, sw[cols], True)
-    exact = bool(np.array_equal(dC.cpu().numpy().view(np.uint16)[:, cols], ref))
-    tops = 2.0 * M * K * N / (ms * 1e-3) / 1e12
-    out["prefill_M2048_K4096_N14336"] = {"us": ms * 1e3, "tops": tops, "frac_of_measured_int8_peak": tops / INT8_PEAK_TOPS,
-                                         "peak_tops": INT8_PEAK_TOPS, "frac_of_nominal_4500": tops / 4500.0, "sampled_exact": exact,
-                                         "includes": "quantise kernel + tcgen05 GEMM"}
+    peak_tops = peak["tops"] if peak else None
+    out = {}
+    if world == 1:
+        ms = _event_time(torch, stream, lambda: ws.enqueue_f16(w, dA, dC, stream.cuda_stream), 10)
+        exact = bool(np.array_equal(dC.cpu().numpy().view(np.uint16)[:, cols], ref))
+        tops = 2.0 * M * K * N / (ms * 1e-3) / 1e12
+        out["prefill_M2048_K4096_N14336"] = {"us": ms * 1e3, "tops": tops, "sampled_exact": exact, "peak_tops_measured_now": peak_tops,
+                                             "frac_of_measured_int8_peak": tops / peak_tops if peak_tops else None,
+                                             "frac_of_nominal_4500": tops / 4500.0, "includes": "quantise kernel + tcgen05 GEMM"}
+        # the one complete-call figure the original project publishes: binary16, M = 128, K = 11008, N = 4096
+        # (about 4.0 ms on its RK3588 target)
+        ws.free(); w.free()
+        M, K, N = 128, 11008, 4096
+        B, sw = make_weights(K, N, seed=22)
+        A = make_activations(M, K, seed=22, dtype="f16")
+        w = rk.Weights(dom, B, sw)
+        ws = rk.Workspace(dom, rk.default_config(M, N, K))
+        dA = torch.from_numpy(A.view(np.int16)).to(dev)
+        dC = torch.zeros((M, N), dtype=torch.int16, device=dev)
+        ms = _event_time(torch, stream, lambda: ws.enqueue_f16(w, dA, dC, stream.cuda_stream), 10)
+        cols = sample_columns(N)
+        _, s, inv = oracle.scales(A)
+        ref = oracle.dequant(oracle.gemm_i32_columns(oracle.quantize(A, inv), B, cols), s, sw[cols], True)
+        out["published_shape_M128_K11008_N4096"] = {
+            "us": ms * 1e3, "tops": 2.0 * M * K * N / (ms * 1e-3) / 1e12, "published_ms_on_rk3588": 4.0,
+            "sampled_exact": bool(np.array_equal(dC.cpu().numpy().view(np.uint16)[:, cols], ref))}
+    else:
+        timed = {}
+        for name, fn in (("compute", lambda: ws.enqueue_local_f16(w, dA, local, stream.cuda_stream)),
+                         ("compute_plus_all_gather", lambda: ws.enqueue_f16(w, dA, dC, stream.cuda_stream))):
+            ms = _max_over_ranks(torch, dist, dev, world, _event_time(torch, stream, fn, 10))
+            timed[name] = {"us": ms * 1e3, "tops_whole_job": 2.0 * M * K * N / (ms * 1e-3) / 1e12}
+        exact = _all_ranks_agree(torch, dist, dev, world, np.array_equal(dC.cpu().numpy().view(np.uint16)[:, cols], ref))
+        if not exact:
+            raise RuntimeError("gathered prefill output differs from the oracle")
+        timed["gathered_exact_on_every_rank"] = exact
+        out["prefill_M2048_K4096_N14336_sharded"] = timed
     ws.free()
     w.free()
-    # the one complete-call figure the original project publishes: binary16, M = 128, K = 11008, N = 4096
-    # (about 4.0 ms on its RK3588 target)
-    M, K, N = 128, 11008, 4096
-    B, sw = make_weights(K, N, seed=22)
-    A = make_activations(M, K, seed=22, dtype="f16")
-    w = rk.Weights(dom, B, sw)
-    ws = rk.Workspace(dom, rk.default_config(M, N, K))
-    dA = torch.from_numpy(A.view(np.int16)).to(dev)
-    dC = torch.zeros((M, N), dtype=torch.int16, device=dev)
-    ms = _event_time(torch, stream, lambda: ws.enqueue_f16(w, dA, dC, stream.cuda_stream), 10)
-    cols = sample_columns(N)
+    return out
+
+
+def _check_ffn(oracle, A, Bg, sg, Bd, sd, middle, C):
+    """Sampled check of an FFN result: middle on 17 features x all rows; the output on 17 columns x all rows, from the
+    given middle's own scales (the staged bar for large shapes); a NULL middle checks the first two rows end to end."""
+    from rknpu2_matmul_open_b200.synthetic import sample_columns
+    F, N = Bd.shape
+    if middle is None:
+        rows = min(A.shape[0], 2)
+        ref = oracle.ffn(A[:rows], Bg, sg, Bd, sd, mode=1)
+        return bool(np.array_equal(C[:rows].view(np.uint32), ref["C"].view(np.uint32)))
+    feats = sample_columns(F)
+    pair = np.concatenate([feats, feats + F]).astype(np.int32)
     _, s, inv = oracle.scales(A)
-    ref = oracle.dequant(oracle.gemm_i32_columns(oracle.quantize(A, inv), B, cols), s, sw[cols], True)
-    out["published_shape_M128_K11008_N4096"] = {
-        "us": ms * 1e3, "tops": 2.0 * M * K * N / (ms * 1e-3) / 1e12, "published_ms_on_rk3588": 4.0,
-        "sampled_exact": bool(np.array_equal(dC.cpu().numpy().view(np.uint16)[:, cols], ref))}
-    ws.free()
-    w.free()
-    K, F, N = 4096, 14336, 4096
-    Bg, sg = make_weights(K, 2 * F, seed=31)
-    Bd, sd = make_weights(F, N, seed=32)
+    ref_mid, _ = oracle.swiglu(oracle.gemm_i32_columns(oracle.quantize(A, inv), Bg, pair), s, sg[pair], mode=1)
+    if not np.array_equal(middle[:, feats].view(np.uint32), ref_mid.view(np.uint32)):
+        return False
+    cols = sample_columns(N)
+    _, s2, inv2 = oracle.scales(middle)
+    ref_c = oracle.dequant(oracle.gemm_i32_columns(oracle.quantize(middle, inv2), Bd, cols), s2, sd[cols], False)
+    return bool(np.array_equal(C[:, cols].view(np.uint32), ref_c.view(np.uint32)))
+
+
+def _ffn_figures(rk, ctx, dom, dev, stream, oracle, dist, world, rank, name, K, F, N, batches, seeds):
+    import torch
+    from rknpu2_matmul_open_b200.synthetic import make_activations, make_weights
+    Bg, sg = _tiled_weights(make_weights, K, 2 * F, seeds[0])
+    Bd, sd = _tiled_weights(make_weights, F, N, seeds[1])
     wg, wd = rk.Weights(dom, Bg, sg), rk.Weights(dom, Bd, sd)
-    for M in (1, 128, 1024):
-        A = make_activations(M, K, seed=31, dtype="f32")
+    weight_bytes = K * 2 * F // 2 + F * N // 2
+    out = {}
+    for M in batches:
+        A = make_activations(M, K, seed=seeds[0], dtype="f32")
         g = rk.Workspace(dom, rk.default_config(M, 2 * F, K))
         d = rk.Workspace(dom, rk.default_config(M, N, F))
         dA = torch.from_numpy(A).to(dev)
         dM = torch.zeros((M, F), dtype=torch.float32, device=dev)
         dC = torch.zeros((M, N), dtype=torch.float32, device=dev)
-        ms = _event_time(torch, stream, lambda: rk.enqueue_ffn_f32(g, wg, d, wd, dA, dM, dC, stream.cuda_stream), 10)
-        rows = min(M, 2)
-        ref = oracle.ffn(A[:rows], Bg, sg, Bd, sd, mode=1)
-        exact = bool(np.array_equal(dC.cpu().numpy()[:rows].view(np.uint32), ref["C"].view(np.uint32)))
-        weight_bytes = K * 2 * F // 2 + F * N // 2
-        out[f"ffn_M{M}"] = {"us": ms * 1e3, "weight_GBps": weight_bytes / (ms * 1e-3) / 1e9,
-                            "tops": 2.0 * M * (K * 2 * F + F * N) / (ms * 1e-3) / 1e12, "rows_checked_exact": exact}
+        # a group may skip the fp32 middle and exchange int8 codes when the caller does not need the middle tensor
+        forms = [("middle returned", dM)] + ([("int8 codes exchanged, middle not returned", None)] if world > 1 and (F // 64) % world == 0 else [])
+        timed, exact = {}, True
+        for label, mid in forms:
+            ms = _event_time(torch, stream, lambda: rk.enqueue_ffn_f32(g, wg, d, wd, dA, mid, dC, stream.cuda_stream), 10 if M <= 1024 else 5)
+            timed[label] = _max_over_ranks(torch, dist, dev, world, ms)
+            ok = _check_ffn(oracle, A, Bg, sg, Bd, sd, dM.cpu().numpy() if mid is not None else None, dC.cpu().numpy())
+            exact = exact and _all_ranks_agree(torch, dist, dev, world, ok)
+        if not exact:
+            raise RuntimeError(f"{name} M={M}: result differs from the oracle")
+        best = min(timed, key=timed.get)
+        ms = timed[best]
+        key = f"{name}_M{M}" if world == 1 else f"M{M}"
+        out[key] = {"us": ms * 1e3, "weight_GBps_whole_job": weight_bytes / (ms * 1e-3) / 1e9,
+                    "tops_whole_job": 2.0 * M * (K * 2 * F + F * N) / (ms * 1e-3) / 1e12, "checked_exact": exact,
+                    "form": best, "us_by_form": {k: v * 1e3 for k, v in timed.items()}}
         g.free()
         d.free()
     wg.free()
     wd.free()
-    return out
+    return out if world == 1 else {f"{name}_sharded": out}
 
 
-def _prefill_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_activations, shard_columns):
-    """Benchmark configuration 2 column-sharded over the ranks: every rank runs the 2048 x 4096 prefill GEMM on its run of
-    64-column blocks of N = 14336; figures are whole-job TOPS from the slowest rank's device time, without and
-    with the all-gather that reassembles the [M, N] output on every rank."""
-    import torch
-    M, K, N = 2048, 4096, 14336
-    B, sw = make_weights(K, N, seed=21)
-    A = make_activations(M, K, seed=21, dtype="f16")
-    n0, n1 = shard_columns(N, world, rank)
-    w = rk.Weights(dom, np.ascontiguousarray(B[:, n0:n1]), np.ascontiguousarray(sw[n0:n1]))
-    ws = rk.Workspace(dom, rk.default_config(M, n1 - n0, K))
-    dA = torch.from_numpy(A.view(np.int16)).to(dev)
-    widest = max(b - a for a, b in (shard_columns(N, world, r) for r in range(world)))
-    dC = torch.zeros((M * widest,), dtype=torch.float16, device=dev)          # equal pieces for the collective
-    parts = torch.zeros((world * M * widest,), dtype=torch.float16, device=dev)
-
-    def compute():
-        rc = ws.enqueue_f16(w, dA, dC, stream.cuda_stream)
-        if rc:
-            raise RuntimeError(f"enqueue failed: {rc}")
-
-    def with_gather():
-        compute()
-        dist.all_gather_into_tensor(parts, dC)
-
-    out = {}
-    for name, fn in (("compute", compute), ("compute_plus_all_gather", with_gather)):
-        ms = _event_time(torch, stream, fn, 10)
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-        out[name] = {"us": ms * 1e3, "tops": 2.0 * M * K * N / (ms * 1e-3) / 1e12}
-    ws.free()
-    w.free()
-    return {"prefill_M2048_K4096_N14336_sharded": out}
+def _ffn_llama8b(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak):
+    """Benchmark configuration 3: fused FFN 4096 -> 2 x 14336 -> 4096 at 1, 128 and 1024 tokens (one GPU only)."""
+    if world > 1:
+        return {}
+    return _ffn_figures(rk, ctx, dom, dev, stream, oracle, dist, world, rank, "ffn", 4096, 14336, 4096, (1, 128, 1024), (31, 32))
 
 
-def _ffn_sharded(rk, dom, dev, stream, dist, world, rank, make_weights, make_activations):
-    """Benchmark configuration 4: the 70B-shaped FFN (hidden 8192, intermediate 28672) column-sharded over the ranks.
-    Gate and up are sharded by the same feature slice so SwiGLU stays local.  The down projection contracts over
-    all of F with the scale of the whole row: the ranks all-reduce (max) their slice maxima, quantise their slice
-    with the combined scale and all-gather the int8 codes; the down projection is sharded by output columns and
-    its outputs are all-gathered.  A maximum is a maximum however it is grouped, so results stay bit-exact."""
-    import torch
-    from rknpu2_matmul_open_b200.sharding import gather_columns, shard_columns, shard_ffn_weights, shard_weights
-    K, F, N = 8192, 28672, 8192
-    # weights with the benchmark's value distribution, generated once for a 2048-column block and repeated along N
-    # (generating 700 M codes from fp32 normals would take most of a minute per rank; only time is measured here)
-    blk_g, blk_sg = make_weights(K, 2048, seed=41)
-    blk_d, blk_sd = make_weights(F, 2048, seed=42)
-    Bg, sg = np.tile(blk_g, (1, 2 * F // 2048)), np.tile(blk_sg, 2 * F // 2048)
-    Bd, sd = np.tile(blk_d, (1, N // 2048)), np.tile(blk_sd, N // 2048)
-    Bg_s, sg_s, (f0, f1) = shard_ffn_weights(Bg, sg, world, rank)
-    Bd_s, sd_s, (n0, n1) = shard_weights(Bd, sd, world, rank)
-    del Bg, Bd
-    wg, wd = rk.Weights(dom, Bg_s, sg_s), rk.Weights(dom, Bd_s, sd_s)
-    out = {}
-    for M in (32, 1024, 4096):
-        A = make_activations(M, K, seed=41, dtype="f32")
-        gu = rk.Workspace(dom, rk.default_config(M, 2 * (f1 - f0), K))
-        dn = rk.Workspace(dom, rk.default_config(M, n1 - n0, F))
-        dA = torch.from_numpy(A).to(dev)
-        dMid = torch.zeros((M, f1 - f0), dtype=torch.float32, device=dev)
-        dC = torch.zeros((M, n1 - n0), dtype=torch.float32, device=dev)
-
-        # Equal feature slices that are multiples of 16: the ranks exchange int8 codes (a quarter of the fp32
-        # middle's bytes) after agreeing on the row maxima; otherwise the fp32 middle is gathered.
-        even = (F // 64) % world == 0 and (N // 64) % world == 0
-        if even:
-            maxima = torch.zeros(M, dtype=torch.int32, device=dev)
-            codes = torch.empty((M, f1 - f0), dtype=torch.int8, device=dev)
-            code_parts = torch.empty((world, M, f1 - f0), dtype=torch.int8, device=dev)
-            out_parts = torch.empty((world, M, n1 - n0), dtype=torch.float32, device=dev)
-            out_full = torch.empty((M, N), dtype=torch.float32, device=dev)
-            mid_parts = torch.empty((world, M, f1 - f0), dtype=torch.float32, device=dev)
-            mid_full = torch.empty((M, F), dtype=torch.float32, device=dev)
-
-        def step(codes_exchange=even):
-            if codes_exchange:
-                rc = gu.enqueue_swiglu_collect_f32(wg, dA, dMid, maxima, stream.cuda_stream)
-                dist.all_reduce(maxima, op=dist.ReduceOp.MAX)        # bit patterns of non-negative floats order like ints
-                rc = rc or gu.enqueue_quantize_slice(dMid, maxima, codes, stream.cuda_stream)
-                dist.all_gather_into_tensor(code_parts, codes)
-                rc = rc or dn.enqueue_codes_f32(wd, code_parts, world, maxima, dC, stream.cuda_stream)
-                if rc:
-                    raise RuntimeError(f"enqueue failed: {rc}")
-                dist.all_gather_into_tensor(out_parts, dC)
-                out_full.view(M, world, n1 - n0).copy_(out_parts.permute(1, 0, 2))
-                return out_full
-            rc = gu.enqueue_swiglu_f32(wg, dA, dMid, stream.cuda_stream)
-            if even:   # equal shards: one collective into [world, M, cols] and one strided copy into [M, world * cols]
-                dist.all_gather_into_tensor(mid_parts, dMid)
-                mid_full.view(M, world, f1 - f0).copy_(mid_parts.permute(1, 0, 2))
-                middle = mid_full
-            else:
-                middle = gather_columns(dMid, F)                   # [M, F] on every rank, shards padded to the widest
-            rc = rc or dn.enqueue_f32(wd, middle, dC, stream.cuda_stream)   # rescans the gathered rows: same maxima
-            if rc:
-                raise RuntimeError(f"enqueue failed: {rc}")
-            if even:
-                dist.all_gather_into_tensor(out_parts, dC)
-                out_full.view(M, world, n1 - n0).copy_(out_parts.permute(1, 0, 2))
-                return out_full
-            return gather_columns(dC, N)
-
-        # Both exchanges are timed where both apply: with few tokens the extra all-reduce of the code exchange
-        # costs more than the bytes it saves; every rank takes the same (max-reduced) decision.
-        timed = {}
-        for name, flag in ([("int8 codes", True)] if even else []) + [("fp32 middle", False)]:
-            t = torch.tensor([_event_time(torch, stream, lambda: step(flag), 5)], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            timed[name] = float(t.item())
-        best = min(timed, key=timed.get)
-        ms = timed[best]
-        weight_bytes = K * 2 * F // 2 + F * N // 2
-        out[f"M{M}"] = {"us": ms * 1e3, "weight_GBps_whole_job": weight_bytes / (ms * 1e-3) / 1e9,
-                        "tops_whole_job": 2.0 * M * (K * 2 * F + F * N) / (ms * 1e-3) / 1e12,
-                        "exchange": best, "us_by_exchange": {k: v * 1e3 for k, v in timed.items()}}
-        gu.free()
-        dn.free()
-    wg.free()
-    wd.free()
-    return {"ffn_8192_28672_sharded": out}
+def _ffn_70b(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak):
+    """Benchmark configuration 4: the 70B-shaped FFN (hidden 8192, intermediate 28672) at 32 and 4096 tokens, on one GPU
+    (the baseline of the scaling figures) and column-sharded inside the library on a group."""
+    return _ffn_figures(rk, ctx, dom, dev, stream, oracle, dist, world, rank, "ffn_8192_28672", 8192, 28672, 8192, (32, 4096), (41, 42))
 
 
 def cpu_baseline(M, Reference, oracle, make_weights, make_activations):
@@ -722,6 +719,139 @@ def cpu_baseline(M, Reference, oracle, make_weights, make_activations):
             "sample": f"one decoder layer (7 linears) at M={M}, best of 3 passes, {best * 1e3:.1f} ms per pass"}
 
 
+# ------------------------------------------------------------------ small fixed workloads for profilers
+def _case_weights(rng, K, N):
+    B = rng.integers(-7, 8, size=(K, N), dtype=np.int8)
+    scale = rng.uniform(0.001, 0.01, size=N).astype(np.float32)
+    return B, scale
+
+
+def _case_activations(rng, M, K, dtype):
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    x[:, rng.random(K) < 0.005] *= 20.0
+    return x.astype(dtype)
+
+
+def run_case(args):
+    """`--case decode|prefill|mid|ffn [--repeat R] [--tokens M] [--stamps]`: a handful of launches of one hot-path
+    configuration on seeded synthetic data, so that a kernel profiler can capture one to three launches of the
+    kernel of interest in a minute or two (no JSON line, no timing claims):
+      decode   the seven Llama-7B decode linears (4 x 4096->4096, 2 x 4096->11008, 11008->4096), M = 8, binary16
+      prefill  one 2048 x 4096 x 14336 linear, binary16
+      mid      one 128 x 11008 x 8192 linear, binary16 (few tiles, long K)
+      ffn      gate/up 4096 -> 2 x 14336, SwiGLU, down 14336 -> 4096 at M = 1024, fp32
+    --stamps enables the kernels' phase stamps after the launches, runs the set again (the decode set as one CUDA
+    graph, the steady state of a dependent chain) and prints them."""
+    import torch
+
+    import rknpu2_matmul_open_b200 as rk
+
+    rng = np.random.default_rng(0)
+    ctx = rk.Context()
+    dom = ctx.domain(0)
+    dev = torch.device("cuda", ctx.device)
+    stream = torch.cuda.Stream(device=dev)
+    calls = []
+    if args.case in ("decode", "prefill", "mid"):
+        M = args.case_tokens or {"decode": 8, "prefill": 2048, "mid": 128}[args.case]
+        shapes = {"decode": LLAMA7B_LAYER, "prefill": [(4096, 14336)], "mid": [(11008, 8192)]}[args.case]
+        for K, N in shapes:
+            B, sw = _case_weights(rng, K, N)
+            w = rk.Weights(dom, B, sw)
+            ws = rk.Workspace(dom, rk.default_config(M, N, K))
+            dA = torch.from_numpy(_case_activations(rng, M, K, np.float16).view(np.int16)).to(dev)
+            dC = torch.zeros((M, N), dtype=torch.int16, device=dev)
+            calls.append((lambda ws=ws, w=w, dA=dA, dC=dC: ws.enqueue_f16(w, dA, dC, stream.cuda_stream), ws))
+    else:
+        M = args.case_tokens or 1024
+        K, F, N = 4096, 14336, 4096
+        Bg, sg = _case_weights(rng, K, 2 * F)
+        Bd, sd = _case_weights(rng, F, N)
+        wg, wd = rk.Weights(dom, Bg, sg), rk.Weights(dom, Bd, sd)
+        g = rk.Workspace(dom, rk.default_config(M, 2 * F, K))
+        d = rk.Workspace(dom, rk.default_config(M, N, F))
+        dA = torch.from_numpy(_case_activations(rng, M, K, np.float32)).to(dev)
+        dM = torch.zeros((M, F), dtype=torch.float32, device=dev)
+        dC = torch.zeros((M, N), dtype=torch.float32, device=dev)
+        calls.append((lambda: rk.enqueue_ffn_f32(g, wg, d, wd, dA, dM, dC, stream.cuda_stream), d))
+        calls.append((lambda: 0, g))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for rep in range(args.repeat):
+        with torch.cuda.stream(stream):
+            if rep == args.repeat - 1:
+                e0.record(stream)
+            for fn, _ in calls:
+                rc = fn()
+                if rc:
+                    raise RuntimeError(f"enqueue failed: {rc}")
+            if rep == args.repeat - 1:
+                e1.record(stream)
+        stream.synchronize()
+    for _, ws in calls:
+        if ws.finish() != 0:
+            raise RuntimeError("device status not clean")
+    print(f"{args.case}: M={M}, last set {e0.elapsed_time(e1) * 1e3:.1f} us for {len(calls)} call(s)")
+    if args.stamps:
+        _print_stamps(rk, args.case, calls, stream, torch)
+
+
+def _print_stamps(rk, case, calls, stream, torch):
+    lib = rk.capi.load()
+    for _, ws in calls:
+        lib.rk_npu_b200_w4a8_trace_enable(ws.handle, 1)
+    graph = None
+    if case == "decode":     # steady state of a dependent chain: replay the set as one CUDA graph
+        with torch.cuda.stream(stream):
+            for fn, _ in calls:
+                fn()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for fn, _ in calls:
+                fn()
+    for _ in range(3):
+        with torch.cuda.stream(stream):
+            if graph is not None:
+                graph.replay()
+            else:
+                for fn, _ in calls:
+                    fn()
+        stream.synchronize()
+    torch.cuda.synchronize()
+    if graph is not None:
+        ms = _event_time(torch, stream, graph.replay, 20)
+        print(f"graph replay: {ms * 1e3:.1f} us per set of {len(calls)} linears")
+    if case == "decode":
+        prev_end = None
+        print("per linear, ns relative to the previous linear's last CTA end: first/last CTA start, first/last CTA end;"
+              " then median cycles since CTA start at: before the dependency wait, dependency met, share"
+              " quantised and sent, all codes landed, last contraction done, last output stored")
+        for i, (_, ws) in enumerate(calls):
+            buf = np.zeros((4112, 8), np.uint64)
+            lib.rk_npu_b200_w4a8_trace_read(ws.handle, buf.ctypes.data, 4112)
+            stages = buf[4096:4098].reshape(-1).astype(np.int64)
+            scan = buf[4104].astype(np.int64)[:4]
+            v = buf[:4096]
+            v = v[v[:, 0] > 0].astype(np.int64)
+            if not len(v):
+                continue
+            s0, s1, e0, e1 = v[:, 0].min(), v[:, 0].max(), v[:, 7].min(), v[:, 7].max()
+            ref = prev_end if prev_end is not None else s0
+            cyc = [int(x) for x in np.median(v[:, 1:7], axis=0)]
+            print(f"linear {i}: K={ws.cfg.K} N={ws.cfg.N} ctas={len(v)} start[{s0 - ref},{s1 - ref}] end[{e0 - ref},{e1 - ref}] cycles {cyc}")
+            print(f"   CTA 0, cycles since its start: loads issued, own maxima in, row maxima known, share quantised: {[int(x) for x in scan]};"
+                  f" first weight stages (wait begins, wait ends): {[int(x) for x in stages]}")
+            prev_end = e1
+    elif case == "prefill":
+        raw = np.zeros(256, np.uint64)
+        lib.rk_npu_b200_w4a8_trace_read(calls[0][1].handle, raw.ctypes.data, 32)
+        print(f"clusters in the grid: {int(raw[200])}; per tile of cluster 0 (cycles since kernel start): MMA issuer begins,"
+              " first MMA issued, last commit, epilogue sees the accumulator, tensor memory handed back, tile stored,"
+              " cycles the issuer waited for operands | unpack warp: waited for weights, for a free buffer, for activations")
+        for j in range(7):
+            print(f"tile {j}: {[int(x) for x in raw[j * 8:j * 8 + 7]]} | {int(raw[128 + 2 * j])} {int(raw[129 + 2 * j])} {int(raw[160 + j])}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -734,10 +864,17 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--case", choices=["decode", "prefill", "mid", "ffn"], help="run a small profiler workload instead of the benchmark")
+    ap.add_argument("--repeat", type=int, default=4, help="--case: launch sets")
+    ap.add_argument("--case-tokens", type=int, default=0, help="--case: override the batch")
+    ap.add_argument("--stamps", action="store_true", help="--case: print the kernels' phase stamps")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.case:
+        run_case(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return

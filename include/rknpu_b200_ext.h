@@ -89,6 +89,20 @@ int rk_npu_b200_w4a8_enqueue_ffn_f32(rk_npu_w4a8_workspace *gate_up, const rk_np
                                      rk_npu_w4a8_workspace *down, const rk_npu_w4a8_weights *down_weights,
                                      const float *dA, float *dMiddle, float *dC, void *cuda_stream);
 
+/* Several INDEPENDENT linears in one launch.  On a stream, every queued linear waits for the one in front, so a
+ * decoder layer's q / k / v projections (or gate and up), which read the same activations and do not depend on
+ * each other, pay the dependent latency of a small-batch launch three times.  This call queues up to four
+ * linears of up to eight tokens (the same token count for all, binary16, workspaces of the single-launch decode
+ * family) as ONE kernel launch: they wait once for whatever is in front of them on the stream and then run
+ * side by side.  Outputs are written as by rk_npu_b200_w4a8_enqueue_local_f16 (on one GPU: the whole
+ * [M,N]; in a group: this rank's columns, compact).  The caller states the independence: no dLocal[i] may
+ * be read as a dA[j] of the same call.  The launch is counted on the first workspace.
+ * RK_NPU_ERR_PARAM for other workspace families, mixed token counts or repeated workspaces / outputs.
+ * No counterpart in the original project. */
+int rk_npu_b200_w4a8_enqueue_batch_f16(int count, rk_npu_w4a8_workspace *const *workspaces,
+                                       const rk_npu_w4a8_weights *const *weights, const uint16_t *const *dA,
+                                       uint16_t *const *dLocal, void *cuda_stream);
+
 /* ---- Column-sharded FFN: the pieces around the exchange between GPUs ----------------------
  * When gate/up and down are sharded by output columns over g GPUs (each GPU holds the gate and
  * up columns of one feature slice f0..f1 and a column slice of down), a GPU produces

@@ -222,6 +222,7 @@ _SIGNATURES = {
     "rk_npu_b200_w4a8_enqueue_local_f16": (C.c_int, [_P, _P, _P, _P, _P]),
     "rk_npu_b200_w4a8_enqueue_local_f32": (C.c_int, [_P, _P, _P, _P, _P]),
     "rk_npu_b200_group_all_gather": (C.c_int, [_P, _P, C.c_size_t, _P]),
+    "rk_npu_b200_w4a8_enqueue_batch_f16": (C.c_int, [C.c_int, C.POINTER(_P), C.POINTER(_P), C.POINTER(_P), C.POINTER(_P), _P]),
     "rk_npu_b200_open_offline": (_P, [C.c_uint32]),
     "rk_npu_b200_w4a8_enqueue_f32": (C.c_int, [_P, _P, _P, _P, _P]),
     "rk_npu_b200_w4a8_enqueue_f16": (C.c_int, [_P, _P, _P, _P, _P]),

@@ -310,6 +310,35 @@ int fused_tiles_per_cta(const rk_npu_w4a8_workspace& ws, int tiles, int split, i
     return all > half_gpu ? 2 : 1;
 }
 
+// Launch parameters of the decode kernel for one call (its workspace runs that family).
+void decode_params(const Call& c, DecodeParams& d, int cluster_override = 0)
+{
+    auto& ws = *c.ws;
+    const auto& cfg = ws.config;
+    const int N = ws.shard_N;
+    const bool swiglu = c.epi == EPI_SWIGLU;
+    const int F = swiglu ? N / 2 : 0;
+    d.Wp = c.w->packed;
+    d.A = c.dA;
+    d.sw = c.w->scales;
+    d.out = c.dOut;
+    d.rowmax_out = c.rowmax_out;
+    d.rowmax_in = c.rowmax_in;
+    d.scales_out = ws.scales;
+    d.codes_out = c.keep_codes ? ws.codes : nullptr;
+    d.status = ws.status;
+    d.M = cfg.M; d.N = N; d.K = cfg.K;
+    d.KB = ws.KB; d.NG = c.w->NG; d.F = F; d.epi = c.epi;
+    d.half = c.half ? 1 : 0;
+    d.cluster = cluster_override ? cluster_override : ws.split_override ? ws.split_override : gemm_decode_cluster(cfg.M, ws.KB);
+    d.ring = gemm_decode_ring(cfg.M, ws.KB, swiglu);
+    const int slot = d.cluster == 1 ? 0 : d.cluster == 2 ? 1 : d.cluster == 4 ? 2 : 3;
+    d.ctas = gemm_decode_ctas(swiglu ? F / GROUP : (N + GROUP - 1) / GROUP, d.cluster, ws.decode_cap[slot]);
+    d.timeout_ns = (unsigned long long)cfg.timeout_ms * 1000000ull;
+    d.trace = ws.trace;
+    d.starve = ws.starve ? 1 : 0;
+}
+
 int enqueue(const Call& c)
 {
     auto& ws = *c.ws;
@@ -323,26 +352,7 @@ int enqueue(const Call& c)
     if (ws.variant == 5 && !c.codes_in) {
         // One kernel, whole-K CTAs: scan + quantise (shared by a cluster) + GEMM + epilogue.
         DecodeParams d{};
-        d.Wp = c.w->packed;
-        d.A = c.dA;
-        d.sw = c.w->scales;
-        d.out = c.dOut;
-        d.rowmax_out = c.rowmax_out;
-        d.rowmax_in = c.rowmax_in;
-        d.scales_out = ws.scales;
-        d.codes_out = c.keep_codes ? ws.codes : nullptr;
-        d.status = ws.status;
-        d.M = cfg.M; d.N = N; d.K = cfg.K;
-        d.KB = ws.KB; d.NG = c.w->NG; d.F = F; d.epi = c.epi;
-        d.half = c.half ? 1 : 0;
-        const bool swiglu = c.epi == EPI_SWIGLU;
-        d.cluster = ws.split_override ? ws.split_override : gemm_decode_cluster(cfg.M, ws.KB);
-        d.ring = gemm_decode_ring(cfg.M, ws.KB, swiglu);
-        const int slot = d.cluster == 1 ? 0 : d.cluster == 2 ? 1 : d.cluster == 4 ? 2 : 3;
-        d.ctas = gemm_decode_ctas(swiglu ? F / GROUP : (N + GROUP - 1) / GROUP, d.cluster, ws.decode_cap[slot]);
-        d.timeout_ns = timeout_ns;
-        d.trace = ws.trace;
-        d.starve = ws.starve ? 1 : 0;
+        decode_params(c, d);
         if (c.events) cudaEventRecord(c.events[1], c.stream);
         if (launch_gemm_decode(d, c.stream, pdl) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
         if (c.events) cudaEventRecord(c.events[2], c.stream);
@@ -1175,6 +1185,44 @@ extern "C" int rk_npu_b200_w4a8_enqueue_f16(rk_npu_w4a8_workspace* ws, const rk_
 {
     return enqueue_public(ws, w, dA, dC, true, EPI_F16, stream);
 }
+// ---- several independent linears in one launch
+extern "C" int rk_npu_b200_w4a8_enqueue_batch_f16(int count, rk_npu_w4a8_workspace* const* workspaces,
+                                                  const rk_npu_w4a8_weights* const* weights, const uint16_t* const* dA,
+                                                  uint16_t* const* dLocal, void* stream)
+{
+    if (count < 1 || count > DEC_MAX_BATCH || !workspaces || !weights || !dA || !dLocal) return RK_NPU_ERR_PARAM;
+    for (int i = 0; i < count; ++i) {
+        const int rc = validate(workspaces[i], weights[i], dA[i], dLocal[i], false);
+        if (rc) return rc;
+        for (int j = 0; j < i; ++j)
+            if (workspaces[j] == workspaces[i] || dLocal[j] == dLocal[i]) return RK_NPU_ERR_PARAM;
+        const auto* ws = workspaces[i];
+        if (ws->variant != 5 || ws->config.M != workspaces[0]->config.M || ws->ctx_id != workspaces[0]->ctx_id) return RK_NPU_ERR_PARAM;
+    }
+    // one cluster size for the launch: the one the longest reduction asks for
+    int cluster = 1;
+    for (int i = 0; i < count; ++i) cluster = std::max(cluster, gemm_decode_cluster(workspaces[i]->config.M, workspaces[i]->KB));
+    std::unique_ptr<WorkspaceLock> locks[DEC_MAX_BATCH];
+    for (int i = 0; i < count; ++i) {
+        locks[i].reset(new WorkspaceLock(*workspaces[i]));
+        if (!*locks[i]) return RK_NPU_ERR_BUSY;
+    }
+    if (cudaSetDevice(workspaces[0]->domain->ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    DecodeBatch batch{};
+    batch.count = count;
+    batch.first_cta[0] = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    for (int i = 0; i < count; ++i) {
+        Call call{workspaces[i], weights[i], dA[i], dLocal[i], true, EPI_F16, nullptr, nullptr, s, nullptr};
+        decode_params(call, batch.p[i], cluster);
+        batch.p[i].trace = nullptr;
+        batch.first_cta[i + 1] = batch.first_cta[i] + batch.p[i].ctas;
+    }
+    if (launch_gemm_decode_batch(batch, s, env_flag("RK_NPU_B200_PDL", true)) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+    workspaces[0]->launches.fetch_add(1, std::memory_order_relaxed);
+    return RK_NPU_OK;
+}
+
 // ---- group of GPUs without the exchange: this rank's columns only, compact [M][columns]
 extern "C" int rk_npu_b200_w4a8_workspace_shard(const rk_npu_w4a8_workspace* ws, int* two_range, int* n0, int* n1, int* columns)
 {

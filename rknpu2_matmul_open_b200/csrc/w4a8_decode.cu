@@ -72,8 +72,9 @@ __device__ __forceinline__ int red_index(int warp, int rows, int row, int tok)
 
 // DOT: up to four tokens, contraction on the integer dot-product units (eight-column tensor-core tiles would be
 // at most half empty, and this GPU's legacy mma.sync int8 path issues one tile per ~11 cycles per SM).
+// One CTA of one linear: `cta` of `nctas` (the kernels below map the grid onto one or several linears).
 template <bool HALF, bool DOT, bool TRACE>
-__global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const DecodeParams p)
+__device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned cta, const unsigned nctas)
 {
     using AT = typename ActType<HALF>::type;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -94,14 +95,14 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
 
     pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int S = p.cluster, rank = S > 1 ? (int)(blockIdx.x % (unsigned)S) : 0;
-    const int ncta = (int)gridDim.x;
+    const int S = p.cluster, rank = S > 1 ? (int)(cta % (unsigned)S) : 0;
+    const int ncta = (int)nctas;
     const int items = swiglu ? p.F / GROUP : (p.N + GROUP - 1) / GROUP;
     const int spg = (KC + DEC_STAGE_CHUNKS - 1) / DEC_STAGE_CHUNKS;             // stages per weight group
     const int gpi = swiglu ? 2 : 1;                                              // weight groups per item
-    const int my_items = (int)blockIdx.x < items ? (items - 1 - (int)blockIdx.x) / ncta + 1 : 0;
+    const int my_items = (int)cta < items ? (items - 1 - (int)cta) / ncta + 1 : 0;
     const int my_stages = my_items * gpi * spg;
-    unsigned long long* const trace = (TRACE && p.trace && tid == 0) ? p.trace + (size_t)blockIdx.x * 8 : nullptr;
+    unsigned long long* const trace = (TRACE && p.trace && tid == 0) ? p.trace + (size_t)cta * 8 : nullptr;
     long long c_start = 0;
     if (TRACE) { c_start = clock64(); if (trace) trace[0] = global_ns(); }
 
@@ -135,7 +136,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
                 }
                 const int j = i / per_item, rem = i - j * per_item;
                 const int g = rem / spg, s = rem - g * spg;
-                const int item = (int)blockIdx.x + j * ncta;
+                const int item = (int)cta + j * ncta;
                 const int group = g == 0 ? item : p.F / GROUP + item;
                 const int c0 = s * DEC_STAGE_CHUNKS;
                 const uint32_t bytes = (uint32_t)min(DEC_STAGE_CHUNKS, KC - c0) * 512u;
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
         sw_a = n < p.NG * GROUP ? p.sw[n] : 0.f;
         if (swiglu) sw_b = p.sw[p.F + n];
     };
-    if (my_items > 0) load_channel_scales((int)blockIdx.x);
+    if (my_items > 0) load_channel_scales((int)cta);
 
     // ---- 1. this CTA's share of the quantisation.  Mc >= S: whole rows of TQ tokens; else one token's
     // K range is split over P CTAs, each of which still scans the whole row for the maximum.
@@ -207,7 +208,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
             }
         }
     }
-    if (TRACE && trace && blockIdx.x == 0) p.trace[8 * 4096 + 64] = (unsigned long long)(clock64() - c_start);   // loads issued
+    if (TRACE && trace && cta == 0) p.trace[8 * 4096 + 64] = (unsigned long long)(clock64() - c_start);   // loads issued
     if (!no_scan) {
 #pragma unroll
         for (int it = 0; it < UMAX; ++it) {
@@ -229,10 +230,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
                 atomicMax(&s_max[tl], raw_maxbits<HALF>(r));
             }
         }
-        if (TRACE && trace && blockIdx.x == 0) p.trace[8 * 4096 + 65] = (unsigned long long)(clock64() - c_start);   // own maxima in
+        if (TRACE && trace && cta == 0) p.trace[8 * 4096 + 65] = (unsigned long long)(clock64() - c_start);   // own maxima in
         bar_sync_contraction();
     }
-    if (TRACE && trace && blockIdx.x == 0) p.trace[8 * 4096 + 66] = (unsigned long long)(clock64() - c_start);       // row maxima known
+    if (TRACE && trace && cta == 0) p.trace[8 * 4096 + 66] = (unsigned long long)(clock64() - c_start);       // row maxima known
     // scale of one of this CTA's tokens; every CTA that shares a token derives the same values
     auto token_scale = [&](int tl, uint32_t collected, float& s, float& inv) -> int {
         int bad;
@@ -248,7 +249,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
         scale_from_max(maximum, bad != 0, s, inv);
         return bad;
     };
-    const bool first_cluster = (int)blockIdx.x < S;
+    const bool first_cluster = (int)cta < S;
     const uint32_t xs_base = smem_u32(xs), bar_base = smem_u32(code_bar);
     if (S > 1) cluster_wait();
     auto publish = [&](int tok, int u, const uint4& q) {
@@ -284,7 +285,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
             publish(tok, u, quantize16(v, inv, u * 16, p.K));
         }
     }
-    if (TRACE && trace && blockIdx.x == 0) p.trace[8 * 4096 + 67] = (unsigned long long)(clock64() - c_start);       // share quantised
+    if (TRACE && trace && cta == 0) p.trace[8 * 4096 + 67] = (unsigned long long)(clock64() - c_start);       // share quantised
     if (part == 0 && tid < TQ && t0 + tid < M) {
         // the token's scale (or the reason it has none) travels with the codes
         const int tok = t0 + tid;
@@ -317,7 +318,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
     uint32_t run_max = 0;
     int stage_i = 0;
     for (int j = 0; j < my_items; ++j) {
-        const int item = (int)blockIdx.x + j * ncta;
+        const int item = (int)cta + j * ncta;
         if constexpr (DOT) {
             // Integer dot products: lane = channel of the group, every lane the same 32 activations of a chunk
             // (broadcast reads).  One weight word holds eight codes; (w << 4) & mask and w & mask are the two
@@ -338,9 +339,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
                     for (int t = 0; t < 4; ++t) dacc4[i][t] = 0;
                 for (int s = 0; s < spg; ++s, ++stage_i) {
                     const int slot = stage_i % R;
-                    if (TRACE && trace && blockIdx.x == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i] = (unsigned long long)(clock64() - c_start);
+                    if (TRACE && trace && cta == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i] = (unsigned long long)(clock64() - c_start);
                     if (!mbar_wait_all_lanes(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
-                    if (TRACE && trace && blockIdx.x == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i + 1] = (unsigned long long)(clock64() - c_start);
+                    if (TRACE && trace && cta == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i + 1] = (unsigned long long)(clock64() - c_start);
                     if (!verdict && !failed) {
                         const int c0 = s * DEC_STAGE_CHUNKS, nch = min(DEC_STAGE_CHUNKS, KC - c0);
                         // a warp's four chunks of the stage: every load first, then four independent dot-product chains per token
@@ -403,9 +404,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
                         for (int e = 0; e < 4; ++e) a[i][m][e] = 0;
                 for (int s = 0; s < spg; ++s, ++stage_i) {
                     const int slot = stage_i % R;
-                    if (TRACE && trace && blockIdx.x == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i] = (unsigned long long)(clock64() - c_start);
+                    if (TRACE && trace && cta == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i] = (unsigned long long)(clock64() - c_start);
                     if (!mbar_wait_all_lanes(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
-                    if (TRACE && trace && blockIdx.x == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i + 1] = (unsigned long long)(clock64() - c_start);
+                    if (TRACE && trace && cta == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i + 1] = (unsigned long long)(clock64() - c_start);
                     if (!verdict && !failed) {
                         const int c0 = s * DEC_STAGE_CHUNKS, nch = min(DEC_STAGE_CHUNKS, KC - c0);
                         const uint32_t* const wslot = reinterpret_cast<const uint32_t*>(ring + (size_t)slot * DEC_STAGE_BYTES) + g8 * 4 + t4;
@@ -490,15 +491,33 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const Decod
     if (failed && lane == 0) atomicExch(&p.status->device_error, 1);
     if (TRACE && trace) trace[7] = global_ns();
     if (tid == 0) {
-        if (blockIdx.x == 0) p.status->bad_input = verdict;
+        if (cta == 0) p.status->bad_input = verdict;
         if (no_scan) {
             // Every CTA has read the collected maxima by now; the last one to get here clears them
             // for the next SwiGLU epilogue.  The ticket counter wraps by itself.
             __threadfence();
-            if (atomicInc(&p.status->done, gridDim.x - 1u) == gridDim.x - 1u)
+            if (atomicInc(&p.status->done, nctas - 1u) == nctas - 1u)
                 for (int t = 0; t < M; ++t) p.rowmax_in[t] = 0u;
         }
     }
+}
+
+template <bool HALF, bool DOT, bool TRACE>
+__global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const DecodeParams p)
+{
+    decode_cta<HALF, DOT, TRACE>(p, blockIdx.x, gridDim.x);
+}
+
+// Several INDEPENDENT linears (same token count, activation type and cluster size) in one launch: the grid is the
+// concatenation of their CTAs.  A decoder layer's q/k/v (or gate/up) projections read the same activations and
+// do not depend on each other; launched one by one on a stream each would wait for the one in front, in one
+// launch they pay the dependent latency once while their weights stream together.
+template <bool HALF, bool DOT>
+__global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_batch_kernel(const DecodeBatch b)
+{
+    int i = 0;
+    while (i + 1 < b.count && (int)blockIdx.x >= b.first_cta[i + 1]) ++i;
+    decode_cta<HALF, DOT, false>(b.p[i], blockIdx.x - (unsigned)b.first_cta[i], (unsigned)(b.first_cta[i + 1] - b.first_cta[i]));
 }
 
 // ---------------------------------------------------------------------------------- host side
@@ -601,6 +620,64 @@ cudaError_t launch_gemm_decode(const DecodeParams& p, cudaStream_t stream, bool 
     }
     if (dot) return p.half ? launch_decode_inst<true, true, false>(p, stream, pdl) : launch_decode_inst<false, true, false>(p, stream, pdl);
     return p.half ? launch_decode_inst<true, false, false>(p, stream, pdl) : launch_decode_inst<false, false, false>(p, stream, pdl);
+}
+
+template <bool HALF, bool DOT>
+static cudaError_t launch_decode_batch_inst(const DecodeBatch& b, cudaStream_t stream, bool pdl)
+{
+    auto kernel = gemm_decode_batch_kernel<HALF, DOT>;
+    static PerDeviceOnce configured;
+    int device = -1;
+    if (configured.needed(device)) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_LIMIT);
+        if (e != cudaSuccess) return e;
+        configured.mark(device);
+    }
+    size_t smem = 0;
+    for (int i = 0; i < b.count; ++i) {
+        const size_t need = dec_smem_bytes(b.p[i].M, b.p[i].KB, b.p[i].epi == EPI_SWIGLU, b.p[i].ring);
+        smem = need > smem ? need : smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)b.first_cta[b.count], 1, 1);
+    cfg.blockDim = dim3(DEC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (b.p[0].cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)b.p[0].cluster;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, b);
+}
+
+// All linears of a batch: same M, activation type and cluster size; grid pieces are multiples of the cluster size.
+cudaError_t launch_gemm_decode_batch(const DecodeBatch& b, cudaStream_t stream, bool pdl)
+{
+    if (b.count < 1 || b.count > DEC_MAX_BATCH || b.first_cta[0] != 0) return cudaErrorInvalidValue;
+    for (int i = 0; i < b.count; ++i) {
+        const DecodeParams& p = b.p[i];
+        const bool swiglu = p.epi == EPI_SWIGLU;
+        if (p.M != b.p[0].M || p.half != b.p[0].half || p.cluster != b.p[0].cluster || p.trace || p.M < 1 || p.M > 8 ||
+            (p.cluster != 1 && p.cluster != 2 && p.cluster != 4 && p.cluster != 8) || p.ring < 2 || p.ring > DEC_MAX_RING ||
+            p.ctas < p.cluster || p.ctas % p.cluster || b.first_cta[i + 1] - b.first_cta[i] != p.ctas || (swiglu && p.F % GROUP) ||
+            dec_smem_bytes(p.M, p.KB, swiglu, p.ring) > DEC_SMEM_LIMIT || (long long)p.KB * KBLOCK > 131072)
+            return cudaErrorInvalidValue;
+    }
+    const bool dot = b.p[0].M <= 4;
+    if (dot) return b.p[0].half ? launch_decode_batch_inst<true, true>(b, stream, pdl) : launch_decode_batch_inst<false, true>(b, stream, pdl);
+    return b.p[0].half ? launch_decode_batch_inst<true, false>(b, stream, pdl) : launch_decode_batch_inst<false, false>(b, stream, pdl);
 }
 
 // Resident clusters of this kernel with `smem` bytes of dynamic shared memory, times the cluster size:

@@ -178,6 +178,14 @@ struct AssembleParams {
 };
 cudaError_t launch_assemble_columns(const AssembleParams& p, cudaStream_t stream);
 
+// Several independent decode linears in one launch (same token count, activation type, cluster size).
+constexpr int DEC_MAX_BATCH = 4;
+struct DecodeBatch {
+    DecodeParams p[DEC_MAX_BATCH];
+    int first_cta[DEC_MAX_BATCH + 1];   // grid piece of linear i: [first_cta[i], first_cta[i + 1])
+    int count;
+};
+
 struct PackParams {
     const int8_t* B;        // [K,N] codes on the device
     uint8_t* Wp;
@@ -209,6 +217,7 @@ int gemm_decode_cluster(int M, int KB);
 int gemm_decode_ctas(int items, int cluster, int cap);
 int gemm_decode_resident_ctas(int cluster, size_t smem, int sm_count);
 cudaError_t launch_gemm_decode(const DecodeParams& p, cudaStream_t stream, bool pdl);
+cudaError_t launch_gemm_decode_batch(const DecodeBatch& b, cudaStream_t stream, bool pdl);
 // tcgen05 path: p.T is the token tile of the code layout (multiple of 16, <= 256; 128 when p.pair)
 cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl);
 bool gemm_tc_supported(const GemmParams& p);

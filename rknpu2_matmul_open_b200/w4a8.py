@@ -237,6 +237,15 @@ def run_ffn_f32(gate_up: Workspace, gate_up_weights: Weights, down: Workspace, d
                                                C.byref(timings) if timings is not None else None)
 
 
+def enqueue_batch_f16(workspaces, weights, dAs, dLocals, stream: int = 0) -> int:
+    """rk_npu_b200_w4a8_enqueue_batch_f16: up to four independent decode linears (same token count) in one launch."""
+    n = len(workspaces)
+    arr = lambda items: (C.c_void_p * n)(*[x if isinstance(x, C.c_void_p) else C.c_void_p(x) for x in items])
+    return workspaces[0].lib.rk_npu_b200_w4a8_enqueue_batch_f16(
+        n, arr([w.handle for w in workspaces]), arr([w.handle for w in weights]), arr([_ptr(a) for a in dAs]),
+        arr([_ptr(c) for c in dLocals]), C.c_void_p(stream))
+
+
 def enqueue_ffn_f32(gate_up: Workspace, gate_up_weights: Weights, down: Workspace, down_weights: Weights, dA, dMiddle,
                     dC, stream: int = 0) -> int:
     return gate_up.lib.rk_npu_b200_w4a8_enqueue_ffn_f32(gate_up.handle, gate_up_weights.handle, down.handle,
@@ -245,4 +254,4 @@ def enqueue_ffn_f32(gate_up: Workspace, gate_up_weights: Weights, down: Workspac
 
 
 __all__ = ["Context", "Domain", "Weights", "Workspace", "W4A8Error", "default_config", "memory_query", "run_ffn_f32",
-           "enqueue_ffn_f32", "RK_NPU_OK"]
+           "enqueue_ffn_f32", "enqueue_batch_f16", "RK_NPU_OK"]

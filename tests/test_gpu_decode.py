@@ -120,3 +120,41 @@ def test_rejected_inputs_and_reuse(gpu, oracle):
     assert np.array_equal(bits(out), bits(oracle.linear(A, B, sw)[1]))
     ws.free()
     w.free()
+
+
+@pytest.mark.parametrize("M", [1, 4, 8])
+def test_independent_linears_in_one_launch(gpu, oracle, M):
+    # q / k / v style: the same activations through three weights of different widths, then two of different K
+    import torch
+    lib = capi.load()
+    _, dom, _ = gpu
+    stream = torch.cuda.Stream()
+    for shapes in ([(2304, 1000), (2304, 385), (2304, 4096)], [(1057, 193), (4096, 512)], [(513, 64)]):
+        ws, w, dA, dC, ref = [], [], [], [], []
+        for i, (K, N) in enumerate(shapes):
+            B, sw = make_weights(K, N, seed=N + i)
+            A = make_activations(M, K, seed=K, dtype="f16")
+            w.append(rk.Weights(dom, B, sw))
+            ws.append(rk.Workspace(dom, rk.default_config(M, N, K)))
+            dA.append(torch.from_numpy(A.view(np.int16)).cuda())
+            dC.append(torch.full((M, N), 0x5555, dtype=torch.int16, device="cuda"))
+            ref.append(oracle.linear(A, B, sw)[1])
+        torch.cuda.synchronize()
+        before = ws[0].launch_count()
+        assert rk.enqueue_batch_f16(ws, w, dA, dC, stream.cuda_stream) == 0
+        stream.synchronize()
+        assert ws[0].launch_count() == before + 1                      # one launch for all of them
+        for x, c, r in zip(ws, dC, ref):
+            assert x.finish() == 0
+            assert np.array_equal(c.cpu().numpy().view(np.uint16), r)
+        # argument errors: a repeated workspace, mixed token counts
+        assert rk.enqueue_batch_f16([ws[0], ws[0]], [w[0], w[0]], [dA[0], dA[0]], [dC[0], dC[0]], stream.cuda_stream) == capi.RK_NPU_ERR_PARAM
+        if M < 8:
+            other = rk.Workspace(dom, rk.default_config(M + 1, shapes[0][1], shapes[0][0]))
+            dA2 = torch.zeros((M + 1, shapes[0][0]), dtype=torch.int16, device="cuda")
+            dC2 = torch.zeros((M + 1, shapes[0][1]), dtype=torch.int16, device="cuda")
+            if len(ws) > 1:
+                assert rk.enqueue_batch_f16([other, ws[1]], [w[0], w[1]], [dA2, dA[1]], [dC2, dC[1]], stream.cuda_stream) == capi.RK_NPU_ERR_PARAM
+            other.free()
+        for x in ws + w:
+            x.free()
