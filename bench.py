@@ -247,9 +247,10 @@ def measure_int8_peak():
         return None
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
     try:
-        out = subprocess.run([str(exe), "60000"], capture_output=True, text=True, timeout=120).stdout
-    except (OSError, subprocess.TimeoutExpired):
-        out = ""
+        run = subprocess.run([str(exe), "60000"], capture_output=True, text=True, timeout=120)
+        out = run.stdout + run.stderr
+    except (OSError, subprocess.TimeoutExpired) as exc:
+        out = f"{type(exc).__name__}: {exc}"
     clocks = sampler.stop()
     best = 0.0
     for line in out.splitlines():
@@ -258,8 +259,11 @@ def measure_int8_peak():
                 best = max(best, float(line.split("->")[1].split("TOPS")[0]))
             except (IndexError, ValueError):
                 pass
+    if not best:
+        print(f"[bench] int8 peak tool gave no figure: {out[-400:]!r}", file=sys.stderr)
+        return None
     return {"tops": best, "sm_mhz": clocks["sm_mhz"], "reasons": clocks["reasons"],
-            "how": "lib/int8_peak 60000: 128x256x32 kind::i8 MMAs back to back on every SM, best of the runs"} if best else None
+            "how": "lib/int8_peak 60000: 128x256x32 kind::i8 MMAs back to back on every SM, best of the runs"}
 
 
 def run_cuda(args, rank, world, local_rank):

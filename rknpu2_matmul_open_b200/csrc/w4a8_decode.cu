@@ -10,7 +10,7 @@
 //   * A CTA owns whole output channels: 32-channel weight groups (a gate group and its up partner for
 //     SwiGLU) over ALL of K, dealt round-robin to the CTAs.  Nothing is summed across CTAs; the K range
 //     is split over the CTA's own eight contraction warps and summed through its shared memory.
-//   * A ninth warp streams the CTA's weights through a ring of 16 KB stages with bulk async copies.
+//   * A ninth warp streams the CTA's weights through a ring of 32 KB stages with bulk async copies.
 //     Weights never change, so everything the ring holds is requested BEFORE the programmatic
 //     dependency wait and arrives while the launch in front is still running.
 //   * Quantising M x K activations in every CTA would cost more than the whole contraction, so the
@@ -30,7 +30,7 @@ namespace rkb200 {
 
 constexpr int DEC_WARPS = 8;                        // contraction warps
 constexpr int DEC_THREADS = (DEC_WARPS + 1) * 32;   // + the copy warp
-constexpr int DEC_STAGE_CHUNKS = 32;                // 32-element chunks of one weight group per stage
+constexpr int DEC_STAGE_CHUNKS = 64;                // 32-element chunks (2048 reduction elements) of one weight group per stage: 32 KB
 constexpr int DEC_STAGE_BYTES = DEC_STAGE_CHUNKS * 512;
 constexpr size_t DEC_SMEM_LIMIT = 227 * 1024;
 
@@ -39,7 +39,7 @@ __host__ __device__ constexpr size_t dec_fixed_bytes(int M, int KB, bool swiglu)
 {
     return (size_t)dec_token_slots(M) * KB * KBLOCK          // activation codes of all of K
            + (size_t)DEC_WARPS * (swiglu ? 64 : 32) * 8 * 4  // per-warp partial sums
-           + 64 + 8;                                         // row maxima, scale words; + barriers below
+           + 96 + 8;                                         // row maxima, scale words, inverse scales; + barriers below
 }
 __host__ __device__ constexpr size_t dec_smem_bytes(int M, int KB, bool swiglu, int ring)
 {
@@ -73,6 +73,9 @@ __device__ __forceinline__ int red_index(int warp, int rows, int row, int tok)
 // DOT: up to four tokens, contraction on the integer dot-product units (eight-column tensor-core tiles would be
 // at most half empty, and this GPU's legacy mma.sync int8 path issues one tile per ~11 cycles per SM).
 // One CTA of one linear: `cta` of `nctas` (the kernels below map the grid onto one or several linears).
+// The CTA's path between "the activations exist" and "the outputs are stored" is a chain of short phases run by
+// nine warps, so it is bound by instruction latency, not throughput: the code avoids integer divisions, computes a
+// token's scale once, and gives every warp several independent chains per weight stage.
 template <bool HALF, bool DOT, bool TRACE>
 __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned cta, const unsigned nctas)
 {
@@ -89,7 +92,8 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     int* const red = reinterpret_cast<int*>(xs + (size_t)Mc * Kp);
     uint32_t* const s_max = reinterpret_cast<uint32_t*>(red + DEC_WARPS * rows * 8);   // [8] row maxima of this CTA's tokens
     uint32_t* const s_scale = s_max + 8;                                         // [8] scale bits per token (or 0xFFFFFFF0 | verdict)
-    uint64_t* const full = reinterpret_cast<uint64_t*>(s_scale + 8 + 2);
+    float* const s_inv = reinterpret_cast<float*>(s_scale + 8);                  // [8] inverse scales of this CTA's tokens
+    uint64_t* const full = reinterpret_cast<uint64_t*>(s_inv + 8 + 2);
     uint64_t* const empty = full + R;
     uint64_t* const code_bar = empty + R;
 
@@ -101,10 +105,10 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     const int spg = (KC + DEC_STAGE_CHUNKS - 1) / DEC_STAGE_CHUNKS;             // stages per weight group
     const int gpi = swiglu ? 2 : 1;                                              // weight groups per item
     const int my_items = (int)cta < items ? (items - 1 - (int)cta) / ncta + 1 : 0;
-    const int my_stages = my_items * gpi * spg;
     unsigned long long* const trace = (TRACE && p.trace && tid == 0) ? p.trace + (size_t)cta * 8 : nullptr;
     long long c_start = 0;
     if (TRACE) { c_start = clock64(); if (trace) trace[0] = global_ns(); }
+    auto stamp = [&](int slot) { if (TRACE && trace && cta == 0) p.trace[8 * 4096 + slot] = (unsigned long long)(clock64() - c_start); };
 
     if (tid == 0) {
         for (int i = 0; i < R; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], DEC_WARPS); }
@@ -121,29 +125,31 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
         if (S > 1) cluster_wait();
         if (lane == 0) {
             unsigned long long deadline = ~0ull;
-            const int per_item = gpi * spg;
-            for (int i = 0; i < my_stages; ++i) {
-                const int slot = i % R;
-                if (i >= R) {
-                    if (i == R) {   // from here on a slot must be handed back first, which cannot happen before the dependency
-                        pdl_wait();
-                        deadline = global_ns() + p.timeout_ns;
-                    }
-                    if (!mbar_wait(&empty[slot], (uint32_t)((i / R - 1) & 1), deadline)) {
-                        atomicExch(&p.status->device_error, 1);
-                        break;
+            int slot = 0, issued = 0;
+            uint32_t turn = 0;                      // how often the ring has wrapped
+            for (int j = 0; j < my_items; ++j) {
+                const int item = (int)cta + j * ncta;
+                for (int g = 0; g < gpi; ++g) {
+                    const size_t group = (size_t)(g == 0 ? item : p.F / GROUP + item);
+                    for (int c0 = 0; c0 < KC; c0 += DEC_STAGE_CHUNKS, ++issued) {
+                        if (issued >= R) {
+                            if (issued == R) {      // from here on a slot must be handed back first, which cannot happen before the dependency
+                                pdl_wait();
+                                deadline = global_ns() + p.timeout_ns;
+                            }
+                            if (!mbar_wait(&empty[slot], (turn - 1u) & 1u, deadline)) {
+                                atomicExch(&p.status->device_error, 1);
+                                return;
+                            }
+                        }
+                        const uint32_t bytes = (uint32_t)min(DEC_STAGE_CHUNKS, KC - c0) * 512u;
+                        // (test hook: 16 bytes that no copy brings keep the first barrier open until the wait gives up;
+                        // every real copy still lands)
+                        mbar_arrive_expect_tx(&full[slot], bytes + ((p.starve && issued == 0) ? 16u : 0u));
+                        bulk_g2s(ring + (size_t)slot * DEC_STAGE_BYTES, p.Wp + (group * KC + c0) * 512, bytes, &full[slot]);
+                        if (++slot == R) { slot = 0; ++turn; }
                     }
                 }
-                const int j = i / per_item, rem = i - j * per_item;
-                const int g = rem / spg, s = rem - g * spg;
-                const int item = (int)cta + j * ncta;
-                const int group = g == 0 ? item : p.F / GROUP + item;
-                const int c0 = s * DEC_STAGE_CHUNKS;
-                const uint32_t bytes = (uint32_t)min(DEC_STAGE_CHUNKS, KC - c0) * 512u;
-                // (test hook: 16 bytes that no copy brings keep the first barrier open until the wait gives up;
-                // every real copy still lands)
-                mbar_arrive_expect_tx(&full[slot], bytes + ((p.starve && i == 0) ? 16u : 0u));
-                bulk_g2s(ring + (size_t)slot * DEC_STAGE_BYTES, p.Wp + ((size_t)group * KC + c0) * 512, bytes, &full[slot]);
             }
         }
         return;
@@ -168,6 +174,12 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     const bool no_scan = p.rowmax_in != nullptr;
     const int su0 = no_scan ? pu0 : 0, sn = (no_scan ? pu1 : U) - su0;
     const int scan_items = TQ * sn;
+    // item index -> (local token, unit); no division in the common one-token case
+    auto locate = [&](int idx, int& tl, int& u) {
+        tl = 0;
+        if (TQ > 1) tl = idx / sn;
+        u = su0 + idx - tl * sn;
+    };
     const AT* A = reinterpret_cast<const AT*>(p.A);
     const bool vec = (reinterpret_cast<uintptr_t>(A) & 15u) == 0 && (p.K % (HALF ? 8 : 4)) == 0;
     constexpr int UMAX = HALF ? 3 : 2;     // units a thread keeps in registers between the scan and the quantisation
@@ -175,11 +187,12 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     // The rows this CTA will read, pulled towards L2 while the launch in front still runs.  A prefetch is only a
     // hint: the L2 is the point of coherence, so whatever the producer still writes is what the loads below see.
     {
-        const int unit_bytes = HALF ? 32 : 64;
-        for (int idx = tid * (128 / unit_bytes); idx < scan_items; idx += CT * (128 / unit_bytes)) {
-            const int tl = idx / sn, u = su0 + idx - tl * sn, tok = t0 + tl;
-            if (tok < M && u * 16 < p.K)
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(A) + ((size_t)tok * p.K + (size_t)u * 16) * sizeof(AT)));
+        constexpr int per_line = HALF ? 4 : 2;      // 16-element units per 128-byte line
+        for (int idx = tid * per_line; idx < scan_items; idx += CT * per_line) {
+            int tl, u;
+            locate(idx, tl, u);
+            if (t0 + tl < M && u * 16 < p.K)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(A) + ((size_t)(t0 + tl) * p.K + (size_t)u * 16) * sizeof(AT)));
         }
     }
     if (TRACE && trace) trace[1] = (unsigned long long)(clock64() - c_start);
@@ -192,66 +205,78 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     if (TRACE && trace) trace[2] = (unsigned long long)(clock64() - c_start);
 
     Raw16<HALF> kept[UMAX];
-    uint32_t kept_bits[UMAX];              // no_scan: the row's collected maximum
     // every load is issued before anything waits for one: a round trip to L2 costs more than the rest of the scan
 #pragma unroll
     for (int it = 0; it < UMAX; ++it) {
         const int idx = tid + CT * it;
 #pragma unroll
         for (int i = 0; i < (HALF ? 8 : 16); ++i) kept[it].w[i] = 0u;
-        kept_bits[it] = 0u;
         if (idx < scan_items) {
-            const int tl = idx / sn, u = su0 + idx - tl * sn, tok = t0 + tl;
-            if (tok < M) {
-                if (no_scan) kept_bits[it] = p.rowmax_in[tok];
-                if (u * 16 < p.K) load_raw<HALF>(A + (size_t)tok * p.K, u * 16, p.K, vec, kept[it]);
-            }
+            int tl, u;
+            locate(idx, tl, u);
+            if (t0 + tl < M && u * 16 < p.K) load_raw<HALF>(A + (size_t)(t0 + tl) * p.K, u * 16, p.K, vec, kept[it]);
         }
     }
-    if (TRACE && trace && cta == 0) p.trace[8 * 4096 + 64] = (unsigned long long)(clock64() - c_start);   // loads issued
+    uint32_t collected = 0;                   // no_scan: this thread's token's collected maximum
+    if (no_scan && tid < TQ && t0 + tid < M) collected = p.rowmax_in[t0 + tid];
+    stamp(64);
     if (!no_scan) {
 #pragma unroll
         for (int it = 0; it < UMAX; ++it) {
             const int idx = tid + CT * it;
-            const int tl = idx < scan_items ? idx / sn : 0;
+            int tl = 0, u;
+            if (idx < scan_items) locate(idx, tl, u);
             uint32_t bits = raw_maxbits<HALF>(kept[it]);    // units never loaded hold zeros
             // a warp whose 32 units belong to one token reduces first and issues a single shared atomic
-            const int tl0 = __shfl_sync(0xffffffffu, tl, 0);
-            if (__all_sync(0xffffffffu, tl == tl0)) {
+            if (TQ == 1 || __all_sync(0xffffffffu, tl == __shfl_sync(0xffffffffu, tl, 0))) {
                 bits = __reduce_max_sync(0xffffffffu, bits);
-                if (lane == 0 && bits) atomicMax(&s_max[tl0], bits);
+                if (lane == 0 && bits) atomicMax(&s_max[__shfl_sync(0xffffffffu, tl, 0)], bits);
             } else if (bits) atomicMax(&s_max[tl], bits);
         }
         for (int idx = tid + CT * UMAX; idx < scan_items; idx += CT) {
-            const int tl = idx / sn, u = su0 + idx - tl * sn, tok = t0 + tl;
-            if (tok < M && u * 16 < p.K) {
+            int tl, u;
+            locate(idx, tl, u);
+            if (t0 + tl < M && u * 16 < p.K) {
                 Raw16<HALF> r;
-                load_raw<HALF>(A + (size_t)tok * p.K, u * 16, p.K, vec, r);
+                load_raw<HALF>(A + (size_t)(t0 + tl) * p.K, u * 16, p.K, vec, r);
                 atomicMax(&s_max[tl], raw_maxbits<HALF>(r));
             }
         }
-        if (TRACE && trace && cta == 0) p.trace[8 * 4096 + 65] = (unsigned long long)(clock64() - c_start);   // own maxima in
+        stamp(65);
         bar_sync_contraction();
     }
-    if (TRACE && trace && cta == 0) p.trace[8 * 4096 + 66] = (unsigned long long)(clock64() - c_start);       // row maxima known
-    // scale of one of this CTA's tokens; every CTA that shares a token derives the same values
-    auto token_scale = [&](int tl, uint32_t collected, float& s, float& inv) -> int {
-        int bad;
-        float maximum;
-        if (no_scan) {
-            bad = collected >= 0x7f800000u ? 2 : 0;
-            maximum = __uint_as_float(collected);
-        } else {
-            const uint32_t bits = s_max[tl];
-            if constexpr (HALF) { bad = bits >= 0x7c00u ? 1 : 0; maximum = __half2float(__ushort_as_half((uint16_t)bits)); }
-            else { bad = bits >= 0x7f800000u ? 1 : 0; maximum = __uint_as_float(bits); }
-        }
-        scale_from_max(maximum, bad != 0, s, inv);
-        return bad;
-    };
     const bool first_cluster = (int)cta < S;
     const uint32_t xs_base = smem_u32(xs), bar_base = smem_u32(code_bar);
+    // One thread per token derives its scale -- s = max(maximum / 127, FLT_MIN), 1 for a zero row; inverse = 1 / s, two
+    // IEEE divisions -- once, and (from the CTA that holds the token's first K part) sends it to every cluster member.
     if (S > 1) cluster_wait();
+    if (tid < TQ) {
+        const int tok = t0 + tid;
+        int bad = 0;
+        float maximum = 0.f, sc = 1.f, inv = 1.f;
+        if (tok < M) {
+            if (no_scan) {
+                bad = collected >= 0x7f800000u ? 2 : 0;
+                maximum = __uint_as_float(collected);
+            } else {
+                const uint32_t bits = s_max[tid];
+                if constexpr (HALF) { bad = bits >= 0x7c00u ? 1 : 0; maximum = __half2float(__ushort_as_half((uint16_t)bits)); }
+                else { bad = bits >= 0x7f800000u ? 1 : 0; maximum = __uint_as_float(bits); }
+            }
+            scale_from_max(maximum, bad != 0, sc, inv);
+        }
+        s_inv[tid] = inv;
+        if (part == 0 && tok < M) {
+            const uint32_t word = bad ? (0xFFFFFFF0u | (uint32_t)bad) : __float_as_uint(sc);
+            if (S > 1) {
+                for (int d = 0; d < S; ++d)
+                    st_async_u32(map_to_cta(smem_u32(&s_scale[tok]), (uint32_t)d), word, map_to_cta(bar_base, (uint32_t)d));
+            } else s_scale[tok] = word;
+            if (first_cluster && p.scales_out) p.scales_out[tok] = sc;
+        }
+    }
+    bar_sync_contraction();
+    stamp(66);
     auto publish = [&](int tok, int u, const uint4& q) {
         const uint32_t off = (uint32_t)(u * Mc + tok) * 16u;
         if (S > 1) {
@@ -266,38 +291,26 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     for (int it = 0; it < UMAX; ++it) {
         const int idx = tid + CT * it;
         if (idx < scan_items) {
-            const int tl = idx / sn, u = su0 + idx - tl * sn, tok = t0 + tl;
-            if (tok < M && u >= pu0 && u < pu1) {
-                float s, inv, v[16];
-                token_scale(tl, kept_bits[it], s, inv);
+            int tl, u;
+            locate(idx, tl, u);
+            if (t0 + tl < M && u >= pu0 && u < pu1) {
+                float v[16];
                 raw_to_float<HALF>(kept[it], v);
-                publish(tok, u, quantize16(v, inv, u * 16, p.K));
+                publish(t0 + tl, u, quantize16(v, s_inv[tl], u * 16, p.K));
             }
         }
     }
     for (int idx = tid + CT * UMAX; idx < scan_items; idx += CT) {
-        const int tl = idx / sn, u = su0 + idx - tl * sn, tok = t0 + tl;
-        if (tok < M && u >= pu0 && u < pu1) {
-            float s, inv, v[16];
+        int tl, u;
+        locate(idx, tl, u);
+        if (t0 + tl < M && u >= pu0 && u < pu1) {
+            float v[16];
             uint32_t unused = 0;
-            token_scale(tl, no_scan ? p.rowmax_in[tok] : 0u, s, inv);
-            load16<HALF>(A + (size_t)tok * p.K, u * 16, p.K, vec, v, unused);
-            publish(tok, u, quantize16(v, inv, u * 16, p.K));
+            load16<HALF>(A + (size_t)(t0 + tl) * p.K, u * 16, p.K, vec, v, unused);
+            publish(t0 + tl, u, quantize16(v, s_inv[tl], u * 16, p.K));
         }
     }
-    if (TRACE && trace && cta == 0) p.trace[8 * 4096 + 67] = (unsigned long long)(clock64() - c_start);       // share quantised
-    if (part == 0 && tid < TQ && t0 + tid < M) {
-        // the token's scale (or the reason it has none) travels with the codes
-        const int tok = t0 + tid;
-        float s, inv;
-        const int bad = token_scale(tid, no_scan ? p.rowmax_in[tok] : 0u, s, inv);
-        const uint32_t word = bad ? (0xFFFFFFF0u | (uint32_t)bad) : __float_as_uint(s);
-        if (S > 1) {
-            for (int d = 0; d < S; ++d)
-                st_async_u32(map_to_cta(smem_u32(&s_scale[tok]), (uint32_t)d), word, map_to_cta(bar_base, (uint32_t)d));
-        } else s_scale[tok] = word;
-        if (first_cluster && p.scales_out) p.scales_out[tok] = s;
-    }
+    stamp(67);
     if (TRACE && trace) trace[3] = (unsigned long long)(clock64() - c_start);
     bool failed = false;
     if (S > 1) {
@@ -315,8 +328,22 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     const bool col_live = g8 < M;
     const int tok_out = tid >> 5;                         // epilogue: this thread's token; its channel is `lane`
     const float sx = (tok_out < M && !verdict) ? __uint_as_float(s_scale[tok_out]) : 0.f;
+    const bool compute = !verdict;
     uint32_t run_max = 0;
-    int stage_i = 0;
+    int slot = 0, stage_no = 0;
+    uint32_t parity = 0;
+    // hands the stage back and moves on to the next ring slot
+    auto release_stage = [&]() {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[slot]);
+        if (++slot == R) { slot = 0; parity ^= 1u; }
+        ++stage_no;
+    };
+    auto acquire_stage = [&]() {
+        if (TRACE && stage_no < 8) stamp(2 * stage_no);
+        if (!mbar_wait_all_lanes(&full[slot], parity, deadline)) failed = true;
+        if (TRACE && stage_no < 8) stamp(2 * stage_no + 1);
+    };
     for (int j = 0; j < my_items; ++j) {
         const int item = (int)cta + j * ncta;
         if constexpr (DOT) {
@@ -324,66 +351,64 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
             // (broadcast reads).  One weight word holds eight codes; (w << 4) & mask and w & mask are the two
             // int8 x 16 words that pair with the chunk's first and second sixteen activations.
             int dacc[2][4];
+            const uint8_t* const wring = ring + lane * 16;
 #pragma unroll
-            for (int g = 0; g < 2; ++g)
+            for (int g = 0; g < 2; ++g) {
 #pragma unroll
                 for (int t = 0; t < 4; ++t) dacc[g][t] = 0;
-#pragma unroll
-            const uint8_t* const wring = ring + lane * 16;
-            for (int g = 0; g < 2; ++g) {
-                if (g >= gpi) break;
-                int dacc4[4][4];
+                if (g >= gpi) continue;
+                int d4[4][4];                       // four independent chains per token
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) dacc4[i][t] = 0;
-                for (int s = 0; s < spg; ++s, ++stage_i) {
-                    const int slot = stage_i % R;
-                    if (TRACE && trace && cta == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i] = (unsigned long long)(clock64() - c_start);
-                    if (!mbar_wait_all_lanes(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
-                    if (TRACE && trace && cta == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i + 1] = (unsigned long long)(clock64() - c_start);
-                    if (!verdict && !failed) {
-                        const int c0 = s * DEC_STAGE_CHUNKS, nch = min(DEC_STAGE_CHUNKS, KC - c0);
-                        // a warp's four chunks of the stage: every load first, then four independent dot-product chains per token
-                        uint4 w[4];
+                    for (int t = 0; t < 4; ++t) d4[i][t] = 0;
+                for (int c0 = 0; c0 < KC; c0 += DEC_STAGE_CHUNKS) {
+                    acquire_stage();
+                    if (compute && !failed) {
+                        const int nch = min(DEC_STAGE_CHUNKS, KC - c0);
+                        const uint8_t* const wstage = wring + (size_t)slot * DEC_STAGE_BYTES;
+                        const uint4* const xstage = reinterpret_cast<const uint4*>(xs) + (size_t)c0 * 2 * Mc;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int cc = warp + DEC_WARPS * i;
-                            w[i] = cc < nch ? *reinterpret_cast<const uint4*>(wring + (size_t)slot * DEC_STAGE_BYTES + (size_t)cc * 512) : make_uint4(0u, 0u, 0u, 0u);
-                        }
+                        for (int half = 0; half < DEC_STAGE_CHUNKS / (4 * DEC_WARPS); ++half) {
+                            uint4 w[4];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int cc = warp + DEC_WARPS * i;
-                            if (cc < nch) {
-                                const uint4* xp = reinterpret_cast<const uint4*>(xs) + (size_t)(c0 + cc) * 2 * Mc;
-                                const uint32_t wl[4] = {(w[i].x << 4) & 0xF0F0F0F0u, (w[i].y << 4) & 0xF0F0F0F0u, (w[i].z << 4) & 0xF0F0F0F0u, (w[i].w << 4) & 0xF0F0F0F0u};
-                                const uint32_t wh[4] = {w[i].x & 0xF0F0F0F0u, w[i].y & 0xF0F0F0F0u, w[i].z & 0xF0F0F0F0u, w[i].w & 0xF0F0F0F0u};
+                            for (int i = 0; i < 4; ++i) {
+                                const int cc = warp + DEC_WARPS * (4 * half + i);
+                                w[i] = cc < nch ? *reinterpret_cast<const uint4*>(wstage + (size_t)cc * 512) : make_uint4(0u, 0u, 0u, 0u);
+                            }
 #pragma unroll
-                                for (int t = 0; t < 4; ++t) {
-                                    if (t < Mc) {
-                                        const uint4 x0 = xp[t], x1 = xp[Mc + t];
-                                        int a = dacc4[i][t];
-                                        a = __dp4a((int)wl[0], (int)x0.x, a); a = __dp4a((int)wh[0], (int)x1.x, a);
-                                        a = __dp4a((int)wl[1], (int)x0.y, a); a = __dp4a((int)wh[1], (int)x1.y, a);
-                                        a = __dp4a((int)wl[2], (int)x0.z, a); a = __dp4a((int)wh[2], (int)x1.z, a);
-                                        a = __dp4a((int)wl[3], (int)x0.w, a); a = __dp4a((int)wh[3], (int)x1.w, a);
-                                        dacc4[i][t] = a;
+                            for (int i = 0; i < 4; ++i) {
+                                const int cc = warp + DEC_WARPS * (4 * half + i);
+                                if (cc < nch) {
+                                    const uint4* xp = xstage + (size_t)cc * 2 * Mc;
+                                    const uint32_t wl[4] = {(w[i].x << 4) & 0xF0F0F0F0u, (w[i].y << 4) & 0xF0F0F0F0u, (w[i].z << 4) & 0xF0F0F0F0u, (w[i].w << 4) & 0xF0F0F0F0u};
+                                    const uint32_t wh[4] = {w[i].x & 0xF0F0F0F0u, w[i].y & 0xF0F0F0F0u, w[i].z & 0xF0F0F0F0u, w[i].w & 0xF0F0F0F0u};
+#pragma unroll
+                                    for (int t = 0; t < 4; ++t) {
+                                        if (t < Mc) {
+                                            const uint4 x0 = xp[t], x1 = xp[Mc + t];
+                                            int a = d4[i][t];
+                                            a = __dp4a((int)wl[0], (int)x0.x, a); a = __dp4a((int)wh[0], (int)x1.x, a);
+                                            a = __dp4a((int)wl[1], (int)x0.y, a); a = __dp4a((int)wh[1], (int)x1.y, a);
+                                            a = __dp4a((int)wl[2], (int)x0.z, a); a = __dp4a((int)wh[2], (int)x1.z, a);
+                                            a = __dp4a((int)wl[3], (int)x0.w, a); a = __dp4a((int)wh[3], (int)x1.w, a);
+                                            d4[i][t] = a;
+                                        }
                                     }
                                 }
                             }
                         }
                     }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty[slot]);
+                    release_stage();
                 }
 #pragma unroll
-                for (int t = 0; t < 4; ++t) dacc[g][t] = (dacc4[0][t] + dacc4[1][t]) + (dacc4[2][t] + dacc4[3][t]);
+                for (int t = 0; t < 4; ++t) dacc[g][t] = (d4[0][t] + d4[1][t]) + (d4[2][t] + d4[3][t]);
             }
             if (TRACE && trace && j == my_items - 1) trace[5] = (unsigned long long)(clock64() - c_start);
             // partial sums: [warp][token][row], row = lane (+ 32 for the up group)
 #pragma unroll
             for (int g = 0; g < 2; ++g) {
-                if (g >= gpi) break;
+                if (g >= gpi) continue;
 #pragma unroll
                 for (int t = 0; t < 4; ++t)
                     if (t < Mc) red[(warp * 4 + t) * rows + g * 32 + lane] = dacc[g][t];
@@ -392,9 +417,13 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
             int acc[2][2][4];                                 // [gate | up][m16 tile][fragment]
 #pragma unroll
             for (int g = 0; g < 2; ++g) {
-                if (g >= gpi) break;
-                // four accumulator sets: a warp's four chunks of a stage are independent MMAs, so their loads and the
-                // long latency of the legacy int8 MMA overlap
+#pragma unroll
+                for (int m = 0; m < 2; ++m)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[g][m][e] = 0;
+                if (g >= gpi) continue;
+                // four accumulator sets: four of a warp's chunks of a stage are independent MMAs, so their loads and the
+                // latency of the MMAs overlap
                 int a[4][2][4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
@@ -402,37 +431,36 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
                     for (int m = 0; m < 2; ++m)
 #pragma unroll
                         for (int e = 0; e < 4; ++e) a[i][m][e] = 0;
-                for (int s = 0; s < spg; ++s, ++stage_i) {
-                    const int slot = stage_i % R;
-                    if (TRACE && trace && cta == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i] = (unsigned long long)(clock64() - c_start);
-                    if (!mbar_wait_all_lanes(&full[slot], (uint32_t)((stage_i / R) & 1), deadline)) failed = true;
-                    if (TRACE && trace && cta == 0 && stage_i < 32) p.trace[8 * 4096 + 2 * stage_i + 1] = (unsigned long long)(clock64() - c_start);
-                    if (!verdict && !failed) {
-                        const int c0 = s * DEC_STAGE_CHUNKS, nch = min(DEC_STAGE_CHUNKS, KC - c0);
+                for (int c0 = 0; c0 < KC; c0 += DEC_STAGE_CHUNKS) {
+                    acquire_stage();
+                    if (compute && !failed) {
+                        const int nch = min(DEC_STAGE_CHUNKS, KC - c0);
                         const uint32_t* const wslot = reinterpret_cast<const uint32_t*>(ring + (size_t)slot * DEC_STAGE_BYTES) + g8 * 4 + t4;
-                        const uint32_t* const xlane = reinterpret_cast<const uint32_t*>(xs) + g8 * 4 + t4;
-                        uint32_t w[4][4], b[4][2];
+                        const uint32_t* const xlane = reinterpret_cast<const uint32_t*>(xs) + (size_t)c0 * 2 * Mc * 4 + g8 * 4 + t4;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int cc = warp + DEC_WARPS * i;
-                            const bool live = cc < nch;
+                        for (int half = 0; half < DEC_STAGE_CHUNKS / (4 * DEC_WARPS); ++half) {
+                            uint32_t w[4][4], b[4][2];
 #pragma unroll
-                            for (int r = 0; r < 4; ++r) w[i][r] = live ? wslot[cc * 128 + r * 32] : 0u;
-                            b[i][0] = (live && col_live) ? xlane[(c0 + cc) * 2 * Mc * 4] : 0u;
-                            b[i][1] = (live && col_live) ? xlane[((c0 + cc) * 2 + 1) * Mc * 4] : 0u;
-                        }
+                            for (int i = 0; i < 4; ++i) {
+                                const int cc = warp + DEC_WARPS * (4 * half + i);
+                                const bool live = cc < nch;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            if (warp + DEC_WARPS * i < nch) {
-                                mma_s8(a[i][0], (w[i][0] << 4) & 0xF0F0F0F0u, (w[i][1] << 4) & 0xF0F0F0F0u, w[i][0] & 0xF0F0F0F0u,
-                                       w[i][1] & 0xF0F0F0F0u, b[i][0], b[i][1]);
-                                mma_s8(a[i][1], (w[i][2] << 4) & 0xF0F0F0F0u, (w[i][3] << 4) & 0xF0F0F0F0u, w[i][2] & 0xF0F0F0F0u,
-                                       w[i][3] & 0xF0F0F0F0u, b[i][0], b[i][1]);
+                                for (int r = 0; r < 4; ++r) w[i][r] = live ? wslot[cc * 128 + r * 32] : 0u;
+                                b[i][0] = (live && col_live) ? xlane[cc * 2 * Mc * 4] : 0u;
+                                b[i][1] = (live && col_live) ? xlane[(cc * 2 + 1) * Mc * 4] : 0u;
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                if (warp + DEC_WARPS * (4 * half + i) < nch) {
+                                    mma_s8(a[i][0], (w[i][0] << 4) & 0xF0F0F0F0u, (w[i][1] << 4) & 0xF0F0F0F0u, w[i][0] & 0xF0F0F0F0u,
+                                           w[i][1] & 0xF0F0F0F0u, b[i][0], b[i][1]);
+                                    mma_s8(a[i][1], (w[i][2] << 4) & 0xF0F0F0F0u, (w[i][3] << 4) & 0xF0F0F0F0u, w[i][2] & 0xF0F0F0F0u,
+                                           w[i][3] & 0xF0F0F0F0u, b[i][0], b[i][1]);
+                                }
                             }
                         }
                     }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty[slot]);
+                    release_stage();
                 }
 #pragma unroll
                 for (int m = 0; m < 2; ++m)
@@ -442,7 +470,7 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
             if (TRACE && trace && j == my_items - 1) trace[5] = (unsigned long long)(clock64() - c_start);
 #pragma unroll
             for (int g = 0; g < 2; ++g) {
-                if (g >= gpi) break;
+                if (g >= gpi) continue;
 #pragma unroll
                 for (int m = 0; m < 2; ++m)
 #pragma unroll
@@ -454,7 +482,7 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
         bar_sync_contraction();
         const float ca = sw_a, cb = sw_b;
         if (j + 1 < my_items) load_channel_scales(item + ncta);
-        if (!verdict && !failed && tok_out < M) {
+        if (compute && !failed && tok_out < M) {
             int v = 0, u = 0;
 #pragma unroll
             for (int w = 0; w < DEC_WARPS; ++w) {
@@ -482,7 +510,7 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
         if (j + 1 < my_items) bar_sync_contraction();   // the scratch is written again by the next item
     }
     if (TRACE && trace) trace[6] = (unsigned long long)(clock64() - c_start);
-    if (swiglu && p.rowmax_out && !verdict) {
+    if (swiglu && p.rowmax_out && compute) {
         const uint32_t m = __reduce_max_sync(0xffffffffu, run_max);   // a warp's 32 threads share one token
         if (lane == 0 && m && tok_out < M) atomicMax(&p.rowmax_out[tok_out], m);
     }
@@ -537,19 +565,20 @@ int gemm_decode_ring(int M, int KB, bool swiglu)
     const size_t fixed = dec_fixed_bytes(M, KB, swiglu) + 256;
     const size_t stage = DEC_STAGE_BYTES + 16, shared_budget = 112 * 1024;
     int ring = fixed < shared_budget ? (int)((shared_budget - fixed) / stage) : 0;
-    if (ring < 3) {
+    if (ring < 2) {
         ring = fixed < DEC_SMEM_LIMIT ? (int)((DEC_SMEM_LIMIT - fixed) / stage) : 0;
-        if (ring > 8) ring = 8;
+        if (ring > 4) ring = 4;
     }
     return ring < DEC_MAX_RING ? ring : DEC_MAX_RING;
 }
 
-// Cluster size (= how many CTAs share the quantisation): about two 16-element units per thread.
+// Cluster size (= how many CTAs share the quantisation): at most about one and a half 16-element units per
+// thread; quantising a unit costs a thread about as much as the whole exchange does.
 int gemm_decode_cluster(int M, int KB)
 {
     const long long units = (long long)dec_token_slots(M) * KB * 8;
     int s = 1;
-    while (s < 8 && units > 512ll * s) s *= 2;
+    while (s < 8 && units > 384ll * s) s *= 2;
     return s;
 }
 

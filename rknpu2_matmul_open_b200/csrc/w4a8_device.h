@@ -149,7 +149,7 @@ struct DecodeParams {
     int KB, NG, F, epi;
     int half;                   // activations are binary16
     int cluster;                // CTAs that share the quantisation: 1, 2, 4 or 8
-    int ring;                   // 16 KB weight stages per CTA
+    int ring;                   // 32 KB weight stages per CTA
     int ctas;                   // grid size, a multiple of `cluster`
     int starve;                 // test hook: the first weight barrier of every CTA expects 16 bytes that never arrive
     unsigned long long timeout_ns;
