@@ -166,7 +166,7 @@ int rk_npu_b200_w4a8_set_schedule(rk_npu_w4a8_workspace *workspace, int variant,
  * sees the accumulator, hands tensor memory back, has stored the tile, and the cycles the issuer
  * waited for operands; [128 + 2 j], [129 + 2 j], [160 + j] the cycles one unpack warp waited for
  * weights, for a free tensor-memory buffer and for activations; [200] the CTA pairs in the grid.
- * The caller synchronises first.  rknpu2_matmul_open_b200/profile_case.py --stamps prints both. */
+ * The caller synchronises first.  `bench.py --case decode|prefill --stamps` prints both. */
 int rk_npu_b200_w4a8_trace_enable(rk_npu_w4a8_workspace *workspace, int enable);
 int rk_npu_b200_w4a8_trace_read(rk_npu_w4a8_workspace *workspace, unsigned long long *stamps, int ctas);
 

@@ -10,7 +10,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB_DIR = HERE / "lib"
 LIB = LIB_DIR / "librk_npu_matmul_b200.so"
-TOOLS = ["int8_peak.cu", "bulk_copy_bw.cu"]
+TOOLS = ["int8_peak.cu"]   # measures the dense int8 tensor peak; bench.py runs it for its roofline denominator
 SOURCES = ["w4a8_kernels.cu", "w4a8_fused.cu", "w4a8_decode.cu", "w4a8_stream.cu", "w4a8_shard.cu", "w4a8_gemm_tc.cu", "w4a8_gemm_tc_persist.cu", "w4a8_abi.cpp", "w4a8_group.cpp", "w4a8_tune.cpp", "w4a8_autotune.cpp", "w4a8_unbuilt.cpp"]
 HEADERS = ["w4a8_device.h", "w4a8_host.h", "w4a8_tune.h", "w4a8_ptx.cuh", "w4a8_math.cuh", "w4a8_tc.cuh", "../../include/rknpu_b200_w4a8.h", "../../include/rknpu_b200_ext.h"]
 NVCC_FLAGS = [
@@ -53,7 +53,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     out = subprocess.run(link, capture_output=True, text=True)
     if out.returncode:
         raise RuntimeError(f"link failed:\n{out.stdout}\n{out.stderr}")
-    for tool in TOOLS:   # stand-alone measurement programs (roofline denominators)
+    for tool in TOOLS:   # stand-alone measurement program (roofline denominator)
         out = subprocess.run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-o",
                               str(LIB_DIR / tool.rsplit(".", 1)[0]), str(CSRC / tool)], capture_output=True, text=True)
         if out.returncode:
