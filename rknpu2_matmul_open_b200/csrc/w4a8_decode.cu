@@ -228,9 +228,12 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
             if (idx < scan_items) locate(idx, tl, u);
             uint32_t bits = raw_maxbits<HALF>(kept[it]);    // units never loaded hold zeros
             // a warp whose 32 units belong to one token reduces first and issues a single shared atomic
-            if (TQ == 1 || __all_sync(0xffffffffu, tl == __shfl_sync(0xffffffffu, tl, 0))) {
+            // (every warp-wide operation below is executed by all 32 lanes: none sits behind a per-lane condition)
+            const int tl0 = __shfl_sync(0xffffffffu, tl, 0);
+            const bool one_token = TQ == 1 || __all_sync(0xffffffffu, tl == tl0);
+            if (one_token) {
                 bits = __reduce_max_sync(0xffffffffu, bits);
-                if (lane == 0 && bits) atomicMax(&s_max[__shfl_sync(0xffffffffu, tl, 0)], bits);
+                if (lane == 0 && bits) atomicMax(&s_max[tl0], bits);
             } else if (bits) atomicMax(&s_max[tl], bits);
         }
         for (int idx = tid + CT * UMAX; idx < scan_items; idx += CT) {
