@@ -1,13 +1,13 @@
-/* rknpu_b200_quant.h -- the part of the original project's second public header
- * (include/rk_npu_quant_matmul.h) and of include/rk_npu_matmul_i4.h that the W4A8 path's
- * callers touch: the load-only W8 tuning cache and the configuration initialisers.
+/* rknpu_b200_quant.h -- the original project's second public header (include/rk_npu_quant_matmul.h) as this
+ * library implements it, plus the configuration initialiser of include/rk_npu_matmul_i4.h.
  *
- * Every other entry point of those two headers (W8A8 weights / workspaces / runs, the exact
- * int4 x int4 -> int32 API, the W8 search tuners and their family forms, cache saving of
- * the W8 tuner, the DMA-buffer helpers of rk_npu_common.h) is exported by the library so that
- * existing programs link, and answers RK_NPU_ERR_PARAM, NULL or 0: those operators are not
- * built here.  Programs may include the original headers instead of this one; the layouts
- * below are the same.
+ * Built: the typed W8A8 operators with raw int8 weights (weight objects, workspaces made from a strategy, the
+ * blocking run calls, the memory queries, the K-partition query), the load-only W8 tuning cache and the
+ * configuration initialisers.
+ * Exported but declined (RK_NPU_ERR_PARAM, NULL or 0, nothing else happens): the W8 search tuners, their family
+ * forms and cache saving; compressed (DCOMP) weight storage, which encodes for the original device's hardware
+ * decompressor; the exact int4 x int4 -> int32 API; the DMA-buffer helpers of rk_npu_common.h.
+ * Programs may include the original headers instead of this one; names, layouts and values are the same.
  */
 #ifndef RKNPU_B200_QUANT_H
 #define RKNPU_B200_QUANT_H
@@ -89,6 +89,85 @@ void rk_npu_matmul_family_autotune_config_init(rk_npu_matmul_family_autotune_con
 int rk_npu_matmul_autotune_cache_load(rk_npu_ctx *ctx, const char *cache_path, rk_npu_matmul_op_kind kind,
                                       const rk_npu_matmul_autotune_config *cfg, rk_npu_matmul_strategy *fastest,
                                       rk_npu_matmul_strategy *stable);
+
+/* ---------------------------------------------------------------- typed W8A8 operators
+ * include/rk_npu_quant_matmul.h:94-99,149-176,186-188,296-421.  int8 B[K,N] (symmetric, zero point 0) with one
+ * positive scale per output channel; A and C are compact row-major host tensors (device pointers are accepted too)
+ * handed to blocking calls.
+ *
+ *   dynamic   a_scale[m] = max|A[m,:]| / 127 (all-zero row -> 1; no lower clamp, NaN never raises the maximum)
+ *   static    a_scale[m] given by the caller, finite and positive
+ *   codes     clamp(round_half_away(A[m,k] * (1 / a_scale[m])), -127, 127)
+ *   C[m,n]    (float(sum_k code * B) * a_scale[m]) * w_scale[n], rounded once more for binary16
+ *   i8i8i32   no quantisation; sums are exact modulo 2^32
+ * (src/rk_npu_cpu_kernels.cpp:126-131,576-660,853-871,1312).  Unlike the W4A8 path these operators do not reject
+ * non-finite activations: they propagate as in the original's scalar code.
+ *
+ * On this library the contraction runs on the tcgen05 per-tile kernel with int8 weights in tensor memory.  A
+ * strategy's tile, layout and mask fields are validated as the original validates them and otherwise carry no
+ * meaning here; k_tile stays the compatibility key between a workspace and its weights.  Contexts opened as a
+ * rank of a group of GPUs do not create these objects. */
+typedef struct rk_npu_matmul_weight_config {
+    int K;
+    int N;
+    int k_tile;
+} rk_npu_matmul_weight_config;
+typedef struct rk_npu_matmul_workspace_requirements {
+    uint64_t bytes;           /* all device memory of the workspace */
+    uint64_t input_bytes;     /* activation codes and the staged copy of A */
+    uint64_t output_bytes;    /* the staged copy of C */
+    uint64_t control_bytes;   /* scales and the status block */
+    uint32_t wave_count;      /* ceil(K / k_tile), as the original reports it */
+    uint32_t buffer_count;
+} rk_npu_matmul_workspace_requirements;
+typedef struct rk_npu_matmul_weight_requirements {
+    uint64_t bytes;
+    uint64_t packed_b_bytes;
+    uint64_t scale_bytes;
+    uint32_t wave_count;
+    uint32_t buffer_count;
+} rk_npu_matmul_weight_requirements;
+typedef struct rk_npu_i8i8i32_weights rk_npu_i8i8i32_weights;
+typedef struct rk_npu_f16i8f16_weights rk_npu_f16i8f16_weights;
+typedef struct rk_npu_f32i8f32_weights rk_npu_f32i8f32_weights;
+typedef struct rk_npu_matmul_workspace rk_npu_matmul_workspace;
+
+/* The original tuner's conservative K-partition policy, a pure function (src/rk_npu_quant_matmul.cpp:1131-1142,
+ * 1696-1700): OK for an eligible partition, PARAM otherwise. */
+int rk_npu_matmul_k_partition_query(int M, int K, int k_tile);
+int rk_npu_matmul_workspace_memory_query(const rk_npu_matmul_strategy *strategy, rk_npu_matmul_workspace_requirements *out);
+int rk_npu_i8i8i32_weights_memory_query(const rk_npu_matmul_weight_config *config, rk_npu_matmul_weight_requirements *out);
+int rk_npu_f16i8f16_weights_memory_query(const rk_npu_matmul_weight_config *config, rk_npu_matmul_weight_requirements *out);
+int rk_npu_f32i8f32_weights_memory_query(const rk_npu_matmul_weight_config *config, rk_npu_matmul_weight_requirements *out);
+/* Fixed to one exact M and operator; non-reentrant (concurrent use returns BUSY); NULL for an invalid strategy. */
+rk_npu_matmul_workspace *rk_npu_matmul_workspace_create(rk_npu_iommu_domain *domain, const rk_npu_matmul_strategy *strategy);
+void rk_npu_matmul_workspace_free(rk_npu_matmul_workspace *workspace);
+
+rk_npu_i8i8i32_weights *rk_npu_i8i8i32_weights_create(rk_npu_iommu_domain *domain, const rk_npu_matmul_weight_config *config,
+                                                      const int8_t *B_rowmajor);
+void rk_npu_i8i8i32_weights_free(rk_npu_i8i8i32_weights *weights);
+int rk_npu_i8i8i32_run(rk_npu_matmul_workspace *workspace, const rk_npu_i8i8i32_weights *weights, const int8_t *A_rowmajor,
+                       int32_t *C_rowmajor);
+
+/* Every w_scale must be finite and positive; both inputs may be released after creation. */
+rk_npu_f16i8f16_weights *rk_npu_f16i8f16_weights_create(rk_npu_iommu_domain *domain, const rk_npu_matmul_weight_config *config,
+                                                        const int8_t *B_rowmajor, const float *w_scale);
+void rk_npu_f16i8f16_weights_free(rk_npu_f16i8f16_weights *weights);
+int rk_npu_f16i8f16_run_dynamic(rk_npu_matmul_workspace *workspace, const rk_npu_f16i8f16_weights *weights,
+                                const uint16_t *A_fp16_rowmajor, uint16_t *C_fp16_rowmajor);
+int rk_npu_f16i8f16_run_static(rk_npu_matmul_workspace *workspace, const rk_npu_f16i8f16_weights *weights,
+                               const uint16_t *A_fp16_rowmajor, const float *a_scale, uint16_t *C_fp16_rowmajor);
+
+rk_npu_f32i8f32_weights *rk_npu_f32i8f32_weights_create(rk_npu_iommu_domain *domain, const rk_npu_matmul_weight_config *config,
+                                                        const int8_t *B_rowmajor, const float *w_scale);
+void rk_npu_f32i8f32_weights_free(rk_npu_f32i8f32_weights *weights);
+int rk_npu_f32i8f32_run_dynamic(rk_npu_matmul_workspace *workspace, const rk_npu_f32i8f32_weights *weights,
+                                const float *A_fp32_rowmajor, float *C_fp32_rowmajor);
+int rk_npu_f32i8f32_run_static(rk_npu_matmul_workspace *workspace, const rk_npu_f32i8f32_weights *weights,
+                               const float *A_fp32_rowmajor, const float *a_scale, float *C_fp32_rowmajor);
+/* No counterpart in the original: kernels this workspace has launched so far (tests use it to see that the
+ * CUDA path ran). */
+uint64_t rk_npu_b200_matmul_launch_count(const rk_npu_matmul_workspace *workspace);
 
 /* include/rk_npu_matmul_i4.h:26-35; defaults m_tile 128, k_tile 480, n_tile 1024, core mask 1,
  * 500 ms, pipelined, one CPU thread (src/rk_npu_matmul_i4.cpp:10-12). */

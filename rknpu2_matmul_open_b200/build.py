@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import os
+from concurrent.futures import ThreadPoolExecutor
 import subprocess
 import sys
 from pathlib import Path
@@ -11,8 +12,8 @@ CSRC = HERE / "csrc"
 LIB_DIR = HERE / "lib"
 LIB = LIB_DIR / "librk_npu_matmul_b200.so"
 TOOLS = ["int8_peak.cu"]   # measures the dense int8 tensor peak; bench.py runs it for its roofline denominator
-SOURCES = ["w4a8_kernels.cu", "w4a8_fused.cu", "w4a8_decode.cu", "w4a8_stream.cu", "w4a8_shard.cu", "w4a8_gemm_tc.cu", "w4a8_gemm_tc_persist.cu", "w4a8_abi.cpp", "w4a8_group.cpp", "w4a8_tune.cpp", "w4a8_autotune.cpp", "w4a8_unbuilt.cpp"]
-HEADERS = ["w4a8_device.h", "w4a8_host.h", "w4a8_tune.h", "w4a8_ptx.cuh", "w4a8_math.cuh", "w4a8_tc.cuh", "../../include/rknpu_b200_w4a8.h", "../../include/rknpu_b200_ext.h"]
+SOURCES = ["w4a8_kernels.cu", "w4a8_fused.cu", "w4a8_decode.cu", "w4a8_stream.cu", "w4a8_shard.cu", "w4a8_gemm_tc.cu", "w4a8_gemm_tc_persist.cu", "w8a8_kernels.cu", "w4a8_abi.cpp", "w8a8_abi.cpp", "w4a8_group.cpp", "w4a8_tune.cpp", "w4a8_autotune.cpp", "w4a8_unbuilt.cpp"]
+HEADERS = ["w4a8_device.h", "w4a8_host.h", "w4a8_tune.h", "w4a8_ptx.cuh", "w4a8_math.cuh", "w4a8_tc.cuh", "../../include/rknpu_b200_w4a8.h", "../../include/rknpu_b200_ext.h", "../../include/rknpu_b200_quant.h"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-Wall", "-Xptxas", "-v",
@@ -40,10 +41,14 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     LIB_DIR.mkdir(exist_ok=True)
     objects = []
     log = []
-    for src in SOURCES:
+    def compile_one(src):
         obj = LIB_DIR / (src.rsplit(".", 1)[0] + ".o")
         cmd = [_nvcc(), *NVCC_FLAGS, "-x", "cu", "-c", str(CSRC / src), "-o", str(obj)]
-        out = subprocess.run(cmd, capture_output=True, text=True)
+        return src, obj, subprocess.run(cmd, capture_output=True, text=True)
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:   # the translation units are independent
+        results = list(pool.map(compile_one, SOURCES))
+    for src, obj, out in results:
         log.append(out.stderr)
         if out.returncode:
             raise RuntimeError(f"nvcc failed on {src}:\n{out.stdout}\n{out.stderr}")

@@ -1008,7 +1008,8 @@ rk_npu_w4a8_workspace* rkb200::create_workspace_scheduled(rk_npu_iommu_domain* d
         ws->T = ws->TC;
     }
     if (variant == 5)
-        for (int i = 0; i < 4; ++i) ws->decode_cap[i] = gemm_decode_resident_ctas(1 << i, 227 * 1024, ctx->sm_count);
+        for (int i = 0; i < 4; ++i)   // one CTA per SM at most, fewer where whole clusters do not fit
+            ws->decode_cap[i] = gemm_decode_resident_ctas(1 << i, gemm_decode_smem_bytes(cfg->M, ws->KB, true, gemm_decode_ring(cfg->M, ws->KB, true)), ctx->sm_count);
     // cooperating CTAs per column tile: split-K factor of the ring and of the split-K single kernel, cluster size of the
     // decode kernel; ignored where the family balances by itself or the reduction is too short to split
     if (schedule.cluster && (variant == 1 || variant == 5 || (variant == 3 && (ws->KB + schedule.cluster - 1) / schedule.cluster <= FUSED_MAX_STAGES)) &&

@@ -13,14 +13,18 @@
 //   * A ninth warp streams the CTA's weights through a ring of 32 KB stages with bulk async copies.
 //     Weights never change, so everything the ring holds is requested BEFORE the programmatic
 //     dependency wait and arrives while the launch in front is still running.
-//   * Quantising M x K activations in every CTA would cost more than the whole contraction, so the
-//     CTAs of a cluster share it: each scans the full rows of its tokens for the maximum (or its
-//     tokens' scale comes from collected row maxima), quantises its share and pushes the int8 codes
-//     into every cluster member's shared memory with st.async, which counts the bytes on the
-//     receiver's mbarrier.  That is the only exchange of the launch; small problems run without a
-//     cluster and quantise locally.
+//   * Quantising M x K activations costs about eleven instructions per element, more than the whole
+//     contraction when every CTA does all of it, so the CTAs of a cluster share it: each scans the full
+//     rows of its tokens for the maximum (or its tokens' scale comes from collected row maxima),
+//     quantises its share into its own shared memory -- plain int8 rows, one per token -- and hands the
+//     share to every other member with ONE bulk copy per member (shared memory to the peer's shared
+//     memory, counted in bytes on the peer's mbarrier).  That is the only exchange of the launch; small
+//     problems run without a cluster and quantise locally.
+//   * The contraction uses mma.sync m16n8k32 (16 channels x 8 token columns) for every token count: on
+//     this GPU it needs fewer issue slots per weight byte than integer dot products even for one token.
+//     Full 32 KB stages run a loop without per-load predicates; only a K tail takes the guarded form.
 //
-// Integer sums are exact in any order, so the warp split and the two accumulator sets per warp do not
+// Integer sums are exact in any order, so the warp split and the four accumulator sets per warp do not
 // change results.
 #include "w4a8_device.h"
 #include "w4a8_math.cuh"
@@ -32,25 +36,27 @@ constexpr int DEC_WARPS = 8;                        // contraction warps
 constexpr int DEC_THREADS = (DEC_WARPS + 1) * 32;   // + the copy warp
 constexpr int DEC_STAGE_CHUNKS = 64;                // 32-element chunks (2048 reduction elements) of one weight group per stage: 32 KB
 constexpr int DEC_STAGE_BYTES = DEC_STAGE_CHUNKS * 512;
+constexpr int DEC_ROW_PAD = 16;                     // bytes behind a token's code row: rows of different tokens start in different banks
 constexpr size_t DEC_SMEM_LIMIT = 227 * 1024;
 
 __host__ __device__ constexpr int dec_token_slots(int M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8; }
 __host__ __device__ constexpr size_t dec_fixed_bytes(int M, int KB, bool swiglu)
 {
-    return (size_t)dec_token_slots(M) * KB * KBLOCK          // activation codes of all of K
-           + (size_t)DEC_WARPS * (swiglu ? 64 : 32) * 8 * 4  // per-warp partial sums
-           + 96 + 8;                                         // row maxima, scale words, inverse scales; + barriers below
+    return (size_t)dec_token_slots(M) * (KB * KBLOCK + DEC_ROW_PAD)   // activation codes of all of K, one row per token
+           + (size_t)DEC_WARPS * (swiglu ? 64 : 32) * 8 * 4           // per-warp partial sums
+           + 96 + 8;                                                  // row maxima, scale words, inverse scales; + barriers below
 }
 __host__ __device__ constexpr size_t dec_smem_bytes(int M, int KB, bool swiglu, int ring)
 {
     return dec_fixed_bytes(M, KB, swiglu) + (size_t)ring * DEC_STAGE_BYTES + (size_t)(2 * ring + 1) * 8;
 }
 
-// 16-byte store into a cluster member's shared memory that counts its bytes on a barrier there.
-__device__ __forceinline__ void st_async_v4(uint32_t remote_addr, const uint4& v, uint32_t remote_bar)
+// Bulk copy from this CTA's shared memory into a cluster member's, counted in bytes on a barrier there.
+// Both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_s2s(uint32_t remote_dst, uint32_t local_src, uint32_t bytes, uint32_t remote_bar)
 {
-    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(remote_addr),
-                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(remote_bar)
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(remote_dst),
+                 "r"(local_src), "r"(bytes), "r"(remote_bar)
                  : "memory");
 }
 // Wait of a whole warp on an mbarrier phase.  Fast path: the phase is already complete (weights are normally
@@ -70,13 +76,11 @@ __device__ __forceinline__ int red_index(int warp, int rows, int row, int tok)
     return (warp * rows + row) * 8 + (tok ^ ((row >> 2) & 7));
 }
 
-// DOT: up to four tokens, contraction on the integer dot-product units (eight-column tensor-core tiles would be
-// at most half empty, and this GPU's legacy mma.sync int8 path issues one tile per ~11 cycles per SM).
 // One CTA of one linear: `cta` of `nctas` (the kernels below map the grid onto one or several linears).
 // The CTA's path between "the activations exist" and "the outputs are stored" is a chain of short phases run by
-// nine warps, so it is bound by instruction latency, not throughput: the code avoids integer divisions, computes a
-// token's scale once, and gives every warp several independent chains per weight stage.
-template <bool HALF, bool DOT, bool TRACE>
+// nine warps, so it is bound by instruction latency and issue slots, not memory: the code avoids integer
+// divisions, computes a token's scale once, and gives every warp four independent accumulator sets per stage.
+template <bool HALF, bool TRACE>
 __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned cta, const unsigned nctas)
 {
     using AT = typename ActType<HALF>::type;
@@ -85,11 +89,12 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     const int M = p.M;
     const int Mc = dec_token_slots(M);
     const int Kp = p.KB * KBLOCK, U = Kp / 16, KC = p.KB * 4;
+    const int row_bytes = Kp + DEC_ROW_PAD;
     const bool swiglu = p.epi == EPI_SWIGLU;
     const int rows = swiglu ? 64 : 32;
     uint8_t* const ring = smem;
-    uint8_t* const xs = ring + (size_t)R * DEC_STAGE_BYTES;                     // codes: [unit][Mc][16 B]
-    int* const red = reinterpret_cast<int*>(xs + (size_t)Mc * Kp);
+    uint8_t* const xs = ring + (size_t)R * DEC_STAGE_BYTES;                     // codes: [token][Kp + pad] int8
+    int* const red = reinterpret_cast<int*>(xs + (size_t)Mc * row_bytes);
     uint32_t* const s_max = reinterpret_cast<uint32_t*>(red + DEC_WARPS * rows * 8);   // [8] row maxima of this CTA's tokens
     uint32_t* const s_scale = s_max + 8;                                         // [8] scale bits per token (or 0xFFFFFFF0 | verdict)
     float* const s_inv = reinterpret_cast<float*>(s_scale + 8);                  // [8] inverse scales of this CTA's tokens
@@ -102,7 +107,6 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     const int S = p.cluster, rank = S > 1 ? (int)(cta % (unsigned)S) : 0;
     const int ncta = (int)nctas;
     const int items = swiglu ? p.F / GROUP : (p.N + GROUP - 1) / GROUP;
-    const int spg = (KC + DEC_STAGE_CHUNKS - 1) / DEC_STAGE_CHUNKS;             // stages per weight group
     const int gpi = swiglu ? 2 : 1;                                              // weight groups per item
     const int my_items = (int)cta < items ? (items - 1 - (int)cta) / ncta + 1 : 0;
     unsigned long long* const trace = (TRACE && p.trace && tid == 0) ? p.trace + (size_t)cta * 8 : nullptr;
@@ -110,11 +114,26 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     if (TRACE) { c_start = clock64(); if (trace) trace[0] = global_ns(); }
     auto stamp = [&](int slot) { if (TRACE && trace && cta == 0) p.trace[8 * 4096 + slot] = (unsigned long long)(clock64() - c_start); };
 
+    // ---- this CTA's share of the quantisation.  Mc >= S: whole rows of TQ tokens; else one token's
+    // K range is split over P CTAs, each of which still scans the whole row for the maximum.
+    int TQ, P, t0, part;
+    if (Mc >= S) { TQ = Mc / S; P = 1; t0 = rank * TQ; part = 0; }
+    else { TQ = 1; P = S / Mc; t0 = rank / P; part = rank - t0 * P; }
+    const int pu0 = (int)((long long)U * part / P), pu1 = (int)((long long)U * (part + 1) / P);
+    // the bytes of the code rows this CTA produces (contiguous: whole rows, or a piece of one row)
+    const uint32_t share_off = (uint32_t)t0 * (uint32_t)row_bytes + (uint32_t)pu0 * 16u;
+    const uint32_t share_bytes = P == 1 ? (uint32_t)TQ * (uint32_t)row_bytes : (uint32_t)(pu1 - pu0) * 16u;
+
     if (tid == 0) {
         for (int i = 0; i < R; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], DEC_WARPS); }
         mbar_init(code_bar, 1);
         mbar_fence_init();
-        if (S > 1) mbar_arrive_expect_tx(code_bar, (uint32_t)(M * U * 16 + M * 4));
+        if (S > 1) {
+            // what the other members send: every token's row (all of them when rows are split) minus this CTA's own share,
+            // plus one scale word per live token
+            const uint32_t all = P == 1 ? (uint32_t)Mc * (uint32_t)row_bytes : (uint32_t)Mc * (uint32_t)U * 16u;
+            mbar_arrive_expect_tx(code_bar, all - share_bytes + (uint32_t)M * 4u);
+        }
     }
     if (tid < 8) s_max[tid] = 0u;
     __syncthreads();
@@ -165,12 +184,6 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     };
     if (my_items > 0) load_channel_scales((int)cta);
 
-    // ---- 1. this CTA's share of the quantisation.  Mc >= S: whole rows of TQ tokens; else one token's
-    // K range is split over P CTAs, each of which still scans the whole row for the maximum.
-    int TQ, P, t0, part;
-    if (Mc >= S) { TQ = Mc / S; P = 1; t0 = rank * TQ; part = 0; }
-    else { TQ = 1; P = S / Mc; t0 = rank / P; part = rank - t0 * P; }
-    const int pu0 = (int)((long long)U * part / P), pu1 = (int)((long long)U * (part + 1) / P);
     const bool no_scan = p.rowmax_in != nullptr;
     const int su0 = no_scan ? pu0 : 0, sn = (no_scan ? pu1 : U) - su0;
     const int scan_items = TQ * sn;
@@ -201,7 +214,6 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     // launch in front, whose CTAs share this SM while it finishes.
     if (warp == 0) pdl_wait();
     bar_sync_contraction();
-    const unsigned long long deadline = global_ns() + p.timeout_ns;
     if (TRACE && trace) trace[2] = (unsigned long long)(clock64() - c_start);
 
     Raw16<HALF> kept[UMAX];
@@ -219,6 +231,7 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     }
     uint32_t collected = 0;                   // no_scan: this thread's token's collected maximum
     if (no_scan && tid < TQ && t0 + tid < M) collected = p.rowmax_in[t0 + tid];
+    const unsigned long long deadline = global_ns() + p.timeout_ns;
     stamp(64);
     if (!no_scan) {
 #pragma unroll
@@ -280,16 +293,11 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     }
     bar_sync_contraction();
     stamp(66);
-    auto publish = [&](int tok, int u, const uint4& q) {
-        const uint32_t off = (uint32_t)(u * Mc + tok) * 16u;
-        if (S > 1) {
-            for (int d = 0; d < S; ++d) st_async_v4(map_to_cta(xs_base + off, (uint32_t)d), q, map_to_cta(bar_base, (uint32_t)d));
-        } else {
-            *reinterpret_cast<uint4*>(xs + off) = q;
-        }
+    // ---- quantise this CTA's share into its own code rows
+    auto keep_code = [&](int tok, int u, const uint4& q) {
+        *reinterpret_cast<uint4*>(xs + (size_t)tok * row_bytes + (size_t)u * 16) = q;
         if (p.codes_out && first_cluster) reinterpret_cast<uint4*>(p.codes_out)[(size_t)u * 8 + tok] = q;
     };
-    // ---- 2. quantise this CTA's share and hand the codes to every member of the cluster
 #pragma unroll
     for (int it = 0; it < UMAX; ++it) {
         const int idx = tid + CT * it;
@@ -299,7 +307,7 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
             if (t0 + tl < M && u >= pu0 && u < pu1) {
                 float v[16];
                 raw_to_float<HALF>(kept[it], v);
-                publish(t0 + tl, u, quantize16(v, s_inv[tl], u * 16, p.K));
+                keep_code(t0 + tl, u, quantize16(v, s_inv[tl], u * 16, p.K));
             }
         }
     }
@@ -310,15 +318,24 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
             float v[16];
             uint32_t unused = 0;
             load16<HALF>(A + (size_t)(t0 + tl) * p.K, u * 16, p.K, vec, v, unused);
-            publish(t0 + tl, u, quantize16(v, s_inv[tl], u * 16, p.K));
+            keep_code(t0 + tl, u, quantize16(v, s_inv[tl], u * 16, p.K));
         }
     }
     stamp(67);
-    if (TRACE && trace) trace[3] = (unsigned long long)(clock64() - c_start);
     bool failed = false;
     if (S > 1) {
+        // ---- hand the share to every other member: one bulk copy each, issued by one thread per destination once
+        // every thread's stores are visible to the copy engine
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        bar_sync_contraction();
+        if (tid < S && tid != rank)
+            bulk_s2s(map_to_cta(xs_base + share_off, (uint32_t)tid), xs_base + share_off, share_bytes, map_to_cta(bar_base, (uint32_t)tid));
+        if (TRACE && trace) trace[3] = (unsigned long long)(clock64() - c_start);
         if (!mbar_wait_all_lanes(code_bar, 0, deadline)) failed = true;
-    } else bar_sync_contraction();
+    } else {
+        if (TRACE && trace) trace[3] = (unsigned long long)(clock64() - c_start);
+        bar_sync_contraction();
+    }
     if (TRACE && trace) trace[4] = (unsigned long long)(clock64() - c_start);
     int verdict = 0;
     for (int t = 0; t < M; ++t) {
@@ -326,12 +343,14 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
         if (w >= 0xFFFFFFF0u) verdict |= (int)(w & 0xFu);
     }
 
-    // ---- 3. contraction: warp w takes the chunks w, w + 8, ... of every stage, all 32 (64) channels
+    // ---- contraction: warp w takes the chunks w, w + 8, ... of every stage, all 32 (64) channels
     const int g8 = lane >> 2, t4 = lane & 3;
     const bool col_live = g8 < M;
     const int tok_out = tid >> 5;                         // epilogue: this thread's token; its channel is `lane`
     const float sx = (tok_out < M && !verdict) ? __uint_as_float(s_scale[tok_out]) : 0.f;
     const bool compute = !verdict;
+    // this lane's two words of a chunk: token g8's codes k = 32c + 4 t4 .. and k = 32c + 16 + 4 t4 ..
+    const uint32_t* const xlane = reinterpret_cast<const uint32_t*>(xs + (size_t)(col_live ? g8 : 0) * row_bytes) + t4;
     uint32_t run_max = 0;
     int slot = 0, stage_no = 0;
     uint32_t parity = 0;
@@ -349,139 +368,81 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     };
     for (int j = 0; j < my_items; ++j) {
         const int item = (int)cta + j * ncta;
-        if constexpr (DOT) {
-            // Integer dot products: lane = channel of the group, every lane the same 32 activations of a chunk
-            // (broadcast reads).  One weight word holds eight codes; (w << 4) & mask and w & mask are the two
-            // int8 x 16 words that pair with the chunk's first and second sixteen activations.
-            int dacc[2][4];
-            const uint8_t* const wring = ring + lane * 16;
+        int acc[2][2][4];                                 // [gate | up][m16 tile][fragment]
 #pragma unroll
-            for (int g = 0; g < 2; ++g) {
+        for (int g = 0; g < 2; ++g) {
 #pragma unroll
-                for (int t = 0; t < 4; ++t) dacc[g][t] = 0;
-                if (g >= gpi) continue;
-                int d4[4][4];                       // four independent chains per token
+            for (int m = 0; m < 2; ++m)
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
+                for (int e = 0; e < 4; ++e) acc[g][m][e] = 0;
+            if (g >= gpi) continue;
+            // four accumulator sets: four of a warp's chunks of a stage are independent MMAs, so their loads and the
+            // latency of the MMAs overlap
+            int a[4][2][4];
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) d4[i][t] = 0;
-                for (int c0 = 0; c0 < KC; c0 += DEC_STAGE_CHUNKS) {
-                    acquire_stage();
-                    if (compute && !failed) {
-                        const int nch = min(DEC_STAGE_CHUNKS, KC - c0);
-                        const uint8_t* const wstage = wring + (size_t)slot * DEC_STAGE_BYTES;
-                        const uint4* const xstage = reinterpret_cast<const uint4*>(xs) + (size_t)c0 * 2 * Mc;
-#pragma unroll
-                        for (int half = 0; half < DEC_STAGE_CHUNKS / (4 * DEC_WARPS); ++half) {
-                            uint4 w[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int cc = warp + DEC_WARPS * (4 * half + i);
-                                w[i] = cc < nch ? *reinterpret_cast<const uint4*>(wstage + (size_t)cc * 512) : make_uint4(0u, 0u, 0u, 0u);
-                            }
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int cc = warp + DEC_WARPS * (4 * half + i);
-                                if (cc < nch) {
-                                    const uint4* xp = xstage + (size_t)cc * 2 * Mc;
-                                    const uint32_t wl[4] = {(w[i].x << 4) & 0xF0F0F0F0u, (w[i].y << 4) & 0xF0F0F0F0u, (w[i].z << 4) & 0xF0F0F0F0u, (w[i].w << 4) & 0xF0F0F0F0u};
-                                    const uint32_t wh[4] = {w[i].x & 0xF0F0F0F0u, w[i].y & 0xF0F0F0F0u, w[i].z & 0xF0F0F0F0u, w[i].w & 0xF0F0F0F0u};
-#pragma unroll
-                                    for (int t = 0; t < 4; ++t) {
-                                        if (t < Mc) {
-                                            const uint4 x0 = xp[t], x1 = xp[Mc + t];
-                                            int a = d4[i][t];
-                                            a = __dp4a((int)wl[0], (int)x0.x, a); a = __dp4a((int)wh[0], (int)x1.x, a);
-                                            a = __dp4a((int)wl[1], (int)x0.y, a); a = __dp4a((int)wh[1], (int)x1.y, a);
-                                            a = __dp4a((int)wl[2], (int)x0.z, a); a = __dp4a((int)wh[2], (int)x1.z, a);
-                                            a = __dp4a((int)wl[3], (int)x0.w, a); a = __dp4a((int)wh[3], (int)x1.w, a);
-                                            d4[i][t] = a;
-                                        }
-                                    }
-                                }
-                            }
-                        }
-                    }
-                    release_stage();
-                }
-#pragma unroll
-                for (int t = 0; t < 4; ++t) dacc[g][t] = (d4[0][t] + d4[1][t]) + (d4[2][t] + d4[3][t]);
-            }
-            if (TRACE && trace && j == my_items - 1) trace[5] = (unsigned long long)(clock64() - c_start);
-            // partial sums: [warp][token][row], row = lane (+ 32 for the up group)
-#pragma unroll
-            for (int g = 0; g < 2; ++g) {
-                if (g >= gpi) continue;
-#pragma unroll
-                for (int t = 0; t < 4; ++t)
-                    if (t < Mc) red[(warp * 4 + t) * rows + g * 32 + lane] = dacc[g][t];
-            }
-        } else {
-            int acc[2][2][4];                                 // [gate | up][m16 tile][fragment]
-#pragma unroll
-            for (int g = 0; g < 2; ++g) {
+            for (int i = 0; i < 4; ++i)
 #pragma unroll
                 for (int m = 0; m < 2; ++m)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) acc[g][m][e] = 0;
-                if (g >= gpi) continue;
-                // four accumulator sets: four of a warp's chunks of a stage are independent MMAs, so their loads and the
-                // latency of the MMAs overlap
-                int a[4][2][4];
+                    for (int e = 0; e < 4; ++e) a[i][m][e] = 0;
+            for (int c0 = 0; c0 < KC; c0 += DEC_STAGE_CHUNKS) {
+                acquire_stage();
+                if (compute && !failed) {
+                    const int nch = min(DEC_STAGE_CHUNKS, KC - c0);
+                    const uint32_t* const wslot = reinterpret_cast<const uint32_t*>(ring + (size_t)slot * DEC_STAGE_BYTES) + g8 * 4 + t4;
+                    const uint32_t* const xst = xlane + (size_t)c0 * 8;
+                    if (nch == DEC_STAGE_CHUNKS) {
+                        // a full stage: constant trip counts, no per-load conditions
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-#pragma unroll
-                    for (int m = 0; m < 2; ++m)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) a[i][m][e] = 0;
-                for (int c0 = 0; c0 < KC; c0 += DEC_STAGE_CHUNKS) {
-                    acquire_stage();
-                    if (compute && !failed) {
-                        const int nch = min(DEC_STAGE_CHUNKS, KC - c0);
-                        const uint32_t* const wslot = reinterpret_cast<const uint32_t*>(ring + (size_t)slot * DEC_STAGE_BYTES) + g8 * 4 + t4;
-                        const uint32_t* const xlane = reinterpret_cast<const uint32_t*>(xs) + (size_t)c0 * 2 * Mc * 4 + g8 * 4 + t4;
-#pragma unroll
-                        for (int half = 0; half < DEC_STAGE_CHUNKS / (4 * DEC_WARPS); ++half) {
+                        for (int quad = 0; quad < DEC_STAGE_CHUNKS / (4 * DEC_WARPS); ++quad) {
                             uint32_t w[4][4], b[4][2];
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
-                                const int cc = warp + DEC_WARPS * (4 * half + i);
-                                const bool live = cc < nch;
+                                const int cc = warp + DEC_WARPS * (4 * quad + i);
 #pragma unroll
-                                for (int r = 0; r < 4; ++r) w[i][r] = live ? wslot[cc * 128 + r * 32] : 0u;
-                                b[i][0] = (live && col_live) ? xlane[cc * 2 * Mc * 4] : 0u;
-                                b[i][1] = (live && col_live) ? xlane[(cc * 2 + 1) * Mc * 4] : 0u;
+                                for (int r = 0; r < 4; ++r) w[i][r] = wslot[cc * 128 + r * 32];
+                                b[i][0] = xst[cc * 8];
+                                b[i][1] = xst[cc * 8 + 4];
                             }
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
-                                if (warp + DEC_WARPS * (4 * half + i) < nch) {
-                                    mma_s8(a[i][0], (w[i][0] << 4) & 0xF0F0F0F0u, (w[i][1] << 4) & 0xF0F0F0F0u, w[i][0] & 0xF0F0F0F0u,
-                                           w[i][1] & 0xF0F0F0F0u, b[i][0], b[i][1]);
-                                    mma_s8(a[i][1], (w[i][2] << 4) & 0xF0F0F0F0u, (w[i][3] << 4) & 0xF0F0F0F0u, w[i][2] & 0xF0F0F0F0u,
-                                           w[i][3] & 0xF0F0F0F0u, b[i][0], b[i][1]);
-                                }
+                                if (!col_live) { b[i][0] = 0u; b[i][1] = 0u; }
+                                mma_s8(a[i][0], (w[i][0] << 4) & 0xF0F0F0F0u, (w[i][1] << 4) & 0xF0F0F0F0u, w[i][0] & 0xF0F0F0F0u,
+                                       w[i][1] & 0xF0F0F0F0u, b[i][0], b[i][1]);
+                                mma_s8(a[i][1], (w[i][2] << 4) & 0xF0F0F0F0u, (w[i][3] << 4) & 0xF0F0F0F0u, w[i][2] & 0xF0F0F0F0u,
+                                       w[i][3] & 0xF0F0F0F0u, b[i][0], b[i][1]);
                             }
                         }
+                    } else {
+                        // the K tail: fewer chunks than a stage holds (the count is a multiple of four)
+                        for (int cc = warp; cc < nch; cc += DEC_WARPS) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int r = 0; r < 4; ++r) w[r] = wslot[cc * 128 + r * 32];
+                            const uint32_t b0 = col_live ? xst[cc * 8] : 0u, b1 = col_live ? xst[cc * 8 + 4] : 0u;
+                            mma_s8(a[0][0], (w[0] << 4) & 0xF0F0F0F0u, (w[1] << 4) & 0xF0F0F0F0u, w[0] & 0xF0F0F0F0u, w[1] & 0xF0F0F0F0u, b0, b1);
+                            mma_s8(a[0][1], (w[2] << 4) & 0xF0F0F0F0u, (w[3] << 4) & 0xF0F0F0F0u, w[2] & 0xF0F0F0F0u, w[3] & 0xF0F0F0F0u, b0, b1);
+                        }
                     }
-                    release_stage();
                 }
-#pragma unroll
-                for (int m = 0; m < 2; ++m)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) acc[g][m][e] = (a[0][m][e] + a[1][m][e]) + (a[2][m][e] + a[3][m][e]);
+                release_stage();
             }
-            if (TRACE && trace && j == my_items - 1) trace[5] = (unsigned long long)(clock64() - c_start);
 #pragma unroll
-            for (int g = 0; g < 2; ++g) {
-                if (g >= gpi) continue;
+            for (int m = 0; m < 2; ++m)
 #pragma unroll
-                for (int m = 0; m < 2; ++m)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        red[red_index(warp, rows, g * 32 + m * 16 + g8 + (e >> 1) * 8, 2 * t4 + (e & 1))] = acc[g][m][e];
-            }
+                for (int e = 0; e < 4; ++e) acc[g][m][e] = (a[0][m][e] + a[1][m][e]) + (a[2][m][e] + a[3][m][e]);
         }
-        // ---- 4. sum the warps' partial sums, dequantise, store
+        if (TRACE && trace && j == my_items - 1) trace[5] = (unsigned long long)(clock64() - c_start);
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+            if (g >= gpi) continue;
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    red[red_index(warp, rows, g * 32 + m * 16 + g8 + (e >> 1) * 8, 2 * t4 + (e & 1))] = acc[g][m][e];
+        }
+        // ---- sum the warps' partial sums, dequantise, store
         bar_sync_contraction();
         const float ca = sw_a, cb = sw_b;
         if (j + 1 < my_items) load_channel_scales(item + ncta);
@@ -489,13 +450,8 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
             int v = 0, u = 0;
 #pragma unroll
             for (int w = 0; w < DEC_WARPS; ++w) {
-                if constexpr (DOT) {
-                    v += red[(w * 4 + tok_out) * rows + lane];
-                    if (swiglu) u += red[(w * 4 + tok_out) * rows + 32 + lane];
-                } else {
-                    v += red[red_index(w, rows, lane, tok_out)];
-                    if (swiglu) u += red[red_index(w, rows, 32 + lane, tok_out)];
-                }
+                v += red[red_index(w, rows, lane, tok_out)];
+                if (swiglu) u += red[red_index(w, rows, 32 + lane, tok_out)];
             }
             v >>= 4;   // exact: the unpacked weights are 16 x code
             u >>= 4;
@@ -533,22 +489,22 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     }
 }
 
-template <bool HALF, bool DOT, bool TRACE>
+template <bool HALF, bool TRACE>
 __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_kernel(const DecodeParams p)
 {
-    decode_cta<HALF, DOT, TRACE>(p, blockIdx.x, gridDim.x);
+    decode_cta<HALF, TRACE>(p, blockIdx.x, gridDim.x);
 }
 
 // Several INDEPENDENT linears (same token count, activation type and cluster size) in one launch: the grid is the
 // concatenation of their CTAs.  A decoder layer's q/k/v (or gate/up) projections read the same activations and
 // do not depend on each other; launched one by one on a stream each would wait for the one in front, in one
 // launch they pay the dependent latency once while their weights stream together.
-template <bool HALF, bool DOT>
+template <bool HALF>
 __global__ void __launch_bounds__(DEC_THREADS, 2) gemm_decode_batch_kernel(const DecodeBatch b)
 {
     int i = 0;
     while (i + 1 < b.count && (int)blockIdx.x >= b.first_cta[i + 1]) ++i;
-    decode_cta<HALF, DOT, false>(b.p[i], blockIdx.x - (unsigned)b.first_cta[i], (unsigned)(b.first_cta[i + 1] - b.first_cta[i]));
+    decode_cta<HALF, false>(b.p[i], blockIdx.x - (unsigned)b.first_cta[i], (unsigned)(b.first_cta[i + 1] - b.first_cta[i]));
 }
 
 // ---------------------------------------------------------------------------------- host side
@@ -575,14 +531,13 @@ int gemm_decode_ring(int M, int KB, bool swiglu)
     return ring < DEC_MAX_RING ? ring : DEC_MAX_RING;
 }
 
-// Cluster size (= how many CTAs share the quantisation): at most about one and a half 16-element units per
-// thread; quantising a unit costs a thread about as much as the whole exchange does.
+// Cluster size (= how many CTAs share the quantisation).  Quantising a 16-element unit costs a thread about 500
+// cycles of issue slots and the exchange about as much as one and a half units, so up to three units per thread
+// stay local; beyond that four CTAs share (clusters of eight leave half of this GPU's SMs without a CTA).
 int gemm_decode_cluster(int M, int KB)
 {
     const long long units = (long long)dec_token_slots(M) * KB * 8;
-    int s = 1;
-    while (s < 8 && units > 384ll * s) s *= 2;
-    return s;
+    return units <= 768 ? 1 : 4;
 }
 
 // CTAs: at most `cap` (a multiple of the cluster size), and among the counts down to half of that the one
@@ -603,10 +558,10 @@ int gemm_decode_ctas(int items, int cluster, int cap)
     return best;
 }
 
-template <bool HALF, bool DOT, bool TRACE>
+template <bool HALF, bool TRACE>
 static cudaError_t launch_decode_inst(const DecodeParams& p, cudaStream_t stream, bool pdl)
 {
-    auto kernel = gemm_decode_kernel<HALF, DOT, TRACE>;
+    auto kernel = gemm_decode_kernel<HALF, TRACE>;
     static PerDeviceOnce configured;
     int device = -1;
     if (configured.needed(device)) {
@@ -645,19 +600,14 @@ cudaError_t launch_gemm_decode(const DecodeParams& p, cudaStream_t stream, bool 
         p.ring > DEC_MAX_RING || p.ctas < p.cluster || p.ctas % p.cluster || (swiglu && p.F % GROUP) ||
         dec_smem_bytes(p.M, p.KB, swiglu, p.ring) > DEC_SMEM_LIMIT || (long long)p.KB * KBLOCK > 131072)
         return cudaErrorInvalidValue;
-    const bool dot = p.M <= 4;
-    if (p.trace) {
-        if (dot) return p.half ? launch_decode_inst<true, true, true>(p, stream, pdl) : launch_decode_inst<false, true, true>(p, stream, pdl);
-        return p.half ? launch_decode_inst<true, false, true>(p, stream, pdl) : launch_decode_inst<false, false, true>(p, stream, pdl);
-    }
-    if (dot) return p.half ? launch_decode_inst<true, true, false>(p, stream, pdl) : launch_decode_inst<false, true, false>(p, stream, pdl);
-    return p.half ? launch_decode_inst<true, false, false>(p, stream, pdl) : launch_decode_inst<false, false, false>(p, stream, pdl);
+    if (p.trace) return p.half ? launch_decode_inst<true, true>(p, stream, pdl) : launch_decode_inst<false, true>(p, stream, pdl);
+    return p.half ? launch_decode_inst<true, false>(p, stream, pdl) : launch_decode_inst<false, false>(p, stream, pdl);
 }
 
-template <bool HALF, bool DOT>
+template <bool HALF>
 static cudaError_t launch_decode_batch_inst(const DecodeBatch& b, cudaStream_t stream, bool pdl)
 {
-    auto kernel = gemm_decode_batch_kernel<HALF, DOT>;
+    auto kernel = gemm_decode_batch_kernel<HALF>;
     static PerDeviceOnce configured;
     int device = -1;
     if (configured.needed(device)) {
@@ -707,16 +657,14 @@ cudaError_t launch_gemm_decode_batch(const DecodeBatch& b, cudaStream_t stream, 
             dec_smem_bytes(p.M, p.KB, swiglu, p.ring) > DEC_SMEM_LIMIT || (long long)p.KB * KBLOCK > 131072)
             return cudaErrorInvalidValue;
     }
-    const bool dot = b.p[0].M <= 4;
-    if (dot) return b.p[0].half ? launch_decode_batch_inst<true, true>(b, stream, pdl) : launch_decode_batch_inst<false, true>(b, stream, pdl);
-    return b.p[0].half ? launch_decode_batch_inst<true, false>(b, stream, pdl) : launch_decode_batch_inst<false, false>(b, stream, pdl);
+    return b.p[0].half ? launch_decode_batch_inst<true>(b, stream, pdl) : launch_decode_batch_inst<false>(b, stream, pdl);
 }
 
 // Resident clusters of this kernel with `smem` bytes of dynamic shared memory, times the cluster size:
 // the most CTAs a launch may have if all of them are to run at once.
 int gemm_decode_resident_ctas(int cluster, size_t smem, int sm_count)
 {
-    auto kernel = gemm_decode_kernel<true, false, false>;
+    auto kernel = gemm_decode_kernel<true, false>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM_LIMIT) != cudaSuccess) {
         cudaGetLastError();
         return sm_count / cluster * cluster;

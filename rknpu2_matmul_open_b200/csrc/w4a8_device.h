@@ -106,6 +106,7 @@ struct GemmParams {
     int epi;
     int split;              // split-K factor == cluster size along y (1, 2, 4, 8)
     int pair;               // tcgen05 path: 1 = two-CTA tiles (cta_group::2), T must be 128
+    int w8;                 // tcgen05 per-tile kernel: Wp holds int8 codes in the W8 layout (w8a8_kernels.cu), sums are not scaled by 16
     unsigned long long timeout_ns;
     unsigned long long* trace;  // optional cycle stamps of CTA (0,0): [role 0..2][k-block 0..63][2] (nullable)
     int* partials;              // streaming kernel: [2 x CTAs][T / 4][128][4] int32 partial sums (two slots per CTA, never cleared)
@@ -192,6 +193,23 @@ struct PackParams {
     int* error;             // set to 1 when a code lies outside [-8,7]
     int K, N, KC, NG;
 };
+
+// ---- W8A8 operators (w8a8_kernels.cu): int8 weights W8p[g][kb][c][r][16 B], activations in the same Xq layout
+struct W8PackParams {
+    const int8_t* B;        // [K,N] int8 on the device
+    uint8_t* Wp;
+    int K, N, KB, NG;
+};
+struct W8QuantParams {
+    const void* A;              // [M,K] fp32, binary16 or int8
+    const float* static_scale;  // [M] caller's per-token scales on the device, or NULL: scan the rows
+    uint8_t* Xq;
+    float* scales;              // [M] the scales used (1 for int8 input)
+    int M, K, Kp, T;
+    int kind;                   // 0 fp32, 1 binary16, 2 int8 as given
+};
+cudaError_t launch_w8_pack_weights(const W8PackParams& p, cudaStream_t stream);
+cudaError_t launch_w8_quantize(const W8QuantParams& p, cudaStream_t stream);
 
 // Launch wrappers (w4a8_kernels.cu / w4a8_gemm_tc.cu). All return the launch error.
 cudaError_t launch_pack_weights(const PackParams& p, cudaStream_t stream);

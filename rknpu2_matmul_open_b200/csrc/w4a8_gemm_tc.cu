@@ -46,20 +46,23 @@ constexpr int TC_THREADS = 64 + 32 * TC_UNPACK_WARPS;
 constexpr int TC_A_COL0 = 256;      // A buffers live behind the accumulator columns
 constexpr int TC_TMEM_COLS = 512;
 
-__host__ __device__ constexpr size_t tc_stage_bytes(int T) { return 2 * (8192 + (size_t)T * 128); }
-__host__ __device__ constexpr size_t tc_smem_bytes(int T, int stages, int tokens)
+// bytes of one k-block of one 32-channel weight group: int4 codes 2 KB, int8 codes (the W8A8 operators) 4 KB
+__host__ __device__ constexpr size_t tc_group_bytes(bool w8) { return w8 ? 4096 : 2048; }
+__host__ __device__ constexpr size_t tc_stage_bytes(int T, bool w8 = false) { return 2 * (4 * tc_group_bytes(w8) + (size_t)T * 128); }
+__host__ __device__ constexpr size_t tc_smem_bytes(int T, int stages, int tokens, bool w8 = false)
 {
-    return stages * tc_stage_bytes(T) + (size_t)tokens * 4 /* token scales */ + (2 * stages + 2 * TC_ABUF + 1) * 8 + 32;
+    return stages * tc_stage_bytes(T, w8) + (size_t)tokens * 4 /* token scales */ + (2 * stages + 2 * TC_ABUF + 1) * 8 + 32;
 }
 
-template <bool PAIR>
+template <bool PAIR, bool W8>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int NSTAGE = PAIR ? TC_STAGES_PAIR : (p.T <= 128 ? TC_STAGES_DEEP : TC_STAGES);
     const int T = p.T;                              // tokens of this CTA's activation tile (128 when paired)
     const int TOK = PAIR ? 256 : T;                 // tokens (accumulator columns) of the MMA tile
-    const size_t stage_bytes = tc_stage_bytes(T);
+    const size_t stage_bytes = tc_stage_bytes(T, W8);
+    constexpr uint32_t GB = (uint32_t)tc_group_bytes(W8);   // one k-block of one weight group
     uint8_t* const stages = smem;
     float* const s_sx = reinterpret_cast<float*>(smem + NSTAGE * stage_bytes);
     uint64_t* const full = reinterpret_cast<uint64_t*>(s_sx + TOK);
@@ -115,7 +118,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
             // weight group and lane 4 the activation tile, so the five requests issue in parallel.
             const int w = lane & 3;
             const int group = swiglu ? (w < 2 ? tile * 2 + w : p.F / GROUP + tile * 2 + (w - 2)) : tile * 4 + w;
-            const uint8_t* wsrc = p.Wp + (size_t)group * KC * 512;
+            const uint8_t* wsrc = p.Wp + (size_t)group * KB * GB;
             const uint8_t* xtile = p.Xq + (size_t)mt * ((size_t)KB * 8) * T * 16;
             bool ok = true;
             const int nstage_iters = (KB + 1) / 2;
@@ -124,14 +127,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
                 const int kbs = min(2, KB - 2 * it);              // k-blocks in this stage
                 if (lane == 0) {
                     if (it >= NSTAGE) ok = mbar_wait_cluster(&empty[s], ((it / NSTAGE) - 1) & 1, deadline);
-                    if (ok) mbar_arrive_expect_tx(&full[s], (uint32_t)kbs * (8192u + (uint32_t)T * 128u));
+                    if (ok) mbar_arrive_expect_tx(&full[s], (uint32_t)kbs * (4u * GB + (uint32_t)T * 128u));
                     TC_STAMP(0, 2 * it, 0);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) { *s_error = 1; break; }
                 uint8_t* dst = stages + (size_t)s * stage_bytes;
-                if (lane < 4) bulk_g2s(dst + w * 4096, wsrc + (size_t)it * 4096, (uint32_t)kbs * 2048u, &full[s]);
-                else if (lane == 4) bulk_g2s(dst + 16384, xtile + (size_t)it * 16 * T * 16, (uint32_t)kbs * (uint32_t)T * 128u, &full[s]);
+                if (lane < 4) bulk_g2s(dst + w * 2 * GB, wsrc + (size_t)it * 2 * GB, (uint32_t)kbs * GB, &full[s]);
+                else if (lane == 4) bulk_g2s(dst + 8 * GB, xtile + (size_t)it * 16 * T * 16, (uint32_t)kbs * (uint32_t)T * 128u, &full[s]);
             }
         } else if (warp == 1) {
             // ---------------------------------------------------------------- MMA issuer
@@ -148,7 +151,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
                     if (!ok) { *s_error = 1; break; }
                     TC_STAMP(1, kb, 0);
                     tc_fence_after();
-                    const uint32_t xaddr = smem_u32(stages + (size_t)s * stage_bytes + 16384 + (size_t)(kb & 1) * T * 128);
+                    const uint32_t xaddr = smem_u32(stages + (size_t)s * stage_bytes + 8 * GB + (size_t)(kb & 1) * T * 128);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const uint64_t desc = tc_smem_desc(xaddr + (uint32_t)(2 * j) * T * 16, (uint32_t)T * 16u, 128u);
@@ -189,7 +192,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
                 if (!ok) { *s_error = 1; break; }
                 if (q == 2 && lane == 0) TC_STAMP(2, kb, 0);
                 tc_fence_after();
-                const uint4* src = reinterpret_cast<const uint4*>(stages + (size_t)s * stage_bytes + q * 4096) + lane;
+                const uint4* src = reinterpret_cast<const uint4*>(stages + (size_t)s * stage_bytes + q * 2 * GB) + lane;
+                if constexpr (W8) {
+                    // int8 codes need no unpacking: a lane's 16-byte pieces are already the words of its TMEM row
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        if (h < kbs) {
+                            uint32_t r[32];
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) {
+                                const uint4 v = src[(8 * h + c) * 32];
+                                r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;   // k = 16c + 4j .. +3
+                            }
+                            tc_st32(lane_addr + TC_A_COL0 + (h ? b1 : b0) * 32, r);
+                        }
+                    }
+                } else {
                 uint4 w[8];
 #pragma unroll
                 for (int c = 0; c < 8; ++c) w[c] = (c < 4 * kbs) ? src[c * 32] : make_uint4(0u, 0u, 0u, 0u);
@@ -208,6 +226,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
                         }
                         tc_st32(lane_addr + TC_A_COL0 + (h ? b1 : b0) * 32, r);
                     }
+                }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);    // the packed weights of this stage are in registers
@@ -261,7 +280,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
                 if (!swiglu) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int v = (int)r[i] >> 4;   // exact: sums are multiples of 16
+                        const int v = W8 ? (int)r[i] : (int)r[i] >> 4;   // int4 path: exact, sums are multiples of 16
                         uint8_t* cell = stg + (size_t)i * row_bytes + (size_t)ch * esize;
                         if (p.epi == EPI_I32) *reinterpret_cast<int*>(cell) = v;
                         else {
@@ -277,14 +296,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams
                     if (ch >= 64) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            exch[i * 64 + (ch - 64)] = dequant((int)r[i] >> 4, s_sx[min(t0 + i, TOK - 1)], sw);
+                            exch[i * 64 + (ch - 64)] = dequant(W8 ? (int)r[i] : (int)r[i] >> 4, s_sx[min(t0 + i, TOK - 1)], sw);
                     }
                     asm volatile("bar.sync %0, 128;" ::"r"(2 + set) : "memory");
                     if (ch < 64) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             const int m = tok_base + t0 + i;
-                            const float g = dequant((int)r[i] >> 4, s_sx[min(t0 + i, TOK - 1)], sw);
+                            const float g = dequant(W8 ? (int)r[i] : (int)r[i] >> 4, s_sx[min(t0 + i, TOK - 1)], sw);
                             const float y = __fmul_rn(silu_poly(g), exch[i * 64 + ch]);
                             *reinterpret_cast<float*>(stg + (size_t)i * row_bytes + (size_t)ch * 4) = y;
                             if (p.rowmax) {
@@ -350,20 +369,17 @@ bool gemm_tc_supported(const GemmParams& p)
     return p.M >= 1 && (long long)p.KB * KBLOCK <= 131072;
 }
 
-cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl)
+template <bool PAIR, bool W8>
+static cudaError_t launch_tc_inst(const GemmParams& p, cudaStream_t stream, bool pdl)
 {
-    if (p.T < 16 || p.T > 256 || p.T % 16 || !gemm_tc_supported(p)) return cudaErrorInvalidValue;
-    const bool pair = p.pair != 0;
-    if (pair && p.T != 128) return cudaErrorInvalidValue;
+    auto kernel = gemm_tc_kernel<PAIR, W8>;
+    const size_t widest = PAIR ? tc_smem_bytes(128, TC_STAGES_PAIR, 256, W8)
+                               : (tc_smem_bytes(256, TC_STAGES, 256, W8) > tc_smem_bytes(128, TC_STAGES_DEEP, 128, W8)
+                                      ? tc_smem_bytes(256, TC_STAGES, 256, W8) : tc_smem_bytes(128, TC_STAGES_DEEP, 128, W8));
     static PerDeviceOnce configured;
     int configured_device = -1;
     if (configured.needed(configured_device)) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)(tc_smem_bytes(256, TC_STAGES, 256) > tc_smem_bytes(128, TC_STAGES_DEEP, 128)
-                                                       ? tc_smem_bytes(256, TC_STAGES, 256) : tc_smem_bytes(128, TC_STAGES_DEEP, 128)));
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)tc_smem_bytes(128, TC_STAGES_PAIR, 256));
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)widest);
         if (e != cudaSuccess) return e;
         configured.mark(configured_device);
     }
@@ -373,10 +389,10 @@ cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl)
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int n = 0;
-    if (pair) {
+    if (PAIR) {
         // CTA pairs along x: two neighbouring channel tiles share one 256-token tile
         cfg.gridDim = dim3((unsigned)((tiles + 1) / 2 * 2), (unsigned)((p.M + 255) / 256), 1);
-        cfg.dynamicSmemBytes = tc_smem_bytes(128, TC_STAGES_PAIR, 256);
+        cfg.dynamicSmemBytes = tc_smem_bytes(128, TC_STAGES_PAIR, 256, W8);
         attr[n].id = cudaLaunchAttributeClusterDimension;
         attr[n].val.clusterDim.x = 2;
         attr[n].val.clusterDim.y = 1;
@@ -384,7 +400,7 @@ cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl)
         ++n;
     } else {
         cfg.gridDim = dim3((unsigned)tiles, (unsigned)((p.M + p.T - 1) / p.T), 1);
-        cfg.dynamicSmemBytes = tc_smem_bytes(p.T, p.T <= 128 ? TC_STAGES_DEEP : TC_STAGES, p.T);
+        cfg.dynamicSmemBytes = tc_smem_bytes(p.T, p.T <= 128 ? TC_STAGES_DEEP : TC_STAGES, p.T, W8);
     }
     if (pdl) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -393,7 +409,16 @@ cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl)
     }
     cfg.attrs = attr;
     cfg.numAttrs = n;
-    return pair ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, p) : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false>, p);
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
+cudaError_t launch_gemm_tc(const GemmParams& p, cudaStream_t stream, bool pdl)
+{
+    if (p.T < 16 || p.T > 256 || p.T % 16 || !gemm_tc_supported(p)) return cudaErrorInvalidValue;
+    const bool pair = p.pair != 0;
+    if (pair && p.T != 128) return cudaErrorInvalidValue;
+    if (p.w8) return pair ? launch_tc_inst<true, true>(p, stream, pdl) : launch_tc_inst<false, true>(p, stream, pdl);
+    return pair ? launch_tc_inst<true, false>(p, stream, pdl) : launch_tc_inst<false, false>(p, stream, pdl);
 }
 
 } // namespace rkb200

@@ -238,6 +238,9 @@ uint64_t affinity_mask()
             mask |= uint64_t(CPU_ISSET(cpu, &cpus) ? 1 : 0) << cpu;
     return mask ? mask : 1;   // an unreadable or empty affinity counts as CPU 0
 }
+} // namespace
+uint64_t process_cpu_mask() { return affinity_mask(); }
+namespace {
 // Up to `want` CPUs out of `allowed`, CPUs 4..7 before the others (the fast cores of the SoC the cache
 // format was designed on; the resulting mask is a key field, so the order is kept).
 uint64_t pick_cpus(uint64_t allowed, int want, int& picked)

@@ -25,6 +25,7 @@ struct HostResources {
 };
 HostResources host_resources(const rk_npu_w4a8_autotune_config& request);
 int chain_token_limit();   // the environment value alone
+uint64_t process_cpu_mask();   // CPUs 0..63 of the process affinity (CPU 0 when it cannot be read)
 
 // A strategy as the legacy (non-_ex) entry points see it.
 Strategy widen(const rk_npu_w4a8_strategy& s);
