@@ -425,7 +425,10 @@ def run_cuda(args, rank, world, local_rank):
         if args.tokens != 1:
             also["M1_GBps"] = _time_other_m(rk, dom, linears, 1, args, dev, stream)
         also["independent_linears_4_streams_GBps"] = _time_streams(linears, step_bytes, args, dev, 4)
-        also["layer_dependencies_only_GBps"] = _time_batched(rk, linears, step_bytes, args, stream)
+        try:
+            also["layer_dependencies_only_GBps"] = _time_batched(rk, linears, step_bytes, args, stream)
+        except RuntimeError as exc:      # a forced kernel family without the batch form
+            also["layer_dependencies_only_error"] = str(exc)
     if not args.quick:
         peak = measure_int8_peak() if rank == 0 else None
         for name, fn in (("prefill", _prefill), ("ffn_4096_14336", _ffn_llama8b), ("ffn_8192_28672", _ffn_70b)):

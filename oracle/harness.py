@@ -153,6 +153,22 @@ class Oracle:
                                  _ptr(out), _ptr(acc), _ptr(s))
         return rc, out, acc, s
 
+    def w8_linear(self, A, B, w_scale, a_scale=None):
+        """One typed W8A8 linear (dynamic scales, or the caller's static ones).  Returns dict(rc, out, acc, scales, codes)."""
+        half = A.dtype == np.uint16
+        A = _c(A, np.uint16 if half else np.float32)
+        B = _c(B, np.int8)
+        M, K = A.shape
+        N = B.shape[1]
+        out = np.empty((M, N), np.uint16 if half else np.float32)
+        acc = np.empty((M, N), np.int32)
+        s = np.empty(M, np.float32)
+        q = np.empty((M, K), np.int8)
+        static = None if a_scale is None else _c(a_scale, np.float32)
+        rc = getattr(self.lib, 'orc_w8_linear')(_ptr(A), int(half), M, K, N, _ptr(B), _ptr(_c(w_scale, np.float32)), _ptr(static),
+                                               _ptr(out), _ptr(acc), _ptr(s), _ptr(q))
+        return dict(rc=rc, out=out, acc=acc, scales=s, codes=q)
+
     def ffn(self, A, B_gu, s_gu, B_dn, s_dn, mode: int = 1):
         """Returns dict(rc, middle, C, acc_gate_up, acc_down, scales_down_in)."""
         A = _c(A, np.float32)
@@ -256,6 +272,25 @@ class Reference:
                                  C.byref(sat), stage, C.byref(prep))
         return dict(rc=rc, out=out, acc=acc, scales=s, saturated=sat.value, stage_us=list(stage),
                     prepare_us=prep.value)
+
+    def w8_linear(self, A, B, w_scale, a_scale=None):
+        """One typed W8A8 linear (dynamic scales, or the caller's static ones).  Returns dict(rc, out, acc, scales, codes)."""
+        half = A.dtype == np.uint16
+        A = _c(A, np.uint16 if half else np.float32)
+        B = _c(B, np.int8)
+        M, K = A.shape
+        N = B.shape[1]
+        out = np.empty((M, N), np.uint16 if half else np.float32)
+        acc = np.empty((M, N), np.int32)
+        s = np.empty(M, np.float32)
+        q = np.empty((M, K), np.int8)
+        static = None if a_scale is None else _c(a_scale, np.float32)
+        rc = getattr(self.lib, 'ref_w8_linear')(_ptr(A), int(half), M, K, N, _ptr(B), _ptr(_c(w_scale, np.float32)), _ptr(static),
+                                               _ptr(out), _ptr(acc), _ptr(s), _ptr(q))
+        return dict(rc=rc, out=out, acc=acc, scales=s, codes=q)
+
+    def k_partition_query(self, M, K, k_tile) -> int:
+        return int(self.lib.ref_k_partition_query(M, K, k_tile))
 
     def layer(self, B, w_scale, k_tile=480):
         B = _c(B, np.int8)

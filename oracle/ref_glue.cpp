@@ -19,6 +19,8 @@
 #include "rk_npu_i4_bounds.h"
 #include "rk_npu_w4a8_tune_internal.h"
 #include "rk_npu_half_bits.h"
+#include "rk_npu_cpu_kernels.h"
+#include "rk_npu_quant_matmul.h"
 #include <algorithm>
 #include <chrono>
 #include <cstring>
@@ -293,4 +295,42 @@ uint64_t ref_fingerprint(int K, int N, const int8_t* B, const float* w_scale) {
     return hash.value;
 }
 int ref_host_threads(void) { return omp_get_max_threads(); }
+// One typed W8A8 linear through the reference's own CPU stages (src/rk_npu_cpu_kernels.cpp): per-token scales,
+// quantise + row-major packing, and the fused native-int32 dequantisation.  Only the device step between them --
+// int8 x int8 -> int32, exact modulo 2^32, written in the device's native C layout src[((n/4)*M + m)*4 + n%4]
+// (src/rk_npu_cpu_kernels.h:18-25,170-172) -- is restated here.
+int ref_w8_linear(const void* A, int half, int M, int K, int N, const int8_t* B, const float* w_scale,
+                  const float* a_scale_static, void* out, int32_t* acc_out, float* scales_out, int8_t* codes_out) {
+    namespace cpu = rknpu2_matmul_open::cpu;
+    if (!A || !B || !w_scale || !out || M < 1 || K < 1 || N < 1) return RK_NPU_ERR_PARAM;
+    std::vector<float> scale(M);
+    if (a_scale_static) std::copy(a_scale_static, a_scale_static + M, scale.begin());
+    else if (half) cpu::i8_compute_dynamic_per_token_scale_f16(M, K, static_cast<const uint16_t*>(A), K, scale.data());
+    else cpu::i8_compute_dynamic_per_token_scale_f32(M, K, static_cast<const float*>(A), K, scale.data());
+    std::vector<int8_t> q(size_t(M) * K);
+    if (half) cpu::i8_pack_a_f16_quant_normal_strided(M, K, K, static_cast<const uint16_t*>(A), K, scale.data(), q.data());
+    else cpu::i8_pack_a_f32_quant_normal_strided(M, K, K, static_cast<const float*>(A), K, scale.data(), q.data());
+    const int nb_count = (N + 3) / 4;
+    std::vector<int32_t> native(size_t(nb_count) * M * 4, 0);
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            uint32_t sum = 0;
+            for (int k = 0; k < K; ++k) sum += uint32_t(int32_t(q[size_t(m) * K + k]) * int32_t(B[size_t(k) * N + n]));
+            native[(size_t(n / 4) * M + m) * 4 + n % 4] = int32_t(sum);
+        }
+    if (half) cpu::i8_unpack_c_native_i32_dequant_f16(M, N, native.data(), scale.data(), w_scale, nullptr, cpu::ActivationOp::None,
+                                                      static_cast<uint16_t*>(out));
+    else cpu::i8_unpack_c_native_i32_dequant_f32(M, N, native.data(), scale.data(), w_scale, nullptr, cpu::ActivationOp::None,
+                                                 static_cast<float*>(out));
+    if (acc_out)
+        for (int m = 0; m < M; ++m)
+            for (int n = 0; n < N; ++n) acc_out[size_t(m) * N + n] = native[(size_t(n / 4) * M + m) * 4 + n % 4];
+    if (scales_out) std::copy(scale.begin(), scale.end(), scales_out);
+    if (codes_out) std::copy(q.begin(), q.end(), codes_out);
+    return RK_NPU_OK;
+}
+// src/rk_npu_quant_matmul.cpp:1696-1700, the public K-partition query of the reference itself
+int ref_k_partition_query(int M, int K, int k_tile) { return rk_npu_matmul_k_partition_query(M, K, k_tile); }
+
 } // extern "C"

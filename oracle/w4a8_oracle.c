@@ -202,6 +202,56 @@ void orc_dequant(int M, int N, const int32_t *acc, const float *a_scale, const f
         }
 }
 
+/* ================================================================ typed W8A8 operators
+ * include/rk_npu_quant_matmul.h:358-372, src/rk_npu_cpu_kernels.cpp (scalar branches).
+ * Dynamic scale: max|x| / 127 when the maximum is positive, else 1 (:576-589, :853-871).  std::max(a, b) keeps a
+ * when b is NaN, so a NaN never raises the maximum; no lower clamp, no rejection of non-finite input. */
+void orc_w8_scales(const void *A, int half, int M, int K, float *scales)
+{
+    for (int m = 0; m < M; ++m) {
+        float maximum = 0.f;
+        for (int k = 0; k < K; ++k) {
+            const float a = fabsf(load_act(A, half, (int64_t)m * K + k));
+            if (maximum < a) maximum = a;
+        }
+        scales[m] = maximum > 0.f ? maximum / 127.0f : 1.0f;
+    }
+}
+
+/* :126-131 (quantize_s8_symmetric) and :598-606: a scale that is not positive gives zeros; otherwise
+ * q = max(-127, min(127, round(x * (1 / scale)))) with std::min / std::max argument order, so NaN -> 127. */
+void orc_w8_quantize(const void *A, int half, int M, int K, const float *scales, int8_t *q)
+{
+    for (int m = 0; m < M; ++m) {
+        const float scale = scales[m];
+        for (int k = 0; k < K; ++k) {
+            int8_t code = 0;
+            if (scale > 0.0f) {
+                float r = roundf(load_act(A, half, (int64_t)m * K + k) * (1.0f / scale));
+                r = (r < 127.0f) ? r : 127.0f;         /* std::min(127.0f, r) */
+                r = (-127.0f < r) ? r : -127.0f;       /* std::max(-127.0f, r) */
+                code = (int8_t)r;
+            }
+            q[(int64_t)m * K + k] = code;
+        }
+    }
+}
+
+/* One W8A8 linear: scales (dynamic, or the caller's when a_scale_static is given), codes, exact int32 sums modulo 2^32
+ * (include/rk_npu_quant_matmul.h:335-340), y = float(acc) * a_scale[m] * w_scale[n] evaluated left to right
+ * (src/rk_npu_cpu_kernels.cpp:1312), one more rounding for binary16 output. */
+int orc_w8_linear(const void *A, int half, int M, int K, int N, const int8_t *B, const float *w_scale,
+                  const float *a_scale_static, void *out, int32_t *acc, float *scales_used, int8_t *codes)
+{
+    if (!A || !B || !w_scale || !out || !acc || !scales_used || !codes || M < 1 || K < 1 || N < 1) return ORC_ERR_PARAM;
+    if (a_scale_static) memcpy(scales_used, a_scale_static, sizeof(float) * (size_t)M);
+    else orc_w8_scales(A, half, M, K, scales_used);
+    orc_w8_quantize(A, half, M, K, scales_used, codes);
+    orc_gemm_i32(codes, B, M, K, N, acc);
+    orc_dequant(M, N, acc, scales_used, w_scale, half, out);
+    return ORC_OK;
+}
+
 /* ------------------------------------------------------------------- SwiGLU
  * Two activations exist in the reference:
  *   mode 0: src/rk_npu_w4a8_swiglu.cpp:71  y = (g / (1 + expf(-g))) * u

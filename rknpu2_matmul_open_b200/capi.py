@@ -114,6 +114,21 @@ class MatmulStrategy(C.Structure):
                 ("total_us", C.c_double), ("jitter_pct", C.c_double), ("robust_us", C.c_double), ("c_layout", C.c_int)]
 
 
+class MatmulWeightConfig(C.Structure):
+    """rk_npu_matmul_weight_config: the (K, N, k_tile) key of a W8 weight object."""
+    _fields_ = [("K", C.c_int), ("N", C.c_int), ("k_tile", C.c_int)]
+
+
+class MatmulWorkspaceRequirements(C.Structure):
+    _fields_ = [("bytes", C.c_uint64), ("input_bytes", C.c_uint64), ("output_bytes", C.c_uint64), ("control_bytes", C.c_uint64),
+                ("wave_count", C.c_uint32), ("buffer_count", C.c_uint32)]
+
+
+class MatmulWeightRequirements(C.Structure):
+    _fields_ = [("bytes", C.c_uint64), ("packed_b_bytes", C.c_uint64), ("scale_bytes", C.c_uint64), ("wave_count", C.c_uint32),
+                ("buffer_count", C.c_uint32)]
+
+
 class I4Config(C.Structure):
     _fields_ = [("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("m_tile", C.c_int), ("k_tile", C.c_int),
                 ("n_tile", C.c_int), ("npu_core_mask", C.c_uint32), ("timeout_ms", C.c_uint32), ("pipeline", C.c_int),
@@ -188,6 +203,26 @@ _SIGNATURES = {
     "rk_npu_matmul_autotune_cache_load": (C.c_int, [_P, C.c_char_p, C.c_int, C.POINTER(MatmulAutotuneConfig),
                                                     C.POINTER(MatmulStrategy), C.POINTER(MatmulStrategy)]),
     "rk_npu_i4_config_init": (None, [C.POINTER(I4Config), C.c_int, C.c_int, C.c_int]),
+    # typed W8A8 operators
+    "rk_npu_matmul_k_partition_query": (C.c_int, [C.c_int, C.c_int, C.c_int]),
+    "rk_npu_matmul_workspace_memory_query": (C.c_int, [C.POINTER(MatmulStrategy), C.POINTER(MatmulWorkspaceRequirements)]),
+    "rk_npu_i8i8i32_weights_memory_query": (C.c_int, [C.POINTER(MatmulWeightConfig), C.POINTER(MatmulWeightRequirements)]),
+    "rk_npu_f16i8f16_weights_memory_query": (C.c_int, [C.POINTER(MatmulWeightConfig), C.POINTER(MatmulWeightRequirements)]),
+    "rk_npu_f32i8f32_weights_memory_query": (C.c_int, [C.POINTER(MatmulWeightConfig), C.POINTER(MatmulWeightRequirements)]),
+    "rk_npu_matmul_workspace_create": (_P, [_P, C.POINTER(MatmulStrategy)]),
+    "rk_npu_matmul_workspace_free": (None, [_P]),
+    "rk_npu_i8i8i32_weights_create": (_P, [_P, C.POINTER(MatmulWeightConfig), _P]),
+    "rk_npu_i8i8i32_weights_free": (None, [_P]),
+    "rk_npu_i8i8i32_run": (C.c_int, [_P, _P, _P, _P]),
+    "rk_npu_f16i8f16_weights_create": (_P, [_P, C.POINTER(MatmulWeightConfig), _P, _P]),
+    "rk_npu_f16i8f16_weights_free": (None, [_P]),
+    "rk_npu_f16i8f16_run_dynamic": (C.c_int, [_P, _P, _P, _P]),
+    "rk_npu_f16i8f16_run_static": (C.c_int, [_P, _P, _P, _P, _P]),
+    "rk_npu_f32i8f32_weights_create": (_P, [_P, C.POINTER(MatmulWeightConfig), _P, _P]),
+    "rk_npu_f32i8f32_weights_free": (None, [_P]),
+    "rk_npu_f32i8f32_run_dynamic": (C.c_int, [_P, _P, _P, _P]),
+    "rk_npu_f32i8f32_run_static": (C.c_int, [_P, _P, _P, _P, _P]),
+    "rk_npu_b200_matmul_launch_count": (C.c_uint64, [_P]),
     "rk_npu_w4a8_family_config_init": (None, [C.POINTER(W4A8FamilyConfig), C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int)]),
     # search tuner
     "rk_npu_w4a8_autotune": (C.c_int, [_P, C.POINTER(W4A8AutotuneConfig), _P, _P, C.POINTER(W4A8Strategy), C.POINTER(W4A8Strategy)]),

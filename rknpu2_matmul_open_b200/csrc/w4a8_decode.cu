@@ -208,6 +208,20 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(A) + ((size_t)(t0 + tl) * p.K + (size_t)u * 16) * sizeof(AT)));
         }
     }
+    // Everything that does not need the activations is settled before the wait: where this thread's units lie (no
+    // division behind the dependency) and the time limit (reading the global timer is slow; the few microseconds the
+    // launch in front still runs are charged to this launch's limit).
+    int pos_tl[UMAX], pos_u[UMAX];
+    bool pos_live[UMAX];
+#pragma unroll
+    for (int it = 0; it < UMAX; ++it) {
+        const int idx = tid + CT * it;
+        pos_tl[it] = 0;
+        pos_u[it] = 0;
+        if (idx < scan_items) locate(idx, pos_tl[it], pos_u[it]);
+        pos_live[it] = idx < scan_items && t0 + pos_tl[it] < M;
+    }
+    const unsigned long long deadline = global_ns() + p.timeout_ns;
     if (TRACE && trace) trace[1] = (unsigned long long)(clock64() - c_start);
     // The producer of A (and of the collected row maxima) has finished once the dependency wait returns.  One warp
     // executes it; the others block at the hardware barrier behind it, where they take no issue slots from the
@@ -220,25 +234,17 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     // every load is issued before anything waits for one: a round trip to L2 costs more than the rest of the scan
 #pragma unroll
     for (int it = 0; it < UMAX; ++it) {
-        const int idx = tid + CT * it;
 #pragma unroll
         for (int i = 0; i < (HALF ? 8 : 16); ++i) kept[it].w[i] = 0u;
-        if (idx < scan_items) {
-            int tl, u;
-            locate(idx, tl, u);
-            if (t0 + tl < M && u * 16 < p.K) load_raw<HALF>(A + (size_t)(t0 + tl) * p.K, u * 16, p.K, vec, kept[it]);
-        }
+        if (pos_live[it] && pos_u[it] * 16 < p.K) load_raw<HALF>(A + (size_t)(t0 + pos_tl[it]) * p.K, pos_u[it] * 16, p.K, vec, kept[it]);
     }
     uint32_t collected = 0;                   // no_scan: this thread's token's collected maximum
     if (no_scan && tid < TQ && t0 + tid < M) collected = p.rowmax_in[t0 + tid];
-    const unsigned long long deadline = global_ns() + p.timeout_ns;
     stamp(64);
     if (!no_scan) {
 #pragma unroll
         for (int it = 0; it < UMAX; ++it) {
-            const int idx = tid + CT * it;
-            int tl = 0, u;
-            if (idx < scan_items) locate(idx, tl, u);
+            const int tl = pos_tl[it];
             uint32_t bits = raw_maxbits<HALF>(kept[it]);    // units never loaded hold zeros
             // a warp whose 32 units belong to one token reduces first and issues a single shared atomic
             // (every warp-wide operation below is executed by all 32 lanes: none sits behind a per-lane condition)
@@ -300,15 +306,11 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     };
 #pragma unroll
     for (int it = 0; it < UMAX; ++it) {
-        const int idx = tid + CT * it;
-        if (idx < scan_items) {
-            int tl, u;
-            locate(idx, tl, u);
-            if (t0 + tl < M && u >= pu0 && u < pu1) {
-                float v[16];
-                raw_to_float<HALF>(kept[it], v);
-                keep_code(t0 + tl, u, quantize16(v, s_inv[tl], u * 16, p.K));
-            }
+        const int tl = pos_tl[it], u = pos_u[it];
+        if (pos_live[it] && u >= pu0 && u < pu1) {
+            float v[16];
+            raw_to_float<HALF>(kept[it], v);
+            keep_code(t0 + tl, u, quantize16(v, s_inv[tl], u * 16, p.K));
         }
     }
     for (int idx = tid + CT * UMAX; idx < scan_items; idx += CT) {
@@ -338,8 +340,9 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     }
     if (TRACE && trace) trace[4] = (unsigned long long)(clock64() - c_start);
     int verdict = 0;
-    for (int t = 0; t < M; ++t) {
-        const uint32_t w = s_scale[t];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {            // eight independent broadcast reads, not a chain of them
+        const uint32_t w = t < M ? s_scale[t] : 0u;
         if (w >= 0xFFFFFFF0u) verdict |= (int)(w & 0xFu);
     }
 

@@ -53,12 +53,19 @@ __host__ __device__ constexpr size_t tc_smem_bytes(int T, int stages, int tokens
 {
     return stages * tc_stage_bytes(T, w8) + (size_t)tokens * 4 /* token scales */ + (2 * stages + 2 * TC_ABUF + 1) * 8 + 32;
 }
+// Ring depth of a form: the depth the int4 form was tuned with, fewer where int8 weights (twice the bytes) would not fit
+__host__ __device__ constexpr int tc_stage_count(int T, bool pair, bool w8)
+{
+    int stages = pair ? TC_STAGES_PAIR : (T <= 128 ? TC_STAGES_DEEP : TC_STAGES);
+    while (stages > 2 && tc_smem_bytes(T, stages, pair ? 256 : T, w8) > 225 * 1024) --stages;
+    return stages;
+}
 
 template <bool PAIR, bool W8>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const GemmParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
-    const int NSTAGE = PAIR ? TC_STAGES_PAIR : (p.T <= 128 ? TC_STAGES_DEEP : TC_STAGES);
+    const int NSTAGE = tc_stage_count(p.T, PAIR, W8);
     const int T = p.T;                              // tokens of this CTA's activation tile (128 when paired)
     const int TOK = PAIR ? 256 : T;                 // tokens (accumulator columns) of the MMA tile
     const size_t stage_bytes = tc_stage_bytes(T, W8);
@@ -373,9 +380,7 @@ template <bool PAIR, bool W8>
 static cudaError_t launch_tc_inst(const GemmParams& p, cudaStream_t stream, bool pdl)
 {
     auto kernel = gemm_tc_kernel<PAIR, W8>;
-    const size_t widest = PAIR ? tc_smem_bytes(128, TC_STAGES_PAIR, 256, W8)
-                               : (tc_smem_bytes(256, TC_STAGES, 256, W8) > tc_smem_bytes(128, TC_STAGES_DEEP, 128, W8)
-                                      ? tc_smem_bytes(256, TC_STAGES, 256, W8) : tc_smem_bytes(128, TC_STAGES_DEEP, 128, W8));
+    const size_t widest = 227 * 1024;   // the opt-in limit; each launch asks for what its form needs
     static PerDeviceOnce configured;
     int configured_device = -1;
     if (configured.needed(configured_device)) {
@@ -392,7 +397,7 @@ static cudaError_t launch_tc_inst(const GemmParams& p, cudaStream_t stream, bool
     if (PAIR) {
         // CTA pairs along x: two neighbouring channel tiles share one 256-token tile
         cfg.gridDim = dim3((unsigned)((tiles + 1) / 2 * 2), (unsigned)((p.M + 255) / 256), 1);
-        cfg.dynamicSmemBytes = tc_smem_bytes(128, TC_STAGES_PAIR, 256, W8);
+        cfg.dynamicSmemBytes = tc_smem_bytes(128, tc_stage_count(128, true, W8), 256, W8);
         attr[n].id = cudaLaunchAttributeClusterDimension;
         attr[n].val.clusterDim.x = 2;
         attr[n].val.clusterDim.y = 1;
@@ -400,7 +405,7 @@ static cudaError_t launch_tc_inst(const GemmParams& p, cudaStream_t stream, bool
         ++n;
     } else {
         cfg.gridDim = dim3((unsigned)tiles, (unsigned)((p.M + p.T - 1) / p.T), 1);
-        cfg.dynamicSmemBytes = tc_smem_bytes(p.T, p.T <= 128 ? TC_STAGES_DEEP : TC_STAGES, p.T, W8);
+        cfg.dynamicSmemBytes = tc_smem_bytes(p.T, tc_stage_count(p.T, false, W8), p.T, W8);
     }
     if (pdl) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;

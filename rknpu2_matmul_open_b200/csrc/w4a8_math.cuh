@@ -145,7 +145,7 @@ __device__ __forceinline__ void store4_i32(int* out, const int (&v)[4], int vali
 __device__ __forceinline__ void scale_from_max(float maximum, bool bad, float& s, float& inv)
 {
     s = (maximum == 0.f || bad) ? 1.0f : fmaxf(__fdiv_rn(maximum, 127.0f), FLT_MIN);
-    inv = __fdiv_rn(1.0f, s);
+    inv = __frcp_rn(s);   // the correctly rounded reciprocal: the same value as the IEEE division 1 / s
 }
 // round half away from zero, then clamp to [-127, 127], without conversion instructions.
 // |x| + 0.5 added with rounding TOWARD ZERO never reaches an integer the exact sum does not reach,
@@ -159,17 +159,47 @@ __device__ __forceinline__ int round_clamp(float x)
     const int m = __float_as_int(x) >> 31;                                    // 0 or -1
     return (n ^ m) - m;
 }
-// 16 activations -> 16 int8 codes packed in four words (ties away from zero, clamp +-127).
+// Four products -> four int8 codes in one word (byte i = code of y[i]), ties away from zero.
+// Magnitudes: |y| + 0.5 added toward zero, then 1.5 * 2^23 added toward zero leaves floor(|y| + 0.5) in the low byte of
+// the float's bits (see round_clamp).  No clamp: every caller's scale is max(max|row| / 127, FLT_MIN) of the row the
+// product comes from, so |y| <= 127 (1 + 2^-22) and the floor never exceeds 127.  Signs: one byte of ones per negative
+// product (byte permutes that replicate the sign bit), then a bytewise two's-complement negation in five word
+// operations: x = n ^ s; low seven bits of x plus one where s is set cannot carry out of their byte.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector)
+{
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
+    return d;
+}
+__device__ __forceinline__ uint32_t quantize4(float y0, float y1, float y2, float y3)
+{
+    const uint32_t g0 = __float_as_uint(__fadd_rz(__fadd_rz(fabsf(y0), 0.5f), 12582912.0f));
+    const uint32_t g1 = __float_as_uint(__fadd_rz(__fadd_rz(fabsf(y1), 0.5f), 12582912.0f));
+    const uint32_t g2 = __float_as_uint(__fadd_rz(__fadd_rz(fabsf(y2), 0.5f), 12582912.0f));
+    const uint32_t g3 = __float_as_uint(__fadd_rz(__fadd_rz(fabsf(y3), 0.5f), 12582912.0f));
+    const uint32_t n = prmt(prmt(g0, g1, 0x0040u), prmt(g2, g3, 0x0040u), 0x5410u);
+    // selector nibbles 0xB / 0xF: byte 3 of the first / second operand with its sign bit replicated
+    const uint32_t sgn = prmt(prmt(__float_as_uint(y0), __float_as_uint(y1), 0x00FBu), prmt(__float_as_uint(y2), __float_as_uint(y3), 0x00FBu), 0x5410u);
+    const uint32_t x = n ^ sgn;
+    return (((x & 0x7F7F7F7Fu) + (sgn & 0x01010101u)) ^ (x & 0x80808080u));
+}
+// 16 activations -> 16 int8 codes packed in four words (ties away from zero; |code| <= 127 by the scale's construction).
 __device__ __forceinline__ uint4 quantize16(const float (&v)[16], float inv, int k0, int K)
 {
     uint32_t w[4];
+    if (k0 + 16 <= K) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        int q[4];
+        for (int j = 0; j < 4; ++j)
+            w[j] = quantize4(__fmul_rn(v[4 * j], inv), __fmul_rn(v[4 * j + 1], inv), __fmul_rn(v[4 * j + 2], inv), __fmul_rn(v[4 * j + 3], inv));
+    } else {
+        // the unit that straddles K: elements at or beyond K are zero codes
 #pragma unroll
-        for (int i = 0; i < 4; ++i) q[i] = (k0 + 4 * j + i < K) ? round_clamp(__fmul_rn(v[4 * j + i], inv)) : 0;
-        // low bytes of four ints -> one word: three byte permutes
-        w[j] = __byte_perm(__byte_perm((uint32_t)q[0], (uint32_t)q[1], 0x0040), __byte_perm((uint32_t)q[2], (uint32_t)q[3], 0x0040), 0x5410);
+        for (int j = 0; j < 4; ++j) {
+            int q[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) q[i] = (k0 + 4 * j + i < K) ? round_clamp(__fmul_rn(v[4 * j + i], inv)) : 0;
+            w[j] = __byte_perm(__byte_perm((uint32_t)q[0], (uint32_t)q[1], 0x0040), __byte_perm((uint32_t)q[2], (uint32_t)q[3], 0x0040), 0x5410);
+        }
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
 }

@@ -287,15 +287,20 @@ def test_every_entry_point_of_the_original_headers_links(lib):
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, missing
     # operators that are not built decline instead of pretending
-    for name in ("rk_npu_i8i8i32_run", "rk_npu_f16i8f16_run_dynamic", "rk_npu_i4i4i32_run",
+    for name in ("rk_npu_i8i8i32_autotune", "rk_npu_f16i8f16_dynamic_autotune_family", "rk_npu_i4i4i32_run",
                  "rk_npu_matmul_autotune_cache_save", "rk_npu_mem_alloc"):
-        fn = getattr(lib, name)
+        fn = C.CDLL(str(capi.LIB_PATH))[name]
         fn.restype, fn.argtypes = C.c_int, []
         assert fn() == capi.RK_NPU_ERR_PARAM, name
-    for name in ("rk_npu_i8i8i32_weights_create", "rk_npu_matmul_workspace_create", "rk_npu_i4_workspace_create"):
-        fn = getattr(lib, name)
+    for name in ("rk_npu_i8i8i32_weights_create_compress", "rk_npu_f16i8f16_weights_create_from_f32_compress", "rk_npu_i4_workspace_create"):
+        fn = C.CDLL(str(capi.LIB_PATH))[name]
         fn.restype, fn.argtypes = C.c_void_p, []
         assert fn() is None, name
+    # the typed W8A8 operators are built: argument errors are answered as such, without a device
+    assert lib.rk_npu_i8i8i32_run(None, None, None, None) == capi.RK_NPU_ERR_PARAM
+    assert lib.rk_npu_f16i8f16_run_static(None, None, None, None, None) == capi.RK_NPU_ERR_PARAM
+    assert lib.rk_npu_matmul_workspace_create(None, None) is None
+    assert lib.rk_npu_f32i8f32_weights_create(None, None, None, None) is None
     # the search tuners are built: argument errors are answered as such, without a device
     fast = capi.W4A8Strategy()
     assert lib.rk_npu_w4a8_autotune(None, None, None, None, C.byref(fast), None) == capi.RK_NPU_ERR_PARAM
