@@ -426,7 +426,7 @@ def run_cuda(args, rank, world, local_rank):
             also["M1_GBps"] = _time_other_m(rk, dom, linears, 1, args, dev, stream)
         also["independent_linears_4_streams_GBps"] = _time_streams(linears, step_bytes, args, dev, 4)
         try:
-            also["layer_dependencies_only_GBps"] = _time_batched(rk, linears, step_bytes, args, stream)
+            also["layer_dependencies_only_GBps"] = _time_batched(rk, dom, M, linears, step_bytes, args, stream)
         except RuntimeError as exc:      # a forced kernel family without the batch form
             also["layer_dependencies_only_error"] = str(exc)
     if not args.quick:
@@ -462,7 +462,8 @@ def run_cuda(args, rank, world, local_rank):
                              # one read per weight byte (ncu: DRAM bytes read equal the algorithmic bytes to 0.1 %), so the
                              # traffic of a launch is its algorithmic bytes
                              "traffic": bytes_per_launch, "peak_kind": peak_kind,
-                             "kernel": "gemm_decode_kernel (scan + quantise + GEMM + dequantise in one launch)",
+                             "kernel": {3: "gemm_fused_kernel (split-K clusters)", 5: "gemm_decode_kernel (whole-K CTAs)"}.get(
+                                 linears[0]["ws"].schedule()[0], "quantize_kernel + gemm_mma_kernel") + ": scan + quantise + GEMM + dequantise",
                              "frac_of_nominal": value / world / 8000.0, "nominal_peak": 8000.0,   # 8 TB/s data-sheet HBM3e
                              "bytes_per_launch": bytes_per_launch,
                              "us_per_launch": 1e3 * ms_step / len(linears)},
@@ -536,18 +537,26 @@ def _time_streams(linears, step_bytes, args, dev, n_streams):
     return step_bytes / (ms * 1e-3) / 1e9
 
 
-def _time_batched(rk, linears, step_bytes, args, stream):
+def _time_batched(rk, dom, M, linears, step_bytes, args, stream):
     """The same ring with only the dependencies a decoder layer really has: q, k and v read the same activations and
     are independent of each other, so are gate and up.  Each such set goes out as ONE launch
     (rk_npu_b200_w4a8_enqueue_batch_f16); o and down stay launches of their own.  Four launches per layer instead of
     seven, each still waiting for the one in front."""
     import torch
     layers = [linears[i:i + len(LLAMA7B_LAYER)] for i in range(0, len(linears), len(LLAMA7B_LAYER))]
+    # the batch form is the decode kernel's: workspaces of their own, scheduled on it whatever the default family is
+    own = []
+    for l in linears:
+        ws = rk.Workspace(dom, rk.default_config(M, l["N"], l["K"]))
+        if ws.set_schedule(5, 0) != 0:
+            raise RuntimeError("the decode kernel does not run this shape")
+        own.append(ws)
+    batch_ws = {id(l): ws for l, ws in zip(linears, own)}
 
     def step():
         for layer in layers:
             for group in (layer[0:3], layer[3:4], layer[4:6], layer[6:7]):    # q|k|v, o, gate|up, down
-                rc = rk.enqueue_batch_f16([l["ws"] for l in group], [l["w"] for l in group], [l["dA"] for l in group],
+                rc = rk.enqueue_batch_f16([batch_ws[id(l)] for l in group], [l["w"] for l in group], [l["dA"] for l in group],
                                           [l["dC"] for l in group], stream.cuda_stream)
                 if rc:
                     raise RuntimeError(f"batched enqueue failed: {rc}")
@@ -557,6 +566,10 @@ def _time_batched(rk, linears, step_bytes, args, stream):
     stream.synchronize()
     graph = _graph_of(torch, stream, step, not args.no_graph)
     ms = _event_time(torch, stream, (graph.replay if graph else step), args.steps)
+    for ws in own:
+        if ws.finish() != 0:
+            raise RuntimeError("device status not clean after the batched run")
+        ws.free()
     return step_bytes / (ms * 1e-3) / 1e9
 
 

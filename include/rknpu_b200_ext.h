@@ -147,14 +147,17 @@ int rk_npu_b200_w4a8_run_acc_i32(rk_npu_w4a8_workspace *workspace, const rk_npu_
  * single-kernel small-batch path, which otherwise keeps them in shared memory only. Blocking. */
 int rk_npu_b200_w4a8_last_quant(rk_npu_w4a8_workspace *workspace, float *scales, int8_t *codes);
 
-/* Scheduling override for experiments and tuning.  variant: 0 = keep, else it must equal
- * the workspace's kernel family (1 quantise + mma.sync GEMM, 2 quantise + tcgen05 GEMM,
- * 3 single-kernel small batch, 4 quantise + persistent tcgen05 streaming GEMM for up to 32
- * tokens; chosen at creation, RK_NPU_B200_VARIANT overrides where the geometry allows).
- * split_k: 0 = automatic, else the split-K factor (1..8 for family 3; 1, 2, 4, 8 for 1 and 2;
- * ignored by family 4, which balances by itself).
- * Returns RK_NPU_ERR_PARAM when the workspace geometry cannot run the request. */
+/* Scheduling override for experiments and tuning.  variant: 0 = keep, else the workspace's kernel family
+ * (1 quantise + mma.sync GEMM, 2 quantise + tcgen05 GEMM, 3 single-kernel split-K small batch, 4 quantise +
+ * persistent tcgen05 streaming GEMM, 5 single-kernel decode with whole-K CTAs; chosen at creation,
+ * RK_NPU_B200_VARIANT overrides where the geometry allows).  The family is fixed with the activation-code layout at
+ * creation, except that a workspace of up to eight tokens may move between 3 and 5, which share it.
+ * split_k: 0 = automatic, else the number of CTAs that cooperate on a column tile: the split-K factor (1..8 for
+ * family 3; 1, 2, 4, 8 for 1 and 2) or the decode kernel's cluster size (1, 2, 4, 8); ignored by family 4.
+ * Returns RK_NPU_ERR_PARAM when the workspace geometry cannot run the request.
+ * rk_npu_b200_w4a8_schedule reads both back (either pointer may be NULL). */
 int rk_npu_b200_w4a8_set_schedule(rk_npu_w4a8_workspace *workspace, int variant, int split_k);
+int rk_npu_b200_w4a8_schedule(const rk_npu_w4a8_workspace *workspace, int *variant, int *split_k);
 
 /* Diagnostics: with tracing enabled the kernels record device stamps of their latest launch.
  * Single-kernel small-batch path: eight stamps per CTA -- start (global timer, ns), then cycles

@@ -270,6 +270,7 @@ _SIGNATURES = {
     "rk_npu_b200_w4a8_run_acc_i32": (C.c_int, [_P, _P, _P, C.c_int, _P]),
     "rk_npu_b200_w4a8_last_quant": (C.c_int, [_P, _P, _P]),
     "rk_npu_b200_w4a8_set_schedule": (C.c_int, [_P, C.c_int, C.c_int]),
+    "rk_npu_b200_w4a8_schedule": (C.c_int, [_P, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "rk_npu_b200_w4a8_enqueue_f16_static": (C.c_int, [_P, _P, _P, C.c_int, _P]),
     "rk_npu_b200_w4a8_static_status": (C.c_int, [_P, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "rk_npu_b200_test_fail_allocation": (None, [C.c_longlong]),

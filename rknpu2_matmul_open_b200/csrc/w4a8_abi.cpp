@@ -976,9 +976,13 @@ rk_npu_w4a8_workspace* rkb200::create_workspace_scheduled(rk_npu_iommu_domain* d
     // tokens the tcgen05 streaming kernel (4) is opt-in: its time does not depend on the batch
     // size, but it only overtakes the ring at 32 tokens.
     const bool fused_best = fused_ok && cfg->M <= 8 && (long long)cfg->K * local_N / 2 <= (24ll << 20);
-    // Up to eight tokens: the decode kernel (5), whose CTAs own whole output channels over all of K, so a
-    // launch has a single exchange (the int8 codes inside a cluster) instead of the two of the split-K kernel (3).
+    // Up to eight tokens: the decode kernel (5), whose CTAs own whole output channels over all of K.  Up to four
+    // tokens (at most one 16-element unit to quantise per thread of a four-CTA cluster, or none to exchange at all)
+    // it beats the split-K kernel (3) on 7B-class shapes (4 tokens: 1783 against 1718 GB/s on the decode ring);
+    // from five tokens on its exchange of int8 codes costs more than the split-K kernel's exchange of row maxima
+    // and partial sums (8 tokens: 1479 against 1669 GB/s), so the split-K kernel keeps those where it applies.
     const bool decode_ok = gemm_decode_supported(cfg->M, cfg->K);
+    const bool decode_best = decode_ok && (cfg->M <= 4 || !fused_best);
     // 33..128 tokens: the per-tile tcgen05 kernel has one CTA per 128 output channels; when that is less than
     // half the SMs and K is long, the streaming kernel (all SMs, K split between CTAs) is faster.
     const bool stream_best = stream_ok && cfg->M > 32 && cfg->K >= 8192 &&
@@ -988,7 +992,7 @@ rk_npu_w4a8_workspace* rkb200::create_workspace_scheduled(rk_npu_iommu_domain* d
     // pay for combining partial tiles (11008 -> 4096 at 128 tokens: 33 us against 44 and 47 us).
     const bool ring_best = cfg->M > 32 && cfg->M <= 128 &&
                            (long long)((local_N + TILE_N - 1) / TILE_N) * ((cfg->M + 31) / 32) <= ctx->sm_count;
-    int variant = decode_ok ? 5 : ring_best ? 1 : (cfg->M > 32 && stream_best) ? 4 : (cfg->M > 32 && tc_ok) ? 2 : fused_best ? 3 : 1;
+    int variant = decode_best ? 5 : ring_best ? 1 : (cfg->M > 32 && stream_best) ? 4 : (cfg->M > 32 && tc_ok) ? 2 : fused_best ? 3 : 1;
     if (forced == 1 || (forced == 2 && tc_ok) || (forced == 3 && fused_ok) || (forced == 4 && stream_ok) || (forced == 5 && decode_ok))
         variant = forced;
     ws->variant = variant;
@@ -1007,7 +1011,7 @@ rk_npu_w4a8_workspace* rkb200::create_workspace_scheduled(rk_npu_iommu_domain* d
         ws->TC = cfg->M <= 8 ? 8 : cfg->M <= 16 ? 16 : 32;
         ws->T = ws->TC;
     }
-    if (variant == 5)
+    if (decode_ok)   // (also when another family is the default: rk_npu_b200_w4a8_set_schedule may switch to the decode kernel)
         for (int i = 0; i < 4; ++i)   // one CTA per SM at most, fewer where whole clusters do not fit
             ws->decode_cap[i] = gemm_decode_resident_ctas(1 << i, gemm_decode_smem_bytes(cfg->M, ws->KB, true, gemm_decode_ring(cfg->M, ws->KB, true)), ctx->sm_count);
     // cooperating CTAs per column tile: split-K factor of the ring and of the split-K single kernel, cluster size of the
@@ -1393,12 +1397,28 @@ extern "C" int rk_npu_b200_w4a8_last_quant(rk_npu_w4a8_workspace* ws, float* sca
 extern "C" int rk_npu_b200_w4a8_set_schedule(rk_npu_w4a8_workspace* ws, int variant, int split_k)
 {
     if (!ws || variant < 0 || variant > 5 || split_k < 0 || split_k > 8) return RK_NPU_ERR_PARAM;
-    if (ws->variant != 3 && split_k != 0 && split_k != 1 && split_k != 2 && split_k != 4 && split_k != 8) return RK_NPU_ERR_PARAM;
-    if (variant != 0 && variant != ws->variant) return RK_NPU_ERR_PARAM;   // the code layout is fixed at creation
-    if (ws->variant == 3 && split_k && (ws->KB + split_k - 1) / split_k > FUSED_MAX_STAGES) return RK_NPU_ERR_PARAM;
+    int target = variant ? variant : ws->variant;
+    if (target != ws->variant) {
+        // The code layout is fixed at creation.  The two single-kernel families for up to eight tokens share it
+        // (eight-token code tiles), so a workspace may move between them where the geometry allows both.
+        const bool single = (ws->variant == 3 || ws->variant == 5) && ws->config.M <= 8;
+        const bool to_decode = target == 5 && gemm_decode_supported(ws->config.M, ws->config.K) && ws->decode_cap[0] > 0;
+        const bool to_split = target == 3 && ws->KB <= 8 * FUSED_MAX_STAGES;
+        if (!single || !(to_decode || to_split)) return RK_NPU_ERR_PARAM;
+    }
+    if (target != 3 && split_k != 0 && split_k != 1 && split_k != 2 && split_k != 4 && split_k != 8) return RK_NPU_ERR_PARAM;
+    if (target == 3 && split_k && (ws->KB + split_k - 1) / split_k > FUSED_MAX_STAGES) return RK_NPU_ERR_PARAM;
     WorkspaceLock lock(*ws);
     if (!lock) return RK_NPU_ERR_BUSY;
+    ws->variant = target;
     ws->split_override = split_k;
+    return RK_NPU_OK;
+}
+extern "C" int rk_npu_b200_w4a8_schedule(const rk_npu_w4a8_workspace* ws, int* variant, int* split_k)
+{
+    if (!ws) return RK_NPU_ERR_PARAM;
+    if (variant) *variant = ws->variant;
+    if (split_k) *split_k = ws->split_override;
     return RK_NPU_OK;
 }
 extern "C" int rk_npu_b200_w4a8_test_starve(rk_npu_w4a8_workspace* ws, int on)

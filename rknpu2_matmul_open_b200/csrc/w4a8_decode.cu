@@ -543,22 +543,14 @@ int gemm_decode_cluster(int M, int KB)
     return units <= 768 ? 1 : 4;
 }
 
-// CTAs: at most `cap` (a multiple of the cluster size), and among the counts down to half of that the one
-// that deals the items most evenly (every CTA streams the same number of weight groups).
+// CTAs: every resident CTA that has an item to work on (a multiple of the cluster size).  A launch lasts as long as
+// its busiest CTA, ceil(items / CTAs) items, which no smaller grid improves; more CTAs bring more copy engines.
 int gemm_decode_ctas(int items, int cluster, int cap)
 {
     cap = cap / cluster * cluster;
     if (cap < cluster) cap = cluster;
     const int need = (items + cluster - 1) / cluster * cluster;
-    if (need <= cap) return need;
-    int best = cap;
-    double best_eff = 0;
-    for (int n = cap; n >= cap / 2 && n >= cluster; n -= cluster) {
-        const int per = (items + n - 1) / n;
-        const double eff = (double)items / ((double)per * n);
-        if (eff > best_eff + 1e-9) { best_eff = eff; best = n; }
-    }
-    return best;
+    return need <= cap ? need : cap;
 }
 
 template <bool HALF, bool TRACE>

@@ -220,6 +220,12 @@ class Workspace:
     def set_schedule(self, variant: int = 0, split_k: int = 0) -> int:
         return self.lib.rk_npu_b200_w4a8_set_schedule(self.handle, variant, split_k)
 
+    def schedule(self) -> tuple[int, int]:
+        """(kernel family, cooperating CTAs per column tile or 0 = automatic) this workspace runs."""
+        v, k = C.c_int(0), C.c_int(0)
+        self.lib.rk_npu_b200_w4a8_schedule(self.handle, C.byref(v), C.byref(k))
+        return v.value, k.value
+
     def launch_count(self) -> int:
         return int(self.lib.rk_npu_b200_w4a8_launch_count(self.handle))
 
