@@ -471,17 +471,24 @@ def run_cuda(args, rank, world, local_rank):
         print(json.dumps(line), flush=True)
     torch.cuda.synchronize()
     if world > 1:
-        dist.barrier()
-        torch.cuda.synchronize()
+        # Everything is measured and printed.  Communicators that captured graphs still refer to have hung in their
+        # teardown (NCCL's destroy waits for those references), so a group run ends here: the ranks meet on the
+        # host-side store (no collective, bounded wait) and leave without tearing anything down.
+        sys.stdout.flush()
+        sys.stderr.flush()
+        try:
+            store = dist.distributed_c10d._get_default_store()
+            store.add("bench_done", 1)
+            limit = time.time() + 60
+            while int(store.add("bench_done", 0)) < world and time.time() < limit:
+                time.sleep(0.05)
+        finally:
+            os._exit(0)
     for l in linears:
         l["ws"].free()
         l["w"].free()
     dom.free()
     ctx.close()
-    if world > 1:
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(0)     # the process group's teardown under captured graphs has hung at exit; everything is finished
 
 
 def _time_other_m(rk, dom, linears, M, args, dev, stream):
@@ -625,6 +632,12 @@ def _prefill(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak):
         out["published_shape_M128_K11008_N4096"] = {
             "us": ms * 1e3, "tops": 2.0 * M * K * N / (ms * 1e-3) / 1e12, "published_ms_on_rk3588": 4.0,
             "sampled_exact": bool(np.array_equal(dC.cpu().numpy().view(np.uint16)[:, cols], ref))}
+        # next row of the path: the typed W8A8 operator (int8 weights) on the same prefill shape, through its blocking
+        # call on device tensors (wall clock of the call, its stream drained inside)
+        try:
+            out["w8a8_f16_dynamic_M2048_K4096_N14336"] = _w8a8_prefill(rk, dom, dev, oracle, peak_tops)
+        except Exception as exc:
+            out["w8a8_error"] = f"{type(exc).__name__}: {exc}"
     else:
         timed = {}
         for name, fn in (("compute", lambda: ws.enqueue_local_f16(w, dA, local, stream.cuda_stream)),
@@ -639,6 +652,39 @@ def _prefill(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak):
     ws.free()
     w.free()
     return out
+
+
+def _w8a8_prefill(rk, dom, dev, oracle, peak_tops):
+    import torch
+    from rknpu2_matmul_open_b200 import w8a8
+    from rknpu2_matmul_open_b200.synthetic import make_activations, sample_columns
+    M, K, N = 2048, 4096, 14336
+    rng = np.random.default_rng(23)
+    B = rng.integers(-127, 128, size=(K, 2048), dtype=np.int8)
+    B = np.tile(B, (1, N // 2048))
+    sw = np.tile(rng.uniform(1e-3, 2e-2, size=2048).astype(np.float32), N // 2048)
+    A = make_activations(M, K, seed=23, dtype="f16")
+    w = w8a8.MatmulWeights(dom, "f16i8f16", B, sw)
+    ws = w8a8.MatmulWorkspace(dom, w8a8.default_strategy(w8a8.F16_DYNAMIC, M, N, K))
+    dA = torch.from_numpy(A.view(np.int16)).to(dev)
+    dC = torch.zeros((M, N), dtype=torch.int16, device=dev)
+    for _ in range(3):
+        if ws.run_dynamic(w, dA, dC) != 0:
+            raise RuntimeError("W8A8 run failed")
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    reps = 10
+    for _ in range(reps):
+        ws.run_dynamic(w, dA, dC)
+    sec = (time.perf_counter() - t0) / reps
+    cols = sample_columns(N)
+    ref = oracle.w8_linear(A, np.ascontiguousarray(B[:, cols]), sw[cols])
+    exact = bool(np.array_equal(dC.cpu().numpy().view(np.uint16)[:, cols], ref["out"]))
+    tops = 2.0 * M * K * N / sec / 1e12
+    ws.free()
+    w.free()
+    return {"us": sec * 1e6, "tops": tops, "sampled_exact": exact, "frac_of_measured_int8_peak": tops / peak_tops if peak_tops else None,
+            "includes": "w8_quantize_kernel + per-tile tcgen05 GEMM with int8 weights + the call's host synchronisation"}
 
 
 def _check_ffn(oracle, A, Bg, sg, Bd, sd, middle, C):
