@@ -2,11 +2,12 @@
  * library implements it, plus the configuration initialiser of include/rk_npu_matmul_i4.h.
  *
  * Built: the typed W8A8 operators with raw int8 weights (weight objects, workspaces made from a strategy, the
- * blocking run calls, the memory queries, the K-partition query), the load-only W8 tuning cache and the
- * configuration initialisers.
+ * blocking run calls, the memory queries, the K-partition query), the load-only W8 tuning cache, the exact
+ * int4 x int4 -> int32 operator of include/rk_npu_matmul_i4.h (with its producer callback) and the configuration
+ * initialisers.
  * Exported but declined (RK_NPU_ERR_PARAM, NULL or 0, nothing else happens): the W8 search tuners, their family
  * forms and cache saving; compressed (DCOMP) weight storage, which encodes for the original device's hardware
- * decompressor; the exact int4 x int4 -> int32 API; the DMA-buffer helpers of rk_npu_common.h.
+ * decompressor; the DMA-buffer helpers of rk_npu_common.h.
  * Programs may include the original headers instead of this one; names, layouts and values are the same.
  */
 #ifndef RKNPU_B200_QUANT_H
@@ -180,6 +181,43 @@ typedef struct rk_npu_i4_config {
     int cpu_threads;
 } rk_npu_i4_config;
 void rk_npu_i4_config_init(rk_npu_i4_config *cfg, int M, int N, int K);
+
+/* ---------------------------------------------------------------- exact int4 x int4 -> int32 operator
+ * include/rk_npu_matmul_i4.h:37-105.  Host codes are int8 elements in [-8,7]; codes outside that range are an argument
+ * error, never masked.  C is compact row-major int32, exact.  Weights depend only on (K, N, k_tile) and may be shared by
+ * workspaces of any M; a workspace is fixed-shape and non-reentrant (BUSY).  Configuration rules, the memory query's
+ * figures (they describe the original device's buffers) and every return code are the original's; an explicit k_tile
+ * above 480 still needs the weights to prove that no INT16 partial of the original device could saturate.  On this
+ * library the sums are accumulated in int32 directly, so nothing saturates.  A and C may also be device pointers. */
+typedef struct rk_npu_i4_timings {
+    double pack_us;    /* host: code validation, or the producer callbacks and their decoding */
+    double sync_us;    /* host-to-device copy of the activations */
+    double submit_us;  /* the two kernels and the copy of C, until the stream has drained */
+    double reduce_us;  /* always 0 here: there is no host reduction */
+    double total_us;
+} rk_npu_i4_timings;
+typedef struct rk_npu_i4i4i32_weights rk_npu_i4i4i32_weights;
+typedef struct rk_npu_i4_workspace rk_npu_i4_workspace;
+int rk_npu_i4_memory_query(const rk_npu_i4_config *cfg, rk_npu_i4_memory_info *out);
+rk_npu_i4i4i32_weights *rk_npu_i4i4i32_weights_create(rk_npu_iommu_domain *domain, const rk_npu_i4_weight_config *cfg, const int8_t *B);
+void rk_npu_i4i4i32_weights_free(rk_npu_i4i4i32_weights *weights);
+rk_npu_i4_workspace *rk_npu_i4_workspace_create(rk_npu_iommu_domain *domain, const rk_npu_i4_config *cfg);
+void rk_npu_i4_workspace_free(rk_npu_i4_workspace *workspace);
+int rk_npu_i4i4i32_run(rk_npu_i4_workspace *workspace, const rk_npu_i4i4i32_weights *weights, const int8_t *A, int32_t *C,
+                       rk_npu_i4_timings *timings);
+/* Fused preprocessing boundary: the producer is invoked serially on the calling thread for each K wave (k_tile) and M
+ * panel (m_tile), in increasing K then M order, with a zero-initialised [padded_k / 32][rows][32] int4 tile, even element
+ * in the HIGH nibble; it writes the logical codes and returns RK_NPU_OK or an error, which ends the run. */
+typedef struct rk_npu_i4_input_tile {
+    int m0, rows, k0, k, padded_k;
+    uint8_t *dst;
+    uint64_t bytes;
+} rk_npu_i4_input_tile;
+typedef int (*rk_npu_i4_input_producer)(void *user, const rk_npu_i4_input_tile *tile);
+int rk_npu_i4i4i32_run_with_producer(rk_npu_i4_workspace *workspace, const rk_npu_i4i4i32_weights *weights,
+                                     rk_npu_i4_input_producer producer, void *user, int32_t *C, rk_npu_i4_timings *timings);
+/* The reference producer: packs rows [m0, m0 + rows) x columns [k0, k0 + k) of A (leading dimension lda) into the tile. */
+int rk_npu_i4_pack_a_tile(const rk_npu_i4_input_tile *tile, const int8_t *A, int lda);
 
 #ifdef __cplusplus
 }

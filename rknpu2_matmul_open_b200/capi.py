@@ -135,6 +135,19 @@ class I4Config(C.Structure):
                 ("cpu_threads", C.c_int)]
 
 
+class I4Timings(C.Structure):
+    _fields_ = [("pack_us", C.c_double), ("sync_us", C.c_double), ("submit_us", C.c_double), ("reduce_us", C.c_double),
+                ("total_us", C.c_double)]
+
+
+class I4InputTile(C.Structure):
+    _fields_ = [("m0", C.c_int), ("rows", C.c_int), ("k0", C.c_int), ("k", C.c_int), ("padded_k", C.c_int),
+                ("dst", C.POINTER(C.c_uint8)), ("bytes", C.c_uint64)]
+
+
+I4_PRODUCER = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(I4InputTile))
+
+
 class W4A8FamilyConfig(C.Structure):
     _fields_ = [("base", W4A8AutotuneConfig), ("m_count", C.c_int), ("m_values", C.POINTER(C.c_int)),
                 ("frequencies", C.POINTER(C.c_double))]
@@ -203,6 +216,15 @@ _SIGNATURES = {
     "rk_npu_matmul_autotune_cache_load": (C.c_int, [_P, C.c_char_p, C.c_int, C.POINTER(MatmulAutotuneConfig),
                                                     C.POINTER(MatmulStrategy), C.POINTER(MatmulStrategy)]),
     "rk_npu_i4_config_init": (None, [C.POINTER(I4Config), C.c_int, C.c_int, C.c_int]),
+    # exact int4 x int4 -> int32 operator
+    "rk_npu_i4_memory_query": (C.c_int, [C.POINTER(I4Config), C.POINTER(I4MemoryInfo)]),
+    "rk_npu_i4i4i32_weights_create": (_P, [_P, C.POINTER(I4WeightConfig), _P]),
+    "rk_npu_i4i4i32_weights_free": (None, [_P]),
+    "rk_npu_i4_workspace_create": (_P, [_P, C.POINTER(I4Config)]),
+    "rk_npu_i4_workspace_free": (None, [_P]),
+    "rk_npu_i4i4i32_run": (C.c_int, [_P, _P, _P, _P, C.POINTER(I4Timings)]),
+    "rk_npu_i4i4i32_run_with_producer": (C.c_int, [_P, _P, I4_PRODUCER, _P, _P, C.POINTER(I4Timings)]),
+    "rk_npu_i4_pack_a_tile": (C.c_int, [C.POINTER(I4InputTile), _P, C.c_int]),
     # typed W8A8 operators
     "rk_npu_matmul_k_partition_query": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "rk_npu_matmul_workspace_memory_query": (C.c_int, [C.POINTER(MatmulStrategy), C.POINTER(MatmulWorkspaceRequirements)]),

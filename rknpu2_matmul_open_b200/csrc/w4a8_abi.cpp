@@ -6,6 +6,7 @@
 // Behaviour mirrors the reference operator front-end src/rk_npu_w4a8.cpp (validation
 // order :83-94, BUSY guard :70-81, run :98-159, accounting :169-207, FFN :354-380) and
 // the backend geometry rules src/rk_npu_i4_plan.cpp:14-87.
+#include "../../include/rknpu_b200_quant.h"
 #include "w4a8_tune.h"
 #include <algorithm>
 #include <cerrno>
@@ -217,6 +218,27 @@ int geometry_from(const rk_npu_w4a8_config& cfg, bool panel8, DeviceGeometry& ou
     return RK_NPU_OK;
 }
 
+} // namespace
+// The original's accounting for the exact int4 operator (rows = tokens; src/rk_npu_i4_plan.cpp:19-87), for i4_abi.cpp.
+namespace rkb200 {
+int i4_memory(const rk_npu_i4_config& cfg, rk_npu_i4_memory_info& out)
+{
+    DeviceGeometry g;
+    g.rows = cfg.M;
+    g.row_tile = cfg.m_tile;
+    g.N = cfg.N;
+    g.K = cfg.K;
+    g.k_tile = cfg.k_tile;
+    g.n_tile = cfg.n_tile;
+    g.cores = cfg.npu_core_mask;
+    g.timeout_ms = cfg.timeout_ms;
+    g.pipeline = cfg.pipeline;
+    g.threads = cfg.cpu_threads;
+    g.panel8 = false;
+    return g.memory(out);
+}
+}
+namespace {
 // ------------------------------------------------------------------ locking
 class WorkspaceLock {
 public:

@@ -123,6 +123,8 @@ __global__ void __launch_bounds__(BS, 2048 / BS) quantize_kernel(const QuantPara
     const float inv = s_inverse;
     const int mt = m / p.T, t = m - mt * p.T;
     uint4* dst = reinterpret_cast<uint4*>(p.Xq) + ((size_t)mt * chunks) * p.T + t;
+    // (the row is read a second time here, from L2: keeping it in registers between the passes needs more than the 32
+    // registers per thread that let sixteen 128-thread CTAs share an SM -- the compiler spilled it)
     for (int kc = tid; kc < chunks; kc += BS) {
         uint4 q = make_uint4(0u, 0u, 0u, 0u);
         if (kc < live_chunks) {
@@ -158,111 +160,6 @@ __global__ void __launch_bounds__(BS, 2048 / BS) quantize_kernel(const QuantPara
     }
 }
 
-// Eight tokens per CTA, one warp per token, for batches large enough to fill the GPU that way.  A row is read
-// ONCE: each lane keeps its 16-element units in registers between the maximum and the quantisation (the first
-// 256 units of a row; longer rows re-read the rest).  The maximum needs no shared memory (a warp owns the whole
-// row), and the codes leave through a shared-memory stage so that each 128-byte line of the Xq layout -- the
-// same unit of eight consecutive tokens -- is written by eight adjacent threads instead of as eight scattered
-// 16-byte pieces from eight CTAs.
-constexpr int Q8_SEGMENT = 256;   // units staged per pass: (256 + 1) x 8 tokens x 16 B = 32.1 KB
-
-template <bool HALF>
-__global__ void __launch_bounds__(256, 2) quantize_rows8_kernel(const QuantParams p)
-{
-    using T = typename ActType<HALF>::type;
-    pdl_launch_dependents();
-    pdl_wait();
-    extern __shared__ __align__(16) uint4 q8_stage[];   // [token][unit in segment], rows one unit apart in the banks
-    __shared__ int s_bad;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m0 = blockIdx.x * 8, m = m0 + warp;
-    const bool live = m < p.M;
-    const int chunks = p.Kp / 16, live_chunks = (p.K + 15) / 16;
-    const T* row = reinterpret_cast<const T*>(p.A) + (size_t)(live ? m : 0) * p.K;
-    const bool vec = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
-    constexpr int KEEP = HALF ? 8 : 4;
-    if (tid == 0) s_bad = 0;
-    Raw16<HALF> kept[KEEP];
-#pragma unroll
-    for (int i = 0; i < KEEP; ++i) {
-#pragma unroll
-        for (int j = 0; j < (HALF ? 8 : 16); ++j) kept[i].w[j] = 0u;
-        const int kc = lane + 32 * i;
-        if (live && kc < live_chunks) load_raw<HALF>(row, kc * 16, p.K, vec, kept[i]);
-    }
-    float inv = 1.f;
-    int bad = 0;
-    if (live) {
-        float maximum, s;
-        if (p.rowmax == nullptr) {
-            uint32_t bits = 0;
-#pragma unroll
-            for (int i = 0; i < KEEP; ++i) bits = max(bits, raw_maxbits<HALF>(kept[i]));
-            for (int kc = lane + 32 * KEEP; kc < live_chunks; kc += 32) {
-                Raw16<HALF> r;
-                load_raw<HALF>(row, kc * 16, p.K, vec, r);
-                bits = max(bits, raw_maxbits<HALF>(r));
-            }
-            bits = __reduce_max_sync(0xffffffffu, bits);
-            if constexpr (HALF) { bad = bits >= 0x7c00u ? 1 : 0; maximum = __half2float(__ushort_as_half((uint16_t)bits)); }
-            else { bad = bits >= 0x7f800000u ? 1 : 0; maximum = __uint_as_float(bits); }
-        } else {
-            const uint32_t bits = p.rowmax[m];
-            __syncwarp();
-            if (lane == 0) p.rowmax[m] = 0u;   // consumed: the next SwiGLU epilogue maxes into a clean word
-            bad = bits >= 0x7f800000u ? 2 : 0;
-            maximum = __uint_as_float(bits);
-        }
-        scale_from_max(maximum, bad != 0, s, inv);
-        if (lane == 0) {
-            p.scales[m] = s;
-            p.inverse[m] = inv;
-            if (p.rowmax_zero) p.rowmax_zero[m] = 0u;
-        }
-    }
-    __syncthreads();
-    if (bad && lane == 0) atomicOr(&s_bad, bad);
-    const int mt = m0 / p.T, t0 = m0 - mt * p.T;      // the eight tokens share one 128-byte line per unit
-    uint4* const dst = reinterpret_cast<uint4*>(p.Xq) + (size_t)mt * chunks * p.T + t0;
-    for (int seg0 = 0; seg0 < chunks; seg0 += Q8_SEGMENT) {
-        const int n = min(Q8_SEGMENT, chunks - seg0);
-#pragma unroll
-        for (int i = 0; i < Q8_SEGMENT / 32; ++i) {
-            const int kc = seg0 + lane + 32 * i;
-            if (kc < seg0 + n) {
-                uint4 q = make_uint4(0u, 0u, 0u, 0u);
-                if (live && kc < live_chunks) {
-                    float v[16];
-                    if (seg0 == 0 && i < KEEP) raw_to_float<HALF>(kept[i < KEEP ? i : 0], v);
-                    else { uint32_t unused = 0; load16<HALF>(row, kc * 16, p.K, vec, v, unused); }
-                    q = quantize16(v, inv, kc * 16, p.K);
-                }
-                q8_stage[warp * (Q8_SEGMENT + 1) + (kc - seg0)] = q;
-            }
-        }
-        __syncthreads();
-        for (int idx = tid; idx < n * 8; idx += 256) dst[(size_t)(seg0 + (idx >> 3)) * p.T + (idx & 7)] = q8_stage[(idx & 7) * (Q8_SEGMENT + 1) + (idx >> 3)];
-        __syncthreads();
-    }
-    if (tid == 0) {
-        // "any row bad" across CTAs without a reset pass (see quantize_kernel)
-        const int mine = s_bad;
-        if (gridDim.x == 1) {
-            p.status->bad_input = mine;
-            if (p.host_flag) *p.host_flag = mine;
-        } else {
-            if (mine) atomicOr(&p.status->bad_accum, mine);
-            __threadfence();
-            if (atomicInc(&p.status->done, gridDim.x - 1u) == gridDim.x - 1u) {
-                __threadfence();
-                const int any = atomicExch(&p.status->bad_accum, 0);
-                p.status->bad_input = any;
-                if (p.host_flag) *p.host_flag = any;
-            }
-        }
-    }
-}
-
 cudaError_t launch_quantize(const QuantParams& p, cudaStream_t stream, bool pdl)
 {
     cudaLaunchConfig_t cfg = {};
@@ -272,13 +169,6 @@ cudaError_t launch_quantize(const QuantParams& p, cudaStream_t stream, bool pdl)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    if (p.M >= 64 && p.T % 8 == 0) {
-        // eight tokens per CTA: rows read once, whole 128-byte lines written
-        cfg.gridDim = dim3((unsigned)((p.M + 7) / 8));
-        cfg.blockDim = dim3(256);
-        cfg.dynamicSmemBytes = (size_t)(Q8_SEGMENT + 1) * 8 * sizeof(uint4);
-        return p.half ? cudaLaunchKernelEx(&cfg, quantize_rows8_kernel<true>, p) : cudaLaunchKernelEx(&cfg, quantize_rows8_kernel<false>, p);
-    }
     // One CTA per token.  With many tokens the kernel is bound by how many rows are in flight, so
     // rows of up to 4096 elements get 128-thread CTAs (16 resident per SM instead of 8).
     const bool narrow = p.M >= 512 && p.K <= 4096;

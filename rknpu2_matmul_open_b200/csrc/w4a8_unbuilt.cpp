@@ -1,7 +1,6 @@
 // w4a8_unbuilt.cpp -- entry points of the original project's public headers that this library
 // does not implement: the W8 search tuners, their family forms and cache saving, and compressed (DCOMP)
-// weight storage (include/rk_npu_quant_matmul.h), the exact int4 x int4 -> int32 API
-// (include/rk_npu_matmul_i4.h), and the DMA-buffer helpers of include/rk_npu_common.h.  They are
+// weight storage (include/rk_npu_quant_matmul.h), and the DMA-buffer helpers of include/rk_npu_common.h.  They are
 // exported so that programs written against those headers link and start; each one declines: RK_NPU_ERR_PARAM, NULL, or 0, and does nothing else.
 // C linkage carries no parameter types, so the definitions take none; the callers' arguments
 // are ignored.
@@ -21,10 +20,6 @@ RKB200_DECLINE_INT(rk_npu_f32i8f32_dynamic_autotune)
 RKB200_DECLINE_INT(rk_npu_f32i8f32_dynamic_autotune_family)
 RKB200_DECLINE_INT(rk_npu_f32i8f32_static_autotune)
 RKB200_DECLINE_INT(rk_npu_f32i8f32_static_autotune_family)
-RKB200_DECLINE_INT(rk_npu_i4_memory_query)
-RKB200_DECLINE_INT(rk_npu_i4_pack_a_tile)
-RKB200_DECLINE_INT(rk_npu_i4i4i32_run)
-RKB200_DECLINE_INT(rk_npu_i4i4i32_run_with_producer)
 RKB200_DECLINE_INT(rk_npu_i8i8i32_autotune)
 RKB200_DECLINE_INT(rk_npu_i8i8i32_autotune_family)
 RKB200_DECLINE_INT(rk_npu_matmul_autotune_cache_save)
@@ -42,13 +37,9 @@ RKB200_DECLINE_PTR(rk_npu_f16i8f16_weights_create_compress)
 RKB200_DECLINE_PTR(rk_npu_f16i8f16_weights_create_from_f32_compress)
 RKB200_DECLINE_PTR(rk_npu_f32i8f32_weights_create_compress)
 RKB200_DECLINE_PTR(rk_npu_f32i8f32_weights_create_from_f32_compress)
-RKB200_DECLINE_PTR(rk_npu_i4_workspace_create)
-RKB200_DECLINE_PTR(rk_npu_i4i4i32_weights_create)
 RKB200_DECLINE_PTR(rk_npu_i8i8i32_weights_create_compress)
 
 // destructors of objects that are never created, and setters without effect
-RKB200_DECLINE_VOID(rk_npu_i4_workspace_free)
-RKB200_DECLINE_VOID(rk_npu_i4i4i32_weights_free)
 RKB200_DECLINE_VOID(rk_npu_iommu_domain_set_reclaim)
 
 RKB200_DECLINE_U64(rk_npu_f32i8f32_weights_compressed_layout_generation)

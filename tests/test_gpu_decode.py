@@ -136,6 +136,7 @@ def test_independent_linears_in_one_launch(gpu, oracle, M):
             A = make_activations(M, K, seed=K, dtype="f16")
             w.append(rk.Weights(dom, B, sw))
             ws.append(rk.Workspace(dom, rk.default_config(M, N, K)))
+            assert ws[-1].set_schedule(5, 0) == 0              # the batch form belongs to the decode kernel
             dA.append(torch.from_numpy(A.view(np.int16)).cuda())
             dC.append(torch.full((M, N), 0x5555, dtype=torch.int16, device="cuda"))
             ref.append(oracle.linear(A, B, sw)[1])
@@ -151,6 +152,7 @@ def test_independent_linears_in_one_launch(gpu, oracle, M):
         assert rk.enqueue_batch_f16([ws[0], ws[0]], [w[0], w[0]], [dA[0], dA[0]], [dC[0], dC[0]], stream.cuda_stream) == capi.RK_NPU_ERR_PARAM
         if M < 8:
             other = rk.Workspace(dom, rk.default_config(M + 1, shapes[0][1], shapes[0][0]))
+            assert other.set_schedule(5, 0) == 0
             dA2 = torch.zeros((M + 1, shapes[0][0]), dtype=torch.int16, device="cuda")
             dC2 = torch.zeros((M + 1, shapes[0][1]), dtype=torch.int16, device="cuda")
             if len(ws) > 1:

@@ -287,12 +287,12 @@ def test_every_entry_point_of_the_original_headers_links(lib):
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, missing
     # operators that are not built decline instead of pretending
-    for name in ("rk_npu_i8i8i32_autotune", "rk_npu_f16i8f16_dynamic_autotune_family", "rk_npu_i4i4i32_run",
+    for name in ("rk_npu_i8i8i32_autotune", "rk_npu_f16i8f16_dynamic_autotune_family",
                  "rk_npu_matmul_autotune_cache_save", "rk_npu_mem_alloc"):
         fn = C.CDLL(str(capi.LIB_PATH))[name]
         fn.restype, fn.argtypes = C.c_int, []
         assert fn() == capi.RK_NPU_ERR_PARAM, name
-    for name in ("rk_npu_i8i8i32_weights_create_compress", "rk_npu_f16i8f16_weights_create_from_f32_compress", "rk_npu_i4_workspace_create"):
+    for name in ("rk_npu_i8i8i32_weights_create_compress", "rk_npu_f16i8f16_weights_create_from_f32_compress"):
         fn = C.CDLL(str(capi.LIB_PATH))[name]
         fn.restype, fn.argtypes = C.c_void_p, []
         assert fn() is None, name
@@ -301,6 +301,9 @@ def test_every_entry_point_of_the_original_headers_links(lib):
     assert lib.rk_npu_f16i8f16_run_static(None, None, None, None, None) == capi.RK_NPU_ERR_PARAM
     assert lib.rk_npu_matmul_workspace_create(None, None) is None
     assert lib.rk_npu_f32i8f32_weights_create(None, None, None, None) is None
+    # so is the exact int4 operator
+    assert lib.rk_npu_i4i4i32_run(None, None, None, None, None) == capi.RK_NPU_ERR_PARAM
+    assert lib.rk_npu_i4_workspace_create(None, None) is None and lib.rk_npu_i4i4i32_weights_create(None, None, None) is None
     # the search tuners are built: argument errors are answered as such, without a device
     fast = capi.W4A8Strategy()
     assert lib.rk_npu_w4a8_autotune(None, None, None, None, C.byref(fast), None) == capi.RK_NPU_ERR_PARAM
@@ -456,3 +459,47 @@ def test_public_headers_are_valid_c(tmp_path):
     out = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", f"-I{ROOT / 'include'}",
                           str(src)], capture_output=True, text=True)
     assert out.returncode == 0, out.stderr
+
+
+# ---------------------------------------------------------------- exact int4 operator: pure host functions
+def test_i4_memory_query_and_tile_packing_match_the_reference(lib):
+    from oracle.harness import REF_SO, Reference
+    if not Reference.available():
+        pytest.skip("reference checker not built")
+    ref = C.CDLL(str(REF_SO))
+    rng = np.random.default_rng(4)
+    cases = [(1, 64, 32, 1, 32, 64, 1, 1, 1), (128, 4096, 4096, 128, 480, 1024, 7, 1, 4), (33, 1000, 513, 16, 2048, 8128, 3, 0, 2),
+             (5, 64, 40, 129, 480, 1024, 1, 1, 1), (5, 64, 40, 8, 481, 1024, 1, 1, 1), (5, 64, 40, 8, 480, 100, 1, 1, 1),
+             (5, 64, 40, 8, 480, 64, 3, 1, 1), (5, 64, 40, 8, 480, 64, 1, 2, 1), (5, 64, 40, 8, 480, 64, 1, 1, 5), (0, 64, 40, 8, 480, 64, 1, 1, 1)]
+    for _ in range(200):
+        cases.append((int(rng.integers(1, 600)), int(rng.integers(1, 9000)), int(rng.integers(1, 9000)), int(rng.integers(1, 140)),
+                      int(rng.integers(1, 70)) * 32, int(rng.integers(1, 130)) * 64, int(rng.choice([1, 2, 4, 3, 7, 5])),
+                      int(rng.integers(0, 2)), int(rng.integers(1, 5))))
+    for (M, N, K, mt, kt, nt, mask, pipe, thr) in cases:
+        cfg = capi.I4Config(M, N, K, mt, kt, nt, mask, 500, pipe, thr)
+        a, b = capi.I4MemoryInfo(), capi.I4MemoryInfo()
+        ra = lib.rk_npu_i4_memory_query(C.byref(cfg), C.byref(a))
+        rb = ref.rk_npu_i4_memory_query(C.byref(cfg), C.byref(b))
+        assert ra == rb, (M, N, K, mt, kt, nt, mask, pipe, thr)
+        if ra == 0:
+            assert bytes(a) == bytes(b)
+    # the reference producer helper: same bytes, same verdicts
+    M, K = 37, 300
+    A = rng.integers(-8, 8, size=(M, K), dtype=np.int8)
+    for (m0, rows, k0, k) in [(0, 37, 0, 300), (5, 16, 32, 200), (36, 1, 288, 12), (0, 128, 0, 10)]:
+        padded = (k + 31) // 32 * 32
+        outs = []
+        for L in (lib, ref):
+            buf = np.full(max(rows, 1) * padded // 2 + 8, 0x5A, np.uint8)
+            tile = capi.I4InputTile(m0, rows, k0, k, padded, buf.ctypes.data_as(C.POINTER(C.c_uint8)), rows * padded // 2)
+            fn = L.rk_npu_i4_pack_a_tile
+            fn.restype, fn.argtypes = C.c_int, [C.POINTER(capi.I4InputTile), C.c_void_p, C.c_int]
+            rc = fn(C.byref(tile), A.ctypes.data, K) if m0 + rows <= M else capi.RK_NPU_ERR_PARAM
+            outs.append((rc, buf.copy()))
+        assert outs[0][0] == outs[1][0] and np.array_equal(outs[0][1], outs[1][1]), (m0, rows, k0, k)
+    bad = A.copy()
+    bad[3, 17] = 8
+    buf = np.zeros(M * 320 // 2, np.uint8)
+    tile = capi.I4InputTile(0, M, 0, K, 320, buf.ctypes.data_as(C.POINTER(C.c_uint8)), M * 320 // 2)
+    assert lib.rk_npu_i4_pack_a_tile(C.byref(tile), bad.ctypes.data, K) == capi.RK_NPU_ERR_PARAM
+    assert lib.rk_npu_i4_pack_a_tile(C.byref(tile), A.ctypes.data, K - 1) == capi.RK_NPU_ERR_PARAM       # lda too small
