@@ -889,9 +889,12 @@ def _print_stamps(rk, case, calls, stream, torch):
         print(f"graph replay: {ms * 1e3:.1f} us per set of {len(calls)} linears")
     if case == "decode":
         prev_end = None
-        print("per linear, ns relative to the previous linear's last CTA end: first/last CTA start, first/last CTA end;"
-              " then median cycles since CTA start at: before the dependency wait, dependency met, share"
-              " quantised and sent, all codes landed, last contraction done, last output stored")
+        family = calls[0][1].schedule()[0]
+        phases = ("before the dependency wait, dependency met, share quantised and sent, all codes landed, last contraction done,"
+                  " last output stored" if family == 5 else
+                  "weights requested, dependency met, scales known, slice quantised, contraction done, partial sums exchanged")
+        print(f"kernel family {family}; per linear, ns relative to the previous linear's last CTA end: first/last CTA start,"
+              f" first/last CTA end; then median cycles since CTA start at: {phases}")
         for i, (_, ws) in enumerate(calls):
             buf = np.zeros((4112, 8), np.uint64)
             lib.rk_npu_b200_w4a8_trace_read(ws.handle, buf.ctypes.data, 4112)
@@ -905,8 +908,9 @@ def _print_stamps(rk, case, calls, stream, torch):
             ref = prev_end if prev_end is not None else s0
             cyc = [int(x) for x in np.median(v[:, 1:7], axis=0)]
             print(f"linear {i}: K={ws.cfg.K} N={ws.cfg.N} ctas={len(v)} start[{s0 - ref},{s1 - ref}] end[{e0 - ref},{e1 - ref}] cycles {cyc}")
-            print(f"   CTA 0, cycles since its start: loads issued, own maxima in, row maxima known, share quantised: {[int(x) for x in scan]};"
-                  f" first weight stages (wait begins, wait ends): {[int(x) for x in stages]}")
+            if family == 5:
+                print(f"   CTA 0, cycles since its start: loads issued, own maxima in, row maxima known, share quantised: {[int(x) for x in scan]};"
+                      f" first weight stages (wait begins, wait ends): {[int(x) for x in stages]}")
             prev_end = e1
     elif case == "prefill":
         raw = np.zeros(256, np.uint64)

@@ -76,6 +76,39 @@ __device__ __forceinline__ int red_index(int warp, int rows, int row, int tok)
     return (warp * rows + row) * 8 + (tok ^ ((row >> 2) & 7));
 }
 
+// Rows longer than a thread's register budget (more than UMAX units per thread): the remaining units are scanned and
+// later quantised by these two routines, from memory.  Out of line: the shapes the kernel is tuned for never get here,
+// and inlined they were a fifth of the kernel's instruction stream.
+template <bool HALF>
+static __device__ __noinline__ void scan_rest(const typename ActType<HALF>::type* A, int K, bool vec, int first, int scan_items, int TQ, int su0,
+                                              int sn, int t0, int M, uint32_t* s_max)
+{
+    for (int idx = first; idx < scan_items; idx += DEC_WARPS * 32) {
+        const int tl = TQ > 1 ? idx / sn : 0, u = su0 + idx - tl * sn;
+        if (t0 + tl < M && u * 16 < K) {
+            Raw16<HALF> r;
+            load_raw<HALF>(A + (size_t)(t0 + tl) * K, u * 16, K, vec, r);
+            atomicMax(&s_max[tl], raw_maxbits<HALF>(r));
+        }
+    }
+}
+template <bool HALF>
+static __device__ __noinline__ void quantize_rest(const typename ActType<HALF>::type* A, int K, bool vec, int first, int scan_items, int TQ,
+                                                  int su0, int sn, int t0, int M, int pu0, int pu1, const float* s_inv, uint8_t* xs,
+                                                  int row_bytes, uint8_t* codes_out)
+{
+    for (int idx = first; idx < scan_items; idx += DEC_WARPS * 32) {
+        const int tl = TQ > 1 ? idx / sn : 0, u = su0 + idx - tl * sn;
+        if (t0 + tl < M && u >= pu0 && u < pu1) {
+            Raw16<HALF> r;
+            load_raw<HALF>(A + (size_t)(t0 + tl) * K, u * 16, K, vec, r);
+            const uint4 q = quantize_unit<HALF>(r, s_inv[tl], u * 16, K);
+            *reinterpret_cast<uint4*>(xs + (size_t)(t0 + tl) * row_bytes + (size_t)u * 16) = q;
+            if (codes_out) reinterpret_cast<uint4*>(codes_out)[(size_t)u * 8 + t0 + tl] = q;
+        }
+    }
+}
+
 // One CTA of one linear: `cta` of `nctas` (the kernels below map the grid onto one or several linears).
 // The CTA's path between "the activations exist" and "the outputs are stored" is a chain of short phases run by
 // nine warps, so it is bound by instruction latency and issue slots, not memory: the code avoids integer
@@ -197,17 +230,6 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     const bool vec = (reinterpret_cast<uintptr_t>(A) & 15u) == 0 && (p.K % (HALF ? 8 : 4)) == 0;
     constexpr int UMAX = HALF ? 3 : 2;     // units a thread keeps in registers between the scan and the quantisation
     constexpr int CT = DEC_WARPS * 32;
-    // The rows this CTA will read, pulled towards L2 while the launch in front still runs.  A prefetch is only a
-    // hint: the L2 is the point of coherence, so whatever the producer still writes is what the loads below see.
-    {
-        constexpr int per_line = HALF ? 4 : 2;      // 16-element units per 128-byte line
-        for (int idx = tid * per_line; idx < scan_items; idx += CT * per_line) {
-            int tl, u;
-            locate(idx, tl, u);
-            if (t0 + tl < M && u * 16 < p.K)
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(A) + ((size_t)(t0 + tl) * p.K + (size_t)u * 16) * sizeof(AT)));
-        }
-    }
     // Everything that does not need the activations is settled before the wait: where this thread's units lie (no
     // division behind the dependency) and the time limit (reading the global timer is slow; the few microseconds the
     // launch in front still runs are charged to this launch's limit).
@@ -220,6 +242,10 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
         pos_u[it] = 0;
         if (idx < scan_items) locate(idx, pos_tl[it], pos_u[it]);
         pos_live[it] = idx < scan_items && t0 + pos_tl[it] < M;
+        // The unit this thread will read, pulled towards L2 while the launch in front still runs.  A prefetch is only
+        // a hint: the L2 is the point of coherence, so whatever the producer still writes is what the load sees.
+        if (pos_live[it] && pos_u[it] * 16 < p.K)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(A) + ((size_t)(t0 + pos_tl[it]) * p.K + (size_t)pos_u[it] * 16) * sizeof(AT)));
     }
     const unsigned long long deadline = global_ns() + p.timeout_ns;
     if (TRACE && trace) trace[1] = (unsigned long long)(clock64() - c_start);
@@ -245,25 +271,16 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
 #pragma unroll
         for (int it = 0; it < UMAX; ++it) {
             const int tl = pos_tl[it];
-            uint32_t bits = raw_maxbits<HALF>(kept[it]);    // units never loaded hold zeros
-            // a warp whose 32 units belong to one token reduces first and issues a single shared atomic
-            // (every warp-wide operation below is executed by all 32 lanes: none sits behind a per-lane condition)
+            const uint32_t bits = raw_maxbits<HALF>(kept[it]);    // units never loaded hold zeros
+            // a warp whose 32 units belong to one token reduces first and issues a single shared atomic; one code
+            // path for both cases (every warp-wide operation is executed by all 32 lanes, none behind a lane condition)
             const int tl0 = __shfl_sync(0xffffffffu, tl, 0);
-            const bool one_token = TQ == 1 || __all_sync(0xffffffffu, tl == tl0);
-            if (one_token) {
-                bits = __reduce_max_sync(0xffffffffu, bits);
-                if (lane == 0 && bits) atomicMax(&s_max[tl0], bits);
-            } else if (bits) atomicMax(&s_max[tl], bits);
+            const bool uniform = TQ == 1 || __all_sync(0xffffffffu, tl == tl0);
+            const uint32_t reduced = __reduce_max_sync(0xffffffffu, bits);
+            const uint32_t mine = uniform ? reduced : bits;
+            if ((!uniform || lane == 0) && mine) atomicMax(&s_max[uniform ? tl0 : tl], mine);
         }
-        for (int idx = tid + CT * UMAX; idx < scan_items; idx += CT) {
-            int tl, u;
-            locate(idx, tl, u);
-            if (t0 + tl < M && u * 16 < p.K) {
-                Raw16<HALF> r;
-                load_raw<HALF>(A + (size_t)(t0 + tl) * p.K, u * 16, p.K, vec, r);
-                atomicMax(&s_max[tl], raw_maxbits<HALF>(r));
-            }
-        }
+        if (scan_items > CT * UMAX) scan_rest<HALF>(A, p.K, vec, tid + CT * UMAX, scan_items, TQ, su0, sn, t0, M, s_max);
         stamp(65);
         bar_sync_contraction();
     }
@@ -307,22 +324,11 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
 #pragma unroll
     for (int it = 0; it < UMAX; ++it) {
         const int tl = pos_tl[it], u = pos_u[it];
-        if (pos_live[it] && u >= pu0 && u < pu1) {
-            float v[16];
-            raw_to_float<HALF>(kept[it], v);
-            keep_code(t0 + tl, u, quantize16(v, s_inv[tl], u * 16, p.K));
-        }
+        if (pos_live[it] && u >= pu0 && u < pu1) keep_code(t0 + tl, u, quantize_unit<HALF>(kept[it], s_inv[tl], u * 16, p.K));
     }
-    for (int idx = tid + CT * UMAX; idx < scan_items; idx += CT) {
-        int tl, u;
-        locate(idx, tl, u);
-        if (t0 + tl < M && u >= pu0 && u < pu1) {
-            float v[16];
-            uint32_t unused = 0;
-            load16<HALF>(A + (size_t)(t0 + tl) * p.K, u * 16, p.K, vec, v, unused);
-            keep_code(t0 + tl, u, quantize16(v, s_inv[tl], u * 16, p.K));
-        }
-    }
+    if (scan_items > CT * UMAX)
+        quantize_rest<HALF>(A, p.K, vec, tid + CT * UMAX, scan_items, TQ, su0, sn, t0, M, pu0, pu1, s_inv, xs, row_bytes,
+                            (p.codes_out && first_cluster) ? p.codes_out : nullptr);
     stamp(67);
     bool failed = false;
     if (S > 1) {
@@ -371,14 +377,10 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     };
     for (int j = 0; j < my_items; ++j) {
         const int item = (int)cta + j * ncta;
-        int acc[2][2][4];                                 // [gate | up][m16 tile][fragment]
-#pragma unroll
-        for (int g = 0; g < 2; ++g) {
-#pragma unroll
-            for (int m = 0; m < 2; ++m)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) acc[g][m][e] = 0;
-            if (g >= gpi) continue;
+        // One pass per weight group of the item (gate, then up for SwiGLU): a run-time loop, so that the stage loop
+        // exists once in the instruction stream; a pass leaves its partial sums in the scratch rows of its group.
+#pragma unroll 1
+        for (int g = 0; g < gpi; ++g) {
             // four accumulator sets: four of a warp's chunks of a stage are independent MMAs, so their loads and the
             // latency of the MMAs overlap
             int a[4][2][4];
@@ -433,18 +435,11 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
 #pragma unroll
             for (int m = 0; m < 2; ++m)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) acc[g][m][e] = (a[0][m][e] + a[1][m][e]) + (a[2][m][e] + a[3][m][e]);
+                for (int e = 0; e < 4; ++e)
+                    red[red_index(warp, rows, g * 32 + m * 16 + g8 + (e >> 1) * 8, 2 * t4 + (e & 1))] =
+                        (a[0][m][e] + a[1][m][e]) + (a[2][m][e] + a[3][m][e]);
         }
         if (TRACE && trace && j == my_items - 1) trace[5] = (unsigned long long)(clock64() - c_start);
-#pragma unroll
-        for (int g = 0; g < 2; ++g) {
-            if (g >= gpi) continue;
-#pragma unroll
-            for (int m = 0; m < 2; ++m)
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    red[red_index(warp, rows, g * 32 + m * 16 + g8 + (e >> 1) * 8, 2 * t4 + (e & 1))] = acc[g][m][e];
-        }
         // ---- sum the warps' partial sums, dequantise, store
         bar_sync_contraction();
         const float ca = sw_a, cb = sw_b;

@@ -108,12 +108,9 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
     };
     if (tid < 4 && nkb > 0) request_weights(tile_first, &full[1]);
     stage_channel_scales(tile_first);
-    if (trace) trace[1] = (unsigned long long)(clock64() - c_start);
-    pdl_wait();   // the producer of A (and of the row maxima) has finished
-    if (trace) trace[2] = (unsigned long long)(clock64() - c_start);
-
     // ---- 1. row maxima over this CTA's K slice.  Work item = (token, 16-element unit);
-    // the first UMAX items of a thread stay in registers for the quantisation pass.
+    // the first UMAX items of a thread stay in registers for the quantisation pass.  Where they lie is
+    // settled before the dependency wait, so that no integer division sits between "A exists" and the loads.
     const int k_begin = kb0 * KBLOCK;
     const int units = nkb * 8;                          // 16-element units per token in the slice
     const AT* A = reinterpret_cast<const AT*>(p.A);
@@ -122,10 +119,20 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
     Raw16<HALF> kept[UMAX];
     const int items = TC * units;
     const bool warp_one_token = (units & 31) == 0;
+    int pos_tok[UMAX], pos_u[UMAX];
 #pragma unroll
     for (int it = 0; it < UMAX; ++it) {
         const int idx = tid + FUSED_THREADS * it;
-        const int tok = idx / units, u = idx - tok * units;
+        pos_tok[it] = units > 0 ? idx / units : 0;
+        pos_u[it] = idx - pos_tok[it] * units;
+    }
+    if (trace) trace[1] = (unsigned long long)(clock64() - c_start);
+    pdl_wait();   // the producer of A (and of the row maxima) has finished
+    if (trace) trace[2] = (unsigned long long)(clock64() - c_start);
+#pragma unroll
+    for (int it = 0; it < UMAX; ++it) {
+        const int idx = tid + FUSED_THREADS * it;
+        const int tok = pos_tok[it], u = pos_u[it];
         const int k0 = k_begin + u * 16;
 #pragma unroll
         for (int i = 0; i < (HALF ? 8 : 16); ++i) kept[it].w[i] = 0u;
@@ -202,10 +209,8 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
         for (int it = 0; it < UMAX; ++it) {
             const int idx = tid + FUSED_THREADS * it;
             if (idx < items) {
-                const int tok = idx / units, u = idx - tok * units;
-                float v[16];
-                raw_to_float<HALF>(kept[it], v);
-                const uint4 q = quantize16(v, s_inv[tok], k_begin + u * 16, p.K);   // padding rows hold zeros
+                const int tok = pos_tok[it], u = pos_u[it];
+                const uint4 q = quantize_unit<HALF>(kept[it], s_inv[tok], k_begin + u * 16, p.K);   // padding rows hold zeros
                 reinterpret_cast<uint4*>(xs)[(size_t)u * TC + tok] = q;
                 if (p.codes_out && blockIdx.x == 0) reinterpret_cast<uint4*>(p.codes_out)[((size_t)kb0 * 8 + u) * TC + tok] = q;
             }
@@ -215,10 +220,9 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
             const int k0 = k_begin + u * 16;
             uint4 q = make_uint4(0u, 0u, 0u, 0u);
             if (tok < p.M && k0 < p.K) {
-                float v[16];
-                uint32_t unused = 0;
-                load16<HALF>(A + (size_t)tok * p.K, k0, p.K, vec, v, unused);
-                q = quantize16(v, s_inv[tok], k0, p.K);
+                Raw16<HALF> r;
+                load_raw<HALF>(A + (size_t)tok * p.K, k0, p.K, vec, r);
+                q = quantize_unit<HALF>(r, s_inv[tok], k0, p.K);
             }
             reinterpret_cast<uint4*>(xs)[(size_t)u * TC + tok] = q;
             if (p.codes_out && blockIdx.x == 0) reinterpret_cast<uint4*>(p.codes_out)[((size_t)kb0 * 8 + u) * TC + tok] = q;
@@ -253,18 +257,18 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
     // The copies have to land before this CTA may leave, whatever the verdict.
     if (nkb > 0 && !mbar_wait(&full[1 + ti], 0, deadline)) s_flags[1] = 1;
     for (int s = 0; s < (verdict ? 0 : nkb); ++s) {
-        const uint32_t wbase = smem_u32(wst + ((size_t)wgroup * nkb + s) * 2048) + (mtile * 16 + g8) * 16 + t4 * 4;
-        const uint32_t xbase = smem_u32(xs + (size_t)s * TC * 128) + g8 * 16 + t4 * 4;
+        const uint32_t* const wbase = reinterpret_cast<const uint32_t*>(wst + ((size_t)wgroup * nkb + s) * 2048 + (mtile * 16 + g8) * 16) + t4;
+        const uint32_t* const xbase = reinterpret_cast<const uint32_t*>(xs + (size_t)s * TC * 128 + g8 * 16) + t4;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const uint32_t w0 = lds32(wbase + c * 512);
-            const uint32_t w1 = lds32(wbase + c * 512 + 128);
+            const uint32_t w0 = wbase[c * 128];
+            const uint32_t w1 = wbase[c * 128 + 32];
             const uint32_t a0 = (w0 << 4) & 0xF0F0F0F0u, a1 = (w1 << 4) & 0xF0F0F0F0u;
             const uint32_t a2 = w0 & 0xF0F0F0F0u, a3 = w1 & 0xF0F0F0F0u;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                const uint32_t b0 = lds32(xbase + ((2 * c) * TC + 8 * j) * 16);
-                const uint32_t b1 = lds32(xbase + ((2 * c + 1) * TC + 8 * j) * 16);
+                const uint32_t b0 = xbase[((2 * c) * TC + 8 * j) * 4];
+                const uint32_t b1 = xbase[((2 * c + 1) * TC + 8 * j) * 4];
                 // two accumulator sets halve the chain of dependent MMAs (integer sums: any order is exact)
                 if (c & 1) mma_s8(acc2[j], a0, a1, a2, a3, b0, b1);
                 else mma_s8(acc[j], a0, a1, a2, a3, b0, b1);

@@ -16,33 +16,48 @@ template <> struct ActType<false> { using type = float; };
 // elements at or beyond K read as zero.  `vec` says the row allows 16-byte loads.
 template <bool HALF> struct Raw16 { uint32_t w[HALF ? 8 : 16]; };
 
+// The element-by-element form (rows that do not allow 16-byte loads, the unit that straddles K) is kept out of line:
+// the kernels are straight-line code executed once per launch, so every inlined copy of a rare path is instruction
+// fetch on the critical path.
+// (returns four words at a time: a vector return value stays in registers, a reference to the caller's unit would
+// force that unit into local memory)
+template <bool HALF>
+__device__ __noinline__ uint4 load_words_ragged(const typename ActType<HALF>::type* row, int k0, int K)
+{
+    uint32_t w[4];
+    if constexpr (HALF) {
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t lo = (k0 + 2 * i < K) ? row[k0 + 2 * i] : 0u;
+            const uint32_t hi = (k0 + 2 * i + 1 < K) ? row[k0 + 2 * i + 1] : 0u;
+            w[i] = lo | (hi << 16);
+        }
+    } else {
+        for (int i = 0; i < 4; ++i) w[i] = (k0 + i < K) ? __float_as_uint(row[k0 + i]) : 0u;
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
 template <bool HALF>
 __device__ __forceinline__ void load_raw(const typename ActType<HALF>::type* row, int k0, int K, bool vec, Raw16<HALF>& r)
 {
-    if constexpr (HALF) {
-        if (vec && k0 + 16 <= K) {
+    if (vec && k0 + 16 <= K) {
+        if constexpr (HALF) {
             const uint4 a = *reinterpret_cast<const uint4*>(row + k0);
             const uint4 b = *reinterpret_cast<const uint4*>(row + k0 + 8);
             r.w[0] = a.x; r.w[1] = a.y; r.w[2] = a.z; r.w[3] = a.w;
             r.w[4] = b.x; r.w[5] = b.y; r.w[6] = b.z; r.w[7] = b.w;
         } else {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t lo = (k0 + 2 * i < K) ? row[k0 + 2 * i] : 0u;
-                const uint32_t hi = (k0 + 2 * i + 1 < K) ? row[k0 + 2 * i + 1] : 0u;
-                r.w[i] = lo | (hi << 16);
-            }
-        }
-    } else {
-        if (vec && k0 + 16 <= K) {
-#pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const uint4 f = *reinterpret_cast<const uint4*>(row + k0 + 4 * i);
                 r.w[4 * i] = f.x; r.w[4 * i + 1] = f.y; r.w[4 * i + 2] = f.z; r.w[4 * i + 3] = f.w;
             }
-        } else {
+        }
+    } else {
+        constexpr int per = HALF ? 8 : 4;      // elements per four words
 #pragma unroll
-            for (int i = 0; i < 16; ++i) r.w[i] = (k0 + i < K) ? __float_as_uint(row[k0 + i]) : 0u;
+        for (int i = 0; i < (HALF ? 2 : 4); ++i) {
+            const uint4 f = load_words_ragged<HALF>(row, k0 + per * i, K);
+            r.w[4 * i] = f.x; r.w[4 * i + 1] = f.y; r.w[4 * i + 2] = f.z; r.w[4 * i + 3] = f.w;
         }
     }
 }
@@ -183,25 +198,63 @@ __device__ __forceinline__ uint32_t quantize4(float y0, float y1, float y2, floa
     const uint32_t x = n ^ sgn;
     return (((x & 0x7F7F7F7Fu) + (sgn & 0x01010101u)) ^ (x & 0x80808080u));
 }
+// the unit that straddles K: elements at or beyond K are zero codes (out of line; the values travel as vector arguments
+// so that the caller's array stays in registers)
+static __device__ __noinline__ uint4 quantize16_ragged(float4 a, float4 b, float4 c, float4 d, float inv, int k0, int K)
+{
+    const float v[16] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w, c.x, c.y, c.z, c.w, d.x, d.y, d.z, d.w};
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        int q[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) q[i] = (k0 + 4 * j + i < K) ? round_clamp(__fmul_rn(v[4 * j + i], inv)) : 0;
+        w[j] = __byte_perm(__byte_perm((uint32_t)q[0], (uint32_t)q[1], 0x0040), __byte_perm((uint32_t)q[2], (uint32_t)q[3], 0x0040), 0x5410);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
 // 16 activations -> 16 int8 codes packed in four words (ties away from zero; |code| <= 127 by the scale's construction).
 __device__ __forceinline__ uint4 quantize16(const float (&v)[16], float inv, int k0, int K)
 {
+    if (k0 + 16 > K)
+        return quantize16_ragged(make_float4(v[0], v[1], v[2], v[3]), make_float4(v[4], v[5], v[6], v[7]), make_float4(v[8], v[9], v[10], v[11]),
+                                 make_float4(v[12], v[13], v[14], v[15]), inv, k0, K);
     uint32_t w[4];
-    if (k0 + 16 <= K) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            w[j] = quantize4(__fmul_rn(v[4 * j], inv), __fmul_rn(v[4 * j + 1], inv), __fmul_rn(v[4 * j + 2], inv), __fmul_rn(v[4 * j + 3], inv));
-    } else {
-        // the unit that straddles K: elements at or beyond K are zero codes
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            int q[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) q[i] = (k0 + 4 * j + i < K) ? round_clamp(__fmul_rn(v[4 * j + i], inv)) : 0;
-            w[j] = __byte_perm(__byte_perm((uint32_t)q[0], (uint32_t)q[1], 0x0040), __byte_perm((uint32_t)q[2], (uint32_t)q[3], 0x0040), 0x5410);
-        }
-    }
+    for (int j = 0; j < 4; ++j)
+        w[j] = quantize4(__fmul_rn(v[4 * j], inv), __fmul_rn(v[4 * j + 1], inv), __fmul_rn(v[4 * j + 2], inv), __fmul_rn(v[4 * j + 3], inv));
     return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// One 16-element unit from its raw words to int8 codes.  Out of line on purpose: a thread calls it up to three times
+// (plus the tail loop), and four inlined copies of ~130 instructions are fetched once each on the critical path.
+static __device__ __noinline__ uint4 quantize_words_half(uint4 lo, uint4 hi, float inv, int k0, int K)
+{
+    Raw16<true> raw;
+    raw.w[0] = lo.x; raw.w[1] = lo.y; raw.w[2] = lo.z; raw.w[3] = lo.w;
+    raw.w[4] = hi.x; raw.w[5] = hi.y; raw.w[6] = hi.z; raw.w[7] = hi.w;
+    float v[16];
+    raw_to_float<true>(raw, v);
+    return quantize16(v, inv, k0, K);
+}
+static __device__ __noinline__ uint4 quantize_words_float(uint4 a, uint4 b, uint4 c, uint4 d, float inv, int k0, int K)
+{
+    const float v[16] = {__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w),
+                         __uint_as_float(b.x), __uint_as_float(b.y), __uint_as_float(b.z), __uint_as_float(b.w),
+                         __uint_as_float(c.x), __uint_as_float(c.y), __uint_as_float(c.z), __uint_as_float(c.w),
+                         __uint_as_float(d.x), __uint_as_float(d.y), __uint_as_float(d.z), __uint_as_float(d.w)};
+    return quantize16(v, inv, k0, K);
+}
+// (the words travel as vector arguments, which the calling convention keeps in registers; a struct would go through
+// the stack)
+template <bool HALF>
+__device__ __forceinline__ uint4 quantize_unit(const Raw16<HALF>& r, float inv, int k0, int K)
+{
+    if constexpr (HALF)
+        return quantize_words_half(make_uint4(r.w[0], r.w[1], r.w[2], r.w[3]), make_uint4(r.w[4], r.w[5], r.w[6], r.w[7]), inv, k0, K);
+    else
+        return quantize_words_float(make_uint4(r.w[0], r.w[1], r.w[2], r.w[3]), make_uint4(r.w[4], r.w[5], r.w[6], r.w[7]),
+                                    make_uint4(r.w[8], r.w[9], r.w[10], r.w[11]), make_uint4(r.w[12], r.w[13], r.w[14], r.w[15]), inv, k0, K);
 }
 
 } // namespace rkb200
