@@ -289,18 +289,28 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
     if (trace) trace[5] = (unsigned long long)(clock64() - c_start);
     // ---- 4. partial sums to the rank that owns the channel: inbox_sum[source][token][W]
     if (!verdict) {
+        // A thread's fragment holds two channels (rows g8 and g8 + 8 of its m16 tile); who finishes each of them and
+        // where it lands there is worked out once per channel, with a shift for the quad count (16 or 32).
+        int owner2[2], local2[2];
+        uint32_t dst_bar[2];
+        const int lq = swiglu ? 4 : 5;                                  // log2(Q)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int ch = wgroup * 32 + mtile * 16 + g8 + h * 8;
+            const int c = swiglu ? (ch & 63) : ch;
+            owner2[h] = ((((c >> 2) + 1) * S + Q - 1) >> lq) - 1;
+            local2[h] = c - ((owner2[h] * Q) / S) * 4 + ((swiglu && ch >= 64) ? QW * 4 : 0);
+            dst_bar[h] = S > 1 ? map_to_cta(smem_u32(&full[3 + ti]), (uint32_t)owner2[h]) : 0u;
+        }
 #pragma unroll
         for (int j = 0; j < NT; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int ch = wgroup * 32 + mtile * 16 + g8 + (e >> 1) * 8;
+                const int h = e >> 1;
                 const int tok = 8 * j + 2 * t4 + (e & 1);
-                const int c = swiglu ? (ch & 63) : ch;
-                const int owner = (((c >> 2) + 1) * S + Q - 1) / Q - 1;
-                const int local = c - ((owner * Q) / S) * 4 + ((swiglu && ch >= 64) ? QW * 4 : 0);
-                const int word = (rank * TC + tok) * W + local;
+                const int word = (rank * TC + tok) * W + local2[h];
                 const int value = acc[j][e] >> 4;                       // exact: sums are multiples of 16
-                if (S > 1) st_async_u32(map_to_cta(smem_u32(&inbox_sum[word]), (uint32_t)owner), (uint32_t)value, map_to_cta(smem_u32(&full[3 + ti]), (uint32_t)owner));
+                if (S > 1) st_async_u32(map_to_cta(smem_u32(&inbox_sum[word]), (uint32_t)owner2[h]), (uint32_t)value, dst_bar[h]);
                 else inbox_sum[word] = value;
             }
     }
