@@ -62,9 +62,13 @@ __device__ __forceinline__ void bulk_s2s(uint32_t remote_dst, uint32_t local_src
 // Wait of a whole warp on an mbarrier phase.  Fast path: the phase is already complete (weights are normally
 // requested long before they are needed) and one test by every lane both sees that and gives each lane its
 // acquire; otherwise one lane polls with the bounded wait and the others follow it.
-__device__ __forceinline__ bool mbar_wait_all_lanes(uint64_t* bar, uint32_t parity, unsigned long long deadline_ns)
+// The time limit starts the first time a warp really has to wait (reading the global timer costs a few hundred cycles,
+// too many for the path behind the dependency, and a limit taken in front of the dependency wait would charge the
+// launch in front to this one): `deadline_ns` is 0 until then.
+__device__ __forceinline__ bool mbar_wait_all_lanes(uint64_t* bar, uint32_t parity, unsigned long long& deadline_ns, unsigned long long timeout_ns)
 {
     if (__all_sync(0xffffffffu, mbar_test(bar, parity))) return true;
+    if (deadline_ns == 0) deadline_ns = global_ns() + timeout_ns;
     return mbar_wait_warp(bar, parity, deadline_ns);
 }
 __device__ __forceinline__ void bar_sync_contraction() { asm volatile("bar.sync 1, %0;" ::"n"(DEC_WARPS * 32) : "memory"); }
@@ -231,8 +235,7 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     constexpr int UMAX = HALF ? 3 : 2;     // units a thread keeps in registers between the scan and the quantisation
     constexpr int CT = DEC_WARPS * 32;
     // Everything that does not need the activations is settled before the wait: where this thread's units lie (no
-    // division behind the dependency) and the time limit (reading the global timer is slow; the few microseconds the
-    // launch in front still runs are charged to this launch's limit).
+    // division behind the dependency).
     int pos_tl[UMAX], pos_u[UMAX];
     bool pos_live[UMAX];
 #pragma unroll
@@ -247,7 +250,7 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
         if (pos_live[it] && pos_u[it] * 16 < p.K)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(A) + ((size_t)(t0 + pos_tl[it]) * p.K + (size_t)pos_u[it] * 16) * sizeof(AT)));
     }
-    const unsigned long long deadline = global_ns() + p.timeout_ns;
+    unsigned long long deadline = 0;   // set by the first wait that does not find its barrier complete
     if (TRACE && trace) trace[1] = (unsigned long long)(clock64() - c_start);
     // The producer of A (and of the collected row maxima) has finished once the dependency wait returns.  One warp
     // executes it; the others block at the hardware barrier behind it, where they take no issue slots from the
@@ -339,7 +342,13 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
         if (tid < S && tid != rank)
             bulk_s2s(map_to_cta(xs_base + share_off, (uint32_t)tid), xs_base + share_off, share_bytes, map_to_cta(bar_base, (uint32_t)tid));
         if (TRACE && trace) trace[3] = (unsigned long long)(clock64() - c_start);
-        if (!mbar_wait_all_lanes(code_bar, 0, deadline)) failed = true;
+        // (every thread polls this one: on the critical path an elected lane per warp wakes its warp later -- the same
+        // change cost the split-K kernel 8 %)
+        if (!mbar_test(code_bar, 0)) {
+            if (deadline == 0) deadline = global_ns() + p.timeout_ns;
+            if (!mbar_wait(code_bar, 0, deadline)) failed = true;
+        }
+        failed = __any_sync(0xffffffffu, failed);
     } else {
         if (TRACE && trace) trace[3] = (unsigned long long)(clock64() - c_start);
         bar_sync_contraction();
@@ -372,7 +381,7 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     };
     auto acquire_stage = [&]() {
         if (TRACE && stage_no < 8) stamp(2 * stage_no);
-        if (!mbar_wait_all_lanes(&full[slot], parity, deadline)) failed = true;
+        if (!mbar_wait_all_lanes(&full[slot], parity, deadline, p.timeout_ns)) failed = true;
         if (TRACE && stage_no < 8) stamp(2 * stage_no + 1);
     };
     for (int j = 0; j < my_items; ++j) {
