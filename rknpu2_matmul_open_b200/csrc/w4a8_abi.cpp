@@ -316,7 +316,13 @@ int fused_split(const rk_npu_w4a8_workspace& ws, int tiles)
         const long long slots = (long long)sms * std::min<long long>(8, (long long)(smem_per_sm / bytes));
         if ((long long)tiles * split <= slots) best = split;
     }
-    return best ? best : 8;
+    if (!best) return 8;
+    // ... but no finer than about eight k-blocks (1024 reduction elements) per CTA: below that the CTAs of a launch
+    // outnumber the SMs by more than their short slices win back (decode ring at 8 tokens, K = 4096: split 4 against 8,
+    // 1791 against 1709 GB/s; K = 11008 stays at 8, where 6 and 7 measured slower)
+    const int want = std::max(1, std::min(8, (ws.KB + 4) / 8));
+    if (want < best && (ws.KB + want - 1) / want <= FUSED_MAX_STAGES) best = want;
+    return best;
 }
 
 // Column tiles per CTA of the single-kernel path.  Its CTAs hold their whole weight slice in shared memory
@@ -997,7 +1003,9 @@ rk_npu_w4a8_workspace* rkb200::create_workspace_scheduled(rk_npu_iommu_domain* d
     // block; beyond that the two-kernel ring (quantise + mma.sync GEMM) streams better.  Up to 32
     // tokens the tcgen05 streaming kernel (4) is opt-in: its time does not depend on the batch
     // size, but it only overtakes the ring at 32 tokens.
-    const bool fused_best = fused_ok && cfg->M <= 8 && (long long)cfg->K * local_N / 2 <= (24ll << 20);
+    long long fused_limit_mb = 24;
+    if (const char* e = std::getenv("RK_NPU_B200_FUSED_MAX_MB")) fused_limit_mb = std::max(0, std::atoi(e));   // experiments
+    const bool fused_best = fused_ok && cfg->M <= 8 && (long long)cfg->K * local_N / 2 <= (fused_limit_mb << 20);
     // Up to eight tokens: the decode kernel (5), whose CTAs own whole output channels over all of K.  Up to four
     // tokens (at most one 16-element unit to quantise per thread of a four-CTA cluster, or none to exchange at all)
     // it beats the split-K kernel (3) on 7B-class shapes (4 tokens: 1783 against 1718 GB/s on the decode ring);
