@@ -268,6 +268,13 @@ bool on_device(const void* p)
     if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
     return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
 }
+// Page-locked host memory that the GPU can address (cudaHostAlloc / cudaHostRegister): its device alias, else NULL.
+void* mapped_alias(const void* p)
+{
+    cudaPointerAttributes a{};
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return a.type == cudaMemoryTypeHost ? a.devicePointer : nullptr;
+}
 
 // ------------------------------------------------------------------ kernel sequencing
 int pick_split_auto(const rk_npu_w4a8_workspace& ws, int tiles, int token_chunks)
@@ -298,6 +305,7 @@ struct Call {
     bool keep_codes = false;   // fused kernel: also store the activation codes (diagnostic entry only)
     const int8_t* codes_in = nullptr;   // activations arrive as int8 codes [parts][M][K/parts]; scales from rowmax_in
     int parts = 1;
+    Status* status = nullptr;   // single-kernel families: where the launch reports (default: the workspace's device block)
 };
 
 // Split-K factor (= cluster size) of the single-kernel path: the largest split whose CTAs
@@ -354,7 +362,7 @@ void decode_params(const Call& c, DecodeParams& d, int cluster_override = 0)
     d.rowmax_in = c.rowmax_in;
     d.scales_out = ws.scales;
     d.codes_out = c.keep_codes ? ws.codes : nullptr;
-    d.status = ws.status;
+    d.status = c.status ? c.status : ws.status;
     d.M = cfg.M; d.N = N; d.K = cfg.K;
     d.KB = ws.KB; d.NG = c.w->NG; d.F = F; d.epi = c.epi;
     d.half = c.half ? 1 : 0;
@@ -398,7 +406,7 @@ int enqueue(const Call& c)
         f.rowmax_in = c.rowmax_in;
         f.scales_out = ws.scales;
         f.codes_out = c.keep_codes ? ws.codes : nullptr;
-        f.status = ws.status;
+        f.status = c.status ? c.status : ws.status;
         f.M = cfg.M; f.N = N; f.K = cfg.K;
         f.KB = ws.KB; f.NG = c.w->NG; f.F = F; f.epi = c.epi;
         f.split = fused_split(ws, tiles);
@@ -563,16 +571,26 @@ int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const vo
         if (cudaMemcpyAsync(ws->stage_in, A, in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
         dA = ws->stage_in;
     }
-    if (!c_dev) dC = ws->stage_out;
+    // A small batch through one of the single-kernel families writes every output element once and reports through two
+    // plain stores, so a host caller is served without the two copies behind the kernel: the kernel stores straight
+    // into the caller's tensor when that is page-locked memory the GPU can address, and reports into the workspace's
+    // own page-locked status block.  (The activations are still copied in: every CTA reads them.)
+    const bool single_kernel = (ws->variant == 3 || ws->variant == 5) && !grouped(*ws) && epi != EPI_SWIGLU;
+    void* c_alias = (!c_dev && single_kernel && out_bytes <= (size_t(1) << 20)) ? mapped_alias(C) : nullptr;
+    if (c_alias) dC = c_alias;
+    else if (!c_dev) dC = ws->stage_out;
+    Status* status_alias = single_kernel ? static_cast<Status*>(mapped_alias(ws->host_status)) : nullptr;
+    if (status_alias) *ws->host_status = Status{};
     t.sync_us += elapsed_us(copy_start);
     Call call{ws, w, dA, dC, half, epi, nullptr, nullptr, s, metrics ? ws->events : nullptr, epi == EPI_I32};
+    call.status = status_alias;
     int rc = enqueue_linear(call, dC);
     if (rc) { cudaStreamSynchronize(s); return rc; }
     copy_start = Clock::now();
-    // Host tensors are copied straight from and to the caller's (pageable) memory: bouncing small ones through
+    // Other host tensors are copied straight from and to the caller's (pageable) memory: bouncing small ones through
     // pinned buffers was measured slower (the extra host memcpy costs more than the driver's own staging).
-    if (!c_dev) cudaMemcpyAsync(C, dC, out_bytes, cudaMemcpyDeviceToHost, s);
-    cudaMemcpyAsync(ws->host_status, ws->status, sizeof(Status), cudaMemcpyDeviceToHost, s);
+    if (!c_dev && !c_alias) cudaMemcpyAsync(C, dC, out_bytes, cudaMemcpyDeviceToHost, s);
+    if (!status_alias) cudaMemcpyAsync(ws->host_status, ws->status, sizeof(Status), cudaMemcpyDeviceToHost, s);
     if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
     t.sync_us += elapsed_us(copy_start);
     rc = status_to_rc(*ws, s);

@@ -194,7 +194,7 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
                                 deadline = global_ns() + p.timeout_ns;
                             }
                             if (!mbar_wait(&empty[slot], (turn - 1u) & 1u, deadline)) {
-                                atomicExch(&p.status->device_error, 1);
+                                *reinterpret_cast<volatile int*>(&p.status->device_error) = 1;   // (a plain store: the block may be page-locked host memory)
                                 return;
                             }
                         }
@@ -482,7 +482,7 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const unsigned
     }
 
     // ---- bookkeeping
-    if (failed && lane == 0) atomicExch(&p.status->device_error, 1);
+    if (failed && lane == 0) *reinterpret_cast<volatile int*>(&p.status->device_error) = 1;   // (a plain store: the block may be page-locked host memory)
     if (TRACE && trace) trace[7] = global_ns();
     if (tid == 0) {
         if (cta == 0) p.status->bad_input = verdict;

@@ -386,7 +386,7 @@ __global__ void __launch_bounds__(FUSED_THREADS) gemm_fused_kernel(const FusedPa
     // ---- bookkeeping by one thread per CTA
     if (trace) trace[7] = global_ns();
     if (tid == 0) {
-        if (s_flags[1]) atomicExch(&p.status->device_error, 1);
+        if (s_flags[1]) *reinterpret_cast<volatile int*>(&p.status->device_error) = 1;   // (plain store: may be page-locked host memory)
         if (blockIdx.x == 0 && rank == 0) p.status->bad_input = verdict;
         if (p.rowmax_in != nullptr) {
             // Every CTA has read the row maxima by now; the last one to get here clears

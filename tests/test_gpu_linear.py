@@ -328,6 +328,47 @@ def test_device_pointers_and_enqueue(gpu, oracle):
     w.free()
 
 
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (4, 1057, 385), (8, 4096, 4096), (8, 2048, 513), (24, 1057, 385)],
+                         ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_page_locked_host_tensors(gpu, oracle, shape, dtype):
+    # small batches write a page-locked result tensor from the kernel itself and report into page-locked memory:
+    # same numbers, same verdicts, nothing outside the result touched
+    import torch
+    lib = capi.load()
+    _, dom, _ = gpu
+    M, K, N = shape
+    half = dtype == "f16"
+    B, sw = make_weights(K, N, seed=11)
+    A = make_activations(M, K, seed=11, dtype=dtype)
+    ref = oracle.linear(A, B, sw)[1]
+    w = rk.Weights(dom, B, sw)
+    ws = rk.Workspace(dom, rk.default_config(M, N, K, timeout_ms=2))
+    hA = torch.from_numpy(A.view(np.int16) if half else A).pin_memory()
+    guard = 64
+    flat = torch.full((M * N + 2 * guard,), 0x5555 if half else -7, dtype=torch.int16 if half else torch.float32).pin_memory()
+    hC = flat[guard:guard + M * N].view(M, N)
+    run = ws.run_f16 if half else ws.run_f32
+    for _ in range(2):
+        hC.zero_()
+        assert run(w, hA, hC) == 0
+        assert np.array_equal(bits(hC.numpy().view(np.uint16) if half else hC.numpy()), bits(ref))
+    assert torch.all(flat[:guard] == flat[0]) and torch.all(flat[-guard:] == flat[0]), "guard elements touched"
+    bad = hA.clone().pin_memory()
+    bad[M - 1, K - 1] = 0x7c00 if half else float("nan")
+    assert run(w, bad, hC) == capi.RK_NPU_ERR_PARAM
+    assert run(w, hA, hC) == 0
+    if ws.schedule()[0] == 5:
+        assert lib.rk_npu_b200_w4a8_test_starve(ws.handle, 1) == 0
+        assert run(w, hA, hC) == capi.RK_NPU_ERR_SUBMIT      # a bounded wait ran out; reported through the page-locked block
+        assert lib.rk_npu_b200_w4a8_test_starve(ws.handle, 0) == 0
+    hC.zero_()
+    assert run(w, hA, hC) == 0
+    assert np.array_equal(bits(hC.numpy().view(np.uint16) if half else hC.numpy()), bits(ref))
+    ws.free()
+    w.free()
+
+
 def test_full_size_decode_sampled(gpu, oracle):
     # the benchmark's decode shapes at full size: 17 sampled columns x all rows (the reference's
     # own sampling for large shapes) plus linearity in the weights scale as a whole-output property
