@@ -63,6 +63,8 @@ class Oracle:
         L.orc_weight_fingerprint.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         L.orc_fnv_bytes.restype = C.c_uint64
         L.orc_fnv_bytes.argtypes = [C.c_uint64, C.c_void_p, C.c_size_t]
+        L.orc_moe_middle_row.restype = C.c_float
+        L.orc_moe_middle_row.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_void_p, C.c_int, C.c_void_p]
 
     # ---- binary16
     def half_to_float(self, h: np.ndarray) -> np.ndarray:
@@ -169,6 +171,43 @@ class Oracle:
                                                _ptr(out), _ptr(acc), _ptr(s), _ptr(q))
         return dict(rc=rc, out=out, acc=acc, scales=s, codes=q)
 
+    # ---- routed experts
+    def moe_quantize_rows(self, X, validate: bool = True):
+        """Nearest-even row quantisation of the routed operator.  Returns (rc, codes, scales); rc 1: a row was rejected."""
+        X = _c(X, np.float32)
+        rows, n = X.shape
+        q = np.zeros((rows, n), np.int8)
+        s = np.zeros(rows, np.float32)
+        rc = 0
+        for r in range(rows):
+            one = C.c_float(0)
+            rc |= self.lib.orc_moe_quantize_row(_ptr(X[r]), n, int(validate), _ptr(q[r]), C.byref(one))
+            s[r] = one.value
+        return rc, q, s
+
+    def moe_middle_row(self, acc, input_scale, w_scale, mode: int = 1):
+        """acc: [2I] int32 sums, gate then up.  Returns (scale, codes[I])."""
+        acc = _c(acc, np.int32)
+        I = acc.shape[0] // 2
+        q = np.zeros(I, np.int8)
+        scale = self.lib.orc_moe_middle_row(_ptr(acc), I, C.c_float(input_scale), _ptr(_c(w_scale, np.float32)), mode, _ptr(q))
+        return float(scale), q
+
+    def moe_run(self, experts, shared: int, top: int, codes, row_scales, ids, routes, mode: int = 1):
+        """experts: dict(gate_up [E,H,2I] int8, gate_up_scales [E,2I], down [E,I,H] int8, down_scales [E,H]), the
+        shared expert last when shared == 1.  Returns (rc, out [rows,H] fp32)."""
+        G = _c(experts["gate_up"], np.int8)
+        D = _c(experts["down"], np.int8)
+        E, H, I2 = G.shape
+        codes = _c(codes, np.int8)
+        rows = codes.shape[0]
+        out = np.zeros((rows, H), np.float32)
+        rc = self.lib.orc_moe_run(rows, H, I2 // 2, E - shared, shared, top, _ptr(G), _ptr(_c(experts["gate_up_scales"], np.float32)),
+                                  _ptr(D), _ptr(_c(experts["down_scales"], np.float32)), _ptr(codes),
+                                  _ptr(_c(row_scales, np.float32)), _ptr(_c(ids, np.int32)), _ptr(_c(routes, np.float32)), mode,
+                                  _ptr(out))
+        return rc, out
+
     def ffn(self, A, B_gu, s_gu, B_dn, s_dn, mode: int = 1):
         """Returns dict(rc, middle, C, acc_gate_up, acc_down, scales_down_in)."""
         A = _c(A, np.float32)
@@ -229,6 +268,9 @@ class Reference:
         L.ref_float_to_half.argtypes = [C.c_float]
         L.ref_layer_create.restype = C.c_void_p
         L.ref_layer_free.argtypes = [C.c_void_p]
+        if hasattr(L, "ref_moe_middle_row"):
+            L.ref_moe_middle_row.restype = C.c_float
+            L.ref_moe_middle_row.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_void_p, C.c_void_p]
 
     def host_threads(self) -> int:
         return int(self.lib.ref_host_threads())
@@ -291,6 +333,14 @@ class Reference:
 
     def k_partition_query(self, M, K, k_tile) -> int:
         return int(self.lib.ref_k_partition_query(M, K, k_tile))
+
+    def moe_middle_row(self, acc, input_scale, w_scale):
+        """The reference's fused middle stage of the routed operator on one row (its x86 build: std::exp)."""
+        acc = _c(acc, np.int32)
+        I = acc.shape[0] // 2
+        q = np.zeros(I, np.int8)
+        scale = self.lib.ref_moe_middle_row(_ptr(acc), I, C.c_float(input_scale), _ptr(_c(w_scale, np.float32)), _ptr(q))
+        return float(scale), q
 
     def layer(self, B, w_scale, k_tile=480):
         B = _c(B, np.int8)

@@ -21,6 +21,7 @@
 #include "rk_npu_half_bits.h"
 #include "rk_npu_cpu_kernels.h"
 #include "rk_npu_quant_matmul.h"
+#include "rk_npu_moe_cpu.h"
 #include <algorithm>
 #include <chrono>
 #include <cstring>
@@ -334,3 +335,13 @@ int ref_w8_linear(const void* A, int half, int M, int K, int N, const int8_t* B,
 int ref_k_partition_query(int M, int K, int k_tile) { return rk_npu_matmul_k_partition_query(M, K, k_tile); }
 
 } // extern "C"
+
+// ---- routed experts: the reference's fused middle stage (src/rk_npu_moe_cpu.cpp:47-115) on one row of int32
+// sums [gate(I), up(I)], plain int8 output.  Its x86 build evaluates the sigmoid with std::exp.
+extern "C" float ref_moe_middle_row(const int32_t* acc, int I, float input_scale, const float* w_scale, int8_t* q)
+{
+    // W8 partial layout for one row: data[(n / 4) * rows * 4 + row * 4 + n % 4] == data[n] (src/rk_npu_moe_cpu.h:13-16)
+    const rknpu2_matmul_open::moe::MiddleRow row{acc, nullptr, w_scale, input_scale, 1, 0, I, 1, 0, q,
+                                                 rknpu2_matmul_open::moe::MiddleLayout::I8Normal};
+    return rknpu2_matmul_open::moe::swiglu_quantize_row(row);
+}

@@ -507,3 +507,112 @@ uint64_t orc_weight_fingerprint(int K, int N, const int8_t *B, const float *w_sc
     h = orc_fnv_bytes(h, w_scale, (size_t)N * sizeof(float));
     return h;
 }
+
+/* ------------------------------------------------------------------ routed experts (rk_npu_moe_w8.h)
+ *
+ * The routed operator quantises with round-to-nearest-EVEN and without a lower clamp on the scale, unlike the
+ * dense W4A8 path (src/rk_npu_moe_cpu.cpp:21-24 "MoE retains nearest-even rounding", :80 "scale=1 for all-zero
+ * rows").  Pinned against the reference's compiled swiglu_quantize_row (its x86 form evaluates the sigmoid with
+ * std::exp: mode 0 here); mode 1 is the degree-7 polynomial its production target shares with the dense path. */
+
+/* src/rk_npu_moe_w8.cpp:317-343 (quantize<ValidateInput>): maximum of |x|, scale = max ? max/127 : 1,
+ * inverse = 1/scale, code = nearest-even(clamp(x*inverse, -127, 127)).  With `validate` a non-finite element, a
+ * scale that is not positive or an infinite inverse rejects the row (return 1). */
+int orc_moe_quantize_row(const float *x, int n, int validate, int8_t *q, float *scale_out)
+{
+    float maximum = 0.f;
+    for (int i = 0; i < n; ++i) {
+        if (validate && !isfinite(x[i])) return 1;
+        const float a = fabsf(x[i]);
+        if (a > maximum) maximum = a;
+    }
+    const float scale = maximum != 0.f ? maximum / 127.f : 1.f;
+    const float inverse = 1.f / scale;
+    if (validate && (!(scale > 0.f) || !isfinite(inverse))) return 1;
+    for (int i = 0; i < n; ++i) {
+        float v = x[i] * inverse;
+        if (v > 127.f) v = 127.f;
+        if (v < -127.f) v = -127.f;
+        q[i] = (int8_t)lrintf(v);   /* default rounding mode: to nearest, ties to even */
+    }
+    *scale_out = scale;
+    return 0;
+}
+
+/* src/rk_npu_moe_cpu.cpp:47-115 (swiglu_quantize_row), plain int8 output: acc holds the row's [gate(I), up(I)]
+ * int32 sums; both are dequantised as (float(sum) * input_scale) * weight_scale, y = silu(gate) * up, the row
+ * maximum is taken on the bit patterns, and the row is re-quantised with the rule above.  Returns the scale. */
+float orc_moe_middle_row(const int32_t *acc, int I, float input_scale, const float *w_scale, int mode, int8_t *q)
+{
+    float hidden[512];
+    uint32_t maximum = 0;
+    for (int n = 0; n < I; ++n) {
+        const float g = ((float)acc[n] * input_scale) * w_scale[n];
+        const float u = ((float)acc[I + n] * input_scale) * w_scale[I + n];
+        const float s = mode ? orc_silu_poly(g) : orc_silu_expf(g);
+        volatile float y = s * u;
+        hidden[n] = y;
+        float yy = y;
+        uint32_t bits;
+        memcpy(&bits, &yy, 4);
+        bits &= 0x7fffffffu;
+        if (bits > maximum) maximum = bits;
+    }
+    float maxabs;
+    memcpy(&maxabs, &maximum, 4);
+    const float scale = maximum ? maxabs / 127.f : 1.f;
+    const float inverse = 1.f / scale;
+    for (int n = 0; n < I; ++n) {
+        float v = hidden[n] * inverse;
+        if (v > 127.f) v = 127.f;
+        if (v < -127.f) v = -127.f;
+        q[n] = (int8_t)lrintf(v);
+    }
+    return scale;
+}
+
+/* The whole operator for int8 experts: src/rk_npu_moe_w8.cpp:570-817 (Workspace::run) and the independent
+ * reference of tests/test_moe_w8.cpp:27-46.  Experts are flat arrays, expert e at e * stride:
+ * gate_up [E][H][2I], gate_up_scales [E][2I], down [E][I][H], down_scales [E][H]; E = routed + shared, the
+ * shared expert last.  A route with coefficient 0 is left out; the shared expert counts with coefficient 1;
+ * the sum over a token's slots runs in slot order with one fused multiply-add per term (the production
+ * target's vfmaq).  Validation as in the original: ids in range, coefficients finite and >= 0, row scales
+ * finite and > 0.  Returns 0, or 1 for rejected arguments (out untouched). */
+int orc_moe_run(int rows, int H, int I, int routed, int shared, int top, const int8_t *gate_up,
+                const float *gate_up_scales, const int8_t *down, const float *down_scales, const int8_t *input,
+                const float *row_scales, const int32_t *ids, const float *routes, int mode, float *out)
+{
+    for (int i = 0; i < rows * top; ++i)
+        if (ids[i] < 0 || ids[i] >= routed || !isfinite(routes[i]) || routes[i] < 0.f) return 1;
+    for (int r = 0; r < rows; ++r)
+        if (!(row_scales[r] > 0.f) || !isfinite(row_scales[r])) return 1;
+    int32_t *acc = (int32_t *)malloc(sizeof(int32_t) * 2 * (size_t)I);
+    int8_t *q = (int8_t *)malloc((size_t)I);
+    float *sum = (float *)malloc(sizeof(float) * (size_t)H);
+    if (!acc || !q || !sum) { free(acc); free(q); free(sum); return 2; }
+    for (int r = 0; r < rows; ++r) {
+        for (int n = 0; n < H; ++n) sum[n] = 0.f;
+        for (int slot = 0; slot < top + shared; ++slot) {
+            const float coefficient = slot < top ? routes[r * top + slot] : 1.f;
+            if (slot < top && coefficient == 0.f) continue;
+            const int e = slot < top ? ids[r * top + slot] : routed;
+            const int8_t *G = gate_up + (size_t)e * H * 2 * I;
+            const int8_t *D = down + (size_t)e * I * H;
+            for (int c = 0; c < 2 * I; ++c) {
+                int32_t a = 0;
+                for (int k = 0; k < H; ++k) a += (int32_t)input[(size_t)r * H + k] * (int32_t)G[(size_t)k * 2 * I + c];
+                acc[c] = a;
+            }
+            const float scale = orc_moe_middle_row(acc, I, row_scales[r], gate_up_scales + (size_t)e * 2 * I, mode, q);
+            for (int n = 0; n < H; ++n) {
+                int32_t a = 0;
+                for (int k = 0; k < I; ++k) a += (int32_t)q[k] * (int32_t)D[(size_t)k * H + n];
+                const float value = ((float)a * scale) * down_scales[(size_t)e * H + n];
+                sum[n] = fmaf(value, coefficient, sum[n]);
+            }
+        }
+        memcpy(out + (size_t)r * H, sum, sizeof(float) * (size_t)H);
+    }
+    free(acc); free(q); free(sum);
+    return 0;
+}

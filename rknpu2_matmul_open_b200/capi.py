@@ -119,6 +119,30 @@ class MatmulWeightConfig(C.Structure):
     _fields_ = [("K", C.c_int), ("N", C.c_int), ("k_tile", C.c_int)]
 
 
+class MoeWeightConfig(C.Structure):
+    """rk_npu_moe_w8_weight_config"""
+    _fields_ = [("hidden", C.c_int), ("intermediate", C.c_int), ("routed_experts", C.c_int), ("shared_expert", C.c_int)]
+
+
+class MoeConfig(C.Structure):
+    """rk_npu_moe_w8_config"""
+    _fields_ = [("struct_size", C.c_uint32), ("weights", MoeWeightConfig), ("max_rows", C.c_int), ("top_k", C.c_int),
+                ("npu_cores", C.c_int), ("cpu_threads", C.c_int), ("native_input", C.c_int), ("middle", C.c_int),
+                ("timeout_ms", C.c_uint32)]
+
+
+class MoeExpert(C.Structure):
+    """rk_npu_moe_w8_expert: host arrays of one expert"""
+    _fields_ = [("gate_up", C.c_void_p), ("gate_up_scales", C.c_void_p), ("down", C.c_void_p), ("down_scales", C.c_void_p)]
+
+
+class MoeTimings(C.Structure):
+    """rk_npu_moe_w8_timings"""
+    _fields_ = [(n, C.c_double) for n in ("input_us", "schedule_us", "build_us", "sync_us", "gather_us", "gate_us", "middle_npu_us",
+                                          "middle_cpu_us", "down_us", "combine_us", "lut_load_us", "total_us")] + \
+               [(n, C.c_uint32) for n in ("gather_tasks", "middle_tasks", "gemm_tasks")]
+
+
 class MatmulWorkspaceRequirements(C.Structure):
     _fields_ = [("bytes", C.c_uint64), ("input_bytes", C.c_uint64), ("output_bytes", C.c_uint64), ("control_bytes", C.c_uint64),
                 ("wave_count", C.c_uint32), ("buffer_count", C.c_uint32)]
@@ -283,6 +307,28 @@ _SIGNATURES = {
     "rk_npu_b200_open_offline": (_P, [C.c_uint32]),
     "rk_npu_b200_w4a8_enqueue_f32": (C.c_int, [_P, _P, _P, _P, _P]),
     "rk_npu_b200_w4a8_enqueue_f16": (C.c_int, [_P, _P, _P, _P, _P]),
+    # routed experts (include/rknpu_b200_moe.h)
+    "rk_npu_moe_w8_config_init": (None, [C.POINTER(MoeConfig), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "rk_npu_moe_w8_weights_create": (_P, [_P, C.POINTER(MoeWeightConfig), C.POINTER(MoeExpert)]),
+    "rk_npu_moe_w8_weights_free": (None, [_P]),
+    "rk_npu_moe_w8_workspace_create": (_P, [_P, C.POINTER(MoeConfig)]),
+    "rk_npu_moe_w8_workspace_free": (None, [_P]),
+    "rk_npu_moe_w8_weights_device_bytes": (C.c_uint64, [_P]),
+    "rk_npu_moe_w8_workspace_device_bytes": (C.c_uint64, [_P]),
+    "rk_npu_moe_w8_run_quantized": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, _P, _P, C.POINTER(MoeTimings)]),
+    "rk_npu_moe_w8_run_f32": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, _P, C.POINTER(MoeTimings)]),
+    "rk_npu_moe_quant_weights_create": (_P, [_P, C.POINTER(MoeWeightConfig), C.POINTER(MoeExpert)]),
+    "rk_npu_moe_quant_weights_create_full_k": (_P, [_P, C.POINTER(MoeWeightConfig), C.POINTER(MoeExpert)]),
+    "rk_npu_moe_quant_workspace_create": (_P, [_P, C.POINTER(MoeConfig)]),
+    "rk_npu_moe_w4_weights_create": (_P, [_P, C.POINTER(MoeWeightConfig), C.POINTER(MoeExpert)]),
+    "rk_npu_moe_w4_workspace_create": (_P, [_P, C.POINTER(MoeConfig)]),
+    "rk_npu_moe_w4_slots_create": (_P, [_P, C.POINTER(MoeWeightConfig), C.POINTER(MoeExpert)]),
+    "rk_npu_moe_quant_slots_create": (_P, [_P, C.POINTER(MoeWeightConfig)]),
+    "rk_npu_moe_quant_expert_blob_bytes": (C.c_uint64, [_P]),
+    "rk_npu_moe_quant_export_expert": (C.c_int, [_P, C.c_int, _P, C.c_uint64]),
+    "rk_npu_moe_quant_import_expert": (C.c_int, [_P, C.c_int, _P, C.c_uint64]),
+    "rk_npu_moe_quant_import_expert_timed": (C.c_int, [_P, C.c_int, _P, C.c_uint64, _P]),
+    "rk_npu_moe_quant_swap_slots": (C.c_int, [_P, C.c_int, _P, C.c_int]),
     "rk_npu_b200_w4a8_enqueue_swiglu_f32": (C.c_int, [_P, _P, _P, _P, _P]),
     "rk_npu_b200_w4a8_enqueue_ffn_f32": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P]),
     "rk_npu_b200_w4a8_enqueue_swiglu_collect_f32": (C.c_int, [_P, _P, _P, _P, _P, _P]),

@@ -1,0 +1,428 @@
+// moe_abi.cpp -- the routed-experts operator of the original's include/rk_npu_moe_w8.h on this library: int8 expert
+// weight objects, workspaces, the two blocking run calls.
+//
+// The original (src/rk_npu_moe_w8.cpp:570-817) quantises the input rows on the CPU, groups the (token, slot)
+// assignments by expert, gathers and multiplies on the NPU, runs the middle stage and the weighted combine on the
+// CPU.  Here the host only validates and groups (the ids and coefficients are host arrays); quantisation, both
+// projections, the middle stage and the combine are four launches on the workspace's stream (moe_kernels.cu).
+// Validation order and return codes follow the original's moe_run (src/rk_npu_moe_w8.cpp:845-875) and
+// Workspace::run (:582-595).
+#include "w4a8_host.h"
+#include "moe_device.h"
+#include "../../include/rknpu_b200_moe.h"
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <new>
+#include <vector>
+
+using namespace rkb200;
+
+namespace {
+using Clock = std::chrono::steady_clock;
+double since_us(Clock::time_point t) { return std::chrono::duration<double, std::micro>(Clock::now() - t).count(); }
+constexpr int MOE_HIDDEN_MAX = 8192;   // 16 gathered rows of codes must fit one CTA's shared memory
+
+bool valid_weights(const rk_npu_moe_w8_weight_config& c)   // src/rk_npu_moe_w8.cpp:293-298
+{
+    return c.hidden >= 64 && c.hidden % 32 == 0 && c.hidden <= MOE_HIDDEN_MAX && c.intermediate >= 32 && c.intermediate <= 512 &&
+           c.intermediate % 32 == 0 && c.routed_experts >= 1 && (c.shared_expert == 0 || c.shared_expert == 1);
+}
+bool same_weights(const rk_npu_moe_w8_weight_config& a, const rk_npu_moe_w8_weight_config& b)
+{
+    return a.hidden == b.hidden && a.intermediate == b.intermediate && a.routed_experts == b.routed_experts &&
+           a.shared_expert == b.shared_expert;
+}
+bool valid_config(const rk_npu_moe_w8_config& c)           // src/rk_npu_moe_w8.cpp:303-310; the table-lookup middle is not built
+{
+    return c.struct_size == sizeof(c) && valid_weights(c.weights) && c.max_rows >= 1 && c.max_rows <= 256 && c.top_k >= 1 &&
+           c.top_k <= std::min(c.weights.routed_experts, 8) && c.npu_cores >= 1 && c.npu_cores <= 3 && c.cpu_threads >= 1 &&
+           c.cpu_threads <= 4 && (c.native_input == 0 || c.native_input == 1) && c.timeout_ms >= 1 && c.timeout_ms <= 60000 &&
+           c.middle == RK_NPU_MOE_MIDDLE_CPU;
+}
+bool finite_positive(float x) { return std::isfinite(x) && x > 0.0f; }
+bool overlap(const void* a, size_t na, const void* b, size_t nb)
+{
+    const auto x = reinterpret_cast<uintptr_t>(a), y = reinterpret_cast<uintptr_t>(b);
+    return x <= y ? y - x < na : x - y < nb;
+}
+float event_us(cudaEvent_t a, cudaEvent_t b)
+{
+    float ms = 0;
+    if (cudaEventElapsedTime(&ms, a, b) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return ms * 1000.f;
+}
+} // namespace
+
+struct rk_npu_moe_w8_weights {
+    rk_npu_iommu_domain* domain = nullptr;
+    uint64_t ctx_id = 0;
+    uint32_t domain_id = 0;
+    rk_npu_moe_w8_weight_config config{};
+    uint8_t* gate_up = nullptr;   // [E] records of the [H, 2I] matrices
+    uint8_t* down = nullptr;      // [E] records of the [I, H] matrices
+    float* gate_up_scales = nullptr, *down_scales = nullptr;
+    size_t gate_up_expert_bytes = 0, down_expert_bytes = 0;
+    size_t gate_up_bytes = 0, down_bytes = 0, gate_up_scale_bytes = 0, down_scale_bytes = 0;
+};
+
+struct rk_npu_moe_w8_workspace {
+    rk_npu_iommu_domain* domain = nullptr;
+    uint64_t ctx_id = 0;
+    uint32_t domain_id = 0;
+    rk_npu_moe_w8_config config{};
+    std::atomic_flag busy = ATOMIC_FLAG_INIT;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t events[5] = {};
+    int slots = 0, assignments_max = 0;
+    float* input = nullptr;        // [max_rows][H] fp32 rows of run_f32
+    int8_t* codes = nullptr;       // [max_rows][H]
+    float* in_scales = nullptr;    // [max_rows]
+    float* middle = nullptr;       // [assignments][I]
+    uint32_t* row_max = nullptr;   // [assignments]
+    float* expert_out = nullptr;   // [assignments][H]
+    float* out = nullptr;          // [max_rows][H]
+    int* schedule = nullptr;       // job_expert, job_first, job_rows, assign_token [assignments each]; slot_assign, coefficients [max_rows * slots each]
+    Status* status = nullptr;
+    size_t input_bytes = 0, codes_bytes = 0, in_scale_bytes = 0, middle_bytes = 0, row_max_bytes = 0, expert_out_bytes = 0,
+           out_bytes = 0, schedule_bytes = 0;
+    int* host_schedule = nullptr;  // pinned mirror of `schedule`
+    Status* host_status = nullptr; // pinned
+    std::vector<std::vector<int>> groups;   // per expert: token * slots + slot of its assignments
+};
+
+namespace {
+void weights_destroy(rk_npu_moe_w8_weights* w)
+{
+    if (!w) return;
+    auto* d = w->domain;
+    if (d) {
+        cudaSetDevice(d->ctx->device);
+        if (w->gate_up) device_free(d, w->gate_up, w->gate_up_bytes);
+        if (w->down) device_free(d, w->down, w->down_bytes);
+        if (w->gate_up_scales) device_free(d, w->gate_up_scales, w->gate_up_scale_bytes);
+        if (w->down_scales) device_free(d, w->down_scales, w->down_scale_bytes);
+        domain_release(d);
+    }
+    delete w;
+}
+
+void workspace_destroy(rk_npu_moe_w8_workspace* ws)
+{
+    if (!ws) return;
+    auto* d = ws->domain;
+    if (d) cudaSetDevice(d->ctx->device);
+    if (ws->stream) cudaStreamSynchronize(ws->stream);
+    if (ws->input) device_free(d, ws->input, ws->input_bytes);
+    if (ws->codes) device_free(d, ws->codes, ws->codes_bytes);
+    if (ws->in_scales) device_free(d, ws->in_scales, ws->in_scale_bytes);
+    if (ws->middle) device_free(d, ws->middle, ws->middle_bytes);
+    if (ws->row_max) device_free(d, ws->row_max, ws->row_max_bytes);
+    if (ws->expert_out) device_free(d, ws->expert_out, ws->expert_out_bytes);
+    if (ws->out) device_free(d, ws->out, ws->out_bytes);
+    if (ws->schedule) device_free(d, ws->schedule, ws->schedule_bytes);
+    if (ws->status) device_free(d, ws->status, sizeof(Status));
+    if (ws->host_schedule) cudaFreeHost(ws->host_schedule);
+    if (ws->host_status) cudaFreeHost(ws->host_status);
+    for (auto& e : ws->events)
+        if (e) cudaEventDestroy(e);
+    if (ws->stream) cudaStreamDestroy(ws->stream);
+    if (d) domain_release(d);
+    delete ws;
+}
+
+struct Lock {
+    explicit Lock(rk_npu_moe_w8_workspace& ws) : flag(ws.busy), held(!flag.test_and_set(std::memory_order_acquire)) {}
+    ~Lock() { if (held) flag.clear(std::memory_order_release); }
+    std::atomic_flag& flag;
+    bool held;
+};
+
+// Groups the assignments by expert, cuts the groups into jobs and writes the schedule into the pinned mirror.
+// Returns the number of assignments; `jobs` receives the number of jobs.
+int build_schedule(rk_npu_moe_w8_workspace& ws, int rows, const int32_t* ids, const float* routes, int& jobs)
+{
+    const auto& c = ws.config;
+    const int R = c.weights.routed_experts, top = c.top_k, S = ws.slots, A = ws.assignments_max;
+    for (auto& g : ws.groups) g.clear();
+    for (int r = 0; r < rows; ++r) {
+        for (int slot = 0; slot < top; ++slot)
+            if (routes[r * top + slot] != 0.0f) ws.groups[ids[r * top + slot]].push_back(r * S + slot);   // a zero coefficient leaves the route out
+        if (c.weights.shared_expert) ws.groups[R].push_back(r * S + top);
+    }
+    int* job_expert = ws.host_schedule, *job_first = job_expert + A, *job_rows = job_first + A, *assign_token = job_rows + A;
+    int* slot_assign = assign_token + A;
+    float* coefficients = reinterpret_cast<float*>(slot_assign + size_t(c.max_rows) * S);
+    std::fill(slot_assign, slot_assign + size_t(rows) * S, -1);
+    int a = 0;
+    jobs = 0;
+    for (int e = 0; e < int(ws.groups.size()); ++e) {
+        const auto& g = ws.groups[e];
+        for (size_t first = 0; first < g.size(); first += MOE_JOB_ROWS) {
+            const int n = int(std::min<size_t>(MOE_JOB_ROWS, g.size() - first));
+            job_expert[jobs] = e;
+            job_first[jobs] = a;
+            job_rows[jobs] = n;
+            ++jobs;
+            for (int i = 0; i < n; ++i, ++a) {
+                const int key = g[first + i];
+                assign_token[a] = key / S;
+                slot_assign[key] = a;
+            }
+        }
+    }
+    for (int r = 0; r < rows; ++r)
+        for (int slot = 0; slot < S; ++slot) coefficients[r * S + slot] = slot < top ? routes[r * top + slot] : 1.0f;
+    return a;
+}
+
+int moe_run(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int rows, const void* input, bool f32, const float* scales,
+            const int32_t* ids, const float* routes, float* output, rk_npu_moe_w8_timings* timings)
+{
+    if (timings) *timings = rk_npu_moe_w8_timings{};
+    if (!ws || !w || !input || !ids || !routes || !output || (!f32 && !scales) || rows < 1 || rows > ws->config.max_rows)
+        return RK_NPU_ERR_PARAM;
+    const auto& c = ws->config;
+    const int H = c.weights.hidden, I = c.weights.intermediate, R = c.weights.routed_experts, top = c.top_k, S = ws->slots;
+    const size_t values = size_t(rows) * H, routed = size_t(rows) * top;
+    if (overlap(input, values * (f32 ? 4 : 1), output, values * 4) || overlap(ids, routed * 4, output, values * 4) ||
+        overlap(routes, routed * 4, output, values * 4) || (!f32 && overlap(scales, size_t(rows) * 4, output, values * 4)))
+        return RK_NPU_ERR_PARAM;
+    Lock lock(*ws);
+    if (!lock.held) return RK_NPU_ERR_BUSY;
+    const auto begin = Clock::now();
+    if (!same_weights(c.weights, w->config)) return RK_NPU_ERR_PARAM;
+    if (w->ctx_id != ws->ctx_id || w->domain_id != ws->domain_id) return RK_NPU_ERR_DOMAIN;
+    for (size_t i = 0; i < routed; ++i)
+        if (ids[i] < 0 || ids[i] >= R || !std::isfinite(routes[i]) || routes[i] < 0.0f) return RK_NPU_ERR_PARAM;
+    if (!f32)
+        for (int r = 0; r < rows; ++r)
+            if (!finite_positive(scales[r])) return RK_NPU_ERR_PARAM;
+    if (cudaSetDevice(ws->domain->ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    cudaStream_t s = ws->stream;
+    rk_npu_moe_w8_timings t{};
+    try {
+        // ---- input rows
+        auto at = Clock::now();
+        if (timings) cudaEventRecord(ws->events[0], s);
+        bool ok = true;
+        if (f32) {
+            ok = cudaMemsetAsync(ws->status, 0, sizeof(Status), s) == cudaSuccess &&
+                 cudaMemcpyAsync(ws->input, input, values * 4, cudaMemcpyHostToDevice, s) == cudaSuccess;
+            const MoeQuantParams q{ws->input, ws->codes, ws->in_scales, ws->status, rows, H};
+            ok = ok && launch_moe_quantize(q, s) == cudaSuccess;
+        } else {
+            ok = cudaMemcpyAsync(ws->codes, input, values, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+                 cudaMemcpyAsync(ws->in_scales, scales, size_t(rows) * 4, cudaMemcpyHostToDevice, s) == cudaSuccess;
+        }
+        if (!ok) { cudaGetLastError(); cudaStreamSynchronize(s); return RK_NPU_ERR_SUBMIT; }
+        t.input_us = since_us(at);
+        // ---- the routes, grouped by expert
+        at = Clock::now();
+        int jobs = 0;
+        const int assignments = build_schedule(*ws, rows, ids, routes, jobs);
+        t.schedule_us = since_us(at);
+        auto input_verdict = [&]() -> int {    // run_f32: the quantise kernel's verdict on the rows
+            if (!f32) return RK_NPU_OK;
+            cudaMemcpyAsync(ws->host_status, ws->status, sizeof(Status), cudaMemcpyDeviceToHost, s);
+            if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+            return ws->host_status->bad_input ? RK_NPU_ERR_PARAM : RK_NPU_OK;
+        };
+        if (!assignments) {                    // nothing routed: the output is zero and no device work is issued for it
+            if (const int rc = input_verdict()) return rc;
+            at = Clock::now();
+            std::fill_n(output, values, 0.0f);
+            t.combine_us = since_us(at);
+            t.total_us = since_us(begin);
+            if (timings) *timings = t;
+            return RK_NPU_OK;
+        }
+        const int A = ws->assignments_max;
+        int* d_job_expert = ws->schedule, *d_job_first = d_job_expert + A, *d_job_rows = d_job_first + A, *d_assign_token = d_job_rows + A;
+        int* d_slot_assign = d_assign_token + A;
+        float* d_coefficients = reinterpret_cast<float*>(d_slot_assign + size_t(c.max_rows) * S);
+        ok = cudaMemcpyAsync(ws->schedule, ws->host_schedule, ws->schedule_bytes, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+             cudaMemsetAsync(ws->row_max, 0, size_t(assignments) * sizeof(uint32_t), s) == cudaSuccess;
+        if (timings) cudaEventRecord(ws->events[1], s);
+        const MoeSchedule sched{d_job_expert, d_job_first, d_job_rows, d_assign_token, jobs};
+        const MoeGateUpParams gu{sched, w->gate_up, w->gate_up_expert_bytes, w->gate_up_scales, ws->codes, ws->in_scales, ws->middle,
+                                 ws->row_max, H, I};
+        ok = ok && launch_moe_gate_up(gu, s) == cudaSuccess;
+        if (timings) cudaEventRecord(ws->events[2], s);
+        const MoeDownParams dn{sched, w->down, w->down_expert_bytes, w->down_scales, ws->middle, ws->row_max, ws->expert_out, H, I};
+        ok = ok && launch_moe_down(dn, s) == cudaSuccess;
+        if (timings) cudaEventRecord(ws->events[3], s);
+        const MoeCombineParams cb{ws->expert_out, d_slot_assign, d_coefficients, ws->out, rows, S, H};
+        ok = ok && launch_moe_combine(cb, s) == cudaSuccess;
+        if (timings) cudaEventRecord(ws->events[4], s);
+        if (!ok) { cudaGetLastError(); cudaStreamSynchronize(s); return RK_NPU_ERR_SUBMIT; }
+        if (const int rc = input_verdict()) return rc;      // a rejected row: the output is not written
+        at = Clock::now();
+        if (cudaMemcpyAsync(output, ws->out, values * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) {
+            cudaGetLastError();
+            return RK_NPU_ERR_SUBMIT;
+        }
+        t.sync_us = since_us(at);
+        if (timings) {
+            t.input_us = event_us(ws->events[0], ws->events[1]);
+            t.gate_us = event_us(ws->events[1], ws->events[2]);
+            t.down_us = event_us(ws->events[2], ws->events[3]);
+            t.combine_us = event_us(ws->events[3], ws->events[4]);
+            t.gather_tasks = t.middle_tasks = uint32_t(assignments);
+            t.gemm_tasks = uint32_t(2 * jobs);
+            t.total_us = since_us(begin);
+            *timings = t;
+        }
+        return RK_NPU_OK;
+    } catch (const std::bad_alloc&) {
+        return RK_NPU_ERR_NOMEM;
+    } catch (...) {
+        return RK_NPU_ERR_PARAM;
+    }
+}
+} // namespace
+
+// ================================================================== C ABI
+extern "C" void rk_npu_moe_w8_config_init(rk_npu_moe_w8_config* c, int hidden, int intermediate, int routed_experts, int shared_expert,
+                                          int top_k, int max_rows)
+{
+    // src/rk_npu_moe_w8.cpp:824-826: three cores, four threads, normal input, fp32 middle stage, one second
+    if (c) *c = rk_npu_moe_w8_config{uint32_t(sizeof(*c)), {hidden, intermediate, routed_experts, shared_expert}, max_rows, top_k, 3, 4, 0,
+                                     RK_NPU_MOE_MIDDLE_CPU, 1000};
+}
+
+extern "C" rk_npu_moe_w8_weights* rk_npu_moe_w8_weights_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
+                                                               const rk_npu_moe_w8_expert* experts)
+{
+    if (!domain || !domain->ctx || !config || !experts || !valid_weights(*config) || domain->ctx->world > 1) return nullptr;
+    const int H = config->hidden, I = config->intermediate, E = config->routed_experts + config->shared_expert;
+    for (int e = 0; e < E; ++e) {       // src/rk_npu_moe_w8.cpp:453-457
+        const auto& x = experts[e];
+        if (!x.gate_up || !x.down || !x.gate_up_scales || !x.down_scales) return nullptr;
+        for (int n = 0; n < 2 * I; ++n)
+            if (!finite_positive(x.gate_up_scales[n])) return nullptr;
+        for (int n = 0; n < H; ++n)
+            if (!finite_positive(x.down_scales[n])) return nullptr;
+    }
+    rk_npu_ctx* ctx = domain->ctx;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return nullptr;
+    rk_npu_moe_w8_weights* w = new (std::nothrow) rk_npu_moe_w8_weights();
+    if (!w) return nullptr;
+    w->domain = domain;
+    w->ctx_id = ctx->id;
+    w->domain_id = domain->id;
+    w->config = *config;
+    domain_retain(domain);
+    w->gate_up_expert_bytes = moe_packed_bytes(H, 2 * I);
+    w->down_expert_bytes = moe_packed_bytes(I, H);
+    w->gate_up_bytes = w->gate_up_expert_bytes * E;
+    w->down_bytes = w->down_expert_bytes * E;
+    w->gate_up_scale_bytes = sizeof(float) * 2 * size_t(I) * E;
+    w->down_scale_bytes = sizeof(float) * size_t(H) * E;
+    bool ok = !device_alloc(domain, reinterpret_cast<void**>(&w->gate_up), w->gate_up_bytes) &&
+              !device_alloc(domain, reinterpret_cast<void**>(&w->down), w->down_bytes) &&
+              !device_alloc(domain, reinterpret_cast<void**>(&w->gate_up_scales), w->gate_up_scale_bytes) &&
+              !device_alloc(domain, reinterpret_cast<void**>(&w->down_scales), w->down_scale_bytes);
+    int8_t* raw = nullptr;     // one expert's matrices as given, on their way into records
+    const size_t gu_raw = size_t(H) * 2 * I, dn_raw = size_t(I) * H;
+    ok = ok && cudaMalloc(reinterpret_cast<void**>(&raw), gu_raw + dn_raw) == cudaSuccess;
+    cudaStream_t s = ctx->stream;
+    for (int e = 0; ok && e < E; ++e) {
+        const auto& x = experts[e];
+        ok = cudaMemcpyAsync(raw, x.gate_up, gu_raw, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+             cudaMemcpyAsync(raw + gu_raw, x.down, dn_raw, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+             cudaMemcpyAsync(w->gate_up_scales + size_t(e) * 2 * I, x.gate_up_scales, sizeof(float) * 2 * I, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+             cudaMemcpyAsync(w->down_scales + size_t(e) * H, x.down_scales, sizeof(float) * H, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+             launch_moe_pack(MoePackParams{raw, w->gate_up + size_t(e) * w->gate_up_expert_bytes, H, 2 * I}, s) == cudaSuccess &&
+             launch_moe_pack(MoePackParams{raw + gu_raw, w->down + size_t(e) * w->down_expert_bytes, I, H}, s) == cudaSuccess &&
+             cudaStreamSynchronize(s) == cudaSuccess;     // the caller's arrays and `raw` are reused by the next expert
+    }
+    if (raw) cudaFree(raw);
+    if (!ok) { cudaGetLastError(); weights_destroy(w); return nullptr; }
+    return w;
+}
+extern "C" void rk_npu_moe_w8_weights_free(rk_npu_moe_w8_weights* w) { weights_destroy(w); }
+
+extern "C" rk_npu_moe_w8_workspace* rk_npu_moe_w8_workspace_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_config* config)
+{
+    if (!domain || !domain->ctx || !config || !valid_config(*config) || domain->ctx->world > 1) return nullptr;
+    rk_npu_ctx* ctx = domain->ctx;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return nullptr;
+    rk_npu_moe_w8_workspace* ws = nullptr;
+    try { ws = new rk_npu_moe_w8_workspace(); } catch (...) { return nullptr; }
+    ws->domain = domain;
+    ws->ctx_id = ctx->id;
+    ws->domain_id = domain->id;
+    ws->config = *config;
+    domain_retain(domain);
+    const int H = config->weights.hidden, I = config->weights.intermediate, rows = config->max_rows;
+    ws->slots = config->top_k + config->weights.shared_expert;
+    ws->assignments_max = rows * ws->slots;
+    const size_t A = size_t(ws->assignments_max);
+    ws->input_bytes = size_t(rows) * H * 4;
+    ws->codes_bytes = size_t(rows) * H;
+    ws->in_scale_bytes = size_t(rows) * 4;
+    ws->middle_bytes = A * I * 4;
+    ws->row_max_bytes = A * 4;
+    ws->expert_out_bytes = A * H * 4;
+    ws->out_bytes = size_t(rows) * H * 4;
+    ws->schedule_bytes = (4 * A + 2 * size_t(rows) * ws->slots) * 4;
+    bool ok = true;
+    try { ws->groups.resize(size_t(config->weights.routed_experts + config->weights.shared_expert)); } catch (...) { ok = false; }
+    ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->input), ws->input_bytes) &&
+         !device_alloc(domain, reinterpret_cast<void**>(&ws->codes), ws->codes_bytes) &&
+         !device_alloc(domain, reinterpret_cast<void**>(&ws->in_scales), ws->in_scale_bytes) &&
+         !device_alloc(domain, reinterpret_cast<void**>(&ws->middle), ws->middle_bytes) &&
+         !device_alloc(domain, reinterpret_cast<void**>(&ws->row_max), ws->row_max_bytes) &&
+         !device_alloc(domain, reinterpret_cast<void**>(&ws->expert_out), ws->expert_out_bytes) &&
+         !device_alloc(domain, reinterpret_cast<void**>(&ws->out), ws->out_bytes) &&
+         !device_alloc(domain, reinterpret_cast<void**>(&ws->schedule), ws->schedule_bytes) &&
+         !device_alloc(domain, reinterpret_cast<void**>(&ws->status), sizeof(Status));
+    ok = ok && cudaStreamCreateWithFlags(&ws->stream, cudaStreamNonBlocking) == cudaSuccess &&
+         cudaMallocHost(reinterpret_cast<void**>(&ws->host_schedule), ws->schedule_bytes) == cudaSuccess &&
+         cudaMallocHost(reinterpret_cast<void**>(&ws->host_status), sizeof(Status)) == cudaSuccess;
+    for (auto& e : ws->events) ok = ok && cudaEventCreate(&e) == cudaSuccess;
+    ok = ok && cudaMemsetAsync(ws->status, 0, sizeof(Status), ws->stream) == cudaSuccess && cudaStreamSynchronize(ws->stream) == cudaSuccess;
+    if (!ok) { cudaGetLastError(); workspace_destroy(ws); return nullptr; }
+    return ws;
+}
+extern "C" void rk_npu_moe_w8_workspace_free(rk_npu_moe_w8_workspace* ws) { workspace_destroy(ws); }
+
+extern "C" uint64_t rk_npu_moe_w8_weights_device_bytes(const rk_npu_moe_w8_weights* w)
+{
+    return w ? uint64_t(w->gate_up_bytes + w->down_bytes + w->gate_up_scale_bytes + w->down_scale_bytes) : 0;
+}
+extern "C" uint64_t rk_npu_moe_w8_workspace_device_bytes(const rk_npu_moe_w8_workspace* ws)
+{
+    return ws ? uint64_t(ws->input_bytes + ws->codes_bytes + ws->in_scale_bytes + ws->middle_bytes + ws->row_max_bytes +
+                         ws->expert_out_bytes + ws->out_bytes + ws->schedule_bytes + sizeof(Status))
+              : 0;
+}
+
+extern "C" int rk_npu_moe_w8_run_quantized(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int rows, const int8_t* input,
+                                           const float* row_scales, const int32_t* expert_ids, const float* route_weights, float* output,
+                                           rk_npu_moe_w8_timings* timings)
+{
+    return moe_run(ws, w, rows, input, false, row_scales, expert_ids, route_weights, output, timings);
+}
+extern "C" int rk_npu_moe_w8_run_f32(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int rows, const float* input,
+                                     const int32_t* expert_ids, const float* route_weights, float* output, rk_npu_moe_w8_timings* timings)
+{
+    return moe_run(ws, w, rows, input, true, nullptr, expert_ids, route_weights, output, timings);
+}
+
+// ---- the int4 expert forms, their slot banks and cache records: declined (include/rk_npu_moe_w8.h:87-146)
+extern "C" rk_npu_moe_w8_weights* rk_npu_moe_quant_weights_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_weight_config*, const rk_npu_moe_w8_expert*) { return nullptr; }
+extern "C" rk_npu_moe_w8_weights* rk_npu_moe_quant_weights_create_full_k(rk_npu_iommu_domain*, const rk_npu_moe_w8_weight_config*, const rk_npu_moe_w8_expert*) { return nullptr; }
+extern "C" rk_npu_moe_w8_workspace* rk_npu_moe_quant_workspace_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_config*) { return nullptr; }
+extern "C" rk_npu_moe_w8_weights* rk_npu_moe_w4_weights_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_weight_config*, const rk_npu_moe_w8_expert*) { return nullptr; }
+extern "C" rk_npu_moe_w8_workspace* rk_npu_moe_w4_workspace_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_config*) { return nullptr; }
+extern "C" rk_npu_moe_w8_weights* rk_npu_moe_w4_slots_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_weight_config*, const rk_npu_moe_w8_expert*) { return nullptr; }
+extern "C" rk_npu_moe_w8_weights* rk_npu_moe_quant_slots_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_weight_config*) { return nullptr; }
+extern "C" uint64_t rk_npu_moe_quant_expert_blob_bytes(const rk_npu_moe_w8_weights*) { return 0; }
+extern "C" int rk_npu_moe_quant_export_expert(const rk_npu_moe_w8_weights*, int, void*, uint64_t) { return RK_NPU_ERR_PARAM; }
+extern "C" int rk_npu_moe_quant_import_expert(rk_npu_moe_w8_weights*, int, const void*, uint64_t) { return RK_NPU_ERR_PARAM; }
+extern "C" int rk_npu_moe_quant_import_expert_timed(rk_npu_moe_w8_weights*, int, const void*, uint64_t, rk_npu_moe_import_timings*) { return RK_NPU_ERR_PARAM; }
+extern "C" int rk_npu_moe_quant_swap_slots(rk_npu_moe_w8_weights*, int, rk_npu_moe_w8_weights*, int) { return RK_NPU_ERR_PARAM; }

@@ -1,0 +1,79 @@
+// moe_device.h -- device side of the routed-experts operator (rk_npu_moe_w8.h): parameter blocks and launchers.
+//
+// A run is a list of JOBS: up to 16 (token, slot) assignments that use the same expert.  Three launches work
+// on the list: gate/up projection + SwiGLU (fp32 middle rows and their maxima), down projection (re-quantises
+// the middle rows on the way into shared memory), and the weighted sum over each token's slots.
+#pragma once
+#include "w4a8_device.h"
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rkb200 {
+
+constexpr int MOE_JOB_ROWS = 16;     // assignments per job: two 8-token halves of mma.m16n8k32
+constexpr int MOE_KQ = 128;          // k extent of one packed weight record (four k-steps of 32)
+
+// Packed int8 expert matrix W[K][N] (N a multiple of 16): records of 16 channels x 128 k in the register order
+// of the m16n8k32 A operand, [channel block][k quarter-kilo][k-step 0..3][lane][16 B = a0 a1 a2 a3], zero beyond K.
+inline size_t moe_packed_bytes(int K, int N) { return size_t((K + MOE_KQ - 1) / MOE_KQ) * MOE_KQ * size_t(N); }
+
+struct MoePackParams {
+    const int8_t* W;      // [K][N] row-major, on the device
+    uint8_t* packed;
+    int K, N;
+};
+
+struct MoeQuantParams {
+    const float* X;       // [rows][H]
+    int8_t* codes;        // [rows][H]
+    float* scales;        // [rows]
+    Status* status;       // bad_input: a non-finite element, or a scale whose reciprocal is not finite
+    int rows, H;
+};
+
+struct MoeSchedule {
+    const int* job_expert;     // [jobs]
+    const int* job_first;      // [jobs] first assignment of the job
+    const int* job_rows;       // [jobs] 1..16
+    const int* assign_token;   // [assignments] source row of each assignment (assignments of a job are consecutive)
+    int jobs;
+};
+
+struct MoeGateUpParams {
+    MoeSchedule sched;
+    const uint8_t* packed;       // experts' gate/up matrices, expert e at e * expert_bytes
+    size_t expert_bytes;
+    const float* w_scales;       // [E][2I]
+    const int8_t* codes;         // [rows][H]
+    const float* in_scales;      // [rows]
+    float* middle;               // [assignments][I]
+    uint32_t* row_max;           // [assignments] bit patterns of max |middle|, zero before the launch
+    int H, I;
+};
+
+struct MoeDownParams {
+    MoeSchedule sched;
+    const uint8_t* packed;       // experts' down matrices
+    size_t expert_bytes;
+    const float* w_scales;       // [E][H]
+    const float* middle;         // [assignments][I]
+    const uint32_t* row_max;     // [assignments]
+    float* expert_out;           // [assignments][H]
+    int H, I;
+};
+
+struct MoeCombineParams {
+    const float* expert_out;     // [assignments][H]
+    const int* slot_assign;      // [rows][slots] assignment index, -1: the slot takes no part
+    const float* coefficients;   // [rows][slots]
+    float* out;                  // [rows][H]
+    int rows, slots, H;
+};
+
+cudaError_t launch_moe_pack(const MoePackParams& p, cudaStream_t stream);
+cudaError_t launch_moe_quantize(const MoeQuantParams& p, cudaStream_t stream);
+cudaError_t launch_moe_gate_up(const MoeGateUpParams& p, cudaStream_t stream);
+cudaError_t launch_moe_down(const MoeDownParams& p, cudaStream_t stream);
+cudaError_t launch_moe_combine(const MoeCombineParams& p, cudaStream_t stream);
+
+} // namespace rkb200

@@ -1,0 +1,78 @@
+"""Host-side mirror of the routed-experts operator (include/rknpu_b200_moe.h) over the C ABI.
+
+``MoeWeights`` wraps rk_npu_moe_w8_weights (int8 experts, copied and packed at creation), ``MoeWorkspace`` wraps
+rk_npu_moe_w8_workspace; the run methods have the argument meaning and return codes of the C calls (host arrays
+in, host array out, blocking).  All compute happens in the CUDA library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import capi
+from .capi import MoeConfig, MoeExpert, MoeTimings, MoeWeightConfig
+from .w4a8 import W4A8Error, _ptr
+
+
+def default_config(hidden: int, intermediate: int, routed_experts: int, shared_expert: int, top_k: int, max_rows: int) -> MoeConfig:
+    """rk_npu_moe_w8_config_init"""
+    c = MoeConfig()
+    capi.load().rk_npu_moe_w8_config_init(C.byref(c), hidden, intermediate, routed_experts, shared_expert, top_k, max_rows)
+    return c
+
+
+class MoeWeights:
+    """rk_npu_moe_w8_weights_create / _free.  gate_up [E, H, 2I] int8, gate_up_scales [E, 2I], down [E, I, H] int8,
+    down_scales [E, H]; E = routed + shared experts, the shared one last."""
+
+    def __init__(self, domain, gate_up, gate_up_scales, down, down_scales, shared_expert: int = 0):
+        self.lib = capi.load()
+        gate_up = np.ascontiguousarray(gate_up, np.int8)
+        down = np.ascontiguousarray(down, np.int8)
+        gus = np.ascontiguousarray(gate_up_scales, np.float32)
+        dns = np.ascontiguousarray(down_scales, np.float32)
+        E, H, I2 = gate_up.shape
+        self.config = MoeWeightConfig(H, I2 // 2, E - shared_expert, shared_expert)
+        experts = (MoeExpert * E)()
+        for e in range(E):
+            experts[e] = MoeExpert(_ptr(gate_up[e]), _ptr(gus[e]), _ptr(down[e]), _ptr(dns[e]))
+        self.handle = self.lib.rk_npu_moe_w8_weights_create(domain.handle, C.byref(self.config), experts)
+        if not self.handle:
+            raise W4A8Error(capi.RK_NPU_ERR_PARAM, "rk_npu_moe_w8_weights_create")
+
+    def device_bytes(self) -> int:
+        return int(self.lib.rk_npu_moe_w8_weights_device_bytes(self.handle))
+
+    def free(self):
+        if self.handle:
+            self.lib.rk_npu_moe_w8_weights_free(self.handle)
+            self.handle = None
+
+
+class MoeWorkspace:
+    """rk_npu_moe_w8_workspace_create / _free and the two run calls."""
+
+    def __init__(self, domain, config: MoeConfig):
+        self.lib = capi.load()
+        self.config = config
+        self.handle = self.lib.rk_npu_moe_w8_workspace_create(domain.handle, C.byref(config))
+        if not self.handle:
+            raise W4A8Error(capi.RK_NPU_ERR_PARAM, "rk_npu_moe_w8_workspace_create")
+
+    def device_bytes(self) -> int:
+        return int(self.lib.rk_npu_moe_w8_workspace_device_bytes(self.handle))
+
+    def run_quantized(self, weights: MoeWeights, codes, row_scales, expert_ids, route_weights, out, timings: MoeTimings | None = None) -> int:
+        return self.lib.rk_npu_moe_w8_run_quantized(self.handle, weights.handle, int(codes.shape[0]), _ptr(codes), _ptr(row_scales),
+                                                    _ptr(expert_ids), _ptr(route_weights), _ptr(out),
+                                                    C.byref(timings) if timings is not None else None)
+
+    def run_f32(self, weights: MoeWeights, rows, expert_ids, route_weights, out, timings: MoeTimings | None = None) -> int:
+        return self.lib.rk_npu_moe_w8_run_f32(self.handle, weights.handle, int(rows.shape[0]), _ptr(rows), _ptr(expert_ids),
+                                              _ptr(route_weights), _ptr(out), C.byref(timings) if timings is not None else None)
+
+    def free(self):
+        if self.handle:
+            self.lib.rk_npu_moe_w8_workspace_free(self.handle)
+            self.handle = None

@@ -26,7 +26,7 @@ def cfg_of(lib, m, n, k, **kw):
 
 def test_library_exports_every_declared_symbol(lib):
     declared = set()
-    for header in ("rknpu_b200_w4a8.h", "rknpu_b200_quant.h", "rknpu_b200_ext.h"):
+    for header in ("rknpu_b200_w4a8.h", "rknpu_b200_quant.h", "rknpu_b200_moe.h", "rknpu_b200_ext.h"):
         text = (ROOT / "include" / header).read_text()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
         declared |= set(re.findall(r"\b(rk_npu_\w+)\s*\(", text))
@@ -454,8 +454,8 @@ def test_public_headers_are_valid_c(tmp_path):
     if not gcc:
         pytest.skip("no C compiler")
     src = tmp_path / "headers.c"
-    src.write_text('#include "rknpu_b200_w4a8.h"\n#include "rknpu_b200_quant.h"\n#include "rknpu_b200_ext.h"\n'
-                   "int main(void) { rk_npu_w4a8_config c; rk_npu_matmul_strategy s; (void)c; (void)s; return 0; }\n")
+    src.write_text('#include "rknpu_b200_w4a8.h"\n#include "rknpu_b200_quant.h"\n#include "rknpu_b200_moe.h"\n#include "rknpu_b200_ext.h"\n'
+                   "int main(void) { rk_npu_w4a8_config c; rk_npu_matmul_strategy s; rk_npu_moe_w8_config m; (void)c; (void)s; (void)m; return 0; }\n")
     out = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", f"-I{ROOT / 'include'}",
                           str(src)], capture_output=True, text=True)
     assert out.returncode == 0, out.stderr
