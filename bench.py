@@ -431,7 +431,7 @@ def run_cuda(args, rank, world, local_rank):
             also["layer_dependencies_only_error"] = str(exc)
     if not args.quick:
         peak = measure_int8_peak() if rank == 0 else None
-        for name, fn in (("prefill", _prefill), ("ffn_4096_14336", _ffn_llama8b), ("ffn_8192_28672", _ffn_70b)):
+        for name, fn in (("prefill", _prefill), ("ffn_4096_14336", _ffn_llama8b), ("ffn_8192_28672", _ffn_70b), ("moe", _moe)):
             try:
                 also.update(fn(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak))
             except Exception as exc:   # an extra figure must never cost the headline line
@@ -757,6 +757,56 @@ def _ffn_70b(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak):
     """Benchmark configuration 4: the 70B-shaped FFN (hidden 8192, intermediate 28672) at 32 and 4096 tokens, on one GPU
     (the baseline of the scaling figures) and column-sharded inside the library on a group."""
     return _ffn_figures(rk, ctx, dom, dev, stream, oracle, dist, world, rank, "ffn_8192_28672", 8192, 28672, 8192, (32, 4096), (41, 42))
+
+
+def _moe(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak):
+    """Routed experts (rk_npu_moe_w8): 128 int8 experts + a shared one, hidden 1536, intermediate 512, top-8 -- the
+    largest geometry the original documents -- through the blocking host-array entry at 1, 8, 64 and 256 rows.
+    Reported per batch: the complete call (host arrays in, host array out), the device time of the three launches
+    (measured with events between them, which keeps them from overlapping), the expert weights one call streams and
+    the rate that makes; four rows of every result are compared with the oracle bit for bit."""
+    if world > 1:
+        return {}
+    from rknpu2_matmul_open_b200 import capi, moe
+    H, I, R, shared, top = 1536, 512, 128, 1, 8
+    rng = np.random.default_rng(31)
+    E = R + shared
+    ex = dict(gate_up=rng.integers(-127, 128, size=(E, H, 2 * I), dtype=np.int8),
+              gate_up_scales=rng.uniform(2e-4, 6e-4, size=(E, 2 * I)).astype(np.float32),
+              down=rng.integers(-127, 128, size=(E, I, H), dtype=np.int8),
+              down_scales=rng.uniform(1e-3, 3e-3, size=(E, H)).astype(np.float32))
+    w = moe.MoeWeights(dom, shared_expert=shared, **ex)
+    ws = moe.MoeWorkspace(dom, moe.default_config(H, I, R, shared, top, 256))
+    out_fig = {}
+    for rows in (1, 8, 64, 256):
+        codes = rng.integers(-127, 128, size=(rows, H), dtype=np.int8)
+        scales = rng.uniform(0.01, 0.05, size=rows).astype(np.float32)
+        ids = np.stack([rng.choice(R, size=top, replace=False) for _ in range(rows)]).astype(np.int32)
+        routes = rng.uniform(0.05, 0.3, size=(rows, top)).astype(np.float32)
+        out = np.zeros((rows, H), np.float32)
+        t = capi.MoeTimings()
+        stages = None
+        for i in range(8):
+            if ws.run_quantized(w, codes, scales, ids, routes, out, t) != 0:
+                raise RuntimeError("rk_npu_moe_w8_run_quantized failed")
+            if i >= 3 and (stages is None or t.gate_us + t.down_us < stages[0] + stages[1]):
+                stages = (t.gate_us, t.down_us, t.combine_us)
+        t0 = time.perf_counter()
+        for _ in range(20):
+            ws.run_quantized(w, codes, scales, ids, routes, out, None)
+        call_us = (time.perf_counter() - t0) / 20 * 1e6
+        check = sorted(set([0, rows // 3, rows // 2, rows - 1]))
+        rc, ref = oracle.moe_run(ex, shared, top, codes[check], scales[check], ids[check], routes[check], mode=1)
+        exact = rc == 0 and bool(np.array_equal(out[check].view(np.uint32), ref.view(np.uint32)))
+        active = len(set(ids.reshape(-1).tolist())) + shared
+        weight_bytes = active * 3 * H * I
+        out_fig[f"rows_{rows}"] = {"call_us": call_us, "gate_up_us": stages[0], "down_us": stages[1], "combine_us": stages[2],
+                                   "active_experts": active, "expert_weight_MB": weight_bytes / 1e6,
+                                   "GBps_of_weights_per_call": weight_bytes / (call_us * 1e-6) / 1e9,
+                                   "GBps_of_weights_in_the_two_projections": weight_bytes / ((stages[0] + stages[1]) * 1e-6) / 1e9,
+                                   "rows_checked_exact": exact}
+    ws.free(); w.free()
+    return {"moe_w8_H1536_I512_E128_shared_top8": out_fig}
 
 
 def cpu_baseline(M, Reference, oracle, make_weights, make_activations):

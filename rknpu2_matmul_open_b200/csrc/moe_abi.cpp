@@ -77,18 +77,17 @@ struct rk_npu_moe_w8_workspace {
     cudaStream_t stream = nullptr;
     cudaEvent_t events[5] = {};
     int slots = 0, assignments_max = 0;
-    float* input = nullptr;        // [max_rows][H] fp32 rows of run_f32
-    int8_t* codes = nullptr;       // [max_rows][H]
-    float* in_scales = nullptr;    // [max_rows]
+    int8_t* codes = nullptr;       // [max_rows][H] codes made by the quantise kernel (run_f32)
+    float* in_scales = nullptr;    // [max_rows] and their scales
     float* middle = nullptr;       // [assignments][I]
     uint32_t* row_max = nullptr;   // [assignments]
     float* expert_out = nullptr;   // [assignments][H]
     float* out = nullptr;          // [max_rows][H]
-    int* schedule = nullptr;       // job_expert, job_first, job_rows, assign_token [assignments each]; slot_assign, coefficients [max_rows * slots each]
+    uint8_t* upload = nullptr;     // one run's host arrays in one piece (see Upload)
     Status* status = nullptr;
-    size_t input_bytes = 0, codes_bytes = 0, in_scale_bytes = 0, middle_bytes = 0, row_max_bytes = 0, expert_out_bytes = 0,
-           out_bytes = 0, schedule_bytes = 0;
-    int* host_schedule = nullptr;  // pinned mirror of `schedule`
+    size_t codes_bytes = 0, in_scale_bytes = 0, middle_bytes = 0, row_max_bytes = 0, expert_out_bytes = 0, out_bytes = 0,
+           upload_bytes = 0;
+    uint8_t* host_upload = nullptr;   // pinned mirror of `upload`
     Status* host_status = nullptr; // pinned
     std::vector<std::vector<int>> groups;   // per expert: token * slots + slot of its assignments
 };
@@ -115,16 +114,15 @@ void workspace_destroy(rk_npu_moe_w8_workspace* ws)
     auto* d = ws->domain;
     if (d) cudaSetDevice(d->ctx->device);
     if (ws->stream) cudaStreamSynchronize(ws->stream);
-    if (ws->input) device_free(d, ws->input, ws->input_bytes);
     if (ws->codes) device_free(d, ws->codes, ws->codes_bytes);
     if (ws->in_scales) device_free(d, ws->in_scales, ws->in_scale_bytes);
     if (ws->middle) device_free(d, ws->middle, ws->middle_bytes);
     if (ws->row_max) device_free(d, ws->row_max, ws->row_max_bytes);
     if (ws->expert_out) device_free(d, ws->expert_out, ws->expert_out_bytes);
     if (ws->out) device_free(d, ws->out, ws->out_bytes);
-    if (ws->schedule) device_free(d, ws->schedule, ws->schedule_bytes);
+    if (ws->upload) device_free(d, ws->upload, ws->upload_bytes);
     if (ws->status) device_free(d, ws->status, sizeof(Status));
-    if (ws->host_schedule) cudaFreeHost(ws->host_schedule);
+    if (ws->host_upload) cudaFreeHost(ws->host_upload);
     if (ws->host_status) cudaFreeHost(ws->host_status);
     for (auto& e : ws->events)
         if (e) cudaEventDestroy(e);
@@ -140,32 +138,59 @@ struct Lock {
     bool held;
 };
 
-// Groups the assignments by expert, cuts the groups into jobs and writes the schedule into the pinned mirror.
-// Returns the number of assignments; `jobs` receives the number of jobs.
-int build_schedule(rk_npu_moe_w8_workspace& ws, int rows, const int32_t* ids, const float* routes, int& jobs)
+// What one run sends to the device, packed into one page-locked piece so that it travels as ONE copy: the
+// schedule (jobs and assignments, grouped by expert), each token's slots, the coefficients, and the input rows
+// (int8 codes with their scales, or fp32 rows).  Offsets in bytes from the start of the piece.
+struct Upload {
+    size_t job_expert, job_first, job_rows, assign_token, slot_assign, coefficients, scales, rows_data, bytes;
+    int jobs, assignments;
+};
+size_t upload_capacity(int max_rows, int slots, int H)
+{
+    const size_t A = size_t(max_rows) * slots;
+    return (4 * A + 2 * A + size_t(max_rows)) * 4 + 16 + size_t(max_rows) * H * 4;
+}
+
+// Groups the assignments by expert, cuts the groups into jobs of at most 16 and writes everything into the mirror.
+Upload build_upload(rk_npu_moe_w8_workspace& ws, int rows, const void* input, bool f32, const float* scales, const int32_t* ids,
+                    const float* routes)
 {
     const auto& c = ws.config;
-    const int R = c.weights.routed_experts, top = c.top_k, S = ws.slots, A = ws.assignments_max;
+    const int R = c.weights.routed_experts, top = c.top_k, S = ws.slots, H = c.weights.hidden;
     for (auto& g : ws.groups) g.clear();
+    int assignments = 0, jobs = 0;
     for (int r = 0; r < rows; ++r) {
         for (int slot = 0; slot < top; ++slot)
             if (routes[r * top + slot] != 0.0f) ws.groups[ids[r * top + slot]].push_back(r * S + slot);   // a zero coefficient leaves the route out
         if (c.weights.shared_expert) ws.groups[R].push_back(r * S + top);
     }
-    int* job_expert = ws.host_schedule, *job_first = job_expert + A, *job_rows = job_first + A, *assign_token = job_rows + A;
-    int* slot_assign = assign_token + A;
-    float* coefficients = reinterpret_cast<float*>(slot_assign + size_t(c.max_rows) * S);
+    for (const auto& g : ws.groups) { assignments += int(g.size()); jobs += int((g.size() + MOE_JOB_ROWS - 1) / MOE_JOB_ROWS); }
+    Upload u{};
+    u.jobs = jobs;
+    u.assignments = assignments;
+    u.job_expert = 0;
+    u.job_first = u.job_expert + size_t(jobs) * 4;
+    u.job_rows = u.job_first + size_t(jobs) * 4;
+    u.assign_token = u.job_rows + size_t(jobs) * 4;
+    u.slot_assign = u.assign_token + size_t(assignments) * 4;
+    u.coefficients = u.slot_assign + size_t(rows) * S * 4;
+    u.scales = u.coefficients + size_t(rows) * S * 4;
+    u.rows_data = (u.scales + size_t(rows) * 4 + 15) / 16 * 16;
+    u.bytes = u.rows_data + size_t(rows) * H * (f32 ? 4 : 1);
+    uint8_t* base = ws.host_upload;
+    int* job_expert = reinterpret_cast<int*>(base + u.job_expert), *job_first = reinterpret_cast<int*>(base + u.job_first);
+    int* job_rows = reinterpret_cast<int*>(base + u.job_rows), *assign_token = reinterpret_cast<int*>(base + u.assign_token);
+    int* slot_assign = reinterpret_cast<int*>(base + u.slot_assign);
+    float* coefficients = reinterpret_cast<float*>(base + u.coefficients);
     std::fill(slot_assign, slot_assign + size_t(rows) * S, -1);
-    int a = 0;
-    jobs = 0;
+    int a = 0, j = 0;
     for (int e = 0; e < int(ws.groups.size()); ++e) {
         const auto& g = ws.groups[e];
-        for (size_t first = 0; first < g.size(); first += MOE_JOB_ROWS) {
+        for (size_t first = 0; first < g.size(); first += MOE_JOB_ROWS, ++j) {
             const int n = int(std::min<size_t>(MOE_JOB_ROWS, g.size() - first));
-            job_expert[jobs] = e;
-            job_first[jobs] = a;
-            job_rows[jobs] = n;
-            ++jobs;
+            job_expert[j] = e;
+            job_first[j] = a;
+            job_rows[j] = n;
             for (int i = 0; i < n; ++i, ++a) {
                 const int key = g[first + i];
                 assign_token[a] = key / S;
@@ -175,7 +200,9 @@ int build_schedule(rk_npu_moe_w8_workspace& ws, int rows, const int32_t* ids, co
     }
     for (int r = 0; r < rows; ++r)
         for (int slot = 0; slot < S; ++slot) coefficients[r * S + slot] = slot < top ? routes[r * top + slot] : 1.0f;
-    return a;
+    if (!f32) std::memcpy(base + u.scales, scales, size_t(rows) * 4);
+    std::memcpy(base + u.rows_data, input, size_t(rows) * H * (f32 ? 4 : 1));
+    return u;
 }
 
 int moe_run(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int rows, const void* input, bool f32, const float* scales,
@@ -204,26 +231,26 @@ int moe_run(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int row
     cudaStream_t s = ws->stream;
     rk_npu_moe_w8_timings t{};
     try {
-        // ---- input rows
+        // ---- the routes grouped by expert, the input rows: one piece, one copy
         auto at = Clock::now();
+        const Upload u = build_upload(*ws, rows, input, f32, scales, ids, routes);
+        const int assignments = u.assignments, jobs = u.jobs;
+        t.schedule_us = since_us(at);
+        at = Clock::now();
         if (timings) cudaEventRecord(ws->events[0], s);
         bool ok = true;
+        if (assignments || f32) ok = cudaMemcpyAsync(ws->upload, ws->host_upload, u.bytes, cudaMemcpyHostToDevice, s) == cudaSuccess;
+        const int8_t* codes = reinterpret_cast<const int8_t*>(ws->upload + u.rows_data);
+        const float* in_scales = reinterpret_cast<const float*>(ws->upload + u.scales);
         if (f32) {
-            ok = cudaMemsetAsync(ws->status, 0, sizeof(Status), s) == cudaSuccess &&
-                 cudaMemcpyAsync(ws->input, input, values * 4, cudaMemcpyHostToDevice, s) == cudaSuccess;
-            const MoeQuantParams q{ws->input, ws->codes, ws->in_scales, ws->status, rows, H};
+            ok = ok && cudaMemsetAsync(ws->status, 0, sizeof(Status), s) == cudaSuccess;
+            const MoeQuantParams q{reinterpret_cast<const float*>(ws->upload + u.rows_data), ws->codes, ws->in_scales, ws->status, rows, H};
             ok = ok && launch_moe_quantize(q, s) == cudaSuccess;
-        } else {
-            ok = cudaMemcpyAsync(ws->codes, input, values, cudaMemcpyHostToDevice, s) == cudaSuccess &&
-                 cudaMemcpyAsync(ws->in_scales, scales, size_t(rows) * 4, cudaMemcpyHostToDevice, s) == cudaSuccess;
+            codes = ws->codes;
+            in_scales = ws->in_scales;
         }
         if (!ok) { cudaGetLastError(); cudaStreamSynchronize(s); return RK_NPU_ERR_SUBMIT; }
         t.input_us = since_us(at);
-        // ---- the routes, grouped by expert
-        at = Clock::now();
-        int jobs = 0;
-        const int assignments = build_schedule(*ws, rows, ids, routes, jobs);
-        t.schedule_us = since_us(at);
         auto input_verdict = [&]() -> int {    // run_f32: the quantise kernel's verdict on the rows
             if (!f32) return RK_NPU_OK;
             cudaMemcpyAsync(ws->host_status, ws->status, sizeof(Status), cudaMemcpyDeviceToHost, s);
@@ -239,25 +266,25 @@ int moe_run(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int row
             if (timings) *timings = t;
             return RK_NPU_OK;
         }
-        const int A = ws->assignments_max;
-        int* d_job_expert = ws->schedule, *d_job_first = d_job_expert + A, *d_job_rows = d_job_first + A, *d_assign_token = d_job_rows + A;
-        int* d_slot_assign = d_assign_token + A;
-        float* d_coefficients = reinterpret_cast<float*>(d_slot_assign + size_t(c.max_rows) * S);
-        ok = cudaMemcpyAsync(ws->schedule, ws->host_schedule, ws->schedule_bytes, cudaMemcpyHostToDevice, s) == cudaSuccess &&
-             cudaMemsetAsync(ws->row_max, 0, size_t(assignments) * sizeof(uint32_t), s) == cudaSuccess;
         if (timings) cudaEventRecord(ws->events[1], s);
-        const MoeSchedule sched{d_job_expert, d_job_first, d_job_rows, d_assign_token, jobs};
-        const MoeGateUpParams gu{sched, w->gate_up, w->gate_up_expert_bytes, w->gate_up_scales, ws->codes, ws->in_scales, ws->middle,
-                                 ws->row_max, H, I};
-        ok = ok && launch_moe_gate_up(gu, s) == cudaSuccess;
+        const MoeSchedule sched{reinterpret_cast<const int*>(ws->upload + u.job_expert), reinterpret_cast<const int*>(ws->upload + u.job_first),
+                                reinterpret_cast<const int*>(ws->upload + u.job_rows), reinterpret_cast<const int*>(ws->upload + u.assign_token), jobs};
+        const MoeGateUpParams gu{sched, w->gate_up, w->gate_up_expert_bytes, w->gate_up_scales, codes, in_scales, ws->middle, ws->row_max, H, I};
+        ok = launch_moe_gate_up(gu, s) == cudaSuccess;
         if (timings) cudaEventRecord(ws->events[2], s);
         const MoeDownParams dn{sched, w->down, w->down_expert_bytes, w->down_scales, ws->middle, ws->row_max, ws->expert_out, H, I};
         ok = ok && launch_moe_down(dn, s) == cudaSuccess;
         if (timings) cudaEventRecord(ws->events[3], s);
-        const MoeCombineParams cb{ws->expert_out, d_slot_assign, d_coefficients, ws->out, rows, S, H};
+        const MoeCombineParams cb{ws->expert_out, reinterpret_cast<const int*>(ws->upload + u.slot_assign),
+                                  reinterpret_cast<const float*>(ws->upload + u.coefficients), ws->out, ws->row_max, rows, S, H};
         ok = ok && launch_moe_combine(cb, s) == cudaSuccess;
         if (timings) cudaEventRecord(ws->events[4], s);
-        if (!ok) { cudaGetLastError(); cudaStreamSynchronize(s); return RK_NPU_ERR_SUBMIT; }
+        if (!ok) {      // a launch failed part-way: the row maxima may be left behind
+            cudaGetLastError();
+            cudaMemsetAsync(ws->row_max, 0, ws->row_max_bytes, s);
+            cudaStreamSynchronize(s);
+            return RK_NPU_ERR_SUBMIT;
+        }
         if (const int rc = input_verdict()) return rc;      // a rejected row: the output is not written
         at = Clock::now();
         if (cudaMemcpyAsync(output, ws->out, values * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) {
@@ -361,30 +388,30 @@ extern "C" rk_npu_moe_w8_workspace* rk_npu_moe_w8_workspace_create(rk_npu_iommu_
     ws->slots = config->top_k + config->weights.shared_expert;
     ws->assignments_max = rows * ws->slots;
     const size_t A = size_t(ws->assignments_max);
-    ws->input_bytes = size_t(rows) * H * 4;
     ws->codes_bytes = size_t(rows) * H;
     ws->in_scale_bytes = size_t(rows) * 4;
     ws->middle_bytes = A * I * 4;
     ws->row_max_bytes = A * 4;
     ws->expert_out_bytes = A * H * 4;
     ws->out_bytes = size_t(rows) * H * 4;
-    ws->schedule_bytes = (4 * A + 2 * size_t(rows) * ws->slots) * 4;
+    ws->upload_bytes = upload_capacity(rows, ws->slots, H);
     bool ok = true;
     try { ws->groups.resize(size_t(config->weights.routed_experts + config->weights.shared_expert)); } catch (...) { ok = false; }
-    ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->input), ws->input_bytes) &&
-         !device_alloc(domain, reinterpret_cast<void**>(&ws->codes), ws->codes_bytes) &&
+    ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->codes), ws->codes_bytes) &&
          !device_alloc(domain, reinterpret_cast<void**>(&ws->in_scales), ws->in_scale_bytes) &&
          !device_alloc(domain, reinterpret_cast<void**>(&ws->middle), ws->middle_bytes) &&
          !device_alloc(domain, reinterpret_cast<void**>(&ws->row_max), ws->row_max_bytes) &&
          !device_alloc(domain, reinterpret_cast<void**>(&ws->expert_out), ws->expert_out_bytes) &&
          !device_alloc(domain, reinterpret_cast<void**>(&ws->out), ws->out_bytes) &&
-         !device_alloc(domain, reinterpret_cast<void**>(&ws->schedule), ws->schedule_bytes) &&
+         !device_alloc(domain, reinterpret_cast<void**>(&ws->upload), ws->upload_bytes) &&
          !device_alloc(domain, reinterpret_cast<void**>(&ws->status), sizeof(Status));
     ok = ok && cudaStreamCreateWithFlags(&ws->stream, cudaStreamNonBlocking) == cudaSuccess &&
-         cudaMallocHost(reinterpret_cast<void**>(&ws->host_schedule), ws->schedule_bytes) == cudaSuccess &&
+         cudaMallocHost(reinterpret_cast<void**>(&ws->host_upload), ws->upload_bytes) == cudaSuccess &&
          cudaMallocHost(reinterpret_cast<void**>(&ws->host_status), sizeof(Status)) == cudaSuccess;
     for (auto& e : ws->events) ok = ok && cudaEventCreate(&e) == cudaSuccess;
-    ok = ok && cudaMemsetAsync(ws->status, 0, sizeof(Status), ws->stream) == cudaSuccess && cudaStreamSynchronize(ws->stream) == cudaSuccess;
+    ok = ok && cudaMemsetAsync(ws->status, 0, sizeof(Status), ws->stream) == cudaSuccess &&
+         cudaMemsetAsync(ws->row_max, 0, ws->row_max_bytes, ws->stream) == cudaSuccess &&     // every run leaves them zero again
+         cudaStreamSynchronize(ws->stream) == cudaSuccess;
     if (!ok) { cudaGetLastError(); workspace_destroy(ws); return nullptr; }
     return ws;
 }
@@ -396,8 +423,8 @@ extern "C" uint64_t rk_npu_moe_w8_weights_device_bytes(const rk_npu_moe_w8_weigh
 }
 extern "C" uint64_t rk_npu_moe_w8_workspace_device_bytes(const rk_npu_moe_w8_workspace* ws)
 {
-    return ws ? uint64_t(ws->input_bytes + ws->codes_bytes + ws->in_scale_bytes + ws->middle_bytes + ws->row_max_bytes +
-                         ws->expert_out_bytes + ws->out_bytes + ws->schedule_bytes + sizeof(Status))
+    return ws ? uint64_t(ws->codes_bytes + ws->in_scale_bytes + ws->middle_bytes + ws->row_max_bytes + ws->expert_out_bytes +
+                         ws->out_bytes + ws->upload_bytes + sizeof(Status))
               : 0;
 }
 

@@ -67,6 +67,7 @@ struct MoeCombineParams {
     const int* slot_assign;      // [rows][slots] assignment index, -1: the slot takes no part
     const float* coefficients;   // [rows][slots]
     float* out;                  // [rows][H]
+    uint32_t* row_max;           // [assignments] cleared here for the next run
     int rows, slots, H;
 };
 

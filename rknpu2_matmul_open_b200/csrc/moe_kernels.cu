@@ -8,22 +8,25 @@
 // rows sit in shared memory; sums are exact int32.
 //
 //   moe_quantize_kernel   fp32 rows -> int8 codes + scales, nearest-even, scale = max/127 (1 for a zero row)
-//   moe_gate_up_kernel    per (job, 64 features): gate and up sums of the same feature in the same thread,
+//   moe_gate_up_kernel    per (job, 64 features): gate and up sums of the same feature in the same thread (two warps
+//                         per 16 features, half of K each, summed through shared memory),
 //                         (float(sum) * s_in) * s_w, y = silu(gate) * up (degree-7 polynomial shared with the dense
 //                         path), fp32 middle rows + atomicMax of |y| bit patterns per assignment
-//   moe_down_kernel       per (job, 128 columns): re-quantises the job's middle rows into shared memory with the
+//   moe_down_kernel       per (job, 256 columns): re-quantises the job's middle rows into shared memory with the
 //                         row scale max/127 (nearest-even), int8 GEMM over I, (float(sum) * s_mid) * s_w
 //   moe_combine_kernel    out[token] = sum over the token's slots, in slot order, one fused multiply-add each
 #include "moe_device.h"
 #include "w4a8_math.cuh"
+#include "w4a8_ptx.cuh"
 #include <algorithm>
 
 namespace rkb200 {
 
 namespace {
-constexpr int MOE_WARPS = 4;
+constexpr int MOE_FEATURE_BLOCKS = 4;    // gate/up kernel: blocks of 16 features per CTA; two warps share one, half of K each
+constexpr int MOE_WARPS = 2 * MOE_FEATURE_BLOCKS;
 constexpr int MOE_THREADS = 32 * MOE_WARPS;
-constexpr int MOE_DOWN_BLOCKS = 2;       // 16-channel blocks per warp of the down kernel
+constexpr int MOE_DOWN_BLOCKS = 2;       // 16-channel blocks per warp of the down kernel (a CTA covers 256 columns)
 constexpr int MOE_ROW_PAD = 16;          // bytes between activation rows in shared memory beyond K: conflict-free fragment loads
 
 __device__ __forceinline__ int8_t nearest_even_code(float v)
@@ -31,31 +34,53 @@ __device__ __forceinline__ int8_t nearest_even_code(float v)
     return (int8_t)__float2int_rn(fminf(fmaxf(v, -127.f), 127.f));
 }
 
-// One 16-channel block against up to 16 activation rows in shared memory: c[half][4] += W(16 x K) * X^T.
-// Fragment mapping of m16n8k32 (g = lane / 4, t = lane % 4): A regs = channels g / g + 8 at k = 4t.. and 16 + 4t..;
-// B regs = token g at the same k; C regs = channels g, g + 8 x tokens 2t, 2t + 1.
-template <bool TWO>
-__device__ __forceinline__ void block_mma(const uint4* __restrict__ w, const uint8_t* xs, int row_bytes, int kq_count, int lane,
-                                          int (&c0)[4], int (&c1)[4])
+// NB 16-channel blocks (their records at w[0..NB)) against up to 16 activation rows in shared memory:
+// c[b][half] += W_b(16 x K) * X^T.  Fragment mapping of m16n8k32 (g = lane / 4, t = lane % 4): A regs = channels g / g + 8
+// at k = 4t.. and 16 + 4t..; B regs = token g at the same k; C regs = channels g, g + 8 x tokens 2t, 2t + 1.
+// The records of 128 k are double-buffered in registers: while one is multiplied the next is on its way.
+template <bool TWO, int NB>
+__device__ __forceinline__ void block_mma(const uint4* const (&w)[NB], const uint8_t* xs, int row_bytes, int kq_begin, int kq_count,
+                                          int lane, int (&c)[NB][2][4])
 {
     const int g = lane >> 2, t = lane & 3;
     const uint8_t* x0 = xs + (size_t)g * row_bytes + 4 * t;
     const uint8_t* x1 = x0 + (size_t)8 * row_bytes;
-    for (int kq = 0; kq < kq_count; ++kq) {
-        uint4 a[4];
+    uint4 even[NB][4], odd[NB][4];
+    auto fetch = [&](uint4 (&a)[NB][4], int kq) {
 #pragma unroll
-        for (int s = 0; s < 4; ++s) a[s] = __ldg(w + (size_t)(kq * 4 + s) * 32 + lane);
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int s = 0; s < 4; ++s) a[b][s] = __ldg(w[b] + (size_t)(kq * 4 + s) * 32 + lane);
+    };
+    auto multiply = [&](const uint4 (&a)[NB][4], int kq) {
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
             const int k = kq * MOE_KQ + s * 32;
             const uint32_t b0 = *reinterpret_cast<const uint32_t*>(x0 + k), b1 = *reinterpret_cast<const uint32_t*>(x0 + k + 16);
-            mma_s8(c0, a[s].x, a[s].y, a[s].z, a[s].w, b0, b1);
-            if (TWO) {
-                const uint32_t d0 = *reinterpret_cast<const uint32_t*>(x1 + k), d1 = *reinterpret_cast<const uint32_t*>(x1 + k + 16);
-                mma_s8(c1, a[s].x, a[s].y, a[s].z, a[s].w, d0, d1);
+            uint32_t d0 = 0, d1 = 0;
+            if (TWO) { d0 = *reinterpret_cast<const uint32_t*>(x1 + k); d1 = *reinterpret_cast<const uint32_t*>(x1 + k + 16); }
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                mma_s8(c[b][0], a[b][s].x, a[b][s].y, a[b][s].z, a[b][s].w, b0, b1);
+                if (TWO) mma_s8(c[b][1], a[b][s].x, a[b][s].y, a[b][s].z, a[b][s].w, d0, d1);
             }
         }
+    };
+    if (kq_begin >= kq_count) return;
+    fetch(even, kq_begin);
+    for (int kq = kq_begin; kq < kq_count; kq += 2) {
+        if (kq + 1 < kq_count) fetch(odd, kq + 1);
+        multiply(even, kq);
+        if (kq + 2 < kq_count) fetch(even, kq + 2);
+        if (kq + 1 < kq_count) multiply(odd, kq + 1);
     }
+}
+
+// Pulls `bytes` starting at p towards L2, one 128-byte line per lane and step (no data dependence: a hint only).
+__device__ __forceinline__ void warp_prefetch_l2(const void* p, size_t bytes, int lane)
+{
+    const char* c = reinterpret_cast<const char*>(p);
+    for (size_t off = (size_t)lane * 128; off < bytes; off += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(c + off));
 }
 } // namespace
 
@@ -121,11 +146,27 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gate_up_kernel(const MoeGateU
     extern __shared__ __align__(16) uint8_t xs[];
     __shared__ float s_scale[MOE_JOB_ROWS];
     __shared__ int s_token[MOE_JOB_ROWS];
+    __shared__ int s_partial[MOE_FEATURE_BLOCKS][16][32];
+    pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int job = blockIdx.y;
+    // the schedule was uploaded before any kernel of this run started; the weights never change
     const int expert = p.sched.job_expert[job], first = p.sched.job_first[job], rows = p.sched.job_rows[job];
     const int kq_count = (p.H + MOE_KQ - 1) / MOE_KQ;
     const int row_bytes = kq_count * MOE_KQ + MOE_ROW_PAD;
+    const int fbi = warp % MOE_FEATURE_BLOCKS, k_half = warp / MOE_FEATURE_BLOCKS;
+    const int fb = blockIdx.x * MOE_FEATURE_BLOCKS + fbi;     // block of 16 features
+    const bool live = fb * 16 < p.I;
+    const int kq_mid = (kq_count + 1) / 2;
+    const int kq_begin = k_half ? kq_mid : 0, kq_end = k_half ? kq_count : kq_mid;
+    const uint4* base = reinterpret_cast<const uint4*>(p.packed + (size_t)expert * p.expert_bytes);
+    const size_t block_vecs = (size_t)kq_count * 4 * 32;
+    const uint4* const w[2] = {base + (size_t)fb * block_vecs, base + (size_t)(p.I / 16 + fb) * block_vecs};
+    if (live && kq_end > kq_begin) {
+        warp_prefetch_l2(w[0] + (size_t)kq_begin * 128, (size_t)(kq_end - kq_begin) * 2048, lane);
+        warp_prefetch_l2(w[1] + (size_t)kq_begin * 128, (size_t)(kq_end - kq_begin) * 2048, lane);
+    }
+    pdl_wait();                                       // fp32 entry: the codes and scales come from the quantise kernel
     if (tid < MOE_JOB_ROWS) {
         const int token = tid < rows ? p.sched.assign_token[first + tid] : -1;
         s_token[tid] = token;
@@ -139,23 +180,25 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gate_up_kernel(const MoeGateU
             const int r = i / vec_per_row, v = i - r * vec_per_row;
             const int token = s_token[r];
             uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (token >= 0 && v < h_vec) val = __ldg(reinterpret_cast<const uint4*>(p.codes + (size_t)token * p.H) + v);
+            if (token >= 0 && v < h_vec) val = *(reinterpret_cast<const uint4*>(p.codes + (size_t)token * p.H) + v);
             *reinterpret_cast<uint4*>(xs + (size_t)r * row_bytes + 16 * v) = val;
         }
     }
     __syncthreads();
-    const int fb = blockIdx.x * MOE_WARPS + warp;     // block of 16 features
-    if (fb * 16 >= p.I) return;
-    const uint4* base = reinterpret_cast<const uint4*>(p.packed + (size_t)expert * p.expert_bytes);
-    const size_t block_vecs = (size_t)kq_count * 4 * 32;
-    int cg0[4] = {0, 0, 0, 0}, cg1[4] = {0, 0, 0, 0}, cu0[4] = {0, 0, 0, 0}, cu1[4] = {0, 0, 0, 0};
-    if (rows > 8) {
-        block_mma<true>(base + (size_t)fb * block_vecs, xs, row_bytes, kq_count, lane, cg0, cg1);
-        block_mma<true>(base + (size_t)(p.I / 16 + fb) * block_vecs, xs, row_bytes, kq_count, lane, cu0, cu1);
-    } else {
-        block_mma<false>(base + (size_t)fb * block_vecs, xs, row_bytes, kq_count, lane, cg0, cg1);
-        block_mma<false>(base + (size_t)(p.I / 16 + fb) * block_vecs, xs, row_bytes, kq_count, lane, cu0, cu1);
+    int c[2][2][4] = {};                              // [gate | up][token half][fragment]
+    if (live) {
+        if (rows > 8) block_mma<true, 2>(w, xs, row_bytes, kq_begin, kq_end, lane, c);
+        else block_mma<false, 2>(w, xs, row_bytes, kq_begin, kq_end, lane, c);
     }
+    // the warp with the upper half of K hands its sums to its partner
+    if (k_half == 1) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) s_partial[fbi][i][lane] = c[i >> 3][(i >> 2) & 1][i & 3];
+    }
+    __syncthreads();
+    if (k_half == 1 || !live) return;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) c[i >> 3][(i >> 2) & 1][i & 3] += s_partial[fbi][i][lane];
     const int g = lane >> 2, t = lane & 3;
     const float* ws = p.w_scales + (size_t)expert * 2 * p.I;
     float wg[2], wu[2];
@@ -164,15 +207,13 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gate_up_kernel(const MoeGateU
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         if (half == 1 && rows <= 8) break;
-        const int (&cg)[4] = half ? cg1 : cg0;
-        const int (&cu)[4] = half ? cu1 : cu0;
         uint32_t mx[2] = {0u, 0u};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int r = half * 8 + 2 * t + (i & 1), h = i >> 1;
             if (r < rows) {
                 const float sc = s_scale[r];
-                const float y = __fmul_rn(silu_poly(dequant(cg[i], sc, wg[h])), dequant(cu[i], sc, wu[h]));
+                const float y = __fmul_rn(silu_poly(dequant(c[0][half][i], sc, wg[h])), dequant(c[1][half][i], sc, wu[h]));
                 p.middle[(size_t)(first + r) * p.I + fb * 16 + g + 8 * h] = y;
                 mx[i & 1] = max(mx[i & 1], __float_as_uint(y) & 0x7fffffffu);
             }
@@ -194,11 +235,20 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_down_kernel(const MoeDownPara
 {
     extern __shared__ __align__(16) uint8_t xs[];
     __shared__ float s_scale[MOE_JOB_ROWS], s_inverse[MOE_JOB_ROWS];
+    pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int job = blockIdx.y;
     const int expert = p.sched.job_expert[job], first = p.sched.job_first[job], rows = p.sched.job_rows[job];
     const int kq_count = (p.I + MOE_KQ - 1) / MOE_KQ;
     const int row_bytes = kq_count * MOE_KQ + MOE_ROW_PAD;
+    const uint4* base = reinterpret_cast<const uint4*>(p.packed + (size_t)expert * p.expert_bytes);
+    const size_t block_vecs = (size_t)kq_count * 4 * 32;
+    const int cb0 = (blockIdx.x * MOE_WARPS + warp) * MOE_DOWN_BLOCKS;
+    {   // this warp's weights on their way to L2 while the gate/up launch still runs
+        const int blocks = min(MOE_DOWN_BLOCKS, p.H / 16 - cb0);
+        if (blocks > 0) warp_prefetch_l2(base + (size_t)cb0 * block_vecs, (size_t)blocks * block_vecs * 16, lane);
+    }
+    pdl_wait();                                       // the middle rows and their maxima come from the launch in front
     if (tid < MOE_JOB_ROWS) {
         // src/rk_npu_moe_cpu.cpp:78-80: scale = max/127, 1 for an all-zero row; inverse = 1/scale
         const uint32_t m = tid < rows ? p.row_max[first + tid] : 0u;
@@ -222,26 +272,24 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_down_kernel(const MoeDownPara
         }
     }
     __syncthreads();
-    const uint4* base = reinterpret_cast<const uint4*>(p.packed + (size_t)expert * p.expert_bytes);
-    const size_t block_vecs = (size_t)kq_count * 4 * 32;
     const float* ws = p.w_scales + (size_t)expert * p.H;
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll 1
     for (int b = 0; b < MOE_DOWN_BLOCKS; ++b) {
-        const int cb = (blockIdx.x * MOE_WARPS + warp) * MOE_DOWN_BLOCKS + b;
+        const int cb = cb0 + b;
         if (cb * 16 >= p.H) break;
-        int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
-        if (rows > 8) block_mma<true>(base + (size_t)cb * block_vecs, xs, row_bytes, kq_count, lane, c0, c1);
-        else block_mma<false>(base + (size_t)cb * block_vecs, xs, row_bytes, kq_count, lane, c0, c1);
+        int c[1][2][4] = {};
+        const uint4* const w[1] = {base + (size_t)cb * block_vecs};
+        if (rows > 8) block_mma<true, 1>(w, xs, row_bytes, 0, kq_count, lane, c);
+        else block_mma<false, 1>(w, xs, row_bytes, 0, kq_count, lane, c);
         const float w0 = __ldg(ws + cb * 16 + g), w1 = __ldg(ws + cb * 16 + g + 8);
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             if (half == 1 && rows <= 8) break;
-            const int (&c)[4] = half ? c1 : c0;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int r = half * 8 + 2 * t + (i & 1), h = i >> 1;
-                if (r < rows) p.expert_out[(size_t)(first + r) * p.H + cb * 16 + g + 8 * h] = dequant(c[i], s_scale[r], h ? w1 : w0);
+                if (r < rows) p.expert_out[(size_t)(first + r) * p.H + cb * 16 + g + 8 * h] = dequant(c[0][half][i], s_scale[r], h ? w1 : w0);
             }
         }
     }
@@ -250,8 +298,15 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_down_kernel(const MoeDownPara
 // ------------------------------------------------------------------ weighted sum over a token's slots (src/rk_npu_moe_w8.cpp:786-816)
 __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombineParams p)
 {
+    pdl_launch_dependents();
     const int token = blockIdx.y;
     const int n = blockIdx.x * 256 + threadIdx.x;
+    pdl_wait();
+    // the row maxima have been consumed by the down projection: leave them zero for the next run
+    if (blockIdx.x == 0 && threadIdx.x < p.slots) {
+        const int a = p.slot_assign[token * p.slots + threadIdx.x];
+        if (a >= 0) p.row_max[a] = 0u;
+    }
     if (n >= p.H) return;
     float sum = 0.f;
     for (int slot = 0; slot < p.slots; ++slot) {
@@ -291,15 +346,32 @@ static cudaError_t allow_shared(const void* kernel, size_t bytes, PerDeviceOnce&
     return bytes <= 200 * 1024 ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// one launch that may start while the kernel in front of it on the stream still runs (each kernel above waits
+// with griddepcontrol.wait before it touches what that kernel writes)
+template <class Params>
+static cudaError_t launch_dependent(void (*kernel)(const Params), dim3 grid, unsigned threads, size_t smem, cudaStream_t stream, const Params& p)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 cudaError_t launch_moe_gate_up(const MoeGateUpParams& p, cudaStream_t stream)
 {
     static PerDeviceOnce once;
     static size_t allowed = 0;
     const size_t smem = size_t(MOE_JOB_ROWS) * ((p.H + MOE_KQ - 1) / MOE_KQ * MOE_KQ + MOE_ROW_PAD);
     if (const cudaError_t e = allow_shared(reinterpret_cast<const void*>(moe_gate_up_kernel), smem, once, allowed)) return e;
-    const dim3 grid((p.I / 16 + MOE_WARPS - 1) / MOE_WARPS, p.sched.jobs);
-    moe_gate_up_kernel<<<grid, MOE_THREADS, smem, stream>>>(p);
-    return cudaGetLastError();
+    const dim3 grid((p.I / 16 + MOE_FEATURE_BLOCKS - 1) / MOE_FEATURE_BLOCKS, p.sched.jobs);
+    return launch_dependent(moe_gate_up_kernel, grid, MOE_THREADS, smem, stream, p);
 }
 
 cudaError_t launch_moe_down(const MoeDownParams& p, cudaStream_t stream)
@@ -307,15 +379,13 @@ cudaError_t launch_moe_down(const MoeDownParams& p, cudaStream_t stream)
     const size_t smem = size_t(MOE_JOB_ROWS) * ((p.I + MOE_KQ - 1) / MOE_KQ * MOE_KQ + MOE_ROW_PAD);   // I <= 512: 8.4 KB
     const int per_cta = 16 * MOE_WARPS * MOE_DOWN_BLOCKS;
     const dim3 grid((p.H + per_cta - 1) / per_cta, p.sched.jobs);
-    moe_down_kernel<<<grid, MOE_THREADS, smem, stream>>>(p);
-    return cudaGetLastError();
+    return launch_dependent(moe_down_kernel, grid, MOE_THREADS, smem, stream, p);
 }
 
 cudaError_t launch_moe_combine(const MoeCombineParams& p, cudaStream_t stream)
 {
     const dim3 grid((p.H + 255) / 256, p.rows);
-    moe_combine_kernel<<<grid, 256, 0, stream>>>(p);
-    return cudaGetLastError();
+    return launch_dependent(moe_combine_kernel, grid, 256, 0, stream, p);
 }
 
 } // namespace rkb200
