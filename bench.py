@@ -856,6 +856,7 @@ def run_case(args):
       prefill  one 2048 x 4096 x 14336 linear, binary16
       mid      one 128 x 11008 x 8192 linear, binary16 (few tiles, long K)
       ffn      gate/up 4096 -> 2 x 14336, SwiGLU, down 14336 -> 4096 at M = 1024, fp32
+      moe      routed experts: 128 + 1 int8 experts, hidden 1536, intermediate 512, top-8, 64 rows (--case-tokens)
     --stamps enables the kernels' phase stamps after the launches, runs the set again (the decode set as one CUDA
     graph, the steady state of a dependent chain) and prints them."""
     import torch
@@ -868,6 +869,32 @@ def run_case(args):
     dev = torch.device("cuda", ctx.device)
     stream = torch.cuda.Stream(device=dev)
     calls = []
+    if args.case == "moe":
+        # routed experts, the geometry of the bench's `moe` figures; blocking calls with host arrays
+        from rknpu2_matmul_open_b200 import moe
+        rows = args.case_tokens or 64
+        H, I, R, shared, top = 1536, 512, 128, 1, 8
+        E = R + shared
+        ex = dict(gate_up=rng.integers(-127, 128, size=(E, H, 2 * I), dtype=np.int8),
+                  gate_up_scales=rng.uniform(2e-4, 6e-4, size=(E, 2 * I)).astype(np.float32),
+                  down=rng.integers(-127, 128, size=(E, I, H), dtype=np.int8),
+                  down_scales=rng.uniform(1e-3, 3e-3, size=(E, H)).astype(np.float32))
+        w = moe.MoeWeights(dom, shared_expert=shared, **ex)
+        ws = moe.MoeWorkspace(dom, moe.default_config(H, I, R, shared, top, max(rows, 1)))
+        codes = rng.integers(-127, 128, size=(rows, H), dtype=np.int8)
+        scales = rng.uniform(0.01, 0.05, size=rows).astype(np.float32)
+        ids = np.stack([rng.choice(R, size=top, replace=False) for _ in range(rows)]).astype(np.int32)
+        routes = rng.uniform(0.05, 0.3, size=(rows, top)).astype(np.float32)
+        out = np.zeros((rows, H), np.float32)
+        t0 = time.perf_counter()
+        for _ in range(args.repeat):
+            rc = ws.run_quantized(w, codes, scales, ids, routes, out, None)
+            if rc:
+                raise RuntimeError(f"rk_npu_moe_w8_run_quantized failed: {rc}")
+        active = len(set(ids.reshape(-1).tolist())) + shared
+        print(f"moe: rows={rows}, {active} active experts ({active * 3 * H * I / 1e6:.1f} MB of int8 weights per call), "
+              f"{(time.perf_counter() - t0) / args.repeat * 1e6:.1f} us per call over {args.repeat} calls")
+        return
     if args.case in ("decode", "prefill", "mid"):
         M = args.case_tokens or {"decode": 8, "prefill": 2048, "mid": 128}[args.case]
         shapes = {"decode": LLAMA7B_LAYER, "prefill": [(4096, 14336)], "mid": [(11008, 8192)]}[args.case]
@@ -984,7 +1011,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--quick", action="store_true")
-    ap.add_argument("--case", choices=["decode", "prefill", "mid", "ffn"], help="run a small profiler workload instead of the benchmark")
+    ap.add_argument("--case", choices=["decode", "prefill", "mid", "ffn", "moe"], help="run a small profiler workload instead of the benchmark")
     ap.add_argument("--repeat", type=int, default=4, help="--case: launch sets")
     ap.add_argument("--case-tokens", type=int, default=0, help="--case: override the batch")
     ap.add_argument("--stamps", action="store_true", help="--case: print the kernels' phase stamps")
