@@ -1,13 +1,17 @@
 /* rknpu_b200_moe.h -- the original project's routed-experts header (include/rk_npu_moe_w8.h) as this library
- * implements it: routed SwiGLU experts with int8 weights plus an optional shared expert; the router is the caller's.
+ * implements it: routed SwiGLU experts with int8 or int4 weights plus an optional shared expert; the router is the
+ * caller's.
  *
- * Built: configuration, int8 expert weight objects, workspaces, the two blocking run calls (int8 rows with scales, or
- * fp32 rows quantised here), the byte queries.  All pointers are host pointers and a call returns when the output is
- * complete, as in the original.
- * Exported but declined (NULL / RK_NPU_ERR_PARAM / 0, nothing else happens): the int4 expert forms
- * (rk_npu_moe_quant_*, rk_npu_moe_w4_*), whose weight "certification" describes INT16 partial sums of the original
- * device, their slot banks and native cache records; RK_NPU_MOE_MIDDLE_NPU_LUT, the original device's approximate
- * table-lookup activation (a workspace that asks for it is not created).
+ * Built: configuration, immutable expert weight objects (int8 experts; int4 experts; routed int4 experts with an int8
+ * shared expert), workspaces of the matching form, the two blocking run calls (int8 rows with scales, or fp32 rows
+ * quantised here), the byte queries.  All pointers are host pointers and a call returns when the output is complete, as
+ * in the original.  Int4 experts are given as int8 arrays of codes in [-8, 7]; they are accepted under the original's
+ * rule (the K tile its device would run must be certified against INT16 partial sums: the whole of K where it would try
+ * that, else slices of 512) and are then stored and multiplied like int8 experts -- the sums are the same integers.
+ * Exported but declined (NULL / RK_NPU_ERR_PARAM / 0, nothing else happens): the mutable slot banks and the native
+ * cache records they import and export (rk_npu_moe_*_slots_create, *_export_expert, *_import_expert*, *_swap_slots,
+ * *_expert_blob_bytes); RK_NPU_MOE_MIDDLE_NPU_LUT, the original device's approximate table-lookup activation (a
+ * workspace that asks for it is not created).
  * Programs may include the original header instead of this one; names, layouts and values are the same.
  */
 #ifndef RKNPU_B200_MOE_H
@@ -99,7 +103,10 @@ int rk_npu_moe_w8_run_f32(rk_npu_moe_w8_workspace* workspace, const rk_npu_moe_w
                           const float* input, const int32_t* expert_ids, const float* route_weights, float* output,
                           rk_npu_moe_w8_timings* timings);
 
-/* ---- declined (see the head of this file): include/rk_npu_moe_w8.h:87-146 */
+/* include/rk_npu_moe_w8.h:87-111: all experts int4 (..._quant_...; _full_k also tries the whole of K for gate/up), or
+ * routed int4 experts with an int8 shared expert (..._w4_...).  hidden and intermediate multiples of 64, hidden <= 8128,
+ * normal input; NULL when a code is outside [-8, 7] or the tile cannot be certified.  The handles use the run / free /
+ * byte-query functions above; a workspace runs weights of its own form only (RK_NPU_ERR_PARAM otherwise). */
 rk_npu_moe_w8_weights* rk_npu_moe_quant_weights_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
                                                        const rk_npu_moe_w8_expert* experts);
 rk_npu_moe_w8_weights* rk_npu_moe_quant_weights_create_full_k(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
@@ -108,6 +115,7 @@ rk_npu_moe_w8_workspace* rk_npu_moe_quant_workspace_create(rk_npu_iommu_domain* 
 rk_npu_moe_w8_weights* rk_npu_moe_w4_weights_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
                                                     const rk_npu_moe_w8_expert* experts);
 rk_npu_moe_w8_workspace* rk_npu_moe_w4_workspace_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_config* config);
+/* ---- declined (see the head of this file): include/rk_npu_moe_w8.h:113-146 */
 rk_npu_moe_w8_weights* rk_npu_moe_w4_slots_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
                                                   const rk_npu_moe_w8_expert* shared);
 rk_npu_moe_w8_weights* rk_npu_moe_quant_slots_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config);

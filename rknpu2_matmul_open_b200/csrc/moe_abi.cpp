@@ -1,5 +1,5 @@
-// moe_abi.cpp -- the routed-experts operator of the original's include/rk_npu_moe_w8.h on this library: int8 expert
-// weight objects, workspaces, the two blocking run calls.
+// moe_abi.cpp -- the routed-experts operator of the original's include/rk_npu_moe_w8.h on this library: immutable expert
+// weight objects (int8, int4, or int4 routed experts with an int8 shared one), workspaces, the two blocking run calls.
 //
 // The original (src/rk_npu_moe_w8.cpp:570-817) quantises the input rows on the CPU, groups the (token, slot)
 // assignments by expert, gathers and multiplies on the NPU, runs the middle stage and the weighted combine on the
@@ -42,6 +42,16 @@ bool valid_config(const rk_npu_moe_w8_config& c)           // src/rk_npu_moe_w8.
            c.cpu_threads <= 4 && (c.native_input == 0 || c.native_input == 1) && c.timeout_ms >= 1 && c.timeout_ms <= 60000 &&
            c.middle == RK_NPU_MOE_MIDDLE_CPU;
 }
+// src/rk_npu_moe_w8.cpp:368-389: which experts hold int4 codes.  Int4 experts are checked like the dense W4A8 weights
+// (codes in [-8, 7]; the K tile the original would run must be certified against its INT16 partial sums) and then
+// stored and multiplied exactly like int8 experts: the sums are the same integers.
+enum class Mode { W8 = 0, RoutedW4SharedW8 = 1, W4 = 2 };
+bool expert_is_w4(Mode mode, int expert, int routed) { return mode == Mode::W4 || (mode == Mode::RoutedW4SharedW8 && expert < routed); }
+bool can_use_full_gate(int hidden) { return hidden > 512 && hidden <= 2048; }
+bool valid_w4(const rk_npu_moe_w8_weight_config& c)
+{
+    return valid_weights(c) && c.hidden % 64 == 0 && c.intermediate % 64 == 0 && c.hidden <= 8128;
+}
 bool finite_positive(float x) { return std::isfinite(x) && x > 0.0f; }
 bool overlap(const void* a, size_t na, const void* b, size_t nb)
 {
@@ -61,6 +71,7 @@ struct rk_npu_moe_w8_weights {
     uint64_t ctx_id = 0;
     uint32_t domain_id = 0;
     rk_npu_moe_w8_weight_config config{};
+    Mode mode = Mode::W8;
     uint8_t* gate_up = nullptr;   // [E] records of the [H, 2I] matrices
     uint8_t* down = nullptr;      // [E] records of the [I, H] matrices
     float* gate_up_scales = nullptr, *down_scales = nullptr;
@@ -73,6 +84,7 @@ struct rk_npu_moe_w8_workspace {
     uint64_t ctx_id = 0;
     uint32_t domain_id = 0;
     rk_npu_moe_w8_config config{};
+    Mode mode = Mode::W8;
     std::atomic_flag busy = ATOMIC_FLAG_INIT;
     cudaStream_t stream = nullptr;
     cudaEvent_t events[5] = {};
@@ -220,7 +232,7 @@ int moe_run(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int row
     Lock lock(*ws);
     if (!lock.held) return RK_NPU_ERR_BUSY;
     const auto begin = Clock::now();
-    if (!same_weights(c.weights, w->config)) return RK_NPU_ERR_PARAM;
+    if (ws->mode != w->mode || !same_weights(c.weights, w->config)) return RK_NPU_ERR_PARAM;
     if (w->ctx_id != ws->ctx_id || w->domain_id != ws->domain_id) return RK_NPU_ERR_DOMAIN;
     for (size_t i = 0; i < routed; ++i)
         if (ids[i] < 0 || ids[i] >= R || !std::isfinite(routes[i]) || routes[i] < 0.0f) return RK_NPU_ERR_PARAM;
@@ -320,18 +332,33 @@ extern "C" void rk_npu_moe_w8_config_init(rk_npu_moe_w8_config* c, int hidden, i
                                      RK_NPU_MOE_MIDDLE_CPU, 1000};
 }
 
-extern "C" rk_npu_moe_w8_weights* rk_npu_moe_w8_weights_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
-                                                               const rk_npu_moe_w8_expert* experts)
+namespace {
+rk_npu_moe_w8_weights* weights_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
+                                      const rk_npu_moe_w8_expert* experts, Mode mode, bool certify_full_k)
 {
-    if (!domain || !domain->ctx || !config || !experts || !valid_weights(*config) || domain->ctx->world > 1) return nullptr;
+    if (!domain || !domain->ctx || !config || !experts || !(mode == Mode::W8 ? valid_weights(*config) : valid_w4(*config)) ||
+        domain->ctx->world > 1)
+        return nullptr;
     const int H = config->hidden, I = config->intermediate, E = config->routed_experts + config->shared_expert;
-    for (int e = 0; e < E; ++e) {       // src/rk_npu_moe_w8.cpp:453-457
+    for (int e = 0; e < E; ++e) {       // src/rk_npu_moe_w8.cpp:453-474
         const auto& x = experts[e];
         if (!x.gate_up || !x.down || !x.gate_up_scales || !x.down_scales) return nullptr;
         for (int n = 0; n < 2 * I; ++n)
             if (!finite_positive(x.gate_up_scales[n])) return nullptr;
         for (int n = 0; n < H; ++n)
             if (!finite_positive(x.down_scales[n])) return nullptr;
+        if (expert_is_w4(mode, e, config->routed_experts)) {
+            // gate/up: the whole of K where the original would try it (and its 512 slices as the fallback), else slices
+            // of at most 512; down: the whole of K = intermediate
+            WeightBound bound;
+            const int slice = std::min(H, 512);
+            const bool try_full = (certify_full_k || mode == Mode::RoutedW4SharedW8) && can_use_full_gate(H);
+            try {
+                if (bound_weights(H, 2 * I, x.gate_up, try_full ? H : slice, bound, try_full ? slice : 0) != RK_NPU_OK ||
+                    bound_weights(I, H, x.down, I, bound) != RK_NPU_OK)
+                    return nullptr;
+            } catch (...) { return nullptr; }
+        }
     }
     rk_npu_ctx* ctx = domain->ctx;
     if (cudaSetDevice(ctx->device) != cudaSuccess) return nullptr;
@@ -341,6 +368,7 @@ extern "C" rk_npu_moe_w8_weights* rk_npu_moe_w8_weights_create(rk_npu_iommu_doma
     w->ctx_id = ctx->id;
     w->domain_id = domain->id;
     w->config = *config;
+    w->mode = mode;
     domain_retain(domain);
     w->gate_up_expert_bytes = moe_packed_bytes(H, 2 * I);
     w->down_expert_bytes = moe_packed_bytes(I, H);
@@ -370,11 +398,20 @@ extern "C" rk_npu_moe_w8_weights* rk_npu_moe_w8_weights_create(rk_npu_iommu_doma
     if (!ok) { cudaGetLastError(); weights_destroy(w); return nullptr; }
     return w;
 }
+} // namespace
+
+extern "C" rk_npu_moe_w8_weights* rk_npu_moe_w8_weights_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
+                                                               const rk_npu_moe_w8_expert* experts)
+{
+    return weights_create(domain, config, experts, Mode::W8, false);
+}
 extern "C" void rk_npu_moe_w8_weights_free(rk_npu_moe_w8_weights* w) { weights_destroy(w); }
 
-extern "C" rk_npu_moe_w8_workspace* rk_npu_moe_w8_workspace_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_config* config)
+namespace {
+rk_npu_moe_w8_workspace* workspace_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_config* config, Mode mode)
 {
     if (!domain || !domain->ctx || !config || !valid_config(*config) || domain->ctx->world > 1) return nullptr;
+    if (mode != Mode::W8 && (!valid_w4(config->weights) || config->native_input)) return nullptr;   // src/rk_npu_moe_w8.cpp:892-893
     rk_npu_ctx* ctx = domain->ctx;
     if (cudaSetDevice(ctx->device) != cudaSuccess) return nullptr;
     rk_npu_moe_w8_workspace* ws = nullptr;
@@ -383,6 +420,7 @@ extern "C" rk_npu_moe_w8_workspace* rk_npu_moe_w8_workspace_create(rk_npu_iommu_
     ws->ctx_id = ctx->id;
     ws->domain_id = domain->id;
     ws->config = *config;
+    ws->mode = mode;
     domain_retain(domain);
     const int H = config->weights.hidden, I = config->weights.intermediate, rows = config->max_rows;
     ws->slots = config->top_k + config->weights.shared_expert;
@@ -415,6 +453,12 @@ extern "C" rk_npu_moe_w8_workspace* rk_npu_moe_w8_workspace_create(rk_npu_iommu_
     if (!ok) { cudaGetLastError(); workspace_destroy(ws); return nullptr; }
     return ws;
 }
+} // namespace
+
+extern "C" rk_npu_moe_w8_workspace* rk_npu_moe_w8_workspace_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_config* config)
+{
+    return workspace_create(domain, config, Mode::W8);
+}
 extern "C" void rk_npu_moe_w8_workspace_free(rk_npu_moe_w8_workspace* ws) { workspace_destroy(ws); }
 
 extern "C" uint64_t rk_npu_moe_w8_weights_device_bytes(const rk_npu_moe_w8_weights* w)
@@ -440,12 +484,33 @@ extern "C" int rk_npu_moe_w8_run_f32(rk_npu_moe_w8_workspace* ws, const rk_npu_m
     return moe_run(ws, w, rows, input, true, nullptr, expert_ids, route_weights, output, timings);
 }
 
-// ---- the int4 expert forms, their slot banks and cache records: declined (include/rk_npu_moe_w8.h:87-146)
-extern "C" rk_npu_moe_w8_weights* rk_npu_moe_quant_weights_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_weight_config*, const rk_npu_moe_w8_expert*) { return nullptr; }
-extern "C" rk_npu_moe_w8_weights* rk_npu_moe_quant_weights_create_full_k(rk_npu_iommu_domain*, const rk_npu_moe_w8_weight_config*, const rk_npu_moe_w8_expert*) { return nullptr; }
-extern "C" rk_npu_moe_w8_workspace* rk_npu_moe_quant_workspace_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_config*) { return nullptr; }
-extern "C" rk_npu_moe_w8_weights* rk_npu_moe_w4_weights_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_weight_config*, const rk_npu_moe_w8_expert*) { return nullptr; }
-extern "C" rk_npu_moe_w8_workspace* rk_npu_moe_w4_workspace_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_config*) { return nullptr; }
+// ---- int4 experts (include/rk_npu_moe_w8.h:87-111): all experts int4, or routed int4 with an int8 shared expert.
+// The handles work with the same run / free / byte-query functions; a workspace runs weights of its own form only.
+extern "C" rk_npu_moe_w8_weights* rk_npu_moe_quant_weights_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
+                                                                  const rk_npu_moe_w8_expert* experts)
+{
+    return weights_create(domain, config, experts, Mode::W4, false);
+}
+extern "C" rk_npu_moe_w8_weights* rk_npu_moe_quant_weights_create_full_k(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
+                                                                         const rk_npu_moe_w8_expert* experts)
+{
+    return weights_create(domain, config, experts, Mode::W4, true);
+}
+extern "C" rk_npu_moe_w8_workspace* rk_npu_moe_quant_workspace_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_config* config)
+{
+    return workspace_create(domain, config, Mode::W4);
+}
+extern "C" rk_npu_moe_w8_weights* rk_npu_moe_w4_weights_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
+                                                               const rk_npu_moe_w8_expert* experts)
+{
+    return weights_create(domain, config, experts, Mode::RoutedW4SharedW8, false);
+}
+extern "C" rk_npu_moe_w8_workspace* rk_npu_moe_w4_workspace_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_config* config)
+{
+    return workspace_create(domain, config, Mode::RoutedW4SharedW8);
+}
+
+// ---- mutable slot banks and the native cache records they import and export: declined (include/rk_npu_moe_w8.h:113-146)
 extern "C" rk_npu_moe_w8_weights* rk_npu_moe_w4_slots_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_weight_config*, const rk_npu_moe_w8_expert*) { return nullptr; }
 extern "C" rk_npu_moe_w8_weights* rk_npu_moe_quant_slots_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_weight_config*) { return nullptr; }
 extern "C" uint64_t rk_npu_moe_quant_expert_blob_bytes(const rk_npu_moe_w8_weights*) { return 0; }

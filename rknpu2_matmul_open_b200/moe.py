@@ -26,7 +26,8 @@ class MoeWeights:
     """rk_npu_moe_w8_weights_create / _free.  gate_up [E, H, 2I] int8, gate_up_scales [E, 2I], down [E, I, H] int8,
     down_scales [E, H]; E = routed + shared experts, the shared one last."""
 
-    def __init__(self, domain, gate_up, gate_up_scales, down, down_scales, shared_expert: int = 0):
+    def __init__(self, domain, gate_up, gate_up_scales, down, down_scales, shared_expert: int = 0, form: str = "w8"):
+        """form: 'w8' int8 experts; 'quant' / 'quant_full_k' all experts int4 codes; 'w4' routed int4 + shared int8."""
         self.lib = capi.load()
         gate_up = np.ascontiguousarray(gate_up, np.int8)
         down = np.ascontiguousarray(down, np.int8)
@@ -37,9 +38,11 @@ class MoeWeights:
         experts = (MoeExpert * E)()
         for e in range(E):
             experts[e] = MoeExpert(_ptr(gate_up[e]), _ptr(gus[e]), _ptr(down[e]), _ptr(dns[e]))
-        self.handle = self.lib.rk_npu_moe_w8_weights_create(domain.handle, C.byref(self.config), experts)
+        name = {"w8": "rk_npu_moe_w8_weights_create", "quant": "rk_npu_moe_quant_weights_create",
+                "quant_full_k": "rk_npu_moe_quant_weights_create_full_k", "w4": "rk_npu_moe_w4_weights_create"}[form]
+        self.handle = getattr(self.lib, name)(domain.handle, C.byref(self.config), experts)
         if not self.handle:
-            raise W4A8Error(capi.RK_NPU_ERR_PARAM, "rk_npu_moe_w8_weights_create")
+            raise W4A8Error(capi.RK_NPU_ERR_PARAM, name)
 
     def device_bytes(self) -> int:
         return int(self.lib.rk_npu_moe_w8_weights_device_bytes(self.handle))
@@ -53,12 +56,14 @@ class MoeWeights:
 class MoeWorkspace:
     """rk_npu_moe_w8_workspace_create / _free and the two run calls."""
 
-    def __init__(self, domain, config: MoeConfig):
+    def __init__(self, domain, config: MoeConfig, form: str = "w8"):
         self.lib = capi.load()
         self.config = config
-        self.handle = self.lib.rk_npu_moe_w8_workspace_create(domain.handle, C.byref(config))
+        name = {"w8": "rk_npu_moe_w8_workspace_create", "quant": "rk_npu_moe_quant_workspace_create",
+                "quant_full_k": "rk_npu_moe_quant_workspace_create", "w4": "rk_npu_moe_w4_workspace_create"}[form]
+        self.handle = getattr(self.lib, name)(domain.handle, C.byref(config))
         if not self.handle:
-            raise W4A8Error(capi.RK_NPU_ERR_PARAM, "rk_npu_moe_w8_workspace_create")
+            raise W4A8Error(capi.RK_NPU_ERR_PARAM, name)
 
     def device_bytes(self) -> int:
         return int(self.lib.rk_npu_moe_w8_workspace_device_bytes(self.handle))

@@ -15,8 +15,9 @@ tests/test_moe_w8.cpp (routed experts; it includes the public header and a heade
 its default mode, the int8 experts: independent integer/float reference within 1e-6 relative L2 (that reference
 evaluates the sigmoid with std::exp, this library with the original's production polynomial), A/B/A weight
 rebinding, 1..256 rows, duplicate and zero-coefficient routes, nearest-even fp32 input, every rejection and the
-untouched output behind it, a foreign domain, empty routes.  Its --w4* modes exercise the int4 expert forms, which
-this library declines.
+untouched output behind it, a foreign domain, empty routes.  Its --w4, --w4-split and --w4-wide modes run the same checks
+on routed int4 experts with an int8 shared expert (a column that needs the 512 + 64 split; hidden size 8128).  Its
+--npu-middle mode asks for the original device's table-lookup activation, which is not offered.
 
 The binaries exist only where the reference tree was present at build time; otherwise the tests skip.
 """
@@ -32,7 +33,8 @@ BIN = Path(__file__).resolve().parents[1] / "oracle" / "_ref"
 
 @pytest.mark.parametrize("program,args", [("conformance_test_w4a8", []), ("conformance_test_w4a8_chain", []),
                                           ("conformance_test_w4a8_multiplier", ["--canary"]),
-                                          ("conformance_test_moe_w8", [])])
+                                          ("conformance_test_moe_w8", []), ("conformance_test_moe_w8", ["--w4"]),
+                                          ("conformance_test_moe_w8", ["--w4-split"]), ("conformance_test_moe_w8", ["--w4-wide"])])
 def test_reference_program_passes_against_this_library(program, args):
     exe = BIN / program
     if not exe.exists():

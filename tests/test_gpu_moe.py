@@ -225,3 +225,85 @@ def test_busy_workspace(gpu):
         t.join()
     assert set(codes_seen) <= {0, capi.RK_NPU_ERR_BUSY} and 0 in codes_seen
     ws.free(); w.free()
+
+
+@pytest.mark.parametrize("form", ["quant", "quant_full_k", "w4"])
+@pytest.mark.parametrize("geometry", [(576, 64, 3, 1, 2), (128, 128, 4, 0, 2), (8128, 64, 3, 1, 2)], ids=lambda g: "x".join(map(str, g)))
+def test_int4_expert_forms(gpu, oracle, form, geometry):
+    # include/rk_npu_moe_w8.h:87-111: experts given as int8 arrays of int4 codes.  Accepted where the original certifies
+    # the K tile its device would run (tests/test_moe_w8.cpp:68-69: a column of -8 overflows one INT16 partial over
+    # K = 576 but fits 512 + 64); the numbers are those of the same codes run as int8 experts.
+    _, dom, _ = gpu
+    H, I, routed, shared, top = geometry
+    E = routed + shared
+    rng = np.random.default_rng(H + I)
+    ex = dict(gate_up=rng.integers(-8, 8, size=(E, H, 2 * I), dtype=np.int8),
+              gate_up_scales=rng.uniform(2e-3, 6e-3, size=(E, 2 * I)).astype(np.float32),
+              down=rng.integers(-8, 8, size=(E, I, H), dtype=np.int8),
+              down_scales=rng.uniform(1e-3, 3e-3, size=(E, H)).astype(np.float32))
+    if H <= 2048:
+        ex["gate_up"][1, 1:, 0] = -8            # needs the 512 + 64 split at K = 576
+    if shared and form == "w4":
+        ex["gate_up"][E - 1, 3, 5] = 100            # the shared expert of the mixed form is int8
+    w = moe.MoeWeights(dom, shared_expert=shared, form=form, **ex)
+    ws = moe.MoeWorkspace(dom, moe.default_config(H, I, routed, shared, top, 8), form=form)
+    rows = 5
+    codes = rng.integers(-128, 128, size=(rows, H), dtype=np.int8)
+    scales = np.full(rows, 0.03125, np.float32)
+    ids, routes = make_routes(rows, routed, top, seed=3)
+    out = np.zeros((rows, H), np.float32)
+    rc_ref, ref = oracle.moe_run(ex, shared, top, codes, scales, ids, routes, mode=1)
+    assert rc_ref == 0 and ws.run_quantized(w, codes, scales, ids, routes, out) == 0
+    assert np.array_equal(bits(out), bits(ref))
+    # a workspace runs weights of its own form only (src/rk_npu_moe_w8.cpp:582)
+    w8 = moe.MoeWeights(dom, shared_expert=shared, **{k: (np.clip(v, -8, 7) if v.dtype == np.int8 else v) for k, v in ex.items()})
+    ws8 = moe.MoeWorkspace(dom, moe.default_config(H, I, routed, shared, top, 8))
+    saved = out.copy()
+    assert ws.run_quantized(w8, codes, scales, ids, routes, out) == capi.RK_NPU_ERR_PARAM
+    assert ws8.run_quantized(w, codes, scales, ids, routes, out) == capi.RK_NPU_ERR_PARAM
+    assert np.array_equal(bits(out), bits(saved))
+    for h in (ws8, w8, ws, w):
+        h.free()
+
+
+def test_int4_expert_forms_validate(gpu, oracle):
+    _, dom, _ = gpu
+    lib = capi.load()
+    H, I, E = 128, 64, 2
+    rng = np.random.default_rng(2)
+
+    def experts():
+        return dict(gate_up=rng.integers(-8, 8, size=(E, H, 2 * I), dtype=np.int8), gate_up_scales=np.full((E, 2 * I), 1e-2, np.float32),
+                    down=rng.integers(-8, 8, size=(E, I, H), dtype=np.int8), down_scales=np.full((E, H), 1e-2, np.float32))
+
+    for form in ("quant", "quant_full_k", "w4"):
+        for field, index, value in (("gate_up", (1, 7, 9), 8), ("gate_up", (0, 0, 0), -9), ("down", (1, 3, 3), 8), ("down", (0, 5, 1), -128)):
+            ex = experts()
+            ex[field][index] = value
+            with pytest.raises(rk.W4A8Error):
+                moe.MoeWeights(dom, shared_expert=0, form=form, **ex)      # a code outside [-8, 7]
+        c = moe.default_config(H, I, E, 0, 2, 8)
+        c.native_input = 1
+        with pytest.raises(rk.W4A8Error):
+            moe.MoeWorkspace(dom, c, form=form)                            # the int4 forms take normal input only
+    # geometry: multiples of 64, hidden at most 8128
+    for Hb, Ib in ((96, 64), (128, 96), (8192, 64)):
+        cfg = capi.MoeWeightConfig(Hb, Ib, 1, 0)
+        arr = (capi.MoeExpert * 1)()
+        assert not lib.rk_npu_moe_quant_weights_create(dom.handle, C.byref(cfg), arr)
+        assert not lib.rk_npu_moe_w4_weights_create(dom.handle, C.byref(cfg), arr)
+        c = moe.default_config(Hb, Ib, 1, 0, 1, 8)
+        assert not lib.rk_npu_moe_quant_workspace_create(dom.handle, C.byref(c))
+    # certification follows the original's bound: a down matrix whose column sums overflow INT16 over K = 512 is refused,
+    # the same column over K = 448 passes (oracle.bound restates src/rk_npu_i4_bounds.cpp)
+    for Ib in (512, 448):
+        ex = dict(gate_up=np.zeros((1, 64, 2 * Ib), np.int8), gate_up_scales=np.full((1, 2 * Ib), 1e-2, np.float32),
+                  down=np.full((1, Ib, 64), -8, np.int8), down_scales=np.full((1, 64), 1e-2, np.float32))
+        expect_ok = oracle.bound(ex["down"][0], requested=Ib)[0] == 0
+        try:
+            w = moe.MoeWeights(dom, shared_expert=0, form="quant", **ex)
+            created = True
+            w.free()
+        except rk.W4A8Error:
+            created = False
+        assert created == expect_ok, Ib
