@@ -7,7 +7,7 @@
  * quantised here), the byte queries.  All pointers are host pointers and a call returns when the output is complete, as
  * in the original.  Int4 experts are given as int8 arrays of codes in [-8, 7]; they are accepted under the original's
  * rule (the K tile its device would run must be certified against INT16 partial sums: the whole of K where it would try
- * that, else slices of 512) and are then stored and multiplied like int8 experts -- the sums are the same integers.
+ * that, else slices of 512) and are then stored two codes per byte; the sums are the same integers as for int8 storage.
  * Exported but declined (NULL / RK_NPU_ERR_PARAM / 0, nothing else happens): the mutable slot banks and the native
  * cache records they import and export (rk_npu_moe_*_slots_create, *_export_expert, *_import_expert*, *_swap_slots,
  * *_expert_blob_bytes); RK_NPU_MOE_MIDDLE_NPU_LUT, the original device's approximate table-lookup activation (a

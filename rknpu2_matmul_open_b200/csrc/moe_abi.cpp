@@ -44,7 +44,7 @@ bool valid_config(const rk_npu_moe_w8_config& c)           // src/rk_npu_moe_w8.
 }
 // src/rk_npu_moe_w8.cpp:368-389: which experts hold int4 codes.  Int4 experts are checked like the dense W4A8 weights
 // (codes in [-8, 7]; the K tile the original would run must be certified against its INT16 partial sums) and then
-// stored and multiplied exactly like int8 experts: the sums are the same integers.
+// stored two codes per byte; the sums are the same integers as with int8 storage.
 enum class Mode { W8 = 0, RoutedW4SharedW8 = 1, W4 = 2 };
 bool expert_is_w4(Mode mode, int expert, int routed) { return mode == Mode::W4 || (mode == Mode::RoutedW4SharedW8 && expert < routed); }
 bool can_use_full_gate(int hidden) { return hidden > 512 && hidden <= 2048; }
@@ -72,10 +72,12 @@ struct rk_npu_moe_w8_weights {
     uint32_t domain_id = 0;
     rk_npu_moe_w8_weight_config config{};
     Mode mode = Mode::W8;
-    uint8_t* gate_up = nullptr;   // [E] records of the [H, 2I] matrices
+    uint8_t* gate_up = nullptr;   // [E] records of the [H, 2I] matrices: the int4 experts first (two codes per byte), then int8
     uint8_t* down = nullptr;      // [E] records of the [I, H] matrices
     float* gate_up_scales = nullptr, *down_scales = nullptr;
-    size_t gate_up_expert_bytes = 0, down_expert_bytes = 0;
+    int nibble_experts = 0;
+    MoeBank gate_up_bank() const { return MoeBank{gate_up, moe_packed_nibble_bytes(config.hidden, 2 * config.intermediate), moe_packed_bytes(config.hidden, 2 * config.intermediate), nibble_experts}; }
+    MoeBank down_bank() const { return MoeBank{down, moe_packed_nibble_bytes(config.intermediate, config.hidden), moe_packed_bytes(config.intermediate, config.hidden), nibble_experts}; }
     size_t gate_up_bytes = 0, down_bytes = 0, gate_up_scale_bytes = 0, down_scale_bytes = 0;
 };
 
@@ -281,10 +283,10 @@ int moe_run(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int row
         if (timings) cudaEventRecord(ws->events[1], s);
         const MoeSchedule sched{reinterpret_cast<const int*>(ws->upload + u.job_expert), reinterpret_cast<const int*>(ws->upload + u.job_first),
                                 reinterpret_cast<const int*>(ws->upload + u.job_rows), reinterpret_cast<const int*>(ws->upload + u.assign_token), jobs};
-        const MoeGateUpParams gu{sched, w->gate_up, w->gate_up_expert_bytes, w->gate_up_scales, codes, in_scales, ws->middle, ws->row_max, H, I};
+        const MoeGateUpParams gu{sched, w->gate_up_bank(), w->gate_up_scales, codes, in_scales, ws->middle, ws->row_max, H, I};
         ok = launch_moe_gate_up(gu, s) == cudaSuccess;
         if (timings) cudaEventRecord(ws->events[2], s);
-        const MoeDownParams dn{sched, w->down, w->down_expert_bytes, w->down_scales, ws->middle, ws->row_max, ws->expert_out, H, I};
+        const MoeDownParams dn{sched, w->down_bank(), w->down_scales, ws->middle, ws->row_max, ws->expert_out, H, I};
         ok = ok && launch_moe_down(dn, s) == cudaSuccess;
         if (timings) cudaEventRecord(ws->events[3], s);
         const MoeCombineParams cb{ws->expert_out, reinterpret_cast<const int*>(ws->upload + u.slot_assign),
@@ -370,10 +372,10 @@ rk_npu_moe_w8_weights* weights_create(rk_npu_iommu_domain* domain, const rk_npu_
     w->config = *config;
     w->mode = mode;
     domain_retain(domain);
-    w->gate_up_expert_bytes = moe_packed_bytes(H, 2 * I);
-    w->down_expert_bytes = moe_packed_bytes(I, H);
-    w->gate_up_bytes = w->gate_up_expert_bytes * E;
-    w->down_bytes = w->down_expert_bytes * E;
+    w->nibble_experts = mode == Mode::W4 ? E : (mode == Mode::RoutedW4SharedW8 ? config->routed_experts : 0);
+    const MoeBank gb = w->gate_up_bank(), db = w->down_bank();
+    w->gate_up_bytes = size_t(w->nibble_experts) * gb.nibble_bytes + size_t(E - w->nibble_experts) * gb.byte_bytes;
+    w->down_bytes = size_t(w->nibble_experts) * db.nibble_bytes + size_t(E - w->nibble_experts) * db.byte_bytes;
     w->gate_up_scale_bytes = sizeof(float) * 2 * size_t(I) * E;
     w->down_scale_bytes = sizeof(float) * size_t(H) * E;
     bool ok = !device_alloc(domain, reinterpret_cast<void**>(&w->gate_up), w->gate_up_bytes) &&
@@ -390,8 +392,8 @@ rk_npu_moe_w8_weights* weights_create(rk_npu_iommu_domain* domain, const rk_npu_
              cudaMemcpyAsync(raw + gu_raw, x.down, dn_raw, cudaMemcpyHostToDevice, s) == cudaSuccess &&
              cudaMemcpyAsync(w->gate_up_scales + size_t(e) * 2 * I, x.gate_up_scales, sizeof(float) * 2 * I, cudaMemcpyHostToDevice, s) == cudaSuccess &&
              cudaMemcpyAsync(w->down_scales + size_t(e) * H, x.down_scales, sizeof(float) * H, cudaMemcpyHostToDevice, s) == cudaSuccess &&
-             launch_moe_pack(MoePackParams{raw, w->gate_up + size_t(e) * w->gate_up_expert_bytes, H, 2 * I}, s) == cudaSuccess &&
-             launch_moe_pack(MoePackParams{raw + gu_raw, w->down + size_t(e) * w->down_expert_bytes, I, H}, s) == cudaSuccess &&
+             launch_moe_pack(MoePackParams{raw, const_cast<uint8_t*>(w->gate_up_bank().expert(e)), H, 2 * I, e < w->nibble_experts}, s) == cudaSuccess &&
+             launch_moe_pack(MoePackParams{raw + gu_raw, const_cast<uint8_t*>(w->down_bank().expert(e)), I, H, e < w->nibble_experts}, s) == cudaSuccess &&
              cudaStreamSynchronize(s) == cudaSuccess;     // the caller's arrays and `raw` are reused by the next expert
     }
     if (raw) cudaFree(raw);

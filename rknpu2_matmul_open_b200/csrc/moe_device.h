@@ -16,11 +16,29 @@ constexpr int MOE_KQ = 128;          // k extent of one packed weight record (fo
 // Packed int8 expert matrix W[K][N] (N a multiple of 16): records of 16 channels x 128 k in the register order
 // of the m16n8k32 A operand, [channel block][k quarter-kilo][k-step 0..3][lane][16 B = a0 a1 a2 a3], zero beyond K.
 inline size_t moe_packed_bytes(int K, int N) { return size_t((K + MOE_KQ - 1) / MOE_KQ) * MOE_KQ * size_t(N); }
+// Int4 experts keep two codes per byte: [channel block][k quarter-kilo][half 0..1][lane][16 B], the 16 bytes being the
+// words of k-steps 2 half and 2 half + 1 for channels g and g + 8; a word w holds the codes at k = 4t.. in its low
+// nibbles and those at k = 16 + 4t.. in its high nibbles, so that (w << 4) & 0xF0F0F0F0 and w & 0xF0F0F0F0 are the two
+// A registers of the channel with every code times 16 (the sums are shifted back, exactly).  Half the bytes.
+inline size_t moe_packed_nibble_bytes(int K, int N) { return moe_packed_bytes(K, N) / 2; }
+// A bank of experts: the first `nibble_experts` hold int4 records, the rest int8 records.
+struct MoeBank {
+    const uint8_t* base;
+    size_t nibble_bytes, byte_bytes;   // one expert's records in either form
+    int nibble_experts;
+    __host__ __device__ const uint8_t* expert(int e) const
+    {
+        return e < nibble_experts ? base + size_t(e) * nibble_bytes
+                                  : base + size_t(nibble_experts) * nibble_bytes + size_t(e - nibble_experts) * byte_bytes;
+    }
+    __host__ __device__ bool nibbles(int e) const { return e < nibble_experts; }
+};
 
 struct MoePackParams {
     const int8_t* W;      // [K][N] row-major, on the device
     uint8_t* packed;
     int K, N;
+    int nibbles;          // 1: int4 codes, two per byte
 };
 
 struct MoeQuantParams {
@@ -41,8 +59,7 @@ struct MoeSchedule {
 
 struct MoeGateUpParams {
     MoeSchedule sched;
-    const uint8_t* packed;       // experts' gate/up matrices, expert e at e * expert_bytes
-    size_t expert_bytes;
+    MoeBank bank;                // experts' gate/up matrices
     const float* w_scales;       // [E][2I]
     const int8_t* codes;         // [rows][H]
     const float* in_scales;      // [rows]
@@ -53,8 +70,7 @@ struct MoeGateUpParams {
 
 struct MoeDownParams {
     MoeSchedule sched;
-    const uint8_t* packed;       // experts' down matrices
-    size_t expert_bytes;
+    MoeBank bank;                // experts' down matrices
     const float* w_scales;       // [E][H]
     const float* middle;         // [assignments][I]
     const uint32_t* row_max;     // [assignments]

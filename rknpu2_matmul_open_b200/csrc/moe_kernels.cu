@@ -38,21 +38,23 @@ __device__ __forceinline__ int8_t nearest_even_code(float v)
 // c[b][half] += W_b(16 x K) * X^T.  Fragment mapping of m16n8k32 (g = lane / 4, t = lane % 4): A regs = channels g / g + 8
 // at k = 4t.. and 16 + 4t..; B regs = token g at the same k; C regs = channels g, g + 8 x tokens 2t, 2t + 1.
 // The records of 128 k are double-buffered in registers: while one is multiplied the next is on its way.
-template <bool TWO, int NB>
+// NIB: int4 records (two 16-byte pieces per 128 k instead of four); the sums come out times 16.
+template <bool TWO, int NB, bool NIB>
 __device__ __forceinline__ void block_mma(const uint4* const (&w)[NB], const uint8_t* xs, int row_bytes, int kq_begin, int kq_count,
                                           int lane, int (&c)[NB][2][4])
 {
+    constexpr int PIECES = NIB ? 2 : 4;
     const int g = lane >> 2, t = lane & 3;
     const uint8_t* x0 = xs + (size_t)g * row_bytes + 4 * t;
     const uint8_t* x1 = x0 + (size_t)8 * row_bytes;
-    uint4 even[NB][4], odd[NB][4];
-    auto fetch = [&](uint4 (&a)[NB][4], int kq) {
+    uint4 even[NB][PIECES], odd[NB][PIECES];
+    auto fetch = [&](uint4 (&a)[NB][PIECES], int kq) {
 #pragma unroll
         for (int b = 0; b < NB; ++b)
 #pragma unroll
-            for (int s = 0; s < 4; ++s) a[b][s] = __ldg(w[b] + (size_t)(kq * 4 + s) * 32 + lane);
+            for (int s = 0; s < PIECES; ++s) a[b][s] = __ldg(w[b] + (size_t)(kq * PIECES + s) * 32 + lane);
     };
-    auto multiply = [&](const uint4 (&a)[NB][4], int kq) {
+    auto multiply = [&](const uint4 (&a)[NB][PIECES], int kq) {
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
             const int k = kq * MOE_KQ + s * 32;
@@ -61,8 +63,18 @@ __device__ __forceinline__ void block_mma(const uint4* const (&w)[NB], const uin
             if (TWO) { d0 = *reinterpret_cast<const uint32_t*>(x1 + k); d1 = *reinterpret_cast<const uint32_t*>(x1 + k + 16); }
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
-                mma_s8(c[b][0], a[b][s].x, a[b][s].y, a[b][s].z, a[b][s].w, b0, b1);
-                if (TWO) mma_s8(c[b][1], a[b][s].x, a[b][s].y, a[b][s].z, a[b][s].w, d0, d1);
+                uint32_t a0, a1, a2, a3;
+                if (NIB) {
+                    const uint4 v = a[b][s >> 1];
+                    const uint32_t wx = (s & 1) ? v.z : v.x, wy = (s & 1) ? v.w : v.y;
+                    a0 = (wx << 4) & 0xF0F0F0F0u; a2 = wx & 0xF0F0F0F0u;
+                    a1 = (wy << 4) & 0xF0F0F0F0u; a3 = wy & 0xF0F0F0F0u;
+                } else {
+                    const uint4 v = a[b][NIB ? 0 : s];
+                    a0 = v.x; a1 = v.y; a2 = v.z; a3 = v.w;
+                }
+                mma_s8(c[b][0], a0, a1, a2, a3, b0, b1);
+                if (TWO) mma_s8(c[b][1], a0, a1, a2, a3, d0, d1);
             }
         }
     };
@@ -88,22 +100,35 @@ __device__ __forceinline__ void warp_prefetch_l2(const void* p, size_t bytes, in
 __global__ void __launch_bounds__(256) moe_pack_kernel(const MoePackParams p)
 {
     const int kq_count = (p.K + MOE_KQ - 1) / MOE_KQ;
-    const size_t total = (size_t)(p.N / 16) * kq_count * 4 * 32;
+    const int pieces = p.nibbles ? 2 : 4;
+    const size_t total = (size_t)(p.N / 16) * kq_count * pieces * 32;
+    auto code = [&](int k, int n) -> uint32_t { return k < p.K ? (uint32_t)(uint8_t)p.W[(size_t)k * p.N + n] : 0u; };
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int lane = (int)(i & 31), s = (int)((i >> 5) & 3);
-        const size_t rec = i >> 7;
+        const int lane = (int)(i & 31), piece = (int)((i >> 5) % pieces);
+        const size_t rec = (i >> 5) / pieces;
         const int kq = (int)(rec % kq_count), cb = (int)(rec / kq_count);
         const int g = lane >> 2, t = lane & 3;
-        const int k0 = kq * MOE_KQ + s * 32 + 4 * t, n0 = cb * 16 + g;
         uint32_t word[4];
+        if (p.nibbles) {
+            // piece = k-steps 2 piece, 2 piece + 1; words: (step, channel g), (step, g + 8), (step + 1, g), (step + 1, g + 8)
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int k = k0 + (r >> 1) * 16, n = n0 + (r & 1) * 8;
-            uint32_t v = 0;
+            for (int r = 0; r < 4; ++r) {
+                const int k0 = kq * MOE_KQ + (2 * piece + (r >> 1)) * 32 + 4 * t, n = cb * 16 + g + (r & 1) * 8;
+                uint32_t v = 0;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (k + j < p.K) v |= (uint32_t)(uint8_t)p.W[(size_t)(k + j) * p.N + n] << (8 * j);
-            word[r] = v;
+                for (int j = 0; j < 4; ++j) v |= ((code(k0 + j, n) & 15u) | ((code(k0 + 16 + j, n) & 15u) << 4)) << (8 * j);
+                word[r] = v;
+            }
+        } else {
+            const int k0 = kq * MOE_KQ + piece * 32 + 4 * t, n0 = cb * 16 + g;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int k = k0 + (r >> 1) * 16, n = n0 + (r & 1) * 8;
+                uint32_t v = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v |= code(k + j, n) << (8 * j);
+                word[r] = v;
+            }
         }
         reinterpret_cast<uint4*>(p.packed)[i] = make_uint4(word[0], word[1], word[2], word[3]);
     }
@@ -159,12 +184,14 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gate_up_kernel(const MoeGateU
     const bool live = fb * 16 < p.I;
     const int kq_mid = (kq_count + 1) / 2;
     const int kq_begin = k_half ? kq_mid : 0, kq_end = k_half ? kq_count : kq_mid;
-    const uint4* base = reinterpret_cast<const uint4*>(p.packed + (size_t)expert * p.expert_bytes);
-    const size_t block_vecs = (size_t)kq_count * 4 * 32;
+    const uint4* base = reinterpret_cast<const uint4*>(p.bank.expert(expert));
+    const bool nib = p.bank.nibbles(expert);
+    const size_t kq_vecs = nib ? 64 : 128;            // 16-byte pieces of one block per 128 k
+    const size_t block_vecs = (size_t)kq_count * kq_vecs;
     const uint4* const w[2] = {base + (size_t)fb * block_vecs, base + (size_t)(p.I / 16 + fb) * block_vecs};
     if (live && kq_end > kq_begin) {
-        warp_prefetch_l2(w[0] + (size_t)kq_begin * 128, (size_t)(kq_end - kq_begin) * 2048, lane);
-        warp_prefetch_l2(w[1] + (size_t)kq_begin * 128, (size_t)(kq_end - kq_begin) * 2048, lane);
+        warp_prefetch_l2(w[0] + (size_t)kq_begin * kq_vecs, (size_t)(kq_end - kq_begin) * kq_vecs * 16, lane);
+        warp_prefetch_l2(w[1] + (size_t)kq_begin * kq_vecs, (size_t)(kq_end - kq_begin) * kq_vecs * 16, lane);
     }
     pdl_wait();                                       // fp32 entry: the codes and scales come from the quantise kernel
     if (tid < MOE_JOB_ROWS) {
@@ -187,8 +214,13 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gate_up_kernel(const MoeGateU
     __syncthreads();
     int c[2][2][4] = {};                              // [gate | up][token half][fragment]
     if (live) {
-        if (rows > 8) block_mma<true, 2>(w, xs, row_bytes, kq_begin, kq_end, lane, c);
-        else block_mma<false, 2>(w, xs, row_bytes, kq_begin, kq_end, lane, c);
+        if (nib) {
+            if (rows > 8) block_mma<true, 2, true>(w, xs, row_bytes, kq_begin, kq_end, lane, c);
+            else block_mma<false, 2, true>(w, xs, row_bytes, kq_begin, kq_end, lane, c);
+        } else {
+            if (rows > 8) block_mma<true, 2, false>(w, xs, row_bytes, kq_begin, kq_end, lane, c);
+            else block_mma<false, 2, false>(w, xs, row_bytes, kq_begin, kq_end, lane, c);
+        }
     }
     // the warp with the upper half of K hands its sums to its partner
     if (k_half == 1) {
@@ -198,7 +230,10 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gate_up_kernel(const MoeGateU
     __syncthreads();
     if (k_half == 1 || !live) return;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) c[i >> 3][(i >> 2) & 1][i & 3] += s_partial[fbi][i][lane];
+    for (int i = 0; i < 16; ++i) {
+        const int sum = c[i >> 3][(i >> 2) & 1][i & 3] + s_partial[fbi][i][lane];
+        c[i >> 3][(i >> 2) & 1][i & 3] = nib ? sum >> 4 : sum;     // int4 records: every code entered times 16
+    }
     const int g = lane >> 2, t = lane & 3;
     const float* ws = p.w_scales + (size_t)expert * 2 * p.I;
     float wg[2], wu[2];
@@ -241,8 +276,9 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_down_kernel(const MoeDownPara
     const int expert = p.sched.job_expert[job], first = p.sched.job_first[job], rows = p.sched.job_rows[job];
     const int kq_count = (p.I + MOE_KQ - 1) / MOE_KQ;
     const int row_bytes = kq_count * MOE_KQ + MOE_ROW_PAD;
-    const uint4* base = reinterpret_cast<const uint4*>(p.packed + (size_t)expert * p.expert_bytes);
-    const size_t block_vecs = (size_t)kq_count * 4 * 32;
+    const uint4* base = reinterpret_cast<const uint4*>(p.bank.expert(expert));
+    const bool nib = p.bank.nibbles(expert);
+    const size_t block_vecs = (size_t)kq_count * (nib ? 64 : 128);
     const int cb0 = (blockIdx.x * MOE_WARPS + warp) * MOE_DOWN_BLOCKS;
     {   // this warp's weights on their way to L2 while the gate/up launch still runs
         const int blocks = min(MOE_DOWN_BLOCKS, p.H / 16 - cb0);
@@ -280,8 +316,14 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_down_kernel(const MoeDownPara
         if (cb * 16 >= p.H) break;
         int c[1][2][4] = {};
         const uint4* const w[1] = {base + (size_t)cb * block_vecs};
-        if (rows > 8) block_mma<true, 1>(w, xs, row_bytes, 0, kq_count, lane, c);
-        else block_mma<false, 1>(w, xs, row_bytes, 0, kq_count, lane, c);
+        if (nib) {
+            if (rows > 8) block_mma<true, 1, true>(w, xs, row_bytes, 0, kq_count, lane, c);
+            else block_mma<false, 1, true>(w, xs, row_bytes, 0, kq_count, lane, c);
+        } else {
+            if (rows > 8) block_mma<true, 1, false>(w, xs, row_bytes, 0, kq_count, lane, c);
+            else block_mma<false, 1, false>(w, xs, row_bytes, 0, kq_count, lane, c);
+        }
+        const int shift = nib ? 4 : 0;
         const float w0 = __ldg(ws + cb * 16 + g), w1 = __ldg(ws + cb * 16 + g + 8);
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -289,7 +331,7 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_down_kernel(const MoeDownPara
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int r = half * 8 + 2 * t + (i & 1), h = i >> 1;
-                if (r < rows) p.expert_out[(size_t)(first + r) * p.H + cb * 16 + g + 8 * h] = dequant(c[0][half][i], s_scale[r], h ? w1 : w0);
+                if (r < rows) p.expert_out[(size_t)(first + r) * p.H + cb * 16 + g + 8 * h] = dequant(c[0][half][i] >> shift, s_scale[r], h ? w1 : w0);
             }
         }
     }
@@ -320,7 +362,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombineParams
 // ------------------------------------------------------------------ launchers
 cudaError_t launch_moe_pack(const MoePackParams& p, cudaStream_t stream)
 {
-    const size_t total = moe_packed_bytes(p.K, p.N) / 16;
+    const size_t total = (p.nibbles ? moe_packed_nibble_bytes(p.K, p.N) : moe_packed_bytes(p.K, p.N)) / 16;
     const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, 148 * 8);
     moe_pack_kernel<<<blocks, 256, 0, stream>>>(p);
     return cudaGetLastError();
