@@ -102,7 +102,11 @@ struct rk_npu_moe_w8_workspace {
     size_t codes_bytes = 0, in_scale_bytes = 0, middle_bytes = 0, row_max_bytes = 0, expert_out_bytes = 0, out_bytes = 0,
            upload_bytes = 0;
     uint8_t* host_upload = nullptr;   // pinned mirror of `upload`
-    Status* host_status = nullptr; // pinned
+    Status* host_status = nullptr; // pinned; the quantise kernel reports into it through its device alias
+    Status* host_status_alias = nullptr;
+    float* host_out = nullptr;     // pinned landing place of small results, written by the combine kernel through its alias
+    float* host_out_alias = nullptr;
+    size_t host_out_bytes = 0;
     std::vector<std::vector<int>> groups;   // per expert: token * slots + slot of its assignments
 };
 
@@ -138,6 +142,7 @@ void workspace_destroy(rk_npu_moe_w8_workspace* ws)
     if (ws->status) device_free(d, ws->status, sizeof(Status));
     if (ws->host_upload) cudaFreeHost(ws->host_upload);
     if (ws->host_status) cudaFreeHost(ws->host_status);
+    if (ws->host_out) cudaFreeHost(ws->host_out);
     for (auto& e : ws->events)
         if (e) cudaEventDestroy(e);
     if (ws->stream) cudaStreamDestroy(ws->stream);
@@ -257,22 +262,20 @@ int moe_run(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int row
         const int8_t* codes = reinterpret_cast<const int8_t*>(ws->upload + u.rows_data);
         const float* in_scales = reinterpret_cast<const float*>(ws->upload + u.scales);
         if (f32) {
-            ok = ok && cudaMemsetAsync(ws->status, 0, sizeof(Status), s) == cudaSuccess;
-            const MoeQuantParams q{reinterpret_cast<const float*>(ws->upload + u.rows_data), ws->codes, ws->in_scales, ws->status, rows, H};
+            // the kernel's verdict lands in page-locked memory by itself: no copy, no second wait
+            *ws->host_status = Status{};
+            const MoeQuantParams q{reinterpret_cast<const float*>(ws->upload + u.rows_data), ws->codes, ws->in_scales, ws->host_status_alias, rows, H};
             ok = ok && launch_moe_quantize(q, s) == cudaSuccess;
             codes = ws->codes;
             in_scales = ws->in_scales;
         }
         if (!ok) { cudaGetLastError(); cudaStreamSynchronize(s); return RK_NPU_ERR_SUBMIT; }
         t.input_us = since_us(at);
-        auto input_verdict = [&]() -> int {    // run_f32: the quantise kernel's verdict on the rows
-            if (!f32) return RK_NPU_OK;
-            cudaMemcpyAsync(ws->host_status, ws->status, sizeof(Status), cudaMemcpyDeviceToHost, s);
-            if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
-            return ws->host_status->bad_input ? RK_NPU_ERR_PARAM : RK_NPU_OK;
-        };
         if (!assignments) {                    // nothing routed: the output is zero and no device work is issued for it
-            if (const int rc = input_verdict()) return rc;
+            if (f32) {                         // (the rows are still judged)
+                if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+                if (ws->host_status->bad_input) return RK_NPU_ERR_PARAM;
+            }
             at = Clock::now();
             std::fill_n(output, values, 0.0f);
             t.combine_us = since_us(at);
@@ -281,6 +284,10 @@ int moe_run(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int row
             return RK_NPU_OK;
         }
         if (timings) cudaEventRecord(ws->events[1], s);
+        // A small result is stored by the combine kernel straight into page-locked host memory and copied to the caller's
+        // array by the host after the wait (a rejected call must not touch that array); a large one takes the copy engine.
+        const bool direct = values * 4 <= ws->host_out_bytes;
+        float* const landing = direct ? ws->host_out_alias : ws->out;
         const MoeSchedule sched{reinterpret_cast<const int*>(ws->upload + u.job_expert), reinterpret_cast<const int*>(ws->upload + u.job_first),
                                 reinterpret_cast<const int*>(ws->upload + u.job_rows), reinterpret_cast<const int*>(ws->upload + u.assign_token), jobs};
         const MoeGateUpParams gu{sched, w->gate_up_bank(), w->gate_up_scales, codes, in_scales, ws->middle, ws->row_max, H, I};
@@ -290,7 +297,7 @@ int moe_run(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int row
         ok = ok && launch_moe_down(dn, s) == cudaSuccess;
         if (timings) cudaEventRecord(ws->events[3], s);
         const MoeCombineParams cb{ws->expert_out, reinterpret_cast<const int*>(ws->upload + u.slot_assign),
-                                  reinterpret_cast<const float*>(ws->upload + u.coefficients), ws->out, ws->row_max, rows, S, H};
+                                  reinterpret_cast<const float*>(ws->upload + u.coefficients), landing, ws->row_max, rows, S, H};
         ok = ok && launch_moe_combine(cb, s) == cudaSuccess;
         if (timings) cudaEventRecord(ws->events[4], s);
         if (!ok) {      // a launch failed part-way: the row maxima may be left behind
@@ -299,9 +306,13 @@ int moe_run(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int row
             cudaStreamSynchronize(s);
             return RK_NPU_ERR_SUBMIT;
         }
-        if (const int rc = input_verdict()) return rc;      // a rejected row: the output is not written
         at = Clock::now();
-        if (cudaMemcpyAsync(output, ws->out, values * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) {
+        if (!direct && !f32 && cudaMemcpyAsync(output, ws->out, values * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) ok = false;
+        if (!ok || cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+        if (f32 && ws->host_status->bad_input) return RK_NPU_ERR_PARAM;      // a rejected row: the output is not written
+        if (direct) std::memcpy(output, ws->host_out, values * 4);
+        else if (f32 && (cudaMemcpyAsync(output, ws->out, values * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+                         cudaStreamSynchronize(s) != cudaSuccess)) {
             cudaGetLastError();
             return RK_NPU_ERR_SUBMIT;
         }
@@ -447,7 +458,11 @@ rk_npu_moe_w8_workspace* workspace_create(rk_npu_iommu_domain* domain, const rk_
          !device_alloc(domain, reinterpret_cast<void**>(&ws->status), sizeof(Status));
     ok = ok && cudaStreamCreateWithFlags(&ws->stream, cudaStreamNonBlocking) == cudaSuccess &&
          cudaMallocHost(reinterpret_cast<void**>(&ws->host_upload), ws->upload_bytes) == cudaSuccess &&
-         cudaMallocHost(reinterpret_cast<void**>(&ws->host_status), sizeof(Status)) == cudaSuccess;
+         cudaHostAlloc(reinterpret_cast<void**>(&ws->host_status), sizeof(Status), cudaHostAllocMapped) == cudaSuccess &&
+         cudaHostGetDevicePointer(reinterpret_cast<void**>(&ws->host_status_alias), ws->host_status, 0) == cudaSuccess;
+    ws->host_out_bytes = std::min<size_t>(ws->out_bytes, size_t(256) << 10);
+    ok = ok && cudaHostAlloc(reinterpret_cast<void**>(&ws->host_out), ws->host_out_bytes, cudaHostAllocMapped) == cudaSuccess &&
+         cudaHostGetDevicePointer(reinterpret_cast<void**>(&ws->host_out_alias), ws->host_out, 0) == cudaSuccess;
     for (auto& e : ws->events) ok = ok && cudaEventCreate(&e) == cudaSuccess;
     ok = ok && cudaMemsetAsync(ws->status, 0, sizeof(Status), ws->stream) == cudaSuccess &&
          cudaMemsetAsync(ws->row_max, 0, ws->row_max_bytes, ws->stream) == cudaSuccess &&     // every run leaves them zero again
