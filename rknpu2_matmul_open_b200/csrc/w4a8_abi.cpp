@@ -275,6 +275,14 @@ void* mapped_alias(const void* p)
     if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return nullptr; }
     return a.type == cudaMemoryTypeHost ? a.devicePointer : nullptr;
 }
+// One query per tensor of a blocking call: is it device memory, and if it is page-locked host memory, its device alias.
+struct Placement { bool device = false; void* alias = nullptr; };
+Placement placement(const void* p)
+{
+    cudaPointerAttributes a{};
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return {}; }
+    return {a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged, a.type == cudaMemoryTypeHost ? a.devicePointer : nullptr};
+}
 
 // ------------------------------------------------------------------ kernel sequencing
 int pick_split_auto(const rk_npu_w4a8_workspace& ws, int tiles, int token_chunks)
@@ -562,13 +570,18 @@ int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const vo
     const size_t in_bytes = size_t(cfg.M) * cfg.K * (half ? 2 : 4);
     const int out_cols = epi == EPI_SWIGLU ? cfg.N / 2 : cfg.N;
     const size_t out_bytes = size_t(cfg.M) * out_cols * (epi == EPI_F16 ? 2 : 4);
-    const bool a_dev = on_device(A), c_dev = on_device(C);
+    const Placement a_at = placement(A), c_at = placement(C);
+    const bool a_dev = a_at.device, c_dev = c_at.device;
     cudaStream_t s = ws->stream;
     const void* dA = A;
     void* dC = C;
     auto copy_start = Clock::now();
     if (!a_dev) {
-        if (cudaMemcpyAsync(ws->stage_in, A, in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+        // ordinary (pageable) host memory: a small tensor is copied into the workspace's page-locked piece first -- the
+        // host copy is cheaper than the staging the driver does for pageable memory
+        const void* from = A;
+        if (!a_at.alias && ws->bounce_in && in_bytes <= ws->bounce_bytes) { std::memcpy(ws->bounce_in, A, in_bytes); from = ws->bounce_in; }
+        if (cudaMemcpyAsync(ws->stage_in, from, in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
         dA = ws->stage_in;
     }
     // A small batch through one of the single-kernel families writes every output element once and reports through two
@@ -576,10 +589,13 @@ int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const vo
     // into the caller's tensor when that is page-locked memory the GPU can address, and reports into the workspace's
     // own page-locked status block.  (The activations are still copied in: every CTA reads them.)
     const bool single_kernel = (ws->variant == 3 || ws->variant == 5) && !grouped(*ws) && epi != EPI_SWIGLU;
-    void* c_alias = (!c_dev && single_kernel && out_bytes <= (size_t(1) << 20)) ? mapped_alias(C) : nullptr;
+    void* c_alias = (!c_dev && single_kernel && out_bytes <= (size_t(1) << 20)) ? c_at.alias : nullptr;
+    // ... and an ordinary host result of a small batch lands in the workspace's page-locked piece and is copied out by the host
+    const bool bounce_out = !c_dev && !c_alias && single_kernel && ws->bounce_out_alias && out_bytes <= ws->bounce_bytes;
+    if (bounce_out) c_alias = ws->bounce_out_alias;
     if (c_alias) dC = c_alias;
     else if (!c_dev) dC = ws->stage_out;
-    Status* status_alias = single_kernel ? static_cast<Status*>(mapped_alias(ws->host_status)) : nullptr;
+    Status* status_alias = single_kernel ? ws->host_status_alias : nullptr;
     if (status_alias) *ws->host_status = Status{};
     t.sync_us += elapsed_us(copy_start);
     Call call{ws, w, dA, dC, half, epi, nullptr, nullptr, s, metrics ? ws->events : nullptr, epi == EPI_I32};
@@ -587,13 +603,13 @@ int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const vo
     int rc = enqueue_linear(call, dC);
     if (rc) { cudaStreamSynchronize(s); return rc; }
     copy_start = Clock::now();
-    // Other host tensors are copied straight from and to the caller's (pageable) memory: bouncing small ones through
-    // pinned buffers was measured slower (the extra host memcpy costs more than the driver's own staging).
+    // Other host tensors are copied straight from and to the caller's memory.
     if (!c_dev && !c_alias) cudaMemcpyAsync(C, dC, out_bytes, cudaMemcpyDeviceToHost, s);
     if (!status_alias) cudaMemcpyAsync(ws->host_status, ws->status, sizeof(Status), cudaMemcpyDeviceToHost, s);
     if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
-    t.sync_us += elapsed_us(copy_start);
     rc = status_to_rc(*ws, s);
+    if (bounce_out && rc == RK_NPU_OK) std::memcpy(C, ws->bounce_out, out_bytes);
+    t.sync_us += elapsed_us(copy_start);
     if (metrics) {
         t.activation_scan_us = event_us(ws->events[0], ws->events[1]);
         t.submit_us = rc ? 0.0 : event_us(ws->events[1], ws->events[2]);   // a rejected input did no GEMM work
@@ -626,6 +642,8 @@ void workspace_destroy(rk_npu_w4a8_workspace* ws)
     if (ws->status) device_free(d, ws->status, sizeof(Status));
     if (ws->stage_in) device_free(d, ws->stage_in, ws->stage_in_bytes);
     if (ws->stage_out) device_free(d, ws->stage_out, ws->stage_out_bytes);
+    if (ws->bounce_in) cudaFreeHost(ws->bounce_in);
+    if (ws->bounce_out) cudaFreeHost(ws->bounce_out);
     if (ws->trace) device_free(d, ws->trace, ws->trace_bytes);
     if (ws->partials) device_free(d, ws->partials, ws->partials_bytes);
     if (ws->counts) device_free(d, ws->counts, ws->counts_bytes);
@@ -1108,6 +1126,21 @@ rk_npu_w4a8_workspace* rkb200::create_workspace_scheduled(rk_npu_iommu_domain* d
              (!ws->counts || cudaMemsetAsync(ws->counts, 0, ws->counts_bytes, ws->stream) == cudaSuccess) &&
              cudaStreamSynchronize(ws->stream) == cudaSuccess;
         std::memset(ws->host_status, 0, sizeof(Status));
+        ws->host_status_alias = static_cast<Status*>(mapped_alias(ws->host_status));
+        // page-locked pieces for small host tensors of the blocking calls (optional: without them the calls copy directly)
+        const size_t most = std::max(ws->stage_in_bytes, ws->stage_out_bytes);
+        if ((variant == 3 || variant == 5) && ctx->world == 1 && most <= (size_t(1) << 20)) {
+            if (cudaHostAlloc(&ws->bounce_in, most, cudaHostAllocDefault) == cudaSuccess &&
+                cudaHostAlloc(&ws->bounce_out, most, cudaHostAllocMapped) == cudaSuccess) {
+                ws->bounce_bytes = most;
+                ws->bounce_out_alias = mapped_alias(ws->bounce_out);
+            } else {
+                cudaGetLastError();
+                if (ws->bounce_in) cudaFreeHost(ws->bounce_in);
+                if (ws->bounce_out) cudaFreeHost(ws->bounce_out);
+                ws->bounce_in = ws->bounce_out = nullptr;
+            }
+        }
     }
     if (!ok) { cudaGetLastError(); workspace_destroy(ws); return nullptr; }
     return ws;

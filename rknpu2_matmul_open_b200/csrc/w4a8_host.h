@@ -129,6 +129,10 @@ struct rk_npu_w4a8_workspace {
     void* stage_out = nullptr;  // device copy of host outputs
     size_t codes_bytes = 0, stage_in_bytes = 0, stage_out_bytes = 0;
     rkb200::Status* host_status = nullptr;  // pinned
+    rkb200::Status* host_status_alias = nullptr;   // its device address (NULL if the GPU cannot address it)
+    void* bounce_in = nullptr;        // page-locked pieces the blocking calls copy small ordinary host tensors through
+    void* bounce_out = nullptr, *bounce_out_alias = nullptr;
+    size_t bounce_bytes = 0;
     cudaEvent_t events[8]{};
     std::atomic<uint64_t> launches{0};
     unsigned long long* trace = nullptr;   // device stamps, allocated by rk_npu_b200_w4a8_trace_enable
