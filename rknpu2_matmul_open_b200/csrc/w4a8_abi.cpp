@@ -481,6 +481,8 @@ int enqueue(const Call& c)
     if (ws.variant == 2) {
         g.split = 1;
         g.pair = ws.pair ? 1 : 0;
+        // parking pays where finishing a chunk is expensive: the SwiGLU epilogue (see DESIGN); RK_NPU_B200_PARK_ALL=1 for all
+        if (c.epi == EPI_SWIGLU || env_flag("RK_NPU_B200_PARK_ALL", false)) g.partials = ws.partials;
         if (gemm_tc_persist_supported(g) && !env_flag("RK_NPU_B200_NO_PERSIST", false)) err = launch_gemm_tc_persist(g, c.stream, pdl);
         else err = launch_gemm_tc(g, c.stream, pdl);
     } else if (ws.variant == 4) {
@@ -1100,6 +1102,11 @@ rk_npu_w4a8_workspace* rkb200::create_workspace_scheduled(rk_npu_iommu_domain* d
         ws->counts_bytes = tiles * sizeof(unsigned int);
         ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->partials), ws->partials_bytes);
         ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->counts), ws->counts_bytes);
+    }
+    if (variant == 2 && ws->pair && env_flag("RK_NPU_B200_PARK", true)) {
+        // the persistent kernel parks accumulator chunks here between reading them out of tensor memory and finishing them
+        ws->partials_bytes = gemm_tc_persist_park_bytes(ctx->sm_count);
+        ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->partials), ws->partials_bytes);
     }
     if (ctx->world > 1) {
         ws->gather_slot = size_t(cfg->M) * size_t(shard_plan(cfg->N, ctx->world, 0).columns()) * 4;   // rank 0's share is the widest

@@ -242,5 +242,8 @@ bool gemm_tc_supported(const GemmParams& p);
 // persistent two-CTA form (binary16 output or fused SwiGLU); p.pair and p.T == 128 required
 cudaError_t launch_gemm_tc_persist(const GemmParams& p, cudaStream_t stream, bool pdl);
 bool gemm_tc_persist_supported(const GemmParams& p);
+// Bytes of GemmParams.partials the persistent kernel uses to park accumulator chunks (NULL: chunks are finished one by
+// one before the accumulator is handed back).  No initial contents needed.
+size_t gemm_tc_persist_park_bytes(int sm_count);
 
 } // namespace rkb200

@@ -14,7 +14,10 @@
 //     shallower ring;
 //   * eight dedicated epilogue warps read the accumulator out of tensor memory, hand it back
 //     after the last read and store straight from registers: the 32 lanes of a warp hold 32
-//     neighbouring channels of one token, i.e. 64..128 contiguous bytes per store;
+//     neighbouring channels of one token, i.e. 64..128 contiguous bytes per store.  For the
+//     SwiGLU epilogue, where finishing a chunk costs far more than reading it, three of the four
+//     chunks are parked in an L2-resident scratch so that the tensor pipe gets the accumulator
+//     back after four reads;
 //   * for SwiGLU the unpack warps place gate channels in lanes 0-15 and the matching up
 //     channels in lanes 16-31 of every tensor-memory lane quarter, so the epilogue pairs them
 //     with one warp shuffle.
@@ -43,6 +46,7 @@ constexpr size_t PS_XA_BYTES = 2 * (size_t)PS_T * 128;   // 32768
 constexpr size_t PS_XW_BYTES = 2 * 8192;                 // 16384
 constexpr int PS_BARRIERS = 2 * PS_XA + 2 * PS_XW + 2 * PS_ABUF + 2;
 constexpr size_t PS_SMEM_BYTES = PS_XA * PS_XA_BYTES + PS_XW * PS_XW_BYTES + 2 * PS_TOK * 4 + PS_BARRIERS * 8 + 32;
+constexpr int PS_PARK_INTS = 3 * 32 * 32 * PS_EPI_WARPS;   // per CTA: three parked chunks of 32 sums per epilogue thread (96 KB)
 static_assert(PS_SMEM_BYTES <= 232448, "exceeds the shared memory of one CTA");
 static_assert(PS_XW == PS_ABUF, "a weight stage and its tensor-memory buffer share one index");
 
@@ -300,16 +304,41 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
             if (!ok) { *s_error = 1; break; }
             if (sid == 0) PS_STAMP(j, 3);
             tc_fence_after();
+            // The tensor pipe stands still until the accumulator is handed back.  Where finishing a chunk is expensive
+            // (`park`: the SwiGLU epilogue, fp32 / int32 stores) the first three chunks are only moved: tensor memory ->
+            // registers -> this thread's own slots of a scratch in global memory (it stays in L2); the fourth stays in
+            // registers, the accumulator goes back, and then the four chunks are finished, the parked ones read back
+            // by the thread that wrote them.
+            const bool park = p.partials != nullptr && t + num_clusters < total;   // (nothing waits behind a cluster's last tile)
+            int* const park_at = park ? p.partials + (size_t)blockIdx.x * PS_PARK_INTS + sid : nullptr;
+            if (park) {
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < 3; ++c) {
+                    const int t0 = eset * 32 + 64 * c;
+                    if (tok_base + t0 >= p.M) continue;
+                    uint32_t r[32];
+                    tc_ld32(lane_addr + t0, r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) __stcg(park_at + (c * 32 + i) * 256, (int)r[i]);
+                }
+            }
+#pragma unroll 1
+            for (int k = 0; k < 4; ++k) {
+                const int c = park ? (k + 3) & 3 : k;
                 const int t0 = eset * 32 + 64 * c;
                 const bool live_chunk = tok_base + t0 < p.M;
                 uint32_t r[32];
                 if (live_chunk) {
-                    tc_ld32(lane_addr + t0, r);
-                    tc_wait_ld();
+                    if (!park || k == 0) {
+                        tc_ld32(lane_addr + t0, r);
+                        tc_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = (uint32_t)__ldcg(park_at + (c * 32 + i) * 256);
+                    }
                 }
-                if (c == 3) {
+                if (k == (park ? 0 : 3)) {
                     // ---- this warp is done with tensor memory: the next tile's MMAs may overwrite it
                     tc_fence_before();
                     __syncwarp();
@@ -460,6 +489,8 @@ bool gemm_tc_persist_supported(const GemmParams& p)
 {
     return p.pair && p.T == PS_T && (long long)p.KB * KBLOCK <= 131072;
 }
+
+size_t gemm_tc_persist_park_bytes(int sm_count) { return size_t(sm_count) * PS_PARK_INTS * sizeof(int); }
 
 cudaError_t launch_gemm_tc_persist(const GemmParams& p, cudaStream_t stream, bool pdl)
 {
