@@ -590,7 +590,9 @@ int run_locked(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, const vo
     // plain stores, so a host caller is served without the two copies behind the kernel: the kernel stores straight
     // into the caller's tensor when that is page-locked memory the GPU can address, and reports into the workspace's
     // own page-locked status block.  (The activations are still copied in: every CTA reads them.)
-    const bool single_kernel = (ws->variant == 3 || ws->variant == 5) && !grouped(*ws) && epi != EPI_SWIGLU;
+    // (Not when the caller asks for stage timings: the device part of a call must not contain stores that cross the bus,
+    // or the figures of different kernel families -- which the search tuner ranks -- stop being comparable.)
+    const bool single_kernel = (ws->variant == 3 || ws->variant == 5) && !grouped(*ws) && epi != EPI_SWIGLU && !metrics;
     void* c_alias = (!c_dev && single_kernel && out_bytes <= (size_t(1) << 20)) ? c_at.alias : nullptr;
     // ... and an ordinary host result of a small batch lands in the workspace's page-locked piece and is copied out by the host
     const bool bounce_out = !c_dev && !c_alias && single_kernel && ws->bounce_out_alias && out_bytes <= ws->bounce_bytes;
