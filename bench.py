@@ -684,7 +684,7 @@ def _w8a8_prefill(rk, dom, dev, oracle, peak_tops):
     ws.free()
     w.free()
     return {"us": sec * 1e6, "tops": tops, "sampled_exact": exact, "frac_of_measured_int8_peak": tops / peak_tops if peak_tops else None,
-            "includes": "w8_quantize_kernel + per-tile tcgen05 GEMM with int8 weights + the call's host synchronisation"}
+            "includes": "w8_quantize_kernel + persistent tcgen05 GEMM with int8 weights + the call's host synchronisation"}
 
 
 def _check_ffn(oracle, A, Bg, sg, Bd, sd, middle, C):

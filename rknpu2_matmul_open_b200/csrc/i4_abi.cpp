@@ -125,9 +125,12 @@ int contract(rk_npu_i4_workspace* ws, const rk_npu_i4i4i32_weights* w, const int
     g.KB = ws->KB; g.NG = w->NG; g.T = ws->T;
     g.epi = EPI_I32;
     g.split = 1;
+    g.pair = cfg.M > 128 ? 1 : 0;              // beyond 128 tokens: 128-token tiles, two per CTA pair of the persistent kernel
     g.timeout_ns = (unsigned long long)cfg.timeout_ms * 1000000ull;
     const auto t0 = Clock::now();
-    if (launch_w8_quantize(q, s) != cudaSuccess || launch_gemm_tc(g, s, false) != cudaSuccess) {
+    const bool persistent = g.pair && gemm_tc_persist_supported(g);
+    if (launch_w8_quantize(q, s) != cudaSuccess ||
+        (persistent ? launch_gemm_tc_persist(g, s, false) : launch_gemm_tc(g, s, false)) != cudaSuccess) {
         cudaGetLastError();
         cudaStreamSynchronize(s);
         return RK_NPU_ERR_SUBMIT;
@@ -232,9 +235,9 @@ extern "C" rk_npu_i4_workspace* rk_npu_i4_workspace_create(rk_npu_iommu_domain* 
         ws->ctx_id = ctx->id;
         ws->domain_id = domain->id;
         domain_retain(domain);
-        ws->T = std::min(256, align_up(cfg->M, 16));
+        ws->T = cfg->M > 128 ? 128 : align_up(cfg->M, 16);
         ws->KB = (cfg->K + KBLOCK - 1) / KBLOCK;
-        ws->codes_bytes = size_t(align_up(cfg->M, ws->T)) * size_t(ws->KB) * KBLOCK;
+        ws->codes_bytes = size_t(align_up(cfg->M, cfg->M > 128 ? 256 : ws->T)) * size_t(ws->KB) * KBLOCK;
         ws->stage_in_bytes = size_t(cfg->M) * cfg->K;
         ws->stage_out_bytes = size_t(cfg->M) * cfg->N * sizeof(int32_t);
         bool ok = cudaStreamCreateWithFlags(&ws->stream, cudaStreamNonBlocking) == cudaSuccess &&

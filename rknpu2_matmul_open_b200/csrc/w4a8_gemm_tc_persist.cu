@@ -30,8 +30,10 @@
 
 namespace rkb200 {
 
-constexpr int PS_XA = 5;                     // activation ring: stages of 2 k-blocks (2 x 16 KB)
-constexpr int PS_XW = 4;                     // weight ring: stages of 2 k-blocks (4 groups x 2 x 2 KB)
+// activation ring: stages of 2 k-blocks (2 x 16 KB); five deep for int4 weights, three where int8 weights (the
+// W8A8 operators) take twice the room in the weight ring
+__host__ __device__ constexpr int ps_xa(bool w8) { return w8 ? 3 : 5; }
+constexpr int PS_XW = 4;                     // weight ring: stages of 2 k-blocks (4 groups x 2 x 2 KB, or x 4 KB for int8 weights)
 constexpr int PS_ABUF = 4;                   // weight buffers in tensor memory, one stage (2 k-blocks, 64 columns) each
 constexpr int PS_UNPACK_WARPS = 8;
 constexpr int PS_EPI_WARPS = 8;              // two per tensor-memory lane quarter, alternating 32-token chunks
@@ -43,15 +45,25 @@ constexpr int PS_TOK = 256;                  // tokens of the MMA tile (accumula
 constexpr int PS_A_COL0 = 256;
 constexpr int PS_TMEM_COLS = 512;
 constexpr size_t PS_XA_BYTES = 2 * (size_t)PS_T * 128;   // 32768
-constexpr size_t PS_XW_BYTES = 2 * 8192;                 // 16384
-constexpr int PS_BARRIERS = 2 * PS_XA + 2 * PS_XW + 2 * PS_ABUF + 2;
-constexpr size_t PS_SMEM_BYTES = PS_XA * PS_XA_BYTES + PS_XW * PS_XW_BYTES + 2 * PS_TOK * 4 + PS_BARRIERS * 8 + 32;
+__host__ __device__ constexpr size_t ps_group_bytes(bool w8) { return w8 ? 4096 : 2048; }   // one k-block of one 32-channel group
+__host__ __device__ constexpr size_t ps_xw_bytes(bool w8) { return 2 * 4 * ps_group_bytes(w8); }   // 16384 / 32768
+__host__ __device__ constexpr int ps_barriers(bool w8) { return 2 * ps_xa(w8) + 2 * PS_XW + 2 * PS_ABUF + 2; }
+__host__ __device__ constexpr size_t ps_smem_bytes(bool w8)
+{
+    return ps_xa(w8) * PS_XA_BYTES + PS_XW * ps_xw_bytes(w8) + 2 * PS_TOK * 4 + ps_barriers(w8) * 8 + 32;
+}
 constexpr int PS_PARK_INTS = 3 * 32 * 32 * PS_EPI_WARPS;   // per CTA: three parked chunks of 32 sums per epilogue thread (96 KB)
-static_assert(PS_SMEM_BYTES <= 232448, "exceeds the shared memory of one CTA");
+static_assert(ps_smem_bytes(false) <= 232448 && ps_smem_bytes(true) <= 232448, "exceeds the shared memory of one CTA");
 static_assert(PS_XW == PS_ABUF, "a weight stage and its tensor-memory buffer share one index");
 
+// W8: the weights are int8 codes in the W8 layout (w8a8_kernels.cu): "unpacking" is a copy into tensor memory and the sums
+// are not scaled by 16.
+template <bool W8>
 __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const GemmParams p, int num_clusters)
 {
+    constexpr int PS_XA = ps_xa(W8);
+    constexpr size_t PS_XW_BYTES = ps_xw_bytes(W8);
+    constexpr uint32_t GB = (uint32_t)ps_group_bytes(W8);
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* const acts = smem;
     uint8_t* const wts = acts + PS_XA * PS_XA_BYTES;
@@ -118,16 +130,16 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
         while (wp_t < total && wp_gi < limit) {
             const int tile = 2 * (wp_t % pairs_n) + (int)rank;
             const int group = swiglu ? (w < 2 ? tile * 2 + w : p.F / GROUP + tile * 2 + (w - 2)) : tile * 4 + w;
-            const uint8_t* wsrc = p.Wp + (size_t)group * KC * 512;
+            const uint8_t* wsrc = p.Wp + (size_t)group * KB * GB;
             const int s = wp_gi % PS_XW;
             const int kbs = min(2, KB - 2 * wp_it);
             if (lane == 0) {
                 if (wp_gi >= PS_XW) ok = mbar_wait(&wempty[s], ((wp_gi / PS_XW) - 1) & 1, deadline);
-                if (ok) mbar_arrive_expect_tx(&wfull[s], (uint32_t)kbs * 8192u);
+                if (ok) mbar_arrive_expect_tx(&wfull[s], (uint32_t)kbs * 4u * GB);
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) { *s_error = 1; return false; }
-            if (lane < 4) bulk_g2s(wts + (size_t)s * PS_XW_BYTES + w * 4096, wsrc + (size_t)wp_it * 4096, (uint32_t)kbs * 2048u, &wfull[s]);
+            if (lane < 4) bulk_g2s(wts + (size_t)s * PS_XW_BYTES + w * 2 * GB, wsrc + (size_t)wp_it * 2 * GB, (uint32_t)kbs * GB, &wfull[s]);
             ++wp_gi;
             if (++wp_it == nst) { wp_it = 0; wp_t += num_clusters; }
         }
@@ -232,7 +244,26 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) { *s_error = 1; break; }
                 tc_fence_after();
-                const uint4* src = reinterpret_cast<const uint4*>(wts + (size_t)s * PS_XW_BYTES + src_group * 4096) + src_row;
+                const uint4* src = reinterpret_cast<const uint4*>(wts + (size_t)s * PS_XW_BYTES + src_group * 2 * GB) + src_row;
+                if constexpr (W8) {
+                    // int8 codes: a lane's sixteen 16-byte pieces of the stage are the words of its tensor-memory row in order
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        if (h < kbs) {
+                            uint32_t r[32];
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) {
+                                const uint4 v = src[(8 * h + c) * 32];
+                                r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
+                            }
+                            if (h == kbs - 1) {
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(&wempty[s]);    // the stage has been read into registers
+                            }
+                            tc_st32(lane_addr + PS_A_COL0 + b * 64 + h * 32, r);
+                        }
+                    }
+                } else {
                 uint4 w[8];
 #pragma unroll
                 for (int c = 0; c < 8; ++c) w[c] = (c < 4 * kbs) ? src[c * 32] : make_uint4(0u, 0u, 0u, 0u);
@@ -253,6 +284,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                         }
                         tc_st32(lane_addr + PS_A_COL0 + b * 64 + h * 32, r);
                     }
+                }
                 }
                 tc_wait_st();
                 tc_fence_before();
@@ -283,7 +315,8 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
         const bool up_lane = swiglu && lane >= 16;
         const int odd = lane & 1;
         const bool quad_ok = (out_cols % 4 == 0) && (reinterpret_cast<uintptr_t>(p.out) & 7u) == 0;
-        const bool small_sums = (long long)KB * KBLOCK * 7 * 127 < (1ll << 22);
+        constexpr int SHIFT = W8 ? 0 : 4;             // int4 records enter the MMA times 16
+        const bool small_sums = (long long)KB * KBLOCK * (W8 ? 127 : 7) * 127 < (1ll << 22);
         bool ok = !skip;
         int j = 0;
         for (int t = cluster_id; t < total && ok; t += num_clusters, ++j) {
@@ -366,10 +399,10 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                 if (p.epi != EPI_I32) {
                     if (small_sums) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__fsub_rn(__uint_as_float(0x4B400000u + (uint32_t)((int)r[i] >> 4)), 12582912.f));
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__fsub_rn(__uint_as_float(0x4B400000u + (uint32_t)((int)r[i] >> SHIFT)), 12582912.f));
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__int2float_rn((int)r[i] >> 4));
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__int2float_rn((int)r[i] >> SHIFT));
                     }
                 }
                 if (p.epi == EPI_F16) {
@@ -420,7 +453,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                     const bool f32 = p.epi == EPI_F32;
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        r[i] = f32 ? __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r[i]), sxr[i]), sw)) : (uint32_t)((int)r[i] >> 4);
+                        r[i] = f32 ? __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r[i]), sxr[i]), sw)) : (uint32_t)((int)r[i] >> SHIFT);
                     }
                     uint32_t* const row0 = reinterpret_cast<uint32_t*>(p.out) + (size_t)m0 * out_cols + n;
                     if (n_ok) {
@@ -492,9 +525,10 @@ bool gemm_tc_persist_supported(const GemmParams& p)
 
 size_t gemm_tc_persist_park_bytes(int sm_count) { return size_t(sm_count) * PS_PARK_INTS * sizeof(int); }
 
-cudaError_t launch_gemm_tc_persist(const GemmParams& p, cudaStream_t stream, bool pdl)
+template <bool W8>
+static cudaError_t launch_persist_inst(const GemmParams& p, cudaStream_t stream, bool pdl)
 {
-    if (!gemm_tc_persist_supported(p)) return cudaErrorInvalidValue;
+    auto kernel = gemm_tc_persist_kernel<W8>;
     static PerDeviceOnce configured;
     static int clusters_of_device[64] = {};   // resident CTA pairs, per CUDA ordinal
     int device = -1;
@@ -503,7 +537,7 @@ cudaError_t launch_gemm_tc_persist(const GemmParams& p, cudaStream_t stream, boo
     if (!setup) max_clusters = clusters_of_device[device];
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(PS_THREADS);
-    cfg.dynamicSmemBytes = PS_SMEM_BYTES;
+    cfg.dynamicSmemBytes = ps_smem_bytes(W8);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -511,14 +545,14 @@ cudaError_t launch_gemm_tc_persist(const GemmParams& p, cudaStream_t stream, boo
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     if (setup || !max_clusters) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PS_SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ps_smem_bytes(W8));
         if (e != cudaSuccess) return e;
         // how many CTA pairs can be resident at once: the grid is exactly that many
         cfg.gridDim = dim3(2, 1, 1);
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         int n = 0;
-        e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_persist_kernel, &cfg);
+        e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
         if (e != cudaSuccess || n < 1) { cudaGetLastError(); int dev = 0, sms = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); n = sms / 2; }
         max_clusters = n;
         if (device >= 0 && device < 64) { clusters_of_device[device] = n; configured.mark(device); }
@@ -535,7 +569,13 @@ cudaError_t launch_gemm_tc_persist(const GemmParams& p, cudaStream_t stream, boo
     }
     cfg.attrs = attr;
     cfg.numAttrs = n;
-    return cudaLaunchKernelEx(&cfg, gemm_tc_persist_kernel, p, clusters);
+    return cudaLaunchKernelEx(&cfg, kernel, p, clusters);
+}
+
+cudaError_t launch_gemm_tc_persist(const GemmParams& p, cudaStream_t stream, bool pdl)
+{
+    if (!gemm_tc_persist_supported(p)) return cudaErrorInvalidValue;
+    return p.w8 ? launch_persist_inst<true>(p, stream, pdl) : launch_persist_inst<false>(p, stream, pdl);
 }
 
 } // namespace rkb200

@@ -88,7 +88,10 @@ bool valid_strategy(const rk_npu_matmul_strategy* s)
 }
 // what the kernels need on top: K within the contraction kernel's range, sizes that fit
 bool runnable_shape(int M, int N, int K) { return K <= 131072 && (int64_t)M * K <= INT32_MAX && (int64_t)M * N <= INT32_MAX; }
-int token_tile(int M) { return std::min(256, align_up(M, 16)); }
+// Up to 128 tokens: one token tile per CTA of the per-tile kernel.  Beyond: 128-token tiles, two per CTA pair of the
+// persistent kernel (the code buffer then covers whole pairs of tiles).
+int token_tile(int M) { return M > 128 ? 128 : align_up(M, 16); }
+int token_span(int M) { return M > 128 ? 256 : token_tile(M); }
 
 struct Sizes {
     int T, KB, NG;
@@ -100,7 +103,7 @@ Sizes sizes_of(int M, int N, int K, int kind)
     z.T = token_tile(M);
     z.KB = (K + KBLOCK - 1) / KBLOCK;
     z.NG = align_up((N + GROUP - 1) / GROUP, 8) + 8;   // zero groups behind the last tile, as for the int4 weights
-    z.codes = size_t(align_up(M, z.T)) * size_t(z.KB) * KBLOCK;
+    z.codes = size_t(align_up(M, token_span(M))) * size_t(z.KB) * KBLOCK;
     z.scales = sizeof(float) * 2 * size_t(M);
     const int in_elem = kind == RK_NPU_MATMUL_I8I8I32 ? 1 : (kind <= RK_NPU_MATMUL_F16I8F16_STATIC ? 2 : 4);
     const int out_elem = kind == RK_NPU_MATMUL_I8I8I32 ? 4 : (kind <= RK_NPU_MATMUL_F16I8F16_STATIC ? 2 : 4);
@@ -263,8 +266,11 @@ int run(rk_npu_matmul_workspace* ws, const W8Weights* w, int kind, const void* A
     g.epi = kind == RK_NPU_MATMUL_I8I8I32 ? EPI_I32 : (kind <= RK_NPU_MATMUL_F16I8F16_STATIC ? EPI_F16 : EPI_F32);
     g.split = 1;
     g.w8 = 1;
+    g.pair = st.M > 128 ? 1 : 0;
     g.timeout_ns = (unsigned long long)W8_TIMEOUT_MS * 1000000ull;
-    if (launch_w8_quantize(q, s) != cudaSuccess || launch_gemm_tc(g, s, false) != cudaSuccess) {
+    const bool persistent = g.pair && gemm_tc_persist_supported(g);
+    if (launch_w8_quantize(q, s) != cudaSuccess ||
+        (persistent ? launch_gemm_tc_persist(g, s, false) : launch_gemm_tc(g, s, false)) != cudaSuccess) {
         cudaGetLastError();
         cudaStreamSynchronize(s);
         return RK_NPU_ERR_SUBMIT;

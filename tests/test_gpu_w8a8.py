@@ -35,7 +35,7 @@ def activations(M, K, seed, dtype):
 
 @pytest.mark.parametrize("dtype", ["f16", "f32"])
 @pytest.mark.parametrize("shape", [(1, 33, 5), (8, 4096, 4096), (16, 257, 70), (17, 1000, 131), (128, 2048, 384), (256, 640, 129),
-                                   (300, 1057, 513), (1024, 512, 256)], ids=lambda s: "x".join(map(str, s)))
+                                   (300, 1057, 513), (1024, 512, 256), (520, 768, 9985)], ids=lambda s: "x".join(map(str, s)))
 def test_dynamic_and_static(gpu, oracle, shape, dtype):
     _, dom, _ = gpu
     M, K, N = shape
