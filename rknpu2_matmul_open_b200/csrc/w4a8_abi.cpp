@@ -481,7 +481,9 @@ int enqueue(const Call& c)
     if (ws.variant == 2) {
         g.split = 1;
         g.pair = ws.pair ? 1 : 0;
-        // parking pays where finishing a chunk is expensive: the SwiGLU epilogue (see DESIGN); RK_NPU_B200_PARK_ALL=1 for all
+        // parking pays where finishing a chunk is expensive, i.e. for the SwiGLU epilogue (measured: the plain epilogues gain
+        // nothing, the extra L2 traffic lengthens their MMA phase as much as the earlier hand-back saves);
+        // RK_NPU_B200_PARK_ALL=1 parks for every epilogue (experiments)
         if (c.epi == EPI_SWIGLU || env_flag("RK_NPU_B200_PARK_ALL", false)) g.partials = ws.partials;
         if (gemm_tc_persist_supported(g) && !env_flag("RK_NPU_B200_NO_PERSIST", false)) err = launch_gemm_tc_persist(g, c.stream, pdl);
         else err = launch_gemm_tc(g, c.stream, pdl);
