@@ -67,8 +67,9 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* const acts = smem;
     uint8_t* const wts = acts + PS_XA * PS_XA_BYTES;
-    float* const s_sx = reinterpret_cast<float*>(wts + PS_XW * PS_XW_BYTES);   // two tiles' worth, alternating
-    uint64_t* const xfull = reinterpret_cast<uint64_t*>(s_sx + 2 * PS_TOK);
+    float* const s_sx = reinterpret_cast<float*>(wts + PS_XW * PS_XW_BYTES);   // token scales of the tile being finished
+    uint32_t* const s_tilemax = reinterpret_cast<uint32_t*>(s_sx + PS_TOK);      // SwiGLU: the CTA's row maxima of that tile
+    uint64_t* const xfull = reinterpret_cast<uint64_t*>(s_tilemax + PS_TOK);
     uint64_t* const xempty = xfull + PS_XA;
     uint64_t* const wfull = xempty + PS_XA;
     uint64_t* const wempty = wfull + PS_XW;
@@ -109,6 +110,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
         mbar_fence_init();
         *s_error = 0;
     }
+    if (tid < PS_TOK) s_tilemax[tid] = 0u;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(PS_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
@@ -326,12 +328,12 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
             const int n = col0 + col;
             const bool n_ok = n < out_cols;
             const float sw = n_ok ? p.sw[(up_lane ? p.F : 0) + n] : 0.f;
-            float* const sx = s_sx + (j & 1) * PS_TOK;
+            float* const sx = s_sx;
             {
                 const int m = tok_base + sid;
                 sx[sid] = m < p.M ? p.sx[m] : 0.f;
             }
-            asm volatile("bar.sync 1, 256;" ::: "memory");   // scales staged (the other half still serves stragglers of tile j-1)
+            asm volatile("bar.sync 1, 256;" ::: "memory");   // scales staged (the barrier at the end of a tile keeps stragglers out)
             ok = mbar_wait_cluster(acc_full, j & 1, deadline);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { *s_error = 1; break; }
@@ -481,28 +483,41 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                         const bool live = n_ok && mine_row + 2 * i < p.M;
                         mx[i] = live ? (__float_as_uint(y[i]) & 0x7fffffffu) : 0u;
                     }
-                    if (p.rowmax) {
-                        // maxima over the 16 lanes of each half (one token each)
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-#pragma unroll
-                            for (int o = 8; o > 0; o >>= 1) mx[i] = max(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], o));
-                        }
-                    }
                     float* const row0 = reinterpret_cast<float*>(p.out) + (size_t)mine_row * out_cols + n;
                     if (n_ok) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
                             if (mine_row + 2 * i < p.M) row0[(size_t)(2 * i) * out_cols] = y[i];
                     }
-                    if (p.rowmax && (lane & 15) == 0) {
+                    if (p.rowmax) {
+                        // Maxima over the 16 lanes of each half, one token per value: a folding exchange that halves
+                        // the values a lane holds at every step (8 + 4 + 2 + 1 shuffles instead of 16 x 4); lane l of
+                        // a half ends up with the maximum of token l & 15 and issues that token's one atomic.
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            if (mx[i]) atomicMax(&p.rowmax[mine_row + 2 * i], mx[i]);
+                        for (int width = 8; width > 0; width >>= 1) {
+                            const bool upper = (lane & width) != 0;
+#pragma unroll
+                            for (int k = 0; k < width; ++k) {
+                                const uint32_t keep = upper ? mx[k + width] : mx[k];
+                                const uint32_t give = upper ? mx[k] : mx[k + width];
+                                mx[k] = max(keep, __shfl_xor_sync(0xffffffffu, give, width));
+                            }
+                        }
+                        // collected per CTA and tile in shared memory first: one global atomic per token and tile
+                        // instead of one per token, tile and 16 features
+                        if (mx[0]) atomicMax(&s_tilemax[t0 + (up_lane ? 1 : 0) + 2 * (lane & 15)], mx[0]);
                     }
                 }
             }
             if (sid == 0) PS_STAMP(j, 5);
+            asm volatile("bar.sync 1, 256;" ::: "memory");   // every epilogue warp is done with this tile's scales and maxima
+            if (swiglu && p.rowmax) {
+                const uint32_t m = s_tilemax[sid];
+                if (m) {
+                    atomicMax(&p.rowmax[tok_base + sid], m);
+                    s_tilemax[sid] = 0u;
+                }
+            }
         }
     }
 
