@@ -1073,9 +1073,13 @@ rk_npu_w4a8_workspace* rkb200::create_workspace_scheduled(rk_npu_iommu_domain* d
         ws->tiles_per_cta_override = (v == 1 || v == 2) ? v : 0;
     }
     if (variant == 2) {
-        // Batches above 128 tokens run two-CTA tiles: 128-token code tiles, two per MMA tile.
+        // Two-CTA tiles (128-token code tiles, two per MMA tile) on the persistent kernel.  Also for 33..128 tokens,
+        // where half of every MMA multiplies zero tokens: its resident CTA pairs still beat one launch-and-leave CTA
+        // per tile (FFN 4096 -> 2 x 14336 -> 4096 at 128 tokens 129 -> 104 us, the 128 x 4096 x 28672 linear 49 -> 41 us).
         ws->TC = 0;
-        ws->pair = cfg->M > 128 && !env_flag("RK_NPU_B200_NO_PAIR", false);
+        int pair_min = 33;
+        if (const char* e = std::getenv("RK_NPU_B200_PAIR_MIN")) pair_min = std::max(1, std::atoi(e));   // experiments
+        ws->pair = cfg->M >= pair_min && !env_flag("RK_NPU_B200_NO_PAIR", false);
         ws->T = ws->pair ? 128 : (cfg->M >= 256 ? 256 : align_up(cfg->M, 16));
     } else if (variant == 4) {
         ws->TC = ws->T = cfg->M <= 16 ? 16 : cfg->M <= 32 ? 32 : cfg->M <= 64 ? 64 : 128;   // tcgen05 N

@@ -7,8 +7,12 @@
 // The protocol is the original's: complete blocking calls on a deterministic calibration tensor, every
 // candidate's output compared with an anchor result that was itself checked against the int64 formula,
 // warm-up + loops x repeats, median over the repeats, jitter = range / median, robust = median + half
-// the range.  The winner is written into the strategy's existing fields (w4a8_tune.h: schedule_of), so
-// cache files keep their format and a tuned workspace honours the choice.
+// the range.  What RANKS the candidates is measured the way the kernels are used in a model: `loops`
+// launches queued back to back on one stream over device tensors, timed by two events (a blocking
+// call's own device window is a few microseconds of kernel inside tens of microseconds of launch
+// latency and cannot tell the families apart on small shapes).  The winner is written into the
+// strategy's existing fields (w4a8_tune.h: schedule_of), so cache files keep their format and a tuned
+// workspace honours the choice.
 #include "w4a8_tune.h"
 #include <algorithm>
 #include <cfloat>
@@ -53,6 +57,49 @@ struct Calibration {
     std::vector<float> a32;
     std::vector<uint16_t> a16;
     std::vector<uint8_t> out, anchor;      // raw output bytes of the last run / of the anchor run
+    void* dA = nullptr;                    // the same tensor and an output on the device, for the queued timing
+    void* dC = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+
+    Calibration(const Calibration&) = delete;
+    Calibration& operator=(const Calibration&) = delete;
+    ~Calibration()
+    {
+        if (dA) cudaFree(dA);
+        if (dC) cudaFree(dC);
+        if (e0) cudaEventDestroy(e0);
+        if (e1) cudaEventDestroy(e1);
+    }
+    // device copies, made on first use (the CUDA device of the search is current)
+    bool on_device()
+    {
+        if (dA) return true;
+        const size_t a_bytes = half ? a16.size() * 2 : a32.size() * 4;
+        const bool ok = cudaMalloc(&dA, a_bytes) == cudaSuccess && cudaMalloc(&dC, out.size()) == cudaSuccess &&
+                        cudaMemcpy(dA, half ? static_cast<const void*>(a16.data()) : static_cast<const void*>(a32.data()), a_bytes,
+                                   cudaMemcpyHostToDevice) == cudaSuccess &&
+                        cudaEventCreate(&e0) == cudaSuccess && cudaEventCreate(&e1) == cudaSuccess;
+        if (!ok) cudaGetLastError();
+        return ok;
+    }
+    // `loops` launches queued back to back on the workspace's stream: microseconds per launch, < 0 on failure
+    double queued_us(rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weights* w, int loops)
+    {
+        if (!on_device()) return -1;
+        cudaStream_t s = ws->stream;
+        cudaEventRecord(e0, s);
+        for (int l = 0; l < loops; ++l) {
+            const int rc = half ? rk_npu_b200_w4a8_enqueue_f16(ws, w, static_cast<const uint16_t*>(dA), static_cast<uint16_t*>(dC), s)
+                                : rk_npu_b200_w4a8_enqueue_f32(ws, w, static_cast<const float*>(dA), static_cast<float*>(dC), s);
+            if (rc) { cudaStreamSynchronize(s); return -1; }
+        }
+        cudaEventRecord(e1, s);
+        if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return -1; }
+        if (rk_npu_b200_w4a8_finish(ws) != RK_NPU_OK) return -1;
+        float ms = 0;
+        if (cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess) { cudaGetLastError(); return -1; }
+        return double(ms) * 1000.0 / loops;
+    }
 
     explicit Calibration(const rk_npu_w4a8_autotune_config& c)
         : M(c.M), K(c.K), N(c.N), half(c.activation_type == RK_NPU_W4A8_F16), a32(size_t(c.M) * c.K),
@@ -198,7 +245,9 @@ int measure(Calibration& data, rk_npu_w4a8_workspace* ws, const rk_npu_w4a8_weig
         const double n = request.loops;
         total.push_back(s_total / n); input.push_back(s_input / n); device.push_back(s_device / n);
         sync.push_back(s_sync / n); output.push_back(s_output / n);
-        work.push_back((s_input + s_device + s_output) / n);
+        // what ranks the candidate: launches queued back to back (at least eight, so that launch latency is hidden)
+        const double queued = data.queued_us(ws, w, std::max(8, request.loops));
+        work.push_back(queued >= 0 ? queued : (s_input + s_device + s_output) / n);
     }
     score.total_us = median_of(total);
     score.input_us = median_of(input);
