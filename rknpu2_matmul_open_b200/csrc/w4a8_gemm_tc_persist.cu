@@ -473,15 +473,25 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                     uint32_t mx[16];
                     const int mine_row = m0 + (up_lane ? 1 : 0);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float a0 = __uint_as_float(r[2 * i]), a1 = __uint_as_float(r[2 * i + 1]);
-                        const float o0 = __shfl_xor_sync(0xffffffffu, a0, 16);   // gate lanes: u of token 2i; up lanes: g of token 2i
-                        const float o1 = __shfl_xor_sync(0xffffffffu, a1, 16);   // gate lanes: u of token 2i+1; up lanes: g of token 2i+1
-                        const float g = up_lane ? o1 : a0;
-                        const float u = up_lane ? a1 : o0;
-                        y[i] = __fmul_rn(silu_poly(g), u);
-                        const bool live = n_ok && mine_row + 2 * i < p.M;
-                        mx[i] = live ? (__float_as_uint(y[i]) & 0x7fffffffu) : 0u;
+                    for (int i0 = 0; i0 < 16; i0 += 4) {     // four tokens in lock step (see silu_poly4)
+                        float g4[4], u4[4], s4[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int i = i0 + k;
+                            const float a0 = __uint_as_float(r[2 * i]), a1 = __uint_as_float(r[2 * i + 1]);
+                            const float o0 = __shfl_xor_sync(0xffffffffu, a0, 16);   // gate lanes: u of token 2i; up lanes: g of token 2i
+                            const float o1 = __shfl_xor_sync(0xffffffffu, a1, 16);   // gate lanes: u of token 2i+1; up lanes: g of token 2i+1
+                            g4[k] = up_lane ? o1 : a0;
+                            u4[k] = up_lane ? a1 : o0;
+                        }
+                        silu_poly4(g4, s4);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int i = i0 + k;
+                            y[i] = __fmul_rn(s4[k], u4[k]);
+                            const bool live = n_ok && mine_row + 2 * i < p.M;
+                            mx[i] = live ? (__float_as_uint(y[i]) & 0x7fffffffu) : 0u;
+                        }
                     }
                     float* const row0 = reinterpret_cast<float*>(p.out) + (size_t)mine_row * out_cols + n;
                     if (n_ok) {

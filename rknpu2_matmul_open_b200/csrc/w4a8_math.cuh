@@ -119,6 +119,41 @@ __device__ __forceinline__ float silu_poly(float g)
     const float d = __fadd_rn(1.f, __fmul_rn(q, power));
     return g < -80.f ? -0.f : __fdiv_rn(g, d);
 }
+// The same function for four arguments in lock step: every statement is applied to all four values before the next
+// one.  Each value goes through exactly the operations of silu_poly (same bits); what changes is that the four
+// dependent chains are interleaved in program order -- written one value after the other, sixteen evaluations took
+// 2190 cycles per warp, in lock step 1420 (the divisions sit in separate basic blocks and are not interleaved by
+// the compiler on its own).
+__device__ __forceinline__ void silu_poly4(const float (&g)[4], float (&y)[4])
+{
+    float x[4], n[4], r[4], q[4], d[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[j] = fminf(fmaxf(-g[j], -80.f), 80.f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) n[j] = floorf(fmaf(x[j], 1.4426950408889634f, 0.5f));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) r[j] = fmaf(-n[j], 0.693145751953125f, x[j]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) r[j] = fmaf(-n[j], 1.428606765330187e-6f, r[j]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = fmaf(1.f / 5040.f, r[j], 1.f / 720.f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = fmaf(q[j], r[j], 1.f / 120.f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = fmaf(q[j], r[j], 1.f / 24.f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = fmaf(q[j], r[j], 1.f / 6.f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = fmaf(q[j], r[j], 0.5f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = fmaf(q[j], r[j], 1.f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = fmaf(q[j], r[j], 1.f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) d[j] = __fadd_rn(1.f, __fmul_rn(q[j], __int_as_float(((int)n[j] + 127) << 23)));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) y[j] = g[j] < -80.f ? -0.f : __fdiv_rn(g[j], d[j]);
+}
 __device__ __forceinline__ float dequant(int acc, float sx, float sw)
 {
     return __fmul_rn(__fmul_rn(__int2float_rn(acc), sx), sw);
