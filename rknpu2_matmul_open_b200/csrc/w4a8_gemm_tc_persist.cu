@@ -358,6 +358,13 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                     for (int i = 0; i < 32; ++i) __stcg(park_at + (c * 32 + i) * 256, (int)r[i]);
                 }
             }
+            long long phase_t = (trace && sid == 0) ? clock64() : 0;
+            // (diagnostics) cycles the first epilogue thread spends per phase of finishing, summed over the launch:
+            // [176] getting a chunk into registers, [177] scales and conversion, [178] the epilogue proper and its stores
+            // (SwiGLU: [180] dequantisation, [181] pairing and SiLU, [182] stores, and [178] what is left: the row maxima)
+            auto phase = [&](int which) {
+                if (trace && sid == 0) { const long long now = clock64(); trace[176 + which] += (unsigned long long)(now - phase_t); phase_t = now; }
+            };
 #pragma unroll 1
             for (int k = 0; k < 4; ++k) {
                 const int c = park ? (k + 3) & 3 : k;
@@ -381,6 +388,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                     if (sid == 0) PS_STAMP(j, 4);
                 }
                 if (!live_chunk) continue;
+                phase(0);
                 // All loads of a chunk come first, then the arithmetic, then the stores: the compiler
                 // may not move a load across a store it cannot prove unrelated, and one store per
                 // loop iteration would serialise the whole chunk on the latency of each iteration.
@@ -407,6 +415,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__int2float_rn((int)r[i] >> SHIFT));
                     }
                 }
+                phase(1);
                 if (p.epi == EPI_F16) {
                     // a lane holds one channel of 32 tokens; neighbouring lanes swap halves so that
                     // every lane stores two neighbouring channels of one token as one 32-bit word
@@ -472,6 +481,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                     float y[16];
                     uint32_t mx[16];
                     const int mine_row = m0 + (up_lane ? 1 : 0);
+                    phase(4);
 #pragma unroll
                     for (int i0 = 0; i0 < 16; i0 += 4) {     // four tokens in lock step (see silu_poly4)
                         float g4[4], u4[4], s4[4];
@@ -493,12 +503,14 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                             mx[i] = live ? (__float_as_uint(y[i]) & 0x7fffffffu) : 0u;
                         }
                     }
+                    phase(5);
                     float* const row0 = reinterpret_cast<float*>(p.out) + (size_t)mine_row * out_cols + n;
                     if (n_ok) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
                             if (mine_row + 2 * i < p.M) row0[(size_t)(2 * i) * out_cols] = y[i];
                     }
+                    phase(6);
                     if (p.rowmax) {
                         // Maxima over the 16 lanes of each half, one token per value: a folding exchange that halves
                         // the values a lane holds at every step (8 + 4 + 2 + 1 shuffles instead of 16 x 4); lane l of
@@ -518,9 +530,11 @@ __global__ void __launch_bounds__(PS_THREADS, 1) gemm_tc_persist_kernel(const Ge
                         if (mx[0]) atomicMax(&s_tilemax[t0 + (up_lane ? 1 : 0) + 2 * (lane & 15)], mx[0]);
                     }
                 }
+                phase(2);
             }
             if (sid == 0) PS_STAMP(j, 5);
             asm volatile("bar.sync 1, 256;" ::: "memory");   // every epilogue warp is done with this tile's scales and maxima
+            phase(3);
             if (swiglu && p.rowmax) {
                 const uint32_t m = s_tilemax[sid];
                 if (m) {
