@@ -35,6 +35,50 @@ def test_library_exports_every_declared_symbol(lib):
         assert hasattr(lib, name), name
 
 
+def _abi_layout():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("abi_layout", ROOT / "tests" / "golden" / "abi_layout.py")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module
+
+
+def test_struct_layouts_and_constants_equal_the_original_headers():
+    # tests/golden/reference_abi_layout.txt holds, for every struct, member, enumerator and macro constant that
+    # include/*.h declares, the size / offset / value a C compiler derives from the ORIGINAL project's headers; the same
+    # program compiled against include/*.h must print the same text, so a caller compiled against either header
+    # passes structs this library reads correctly.
+    abi = _abi_layout()
+    structs, constants = abi.declared_names()
+    assert len(structs) == 28 and "rk_npu_moe_w8_timings" in structs and "RK_NPU_ERR_BUSY" in constants
+    assert structs["rk_npu_moe_w8_timings"][:3] == ["input_us", "schedule_us", "build_us"]      # "double a, b, c;"
+    ours = abi.layout(ROOT / "include", abi.OURS)
+    golden = (ROOT / "tests" / "golden" / "reference_abi_layout.txt").read_text()
+    assert ours == golden
+    reference = Path(os.environ.get("REF", "/root/reference")) / "include"      # oracle/Makefile's REF
+    if reference.is_dir():           # where the original tree is at hand, the golden file itself is re-derived
+        assert abi.layout(reference, abi.THEIRS) == golden
+        assert abi.functions(reference, abi.THEIRS) == (ROOT / "tests" / "golden" / "reference_header_symbols.txt").read_text().split()
+
+
+def test_ctypes_mirrors_have_the_c_sizes():
+    # the Python structs the tests and the bench pass through the ABI are the sizes the C headers give
+    abi = _abi_layout()
+    text = abi.layout(ROOT / "include", abi.OURS).splitlines()
+    sizes = dict(line.split()[1:3] for line in text if line.startswith("sizeof"))
+    offsets = {tuple(line.split()[1:3]): int(line.split()[3]) for line in text if line.startswith("offsetof")}
+    mirrors = {"rk_npu_w4a8_config": capi.W4A8Config, "rk_npu_w4a8_options": capi.W4A8Options,
+               "rk_npu_w4a8_memory_info": capi.W4A8MemoryInfo, "rk_npu_w4a8_memory_info_ex": capi.W4A8MemoryInfoEx,
+               "rk_npu_w4a8_strategy": capi.W4A8Strategy, "rk_npu_w4a8_strategy_ex": capi.W4A8StrategyEx,
+               "rk_npu_w4a8_autotune_config": capi.W4A8AutotuneConfig, "rk_npu_i4_weight_config": capi.I4WeightConfig,
+               "rk_npu_moe_w8_weight_config": capi.MoeWeightConfig, "rk_npu_moe_w8_config": capi.MoeConfig,
+               "rk_npu_moe_w8_expert": capi.MoeExpert, "rk_npu_moe_w8_timings": capi.MoeTimings}
+    for name, mirror in mirrors.items():
+        assert C.sizeof(mirror) == int(sizes[name]), name
+        for field, _ in mirror._fields_:
+            assert getattr(mirror, field).offset == offsets[(name, field)], (name, field)
+
+
 def test_no_gpu_means_open_fails_loudly(lib):
     import torch
     if torch.cuda.is_available():
@@ -280,10 +324,11 @@ def test_cache_files_interoperate_with_reference_build(cache_case, reference, tm
 
 # ---------------------------------------------------------------- the rest of the original headers
 def test_every_entry_point_of_the_original_headers_links(lib):
-    # tests/golden/reference_header_symbols.txt: every function the five public headers of the path declare
-    # (rk_npu_common.h, rk_npu_matmul_i4.h, rk_npu_w4a8.h, rk_npu_w4a8_tune.h, rk_npu_quant_matmul.h)
+    # tests/golden/reference_header_symbols.txt (written by tests/golden/abi_layout.py --symbols): every function the
+    # six public headers of the path declare (rk_npu_common.h, rk_npu_matmul_i4.h, rk_npu_w4a8.h, rk_npu_w4a8_tune.h,
+    # rk_npu_quant_matmul.h, rk_npu_moe_w8.h)
     names = (ROOT / "tests" / "golden" / "reference_header_symbols.txt").read_text().split()
-    assert len(names) > 90
+    assert len(names) == 120
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, missing
     # operators that are not built decline instead of pretending
