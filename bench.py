@@ -18,7 +18,7 @@ The device-resident figure keeps column-parallel outputs sharded and gathers the
 step; the end-to-end figure uses the blocking call, which gathers inside every call.
 Total work is fixed, so scaling is "strong".
 
-`--case decode|prefill|mid|ffn` runs a small fixed workload for a kernel profiler instead.
+`--case decode|prefill|mid|ffn|moe|rmsnorm` runs a small fixed workload for a kernel profiler instead.
 
 `--impl reference` times the reference's own CPU stages (oracle/_ref, or the C port when
 that was not built) on the host cores for the same workload.
@@ -431,7 +431,8 @@ def run_cuda(args, rank, world, local_rank):
             also["layer_dependencies_only_error"] = str(exc)
     if not args.quick:
         peak = measure_int8_peak() if rank == 0 else None
-        for name, fn in (("prefill", _prefill), ("ffn_4096_14336", _ffn_llama8b), ("ffn_8192_28672", _ffn_70b), ("moe", _moe)):
+        for name, fn in (("prefill", _prefill), ("ffn_4096_14336", _ffn_llama8b), ("ffn_8192_28672", _ffn_70b), ("moe", _moe),
+                         ("add_rmsnorm", _add_rmsnorm)):
             try:
                 also.update(fn(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak))
             except Exception as exc:   # an extra figure must never cost the headline line
@@ -809,6 +810,82 @@ def _moe(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak):
     return {"moe_w8_H1536_I512_E128_shared_top8": out_fig}
 
 
+def _add_rmsnorm(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak):
+    """Residual add + RMSNorm (rk_npu_add_rmsnorm_f16), the step before the quantised FFN.  Device tensors through the
+    enqueue form: 4096 rows of 8192 and of 4096 in both layouts (each tensor set is 268 / 134 MB, larger than L2, and
+    the launches rotate over two sets), HBM rate = 4 tensors x 2 M D bytes over the device time; 128 x 4096 and 1 x 4096
+    as latency figures (launches queued back to back).  The original's blocking call on its own buffers (page-locked
+    host memory the kernel addresses over PCIe) at its two validated shapes, wall clock.  Eight rows of every result
+    are compared with the oracle bit for bit."""
+    if world > 1:
+        return {}
+    import torch
+    from rknpu2_matmul_open_b200 import rmsnorm
+    hbm, _, hbm_source = measured_peaks()
+    fig = {}
+    rng = np.random.default_rng(41)
+
+    def tensors(M, D):
+        x = np.clip(rng.normal(0, 0.8, (M, D)), -3, 3).astype(np.float16).view(np.uint16)
+        r = np.clip(rng.normal(0, 0.35, (M, D)), -1.5, 1.5).astype(np.float16).view(np.uint16)
+        return x, r
+
+    for M, D, reps in ((4096, 8192, 20), (4096, 4096, 20), (128, 4096, 100), (1, 4096, 100)):
+        gamma = (0.75 + 0.5 * np.arange(D) / (D - 1)).astype(np.float16).view(np.uint16)
+        plan = rmsnorm.AddRmsNormPlan(dom, rmsnorm.default_config(M, D), gamma)
+        x, r = tensors(M, D)
+        check = sorted(set(np.linspace(0, M - 1, 8).astype(int).tolist()))
+        want_s, want_n = oracle.add_rmsnorm_f16(x[check], r[check], gamma)
+        for row_major in (False, True):
+            lay = (lambda a: a.reshape(-1)) if row_major else rmsnorm.to_block8
+            sets = []
+            for _ in range(2 if M > 1024 else 8):
+                dx = torch.from_numpy(lay(x).astype(np.int16)).to(dev)
+                dr = torch.from_numpy(lay(r).astype(np.int16)).to(dev)
+                sets.append((dx, dr, torch.empty_like(dx), torch.empty_like(dx)))
+            turn = [0]
+
+            def one():
+                dx, dr, ds, dn = sets[turn[0] % len(sets)]
+                turn[0] += 1
+                if plan.enqueue(M, row_major, dx.data_ptr(), dr.data_ptr(), ds.data_ptr(), dn.data_ptr(), stream.cuda_stream):
+                    raise RuntimeError("rk_npu_b200_add_rmsnorm_f16_enqueue failed")
+
+            us = _event_time(torch, stream, one, reps) * 1e3
+            ds, dn = sets[0][2].cpu().numpy().view(np.uint16), sets[0][3].cpu().numpy().view(np.uint16)
+            if not row_major:
+                ds, dn = rmsnorm.from_block8(ds, M, D), rmsnorm.from_block8(dn, M, D)
+            exact = bool(np.array_equal(ds.reshape(M, D)[check], want_s) and np.array_equal(dn.reshape(M, D)[check], want_n))
+            gbps = 8.0 * M * D / (us * 1e-6) / 1e9
+            fig[f"enqueue_{M}x{D}_{'rows' if row_major else 'block8'}"] = {
+                "us": us, "GBps": gbps, f"frac_of_{hbm_source}_hbm": gbps / hbm, "rows_checked_exact": exact}
+            del sets
+        plan.free()
+    for M, D in ((1, 4096), (128, 4096)):
+        gamma = (0.75 + 0.5 * np.arange(D) / (D - 1)).astype(np.float16).view(np.uint16)
+        cfg = rmsnorm.default_config(M, D)
+        plan = rmsnorm.AddRmsNormPlan(dom, cfg, gamma)
+        bufs = [rmsnorm.Buffer(dom, rmsnorm.query(cfg).tensor_bytes) for _ in range(4)]
+        x, r = tensors(M, D)
+        bufs[0].array()[:] = rmsnorm.to_block8(x)
+        bufs[1].array()[:] = rmsnorm.to_block8(r)
+        for _ in range(3):
+            if plan.run(*bufs):
+                raise RuntimeError("rk_npu_add_rmsnorm_f16_run failed")
+        t0 = time.perf_counter()
+        for _ in range(50):
+            plan.run(*bufs)
+        call_us = (time.perf_counter() - t0) / 50 * 1e6
+        want_s, want_n = oracle.add_rmsnorm_f16(x, r, gamma)
+        exact = bool(np.array_equal(rmsnorm.from_block8(bufs[2].array(), M, D), want_s) and
+                     np.array_equal(rmsnorm.from_block8(bufs[3].array(), M, D), want_n))
+        fig[f"blocking_{M}x{D}_host_buffers"] = {"call_us": call_us, "exact": exact}
+        for b in bufs:
+            b.free()
+        plan.free()
+    return {"add_rmsnorm_f16": fig}
+
+
 def cpu_baseline(M, Reference, oracle, make_weights, make_activations):
     """One decoder layer's seven linears on the host, reference stages when built."""
     shapes, counts = [(4096, 4096), (4096, 11008), (11008, 4096)], [4, 2, 1]
@@ -857,6 +934,7 @@ def run_case(args):
       mid      one 128 x 11008 x 8192 linear, binary16 (few tiles, long K)
       ffn      gate/up 4096 -> 2 x 14336, SwiGLU, down 14336 -> 4096 at M = 1024, fp32
       moe      routed experts: 128 + 1 int8 experts, hidden 1536, intermediate 512, top-8, 64 rows (--case-tokens)
+      rmsnorm  residual add + RMSNorm, 4096 rows (--case-tokens) of 4096 on device tensors, block-8 layout
     --stamps enables the kernels' phase stamps after the launches, runs the set again (the decode set as one CUDA
     graph, the steady state of a dependent chain) and prints them."""
     import torch
@@ -894,6 +972,27 @@ def run_case(args):
         active = len(set(ids.reshape(-1).tolist())) + shared
         print(f"moe: rows={rows}, {active} active experts ({active * 3 * H * I / 1e6:.1f} MB of int8 weights per call), "
               f"{(time.perf_counter() - t0) / args.repeat * 1e6:.1f} us per call over {args.repeat} calls")
+        return
+    if args.case == "rmsnorm":
+        # residual add + RMSNorm on device tensors: --case-tokens rows (default 4096) of 4096, block-8 layout
+        from rknpu2_matmul_open_b200 import rmsnorm
+        M, D = args.case_tokens or 4096, 4096
+        gamma = (0.75 + 0.5 * np.arange(D) / (D - 1)).astype(np.float16).view(np.uint16)
+        plan = rmsnorm.AddRmsNormPlan(dom, rmsnorm.default_config(M, D), gamma)
+        dx = (torch.randn(M * D, device=dev) * 0.8).half()
+        dr = (torch.randn(M * D, device=dev) * 0.35).half()
+        ds, dn = torch.empty_like(dx), torch.empty_like(dx)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            for rep in range(args.repeat):
+                if rep == args.repeat - 1:
+                    e0.record(stream)
+                rc = plan.enqueue(M, False, dx.data_ptr(), dr.data_ptr(), ds.data_ptr(), dn.data_ptr(), stream.cuda_stream)
+                if rc:
+                    raise RuntimeError(f"rk_npu_b200_add_rmsnorm_f16_enqueue failed: {rc}")
+            e1.record(stream)
+        stream.synchronize()
+        print(f"rmsnorm: {M} x {D}, last launch {e0.elapsed_time(e1) * 1e3:.1f} us ({8 * M * D / 1e6:.0f} MB of tensors)")
         return
     if args.case in ("decode", "prefill", "mid"):
         M = args.case_tokens or {"decode": 8, "prefill": 2048, "mid": 128}[args.case]
@@ -1011,7 +1110,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--quick", action="store_true")
-    ap.add_argument("--case", choices=["decode", "prefill", "mid", "ffn", "moe"], help="run a small profiler workload instead of the benchmark")
+    ap.add_argument("--case", choices=["decode", "prefill", "mid", "ffn", "moe", "rmsnorm"], help="run a small profiler workload instead of the benchmark")
     ap.add_argument("--repeat", type=int, default=4, help="--case: launch sets")
     ap.add_argument("--case-tokens", type=int, default=0, help="--case: override the batch")
     ap.add_argument("--stamps", action="store_true", help="--case: print the kernels' phase stamps")

@@ -12,6 +12,7 @@
 #define RKNPU_B200_EXT_H
 
 #include "rknpu_b200_w4a8.h"
+#include "rknpu_b200_rmsnorm.h"
 
 #ifdef __cplusplus
 extern "C" {
@@ -203,6 +204,17 @@ int rk_npu_b200_w4a8_enqueue_f16_static(const rk_npu_w4a8_weights *weights, cons
  * (bad input) or RK_NPU_ERR_SUBMIT (device error or the copy failed).  No counterpart in the
  * original project. */
 int rk_npu_b200_w4a8_static_status(const rk_npu_w4a8_weights *weights, int *bad_input, int *device_error);
+
+/* ---- Residual add + RMSNorm on device tensors ------------------------------------------------------------
+ * The operator of rk_npu_add_rmsnorm_f16_run on the caller's own device tensors and stream: the kernel is queued,
+ * nothing is copied or waited for.  row_major = 0: the original's block-8 layout (D/8, M, 8); row_major = 1: plain
+ * [M, D] rows, the layout rk_npu_b200_w4a8_enqueue_f16 takes, so that the normalised rows feed the quantised FFN
+ * without a transpose.  rows: 1..plan M (a smaller batch than the plan was made for is allowed).  The tensors must
+ * be 16-byte aligned; an output must not overlap an input or the other output.  RK_NPU_ERR_PARAM / RK_NPU_ERR_SUBMIT
+ * as for the blocking call.  No counterpart in the original project. */
+int rk_npu_b200_add_rmsnorm_f16_enqueue(rk_npu_add_rmsnorm_f16_plan *plan, int rows, int row_major, const uint16_t *dX,
+                                        const uint16_t *dResidual, uint16_t *dResidualOut, uint16_t *dNormOut,
+                                        void *cuda_stream);
 
 /* ---- Test hooks: failures produced on the host, or by a wait that is allowed to run out ---------------
  * None of these faults, traps or hangs a GPU.

@@ -68,6 +68,56 @@ typedef struct {
 } rk_npu_domain_memory_stats;
 int rk_npu_iommu_domain_memory_stats(const rk_npu_iommu_domain *domain, rk_npu_domain_memory_stats *stats);
 
+/* ------------------------------------------------------------------ caller-owned device-visible buffers
+ * include/rk_npu_common.h:39-46,63-73,94-106,160-190.  Here a buffer is page-locked host memory mapped into the GPU's
+ * address space: vaddr is the host mapping, dma_addr (= obj_addr) the address kernels use; it is coherent once the call
+ * that used it has returned, so rk_npu_mem_sync validates its arguments and does nothing else.  The allocation flags are
+ * accepted and, except CACHEABLE (recorded in flags), without effect.  The dmabuf import and export are declined
+ * (RK_NPU_ERR_PARAM): there is no dmabuf on this platform. */
+#define RK_NPU_MEM_NON_CONTIGUOUS 0x1
+#define RK_NPU_MEM_NON_CACHEABLE 0x0
+#define RK_NPU_MEM_CACHEABLE 0x2
+#define RK_NPU_MEM_WRITE_COMBINE 0x4
+#define RK_NPU_MEM_KERNEL_MAPPING 0x8
+#define RK_NPU_MEM_IOMMU 0x10
+#define RK_NPU_MEM_IOMMU_LIMIT_IOVA_ALIGNMENT 0x400
+#define RK_NPU_MEM_DATA_DEFAULT (RK_NPU_MEM_NON_CONTIGUOUS | RK_NPU_MEM_CACHEABLE | RK_NPU_MEM_IOMMU)
+#define RK_NPU_MEM_DEFAULT RK_NPU_MEM_DATA_DEFAULT
+#define RK_NPU_MEM_F_OWN_RKNPU (1u << 0) /* owns its storage */
+#define RK_NPU_MEM_F_IMPORTED (1u << 1)
+#define RK_NPU_MEM_F_VIEW (1u << 2)      /* non-owning subrange */
+#define RK_NPU_MEM_F_MAPPED (1u << 3)    /* vaddr is valid */
+#define RK_NPU_MEM_F_CACHEABLE (1u << 4)
+
+typedef enum {
+    RK_NPU_SYNC_TO_DEVICE = 1u << 0,
+    RK_NPU_SYNC_FROM_DEVICE = 1u << 1,
+} rk_npu_sync_dir;
+
+typedef struct {
+    uint32_t handle;   /* nonzero for a live base allocation */
+    uint32_t flags;    /* RK_NPU_MEM_F_* */
+    uint64_t obj_addr;
+    uint64_t dma_addr; /* device address of this view */
+    void *vaddr;       /* host address of this view */
+    uint64_t size;     /* bytes of this view */
+    uint64_t offset;   /* from the base allocation */
+    uint64_t capacity; /* bytes of the base allocation */
+    uint64_t ctx_id;
+    uint32_t iommu_domain_id;
+    uint32_t reserved;
+} rk_npu_mem;
+
+/* RK_NPU_ERR_PARAM: NULL domain / out, size 0; RK_NPU_ERR_NOMEM: the allocation failed. */
+int rk_npu_mem_alloc(rk_npu_iommu_domain *domain, uint64_t size, uint32_t alloc_flags, rk_npu_mem *out);
+int rk_npu_mem_view(const rk_npu_mem *base, uint64_t offset, uint64_t size, rk_npu_mem *out_view);
+int rk_npu_mem_sync(rk_npu_ctx *ctx, const rk_npu_mem *mem, rk_npu_sync_dir dir);
+/* Releases a base allocation, or clears a view; the struct is zeroed. */
+int rk_npu_mem_free(rk_npu_ctx *ctx, rk_npu_mem *mem);
+int rk_npu_mem_import_dmabuf(rk_npu_iommu_domain *domain, int dmabuf_fd, void *cpu_addr, uint64_t size,
+                             uint32_t import_flags, rk_npu_mem *out);
+int rk_npu_mem_export_dmabuf(rk_npu_ctx *ctx, const rk_npu_mem *mem, int *out_fd);
+
 /* ------------------------------------------------------------------ int4 weight key
  * include/rk_npu_matmul_i4.h:22-25,38-46,58. */
 typedef struct rk_npu_i4_weight_config {

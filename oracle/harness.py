@@ -208,6 +208,14 @@ class Oracle:
                                   _ptr(out))
         return rc, out
 
+    def add_rmsnorm_f16(self, x, residual, gamma, eps: float = 1.0e-5):
+        """x, residual: [M, D] fp16 bit patterns (row-major); gamma: [D].  Returns (residual_out, norm_out) bit patterns."""
+        x, residual, gamma = _c(x, np.uint16), _c(residual, np.uint16), _c(gamma, np.uint16)
+        M, D = x.shape
+        sums, norm = np.zeros((M, D), np.uint16), np.zeros((M, D), np.uint16)
+        self.lib.orc_add_rmsnorm_f16(M, D, C.c_float(eps), _ptr(x), _ptr(residual), _ptr(gamma), _ptr(sums), _ptr(norm))
+        return sums, norm
+
     def ffn(self, A, B_gu, s_gu, B_dn, s_dn, mode: int = 1):
         """Returns dict(rc, middle, C, acc_gate_up, acc_down, scales_down_in)."""
         A = _c(A, np.float32)

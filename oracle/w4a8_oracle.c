@@ -616,3 +616,27 @@ int orc_moe_run(int rows, int H, int I, int routed, int shared, int top, const i
     free(acc); free(q); free(sum);
     return 0;
 }
+
+/* ---------------------------------------------------------------- residual add + RMSNorm (rk_npu_add_rmsnorm_f16.h)
+ * The original runs this on its NPU only; what its result must equal is stated by its board test
+ * (tests/test_add_rmsnorm_f16.cpp:96-113), restated here on row-major [M, D] fp16 bit patterns:
+ *   sum  = fp16(float(x) + float(residual))                       (must match bit for bit, :104,107-108)
+ *   inv  = 1 / sqrt(sum over d of double(sum)^2 / D + eps)        (:105-106,110; the squares are added in order of d)
+ *   norm = fp16(float(double(sum) * inv * double(gamma)))         (:112-113; the device is allowed 0.04 around it)
+ */
+void orc_add_rmsnorm_f16(int M, int D, float eps, const uint16_t *x, const uint16_t *residual, const uint16_t *gamma,
+                         uint16_t *residual_out, uint16_t *norm_out)
+{
+    for (int m = 0; m < M; ++m) {
+        const size_t row = (size_t)m * D;
+        double variance = 0.0;
+        for (int d = 0; d < D; ++d) {
+            residual_out[row + d] = orc_float_to_half(orc_half_to_float(x[row + d]) + orc_half_to_float(residual[row + d]));
+            const double v = orc_half_to_float(residual_out[row + d]);
+            variance += v * v;
+        }
+        const double inv = 1.0 / sqrt(variance / D + eps);
+        for (int d = 0; d < D; ++d)
+            norm_out[row + d] = orc_float_to_half((float)(orc_half_to_float(residual_out[row + d]) * inv * orc_half_to_float(gamma[d])));
+    }
+}

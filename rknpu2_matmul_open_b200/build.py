@@ -12,8 +12,8 @@ CSRC = HERE / "csrc"
 LIB_DIR = HERE / "lib"
 LIB = LIB_DIR / "librk_npu_matmul_b200.so"
 TOOLS = ["int8_peak.cu"]   # measures the dense int8 tensor peak; bench.py runs it for its roofline denominator
-SOURCES = ["w4a8_kernels.cu", "w4a8_fused.cu", "w4a8_decode.cu", "w4a8_stream.cu", "w4a8_shard.cu", "w4a8_gemm_tc.cu", "w4a8_gemm_tc_persist.cu", "w8a8_kernels.cu", "moe_kernels.cu", "w4a8_abi.cpp", "w8a8_abi.cpp", "i4_abi.cpp", "moe_abi.cpp", "w4a8_group.cpp", "w4a8_tune.cpp", "w4a8_autotune.cpp", "w4a8_unbuilt.cpp"]
-HEADERS = ["w4a8_device.h", "w4a8_host.h", "w4a8_tune.h", "w4a8_ptx.cuh", "w4a8_math.cuh", "w4a8_tc.cuh", "moe_device.h", "../../include/rknpu_b200_moe.h", "../../include/rknpu_b200_w4a8.h", "../../include/rknpu_b200_ext.h", "../../include/rknpu_b200_quant.h"]
+SOURCES = ["w4a8_kernels.cu", "w4a8_fused.cu", "w4a8_decode.cu", "w4a8_stream.cu", "w4a8_shard.cu", "w4a8_gemm_tc.cu", "w4a8_gemm_tc_persist.cu", "w8a8_kernels.cu", "moe_kernels.cu", "rmsnorm_kernels.cu", "w4a8_abi.cpp", "w8a8_abi.cpp", "i4_abi.cpp", "moe_abi.cpp", "rmsnorm_abi.cpp", "w4a8_group.cpp", "w4a8_tune.cpp", "w4a8_autotune.cpp", "w4a8_unbuilt.cpp"]
+HEADERS = ["w4a8_device.h", "w4a8_host.h", "w4a8_tune.h", "w4a8_ptx.cuh", "w4a8_math.cuh", "w4a8_tc.cuh", "moe_device.h", "rmsnorm_device.h", "../../include/rknpu_b200_moe.h", "../../include/rknpu_b200_rmsnorm.h", "../../include/rknpu_b200_w4a8.h", "../../include/rknpu_b200_ext.h", "../../include/rknpu_b200_quant.h"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-Wall", "-Xptxas", "-v",

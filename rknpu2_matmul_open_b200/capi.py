@@ -143,6 +143,24 @@ class MoeTimings(C.Structure):
                [(n, C.c_uint32) for n in ("gather_tasks", "middle_tasks", "gemm_tasks")]
 
 
+class Mem(C.Structure):
+    """rk_npu_mem"""
+    _fields_ = [("handle", C.c_uint32), ("flags", C.c_uint32), ("obj_addr", C.c_uint64), ("dma_addr", C.c_uint64),
+                ("vaddr", C.c_void_p), ("size", C.c_uint64), ("offset", C.c_uint64), ("capacity", C.c_uint64),
+                ("ctx_id", C.c_uint64), ("iommu_domain_id", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class AddRmsNormConfig(C.Structure):
+    """rk_npu_add_rmsnorm_f16_config"""
+    _fields_ = [("M", C.c_int), ("D", C.c_int), ("eps", C.c_float), ("timeout_ms", C.c_uint32)]
+
+
+class AddRmsNormSizes(C.Structure):
+    """rk_npu_add_rmsnorm_f16_sizes"""
+    _fields_ = [("tensor_bytes", C.c_uint64), ("internal_bytes", C.c_uint64), ("weight_bytes", C.c_uint64),
+                ("regcmd_bytes", C.c_uint64), ("task_bytes", C.c_uint64), ("num_tasks", C.c_int)]
+
+
 class MatmulWorkspaceRequirements(C.Structure):
     _fields_ = [("bytes", C.c_uint64), ("input_bytes", C.c_uint64), ("output_bytes", C.c_uint64), ("control_bytes", C.c_uint64),
                 ("wave_count", C.c_uint32), ("buffer_count", C.c_uint32)]
@@ -341,6 +359,18 @@ _SIGNATURES = {
     "rk_npu_b200_w4a8_schedule": (C.c_int, [_P, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "rk_npu_b200_w4a8_enqueue_f16_static": (C.c_int, [_P, _P, _P, C.c_int, _P]),
     "rk_npu_b200_w4a8_static_status": (C.c_int, [_P, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "rk_npu_mem_alloc": (C.c_int, [_P, C.c_uint64, C.c_uint32, C.POINTER(Mem)]),
+    "rk_npu_mem_view": (C.c_int, [C.POINTER(Mem), C.c_uint64, C.c_uint64, C.POINTER(Mem)]),
+    "rk_npu_mem_sync": (C.c_int, [_P, C.POINTER(Mem), C.c_int]),
+    "rk_npu_mem_free": (C.c_int, [_P, C.POINTER(Mem)]),
+    "rk_npu_mem_import_dmabuf": (C.c_int, [_P, C.c_int, _P, C.c_uint64, C.c_uint32, C.POINTER(Mem)]),
+    "rk_npu_mem_export_dmabuf": (C.c_int, [_P, C.POINTER(Mem), C.POINTER(C.c_int)]),
+    "rk_npu_add_rmsnorm_f16_config_init": (None, [C.POINTER(AddRmsNormConfig), C.c_int, C.c_int]),
+    "rk_npu_add_rmsnorm_f16_query": (C.c_int, [C.POINTER(AddRmsNormConfig), C.POINTER(AddRmsNormSizes)]),
+    "rk_npu_add_rmsnorm_f16_plan_create": (_P, [_P, C.POINTER(AddRmsNormConfig), _P]),
+    "rk_npu_add_rmsnorm_f16_run": (C.c_int, [_P, _P, C.POINTER(Mem), C.POINTER(Mem), C.POINTER(Mem), C.POINTER(Mem)]),
+    "rk_npu_add_rmsnorm_f16_plan_free": (None, [_P]),
+    "rk_npu_b200_add_rmsnorm_f16_enqueue": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, _P, _P]),
     "rk_npu_b200_test_fail_allocation": (None, [C.c_longlong]),
     "rk_npu_b200_w4a8_test_starve": (C.c_int, [_P, C.c_int]),
     "rk_npu_b200_w4a8_test_device_error": (C.c_int, [_P]),

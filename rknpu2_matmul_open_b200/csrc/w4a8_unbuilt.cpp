@@ -1,6 +1,6 @@
 // w4a8_unbuilt.cpp -- entry points of the original project's public headers that this library
 // does not implement: the W8 search tuners, their family forms and cache saving, and compressed (DCOMP)
-// weight storage (include/rk_npu_quant_matmul.h), and the DMA-buffer helpers of include/rk_npu_common.h.  They are
+// weight storage (include/rk_npu_quant_matmul.h).  They are
 // exported so that programs written against those headers link and start; each one declines: RK_NPU_ERR_PARAM, NULL, or 0, and does nothing else.
 // C linkage carries no parameter types, so the definitions take none; the callers' arguments
 // are ignored.
@@ -25,12 +25,6 @@ RKB200_DECLINE_INT(rk_npu_i8i8i32_autotune_family)
 RKB200_DECLINE_INT(rk_npu_matmul_autotune_cache_save)
 RKB200_DECLINE_INT(rk_npu_matmul_autotune_cached)
 RKB200_DECLINE_INT(rk_npu_matmul_autotune_family_cached)
-RKB200_DECLINE_INT(rk_npu_mem_alloc)
-RKB200_DECLINE_INT(rk_npu_mem_export_dmabuf)
-RKB200_DECLINE_INT(rk_npu_mem_free)
-RKB200_DECLINE_INT(rk_npu_mem_import_dmabuf)
-RKB200_DECLINE_INT(rk_npu_mem_sync)
-RKB200_DECLINE_INT(rk_npu_mem_view)
 
 // constructors: no object
 RKB200_DECLINE_PTR(rk_npu_f16i8f16_weights_create_compress)

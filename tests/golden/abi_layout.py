@@ -21,10 +21,10 @@ import tempfile
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parents[2]
-OURS = ("rknpu_b200_w4a8.h", "rknpu_b200_quant.h", "rknpu_b200_moe.h")
+OURS = ("rknpu_b200_w4a8.h", "rknpu_b200_quant.h", "rknpu_b200_moe.h", "rknpu_b200_rmsnorm.h")
 # the original's headers that declare the same types (include/ of the original project)
 THEIRS = ("rk_npu_common.h", "rk_npu_w4a8.h", "rk_npu_w4a8_tune.h", "rk_npu_matmul_i4.h", "rk_npu_quant_matmul.h",
-          "rk_npu_moe_w8.h")
+          "rk_npu_moe_w8.h", "rk_npu_add_rmsnorm_f16.h")
 
 
 def _strip_comments(text: str) -> str:
@@ -39,7 +39,7 @@ def declared_names(headers=OURS):
     for header in headers:
         text = _strip_comments((ROOT / "include" / header).read_text())
         enumerators += re.findall(r"^#define[ \t]+(RK_NPU_\w+)[ \t]+\S", text, flags=re.M)
-        for body, name in re.findall(r"typedef\s+struct\s+\w+\s*\{(.*?)\}\s*(\w+)\s*;", text, flags=re.S):
+        for body, name in re.findall(r"typedef\s+struct(?:\s+\w+)?\s*\{(.*?)\}\s*(\w+)\s*;", text, flags=re.S):
             members = []
             for statement in body.split(";"):
                 statement = statement.strip()
@@ -53,7 +53,7 @@ def declared_names(headers=OURS):
                     part = re.sub(r"\[[^\]]*\]", "", part).strip()
                     members.append(re.findall(r"\w+", part)[-1])
             structs[name] = members
-        for body, _ in re.findall(r"typedef\s+enum\s+\w+\s*\{(.*?)\}\s*(\w+)\s*;", text, flags=re.S):
+        for body, _ in re.findall(r"typedef\s+enum(?:\s+\w+)?\s*\{(.*?)\}\s*(\w+)\s*;", text, flags=re.S):
             for part in body.split(","):
                 part = part.strip()
                 if part:

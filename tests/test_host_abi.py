@@ -26,7 +26,7 @@ def cfg_of(lib, m, n, k, **kw):
 
 def test_library_exports_every_declared_symbol(lib):
     declared = set()
-    for header in ("rknpu_b200_w4a8.h", "rknpu_b200_quant.h", "rknpu_b200_moe.h", "rknpu_b200_ext.h"):
+    for header in ("rknpu_b200_w4a8.h", "rknpu_b200_quant.h", "rknpu_b200_moe.h", "rknpu_b200_rmsnorm.h", "rknpu_b200_ext.h"):
         text = (ROOT / "include" / header).read_text()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
         declared |= set(re.findall(r"\b(rk_npu_\w+)\s*\(", text))
@@ -50,7 +50,7 @@ def test_struct_layouts_and_constants_equal_the_original_headers():
     # passes structs this library reads correctly.
     abi = _abi_layout()
     structs, constants = abi.declared_names()
-    assert len(structs) == 28 and "rk_npu_moe_w8_timings" in structs and "RK_NPU_ERR_BUSY" in constants
+    assert len(structs) == 32 and "rk_npu_moe_w8_timings" in structs and "RK_NPU_ERR_BUSY" in constants
     assert structs["rk_npu_moe_w8_timings"][:3] == ["input_us", "schedule_us", "build_us"]      # "double a, b, c;"
     ours = abi.layout(ROOT / "include", abi.OURS)
     golden = (ROOT / "tests" / "golden" / "reference_abi_layout.txt").read_text()
@@ -72,7 +72,9 @@ def test_ctypes_mirrors_have_the_c_sizes():
                "rk_npu_w4a8_strategy": capi.W4A8Strategy, "rk_npu_w4a8_strategy_ex": capi.W4A8StrategyEx,
                "rk_npu_w4a8_autotune_config": capi.W4A8AutotuneConfig, "rk_npu_i4_weight_config": capi.I4WeightConfig,
                "rk_npu_moe_w8_weight_config": capi.MoeWeightConfig, "rk_npu_moe_w8_config": capi.MoeConfig,
-               "rk_npu_moe_w8_expert": capi.MoeExpert, "rk_npu_moe_w8_timings": capi.MoeTimings}
+               "rk_npu_moe_w8_expert": capi.MoeExpert, "rk_npu_moe_w8_timings": capi.MoeTimings, "rk_npu_mem": capi.Mem,
+               "rk_npu_add_rmsnorm_f16_config": capi.AddRmsNormConfig, "rk_npu_add_rmsnorm_f16_sizes": capi.AddRmsNormSizes,
+               "rk_npu_domain_memory_stats": capi.DomainMemoryStats}
     for name, mirror in mirrors.items():
         assert C.sizeof(mirror) == int(sizes[name]), name
         for field, _ in mirror._fields_:
@@ -325,15 +327,15 @@ def test_cache_files_interoperate_with_reference_build(cache_case, reference, tm
 # ---------------------------------------------------------------- the rest of the original headers
 def test_every_entry_point_of_the_original_headers_links(lib):
     # tests/golden/reference_header_symbols.txt (written by tests/golden/abi_layout.py --symbols): every function the
-    # six public headers of the path declare (rk_npu_common.h, rk_npu_matmul_i4.h, rk_npu_w4a8.h, rk_npu_w4a8_tune.h,
-    # rk_npu_quant_matmul.h, rk_npu_moe_w8.h)
+    # seven public headers of the path declare (rk_npu_common.h, rk_npu_matmul_i4.h, rk_npu_w4a8.h, rk_npu_w4a8_tune.h,
+    # rk_npu_quant_matmul.h, rk_npu_moe_w8.h, rk_npu_add_rmsnorm_f16.h)
     names = (ROOT / "tests" / "golden" / "reference_header_symbols.txt").read_text().split()
-    assert len(names) == 120
+    assert len(names) == 125
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, missing
     # operators that are not built decline instead of pretending
     for name in ("rk_npu_i8i8i32_autotune", "rk_npu_f16i8f16_dynamic_autotune_family",
-                 "rk_npu_matmul_autotune_cache_save", "rk_npu_mem_alloc"):
+                 "rk_npu_matmul_autotune_cache_save", "rk_npu_matmul_autotune_cached"):
         fn = C.CDLL(str(capi.LIB_PATH))[name]
         fn.restype, fn.argtypes = C.c_int, []
         assert fn() == capi.RK_NPU_ERR_PARAM, name
@@ -499,7 +501,7 @@ def test_public_headers_are_valid_c(tmp_path):
     if not gcc:
         pytest.skip("no C compiler")
     src = tmp_path / "headers.c"
-    src.write_text('#include "rknpu_b200_w4a8.h"\n#include "rknpu_b200_quant.h"\n#include "rknpu_b200_moe.h"\n#include "rknpu_b200_ext.h"\n'
+    src.write_text('#include "rknpu_b200_w4a8.h"\n#include "rknpu_b200_quant.h"\n#include "rknpu_b200_moe.h"\n#include "rknpu_b200_rmsnorm.h"\n#include "rknpu_b200_ext.h"\n'
                    "int main(void) { rk_npu_w4a8_config c; rk_npu_matmul_strategy s; rk_npu_moe_w8_config m; (void)c; (void)s; (void)m; return 0; }\n")
     out = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", f"-I{ROOT / 'include'}",
                           str(src)], capture_output=True, text=True)
