@@ -10,7 +10,7 @@
  * + eps), fp16(float(double(v) * inv * double(gamma)))".  This library evaluates that double-precision expression;
  * the squares are added in a fixed tree order instead of one after the other, so the sum can differ from the
  * sequential one in its last bits (about 1e-16 relative), which moves an fp16 output only if a product lies that close
- * to a rounding boundary.  Results do not depend on the launch geometry or the schedule: the same inputs give the same
+ * to a rounding boundary.  The order is fixed by the shape (rows, D), not by the schedule: the same call gives the same
  * bits every time.
  * The original accepts M = 1 or 128, D = 4096, eps = 1e-5 only (its validated programs); this library accepts those and
  * every 1 <= M <= 65536, D a multiple of 8 in 8..32768, eps finite and >= 0.

@@ -4,11 +4,13 @@
 //   norm = fp16(float(double(sum) * inv * double(gamma))),  inv = 1 / sqrt(sum of double(sum)^2 / D + eps)   -> norm_out
 //
 // the double-precision statement of the original's board test (tests/test_add_rmsnorm_f16.cpp:96-113), which is what
-// the original device's result is checked against.
+// the original device's result is checked against.  Double-precision conversions run at a quarter of the fp32 rate and
+// would be the busiest pipe of this kernel, so the second pass proves per value that single precision
+// gives the same fp16 bits and falls back to the defining expression where it cannot (scale_one).
 //
 // HBM-bound: 4 tensors of 2 M D bytes cross DRAM once each.  A tile of TM tokens is shared by a CLUSTER of CS CTAs,
-// each taking a slice of D: the sums stay in that CTA's shared memory between the two passes (no second read of
-// residual_out), the per-token sums of squares are exchanged through distributed shared memory and added in rank
+// each taking a slice of D: the sums stay in that CTA's shared memory between the two passes (both outputs are stored
+// in the second one, so that no global store is in flight at the cluster barrier), the per-token sums of squares are exchanged through distributed shared memory and added in rank
 // order by every CTA, so that the result does not depend on the schedule.  Both tensor layouts move 16-byte chunks
 // (8 elements): in the block-8 layout (D/8, M, 8) consecutive TOKENS of one chunk column are contiguous, in row-major
 // [M, D] consecutive CHUNKS of one token are; the thread index is split accordingly so that a warp touches 512
@@ -16,6 +18,7 @@
 #include "rmsnorm_device.h"
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
+#include <atomic>
 
 namespace cg = cooperative_groups;
 
@@ -24,6 +27,7 @@ namespace {
 
 constexpr int RN_THREADS = 512;
 constexpr int RN_BATCH = 4;
+constexpr int RN_MAX_DEVICES = 64;
 constexpr int RN_SMEM_SUMS = 64 * 1024;   // bytes of sums one CTA keeps: TM * ceil(D/8/CS) * 16
 
 __device__ __forceinline__ uint4 ld_stream(const uint4* p)
@@ -37,25 +41,41 @@ __device__ __forceinline__ void st_stream(uint4* p, const uint4& v)
     asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// fp16(float(a) + float(b)) for two packed pairs; the squares of the two sums are added to acc in element order
+// fp16(float(a) + float(b)) for a packed pair.  With 24 >= 2 * 11 + 2 mantissa bits the float sum rounded to fp16 equals
+// the correctly rounded fp16 sum (double rounding is innocuous), which is what the packed fp16 add returns.  The squares
+// of the two sums are added to acc in element order.
 __device__ __forceinline__ uint32_t add_pair(uint32_t a, uint32_t b, double& acc)
 {
-    const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&a));
-    const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&b));
-    const __half2 s = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
+    const __half2 s = __hadd2_rn(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
     const float2 fs = __half22float2(s);
     const double lo = double(fs.x), hi = double(fs.y);
     acc += lo * lo;       // a product of two fp16 values is exact in double
     acc += hi * hi;
     return *reinterpret_cast<const uint32_t*>(&s);
 }
-__device__ __forceinline__ uint32_t scale_pair(uint32_t v, uint32_t g, double inv)
+// One output: fp16(float(double(v) * inv * double(g))), the defining expression, evaluated in double only when needed.
+// y = fl32(fl32(v * inv_f) * g) with inv_f = fl32(inv) differs from the exact product x by at most 3 * 2^-24 |x|, and
+// the float the defining expression rounds to fp16 by at most (2^-24 + 2^-52) |x|: the two are less than 4.000001
+// float ulps apart.  fp16 rounding of a float in the normal fp16 range is decided by its low 13 mantissa bits L
+// against the midpoint 0x1000; when |L - 0x1000| >= 8 no midpoint lies between the two floats (or on one of them), so
+// fp16(y) IS the defined result.  About 0.2 % of the values, everything outside the normal fp16 range, and rows whose
+// inv is not a normal float take the double path.
+// A real call, so that the rare double-precision path is branched around instead of being evaluated for every value.
+__device__ __noinline__ float scale_defined(float v, float g, double inv) { return __double2float_rn(double(v) * inv * double(g)); }
+__device__ __forceinline__ float scale_one(float v, float g, double inv, float inv_f, bool fast)
+{
+    float y = __fmul_rn(__fmul_rn(v, inv_f), g);
+    const uint32_t u = __float_as_uint(y);
+    const bool in_range = (u & 0x7f800000u) - (113u << 23) <= (29u << 23);        // exponent field 113..142: 2^-14 <= |y| < 2^16
+    const bool clear = (u & 0x1fffu) - (0x1000u - 7u) > 14u;                       // |L - 0x1000| >= 8
+    if (!(fast && in_range && clear)) y = scale_defined(v, g, inv);
+    return y;
+}
+__device__ __forceinline__ uint32_t scale_pair(uint32_t v, uint32_t g, double inv, float inv_f, bool fast)
 {
     const float2 fv = __half22float2(*reinterpret_cast<const __half2*>(&v));
     const float2 fg = __half22float2(*reinterpret_cast<const __half2*>(&g));
-    const float lo = __double2float_rn(double(fv.x) * inv * double(fg.x));
-    const float hi = __double2float_rn(double(fv.y) * inv * double(fg.y));
-    const __half2 o = __floats2half2_rn(lo, hi);
+    const __half2 o = __floats2half2_rn(scale_one(fv.x, fg.x, inv, inv_f, fast), scale_one(fv.y, fg.y, inv, inv_f, fast));
     return *reinterpret_cast<const uint32_t*>(&o);
 }
 
@@ -100,55 +120,82 @@ __global__ void __launch_bounds__(RN_THREADS) add_rmsnorm_kernel(AddRmsNormParam
                     s.y = add_pair(a[u].y, b[u].y, acc);
                     s.z = add_pair(a[u].z, b[u].z, acc);
                     s.w = add_pair(a[u].w, b[u].w, acc);
-                    st_stream(p.residual_out + global_at(j + u * JL), s);
                     s_sum[shared_at(j + u * JL)] = s;
                 }
         }
     }
     s_part[tid] = acc;
     __syncthreads();
-    for (int step = JL / 2; step > 0; step >>= 1) {           // fixed tree over the chunk lanes of each token
-        if (jl < step) s_part[tid] += s_part[lane_of(dm, jl + step)];
-        __syncthreads();
+    if (JL <= 16) {                                            // few lanes per token: one thread adds them in lane order
+        if (jl == 0) {
+            double sum = acc;
+            for (int lane = 1; lane < JL; ++lane) sum += s_part[lane_of(dm, lane)];
+            s_token[dm] = sum;
+        }
+    } else {
+        for (int step = JL / 2; step > 0; step >>= 1) {        // fixed tree over the chunk lanes of each token
+            if (jl < step) s_part[tid] += s_part[lane_of(dm, jl + step)];
+            __syncthreads();
+        }
+        if (jl == 0) s_token[dm] = s_part[tid];
     }
-    if (jl == 0) s_token[dm] = s_part[tid];
     if (CS > 1) cluster.sync(); else __syncthreads();
     double total = 0.0;
     for (int r = 0; r < CS; ++r) total += CS > 1 ? cluster.map_shared_rank(s_token, r)[dm] : s_token[dm];
     const double inv = 1.0 / sqrt(total / double(p.D) + double(p.eps));
+    const float inv_f = __double2float_rn(inv);
+    const bool fast = inv_f >= 1.17549435e-38f && inv_f <= 3.402823466e38f;       // a normal float (false for NaN)
 
     if (live) {
 #pragma unroll 4
         for (int j = j0 + jl; j < j1; j += JL) {
             const uint4 s = s_sum[shared_at(j)];
             const uint4 g = __ldg(p.gamma + j);
+            st_stream(p.residual_out + global_at(j), s);
             uint4 o;
-            o.x = scale_pair(s.x, g.x, inv);
-            o.y = scale_pair(s.y, g.y, inv);
-            o.z = scale_pair(s.z, g.z, inv);
-            o.w = scale_pair(s.w, g.w, inv);
+            o.x = scale_pair(s.x, g.x, inv, inv_f, fast);
+            o.y = scale_pair(s.y, g.y, inv, inv_f, fast);
+            o.z = scale_pair(s.z, g.z, inv, inv_f, fast);
+            o.w = scale_pair(s.w, g.w, inv, inv_f, fast);
             st_stream(p.norm_out + global_at(j), o);
         }
     }
-    if (CS > 1) cluster.sync();       // a CTA's s_token stays readable until every peer has read it
+    // A CTA's s_token must stay readable until every peer has read it.  Nothing this CTA wrote has to become visible
+    // for that, so the arrival is relaxed: a releasing one would wait for the output stores still in flight.
+    if (CS > 1) {
+        asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+    }
 }
 
 } // namespace
 
-// Tile and cluster: as many tokens per tile as the batch has, up to 32 (a warp's worth of contiguous 16-byte chunks
-// in the block-8 layout); the smallest cluster whose per-CTA slice of the sums fits RN_SMEM_SUMS, else fewer tokens.
+// Tile and cluster.  Candidates: tokens per tile a power of two up to 32 (a warp's worth of contiguous 16-byte
+// chunks in the block-8 layout) and up to the batch, clusters of 1, 2, 4 or 8 CTAs; a candidate must keep its slice
+// of the sums within RN_SMEM_SUMS and give every thread at least one chunk (or be the single-CTA form).  Taken: the
+// one with the most CTAs up to 128 (enough to occupy the GPU), then the most tokens per tile, then the smallest
+// cluster -- large batches get 32-token tiles, small ones are spread over more SMs.
 void add_rmsnorm_geometry(int M, int D, int& tile_tokens, int& cluster)
 {
-    int tm = 1;
-    while (tm < 32 && tm < M) tm <<= 1;
+    int top = 1;
+    while (top < 32 && top < M) top <<= 1;
     const int chunks = D / 8;
-    for (;; tm >>= 1) {
-        for (int cs = 1; cs <= 8; cs <<= 1)
-            if (size_t(tm) * ((chunks + cs - 1) / cs) * 16 <= size_t(RN_SMEM_SUMS)) { tile_tokens = tm; cluster = cs; return; }
-        if (tm == 1) break;
-    }
+    int best_score = -1;
     tile_tokens = 1;
-    cluster = 8;      // D <= 32768: 4096 chunks / 8 * 16 B = 8 KB
+    cluster = 8;
+    for (int tm = top; tm >= 1; tm >>= 1)
+        for (int cs = 1; cs <= 8; cs <<= 1) {
+            const int per = (chunks + cs - 1) / cs;
+            if (size_t(tm) * per * 16 > size_t(RN_SMEM_SUMS)) continue;
+            if (cs > 1 && tm * per < RN_THREADS) continue;
+            const int ctas = (M + tm - 1) / tm * cs;
+            const int score = ctas < 128 ? ctas : 128;
+            if (score > best_score) {
+                best_score = score;
+                tile_tokens = tm;
+                cluster = cs;
+            }
+        }
 }
 
 cudaError_t launch_add_rmsnorm(const AddRmsNormParams& q, cudaStream_t stream)
@@ -159,8 +206,19 @@ cudaError_t launch_add_rmsnorm(const AddRmsNormParams& q, cudaStream_t stream)
     const int per = (p.D / 8 + cs - 1) / cs;
     const size_t shared = size_t(p.tile_tokens) * per * 16 + size_t(RN_THREADS + p.tile_tokens) * sizeof(double);
     auto kernel = p.row_major ? add_rmsnorm_kernel<true> : add_rmsnorm_kernel<false>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared));
+    // function attributes are per device: remember what this device's copy of the kernel already allows
+    static std::atomic<int> allowed[2][RN_MAX_DEVICES];
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
     if (err != cudaSuccess) return err;
+    std::atomic<int>* known = device >= 0 && device < RN_MAX_DEVICES ? &allowed[p.row_major ? 1 : 0][device] : nullptr;
+    if (!known || known->load(std::memory_order_relaxed) < int(shared)) {
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(RN_SMEM_SUMS + (RN_THREADS + 32) * sizeof(double)));
+        if (err != cudaSuccess) return err;
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, int(cudaSharedmemCarveoutMaxShared));
+        if (err != cudaSuccess) return err;
+        if (known) known->store(int(RN_SMEM_SUMS + (RN_THREADS + 32) * sizeof(double)), std::memory_order_relaxed);
+    }
     cudaLaunchConfig_t cfg{};
     const int tiles = (p.M + p.tile_tokens - 1) / p.tile_tokens;
     cfg.gridDim = dim3(unsigned(tiles) * unsigned(cs));

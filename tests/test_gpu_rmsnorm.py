@@ -76,6 +76,34 @@ def test_enqueue_on_device_tensors_equals_the_oracle(gpu, oracle, M, D, rows, ro
     plan.free()
 
 
+def test_outputs_outside_the_normal_fp16_range(gpu, oracle):
+    # gamma of 60000 overflows the normalised value to infinity, gamma near 2^-14 and below makes it subnormal or zero:
+    # the kernel's single-precision shortcut must hand all of these to the defining double-precision expression
+    import torch
+    ctx, d0, _ = gpu
+    M, D = 6, 512
+    rng = np.random.default_rng(77)
+    x = rng.normal(0, 1, (M, D)) * np.array([1, 1e-3, 2000, 1, 30, 1e-2])[:, None]
+    r = rng.normal(0, 0.3, (M, D)) * np.array([1, 1e-3, 100, 0, 1, 1e-4])[:, None]
+    g = np.tile(np.array([60000, 6.1e-5, 1, 3e-6, 0.5, 6e-8, -2, 0], np.float64), D // 8)
+    x, r, g = (a.astype(np.float16).view(np.uint16) for a in (x, r, g))
+    want_sums, want_norm = oracle.add_rmsnorm_f16(x, r, g)
+    out = want_norm.view(np.float16)
+    assert np.isinf(out).any() and ((out != 0) & (np.abs(out) < 6.1e-5)).any() and (out == 0).any() and not np.isnan(out).any()
+    plan = rmsnorm.AddRmsNormPlan(d0, rmsnorm.default_config(M, D), g)
+    for row_major in (False, True):
+        lay = (lambda a: a) if row_major else rmsnorm.to_block8
+        dx, dr = (torch.from_numpy(lay(a).astype(np.int16)).cuda() for a in (x, r))
+        ds, dn = torch.zeros_like(dx), torch.zeros_like(dx)
+        assert plan.enqueue(M, row_major, dx.data_ptr(), dr.data_ptr(), ds.data_ptr(), dn.data_ptr(), 0) == capi.RK_NPU_OK
+        torch.cuda.synchronize()
+        got_s, got_n = ds.cpu().numpy().view(np.uint16), dn.cpu().numpy().view(np.uint16)
+        if not row_major:
+            got_s, got_n = rmsnorm.from_block8(got_s, M, D), rmsnorm.from_block8(got_n, M, D)
+        assert np.array_equal(got_s.reshape(M, D), want_sums) and np.array_equal(got_n.reshape(M, D), want_norm)
+    plan.free()
+
+
 def test_rejections_follow_the_original_order(gpu, lib):
     ctx, d0, d1 = gpu
     M, D = 4, 64
