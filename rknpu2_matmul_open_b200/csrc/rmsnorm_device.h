@@ -18,7 +18,7 @@ struct AddRmsNormParams {
 };
 
 // Tokens per tile (a power of two up to 32) and CTAs per cluster (1, 2, 4 or 8) the launcher uses for a shape.
-void add_rmsnorm_geometry(int M, int D, int& tile_tokens, int& cluster);
+void add_rmsnorm_geometry(int M, int D, int row_major, int& tile_tokens, int& cluster);
 cudaError_t launch_add_rmsnorm(const AddRmsNormParams& p, cudaStream_t stream);
 
 } // namespace rkb200

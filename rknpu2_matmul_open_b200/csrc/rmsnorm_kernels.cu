@@ -19,6 +19,8 @@
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <atomic>
+#include <cstdio>
+#include <cstdlib>
 
 namespace cg = cooperative_groups;
 
@@ -26,9 +28,10 @@ namespace rkb200 {
 namespace {
 
 constexpr int RN_THREADS = 512;
-constexpr int RN_BATCH = 4;
+constexpr int RN_BATCH = 4;     // chunks of each input a thread requests before it uses the first
+constexpr int RN_CTAS = 2;      // CTAs per SM the register budget is set for
 constexpr int RN_MAX_DEVICES = 64;
-constexpr int RN_SMEM_SUMS = 64 * 1024;   // bytes of sums one CTA keeps: TM * ceil(D/8/CS) * 16
+constexpr int RN_SMEM_SUMS = 64 * 1024;   // most bytes of sums one CTA keeps: TM * ceil(D/8/CS) * 16
 
 __device__ __forceinline__ uint4 ld_stream(const uint4* p)
 {
@@ -59,29 +62,44 @@ __device__ __forceinline__ uint32_t add_pair(uint32_t a, uint32_t b, double& acc
 // float ulps apart.  fp16 rounding of a float in the normal fp16 range is decided by its low 13 mantissa bits L
 // against the midpoint 0x1000; when |L - 0x1000| >= 8 no midpoint lies between the two floats (or on one of them), so
 // fp16(y) IS the defined result.  About 0.2 % of the values, everything outside the normal fp16 range, and rows whose
-// inv is not a normal float take the double path.
-// A real call, so that the rare double-precision path is branched around instead of being evaluated for every value.
-__device__ __noinline__ float scale_defined(float v, float g, double inv) { return __double2float_rn(double(v) * inv * double(g)); }
-__device__ __forceinline__ float scale_one(float v, float g, double inv, float inv_f, bool fast)
-{
-    float y = __fmul_rn(__fmul_rn(v, inv_f), g);
-    const uint32_t u = __float_as_uint(y);
-    const bool in_range = (u & 0x7f800000u) - (113u << 23) <= (29u << 23);        // exponent field 113..142: 2^-14 <= |y| < 2^16
-    const bool clear = (u & 0x1fffu) - (0x1000u - 7u) > 14u;                       // |L - 0x1000| >= 8
-    if (!(fast && in_range && clear)) y = scale_defined(v, g, inv);
-    return y;
-}
-__device__ __forceinline__ uint32_t scale_pair(uint32_t v, uint32_t g, double inv, float inv_f, bool fast)
+// inv is not a normal float are not proven; a chunk of eight with such a value is evaluated in double.
+
+// The defining expression for one chunk.  A real call, so that this rare path is branched around instead of being
+// evaluated for every value.
+__device__ __forceinline__ uint32_t scale_pair_defined(uint32_t v, uint32_t g, double inv)
 {
     const float2 fv = __half22float2(*reinterpret_cast<const __half2*>(&v));
     const float2 fg = __half22float2(*reinterpret_cast<const __half2*>(&g));
-    const __half2 o = __floats2half2_rn(scale_one(fv.x, fg.x, inv, inv_f, fast), scale_one(fv.y, fg.y, inv, inv_f, fast));
+    const __half2 o = __floats2half2_rn(__double2float_rn(double(fv.x) * inv * double(fg.x)),
+                                        __double2float_rn(double(fv.y) * inv * double(fg.y)));
+    return *reinterpret_cast<const uint32_t*>(&o);
+}
+__device__ __noinline__ uint4 scale_chunk_defined(uint4 v, uint4 g, double inv)
+{
+    return make_uint4(scale_pair_defined(v.x, g.x, inv), scale_pair_defined(v.y, g.y, inv), scale_pair_defined(v.z, g.z, inv),
+                      scale_pair_defined(v.w, g.w, inv));
+}
+// The single-precision value of one output and whether it is proven (see above); `proven` only ever goes false.
+__device__ __forceinline__ float scale_one(float v, float g, float inv_f, bool& proven)
+{
+    const float y = __fmul_rn(__fmul_rn(v, inv_f), g);
+    const uint32_t u = __float_as_uint(y);
+    proven = proven && fabsf(y) >= 6.103515625e-05f && fabsf(y) < 65536.f      // 2^-14 <= |y| < 2^16 (false for NaN)
+             && ((u - (0x1000u - 7u)) & 0x1fffu) > 14u;                        // |L - 0x1000| >= 8
+    return y;
+}
+__device__ __forceinline__ uint32_t scale_pair(uint32_t v, uint32_t g, float inv_f, bool& proven)
+{
+    const float2 fv = __half22float2(*reinterpret_cast<const __half2*>(&v));
+    const float2 fg = __half22float2(*reinterpret_cast<const __half2*>(&g));
+    const float lo = scale_one(fv.x, fg.x, inv_f, proven), hi = scale_one(fv.y, fg.y, inv_f, proven);
+    const __half2 o = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&o);
 }
 
 // ROWS: row-major [M, D]; else block-8 (D/8, M, 8).  grid = tiles * CS CTAs in clusters of CS.
 template <bool ROWS>
-__global__ void __launch_bounds__(RN_THREADS) add_rmsnorm_kernel(AddRmsNormParams p)
+__global__ void __launch_bounds__(RN_THREADS, RN_CTAS) add_rmsnorm_kernel(AddRmsNormParams p)
 {
     extern __shared__ __align__(16) uint8_t smem[];
     cg::cluster_group cluster = cg::this_cluster();
@@ -152,11 +170,13 @@ __global__ void __launch_bounds__(RN_THREADS) add_rmsnorm_kernel(AddRmsNormParam
             const uint4 s = s_sum[shared_at(j)];
             const uint4 g = __ldg(p.gamma + j);
             st_stream(p.residual_out + global_at(j), s);
+            bool proven = fast;
             uint4 o;
-            o.x = scale_pair(s.x, g.x, inv, inv_f, fast);
-            o.y = scale_pair(s.y, g.y, inv, inv_f, fast);
-            o.z = scale_pair(s.z, g.z, inv, inv_f, fast);
-            o.w = scale_pair(s.w, g.w, inv, inv_f, fast);
+            o.x = scale_pair(s.x, g.x, inv_f, proven);
+            o.y = scale_pair(s.y, g.y, inv_f, proven);
+            o.z = scale_pair(s.z, g.z, inv_f, proven);
+            o.w = scale_pair(s.w, g.w, inv_f, proven);
+            if (!proven) o = scale_chunk_defined(s, g, inv);       // about one chunk in sixty
             st_stream(p.norm_out + global_at(j), o);
         }
     }
@@ -170,39 +190,51 @@ __global__ void __launch_bounds__(RN_THREADS) add_rmsnorm_kernel(AddRmsNormParam
 
 } // namespace
 
-// Tile and cluster.  Candidates: tokens per tile a power of two up to 32 (a warp's worth of contiguous 16-byte
-// chunks in the block-8 layout) and up to the batch, clusters of 1, 2, 4 or 8 CTAs; a candidate must keep its slice
-// of the sums within RN_SMEM_SUMS and give every thread at least one chunk (or be the single-CTA form).  Taken: the
-// one with the most CTAs up to 128 (enough to occupy the GPU), then the most tokens per tile, then the smallest
-// cluster -- large batches get 32-token tiles, small ones are spread over more SMs.
-void add_rmsnorm_geometry(int M, int D, int& tile_tokens, int& cluster)
+// Tile and cluster.  Candidates: tokens per tile a power of two up to 32 and up to the batch (in the block-8 layout
+// at least 8 where the batch has them, so that a tile's chunks of one column are 128 contiguous bytes); clusters of
+// 1, 2, 4 or 8 CTAs over D; the CTA's slice of the sums within RN_SMEM_SUMS; every thread of a cluster member with at
+// least one chunk.  Taken: the candidate with the most CTAs up to 128 (small batches are spread over the GPU), then
+// the smallest cluster, then the most tokens per tile.  Measured on 4096 rows: time falls with the work per CTA (a
+// CTA's fixed cost -- start, load latency, two barriers, store drain -- is about 4 us) and rises with the cluster size.
+void add_rmsnorm_geometry(int M, int D, int row_major, int& tile_tokens, int& cluster)
 {
     int top = 1;
     while (top < 32 && top < M) top <<= 1;
+    const int floor_tokens = row_major ? 1 : (top < 8 ? top : 8);
     const int chunks = D / 8;
+    if (const char* text = std::getenv("RK_NPU_B200_RMSNORM_TILE")) {      // experiments: "tokens,cluster"
+        int tm = 0, cs = 0;
+        if (std::sscanf(text, "%d,%d", &tm, &cs) == 2 && tm >= 1 && tm <= 32 && (tm & (tm - 1)) == 0 && (cs == 1 || cs == 2 || cs == 4 || cs == 8) &&
+            size_t(tm) * ((chunks + cs - 1) / cs) * 16 <= size_t(RN_SMEM_SUMS)) {
+            tile_tokens = tm;
+            cluster = cs;
+            return;
+        }
+    }
     int best_score = -1;
     tile_tokens = 1;
-    cluster = 8;
-    for (int tm = top; tm >= 1; tm >>= 1)
-        for (int cs = 1; cs <= 8; cs <<= 1) {
-            const int per = (chunks + cs - 1) / cs;
-            if (size_t(tm) * per * 16 > size_t(RN_SMEM_SUMS)) continue;
-            if (cs > 1 && tm * per < RN_THREADS) continue;
-            const int ctas = (M + tm - 1) / tm * cs;
-            const int score = ctas < 128 ? ctas : 128;
-            if (score > best_score) {
-                best_score = score;
-                tile_tokens = tm;
-                cluster = cs;
+    cluster = 8;        // D <= 32768: 512 chunks per CTA, one per thread
+    for (int pass = 0; pass < 2 && best_score < 0; ++pass)      // second pass: without the block-8 floor, if nothing fitted
+        for (int cs = 1; cs <= 8; cs <<= 1)
+            for (int tm = top; tm >= (pass ? 1 : floor_tokens); tm >>= 1) {
+                const int per = (chunks + cs - 1) / cs;
+                if (size_t(tm) * per * 16 > size_t(RN_SMEM_SUMS)) continue;
+                if (cs > 1 && tm * per < RN_THREADS) continue;
+                const int ctas = (M + tm - 1) / tm * cs;
+                const int score = ctas < 128 ? ctas : 128;
+                if (score > best_score) {
+                    best_score = score;
+                    tile_tokens = tm;
+                    cluster = cs;
+                }
             }
-        }
 }
 
 cudaError_t launch_add_rmsnorm(const AddRmsNormParams& q, cudaStream_t stream)
 {
     AddRmsNormParams p = q;
     int cs = 1;
-    add_rmsnorm_geometry(p.M, p.D, p.tile_tokens, cs);
+    add_rmsnorm_geometry(p.M, p.D, p.row_major, p.tile_tokens, cs);
     const int per = (p.D / 8 + cs - 1) / cs;
     const size_t shared = size_t(p.tile_tokens) * per * 16 + size_t(RN_THREADS + p.tile_tokens) * sizeof(double);
     auto kernel = p.row_major ? add_rmsnorm_kernel<true> : add_rmsnorm_kernel<false>;
