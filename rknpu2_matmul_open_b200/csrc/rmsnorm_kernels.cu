@@ -62,38 +62,26 @@ __device__ __forceinline__ uint32_t add_pair(uint32_t a, uint32_t b, double& acc
 // float ulps apart.  fp16 rounding of a float in the normal fp16 range is decided by its low 13 mantissa bits L
 // against the midpoint 0x1000; when |L - 0x1000| >= 8 no midpoint lies between the two floats (or on one of them), so
 // fp16(y) IS the defined result.  About 0.2 % of the values, everything outside the normal fp16 range, and rows whose
-// inv is not a normal float are not proven; a chunk of eight with such a value is evaluated in double.
+// inv is not a normal float are not proven and are evaluated in double.
 
-// The defining expression for one chunk.  A real call, so that this rare path is branched around instead of being
-// evaluated for every value.
-__device__ __forceinline__ uint32_t scale_pair_defined(uint32_t v, uint32_t g, double inv)
+// The defining expression.  A real call, so that this rare path is branched around instead of being evaluated for
+// every value (checking per value and not per chunk keeps the double-precision conversions, the slowest instructions
+// here, to the values that need them).
+__device__ __noinline__ float scale_defined(float v, float g, double inv) { return __double2float_rn(double(v) * inv * double(g)); }
+__device__ __forceinline__ float scale_one(float v, float g, double inv, float inv_f, bool fast)
 {
-    const float2 fv = __half22float2(*reinterpret_cast<const __half2*>(&v));
-    const float2 fg = __half22float2(*reinterpret_cast<const __half2*>(&g));
-    const __half2 o = __floats2half2_rn(__double2float_rn(double(fv.x) * inv * double(fg.x)),
-                                        __double2float_rn(double(fv.y) * inv * double(fg.y)));
-    return *reinterpret_cast<const uint32_t*>(&o);
-}
-__device__ __noinline__ uint4 scale_chunk_defined(uint4 v, uint4 g, double inv)
-{
-    return make_uint4(scale_pair_defined(v.x, g.x, inv), scale_pair_defined(v.y, g.y, inv), scale_pair_defined(v.z, g.z, inv),
-                      scale_pair_defined(v.w, g.w, inv));
-}
-// The single-precision value of one output and whether it is proven (see above); `proven` only ever goes false.
-__device__ __forceinline__ float scale_one(float v, float g, float inv_f, bool& proven)
-{
-    const float y = __fmul_rn(__fmul_rn(v, inv_f), g);
+    float y = __fmul_rn(__fmul_rn(v, inv_f), g);
     const uint32_t u = __float_as_uint(y);
-    proven = proven && fabsf(y) >= 6.103515625e-05f && fabsf(y) < 65536.f      // 2^-14 <= |y| < 2^16 (false for NaN)
-             && ((u - (0x1000u - 7u)) & 0x1fffu) > 14u;                        // |L - 0x1000| >= 8
+    const bool proven = fast && fabsf(y) >= 6.103515625e-05f && fabsf(y) < 65536.f      // 2^-14 <= |y| < 2^16 (false for NaN)
+                        && ((u - (0x1000u - 7u)) & 0x1fffu) > 14u;                      // |L - 0x1000| >= 8
+    if (!proven) y = scale_defined(v, g, inv);
     return y;
 }
-__device__ __forceinline__ uint32_t scale_pair(uint32_t v, uint32_t g, float inv_f, bool& proven)
+__device__ __forceinline__ uint32_t scale_pair(uint32_t v, uint32_t g, double inv, float inv_f, bool fast)
 {
     const float2 fv = __half22float2(*reinterpret_cast<const __half2*>(&v));
     const float2 fg = __half22float2(*reinterpret_cast<const __half2*>(&g));
-    const float lo = scale_one(fv.x, fg.x, inv_f, proven), hi = scale_one(fv.y, fg.y, inv_f, proven);
-    const __half2 o = __floats2half2_rn(lo, hi);
+    const __half2 o = __floats2half2_rn(scale_one(fv.x, fg.x, inv, inv_f, fast), scale_one(fv.y, fg.y, inv, inv_f, fast));
     return *reinterpret_cast<const uint32_t*>(&o);
 }
 
@@ -170,13 +158,11 @@ __global__ void __launch_bounds__(RN_THREADS, RN_CTAS) add_rmsnorm_kernel(AddRms
             const uint4 s = s_sum[shared_at(j)];
             const uint4 g = __ldg(p.gamma + j);
             st_stream(p.residual_out + global_at(j), s);
-            bool proven = fast;
             uint4 o;
-            o.x = scale_pair(s.x, g.x, inv_f, proven);
-            o.y = scale_pair(s.y, g.y, inv_f, proven);
-            o.z = scale_pair(s.z, g.z, inv_f, proven);
-            o.w = scale_pair(s.w, g.w, inv_f, proven);
-            if (!proven) o = scale_chunk_defined(s, g, inv);       // about one chunk in sixty
+            o.x = scale_pair(s.x, g.x, inv, inv_f, fast);
+            o.y = scale_pair(s.y, g.y, inv, inv_f, fast);
+            o.z = scale_pair(s.z, g.z, inv, inv_f, fast);
+            o.w = scale_pair(s.w, g.w, inv, inv_f, fast);
             st_stream(p.norm_out + global_at(j), o);
         }
     }
