@@ -807,6 +807,29 @@ def _moe(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak):
                                    "GBps_of_weights_in_the_two_projections": weight_bytes / ((stages[0] + stages[1]) * 1e-6) / 1e9,
                                    "rows_checked_exact": exact}
     ws.free(); w.free()
+    # expert paging: one int4 expert of this geometry as a cache record, imported into a slot from ordinary host memory
+    # and exchanged into a second bank (rk_npu_moe_quant_import_expert / _swap_slots)
+    small = {k: (np.clip(v[:2], -7, 7) if v.dtype == np.int8 else v[:2]) for k, v in ex.items()}
+    source = moe.MoeWeights(dom, form="quant", **small)
+    hot, stage = moe.MoeWeights.slot_bank(dom, H, I, 2), moe.MoeWeights.slot_bank(dom, H, I, 2)
+    record = np.zeros(source.record_bytes(), np.uint8)
+    back = np.zeros_like(record)
+    ok = source.export_expert(1, record) == 0
+    for _ in range(3):
+        ok = ok and stage.import_expert(0, record) == 0
+    t0 = time.perf_counter()
+    for _ in range(20):
+        stage.import_expert(0, record)
+    import_us = (time.perf_counter() - t0) / 20 * 1e6
+    t0 = time.perf_counter()
+    for _ in range(200):
+        hot.swap_slot(0, stage, 0)
+    swap_us = (time.perf_counter() - t0) / 200 * 1e6
+    ok = ok and stage.export_expert(0, back) == 0 and bool(np.array_equal(back, record))
+    out_fig["int4_expert_record"] = {"MB": record.nbytes / 1e6, "import_us": import_us, "import_GBps": record.nbytes / (import_us * 1e-6) / 1e9,
+                                     "swap_slots_us": swap_us, "round_trip_exact": ok}
+    for h in (stage, hot, source):
+        h.free()
     return {"moe_w8_H1536_I512_E128_shared_top8": out_fig}
 
 

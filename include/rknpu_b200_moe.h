@@ -3,14 +3,14 @@
  * caller's.
  *
  * Built: configuration, immutable expert weight objects (int8 experts; int4 experts; routed int4 experts with an int8
- * shared expert), workspaces of the matching form, the two blocking run calls (int8 rows with scales, or fp32 rows
+ * shared expert), mutable slot banks of int4 experts with their cache records, workspaces of the matching form, the two blocking run calls (int8 rows with scales, or fp32 rows
  * quantised here), the byte queries.  All pointers are host pointers and a call returns when the output is complete, as
  * in the original.  Int4 experts are given as int8 arrays of codes in [-8, 7]; they are accepted under the original's
  * rule (the K tile its device would run must be certified against INT16 partial sums: the whole of K where it would try
  * that, else slices of 512) and are then stored two codes per byte; the sums are the same integers as for int8 storage.
- * Exported but declined (NULL / RK_NPU_ERR_PARAM / 0, nothing else happens): the mutable slot banks and the native
- * cache records they import and export (rk_npu_moe_*_slots_create, *_export_expert, *_import_expert*, *_swap_slots,
- * *_expert_blob_bytes); RK_NPU_MOE_MIDDLE_NPU_LUT, the original device's approximate table-lookup activation (a
+ * Mutable slot banks (rk_npu_moe_*_slots_create) hold int4 experts that come and go as cache records: export from any
+ * bank with int4 experts, import into any slot, exchange slots between two banks without a copy.
+ * Exported but declined: RK_NPU_MOE_MIDDLE_NPU_LUT, the original device's approximate table-lookup activation (a
  * workspace that asks for it is not created).
  * Programs may include the original header instead of this one; names, layouts and values are the same.
  */
@@ -84,7 +84,7 @@ void rk_npu_moe_w8_weights_free(rk_npu_moe_w8_weights* weights);
 rk_npu_moe_w8_workspace* rk_npu_moe_w8_workspace_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_config* config);
 void rk_npu_moe_w8_workspace_free(rk_npu_moe_w8_workspace* workspace);
 
-/* include/rk_npu_moe_w8.h:148-152: device payload bytes of a handle. */
+/* include/rk_npu_moe_w8.h:148-152: device payload bytes of a handle; a slot bank counts the slots it holds now. */
 uint64_t rk_npu_moe_w8_weights_device_bytes(const rk_npu_moe_w8_weights* weights);
 uint64_t rk_npu_moe_w8_workspace_device_bytes(const rk_npu_moe_w8_workspace* workspace);
 
@@ -115,7 +115,29 @@ rk_npu_moe_w8_workspace* rk_npu_moe_quant_workspace_create(rk_npu_iommu_domain* 
 rk_npu_moe_w8_weights* rk_npu_moe_w4_weights_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
                                                     const rk_npu_moe_w8_expert* experts);
 rk_npu_moe_w8_workspace* rk_npu_moe_w4_workspace_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_config* config);
-/* ---- declined (see the head of this file): include/rk_npu_moe_w8.h:113-146 */
+/* ---- mutable slot banks and cache records: include/rk_npu_moe_w8.h:113-146
+ * A slot bank has the geometry of a weight object but no experts yet: every slot is imported before it is selected (an
+ * empty slot contributes zero).  rk_npu_moe_quant_slots_create: all slots int4 experts (shared_expert must be 0);
+ * rk_npu_moe_w4_slots_create: routed int4 slots plus the immutable int8 shared expert given here (shared_expert must
+ * be 1).  The caller owns the mapping of logical experts to slots.  A slot bank runs with the workspace of its form
+ * (quant / w4) like any other weight object.
+ *
+ * A cache record is one int4 expert in this library's execution layout: gate/up records, down records, the two scale
+ * arrays, and a 16-byte trailer (magic, hidden, intermediate, and in the low three bits of the LAST 32-bit word the
+ * original's tag: 1 = gate/up certified in slices, 2 = over the whole of K).  rk_npu_moe_quant_expert_blob_bytes is its
+ * size (0 for a bank without int4 experts); buffers may be larger (a file store can page-align its stride).  Records of
+ * the same expert exported from an immutable all-int4 bank, a whole-K certified one, the mixed form or a slot are the
+ * same bytes.  They are NOT the original device's records: a cache written on the original board is refused by the
+ * trailer check.
+ * export: RK_NPU_ERR_PARAM for NULL, a short buffer, an index out of range or the int8 shared expert.
+ * import: additionally RK_NPU_ERR_PARAM for a foreign or untagged trailer, another geometry, a whole-K tag where hidden
+ * does not allow it, or a scale that is not positive and finite; the record is checked before anything is copied, so a
+ * refused record leaves the slot as it was.  Import only between blocking runs that use the bank; imports into
+ * different slots, and into a bank that is not running, may overlap runs and each other.  _timed fills validate_us,
+ * gate_sync_us (the transfer; for an immutable bank the gate/up part) and down_sync_us, total_us; copy_us stays 0.
+ * swap: exchanges the storage and tags of two slots of two all-int4 SLOT banks of one geometry, context and domain --
+ * no copy, no wait; storage ownership follows the slot, either bank may be freed afterwards.  RK_NPU_ERR_PARAM
+ * otherwise (the original also accepts its immutable all-int4 banks, whose experts are separate allocations there). */
 rk_npu_moe_w8_weights* rk_npu_moe_w4_slots_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
                                                   const rk_npu_moe_w8_expert* shared);
 rk_npu_moe_w8_weights* rk_npu_moe_quant_slots_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config);

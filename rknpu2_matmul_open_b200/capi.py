@@ -161,6 +161,11 @@ class AddRmsNormSizes(C.Structure):
                 ("regcmd_bytes", C.c_uint64), ("task_bytes", C.c_uint64), ("num_tasks", C.c_int)]
 
 
+class MoeImportTimings(C.Structure):
+    """rk_npu_moe_import_timings"""
+    _fields_ = [(n, C.c_double) for n in ("copy_us", "validate_us", "gate_sync_us", "down_sync_us", "total_us")]
+
+
 class MatmulWorkspaceRequirements(C.Structure):
     _fields_ = [("bytes", C.c_uint64), ("input_bytes", C.c_uint64), ("output_bytes", C.c_uint64), ("control_bytes", C.c_uint64),
                 ("wave_count", C.c_uint32), ("buffer_count", C.c_uint32)]
@@ -345,7 +350,7 @@ _SIGNATURES = {
     "rk_npu_moe_quant_expert_blob_bytes": (C.c_uint64, [_P]),
     "rk_npu_moe_quant_export_expert": (C.c_int, [_P, C.c_int, _P, C.c_uint64]),
     "rk_npu_moe_quant_import_expert": (C.c_int, [_P, C.c_int, _P, C.c_uint64]),
-    "rk_npu_moe_quant_import_expert_timed": (C.c_int, [_P, C.c_int, _P, C.c_uint64, _P]),
+    "rk_npu_moe_quant_import_expert_timed": (C.c_int, [_P, C.c_int, _P, C.c_uint64, C.POINTER(MoeImportTimings)]),
     "rk_npu_moe_quant_swap_slots": (C.c_int, [_P, C.c_int, _P, C.c_int]),
     "rk_npu_b200_w4a8_enqueue_swiglu_f32": (C.c_int, [_P, _P, _P, _P, _P]),
     "rk_npu_b200_w4a8_enqueue_ffn_f32": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P]),

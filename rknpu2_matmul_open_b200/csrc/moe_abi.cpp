@@ -1,5 +1,6 @@
 // moe_abi.cpp -- the routed-experts operator of the original's include/rk_npu_moe_w8.h on this library: immutable expert
-// weight objects (int8, int4, or int4 routed experts with an int8 shared one), workspaces, the two blocking run calls.
+// weight objects (int8, int4, or int4 routed experts with an int8 shared one), mutable slot banks of int4 experts with
+// the cache records they import and export, workspaces, the two blocking run calls.
 //
 // The original (src/rk_npu_moe_w8.cpp:570-817) quantises the input rows on the CPU, groups the (token, slot)
 // assignments by expert, gathers and multiplies on the NPU, runs the middle stage and the weighted combine on the
@@ -15,6 +16,7 @@
 #include <cmath>
 #include <cstring>
 #include <memory>
+#include <mutex>
 #include <new>
 #include <vector>
 
@@ -48,6 +50,16 @@ bool valid_config(const rk_npu_moe_w8_config& c)           // src/rk_npu_moe_w8.
 enum class Mode { W8 = 0, RoutedW4SharedW8 = 1, W4 = 2 };
 bool expert_is_w4(Mode mode, int expert, int routed) { return mode == Mode::W4 || (mode == Mode::RoutedW4SharedW8 && expert < routed); }
 bool can_use_full_gate(int hidden) { return hidden > 512 && hidden <= 2048; }
+// Cache records (src/rk_npu_moe_w8.cpp:383): the last 32-bit word of a record carries, in its low three bits, whether
+// the original device would run the gate/up projection over the whole of K or in slices.  Nothing here depends on it
+// (the sums are exact either way); it is kept, checked and handed on so that a record says what it was certified for.
+constexpr int32_t record_tag_mask = 7, record_sliced = 1, record_full_k = 2;
+constexpr uint32_t record_magic = 0x34424b52u;      // "RKB4": an int4 expert in this library's record layout
+struct RecordTrailer {                               // the last 16 bytes of a record
+    uint32_t magic;
+    int32_t hidden, intermediate;
+    int32_t tag;
+};
 bool valid_w4(const rk_npu_moe_w8_weight_config& c)
 {
     return valid_weights(c) && c.hidden % 64 == 0 && c.intermediate % 64 == 0 && c.hidden <= 8128;
@@ -79,6 +91,35 @@ struct rk_npu_moe_w8_weights {
     MoeBank gate_up_bank() const { return MoeBank{gate_up, moe_packed_nibble_bytes(config.hidden, 2 * config.intermediate), moe_packed_bytes(config.hidden, 2 * config.intermediate), nibble_experts}; }
     MoeBank down_bank() const { return MoeBank{down, moe_packed_nibble_bytes(config.intermediate, config.hidden), moe_packed_bytes(config.intermediate, config.hidden), nibble_experts}; }
     size_t gate_up_bytes = 0, down_bytes = 0, gate_up_scale_bytes = 0, down_scale_bytes = 0;
+    std::vector<int32_t> tags;    // per int4 expert: record_sliced or record_full_k
+    // A slot bank (rk_npu_moe_*_slots_create) keeps every expert in an allocation of its own, laid out like a cache
+    // record: [gate/up records | down records | gate/up scales | down scales].  Slots change hands between banks by
+    // exchanging these structs; the four arrays above stay null.
+    struct Slot {
+        uint8_t* storage = nullptr;
+        size_t bytes = 0;
+    };
+    bool slotted = false;
+    std::vector<Slot> slots;
+    cudaStream_t stream = nullptr;   // imports and exports
+    std::mutex transfer;             // one of them at a time on `stream`
+    int experts() const { return config.routed_experts + config.shared_expert; }
+    size_t gate_up_record_bytes(int e) const { return e < nibble_experts ? moe_packed_nibble_bytes(config.hidden, 2 * config.intermediate) : moe_packed_bytes(config.hidden, 2 * config.intermediate); }
+    size_t down_record_bytes(int e) const { return e < nibble_experts ? moe_packed_nibble_bytes(config.intermediate, config.hidden) : moe_packed_bytes(config.intermediate, config.hidden); }
+    size_t slot_bytes(int e) const { return gate_up_record_bytes(e) + down_record_bytes(e) + sizeof(float) * (2 * size_t(config.intermediate) + size_t(config.hidden)); }
+    // where expert e's four pieces are, in either representation
+    uint8_t* gate_up_at(int e) const { return slotted ? slots[e].storage : const_cast<uint8_t*>(gate_up_bank().expert(e)); }
+    uint8_t* down_at(int e) const { return slotted ? slots[e].storage + gate_up_record_bytes(e) : const_cast<uint8_t*>(down_bank().expert(e)); }
+    float* gate_up_scales_at(int e) const
+    {
+        return slotted ? reinterpret_cast<float*>(slots[e].storage + gate_up_record_bytes(e) + down_record_bytes(e))
+                       : gate_up_scales + size_t(e) * 2 * config.intermediate;
+    }
+    float* down_scales_at(int e) const { return slotted ? gate_up_scales_at(e) + 2 * config.intermediate : down_scales + size_t(e) * config.hidden; }
+    uint64_t record_bytes() const      // one int4 expert as a cache record; 0 for banks without int4 experts
+    {
+        return nibble_experts ? uint64_t(slot_bytes(0) + sizeof(RecordTrailer)) : 0;
+    }
 };
 
 struct rk_npu_moe_w8_workspace {
@@ -121,6 +162,9 @@ void weights_destroy(rk_npu_moe_w8_weights* w)
         if (w->down) device_free(d, w->down, w->down_bytes);
         if (w->gate_up_scales) device_free(d, w->gate_up_scales, w->gate_up_scale_bytes);
         if (w->down_scales) device_free(d, w->down_scales, w->down_scale_bytes);
+        for (auto& slot : w->slots)
+            if (slot.storage) device_free(d, slot.storage, slot.bytes);
+        if (w->stream) { cudaStreamSynchronize(w->stream); cudaStreamDestroy(w->stream); }
         domain_release(d);
     }
     delete w;
@@ -164,10 +208,10 @@ struct Upload {
     size_t job_expert, job_first, job_rows, assign_token, slot_assign, coefficients, scales, rows_data, bytes;
     int jobs, assignments;
 };
-size_t upload_capacity(int max_rows, int slots, int H)
+size_t upload_capacity(int max_rows, int slots, int H, int experts)
 {
     const size_t A = size_t(max_rows) * slots;
-    return (4 * A + 2 * A + size_t(max_rows)) * 4 + 16 + size_t(max_rows) * H * 4;
+    return (4 * A + 2 * A + size_t(max_rows)) * 4 + 16 + size_t(max_rows) * H * 4 + 16 + 4 * sizeof(void*) * size_t(experts);   // + a slot bank's tables
 }
 
 // Groups the assignments by expert, cuts the groups into jobs of at most 16 and writes everything into the mirror.
@@ -252,8 +296,26 @@ int moe_run(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int row
     try {
         // ---- the routes grouped by expert, the input rows: one piece, one copy
         auto at = Clock::now();
-        const Upload u = build_upload(*ws, rows, input, f32, scales, ids, routes);
+        Upload u = build_upload(*ws, rows, input, f32, scales, ids, routes);
         const int assignments = u.assignments, jobs = u.jobs;
+        MoeBank gate_up_bank = w->gate_up_bank(), down_bank = w->down_bank();
+        if (w->slotted) {      // where every expert lives right now travels with the run: records and scales of both projections
+            const int E = w->experts();
+            const size_t tables = (u.bytes + 15) / 16 * 16;
+            const void** host = reinterpret_cast<const void**>(ws->host_upload + tables);
+            for (int e = 0; e < E; ++e) {
+                host[e] = w->gate_up_at(e);
+                host[E + e] = w->down_at(e);
+                host[2 * E + e] = w->gate_up_scales_at(e);
+                host[3 * E + e] = w->down_scales_at(e);
+            }
+            const uint8_t* device = ws->upload + tables;
+            gate_up_bank.table = reinterpret_cast<const uint8_t* const*>(device);
+            down_bank.table = reinterpret_cast<const uint8_t* const*>(device + sizeof(void*) * E);
+            gate_up_bank.scale_table = reinterpret_cast<const float* const*>(device + 2 * sizeof(void*) * E);
+            down_bank.scale_table = reinterpret_cast<const float* const*>(device + 3 * sizeof(void*) * E);
+            u.bytes = tables + 4 * sizeof(void*) * E;
+        }
         t.schedule_us = since_us(at);
         at = Clock::now();
         if (timings) cudaEventRecord(ws->events[0], s);
@@ -290,10 +352,10 @@ int moe_run(rk_npu_moe_w8_workspace* ws, const rk_npu_moe_w8_weights* w, int row
         float* const landing = direct ? ws->host_out_alias : ws->out;
         const MoeSchedule sched{reinterpret_cast<const int*>(ws->upload + u.job_expert), reinterpret_cast<const int*>(ws->upload + u.job_first),
                                 reinterpret_cast<const int*>(ws->upload + u.job_rows), reinterpret_cast<const int*>(ws->upload + u.assign_token), jobs};
-        const MoeGateUpParams gu{sched, w->gate_up_bank(), w->gate_up_scales, codes, in_scales, ws->middle, ws->row_max, H, I};
+        const MoeGateUpParams gu{sched, gate_up_bank, w->gate_up_scales, codes, in_scales, ws->middle, ws->row_max, H, I};
         ok = launch_moe_gate_up(gu, s) == cudaSuccess;
         if (timings) cudaEventRecord(ws->events[2], s);
-        const MoeDownParams dn{sched, w->down_bank(), w->down_scales, ws->middle, ws->row_max, ws->expert_out, H, I};
+        const MoeDownParams dn{sched, down_bank, w->down_scales, ws->middle, ws->row_max, ws->expert_out, H, I};
         ok = ok && launch_moe_down(dn, s) == cudaSuccess;
         if (timings) cudaEventRecord(ws->events[3], s);
         const MoeCombineParams cb{ws->expert_out, reinterpret_cast<const int*>(ws->upload + u.slot_assign),
@@ -346,67 +408,103 @@ extern "C" void rk_npu_moe_w8_config_init(rk_npu_moe_w8_config* c, int hidden, i
 }
 
 namespace {
-rk_npu_moe_w8_weights* weights_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
-                                      const rk_npu_moe_w8_expert* experts, Mode mode, bool certify_full_k)
+// src/rk_npu_moe_w8.cpp:453-474: one expert as the caller gives it.  Int4 experts: gate/up is certified over the whole
+// of K where the original would try that (with its 512 slices as the fallback), else over slices of at most 512; down
+// over the whole of K = intermediate.  `tag` says which gate/up certification held.
+bool valid_expert(const rk_npu_moe_w8_expert& x, int H, int I, bool int4, bool try_full, int32_t& tag)
 {
-    if (!domain || !domain->ctx || !config || !experts || !(mode == Mode::W8 ? valid_weights(*config) : valid_w4(*config)) ||
-        domain->ctx->world > 1)
+    tag = record_sliced;
+    if (!x.gate_up || !x.down || !x.gate_up_scales || !x.down_scales) return false;
+    for (int n = 0; n < 2 * I; ++n)
+        if (!finite_positive(x.gate_up_scales[n])) return false;
+    for (int n = 0; n < H; ++n)
+        if (!finite_positive(x.down_scales[n])) return false;
+    if (!int4) return true;
+    WeightBound gate, down;
+    const int slice = std::min(H, 512);
+    try {
+        if (bound_weights(H, 2 * I, x.gate_up, try_full ? H : slice, gate, try_full ? slice : 0) != RK_NPU_OK ||
+            bound_weights(I, H, x.down, I, down) != RK_NPU_OK)
+            return false;
+    } catch (...) { return false; }
+    if (try_full && gate.k_tile > slice) tag = record_full_k;
+    return true;
+}
+
+// Uploads one expert's matrices through `raw` (room for both), packs them into records and copies its scales.
+bool place_expert(const rk_npu_moe_w8_weights& w, int e, const rk_npu_moe_w8_expert& x, int8_t* raw, cudaStream_t s)
+{
+    const int H = w.config.hidden, I = w.config.intermediate;
+    const size_t gu_raw = size_t(H) * 2 * I, dn_raw = size_t(I) * H;
+    const bool nib = e < w.nibble_experts;
+    return cudaMemcpyAsync(raw, x.gate_up, gu_raw, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+           cudaMemcpyAsync(raw + gu_raw, x.down, dn_raw, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+           cudaMemcpyAsync(w.gate_up_scales_at(e), x.gate_up_scales, sizeof(float) * 2 * I, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+           cudaMemcpyAsync(w.down_scales_at(e), x.down_scales, sizeof(float) * H, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+           launch_moe_pack(MoePackParams{raw, w.gate_up_at(e), H, 2 * I, nib}, s) == cudaSuccess &&
+           launch_moe_pack(MoePackParams{raw + gu_raw, w.down_at(e), I, H, nib}, s) == cudaSuccess &&
+           cudaStreamSynchronize(s) == cudaSuccess;     // the caller's arrays and `raw` are reused by the next expert
+}
+
+// experts != null: an immutable bank of all E experts.  experts == null: a slot bank -- E zeroed slots (an expert that
+// was never imported contributes zero), plus the int8 shared expert `shared` packed into the last one where the
+// configuration has it.
+rk_npu_moe_w8_weights* weights_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
+                                      const rk_npu_moe_w8_expert* experts, Mode mode, bool certify_full_k,
+                                      const rk_npu_moe_w8_expert* shared = nullptr)
+{
+    const bool slotted = experts == nullptr;
+    if (!domain || !domain->ctx || !config || !(mode == Mode::W8 ? valid_weights(*config) : valid_w4(*config)) || domain->ctx->world > 1)
         return nullptr;
-    const int H = config->hidden, I = config->intermediate, E = config->routed_experts + config->shared_expert;
-    for (int e = 0; e < E; ++e) {       // src/rk_npu_moe_w8.cpp:453-474
-        const auto& x = experts[e];
-        if (!x.gate_up || !x.down || !x.gate_up_scales || !x.down_scales) return nullptr;
-        for (int n = 0; n < 2 * I; ++n)
-            if (!finite_positive(x.gate_up_scales[n])) return nullptr;
-        for (int n = 0; n < H; ++n)
-            if (!finite_positive(x.down_scales[n])) return nullptr;
-        if (expert_is_w4(mode, e, config->routed_experts)) {
-            // gate/up: the whole of K where the original would try it (and its 512 slices as the fallback), else slices
-            // of at most 512; down: the whole of K = intermediate
-            WeightBound bound;
-            const int slice = std::min(H, 512);
-            const bool try_full = (certify_full_k || mode == Mode::RoutedW4SharedW8) && can_use_full_gate(H);
-            try {
-                if (bound_weights(H, 2 * I, x.gate_up, try_full ? H : slice, bound, try_full ? slice : 0) != RK_NPU_OK ||
-                    bound_weights(I, H, x.down, I, bound) != RK_NPU_OK)
-                    return nullptr;
-            } catch (...) { return nullptr; }
-        }
+    if (slotted && (mode == Mode::W8 || (mode == Mode::W4) != (config->shared_expert == 0) || (config->shared_expert && !shared))) return nullptr;
+    const int H = config->hidden, I = config->intermediate, R = config->routed_experts, E = R + config->shared_expert;
+    std::vector<int32_t> tags;
+    try { tags.assign(size_t(E), record_sliced); } catch (...) { return nullptr; }
+    const bool try_full = (certify_full_k || mode == Mode::RoutedW4SharedW8) && can_use_full_gate(H);
+    if (!slotted) {
+        for (int e = 0; e < E; ++e)
+            if (!valid_expert(experts[e], H, I, expert_is_w4(mode, e, R), try_full, tags[size_t(e)])) return nullptr;
+    } else if (shared && !valid_expert(*shared, H, I, false, false, tags[size_t(R)])) {
+        return nullptr;
     }
     rk_npu_ctx* ctx = domain->ctx;
     if (cudaSetDevice(ctx->device) != cudaSuccess) return nullptr;
-    rk_npu_moe_w8_weights* w = new (std::nothrow) rk_npu_moe_w8_weights();
-    if (!w) return nullptr;
+    rk_npu_moe_w8_weights* w = nullptr;
+    try { w = new rk_npu_moe_w8_weights(); } catch (...) { return nullptr; }
     w->domain = domain;
     w->ctx_id = ctx->id;
     w->domain_id = domain->id;
     w->config = *config;
     w->mode = mode;
+    w->tags.swap(tags);
+    w->slotted = slotted;
     domain_retain(domain);
-    w->nibble_experts = mode == Mode::W4 ? E : (mode == Mode::RoutedW4SharedW8 ? config->routed_experts : 0);
-    const MoeBank gb = w->gate_up_bank(), db = w->down_bank();
-    w->gate_up_bytes = size_t(w->nibble_experts) * gb.nibble_bytes + size_t(E - w->nibble_experts) * gb.byte_bytes;
-    w->down_bytes = size_t(w->nibble_experts) * db.nibble_bytes + size_t(E - w->nibble_experts) * db.byte_bytes;
-    w->gate_up_scale_bytes = sizeof(float) * 2 * size_t(I) * E;
-    w->down_scale_bytes = sizeof(float) * size_t(H) * E;
-    bool ok = !device_alloc(domain, reinterpret_cast<void**>(&w->gate_up), w->gate_up_bytes) &&
-              !device_alloc(domain, reinterpret_cast<void**>(&w->down), w->down_bytes) &&
-              !device_alloc(domain, reinterpret_cast<void**>(&w->gate_up_scales), w->gate_up_scale_bytes) &&
-              !device_alloc(domain, reinterpret_cast<void**>(&w->down_scales), w->down_scale_bytes);
-    int8_t* raw = nullptr;     // one expert's matrices as given, on their way into records
-    const size_t gu_raw = size_t(H) * 2 * I, dn_raw = size_t(I) * H;
-    ok = ok && cudaMalloc(reinterpret_cast<void**>(&raw), gu_raw + dn_raw) == cudaSuccess;
-    cudaStream_t s = ctx->stream;
-    for (int e = 0; ok && e < E; ++e) {
-        const auto& x = experts[e];
-        ok = cudaMemcpyAsync(raw, x.gate_up, gu_raw, cudaMemcpyHostToDevice, s) == cudaSuccess &&
-             cudaMemcpyAsync(raw + gu_raw, x.down, dn_raw, cudaMemcpyHostToDevice, s) == cudaSuccess &&
-             cudaMemcpyAsync(w->gate_up_scales + size_t(e) * 2 * I, x.gate_up_scales, sizeof(float) * 2 * I, cudaMemcpyHostToDevice, s) == cudaSuccess &&
-             cudaMemcpyAsync(w->down_scales + size_t(e) * H, x.down_scales, sizeof(float) * H, cudaMemcpyHostToDevice, s) == cudaSuccess &&
-             launch_moe_pack(MoePackParams{raw, const_cast<uint8_t*>(w->gate_up_bank().expert(e)), H, 2 * I, e < w->nibble_experts}, s) == cudaSuccess &&
-             launch_moe_pack(MoePackParams{raw + gu_raw, const_cast<uint8_t*>(w->down_bank().expert(e)), I, H, e < w->nibble_experts}, s) == cudaSuccess &&
-             cudaStreamSynchronize(s) == cudaSuccess;     // the caller's arrays and `raw` are reused by the next expert
+    w->nibble_experts = mode == Mode::W4 ? E : (mode == Mode::RoutedW4SharedW8 ? R : 0);
+    bool ok = cudaStreamCreateWithFlags(&w->stream, cudaStreamNonBlocking) == cudaSuccess;
+    if (slotted) {
+        try { w->slots.resize(size_t(E)); } catch (...) { ok = false; }
+        for (int e = 0; ok && e < E; ++e) {
+            auto& slot = w->slots[size_t(e)];
+            slot.bytes = w->slot_bytes(e);
+            ok = !device_alloc(domain, reinterpret_cast<void**>(&slot.storage), slot.bytes) &&
+                 cudaMemsetAsync(slot.storage, 0, slot.bytes, w->stream) == cudaSuccess;
+        }
+        ok = ok && cudaStreamSynchronize(w->stream) == cudaSuccess;
+    } else {
+        const MoeBank gb = w->gate_up_bank(), db = w->down_bank();
+        w->gate_up_bytes = size_t(w->nibble_experts) * gb.nibble_bytes + size_t(E - w->nibble_experts) * gb.byte_bytes;
+        w->down_bytes = size_t(w->nibble_experts) * db.nibble_bytes + size_t(E - w->nibble_experts) * db.byte_bytes;
+        w->gate_up_scale_bytes = sizeof(float) * 2 * size_t(I) * E;
+        w->down_scale_bytes = sizeof(float) * size_t(H) * E;
+        ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&w->gate_up), w->gate_up_bytes) &&
+             !device_alloc(domain, reinterpret_cast<void**>(&w->down), w->down_bytes) &&
+             !device_alloc(domain, reinterpret_cast<void**>(&w->gate_up_scales), w->gate_up_scale_bytes) &&
+             !device_alloc(domain, reinterpret_cast<void**>(&w->down_scales), w->down_scale_bytes);
     }
+    int8_t* raw = nullptr;     // one expert's matrices as given, on their way into records
+    if (!slotted || shared) ok = ok && cudaMalloc(reinterpret_cast<void**>(&raw), size_t(H) * 2 * I + size_t(I) * H) == cudaSuccess;
+    for (int e = 0; ok && !slotted && e < E; ++e) ok = place_expert(*w, e, experts[e], raw, ctx->stream);
+    if (ok && slotted && shared) ok = place_expert(*w, R, *shared, raw, ctx->stream);
     if (raw) cudaFree(raw);
     if (!ok) { cudaGetLastError(); weights_destroy(w); return nullptr; }
     return w;
@@ -445,7 +543,7 @@ rk_npu_moe_w8_workspace* workspace_create(rk_npu_iommu_domain* domain, const rk_
     ws->row_max_bytes = A * 4;
     ws->expert_out_bytes = A * H * 4;
     ws->out_bytes = size_t(rows) * H * 4;
-    ws->upload_bytes = upload_capacity(rows, ws->slots, H);
+    ws->upload_bytes = upload_capacity(rows, ws->slots, H, config->weights.routed_experts + config->weights.shared_expert);
     bool ok = true;
     try { ws->groups.resize(size_t(config->weights.routed_experts + config->weights.shared_expert)); } catch (...) { ok = false; }
     ok = ok && !device_alloc(domain, reinterpret_cast<void**>(&ws->codes), ws->codes_bytes) &&
@@ -480,7 +578,10 @@ extern "C" void rk_npu_moe_w8_workspace_free(rk_npu_moe_w8_workspace* ws) { work
 
 extern "C" uint64_t rk_npu_moe_w8_weights_device_bytes(const rk_npu_moe_w8_weights* w)
 {
-    return w ? uint64_t(w->gate_up_bytes + w->down_bytes + w->gate_up_scale_bytes + w->down_scale_bytes) : 0;
+    if (!w) return 0;
+    uint64_t bytes = uint64_t(w->gate_up_bytes + w->down_bytes + w->gate_up_scale_bytes + w->down_scale_bytes);
+    for (const auto& slot : w->slots) bytes += slot.bytes;      // what the bank holds now; exchanged slots count where they are
+    return bytes;
 }
 extern "C" uint64_t rk_npu_moe_w8_workspace_device_bytes(const rk_npu_moe_w8_workspace* ws)
 {
@@ -527,11 +628,123 @@ extern "C" rk_npu_moe_w8_workspace* rk_npu_moe_w4_workspace_create(rk_npu_iommu_
     return workspace_create(domain, config, Mode::RoutedW4SharedW8);
 }
 
-// ---- mutable slot banks and the native cache records they import and export: declined (include/rk_npu_moe_w8.h:113-146)
-extern "C" rk_npu_moe_w8_weights* rk_npu_moe_w4_slots_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_weight_config*, const rk_npu_moe_w8_expert*) { return nullptr; }
-extern "C" rk_npu_moe_w8_weights* rk_npu_moe_quant_slots_create(rk_npu_iommu_domain*, const rk_npu_moe_w8_weight_config*) { return nullptr; }
-extern "C" uint64_t rk_npu_moe_quant_expert_blob_bytes(const rk_npu_moe_w8_weights*) { return 0; }
-extern "C" int rk_npu_moe_quant_export_expert(const rk_npu_moe_w8_weights*, int, void*, uint64_t) { return RK_NPU_ERR_PARAM; }
-extern "C" int rk_npu_moe_quant_import_expert(rk_npu_moe_w8_weights*, int, const void*, uint64_t) { return RK_NPU_ERR_PARAM; }
-extern "C" int rk_npu_moe_quant_import_expert_timed(rk_npu_moe_w8_weights*, int, const void*, uint64_t, rk_npu_moe_import_timings*) { return RK_NPU_ERR_PARAM; }
-extern "C" int rk_npu_moe_quant_swap_slots(rk_npu_moe_w8_weights*, int, rk_npu_moe_w8_weights*, int) { return RK_NPU_ERR_PARAM; }
+// ---- mutable slot banks and their cache records (include/rk_npu_moe_w8.h:113-146, src/rk_npu_moe_w8.cpp:915-1000)
+// A record is one int4 expert exactly as a slot stores it -- gate/up records, down records, gate/up scales, down scales
+// -- followed by a 16-byte trailer (magic, hidden, intermediate, tag).  Records made by an immutable bank, a slot bank or
+// the mixed form are the same bytes for the same expert; import is one copy into the slot.
+extern "C" rk_npu_moe_w8_weights* rk_npu_moe_quant_slots_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config)
+{
+    return weights_create(domain, config, nullptr, Mode::W4, false);
+}
+extern "C" rk_npu_moe_w8_weights* rk_npu_moe_w4_slots_create(rk_npu_iommu_domain* domain, const rk_npu_moe_w8_weight_config* config,
+                                                             const rk_npu_moe_w8_expert* shared)
+{
+    if (!shared) return nullptr;
+    return weights_create(domain, config, nullptr, Mode::RoutedW4SharedW8, false, shared);
+}
+extern "C" uint64_t rk_npu_moe_quant_expert_blob_bytes(const rk_npu_moe_w8_weights* w) { return w ? w->record_bytes() : 0; }
+
+namespace {
+bool record_expert(const rk_npu_moe_w8_weights* w, int e)
+{
+    return w && w->record_bytes() && e >= 0 && e < w->experts() && expert_is_w4(w->mode, e, w->config.routed_experts);
+}
+} // namespace
+
+extern "C" int rk_npu_moe_quant_export_expert(const rk_npu_moe_w8_weights* w, int expert, void* data, uint64_t bytes)
+{
+    if (!record_expert(w, expert) || !data || bytes < w->record_bytes()) return RK_NPU_ERR_PARAM;
+    auto* self = const_cast<rk_npu_moe_w8_weights*>(w);      // the transfer stream and its lock are not part of the value
+    if (cudaSetDevice(w->domain->ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    const int H = w->config.hidden, I = w->config.intermediate;
+    const size_t gu = w->gate_up_record_bytes(expert), dn = w->down_record_bytes(expert);
+    uint8_t* out = static_cast<uint8_t*>(data);
+    std::lock_guard<std::mutex> guard(self->transfer);
+    cudaStream_t s = w->stream;
+    const bool ok = cudaMemcpyAsync(out, w->gate_up_at(expert), gu, cudaMemcpyDeviceToHost, s) == cudaSuccess &&
+                    cudaMemcpyAsync(out + gu, w->down_at(expert), dn, cudaMemcpyDeviceToHost, s) == cudaSuccess &&
+                    cudaMemcpyAsync(out + gu + dn, w->gate_up_scales_at(expert), sizeof(float) * 2 * I, cudaMemcpyDeviceToHost, s) == cudaSuccess &&
+                    cudaMemcpyAsync(out + gu + dn + sizeof(float) * 2 * I, w->down_scales_at(expert), sizeof(float) * H, cudaMemcpyDeviceToHost, s) == cudaSuccess &&
+                    cudaStreamSynchronize(s) == cudaSuccess;
+    if (!ok) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+    const RecordTrailer trailer{record_magic, H, I, w->tags[size_t(expert)]};
+    std::memcpy(out + w->slot_bytes(expert), &trailer, sizeof(trailer));
+    return RK_NPU_OK;
+}
+
+// Import only between blocking runs that use the bank (the original's rule).  The record is checked BEFORE anything is
+// copied -- length, trailer, tag, every scale positive and finite -- so a refused record leaves the slot as it was.
+extern "C" int rk_npu_moe_quant_import_expert_timed(rk_npu_moe_w8_weights* w, int slot, const void* data, uint64_t bytes,
+                                                    rk_npu_moe_import_timings* timings)
+{
+    if (!record_expert(w, slot) || !data || bytes < w->record_bytes()) return RK_NPU_ERR_PARAM;
+    if (timings) *timings = rk_npu_moe_import_timings{};
+    const auto begin = Clock::now();
+    const int H = w->config.hidden, I = w->config.intermediate;
+    const size_t gu = w->gate_up_record_bytes(slot), dn = w->down_record_bytes(slot), payload = w->slot_bytes(slot);
+    const uint8_t* in = static_cast<const uint8_t*>(data);
+    RecordTrailer trailer;
+    std::memcpy(&trailer, in + payload, sizeof(trailer));
+    const int32_t tag = trailer.tag & record_tag_mask;
+    if (trailer.magic != record_magic || trailer.hidden != H || trailer.intermediate != I ||
+        (tag != record_sliced && !(tag == record_full_k && can_use_full_gate(H))))
+        return RK_NPU_ERR_PARAM;
+    const float* scales = reinterpret_cast<const float*>(in + gu + dn);
+    for (int n = 0; n < 2 * I + H; ++n) {
+        float value;
+        std::memcpy(&value, scales + n, sizeof(value));
+        if (!finite_positive(value)) return RK_NPU_ERR_PARAM;
+    }
+    const double validate_us = since_us(begin);
+    if (cudaSetDevice(w->domain->ctx->device) != cudaSuccess) return RK_NPU_ERR_SUBMIT;
+    auto at = Clock::now();
+    double gate_us = 0, down_us = 0;
+    {
+        std::lock_guard<std::mutex> guard(w->transfer);
+        cudaStream_t s = w->stream;
+        bool ok;
+        if (w->slotted) {      // the slot is laid out like the record: one copy
+            ok = cudaMemcpyAsync(w->slots[size_t(slot)].storage, in, payload, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+                 cudaStreamSynchronize(s) == cudaSuccess;
+            gate_us = since_us(at);
+        } else {
+            ok = cudaMemcpyAsync(w->gate_up_at(slot), in, gu, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+                 cudaMemcpyAsync(w->gate_up_scales_at(slot), in + gu + dn, sizeof(float) * 2 * I, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+                 cudaStreamSynchronize(s) == cudaSuccess;
+            gate_us = since_us(at);
+            at = Clock::now();
+            ok = ok && cudaMemcpyAsync(w->down_at(slot), in + gu, dn, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+                 cudaMemcpyAsync(w->down_scales_at(slot), in + gu + dn + sizeof(float) * 2 * I, sizeof(float) * H, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+                 cudaStreamSynchronize(s) == cudaSuccess;
+            down_us = since_us(at);
+        }
+        if (!ok) { cudaGetLastError(); return RK_NPU_ERR_SUBMIT; }
+        w->tags[size_t(slot)] = tag;
+    }
+    if (timings) {      // copy_us: host-side staging in the original, nothing here; the two sync fields: the transfers
+        timings->validate_us = validate_us;
+        timings->gate_sync_us = gate_us;
+        timings->down_sync_us = down_us;
+        timings->total_us = since_us(begin);
+    }
+    return RK_NPU_OK;
+}
+extern "C" int rk_npu_moe_quant_import_expert(rk_npu_moe_w8_weights* w, int slot, const void* data, uint64_t bytes)
+{
+    return rk_npu_moe_quant_import_expert_timed(w, slot, data, bytes, nullptr);
+}
+
+// Exchanges two slots' storage and tags: no copy, no wait.  Both banks are all-int4 slot banks of one geometry, context
+// and domain (the original accepts its immutable all-int4 banks too, whose experts are separate allocations there; here
+// an immutable bank is one allocation and cannot give a piece away).  The caller keeps the two slots idle meanwhile;
+// other slots of either bank may be imported at the same time.
+extern "C" int rk_npu_moe_quant_swap_slots(rk_npu_moe_w8_weights* a, int ai, rk_npu_moe_w8_weights* b, int bi)
+{
+    if (!a || !b || a->mode != Mode::W4 || b->mode != Mode::W4 || !a->slotted || !b->slotted || a->config.hidden != b->config.hidden ||
+        a->config.intermediate != b->config.intermediate || a->ctx_id != b->ctx_id || a->domain_id != b->domain_id || ai < 0 || bi < 0 ||
+        ai >= a->experts() || bi >= b->experts())
+        return RK_NPU_ERR_PARAM;
+    std::swap(a->slots[size_t(ai)], b->slots[size_t(bi)]);
+    std::swap(a->tags[size_t(ai)], b->tags[size_t(bi)]);
+    return RK_NPU_OK;
+}

@@ -21,15 +21,26 @@ inline size_t moe_packed_bytes(int K, int N) { return size_t((K + MOE_KQ - 1) / 
 // nibbles and those at k = 16 + 4t.. in its high nibbles, so that (w << 4) & 0xF0F0F0F0 and w & 0xF0F0F0F0 are the two
 // A registers of the channel with every code times 16 (the sums are shifted back, exactly).  Half the bytes.
 inline size_t moe_packed_nibble_bytes(int K, int N) { return moe_packed_bytes(K, N) / 2; }
-// A bank of experts: the first `nibble_experts` hold int4 records, the rest int8 records.
+// A bank of experts: the first `nibble_experts` hold int4 records, the rest int8 records.  An immutable bank is one
+// allocation (`base`, experts at fixed strides) with its scales in one array; a slot bank keeps every expert in an
+// allocation of its own, which can change hands between banks, and gives the kernels two tables of pointers instead
+// (`table`: each expert's records; `scale_table`: each expert's scales).
 struct MoeBank {
     const uint8_t* base;
     size_t nibble_bytes, byte_bytes;   // one expert's records in either form
     int nibble_experts;
+    const uint8_t* const* table;       // slot banks only, else null
+    const float* const* scale_table;   // slot banks only, else null
     __host__ __device__ const uint8_t* expert(int e) const
     {
+        if (table) return table[e];
         return e < nibble_experts ? base + size_t(e) * nibble_bytes
                                   : base + size_t(nibble_experts) * nibble_bytes + size_t(e - nibble_experts) * byte_bytes;
+    }
+    // the scales of expert e: `all` holds `stride` per expert where there is no table
+    __host__ __device__ const float* scales(int e, const float* all, int stride) const
+    {
+        return scale_table ? scale_table[e] : all + size_t(e) * stride;
     }
     __host__ __device__ bool nibbles(int e) const { return e < nibble_experts; }
 };
@@ -60,7 +71,7 @@ struct MoeSchedule {
 struct MoeGateUpParams {
     MoeSchedule sched;
     MoeBank bank;                // experts' gate/up matrices
-    const float* w_scales;       // [E][2I]
+    const float* w_scales;       // [E][2I] (immutable banks; a slot bank's come from its table)
     const int8_t* codes;         // [rows][H]
     const float* in_scales;      // [rows]
     float* middle;               // [assignments][I]
@@ -71,7 +82,7 @@ struct MoeGateUpParams {
 struct MoeDownParams {
     MoeSchedule sched;
     MoeBank bank;                // experts' down matrices
-    const float* w_scales;       // [E][H]
+    const float* w_scales;       // [E][H] (immutable banks)
     const float* middle;         // [assignments][I]
     const uint32_t* row_max;     // [assignments]
     float* expert_out;           // [assignments][H]

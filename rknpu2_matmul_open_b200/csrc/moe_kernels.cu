@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gate_up_kernel(const MoeGateU
         c[i >> 3][(i >> 2) & 1][i & 3] = nib ? sum >> 4 : sum;     // int4 records: every code entered times 16
     }
     const int g = lane >> 2, t = lane & 3;
-    const float* ws = p.w_scales + (size_t)expert * 2 * p.I;
+    const float* ws = p.bank.scales(expert, p.w_scales, 2 * p.I);
     float wg[2], wu[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) { wg[h] = __ldg(ws + fb * 16 + g + 8 * h); wu[h] = __ldg(ws + p.I + fb * 16 + g + 8 * h); }
@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_down_kernel(const MoeDownPara
         }
     }
     __syncthreads();
-    const float* ws = p.w_scales + (size_t)expert * p.H;
+    const float* ws = p.bank.scales(expert, p.w_scales, p.H);
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll 1
     for (int b = 0; b < MOE_DOWN_BLOCKS; ++b) {

@@ -11,7 +11,7 @@ import ctypes as C
 import numpy as np
 
 from . import capi
-from .capi import MoeConfig, MoeExpert, MoeTimings, MoeWeightConfig
+from .capi import MoeConfig, MoeExpert, MoeImportTimings, MoeTimings, MoeWeightConfig
 from .w4a8 import W4A8Error, _ptr
 
 
@@ -44,8 +44,47 @@ class MoeWeights:
         if not self.handle:
             raise W4A8Error(capi.RK_NPU_ERR_PARAM, name)
 
+    @classmethod
+    def slot_bank(cls, domain, hidden: int, intermediate: int, routed_experts: int, shared=None) -> "MoeWeights":
+        """rk_npu_moe_quant_slots_create (shared is None: every slot an int4 expert) or rk_npu_moe_w4_slots_create
+        (shared = (gate_up [H, 2I] int8, gate_up_scales, down [I, H] int8, down_scales): the immutable int8 shared expert).
+        Slots hold nothing until records are imported."""
+        self = cls.__new__(cls)
+        self.lib = capi.load()
+        self.config = MoeWeightConfig(hidden, intermediate, routed_experts, 0 if shared is None else 1)
+        if shared is None:
+            name = "rk_npu_moe_quant_slots_create"
+            self.handle = self.lib.rk_npu_moe_quant_slots_create(domain.handle, C.byref(self.config))
+        else:
+            name = "rk_npu_moe_w4_slots_create"
+            gu, gus, dn, dns = (np.ascontiguousarray(a, t) for a, t in zip(shared, (np.int8, np.float32, np.int8, np.float32)))
+            expert = MoeExpert(_ptr(gu), _ptr(gus), _ptr(dn), _ptr(dns))
+            self.handle = self.lib.rk_npu_moe_w4_slots_create(domain.handle, C.byref(self.config), C.byref(expert))
+        if not self.handle:
+            raise W4A8Error(capi.RK_NPU_ERR_PARAM, name)
+        return self
+
     def device_bytes(self) -> int:
         return int(self.lib.rk_npu_moe_w8_weights_device_bytes(self.handle))
+
+    def record_bytes(self) -> int:
+        """rk_npu_moe_quant_expert_blob_bytes: the size of one int4 expert's cache record (0: the bank has none)."""
+        return int(self.lib.rk_npu_moe_quant_expert_blob_bytes(self.handle))
+
+    def export_expert(self, expert: int, out: np.ndarray) -> int:
+        """rk_npu_moe_quant_export_expert into a uint8 array; returns the C return code."""
+        return self.lib.rk_npu_moe_quant_export_expert(self.handle, expert, _ptr(out), out.nbytes)
+
+    def import_expert(self, slot: int, record: np.ndarray, timings: MoeImportTimings | None = None, nbytes: int | None = None) -> int:
+        """rk_npu_moe_quant_import_expert[_timed] from a uint8 array; returns the C return code."""
+        size = record.nbytes if nbytes is None else nbytes
+        if timings is None:
+            return self.lib.rk_npu_moe_quant_import_expert(self.handle, slot, _ptr(record), size)
+        return self.lib.rk_npu_moe_quant_import_expert_timed(self.handle, slot, _ptr(record), size, C.byref(timings))
+
+    def swap_slot(self, slot: int, other: "MoeWeights", other_slot: int) -> int:
+        """rk_npu_moe_quant_swap_slots; returns the C return code."""
+        return self.lib.rk_npu_moe_quant_swap_slots(self.handle, slot, other.handle, other_slot)
 
     def free(self):
         if self.handle:

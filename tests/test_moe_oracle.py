@@ -139,7 +139,7 @@ def test_host_entry_points(lib):
     assert lib.rk_npu_moe_w8_run_f32(None, None, 1, None, None, None, None, None) == capi.RK_NPU_ERR_PARAM
     lib.rk_npu_moe_w8_weights_free(None)
     lib.rk_npu_moe_w8_workspace_free(None)
-    # the int4 expert forms validate like the int8 one; the slot banks and their cache records are exported and decline
+    # the int4 expert forms, the slot banks and their cache records validate their arguments like the int8 form
     for name in ("rk_npu_moe_quant_weights_create", "rk_npu_moe_quant_weights_create_full_k", "rk_npu_moe_w4_weights_create",
                  "rk_npu_moe_w4_slots_create"):
         assert not getattr(lib, name)(None, C.byref(c.weights), None)
