@@ -821,12 +821,25 @@ def _moe(rk, ctx, dom, dev, stream, oracle, dist, world, rank, peak):
     for _ in range(20):
         stage.import_expert(0, record)
     import_us = (time.perf_counter() - t0) / 20 * 1e6
+    from rknpu2_matmul_open_b200 import rmsnorm
+    locked = rmsnorm.Buffer(dom, record.nbytes)         # the same record kept in page-locked memory (rk_npu_mem_alloc)
+    pinned = locked.array(np.uint8)
+    pinned[:] = record
+    for _ in range(3):
+        ok = ok and stage.import_expert(0, pinned) == 0
+    t0 = time.perf_counter()
+    for _ in range(20):
+        stage.import_expert(0, pinned)
+    import_locked_us = (time.perf_counter() - t0) / 20 * 1e6
+    locked.free()
     t0 = time.perf_counter()
     for _ in range(200):
         hot.swap_slot(0, stage, 0)
     swap_us = (time.perf_counter() - t0) / 200 * 1e6
     ok = ok and stage.export_expert(0, back) == 0 and bool(np.array_equal(back, record))
     out_fig["int4_expert_record"] = {"MB": record.nbytes / 1e6, "import_us": import_us, "import_GBps": record.nbytes / (import_us * 1e-6) / 1e9,
+                                     "import_from_page_locked_us": import_locked_us,
+                                     "import_from_page_locked_GBps": record.nbytes / (import_locked_us * 1e-6) / 1e9,
                                      "swap_slots_us": swap_us, "round_trip_exact": ok}
     for h in (stage, hot, source):
         h.free()
