@@ -5,9 +5,13 @@
  * blocking run calls, the memory queries, the K-partition query), the load-only W8 tuning cache, the exact
  * int4 x int4 -> int32 operator of include/rk_npu_matmul_i4.h (with its producer callback) and the configuration
  * initialisers.
+ * The *_weights_create_compress constructors (include/rk_npu_quant_matmul.h:321-330,348-350,392-394: lossless
+ * compressed storage of the same B for the original device's hardware decompressor, same run and free functions, same
+ * results) make ordinary weight objects here: the codes are stored as they are, nothing is encoded and no memory is
+ * saved; rk_npu_f32i8f32_weights_compressed_layout_generation is 0 for them, as for every uncompressed object.
  * Exported but declined (RK_NPU_ERR_PARAM, NULL or 0, nothing else happens): the W8 search tuners, their family
- * forms and cache saving; compressed (DCOMP) weight storage, which encodes for the original device's hardware
- * decompressor; the DMA-buffer helpers of rk_npu_common.h.
+ * forms and cache saving; the *_create_from_f32_compress constructors, which search a quantisation under a size
+ * budget measured in the original device's compressed format.
  * Programs may include the original headers instead of this one; names, layouts and values are the same.
  */
 #ifndef RKNPU_B200_QUANT_H
@@ -162,6 +166,14 @@ int rk_npu_f16i8f16_run_static(rk_npu_matmul_workspace *workspace, const rk_npu_
 rk_npu_f32i8f32_weights *rk_npu_f32i8f32_weights_create(rk_npu_iommu_domain *domain, const rk_npu_matmul_weight_config *config,
                                                         const int8_t *B_rowmajor, const float *w_scale);
 void rk_npu_f32i8f32_weights_free(rk_npu_f32i8f32_weights *weights);
+/* The compressed-storage constructors: the same objects as the plain ones here (see the head of this file). */
+rk_npu_i8i8i32_weights *rk_npu_i8i8i32_weights_create_compress(rk_npu_iommu_domain *domain, const rk_npu_matmul_weight_config *config,
+                                                               const int8_t *B_rowmajor);
+rk_npu_f16i8f16_weights *rk_npu_f16i8f16_weights_create_compress(rk_npu_iommu_domain *domain, const rk_npu_matmul_weight_config *config,
+                                                                 const int8_t *B_rowmajor, const float *w_scale);
+rk_npu_f32i8f32_weights *rk_npu_f32i8f32_weights_create_compress(rk_npu_iommu_domain *domain, const rk_npu_matmul_weight_config *config,
+                                                                 const int8_t *B_rowmajor, const float *w_scale);
+uint64_t rk_npu_f32i8f32_weights_compressed_layout_generation(const rk_npu_f32i8f32_weights *weights);
 int rk_npu_f32i8f32_run_dynamic(rk_npu_matmul_workspace *workspace, const rk_npu_f32i8f32_weights *weights,
                                 const float *A_fp32_rowmajor, float *C_fp32_rowmajor);
 int rk_npu_f32i8f32_run_static(rk_npu_matmul_workspace *workspace, const rk_npu_f32i8f32_weights *weights,

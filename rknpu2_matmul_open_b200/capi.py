@@ -288,6 +288,10 @@ _SIGNATURES = {
     "rk_npu_f16i8f16_run_dynamic": (C.c_int, [_P, _P, _P, _P]),
     "rk_npu_f16i8f16_run_static": (C.c_int, [_P, _P, _P, _P, _P]),
     "rk_npu_f32i8f32_weights_create": (_P, [_P, C.POINTER(MatmulWeightConfig), _P, _P]),
+    "rk_npu_i8i8i32_weights_create_compress": (_P, [_P, C.POINTER(MatmulWeightConfig), _P]),
+    "rk_npu_f16i8f16_weights_create_compress": (_P, [_P, C.POINTER(MatmulWeightConfig), _P, _P]),
+    "rk_npu_f32i8f32_weights_create_compress": (_P, [_P, C.POINTER(MatmulWeightConfig), _P, _P]),
+    "rk_npu_f32i8f32_weights_compressed_layout_generation": (C.c_uint64, [_P]),
     "rk_npu_f32i8f32_weights_free": (None, [_P]),
     "rk_npu_f32i8f32_run_dynamic": (C.c_int, [_P, _P, _P, _P]),
     "rk_npu_f32i8f32_run_static": (C.c_int, [_P, _P, _P, _P, _P]),

@@ -1,6 +1,6 @@
 // w4a8_unbuilt.cpp -- entry points of the original project's public headers that this library
-// does not implement: the W8 search tuners, their family forms and cache saving, and compressed (DCOMP)
-// weight storage (include/rk_npu_quant_matmul.h).  They are
+// does not implement: the W8 search tuners, their family forms and cache saving, and the constructors that
+// quantise under a compressed-size budget (include/rk_npu_quant_matmul.h).  They are
 // exported so that programs written against those headers link and start; each one declines: RK_NPU_ERR_PARAM, NULL, or 0, and does nothing else.
 // C linkage carries no parameter types, so the definitions take none; the callers' arguments
 // are ignored.
@@ -27,13 +27,9 @@ RKB200_DECLINE_INT(rk_npu_matmul_autotune_cached)
 RKB200_DECLINE_INT(rk_npu_matmul_autotune_family_cached)
 
 // constructors: no object
-RKB200_DECLINE_PTR(rk_npu_f16i8f16_weights_create_compress)
 RKB200_DECLINE_PTR(rk_npu_f16i8f16_weights_create_from_f32_compress)
-RKB200_DECLINE_PTR(rk_npu_f32i8f32_weights_create_compress)
 RKB200_DECLINE_PTR(rk_npu_f32i8f32_weights_create_from_f32_compress)
-RKB200_DECLINE_PTR(rk_npu_i8i8i32_weights_create_compress)
 
 // destructors of objects that are never created, and setters without effect
 RKB200_DECLINE_VOID(rk_npu_iommu_domain_set_reclaim)
 
-RKB200_DECLINE_U64(rk_npu_f32i8f32_weights_compressed_layout_generation)

@@ -407,3 +407,23 @@ extern "C" int rk_npu_f32i8f32_run_static(rk_npu_matmul_workspace* ws, const rk_
 {
     return run(ws, w ? &w->w : nullptr, RK_NPU_MATMUL_F32I8F32_STATIC, A, a_scale, C);
 }
+
+// The original's *_weights_create_compress keep the same B in a lossless compressed form for its hardware decompressor
+// (include/rk_npu_quant_matmul.h:321-330): same run and free functions, same results.  Here the codes are stored as they
+// are -- HBM is not the scarce resource the original board's DRAM bandwidth is -- so these are the plain constructors.
+extern "C" rk_npu_i8i8i32_weights* rk_npu_i8i8i32_weights_create_compress(rk_npu_iommu_domain* d, const rk_npu_matmul_weight_config* c, const int8_t* B)
+{
+    return rk_npu_i8i8i32_weights_create(d, c, B);
+}
+extern "C" rk_npu_f16i8f16_weights* rk_npu_f16i8f16_weights_create_compress(rk_npu_iommu_domain* d, const rk_npu_matmul_weight_config* c,
+                                                                            const int8_t* B, const float* w_scale)
+{
+    return rk_npu_f16i8f16_weights_create(d, c, B, w_scale);
+}
+extern "C" rk_npu_f32i8f32_weights* rk_npu_f32i8f32_weights_create_compress(rk_npu_iommu_domain* d, const rk_npu_matmul_weight_config* c,
+                                                                            const int8_t* B, const float* w_scale)
+{
+    return rk_npu_f32i8f32_weights_create(d, c, B, w_scale);
+}
+// include/rk_npu_quant_matmul.h:395-399: raw weights and NULL return zero
+extern "C" uint64_t rk_npu_f32i8f32_weights_compressed_layout_generation(const rk_npu_f32i8f32_weights*) { return 0; }

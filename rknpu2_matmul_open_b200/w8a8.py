@@ -39,13 +39,15 @@ def default_strategy(kind: int, M: int, N: int, K: int, k_tile: int | None = Non
 class MatmulWeights:
     """rk_npu_<family>_weights_create / _free.  `family`: 'i8i8i32' (no scales), 'f16i8f16' or 'f32i8f32'."""
 
-    def __init__(self, domain, family: str, B: np.ndarray, w_scale: np.ndarray | None = None, k_tile: int | None = None):
+    def __init__(self, domain, family: str, B: np.ndarray, w_scale: np.ndarray | None = None, k_tile: int | None = None,
+                 compress: bool = False):
+        """compress: the *_weights_create_compress constructor (the same object in this library)."""
         self.lib = capi.load()
         self.family = family
         B = np.ascontiguousarray(B, np.int8)
         K, N = B.shape
         self.config = MatmulWeightConfig(K, N, k_tile or K)
-        create = getattr(self.lib, f"rk_npu_{family}_weights_create")
+        create = getattr(self.lib, f"rk_npu_{family}_weights_create" + ("_compress" if compress else ""))
         if family == "i8i8i32":
             self.handle = create(domain.handle, C.byref(self.config), _ptr(B))
         else:

@@ -86,6 +86,33 @@ def test_int8_activations_exact_sums(gpu, oracle, shape):
     w.free()
 
 
+def test_compressed_storage_constructors_give_the_plain_results(gpu, oracle):
+    # include/rk_npu_quant_matmul.h:321-330: lossless storage of the same B, same run and free functions, same results
+    _, dom, _ = gpu
+    M, K, N = 20, 640, 200
+    B, sw = w8_weights(K, N, seed=3)
+    for dtype, fam, kind in (("f16", "f16i8f16", w8a8.F16_DYNAMIC), ("f32", "f32i8f32", w8a8.F32_DYNAMIC)):
+        A = activations(M, K, seed=4, dtype=dtype)
+        w = w8a8.MatmulWeights(dom, fam, B, sw, compress=True)
+        ws = w8a8.MatmulWorkspace(dom, w8a8.default_strategy(kind, M, N, K))
+        out = np.zeros((M, N), np.uint16 if dtype == "f16" else np.float32)
+        assert ws.run_dynamic(w, A, out) == 0
+        assert np.array_equal(bits(out), bits(oracle.w8_linear(A, B, sw)["out"]))
+        if fam == "f32i8f32":
+            assert capi.load().rk_npu_f32i8f32_weights_compressed_layout_generation(w.handle) == 0      # stored uncompressed here
+        ws.free(); w.free()
+    rng = np.random.default_rng(6)
+    A8 = rng.integers(-128, 128, size=(M, K), dtype=np.int8)
+    w = w8a8.MatmulWeights(dom, "i8i8i32", B, compress=True)
+    ws = w8a8.MatmulWorkspace(dom, w8a8.default_strategy(w8a8.I8I8I32, M, N, K))
+    acc = np.zeros((M, N), np.int32)
+    assert ws.run_i8(w, A8, acc) == 0
+    assert np.array_equal(acc, A8.astype(np.int32) @ B.astype(np.int32))
+    ws.free(); w.free()
+    with pytest.raises(rk.W4A8Error):
+        w8a8.MatmulWeights(dom, "f16i8f16", B, np.zeros(N, np.float32), compress=True)       # the same validation
+
+
 def test_sums_wrap_modulo_2_32(gpu):
     # include/rk_npu_quant_matmul.h:335-340.  (-128) x (-128) x 131072 = 2^31 wraps to INT32_MIN.
     _, dom, _ = gpu

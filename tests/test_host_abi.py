@@ -339,10 +339,14 @@ def test_every_entry_point_of_the_original_headers_links(lib):
         fn = C.CDLL(str(capi.LIB_PATH))[name]
         fn.restype, fn.argtypes = C.c_int, []
         assert fn() == capi.RK_NPU_ERR_PARAM, name
-    for name in ("rk_npu_i8i8i32_weights_create_compress", "rk_npu_f16i8f16_weights_create_from_f32_compress"):
+    for name in ("rk_npu_f32i8f32_weights_create_from_f32_compress", "rk_npu_f16i8f16_weights_create_from_f32_compress"):
         fn = C.CDLL(str(capi.LIB_PATH))[name]
         fn.restype, fn.argtypes = C.c_void_p, []
         assert fn() is None, name
+    # the compressed-storage constructors are the plain ones here: argument errors are answered alike
+    assert lib.rk_npu_i8i8i32_weights_create_compress(None, None, None) is None
+    assert lib.rk_npu_f16i8f16_weights_create_compress(None, None, None, None) is None
+    assert lib.rk_npu_f32i8f32_weights_compressed_layout_generation(None) == 0
     # the typed W8A8 operators are built: argument errors are answered as such, without a device
     assert lib.rk_npu_i8i8i32_run(None, None, None, None) == capi.RK_NPU_ERR_PARAM
     assert lib.rk_npu_f16i8f16_run_static(None, None, None, None, None) == capi.RK_NPU_ERR_PARAM
