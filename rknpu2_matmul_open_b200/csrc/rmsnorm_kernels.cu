@@ -29,7 +29,7 @@ namespace {
 
 constexpr int RN_THREADS = 512;
 constexpr int RN_BATCH = 4;     // chunks of each input a thread requests before it uses the first
-constexpr int RN_CTAS = 2;      // CTAs per SM the register budget is set for
+constexpr int RN_CTAS = 2;      // CTAs per SM the register allocation is bounded for
 constexpr int RN_MAX_DEVICES = 64;
 constexpr int RN_SMEM_SUMS = 64 * 1024;   // most bytes of sums one CTA keeps: TM * ceil(D/8/CS) * 16
 

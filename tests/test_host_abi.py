@@ -55,7 +55,8 @@ def test_struct_layouts_and_constants_equal_the_original_headers():
     ours = abi.layout(ROOT / "include", abi.OURS)
     golden = (ROOT / "tests" / "golden" / "reference_abi_layout.txt").read_text()
     assert ours == golden
-    reference = Path(os.environ.get("REF", "/root/reference")) / "include"      # oracle/Makefile's REF
+    default = re.search(r"^REF\s*\?=\s*(\S+)", (ROOT / "oracle" / "Makefile").read_text(), flags=re.M).group(1)
+    reference = Path(os.environ.get("REF", default)) / "include"      # where oracle/Makefile looks for the original tree
     if reference.is_dir():           # where the original tree is at hand, the golden file itself is re-derived
         assert abi.layout(reference, abi.THEIRS) == golden
         assert abi.functions(reference, abi.THEIRS) == (ROOT / "tests" / "golden" / "reference_header_symbols.txt").read_text().split()
