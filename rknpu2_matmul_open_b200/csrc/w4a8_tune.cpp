@@ -866,9 +866,9 @@ bool w8_record_ok(const rk_npu_matmul_strategy& s, const W8Key& key)
         !(m == 1u || m == 2u || m == 4u || m == 3u || m == 7u) || s.cpu_core_mask == 0 || s.cpu_threads <= 0 ||
         s.cpu_threads != __builtin_popcountll(s.cpu_core_mask) || (s.cpu_core_mask & ~affinity_mask()))
         return false;
-    // Panel recipes are checked by the original against its device plan; they have no meaning
-    // here and their rules are not restated: such a record is treated as not usable.
-    if (s.a_layout >= RK_NPU_MATMUL_A_LAYOUT_PANEL8 || s.c_layout != RK_NPU_MATMUL_C_LAYOUT_NATIVE) return false;
+    // Panel recipes describe the original device's buffers and change nothing here, but a record is a hit only where
+    // the original would accept it.
+    if (!rkb200::w8_panel_recipe_ok(s.M, s.N, s.k_tile, int(s.a_layout), int(s.c_layout))) return false;
     const int align_n = std::max(W8_CHANNEL_TILE, rkb200::align_up(s.N, W8_CHANNEL_TILE));
     const int nt = std::min(align_n, rkb200::align_up(s.n_tile, W8_CHANNEL_TILE));
     if ((align_n + nt - 1) / nt < __builtin_popcount(m)) return false;
@@ -881,6 +881,20 @@ bool w8_record_ok(const rk_npu_matmul_strategy& s, const W8Key& key)
     return true;
 }
 } // namespace
+
+bool w8_panel_recipe_ok(int M, int N, int k_tile, int a_layout, int c_layout)
+{
+    const int a_width = a_layout == RK_NPU_MATMUL_A_LAYOUT_PANEL8 ? 8 : a_layout == RK_NPU_MATMUL_A_LAYOUT_PANEL16 ? 16 : 0;
+    const int c_width = c_layout == RK_NPU_MATMUL_C_LAYOUT_PANEL8 ? 8 : c_layout == RK_NPU_MATMUL_C_LAYOUT_PANEL16 ? 16 : 0;
+    if (a_width && c_width && c_width != a_width) return false;                 // a panel input writes a native output or panels of its own width
+    if (!a_width && c_width && !(a_layout == RK_NPU_MATMUL_A_LAYOUT_NORMAL && c_width == 8)) return false;
+    const int width = std::max(a_width, c_width);
+    if (!width) return true;
+    // every K wave is checked by the original; the widest is k_tile and every bound falls with K
+    if (M % width || k_tile > 8192 || (a_width == 8 && k_tile > 2048) || (a_width == 16 && k_tile > 4096)) return false;
+    if (c_width && int64_t(rkb200::align_up(N, 32) / 4 - 1) * c_width > 8191) return false;
+    return true;
+}
 } // namespace rkb200
 
 extern "C" void rk_npu_matmul_autotune_config_init(rk_npu_matmul_autotune_config* c, int M, int N, int K)

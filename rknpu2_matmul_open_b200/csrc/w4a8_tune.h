@@ -69,6 +69,12 @@ void schedule_into(const Schedule& s, rk_npu_w4a8_config& config);
 // Families that can run `M` tokens with reduction length `K` (the candidate set of the search tuner).
 std::vector<Schedule> schedule_candidates(int M, int N, int K, int sm_count);
 
+// W8 strategies that name a panel layout (a_layout PANEL8 / PANEL16, or c_layout other than NATIVE) are accepted by
+// the original only when its device plan can be built for them.  Those rules (src/rk_npu_matmul_i8.cpp:65-92, reached
+// through src/rk_npu_kn_plan.cpp:43-70 from src/rk_npu_quant_matmul.cpp:167-177) restated on the strategy's own fields;
+// the layouts are the integer values of rk_npu_matmul_a_layout / rk_npu_matmul_c_layout.  True for non-panel recipes.
+bool w8_panel_recipe_ok(int M, int N, int k_tile, int a_layout, int c_layout);
+
 // Workspace creation with an explicit schedule (w4a8_abi.cpp).
 rk_npu_w4a8_workspace* create_workspace_scheduled(rk_npu_iommu_domain* domain, const rk_npu_w4a8_config* cfg,
                                                   const rk_npu_w4a8_options* options, const Schedule& schedule);

@@ -69,8 +69,8 @@ bool valid_weight_config(const rk_npu_matmul_weight_config* c)   // src/rk_npu_q
     return c && c->K > 0 && c->N > 0 && c->k_tile > 0 && c->k_tile <= c->K;
 }
 bool op_kind_ok(int kind) { return kind >= RK_NPU_MATMUL_I8I8I32 && kind <= RK_NPU_MATMUL_F32I8F32_STATIC; }
-// src/rk_npu_quant_matmul.cpp:153-181.  Panel recipes are additionally checked by the original against its device
-// plan; that geometry means nothing here, so a panel value in range passes.
+// src/rk_npu_quant_matmul.cpp:153-181.  Panel recipes change nothing here (they describe the original device's
+// buffers) but are valid only where the original's device plan accepts them.
 bool valid_strategy(const rk_npu_matmul_strategy* s)
 {
     if (!s || !op_kind_ok(int(s->op_kind)) || s->M <= 0 || s->N <= 0 || s->K <= 0 || s->k_tile <= 0 || s->k_tile > s->K ||
@@ -82,6 +82,7 @@ bool valid_strategy(const rk_npu_matmul_strategy* s)
     if (!(m == 1u || m == 2u || m == 4u || m == 3u || m == 7u) || s->cpu_core_mask == 0 || s->cpu_threads <= 0 ||
         s->cpu_threads != __builtin_popcountll(s->cpu_core_mask) || (s->cpu_core_mask & ~process_cpu_mask()))
         return false;
+    if (!w8_panel_recipe_ok(s->M, s->N, s->k_tile, int(s->a_layout), int(s->c_layout))) return false;
     const int align_n = std::max(W8_CHANNEL_TILE, align_up(s->N, W8_CHANNEL_TILE));
     const int nt = std::min(align_n, align_up(s->n_tile, W8_CHANNEL_TILE));
     return (align_n + nt - 1) / nt >= __builtin_popcount(m);

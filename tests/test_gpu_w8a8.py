@@ -113,6 +113,30 @@ def test_compressed_storage_constructors_give_the_plain_results(gpu, oracle):
         w8a8.MatmulWeights(dom, "f16i8f16", B, np.zeros(N, np.float32), compress=True)       # the same validation
 
 
+def test_panel_recipes_run_like_any_other_and_invalid_ones_are_refused(gpu, oracle):
+    # src/rk_npu_quant_matmul.cpp:167-177: a strategy that names panel layouts is valid where the original's device
+    # plan takes it; the layouts describe that device's buffers, the results are the same
+    _, dom, _ = gpu
+    M, K, N = 48, 512, 200
+    B, sw = w8_weights(K, N, seed=9)
+    A = activations(M, K, seed=9, dtype="f16")
+    w = w8a8.MatmulWeights(dom, "f16i8f16", B, sw)
+    want = oracle.w8_linear(A, B, sw)["out"]
+    for a_layout, c_layout in ((2, 0), (3, 0), (2, 1), (3, 2), (0, 1)):
+        st = w8a8.default_strategy(w8a8.F16_DYNAMIC, M, N, K)
+        st.a_layout, st.c_layout = a_layout, c_layout
+        ws = w8a8.MatmulWorkspace(dom, st)
+        out = np.zeros((M, N), np.uint16)
+        assert ws.run_dynamic(w, A, out) == 0 and np.array_equal(out, want)
+        ws.free()
+    for rows, a_layout, c_layout in ((48, 2, 2), (48, 1, 1), (48, 0, 2), (44, 3, 0), (44, 2, 1)):
+        st = w8a8.default_strategy(w8a8.F16_DYNAMIC, rows, N, K)
+        st.a_layout, st.c_layout = a_layout, c_layout
+        with pytest.raises(rk.W4A8Error):
+            w8a8.MatmulWorkspace(dom, st)
+    w.free()
+
+
 def test_sums_wrap_modulo_2_32(gpu):
     # include/rk_npu_quant_matmul.h:335-340.  (-128) x (-128) x 131072 = 2^31 wraps to INT32_MIN.
     _, dom, _ = gpu

@@ -392,6 +392,12 @@ def _w8_file(path, key, fastest, stable, magic="rk_npu_matmul_tuning_cache_v2"):
                           + record("stable", stable) + "\n")
 
 
+def _w8_record(s):
+    """A MatmulStrategy as the list of values _w8_file writes."""
+    return [s.op_kind, s.M, s.N, s.K, s.k_tile, s.n_tile, s.a_layout, s.c_layout, s.wave_count, s.n_groups, s.npu_core_mask,
+            s.cpu_core_mask, s.cpu_threads, s.input_us, s.npu_us, s.sync_us, s.output_us, s.total_us, s.jitter_pct, s.robust_us]
+
+
 def test_w8_load_only_cache(lib, tmp_path, monkeypatch):
     import os
     monkeypatch.delenv("RK_NPU_I8_NPU_REDUCE", raising=False)
@@ -445,12 +451,20 @@ def test_w8_load_only_cache(lib, tmp_path, monkeypatch):
         assert load() == capi.RK_NPU_ERR_CACHE_MISS
     _w8_file(path, key, rec, rec, magic="rk_npu_matmul_tuning_cache_v1")
     assert load() == capi.RK_NPU_ERR_CACHE_MISS
-    for index, value in ((4, 20000), (5, 1400), (5, 3104), (8, 7), (9, 2), (10, 5), (12, 2), (6, 2), (7, 1), (17, -1.0),
-                         (15, float("nan"))):
+    for index, value in ((4, 20000), (5, 1400), (5, 3104), (8, 7), (9, 2), (10, 5), (12, 2), (7, 2), (7, 1), (17, -1.0),
+                         (15, float("nan"))):     # (7, 1), (7, 2): panels of C need a normal or a panel A, this record's is native
         r2 = list(rec)
         r2[index] = value
         _w8_file(path, key, rec, r2)
         assert load() == capi.RK_NPU_ERR_CACHE_MISS, (index, value)
+    # panel recipes are hits where the original's device plan takes them: 8-row panels of A (128 rows, K tile 1376)
+    r2 = list(rec)
+    r2[6] = 2
+    _w8_file(path, key, rec, r2)
+    assert load() == 0 and s.a_layout == 2
+    r2[6], r2[7] = 0, 1                                  # a normal A with 8-row panels of C
+    _w8_file(path, key, rec, r2)
+    assert load() == 0 and (s.a_layout, s.c_layout) == (0, 1)
     _w8_file(path, key, rec, rec)
     Path(path).write_text(Path(path).read_text() + "junk\n")
     assert load() == capi.RK_NPU_ERR_CACHE_MISS          # trailing bytes
@@ -460,8 +474,10 @@ def test_w8_load_only_cache(lib, tmp_path, monkeypatch):
 def test_w8_cache_files_written_by_the_reference_load_here(lib, reference, tmp_path, monkeypatch):
     """Files written by the reference's own W8 cache writer (src/rk_npu_quant_matmul.cpp:337-349, compiled into the
     reference checker) are hits for this library's loader with identical records, and misses for every other key.
-    Records that name a panel layout are accepted by the reference after a check against its device plan; here they
-    are a documented miss."""
+    Records that name a panel layout are accepted by the reference after a check against its device plan
+    (src/rk_npu_quant_matmul.cpp:167-177); this library restates that check, and the two sides agree on every
+    combination of layouts over a grid of shapes: what the reference's writer refuses or its loader misses, this
+    loader misses, and what it accepts is a hit with the same record."""
     import os
     ref = reference.lib
     if not hasattr(ref, "rk_npu_matmul_autotune_cache_save"):
@@ -495,6 +511,43 @@ def test_w8_cache_files_written_by_the_reference_load_here(lib, reference, tmp_p
         c2.loops += 1
         assert lib.rk_npu_matmul_autotune_cache_load(ctx, path, kind, C.byref(c2), C.byref(f), C.byref(st)) == capi.RK_NPU_ERR_CACHE_MISS
         assert ref.rk_npu_matmul_autotune_cache_load(fake, path, kind, C.byref(c2), C.byref(f2), C.byref(st2)) == capi.RK_NPU_ERR_CACHE_MISS
+
+    # panel recipes: every (a_layout, c_layout) pair over shapes on both sides of each bound
+    accepted = refused = 0
+    kind = 1
+    shapes = [(128, 4096, 4096, 1024), (128, 4096, 4096, 2048), (128, 4096, 4096, 2080), (128, 4096, 8192, 4096), (128, 4096, 8320, 4128),
+              (128, 4096, 16384, 8192), (128, 4096, 16640, 8224), (12, 256, 512, 512), (24, 256, 512, 256), (48, 4096, 1024, 1024),
+              (64, 32768, 256, 256), (64, 65568, 256, 256), (64, 16416, 256, 256), (7, 64, 64, 64), (16, 131072, 64, 64)]
+    for M, N, K, kt in shapes:
+        for a_layout in range(4):
+            for c_layout in range(3):
+                c = capi.MatmulAutotuneConfig()
+                lib.rk_npu_matmul_autotune_config_init(C.byref(c), M, N, K)
+                s = capi.MatmulStrategy()
+                nt = min(2048, max(32, -(-N // 32) * 32))
+                s.op_kind, s.M, s.N, s.K, s.k_tile, s.n_tile = kind, M, N, K, kt, nt
+                s.a_layout, s.c_layout = a_layout, c_layout
+                s.wave_count = -(-K // kt)
+                s.n_groups = -(-max(32, -(-N // 32) * 32) // nt)
+                s.npu_core_mask, s.cpu_core_mask, s.cpu_threads = 1, one_cpu, 1
+                s.input_us, s.npu_us, s.sync_us, s.output_us, s.total_us, s.jitter_pct, s.robust_us = 1.5, 20.25, 3.0, 4.0, 30.0, 2.0, 31.0
+                plain = capi.MatmulStrategy.from_buffer_copy(s)
+                plain.a_layout, plain.c_layout = 1, 0
+                path = str(tmp_path / f"panel_{M}_{N}_{K}_{kt}_{a_layout}_{c_layout}.tune").encode()
+                saved = ref.rk_npu_matmul_autotune_cache_save(fake, path, kind, C.byref(c), C.byref(plain), C.byref(s))
+                f, st, f2, st2 = (capi.MatmulStrategy() for _ in range(4))
+                theirs = ref.rk_npu_matmul_autotune_cache_load(fake, path, kind, C.byref(c), C.byref(f2), C.byref(st2)) if saved == 0 else saved
+                if saved != 0:      # the writer refuses the recipe: the same file written by hand must be a miss here too
+                    key = [2, 6, 0x908, kind, M, N, K, c.allowed_npu_core_mask, affinity, c.warmup, c.loops, c.repeats, c.timeout_ms, 0]
+                    _w8_file(path.decode(), key, _w8_record(plain), _w8_record(s))
+                ours = lib.rk_npu_matmul_autotune_cache_load(ctx, path, kind, C.byref(c), C.byref(f), C.byref(st))
+                assert (ours == 0) == (theirs == 0), (M, N, K, kt, a_layout, c_layout, ours, theirs)
+                if ours == 0:
+                    accepted += 1
+                    assert _fields(st) == _fields(s) == _fields(st2)
+                else:
+                    refused += 1
+    assert accepted >= 40 and refused >= 60, (accepted, refused)
     lib.rk_npu_close(ctx)
 
 
