@@ -2,15 +2,15 @@
  * library implements it, plus the configuration initialiser of include/rk_npu_matmul_i4.h.
  *
  * Built: the typed W8A8 operators with raw int8 weights (weight objects, workspaces made from a strategy, the
- * blocking run calls, the memory queries, the K-partition query), the load-only W8 tuning cache, the exact
+ * blocking run calls, the memory queries, the K-partition query), the W8 tuning cache files (load and save), the exact
  * int4 x int4 -> int32 operator of include/rk_npu_matmul_i4.h (with its producer callback) and the configuration
  * initialisers.
  * The *_weights_create_compress constructors (include/rk_npu_quant_matmul.h:321-330,348-350,392-394: lossless
  * compressed storage of the same B for the original device's hardware decompressor, same run and free functions, same
  * results) make ordinary weight objects here: the codes are stored as they are, nothing is encoded and no memory is
  * saved; rk_npu_f32i8f32_weights_compressed_layout_generation is 0 for them, as for every uncompressed object.
- * Exported but declined (RK_NPU_ERR_PARAM, NULL or 0, nothing else happens): the W8 search tuners, their family
- * forms and cache saving; the *_create_from_f32_compress constructors, which search a quantisation under a size
+ * Exported but declined (RK_NPU_ERR_PARAM, NULL or 0, nothing else happens): the W8 search tuners and their family
+ * forms; the *_create_from_f32_compress constructors, which search a quantisation under a size
  * budget measured in the original device's compressed format.
  * Programs may include the original headers instead of this one; names, layouts and values are the same.
  */
@@ -84,16 +84,21 @@ typedef struct rk_npu_matmul_strategy {
 void rk_npu_matmul_autotune_config_init(rk_npu_matmul_autotune_config *cfg, int M, int N, int K);
 void rk_npu_matmul_family_autotune_config_init(rk_npu_matmul_family_autotune_config *cfg, int N, int K, int m_count,
                                                const int *m_values);
-/* Load-only W8 tuning cache (src/rk_npu_quant_matmul.cpp:183-349,1552-1563): reads one cache
- * file written by the original tuner, checks magic, key (format 2, tuning revision 6 with the
- * execution mode in its upper half, driver version of ctx, operator, shape, permission masks
- * intersected with the process affinity, measurement settings, required K tile) and both
- * records, and returns them.  RK_NPU_ERR_CACHE_MISS for an absent, malformed, stale or
- * foreign file -- and for records that name a panel layout, whose device-specific geometry
- * rules are not restated here; RK_NPU_ERR_PARAM for bad arguments. */
+/* W8 tuning cache files (src/rk_npu_quant_matmul.cpp:183-349,1552-1579), the original's format byte for byte in both
+ * directions.  load reads one file, checks magic, key (format 2, tuning revision 6 with the execution mode in its
+ * upper half, driver version of ctx, operator, shape, permission masks intersected with the process affinity,
+ * measurement settings, required K tile) and both records, and returns them: RK_NPU_ERR_CACHE_MISS for an absent,
+ * malformed, stale or foreign file or a record the original would not accept (records that name panel layouts are
+ * checked by the original's device-plan rule); RK_NPU_ERR_PARAM for bad arguments.  save checks the two strategies
+ * against the same key and rules (RK_NPU_ERR_PARAM) and writes the file under a temporary name, renamed over the target
+ * when complete (RK_NPU_ERR_IO).  The search that would fill such a file on this library is not built: the strategies
+ * come from the caller (for instance from a file made on the original board). */
 int rk_npu_matmul_autotune_cache_load(rk_npu_ctx *ctx, const char *cache_path, rk_npu_matmul_op_kind kind,
                                       const rk_npu_matmul_autotune_config *cfg, rk_npu_matmul_strategy *fastest,
                                       rk_npu_matmul_strategy *stable);
+int rk_npu_matmul_autotune_cache_save(rk_npu_ctx *ctx, const char *cache_path, rk_npu_matmul_op_kind kind,
+                                      const rk_npu_matmul_autotune_config *cfg, const rk_npu_matmul_strategy *fastest,
+                                      const rk_npu_matmul_strategy *stable);
 
 /* ---------------------------------------------------------------- typed W8A8 operators
  * include/rk_npu_quant_matmul.h:94-99,149-176,186-188,296-421.  int8 B[K,N] (symmetric, zero point 0) with one

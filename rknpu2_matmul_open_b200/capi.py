@@ -262,6 +262,8 @@ _SIGNATURES = {
                                                          C.POINTER(C.c_int)]),
     "rk_npu_matmul_autotune_cache_load": (C.c_int, [_P, C.c_char_p, C.c_int, C.POINTER(MatmulAutotuneConfig),
                                                     C.POINTER(MatmulStrategy), C.POINTER(MatmulStrategy)]),
+    "rk_npu_matmul_autotune_cache_save": (C.c_int, [_P, C.c_char_p, C.c_int, C.POINTER(MatmulAutotuneConfig),
+                                                    C.POINTER(MatmulStrategy), C.POINTER(MatmulStrategy)]),
     "rk_npu_i4_config_init": (None, [C.POINTER(I4Config), C.c_int, C.c_int, C.c_int]),
     # exact int4 x int4 -> int32 operator
     "rk_npu_i4_memory_query": (C.c_int, [C.POINTER(I4Config), C.POINTER(I4MemoryInfo)]),

@@ -547,7 +547,12 @@ int cache_read(const std::string& path, const std::string& key, const rk_npu_w4a
 
 // The file appears under its final name only complete: it is written next to it under a name no other
 // writer uses (O_EXCL), flushed to the device, and renamed over the target.
+int write_file_whole(const std::string& path, const std::string& text);
 int cache_write(const std::string& path, const std::string& key, const Strategy& fastest, const Strategy& stable)
+{
+    return write_file_whole(path, std::string(CACHE_MAGIC) + "\n" + key + "\n" + record_text("fastest", fastest) + record_text("stable", stable));
+}
+int write_file_whole(const std::string& path, const std::string& text)
 {
     namespace fs = std::filesystem;
     if (path.empty()) return RK_NPU_ERR_IO;
@@ -557,7 +562,6 @@ int cache_write(const std::string& path, const std::string& key, const Strategy&
         fs::create_directories(target.parent_path(), ec);
         if (ec && !fs::is_directory(target.parent_path())) return RK_NPU_ERR_IO;
     }
-    const std::string text = std::string(CACHE_MAGIC) + "\n" + key + "\n" + record_text("fastest", fastest) + record_text("stable", stable);
     static std::atomic<unsigned> attempt{0};
     std::string scratch;
     int fd = -1;
@@ -944,6 +948,34 @@ extern "C" int rk_npu_matmul_autotune_cache_load(rk_npu_ctx* ctx, const char* pa
         *fastest = f;
         *stable = s;
         return RK_NPU_OK;
+    } catch (...) { return RK_NPU_ERR_PARAM; }
+}
+// src/rk_npu_quant_matmul.cpp:1565-1579 (checks), :266-277,336-349 (text): the same bytes the original writes.
+extern "C" int rk_npu_matmul_autotune_cache_save(rk_npu_ctx* ctx, const char* path, rk_npu_matmul_op_kind kind,
+                                                 const rk_npu_matmul_autotune_config* cfg, const rk_npu_matmul_strategy* fastest,
+                                                 const rk_npu_matmul_strategy* stable)
+{
+    using namespace rkb200;
+    try {
+        if (!path || !*path || !fastest || !stable) return RK_NPU_ERR_PARAM;
+        W8Key key;
+        if (!w8_make_key(ctx, cfg, int(kind), key) || !w8_record_ok(*fastest, key) || !w8_record_ok(*stable, key)) return RK_NPU_ERR_PARAM;
+        std::ostringstream out;
+        out.imbue(std::locale::classic());
+        out << W8_CACHE_MAGIC << '\n'
+            << "key " << key.format << ' ' << key.revision << ' ' << key.driver << ' ' << key.op << ' ' << key.M << ' ' << key.N << ' '
+            << key.K << ' ' << key.npu << ' ' << key.cpu << ' ' << key.warmup << ' ' << key.loops << ' ' << key.repeats << ' '
+            << key.timeout_ms << ' ' << key.required_k_tile << '\n';
+        auto record = [&](const char* label, const rk_npu_matmul_strategy& s) {
+            out << label << ' ' << int(s.op_kind) << ' ' << s.M << ' ' << s.N << ' ' << s.K << ' ' << s.k_tile << ' ' << s.n_tile << ' '
+                << int(s.a_layout) << ' ' << int(s.c_layout) << ' ' << s.wave_count << ' ' << s.n_groups << ' ' << s.npu_core_mask << ' '
+                << s.cpu_core_mask << ' ' << s.cpu_threads;
+            for (double v : {s.input_us, s.npu_us, s.sync_us, s.output_us, s.total_us, s.jitter_pct, s.robust_us}) out << ' ' << double_bits(v);
+            out << '\n';
+        };
+        record("fastest", *fastest);
+        record("stable", *stable);
+        return write_file_whole(path, out.str());
     } catch (...) { return RK_NPU_ERR_PARAM; }
 }
 extern "C" void rk_npu_i4_config_init(rk_npu_i4_config* c, int M, int N, int K)

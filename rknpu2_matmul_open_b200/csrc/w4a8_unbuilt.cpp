@@ -1,5 +1,5 @@
 // w4a8_unbuilt.cpp -- entry points of the original project's public headers that this library
-// does not implement: the W8 search tuners, their family forms and cache saving, and the constructors that
+// does not implement: the W8 search tuners and their family forms, and the constructors that
 // quantise under a compressed-size budget (include/rk_npu_quant_matmul.h).  They are
 // exported so that programs written against those headers link and start; each one declines: RK_NPU_ERR_PARAM, NULL, or 0, and does nothing else.
 // C linkage carries no parameter types, so the definitions take none; the callers' arguments
@@ -22,7 +22,6 @@ RKB200_DECLINE_INT(rk_npu_f32i8f32_static_autotune)
 RKB200_DECLINE_INT(rk_npu_f32i8f32_static_autotune_family)
 RKB200_DECLINE_INT(rk_npu_i8i8i32_autotune)
 RKB200_DECLINE_INT(rk_npu_i8i8i32_autotune_family)
-RKB200_DECLINE_INT(rk_npu_matmul_autotune_cache_save)
 RKB200_DECLINE_INT(rk_npu_matmul_autotune_cached)
 RKB200_DECLINE_INT(rk_npu_matmul_autotune_family_cached)
 

@@ -336,7 +336,7 @@ def test_every_entry_point_of_the_original_headers_links(lib):
     assert not missing, missing
     # operators that are not built decline instead of pretending
     for name in ("rk_npu_i8i8i32_autotune", "rk_npu_f16i8f16_dynamic_autotune_family",
-                 "rk_npu_matmul_autotune_cache_save", "rk_npu_matmul_autotune_cached"):
+                 "rk_npu_matmul_autotune_family_cached", "rk_npu_matmul_autotune_cached"):
         fn = C.CDLL(str(capi.LIB_PATH))[name]
         fn.restype, fn.argtypes = C.c_int, []
         assert fn() == capi.RK_NPU_ERR_PARAM, name
@@ -398,7 +398,7 @@ def _w8_record(s):
             s.cpu_core_mask, s.cpu_threads, s.input_us, s.npu_us, s.sync_us, s.output_us, s.total_us, s.jitter_pct, s.robust_us]
 
 
-def test_w8_load_only_cache(lib, tmp_path, monkeypatch):
+def test_w8_cache_load_and_save(lib, tmp_path, monkeypatch):
     import os
     monkeypatch.delenv("RK_NPU_I8_NPU_REDUCE", raising=False)
     monkeypatch.delenv("RK_NPU_W8A8_NPU_DEQUANT", raising=False)
@@ -465,6 +465,26 @@ def test_w8_load_only_cache(lib, tmp_path, monkeypatch):
     r2[6], r2[7] = 0, 1                                  # a normal A with 8-row panels of C
     _w8_file(path, key, rec, r2)
     assert load() == 0 and (s.a_layout, s.c_layout) == (0, 1)
+    # save: what was loaded goes back out as the same text; arguments and records are checked first
+    _w8_file(path, key, rec, rec)
+    assert load() == 0
+    out_path = str(tmp_path / "saved.tune").encode()
+    assert lib.rk_npu_matmul_autotune_cache_save(ctx, out_path, kind, C.byref(c), C.byref(f), C.byref(s)) == 0
+    assert Path(out_path.decode()).read_text() == Path(path).read_text()
+    assert lib.rk_npu_matmul_autotune_cache_save(ctx, b"", kind, C.byref(c), C.byref(f), C.byref(s)) == capi.RK_NPU_ERR_PARAM
+    assert lib.rk_npu_matmul_autotune_cache_save(ctx, None, kind, C.byref(c), C.byref(f), C.byref(s)) == capi.RK_NPU_ERR_PARAM
+    assert lib.rk_npu_matmul_autotune_cache_save(None, out_path, kind, C.byref(c), C.byref(f), C.byref(s)) == capi.RK_NPU_ERR_PARAM
+    assert lib.rk_npu_matmul_autotune_cache_save(ctx, out_path, kind, C.byref(c), None, C.byref(s)) == capi.RK_NPU_ERR_PARAM
+    assert lib.rk_npu_matmul_autotune_cache_save(ctx, out_path, 2, C.byref(c), C.byref(f), C.byref(s)) == capi.RK_NPU_ERR_PARAM      # another operator
+    wrong = capi.MatmulStrategy.from_buffer_copy(f)
+    wrong.wave_count += 1
+    assert lib.rk_npu_matmul_autotune_cache_save(ctx, out_path, kind, C.byref(c), C.byref(wrong), C.byref(s)) == capi.RK_NPU_ERR_PARAM
+    wrong = capi.MatmulStrategy.from_buffer_copy(f)
+    wrong.total_us = float("nan")
+    assert lib.rk_npu_matmul_autotune_cache_save(ctx, out_path, kind, C.byref(c), C.byref(f), C.byref(wrong)) == capi.RK_NPU_ERR_PARAM
+    blocked = tmp_path / "file_not_dir"
+    blocked.write_text("x")
+    assert lib.rk_npu_matmul_autotune_cache_save(ctx, str(blocked / "a.tune").encode(), kind, C.byref(c), C.byref(f), C.byref(s)) == capi.RK_NPU_ERR_IO
     _w8_file(path, key, rec, rec)
     Path(path).write_text(Path(path).read_text() + "junk\n")
     assert load() == capi.RK_NPU_ERR_CACHE_MISS          # trailing bytes
@@ -502,7 +522,12 @@ def test_w8_cache_files_written_by_the_reference_load_here(lib, reference, tmp_p
         s.input_us, s.npu_us, s.sync_us, s.output_us, s.total_us, s.jitter_pct, s.robust_us = 1.5, 20.25, 3.0, 4.0, 30.0, 2.0, 31.0
         path = str(tmp_path / f"ref_w8_{kind}.tune").encode()
         assert ref.rk_npu_matmul_autotune_cache_save(fake, path, kind, C.byref(c), C.byref(s), C.byref(s)) == 0
+        mine = str(tmp_path / "deep" / "er" / f"mine_w8_{kind}.tune").encode()       # missing directories are made
+        assert lib.rk_npu_matmul_autotune_cache_save(ctx, mine, kind, C.byref(c), C.byref(s), C.byref(s)) == 0
+        assert Path(mine.decode()).read_bytes() == Path(path.decode()).read_bytes()    # the same bytes as the reference's writer
+        assert not [x.name for x in Path(mine.decode()).parent.iterdir() if not x.name.endswith(".tune")]     # no scratch file left
         f, st = capi.MatmulStrategy(), capi.MatmulStrategy()
+        assert ref.rk_npu_matmul_autotune_cache_load(fake, mine, kind, C.byref(c), C.byref(f), C.byref(st)) == 0 and _fields(f) == _fields(s)
         assert lib.rk_npu_matmul_autotune_cache_load(ctx, path, kind, C.byref(c), C.byref(f), C.byref(st)) == 0
         assert _fields(f) == _fields(s) and _fields(st) == _fields(s)
         f2, st2 = capi.MatmulStrategy(), capi.MatmulStrategy()
@@ -535,6 +560,12 @@ def test_w8_cache_files_written_by_the_reference_load_here(lib, reference, tmp_p
                 plain.a_layout, plain.c_layout = 1, 0
                 path = str(tmp_path / f"panel_{M}_{N}_{K}_{kt}_{a_layout}_{c_layout}.tune").encode()
                 saved = ref.rk_npu_matmul_autotune_cache_save(fake, path, kind, C.byref(c), C.byref(plain), C.byref(s))
+                mine = path + b".mine"
+                assert lib.rk_npu_matmul_autotune_cache_save(ctx, mine, kind, C.byref(c), C.byref(plain), C.byref(s)) == saved
+                if saved == 0:
+                    assert Path(mine.decode()).read_bytes() == Path(path.decode()).read_bytes()
+                else:
+                    assert not Path(mine.decode()).exists()
                 f, st, f2, st2 = (capi.MatmulStrategy() for _ in range(4))
                 theirs = ref.rk_npu_matmul_autotune_cache_load(fake, path, kind, C.byref(c), C.byref(f2), C.byref(st2)) if saved == 0 else saved
                 if saved != 0:      # the writer refuses the recipe: the same file written by hand must be a miss here too
