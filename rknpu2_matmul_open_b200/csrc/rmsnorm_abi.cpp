@@ -88,17 +88,22 @@ extern "C" int rk_npu_mem_alloc(rk_npu_iommu_domain* domain, uint64_t size, uint
     return RK_NPU_OK;
 }
 
-// src/rk_npu_core.cpp:318-331
+// A view is the base struct narrowed to [offset, offset + size): both addresses and the offset from the base object
+// move by `offset`, the capacity still names the base object, and of the state bits only the ones that describe the
+// mapping survive -- a view owns nothing.  Semantics of src/rk_npu_core.cpp:318-331.
 extern "C" int rk_npu_mem_view(const rk_npu_mem* base, uint64_t offset, uint64_t size, rk_npu_mem* out_view)
 {
-    if (!base || !out_view || size == 0 || !base->capacity || offset > base->size || size > base->size - offset)
-        return RK_NPU_ERR_PARAM;
-    *out_view = *base;
-    out_view->flags = (base->flags & (RK_NPU_MEM_F_IMPORTED | RK_NPU_MEM_F_MAPPED | RK_NPU_MEM_F_CACHEABLE)) | RK_NPU_MEM_F_VIEW;
-    out_view->dma_addr = base->dma_addr + offset;
-    out_view->vaddr = base->vaddr ? static_cast<void*>(static_cast<uint8_t*>(base->vaddr) + offset) : nullptr;
-    out_view->offset = base->offset + offset;
-    out_view->size = size;
+    const bool usable = base && out_view && base->capacity != 0;
+    const bool inside = usable && size != 0 && offset <= base->size && size <= base->size - offset;
+    if (!inside) return RK_NPU_ERR_PARAM;
+    constexpr uint32_t inherited = RK_NPU_MEM_F_IMPORTED | RK_NPU_MEM_F_MAPPED | RK_NPU_MEM_F_CACHEABLE;
+    rk_npu_mem view = *base;
+    view.flags = (base->flags & inherited) | RK_NPU_MEM_F_VIEW;
+    view.size = size;
+    view.offset += offset;
+    view.dma_addr += offset;
+    if (view.vaddr) view.vaddr = static_cast<uint8_t*>(view.vaddr) + offset;
+    *out_view = view;
     return RK_NPU_OK;
 }
 
@@ -232,23 +237,27 @@ int launch(rk_npu_add_rmsnorm_f16_plan* plan, int rows, int row_major, uint64_t 
 }
 } // namespace
 
-// src/rk_npu_add_rmsnorm_f16.cpp:270-304: the same checks in the same order, then one launch and a wait
+// The original's blocking call (src/rk_npu_add_rmsnorm_f16.cpp:270-304) answers, in this order: missing arguments or a
+// plan of another context (PARAM); per tensor in argument order, a buffer of another context or too small (NOMEM) before
+// one of another domain (DOMAIN); an output lying on an input or on the other output (PARAM); a plan in use (BUSY).
+// The two inputs may be the same tensor.  Here a view at an address the kernel's 16-byte chunks cannot start at is PARAM too.
 extern "C" int rk_npu_add_rmsnorm_f16_run(rk_npu_ctx* ctx, rk_npu_add_rmsnorm_f16_plan* plan, const rk_npu_mem* x,
                                           const rk_npu_mem* residual, rk_npu_mem* residual_out, rk_npu_mem* norm_out)
 {
-    if (!ctx || !plan || ctx != plan->ctx || !x || !residual || !residual_out || !norm_out) return RK_NPU_ERR_PARAM;
-    const uint64_t bytes = uint64_t(plan->cfg.M) * uint64_t(plan->cfg.D) * 2;
-    const rk_npu_mem* all[] = {x, residual, residual_out, norm_out};
-    for (const rk_npu_mem* mem : all) {
-        if (mem->ctx_id != ctx->id || mem->size < bytes) return RK_NPU_ERR_NOMEM;
-        if (mem->iommu_domain_id != plan->domain->id) return RK_NPU_ERR_DOMAIN;
+    const rk_npu_mem* const tensors[4] = {x, residual, residual_out, norm_out};      // inputs first, outputs last
+    if (!ctx || !plan || plan->ctx != ctx) return RK_NPU_ERR_PARAM;
+    for (const rk_npu_mem* t : tensors)
+        if (!t) return RK_NPU_ERR_PARAM;
+    const uint64_t bytes = uint64_t(plan->cfg.M) * uint64_t(plan->cfg.D) * sizeof(uint16_t);
+    for (const rk_npu_mem* t : tensors) {
+        if (t->ctx_id != ctx->id || t->size < bytes) return RK_NPU_ERR_NOMEM;
+        if (t->iommu_domain_id != plan->domain->id) return RK_NPU_ERR_DOMAIN;
     }
-    if (overlaps(x->dma_addr, residual_out->dma_addr, bytes) || overlaps(x->dma_addr, norm_out->dma_addr, bytes) ||
-        overlaps(residual->dma_addr, residual_out->dma_addr, bytes) || overlaps(residual->dma_addr, norm_out->dma_addr, bytes) ||
-        overlaps(residual_out->dma_addr, norm_out->dma_addr, bytes))
-        return RK_NPU_ERR_PARAM;
-    for (const rk_npu_mem* mem : all)
-        if (mem->dma_addr % 16) return RK_NPU_ERR_PARAM;      // a view at an odd offset: the kernel moves 16-byte chunks
+    for (int out = 2; out < 4; ++out)              // each output against everything in front of it
+        for (int other = 0; other < out; ++other)
+            if (overlaps(tensors[other]->dma_addr, tensors[out]->dma_addr, bytes)) return RK_NPU_ERR_PARAM;
+    for (const rk_npu_mem* t : tensors)
+        if (t->dma_addr % 16) return RK_NPU_ERR_PARAM;
     if (plan->busy.test_and_set(std::memory_order_acquire)) return RK_NPU_ERR_BUSY;
     int rc = cudaSetDevice(ctx->device) == cudaSuccess ? RK_NPU_OK : RK_NPU_ERR_SUBMIT;
     if (rc == RK_NPU_OK)
