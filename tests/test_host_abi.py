@@ -597,6 +597,23 @@ def test_public_headers_are_valid_c(tmp_path):
     assert out.returncode == 0, out.stderr
 
 
+def test_the_original_example_programs_link_unchanged(lib, tmp_path):
+    # examples/tune_w4a8.cpp (the search tuner's command-line front end), examples/bench_w4a8.cpp and examples/bench_i4.cpp of
+    # the original use only the public headers of this path (bench_w4a8 also its header-only binary16 helpers): compiled
+    # from where they lie and linked against this library instead of librk_npu_matmul.so, every symbol resolves
+    import shutil
+    import subprocess
+    default = re.search(r"^REF\s*\?=\s*(\S+)", (ROOT / "oracle" / "Makefile").read_text(), flags=re.M).group(1)
+    tree = Path(os.environ.get("REF", default))
+    gxx = shutil.which("g++")
+    if not gxx or not (tree / "examples" / "tune_w4a8.cpp").exists():
+        pytest.skip("needs g++ and the original tree")
+    for name in ("tune_w4a8", "bench_w4a8", "bench_i4"):
+        out = subprocess.run([gxx, "-O1", "-std=c++17", f"-I{tree / 'include'}", "-o", str(tmp_path / name), str(tree / "examples" / f"{name}.cpp"),
+                              f"-L{capi.LIB_PATH.parent}", "-lrk_npu_matmul_b200", "-Wl,--no-undefined"], capture_output=True, text=True)
+        assert out.returncode == 0, f"{name}: {out.stderr[-2000:]}"
+
+
 # ---------------------------------------------------------------- exact int4 operator: pure host functions
 def test_i4_memory_query_and_tile_packing_match_the_reference(lib):
     from oracle.harness import REF_SO, Reference
