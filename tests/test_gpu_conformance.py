@@ -23,6 +23,10 @@ tests/test_add_rmsnorm_f16.cpp (residual add + RMSNorm on caller-owned buffers i
 -D__fp16=_Float16, the x86 spelling of the same type) runs for its two batch sizes, 1 and 128 rows of 4096: the sums bit
 for bit, the normalised rows within its 0.04 / cosine 0.99999 bars (this library meets them with error 0).
 
+examples/tune_w4a8.cpp, the original's command-line front end of its search tuner, is compiled the same way: a first run
+searches (this library's kernel families are the candidates) and writes the cache file, a second run is a hit and
+prints the same two strategies.
+
 The binaries exist only where the reference tree was present at build time; otherwise the tests skip.
 """
 import subprocess
@@ -48,3 +52,20 @@ def test_reference_program_passes_against_this_library(program, args):
     run = subprocess.run([str(exe), *args], capture_output=True, text=True, timeout=600)
     assert run.returncode == 0, f"{program} failed:\n{run.stdout}\n{run.stderr}"
     assert "PASS" in run.stdout or "checks passed" in run.stdout
+
+
+def test_reference_tuner_front_end_searches_then_hits_its_cache(tmp_path):
+    exe = BIN / "conformance_example_tune_w4a8"
+    if not exe.exists():
+        pytest.skip(f"{exe} not built (needs the reference tree at build time)")
+    cache = tmp_path / "tuned.cache"
+    args = [str(exe), "--shape", "8", "1024", "768", "--f16", "--cache", str(cache), "--loops", "4", "--repeats", "2"]
+    first = subprocess.run(args, capture_output=True, text=True, timeout=300)
+    assert first.returncode == 0, f"{first.stdout}\n{first.stderr}"
+    assert "CACHE miss" in first.stdout and "FASTEST" in first.stdout and "STABLE" in first.stdout
+    assert cache.exists() and cache.stat().st_size > 0
+    second = subprocess.run(args, capture_output=True, text=True, timeout=300)
+    assert second.returncode == 0, f"{second.stdout}\n{second.stderr}"
+    assert "CACHE hit" in second.stdout
+    pick = lambda text: [line for line in text.splitlines() if line.startswith(("FASTEST", "STABLE"))]
+    assert pick(first.stdout) == pick(second.stdout) and len(pick(first.stdout)) == 2
